@@ -1,0 +1,104 @@
+"""Engine integration on the tiny hybrid config (CPU, fp32): the served tokens
+must equal an unfused full-sequence fp32 forward, however the work is chunked,
+batched, cached or speculated."""
+import torch
+
+from helpers import autograd_forward, make_engine, rand_prompts
+from tilerl_b200.config import tiny, tiny_hybrid
+from tilerl_b200.engine import EngineOverloaded, SamplingParams, StepLimits
+from tilerl_b200.kv import PrefixStore
+
+
+def dense_greedy(model, prompt, n):
+    seq = list(prompt)
+    with torch.no_grad():
+        for _ in range(n):
+            lg = autograd_forward(model, torch.tensor([seq]), {})
+            seq.append(int(lg[0, -1].argmax()))
+    return seq[len(prompt):]
+
+
+def test_config1_serve_matches_unfused_fp32():
+    cfg = tiny_hybrid()
+    eng = make_engine(cfg)
+    prompts = rand_prompts(cfg, 2, 32)
+    res = eng.generate(prompts, SamplingParams(max_tokens=16))
+    for p, r in zip(prompts, res):
+        assert r.tokens == dense_greedy(eng.model, p, 16)
+        assert r.finish_reason == "length" and r.prompt_tokens == 32
+
+
+def test_chunked_prefill_equals_one_shot_and_batch_equals_single():
+    cfg = tiny_hybrid()
+    prompts = rand_prompts(cfg, 3, 45, seed=5)
+    one = make_engine(cfg, limits=StepLimits(max_batched_tokens=512))
+    ref_out = [one.generate([p], SamplingParams(max_tokens=6))[0].tokens for p in prompts]
+    chunked = make_engine(cfg, limits=StepLimits(max_batched_tokens=16, prefill_align=8))
+    got = chunked.generate(prompts, SamplingParams(max_tokens=6))
+    assert [r.tokens for r in got] == ref_out
+    assert chunked.counters["mixed_ticks"] + chunked.counters["prefill_ticks"] > 3
+
+
+def test_prefix_hit_equals_cold():
+    cfg = tiny_hybrid()
+    eng = make_engine(cfg)
+    eng.prefix = PrefixStore(eng.kv)
+    p = rand_prompts(cfg, 1, 40, seed=9)[0]
+    cold = eng.generate([p], SamplingParams(max_tokens=5))[0]
+    warm = eng.generate([p], SamplingParams(max_tokens=5))[0]
+    assert warm.tokens == cold.tokens
+    assert eng.prefix.hits == 1 and warm.cached_tokens == 32
+    longer = p[:36] + [7, 8, 9]
+    fresh = make_engine(cfg).generate([longer], SamplingParams(max_tokens=5))[0]
+    assert eng.generate([longer], SamplingParams(max_tokens=5))[0].tokens == fresh.tokens
+    eng.invalidate_weights()
+    assert len(eng.prefix) == 0 and eng.kv.used_blocks == 0
+
+
+def test_seeded_sampling_is_reproducible_and_logprobs_returned():
+    cfg = tiny()
+    eng = make_engine(cfg)
+    p = rand_prompts(cfg, 1, 12)[0]
+    sp = SamplingParams(max_tokens=8, temperature=1.0, top_p=0.9, seed=11, logprobs=True)
+    a = eng.generate([p], sp)[0]
+    b = eng.generate([p], sp)[0]
+    assert a.tokens == b.tokens and len(a.logprobs) == 8 and all(l <= 0 for l in a.logprobs)
+    c = eng.generate([p], SamplingParams(max_tokens=8, temperature=1.0, top_p=0.9, seed=12))[0]
+    assert c.tokens != a.tokens
+
+
+def test_stop_ids_cancel_overload_and_pool_release():
+    cfg = tiny()
+    eng = make_engine(cfg, limits=StepLimits(max_inflight=2))
+    p = rand_prompts(cfg, 1, 10)[0]
+    first = eng.generate([p], SamplingParams(max_tokens=4))[0].tokens
+    r = eng.generate([p], SamplingParams(max_tokens=10, stop_ids=(first[1],)))[0]
+    assert r.finish_reason == "stop" and r.tokens == first[:first.index(first[1]) + 1]
+    a = eng.submit(p, SamplingParams(max_tokens=50))
+    b = eng.submit(p, SamplingParams(max_tokens=50))
+    try:
+        eng.submit(p)
+        assert False, "expected overload"
+    except EngineOverloaded:
+        pass
+    eng.step()
+    assert eng.cancel(a) and eng.take(a).finish_reason == "cancelled"
+    while eng.poll(b)["state"] != "done":
+        eng.step()
+    assert eng.kv.used_blocks == 0 and eng.states.free_slots == eng.states.num_slots - 1
+
+
+def test_daemon_loop_and_peek():
+    import time
+    cfg = tiny()
+    eng = make_engine(cfg)
+    eng.run(batching_window_s=0.0)
+    rid = eng.submit(rand_prompts(cfg, 1, 8)[0], SamplingParams(max_tokens=5))
+    for _ in range(400):
+        toks, done = eng.peek(rid)
+        if done:
+            break
+        time.sleep(0.01)
+    eng.stop()
+    assert done and len(eng.take(rid).tokens) == 5
+    assert eng.liveness()["last_progress_age_s"] == 0.0

@@ -1,0 +1,133 @@
+"""Hand-written tape vs torch.autograd, optimizers, and one GRPO step (config 1)."""
+import torch
+
+from helpers import autograd_forward, make_engine, rand_prompts
+from tilerl_b200 import rl
+from tilerl_b200 import tape as T
+from tilerl_b200.config import tiny, tiny_hybrid
+from tilerl_b200.models.hybrid import HybridModel
+from tilerl_b200.optim import AdamW, Adafactor, ISO, clip_grad_norm, cosine_warmup
+from tilerl_b200.ops import ref
+
+
+def _autograd_grads(model, ids, targets, w):
+    tr = model.trainable()
+    leaves = {k: v.detach().clone().requires_grad_(True) for k, v in tr.items()}
+    lg = autograd_forward(model, ids, leaves)
+    lp = torch.log_softmax(lg, -1).gather(-1, targets[..., None]).squeeze(-1)
+    loss = -(w * lp).sum()
+    gs = torch.autograd.grad(loss, list(leaves.values()), allow_unused=True)
+    return float(loss), dict(zip(leaves, gs))
+
+
+def _check(model, ckpt=False):
+    torch.manual_seed(0)
+    cfg = model.cfg
+    ids = torch.randint(0, cfg.vocab, (2, 12))
+    targets = torch.roll(ids, -1, 1)
+    w = torch.rand(2, 12) / 24
+    tr = model.trainable()
+    loss, grads, _ = rl.forward_backward(model, ids, targets, lambda lg: w, trainable=tr,
+                                         checkpoint_layers=ckpt)
+    want_loss, want = _autograd_grads(model, ids, targets, w)
+    assert abs(loss - want_loss) < 1e-4 * max(1, abs(want_loss))
+    assert set(grads) == {k for k, g in want.items() if g is not None}
+    for k, g in grads.items():
+        assert torch.allclose(g, want[k], rtol=2e-3, atol=2e-6), k
+
+
+def test_tape_full_param_grads_match_autograd():
+    _check(HybridModel.build_random(tiny(), seed=2, keep_master=True))
+
+
+def test_tape_checkpointed_grads_match_autograd():
+    _check(HybridModel.build_random(tiny(), seed=2, keep_master=True), ckpt=True)
+
+
+def test_tape_lora_on_frozen_nvfp4_base():
+    m = HybridModel.build_random(tiny_hybrid(), seed=4)
+    keys = m.add_lora(rank=4, alpha=8.0)
+    for k in keys:
+        if k.endswith("lora_b"):
+            m.params[k].normal_(0, 0.02)
+    assert set(m.trainable()) == set(keys)
+    _check(m)
+
+
+def test_streaming_on_grad_sees_every_leaf_once():
+    m = HybridModel.build_random(tiny(), seed=2, keep_master=True)
+    tr = m.trainable()
+    seen = []
+    name_of = {id(v): k for k, v in tr.items()}
+    ids = torch.randint(0, 320, (1, 6))
+    rl.forward_backward(m, ids, torch.roll(ids, -1, 1), lambda lg: torch.full((1, 6), 1 / 6),
+                        trainable=tr, on_grad=lambda t, g: seen.append(name_of[id(t)]))
+    assert sorted(seen) == sorted(tr) and len(set(seen)) == len(seen)
+    assert seen.index("master.L1.down") < seen.index("master.L0.qkv")  # reverse layer order
+
+
+def test_group_advantages():
+    a = rl.group_advantages([1, 0, 0, 1, 5, 5, 5, 5], 4)
+    assert torch.allclose(a[:4], torch.tensor([1., -1., -1., 1.]), atol=1e-4)
+    assert a[4:].abs().sum() == 0  # tied group: no signal
+    b = rl.group_advantages([1, 0, 9, 9], 4, live=[True, True, False, False])
+    assert b[2] == 0 and b[3] == 0 and b[0] > 0 > b[1]
+
+
+def test_optimizers_write_in_place_and_descend():
+    torch.manual_seed(0)
+    for cls in (AdamW, Adafactor, ISO):
+        p = {"w": torch.randn(8, 6), "b": torch.randn(6)}
+        ptr = {k: v.data_ptr() for k, v in p.items()}
+        opt = cls(p, lr=0.05)
+        tgt = {"w": torch.zeros(8, 6), "b": torch.zeros(6)}
+        l0 = sum((p[k] - tgt[k]).pow(2).sum() for k in p)
+        for _ in range(60):
+            opt.step({k: 2 * (p[k] - tgt[k]) for k in p})
+        l1 = sum((p[k] - tgt[k]).pow(2).sum() for k in p)
+        assert l1 < 0.5 * l0, cls.__name__
+        assert all(p[k].data_ptr() == ptr[k] for k in p)
+
+
+def test_clip_and_schedule():
+    g = {"a": torch.ones(4) * 3, "b": torch.ones(4) * 4}
+    n = clip_grad_norm(g, 1.0)
+    assert abs(n - 10.0) < 1e-5
+    assert abs(sum(v.pow(2).sum() for v in g.values()).sqrt() - 1.0) < 1e-4
+    assert cosine_warmup(0, 100, 10, 1.0) == 0.1 and abs(cosine_warmup(100, 100, 10, 1.0) - 0.1) < 1e-6
+
+
+def test_config1_grpo_step_grads_match_autograd_and_policy_moves():
+    """2 prompts x G=4, reward = fraction of even ids, clip 0.2, lr 1e-5."""
+    cfg = tiny_hybrid()
+    eng = make_engine(cfg, keep_master=True)
+    model = eng.model
+    prompts = rand_prompts(cfg, 2, 16)
+    reward = lambda p, c: sum(1 for t in c if t % 2 == 0) / max(1, len(c))
+    opt = AdamW(model.trainable(), lr=1e-5)
+    # gradient check of the objective on a hand-made batch
+    ids = rl.pad_batch([p + [2, 4, 5, 7] for p in prompts])
+    adv = torch.tensor([1.0, -0.5])
+    st = rl.policy_step(model, ids, [16, 16], [20, 20], adv, None, return_grads=True, max_norm=0.0)
+    mask = rl._scored_mask(ids, [16, 16], [20, 20])
+    w = adv[:, None] * mask / mask.sum()
+    _, want = _autograd_grads(model, ids, torch.roll(ids, -1, 1), w)
+    for k, g in st["grads"].items():
+        assert torch.allclose(g, want[k], rtol=2e-3, atol=2e-6), k
+    before = {k: v.clone() for k, v in model.trainable().items()}
+    ms = list(rl.grpo_loop(eng, model, prompts, reward, opt, steps=1, group=4, prompts_per_step=2,
+                           max_tokens=8, post_step=lambda m: m.requantize_()))
+    assert len(ms) == 1 and ms[0]["completion_tokens"] == 64 and 0 <= ms[0]["reward"] <= 1
+    moved = sum(float((v - before[k]).abs().sum()) for k, v in model.trainable().items())
+    assert (moved > 0) == (ms[0]["tied_groups"] < 2)
+    assert eng.kv.used_blocks == 0
+
+
+def test_clipped_ratio_zeroes_gradient():
+    cfg = tiny()
+    m = HybridModel.build_random(cfg, seed=2, keep_master=True)
+    ids = rl.pad_batch([[1, 2, 3, 4, 5, 6]])
+    old = torch.full((1, 6), -50.0)  # rho huge, A > 0 -> every token clipped
+    st = rl.policy_step(m, ids, [3], [6], torch.tensor([1.0]), None, old_logprobs=old,
+                        return_grads=True, max_norm=0.0)
+    assert st["clipped"] == 3 and all(float(g.abs().max()) == 0 for g in st["grads"].values())

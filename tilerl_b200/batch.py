@@ -1,0 +1,76 @@
+"""Per-forward batch descriptor (flat-token layout).
+
+A tick's tokens from all scheduled sequences are concatenated into ``[T]``.
+Decode ticks have one token per sequence, speculative-verify ticks ``W`` per
+sequence, prefill chunks any number.  Every tensor here is an int32 device
+tensor so the same object can be the static input block of a CUDA graph.
+
+Parity: reference ``src/tilerl/kv_cache.py:954`` (``BatchKv``); the reference pads
+rows to a common width and masks with ``seq_q_lens`` -- here rows are ragged.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import torch
+
+from .ops.ref import KV_BLOCK
+
+
+@dataclass
+class Batch:
+    token_ids: torch.Tensor      # [T] int32
+    positions: torch.Tensor      # [T] int32 absolute position of each token
+    seq_ids: torch.Tensor        # [T] int32 row of the per-sequence arrays
+    slot_mapping: torch.Tensor   # [T] int32 physical KV row (block*16+off), -1 = no write
+    q_start: torch.Tensor        # [B] int32 first token index of each sequence
+    q_len: torch.Tensor          # [B] int32 tokens of each sequence in this tick
+    kv_len: torch.Tensor         # [B] int32 KV length after this tick
+    state_slots: torch.Tensor    # [B] int32 GDN state slot of each sequence
+    block_table: torch.Tensor    # [B, max_blocks] int32
+    last_idx: torch.Tensor       # [B] int32 index in [T] of each sequence's last token
+    n_seqs: int = 0
+    n_tokens: int = 0
+    max_q_len: int = 1
+    keep_steps: int = 0          # >0: verify tick, keep the GDN state after each token
+    sparse: Optional[object] = None   # per-layer selected page lists (sparse KV)
+    host_q_len: List[int] = field(default_factory=list)
+    host_kv_len: List[int] = field(default_factory=list)
+    keep_rows: List[bool] = field(default_factory=list)   # per sequence: store per-token GDN states
+    keep_flags: Optional[torch.Tensor] = None             # [B] int32 device copy of keep_rows
+
+    @staticmethod
+    def build(seqs: Sequence[dict], device, max_blocks: Optional[int] = None,
+              keep_steps: int = 0, pad_to: Optional[int] = None) -> "Batch":
+        """``seqs``: dicts with ``tokens`` (ids of this tick), ``start`` (position of
+        the first), ``blocks`` (physical block ids), ``slot`` (GDN state slot)."""
+        ids, pos, sid, smap, qs, ql, kl, slots, last, keep = [], [], [], [], [], [], [], [], [], []
+        mb = max_blocks or max(1, max(len(s["blocks"]) for s in seqs))
+        table = torch.zeros(len(seqs), mb, dtype=torch.int32)
+        t = 0
+        for r, s in enumerate(seqs):
+            toks, start, blocks = list(s["tokens"]), int(s["start"]), s["blocks"]
+            qs.append(t)
+            ql.append(len(toks))
+            for j, tok in enumerate(toks):
+                p = start + j
+                ids.append(tok)
+                pos.append(p)
+                sid.append(r)
+                smap.append(blocks[p // KV_BLOCK] * KV_BLOCK + p % KV_BLOCK)
+            t += len(toks)
+            last.append(t - 1)
+            kl.append(start + len(toks))
+            slots.append(int(s["slot"]))
+            keep.append(bool(s.get("keep", False)) and keep_steps > 0)
+            if blocks:
+                table[r, :len(blocks)] = torch.tensor(blocks, dtype=torch.int32)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
+        return Batch(
+            token_ids=i32(ids), positions=i32(pos), seq_ids=i32(sid), slot_mapping=i32(smap),
+            q_start=i32(qs), q_len=i32(ql), kv_len=i32(kl), state_slots=i32(slots),
+            block_table=table.to(device), last_idx=i32(last), n_seqs=len(seqs), n_tokens=t,
+            max_q_len=max(ql), keep_steps=keep_steps, host_q_len=ql, host_kv_len=kl,
+            keep_rows=keep, keep_flags=i32([int(k) for k in keep]),
+        )

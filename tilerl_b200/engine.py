@@ -1,0 +1,536 @@
+"""Continuous-batching engine: ``submit`` / ``poll`` / ``step``.
+
+One model forward per tick.  A tick mixes, in one flat token batch, every
+sequence that is decoding (one token each, or a width-W speculative chain) with
+as many prefill-chunk tokens as the token budget allows.  Admission is FIFO and
+happens only when a GDN state slot and enough KV blocks are free; a prefix hit
+adopts refcounted blocks plus the GDN snapshot stored with them.  The engine can
+be driven tick by tick from tests and from the GRPO loop, or run as a daemon
+thread behind the HTTP server.
+
+Decode-only ticks go through a CUDA-graph runner when one is attached
+(:mod:`tilerl_b200.graph`); everything else is an eager forward.
+
+Parity: reference ``src/tilerl/engine.py`` -- ``SamplingParams:517``,
+``StepLimits:568``, ``Engine.submit:1097``, ``poll:1195``, ``peek:1229``,
+``take:1247``, ``step:1256``, ``_admit:1333``, ``_build_plan:1570``,
+``_verify:2625``, ``_commit:2705``, ``cancel:2868``, ``_loop:2895``,
+``stats:1711``, liveness ``:1688``.
+"""
+from __future__ import annotations
+
+import os
+import threading
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Callable, Deque, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .batch import Batch
+from .kv import GdnStatePool, NoPrefixStore, PagedKvPool, PoolExhausted
+from .ops import ref
+from .ops.ref import KV_BLOCK
+
+
+class EngineOverloaded(RuntimeError):
+    """Raised by ``submit`` when ``max_inflight`` requests are already queued."""
+
+
+class RequestFailed(RuntimeError):
+    pass
+
+
+class FatalDeviceError(RuntimeError):
+    """The device is gone (OOM / sticky CUDA error): the process should exit so a
+    supervisor restarts it."""
+
+
+FATAL_EXIT_CODE = 11
+
+
+def fatal_device_exit(msg: str) -> None:  # pragma: no cover - terminates the process
+    print(f"FATAL_DEVICE: {msg}", flush=True)
+    os._exit(FATAL_EXIT_CODE)
+
+
+@dataclass
+class SamplingParams:
+    max_tokens: int = 16
+    temperature: float = 0.0
+    top_p: float = 1.0
+    top_k: int = 0
+    seed: int = 0
+    stop_ids: Tuple[int, ...] = ()
+    stop_texts: Tuple[str, ...] = ()
+    logprobs: bool = False
+    allowed_ids: Optional[Tuple[int, ...]] = None
+    max_think_tokens: Optional[int] = None
+    ignore_eos: bool = False
+
+    @property
+    def untruncated(self) -> bool:
+        """True when samples come from the model's full distribution (on-policy RL)."""
+        return self.temperature == 1.0 and self.top_p >= 1.0 and self.top_k == 0 \
+            and self.allowed_ids is None
+
+
+@dataclass
+class StepLimits:
+    max_batch: int = 64              # sequences per tick
+    max_batched_tokens: int = 512    # tokens per tick (prefill chunk budget)
+    max_total_tokens: int = 1 << 30  # KV tokens across running sequences
+    max_inflight: int = 1024         # waiting + running requests
+    prefill_align: int = 64          # prefill chunk widths are multiples of this
+
+
+WAITING, PREFILL, DECODE, DONE = "waiting", "prefill", "decode", "done"
+
+
+@dataclass
+class _Req:
+    rid: int
+    prompt: List[int]
+    params: SamplingParams
+    state: str = WAITING
+    out: List[int] = field(default_factory=list)
+    logprobs: List[float] = field(default_factory=list)
+    n_computed: int = 0
+    blocks: List[int] = field(default_factory=list)
+    slot: int = -1
+    finish_reason: Optional[str] = None
+    error: Optional[str] = None
+    drafts: List[int] = field(default_factory=list)
+    think_tokens: int = 0
+    in_think: bool = False
+    t_submit: float = 0.0
+    t_first: float = 0.0
+    t_done: float = 0.0
+    prefix_tokens: int = 0
+    published: bool = False
+
+    @property
+    def toks(self) -> List[int]:
+        return self.prompt + self.out
+
+
+@dataclass
+class Result:
+    rid: int
+    tokens: List[int]
+    logprobs: List[float]
+    finish_reason: str
+    prompt_tokens: int
+    error: Optional[str] = None
+    ttft_s: float = 0.0
+    total_s: float = 0.0
+    cached_tokens: int = 0
+
+
+class Engine:
+    def __init__(self, model, ops, kv_pool: PagedKvPool, state_pool: GdnStatePool, *,
+                 limits: Optional[StepLimits] = None, prefix_store=None, eos_id: Optional[int] = None,
+                 detokenize: Optional[Callable[[Sequence[int]], str]] = None,
+                 think_ids: Optional[Tuple[int, int]] = None, drafter=None, spec_width: int = 0,
+                 graph_runner=None, sparse=None):
+        self.model, self.ops = model, ops
+        self.kv, self.states = kv_pool, state_pool
+        self.limits = limits or StepLimits()
+        self.prefix = prefix_store if prefix_store is not None else NoPrefixStore()
+        self.eos_id = eos_id
+        self.detok = detokenize
+        self.think_ids = think_ids
+        self.drafter = drafter
+        self.spec_width = spec_width if drafter is not None else 0
+        self.graph = graph_runner
+        self.sparse = sparse
+        self.device = kv_pool.k.device
+        self._lock = threading.RLock()
+        self._next = 1
+        self._waiting: Deque[_Req] = deque()
+        self._running: List[_Req] = []
+        self._reqs: Dict[int, _Req] = {}
+        self._thread: Optional[threading.Thread] = None
+        self._stop = threading.Event()
+        self._wake = threading.Event()
+        self._last_progress = time.monotonic()
+        self._degraded: Optional[str] = None
+        self.counters = dict(ticks=0, prefill_ticks=0, decode_ticks=0, mixed_ticks=0,
+                             graph_ticks=0, tokens_generated=0, prompt_tokens=0,
+                             spec_drafted=0, spec_accepted=0, cancelled=0, failed=0,
+                             finished=0, preempted=0)
+        self.timing = os.environ.get("TRL_STEP_TIMING") == "1"
+        self.last_tick_ms: Dict[str, float] = {}
+
+    # ---- public API -------------------------------------------------------------
+    def submit(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
+        params = params or SamplingParams()
+        if len(prompt) == 0:
+            raise ValueError("empty prompt")
+        if len(prompt) + params.max_tokens > self.model.cfg.max_ctx:
+            raise ValueError("prompt + max_tokens exceeds the model context")
+        with self._lock:
+            if len(self._waiting) + len(self._running) >= self.limits.max_inflight:
+                raise EngineOverloaded(f"{self.limits.max_inflight} requests already in flight")
+            r = _Req(self._next, [int(t) for t in prompt], params, t_submit=time.monotonic())
+            self._next += 1
+            self._reqs[r.rid] = r
+            self._waiting.append(r)
+        self._wake.set()
+        return r.rid
+
+    def poll(self, rid: int) -> Dict[str, object]:
+        with self._lock:
+            r = self._reqs[rid]
+            return dict(state=r.state, n_out=len(r.out), finish_reason=r.finish_reason)
+
+    def peek(self, rid: int) -> Tuple[List[int], bool]:
+        """Lock-free snapshot of the tokens generated so far (list slicing is atomic
+        under the GIL); used by the streaming endpoints."""
+        r = self._reqs.get(rid)
+        if r is None:
+            return [], True
+        return r.out[:], r.state == DONE
+
+    def take(self, rid: int) -> Optional[Result]:
+        with self._lock:
+            r = self._reqs.get(rid)
+            if r is None or r.state != DONE:
+                return None
+            del self._reqs[rid]
+            return Result(r.rid, r.out[:], r.logprobs[:], r.finish_reason or "stop", len(r.prompt),
+                          r.error, max(0.0, r.t_first - r.t_submit), max(0.0, r.t_done - r.t_submit),
+                          r.prefix_tokens)
+
+    def cancel(self, rid: int) -> bool:
+        with self._lock:
+            r = self._reqs.get(rid)
+            if r is None or r.state == DONE:
+                return False
+            if r in self._waiting:
+                self._waiting.remove(r)
+            if r in self._running:
+                self._running.remove(r)
+            self._finish(r, "cancelled")
+            self.counters["cancelled"] += 1
+            return True
+
+    def has_work(self) -> bool:
+        return bool(self._waiting or self._running)
+
+    def generate(self, prompts: Sequence[Sequence[int]], params=None) -> List[Result]:
+        """Convenience: submit, drain, return results in order."""
+        plist = params if isinstance(params, (list, tuple)) else [params] * len(prompts)
+        rids = [self.submit(p, sp) for p, sp in zip(prompts, plist)]
+        while any(self._reqs[r].state != DONE for r in rids):
+            if not self.step():
+                raise RuntimeError("engine stalled with unfinished requests")
+        return [self.take(r) for r in rids]
+
+    def invalidate_weights(self) -> None:
+        """Weights changed in place: cached KV/prefix content is stale, captured
+        graphs stay valid (addresses are unchanged)."""
+        with self._lock:
+            self.prefix.clear()
+            if self.drafter is not None and hasattr(self.drafter, "invalidate"):
+                self.drafter.invalidate()
+
+    def precapture(self, batches: Sequence[int] = (1,)) -> None:
+        if self.graph is not None:
+            self.graph.precapture(batches)
+
+    # ---- liveness / stats ---------------------------------------------------------------
+    def liveness(self) -> Dict[str, object]:
+        idle = not self.has_work()
+        return dict(last_progress_age_s=0.0 if idle else time.monotonic() - self._last_progress,
+                    degraded=self._degraded, running=len(self._running), waiting=len(self._waiting))
+
+    def stats(self) -> Dict[str, object]:
+        return dict(
+            waiting=len(self._waiting), running=len(self._running),
+            blocks_used=self.kv.used_blocks, blocks_free=self.kv.free_blocks,
+            slots_free=self.states.free_slots,
+            prefix_entries=len(self.prefix), prefix_hits=self.prefix.hits,
+            prefix_misses=self.prefix.misses, prefix_evictions=self.prefix.evictions,
+            **self.counters,
+        )
+
+    # ---- daemon loop ----------------------------------------------------------------------
+    def run(self, batching_window_s: float = 0.010) -> None:
+        if self._thread is not None:
+            return
+        self._stop.clear()
+
+        def loop():
+            while not self._stop.is_set():
+                if not self.has_work():
+                    self._wake.wait(0.05)
+                    self._wake.clear()
+                    continue
+                if not self._running and batching_window_s > 0:
+                    time.sleep(batching_window_s)  # let concurrent submits coalesce
+                try:
+                    self.step()
+                except FatalDeviceError as e:  # pragma: no cover
+                    self._degraded = str(e)
+                    fatal_device_exit(str(e))
+                except Exception as e:  # noqa: BLE001 - isolate failures to running rows
+                    self._fail_running(repr(e))
+
+        self._thread = threading.Thread(target=loop, name="engine", daemon=True)
+        self._thread.start()
+
+    def stop(self) -> None:
+        self._stop.set()
+        self._wake.set()
+        if self._thread is not None:
+            self._thread.join(timeout=5)
+            self._thread = None
+
+    def _fail_running(self, msg: str) -> None:
+        with self._lock:
+            for r in list(self._running):
+                self._running.remove(r)
+                r.error = msg
+                self._finish(r, "error")
+                self.counters["failed"] += 1
+
+    # ---- one tick ----------------------------------------------------------------------------
+    def step(self) -> bool:
+        with self._lock:
+            t0 = time.perf_counter()
+            self._admit()
+            plan = self._build_plan()
+            if not plan:
+                return False
+            t1 = time.perf_counter()
+            self._run(plan)
+            self.counters["ticks"] += 1
+            self._last_progress = time.monotonic()
+            if self.timing:
+                self.last_tick_ms = dict(prep=(t1 - t0) * 1e3, run=(time.perf_counter() - t1) * 1e3)
+            return True
+
+    def _blocks_needed(self, n_tokens: int) -> int:
+        return (n_tokens + KV_BLOCK - 1) // KV_BLOCK
+
+    def _admit(self) -> None:
+        while self._waiting and len(self._running) < self.limits.max_batch:
+            r = self._waiting[0]
+            spec_pad = self.spec_width
+            need_tokens = len(r.prompt) + 1 + spec_pad
+            hit = self.prefix.lookup(r.prompt)
+            have = len(hit.blocks) if hit else 0
+            need = self._blocks_needed(need_tokens) - have
+            if self.kv.free_blocks < need:
+                self.prefix.evict_until_free(need)
+            if self.kv.free_blocks < need or self.states.free_slots < 1:
+                if hit:
+                    for b in hit.blocks:
+                        self.kv.release(b)
+                if not self._running:
+                    # nothing will ever free memory for it: fail instead of spinning
+                    self._waiting.popleft()
+                    r.error = "request does not fit in the KV pool"
+                    self._finish(r, "error")
+                    self.counters["failed"] += 1
+                    continue
+                break
+            self._waiting.popleft()
+            r.slot = self.states.alloc_slot()
+            if hit:
+                r.blocks = list(hit.blocks)
+                r.n_computed = r.prefix_tokens = hit.n_tokens
+                if hit.snapshot is not None:
+                    self.states.restore(r.slot, hit.snapshot)
+            for _ in range(need):
+                r.blocks.append(self.kv.alloc_block())
+            r.state = PREFILL
+            self._running.append(r)
+            self.counters["prompt_tokens"] += len(r.prompt)
+
+    def _grow(self, r: _Req, upto_tokens: int) -> bool:
+        while len(r.blocks) * KV_BLOCK < upto_tokens:
+            if self.kv.free_blocks < 1:
+                self.prefix.evict_until_free(1)
+            try:
+                r.blocks.append(self.kv.alloc_block())
+            except PoolExhausted:
+                return False
+        return True
+
+    def _build_plan(self) -> List[Tuple[_Req, List[int], int]]:
+        """[(request, tokens to run this tick, start position)]."""
+        plan: List[Tuple[_Req, List[int], int]] = []
+        budget = self.limits.max_batched_tokens
+        for r in list(self._running):
+            if r.state != DECODE:
+                continue
+            chain = [r.toks[-1]] + (r.drafts if self.spec_width else [])
+            start = len(r.toks) - 1
+            if not self._grow(r, start + len(chain)):
+                self._running.remove(r)
+                self._finish(r, "length" if r.out else "error")
+                self.counters["preempted"] += 1
+                continue
+            plan.append((r, chain, start))
+            budget -= len(chain)
+        for r in self._running:
+            if r.state != PREFILL or budget <= 0:
+                continue
+            n_prompt = len(r.prompt)
+            end = min(n_prompt, r.n_computed + budget)
+            if end < n_prompt:
+                al = self.limits.prefill_align
+                end = max(r.n_computed + 1, r.n_computed + (end - r.n_computed) // al * al)
+            boundary = (n_prompt - 1) // KV_BLOCK * KV_BLOCK
+            if not isinstance(self.prefix, NoPrefixStore) and r.n_computed < boundary < end \
+                    and not r.published:
+                end = boundary  # stop at the block boundary so the GDN snapshot matches it
+            toks = r.prompt[r.n_computed:end]
+            plan.append((r, toks, r.n_computed))
+            budget -= len(toks)
+        return plan
+
+    def _run(self, plan) -> None:
+        verify = self.spec_width > 0 and any(r.state == DECODE and len(t) > 1 for r, t, _ in plan)
+        decode_only = all(r.state == DECODE for r, _, _ in plan)
+        seqs = [dict(tokens=t, start=s, blocks=r.blocks, slot=r.slot,
+                     keep=verify and r.state == DECODE) for r, t, s in plan]
+        logits = None
+        if self.graph is not None and decode_only and not verify and self.sparse is None:
+            logits = self.graph.run(seqs)
+            if logits is not None:
+                self.counters["graph_ticks"] += 1
+        taps = hidden = None
+        if logits is None:
+            keep = max(len(t) for _, t, _ in plan) if verify else 0
+            batch = Batch.build(seqs, self.device, keep_steps=keep)
+            if self.sparse is not None:
+                batch.sparse = self.sparse.for_batch(batch, [r.rid for r, _, _ in plan])
+            aux = tuple(self.drafter.aux_layers) if self.drafter is not None else ()
+            res = self.model.forward(batch, self.ops, self.kv, self.states,
+                                     last_only=not verify, aux_layers=aux)
+            if aux:
+                logits, hidden, taps = res
+            else:
+                logits = res
+        kinds = {r.state for r, _, _ in plan}
+        key = "mixed_ticks" if len(kinds) > 1 else ("decode_ticks" if DECODE in kinds else "prefill_ticks")
+        self.counters[key] += 1
+        row = 0  # row of `logits` when last_only; token offset otherwise
+        tok_off = 0
+        for i, (r, toks, start) in enumerate(plan):
+            n = len(toks)
+            if verify:
+                lrows = logits[tok_off:tok_off + n]
+            else:
+                lrows = logits[i:i + 1]
+            if r.state == PREFILL:
+                r.n_computed = start + n
+                self._maybe_publish(r)
+                if r.n_computed == len(r.prompt):
+                    r.state = DECODE
+                    r.t_first = time.monotonic()
+                    self._commit(r, [self._sample(r, lrows[-1], 0)])
+                    self._offer_draft(r, taps, tok_off, n)
+            else:
+                self._verify_commit(r, toks, lrows, verify)
+                self._offer_draft(r, taps, tok_off, n)
+            tok_off += n
+
+    # ---- sampling / commit ------------------------------------------------------------------------
+    def _sample(self, r: _Req, logits_row: torch.Tensor, k: int) -> Tuple[int, float]:
+        p = r.params
+        idx = len(r.out) + k
+        if self.think_ids and p.max_think_tokens is not None and r.in_think \
+                and r.think_tokens + k >= p.max_think_tokens:
+            return self.think_ids[1], 0.0  # forced </think>
+        allowed = None if p.allowed_ids is None else torch.tensor(p.allowed_ids)
+        if p.temperature <= 0.0 and allowed is None and not p.logprobs:
+            return int(torch.argmax(logits_row)), 0.0
+        return ref.sample(logits_row.detach().float().cpu(), p.temperature, p.top_p, p.top_k,
+                          ref.sample_seed(p.seed, idx), allowed)
+
+    def _verify_commit(self, r: _Req, chain: List[int], lrows: torch.Tensor, verify: bool) -> None:
+        if not verify or len(chain) == 1:
+            self._commit(r, [self._sample(r, lrows[-1] if not verify else lrows[0], 0)])
+            if verify:
+                self.states.select_step(r.slot, 0)
+            return
+        drafts = chain[1:]
+        accepted: List[Tuple[int, float]] = []
+        n_ok = 0
+        for k in range(len(chain)):
+            tok = self._sample(r, lrows[k], k)
+            accepted.append(tok)
+            if k < len(drafts) and tok[0] == drafts[k]:
+                n_ok += 1
+                continue
+            break
+        self.counters["spec_drafted"] += len(drafts)
+        self.counters["spec_accepted"] += n_ok
+        # state after the n_ok+1 chain tokens that were really part of the sequence
+        self.states.select_step(r.slot, n_ok)
+        self._commit(r, accepted)
+
+    def _commit(self, r: _Req, toks: List[Tuple[int, float]]) -> None:
+        p = r.params
+        for tok, lp in toks:
+            r.out.append(tok)
+            if p.logprobs:
+                r.logprobs.append(lp)
+            self.counters["tokens_generated"] += 1
+            if self.think_ids:
+                if tok == self.think_ids[0]:
+                    r.in_think, r.think_tokens = True, 0
+                elif tok == self.think_ids[1]:
+                    r.in_think = False
+                elif r.in_think:
+                    r.think_tokens += 1
+            reason = None
+            if tok in p.stop_ids or (self.eos_id is not None and tok == self.eos_id and not p.ignore_eos):
+                reason = "stop"
+            elif p.stop_texts and self.detok is not None:
+                text = self.detok(r.out)
+                if any(s in text for s in p.stop_texts):
+                    reason = "stop"
+            if reason is None and len(r.out) >= p.max_tokens:
+                reason = "length"
+            if reason:
+                self._running.remove(r)
+                self._finish(r, reason)
+                self.counters["finished"] += 1
+                return
+        r.n_computed = len(r.toks) - 1
+        r.drafts = []
+
+    def _offer_draft(self, r: _Req, taps, tok_off: int, n: int) -> None:
+        if self.drafter is None or r.state != DECODE:
+            return
+        r.drafts = self.drafter.propose(self, r, taps, tok_off, n, self.spec_width - 1)
+
+    def _maybe_publish(self, r: _Req) -> None:
+        if r.published or isinstance(self.prefix, NoPrefixStore):
+            return
+        boundary = (len(r.prompt) - 1) // KV_BLOCK * KV_BLOCK
+        if boundary and r.n_computed == boundary:
+            snap = self.states.snapshot(r.slot) if self.model.cfg.n_gdn_layers else None
+            self.prefix.insert(r.prompt[:boundary], r.blocks, snap)
+            r.published = True
+
+    def _finish(self, r: _Req, reason: str) -> None:
+        r.finish_reason = reason
+        r.state = DONE
+        r.t_done = time.monotonic()
+        for b in r.blocks:
+            self.kv.release(b)
+        r.blocks = []
+        if r.slot > 0:
+            self.states.release(r.slot)
+            r.slot = -1
+        if self.drafter is not None and hasattr(self.drafter, "release"):
+            self.drafter.release(r.rid)
+        if self.sparse is not None:
+            self.sparse.release(r.rid)

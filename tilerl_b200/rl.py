@@ -1,0 +1,313 @@
+"""Training loops on the hand-written tape: SFT, GRPO, on-policy distillation.
+
+``policy_step`` implements the clipped GRPO surrogate with the rollout
+log-probabilities as ``pi_old``:
+
+    L = -1/N * sum_i min(rho_i A_i, clip(rho_i, 1-eps, 1+eps) A_i) + beta * KL_k3
+
+Its gradient w.r.t. the logits is a weighted cross-entropy gradient with
+per-token weight ``w_i = (A_i rho_i [unclipped_i] - beta (1 - exp(ref_i - logp_i))) / N``,
+so the tape's ``cross_entropy`` op (which emits loss and gradient together and
+never differentiates a softmax twice) is the whole objective.  With one
+on-policy update ``rho == 1`` and the weights reduce to ``A_i / N`` -- exactly the
+REINFORCE-with-baseline form of the reference.  ``N`` is the batch-wide scored
+token count, not the micro-batch's.
+
+``grpo_loop`` rolls out through the *same* engine that serves (P prompts x G
+samples with per-sample seeds), scores, normalises advantages per group, runs
+``policy_step``, re-quantises the served weights in place and invalidates the
+engine's caches.
+
+Parity: reference ``src/tilerl/train.py`` -- ``_step:164-310``,
+``train_step:716``, ``group_advantages:740``, ``rl_step:805``,
+``_require_on_policy:864``, ``grpo_loop:936-1135``, ``opd_loop:1138``,
+``pretrain:1222``.
+"""
+from __future__ import annotations
+
+import json
+import os
+import time
+from dataclasses import dataclass
+from typing import Callable, Dict, Iterator, List, Optional, Sequence
+
+import torch
+
+from . import tape as T
+from .engine import Engine, SamplingParams
+from .optim import clip_grad_norm, cosine_warmup
+from .ops import ref
+
+
+def group_advantages(rewards: Sequence[float], group: int, live: Optional[Sequence[bool]] = None,
+                     eps: float = 1e-6) -> torch.Tensor:
+    """``(r - mean_g) / std_g`` within each group of ``group`` consecutive samples.
+    A group whose live samples all tie gets zeros (no signal); dead samples (empty
+    completions) get zero and do not enter the statistics."""
+    r = torch.tensor(list(rewards), dtype=torch.float32)
+    lv = torch.ones_like(r, dtype=torch.bool) if live is None else torch.tensor(list(live), dtype=torch.bool)
+    adv = torch.zeros_like(r)
+    for g0 in range(0, len(r), group):
+        sl = slice(g0, g0 + group)
+        m = lv[sl]
+        if m.sum() < 2:
+            continue
+        x = r[sl][m]
+        sd = x.std(unbiased=False)
+        if float(sd) < eps:
+            continue
+        a = torch.zeros(m.shape[0])
+        a[m] = (x - x.mean()) / (sd + eps)
+        adv[sl] = a
+    return adv
+
+
+def require_on_policy(p: SamplingParams) -> None:
+    if not p.untruncated:
+        raise ValueError("GRPO rollouts must sample the untruncated policy "
+                         "(temperature 1, top_p 1, top_k 0, no allowed_ids)")
+
+
+def pad_batch(seqs: Sequence[Sequence[int]], pad: int = 0, pow2: bool = False):
+    width = max(len(s) for s in seqs)
+    if pow2:
+        w = 1
+        while w < width:
+            w *= 2
+        width = w
+    ids = torch.full((len(seqs), width), pad, dtype=torch.long)
+    for i, s in enumerate(seqs):
+        ids[i, :len(s)] = torch.tensor(list(s), dtype=torch.long)
+    return ids
+
+
+def _named_grads(trainable: Dict[str, torch.Tensor], grads_by_id) -> Dict[str, torch.Tensor]:
+    return {n: grads_by_id[id(t)] for n, t in trainable.items() if id(t) in grads_by_id}
+
+
+def _scored_mask(ids: torch.Tensor, prompt_lens, seq_lens) -> torch.Tensor:
+    """Positions i whose *next* token is a completion token: plen-1 <= i < slen-1."""
+    b, t = ids.shape
+    pos = torch.arange(t)[None, :]
+    pl = torch.as_tensor(prompt_lens)[:, None]
+    sl = torch.as_tensor(seq_lens)[:, None]
+    return (pos >= pl - 1) & (pos < sl - 1)
+
+
+def forward_backward(model, ids: torch.Tensor, targets: torch.Tensor, weights_fn, *,
+                     trainable: Dict[str, torch.Tensor], tp_group=None, tp_world: int = 1,
+                     checkpoint_layers: bool = False, on_grad=None):
+    """One micro-batch: dense forward on a fresh tape, weights from ``weights_fn(logits)``,
+    cross-entropy op, backward.  Returns (loss, named grads, logits)."""
+    tp = T.Tape(tp_group, tp_world)
+    tp.watch(*trainable.values())
+    logits = model.forward_dense(tp, ids, checkpoint_layers=checkpoint_layers)
+    w = weights_fn(logits)
+    loss = T.cross_entropy(tp, logits, targets, w)
+    grads = tp.backward(loss, on_grad=on_grad)
+    return float(loss), _named_grads(trainable, grads), logits
+
+
+def train_step(model, ids: torch.Tensor, optimizer, *, seq_lens=None, max_norm: float = 1.0,
+               lr: Optional[float] = None, micro: int = 0, **fb) -> Dict[str, float]:
+    """Supervised next-token CE, mean over the B*(T-1) (or valid) positions."""
+    b, t = ids.shape
+    sl = torch.full((b,), t) if seq_lens is None else torch.as_tensor(seq_lens)
+    mask = torch.arange(t)[None, :] < (sl[:, None] - 1)
+    n = float(mask.sum())
+    targets = torch.roll(ids, -1, 1)
+    trainable = model.trainable()
+    total, acc = 0.0, {}
+    mb = micro or b
+    for s in range(0, b, mb):
+        m = mask[s:s + mb].float() / n
+        loss, grads, _ = forward_backward(model, ids[s:s + mb], targets[s:s + mb],
+                                          lambda lg, m=m: m.to(lg.device), trainable=trainable, **fb)
+        total += loss
+        for k, g in grads.items():
+            acc[k] = g if k not in acc else acc[k] + g
+    norm = clip_grad_norm(acc, max_norm)
+    optimizer.step(acc, lr)
+    return dict(loss=total, grad_norm=norm, tokens=n)
+
+
+def policy_step(model, ids: torch.Tensor, prompt_lens, seq_lens, advantages: torch.Tensor,
+                optimizer, *, old_logprobs: Optional[torch.Tensor] = None, clip_eps: float = 0.2,
+                kl_coef: float = 0.0, ref_logprobs: Optional[torch.Tensor] = None,
+                max_norm: float = 1.0, lr: Optional[float] = None, micro: int = 0,
+                return_grads: bool = False, **fb) -> Dict[str, object]:
+    """One GRPO update on padded ``ids [B, T]``.  ``old_logprobs [B, T]`` holds
+    log pi_old of token i+1 at position i (None: on-policy, rho = 1)."""
+    b, t = ids.shape
+    mask = _scored_mask(ids, prompt_lens, seq_lens)
+    n = max(1.0, float(mask.sum()))
+    targets = torch.roll(ids, -1, 1)
+    trainable = model.trainable()
+    acc: Dict[str, torch.Tensor] = {}
+    stats = dict(loss=0.0, clipped=0.0, ratio_mean=0.0)
+    mb = micro or b
+    for s in range(0, b, mb):
+        sl = slice(s, s + mb)
+        adv = advantages[sl, None].float()
+
+        def weights(lg, sl=sl, adv=adv):
+            lp = ref.token_logprobs(lg.reshape(-1, lg.shape[-1]), targets[sl].reshape(-1)).view(lg.shape[:2])
+            if old_logprobs is None:
+                rho = torch.ones_like(lp)
+            else:
+                rho = torch.exp(lp - old_logprobs[sl].to(lp.device))
+            a = adv.to(lp.device)
+            unclipped = ~(((rho > 1 + clip_eps) & (a > 0)) | ((rho < 1 - clip_eps) & (a < 0)))
+            w = a * rho * unclipped
+            if kl_coef and ref_logprobs is not None:
+                w = w - kl_coef * (1 - torch.exp(ref_logprobs[sl].to(lp.device) - lp))
+            m = mask[sl].to(lp.device)
+            stats["clipped"] += float((~unclipped & m).sum())
+            stats["ratio_mean"] += float((rho * m).sum())
+            return w * m / n
+
+        loss, grads, _ = forward_backward(model, ids[sl], targets[sl], weights, trainable=trainable, **fb)
+        stats["loss"] += loss
+        for k, g in grads.items():
+            acc[k] = g if k not in acc else acc[k] + g
+    stats["ratio_mean"] /= n
+    stats["grad_norm"] = clip_grad_norm(acc, max_norm)
+    stats["tokens"] = n
+    if optimizer is not None:
+        optimizer.step(acc, lr)
+    if return_grads:
+        stats["grads"] = acc
+    return stats
+
+
+def drain(engine: Engine, rids: Sequence[int], max_ticks: int = 1 << 30) -> List:
+    """Step the engine until every request finished.  A request the pool could not
+    hold comes back empty (dead sample) instead of aborting the step."""
+    ticks = 0
+    while ticks < max_ticks:
+        if all(engine.poll(r)["state"] == "done" for r in rids):
+            break
+        if not engine.step():
+            break
+        ticks += 1
+    return [engine.take(r) for r in rids]
+
+
+def grpo_loop(engine: Engine, model, prompts: Sequence[Sequence[int]], reward_fn: Callable,
+              optimizer, *, steps: int, group: int = 4, prompts_per_step: int = 2,
+              max_tokens: int = 16, clip_eps: float = 0.2, kl_coef: float = 0.0, lr: Optional[float] = None,
+              micro: int = 0, seed: int = 0, on_policy_updates: int = 1, post_step: Optional[Callable] = None,
+              length_penalty: float = 0.0, **fb) -> Iterator[Dict[str, object]]:
+    """Yields one metrics dict per RL step (mean reward, loss, seconds by phase)."""
+    engine.invalidate_weights()
+    cursor = 0
+    for step in range(steps):
+        t0 = time.perf_counter()
+        batch_prompts = [prompts[(cursor + i) % len(prompts)] for i in range(prompts_per_step)]
+        cursor += prompts_per_step
+        rids = []
+        for pi, p in enumerate(batch_prompts):
+            for g in range(group):
+                sp = SamplingParams(max_tokens=max_tokens, temperature=1.0, top_p=1.0, top_k=0,
+                                    seed=seed + ((step * 1009 + pi) * 131 + g), logprobs=True)
+                require_on_policy(sp)
+                rids.append(engine.submit(p, sp))
+        results = drain(engine, rids)
+        t1 = time.perf_counter()
+        comps = [r.tokens if r is not None else [] for r in results]
+        live = [len(c) > 0 for c in comps]
+        rewards = [float(reward_fn(batch_prompts[i // group], c)) - length_penalty * len(c)
+                   for i, c in enumerate(comps)]
+        adv = group_advantages(rewards, group, live)
+        seqs = [list(batch_prompts[i // group]) + c for i, c in enumerate(comps)]
+        plens = [len(batch_prompts[i // group]) for i in range(len(seqs))]
+        slens = [len(s) for s in seqs]
+        ids = pad_batch(seqs, pow2=False)
+        old = None
+        if on_policy_updates > 1:
+            old = torch.zeros(ids.shape, dtype=torch.float32)
+            for i, r in enumerate(results):
+                if r is not None and r.logprobs:
+                    old[i, plens[i] - 1:plens[i] - 1 + len(r.logprobs)] = torch.tensor(r.logprobs)
+        t2 = time.perf_counter()
+        stats = {}
+        for _ in range(on_policy_updates):
+            stats = policy_step(model, ids.to(engine.device), plens, slens, adv, optimizer,
+                                old_logprobs=old, clip_eps=clip_eps, kl_coef=kl_coef, lr=lr,
+                                micro=micro, **fb)
+        t3 = time.perf_counter()
+        if post_step is not None:
+            post_step(model)
+        engine.invalidate_weights()
+        t4 = time.perf_counter()
+        n_tied = sum(1 for g0 in range(0, len(rewards), group)
+                     if len(set(rewards[g0:g0 + group])) == 1)
+        yield dict(step=step, reward=sum(rewards) / len(rewards), loss=stats.get("loss", 0.0),
+                   grad_norm=stats.get("grad_norm", 0.0), tokens=stats.get("tokens", 0),
+                   tied_groups=n_tied, completion_tokens=sum(len(c) for c in comps),
+                   timings=dict(rollout=t1 - t0, score=t2 - t1, train=t3 - t2,
+                                invalidate=t4 - t3, total=t4 - t0))
+
+
+def opd_loop(engine: Engine, model, prompts, optimizer, *, steps: int, max_tokens: int = 16,
+             ema: float = 0.99, prompts_per_step: int = 2, lr=None, seed: int = 0, **fb):
+    """On-policy self-distillation: the student samples, an EMA copy of the
+    trainable tensors (the teacher) scores the same tokens, and the student
+    minimises the token-level reverse-KL estimate ``logp_s - logp_t`` on its own
+    samples (weights = stop-gradient of that gap)."""
+    trainable = model.trainable()
+    teacher = {k: v.detach().clone() for k, v in trainable.items()}
+    cursor = 0
+    for step in range(steps):
+        ps = [prompts[(cursor + i) % len(prompts)] for i in range(prompts_per_step)]
+        cursor += prompts_per_step
+        rids = [engine.submit(p, SamplingParams(max_tokens=max_tokens, temperature=1.0, seed=seed + step * 131 + i))
+                for i, p in enumerate(ps)]
+        results = drain(engine, rids)
+        seqs = [list(p) + (r.tokens if r else []) for p, r in zip(ps, results)]
+        ids = pad_batch(seqs).to(engine.device)
+        plens, slens = [len(p) for p in ps], [len(s) for s in seqs]
+        mask = _scored_mask(ids, plens, slens)
+        n = max(1.0, float(mask.sum()))
+        targets = torch.roll(ids, -1, 1)
+        # teacher scores with EMA weights swapped in
+        saved = {k: v.detach().clone() for k, v in trainable.items()}
+        for k, v in trainable.items():
+            v.copy_(teacher[k])
+        tl = model.forward_dense(T.Tape(), ids)
+        lp_t = ref.token_logprobs(tl.reshape(-1, tl.shape[-1]), targets.reshape(-1)).view(ids.shape)
+        for k, v in trainable.items():
+            v.copy_(saved[k])
+
+        def weights(lg):
+            lp_s = ref.token_logprobs(lg.reshape(-1, lg.shape[-1]), targets.reshape(-1)).view(ids.shape)
+            return -(lp_s - lp_t) * mask / n   # descend on E[(logp_s - logp_t) * grad logp_s]
+
+        loss, grads, _ = forward_backward(model, ids, targets, weights, trainable=trainable, **fb)
+        clip_grad_norm(grads, 1.0)
+        optimizer.step(grads, lr)
+        for k, v in trainable.items():
+            teacher[k].mul_(ema).add_(v.detach(), alpha=1 - ema)
+        model.requantize_()
+        engine.invalidate_weights()
+        yield dict(step=step, loss=loss, tokens=n)
+
+
+def pretrain(model, data: Iterator[torch.Tensor], optimizer, *, steps: int, lr: float, warmup: int = 0,
+             ckpt_every: int = 0, ckpt_dir: Optional[str] = None, log: Optional[Callable] = None, **fb):
+    """SFT/pre-training loop with cosine schedule and periodic checkpoints."""
+    from .checkpoint import save_checkpoint
+    history = []
+    for step in range(steps):
+        ids = next(data)
+        cur = cosine_warmup(step, steps, warmup, lr)
+        m = train_step(model, ids, optimizer, lr=cur, **fb)
+        m.update(step=step, lr=cur)
+        history.append(m)
+        if log:
+            log(json.dumps(m))
+        if ckpt_every and ckpt_dir and (step + 1) % ckpt_every == 0:
+            save_checkpoint(model, os.path.join(ckpt_dir, f"step_{step + 1}"))
+    if ckpt_dir:
+        save_checkpoint(model, os.path.join(ckpt_dir, "final"))
+    return history

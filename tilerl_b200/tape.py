@@ -1,0 +1,393 @@
+"""Hand-written reverse-mode tape.
+
+No ``torch.autograd`` graph is built for the model: every op below runs its
+forward under ``no_grad`` and pushes a node ``(inputs, outputs, backward)`` on the
+tape; ``Tape.backward`` walks the nodes in reverse, keeps gradients in a dict
+keyed by tensor identity, and hands each leaf gradient to ``on_grad`` as soon as
+the last node that can contribute to it has run, so an optimizer (or a ZeRO
+reduce-scatter) can consume and free it while the rest of backward proceeds.
+``checkpoint`` stores only a segment's inputs and replays the segment on a
+private tape during backward.
+
+The collectives are ops on the same tape (``tp_fork``: identity forward /
+all-reduce backward; ``all_reduce``: the converse), so tensor-parallel training
+needs no special casing.
+
+Parity: reference ``src/tilerl/autograd.py`` -- ``RecordingBackend:65``, handler
+table ``_BWD:275-301``, ``Tape:304``, ``backward:360``, streaming release
+``_release:441``, ``checkpoint:34``; collectives on the tape ``:229-255``.
+"""
+from __future__ import annotations
+
+import math
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from .ops import ref
+
+
+class _Node:
+    __slots__ = ("inputs", "outputs", "bwd", "name")
+
+    def __init__(self, name, inputs, outputs, bwd):
+        self.name, self.inputs, self.outputs, self.bwd = name, inputs, outputs, bwd
+
+
+class Tape:
+    def __init__(self, tp_group=None, tp_world: int = 1):
+        self.nodes: List[_Node] = []
+        self.leaves: Dict[int, torch.Tensor] = {}
+        self.tp_group, self.tp_world = tp_group, tp_world
+        self.enabled = True
+
+    # ---- recording -------------------------------------------------------------
+    def watch(self, *tensors: torch.Tensor) -> None:
+        for t in tensors:
+            self.leaves[id(t)] = t
+
+    def record(self, name: str, inputs: Sequence[torch.Tensor], outputs: Sequence[torch.Tensor],
+               bwd: Callable) -> None:
+        if self.enabled:
+            self.nodes.append(_Node(name, tuple(inputs), tuple(outputs), bwd))
+
+    # ---- backward ----------------------------------------------------------------
+    def backward(self, root: torch.Tensor, grad: Optional[torch.Tensor] = None,
+                 on_grad: Optional[Callable[[torch.Tensor, torch.Tensor], None]] = None
+                 ) -> Dict[int, torch.Tensor]:
+        grads: Dict[int, torch.Tensor] = {id(root): torch.ones_like(root) if grad is None else grad}
+        # first node (in forward order) that reads each leaf = last to contribute in reverse
+        first_use: Dict[int, int] = {}
+        for idx, n in enumerate(self.nodes):
+            for t in n.inputs:
+                if id(t) in self.leaves and id(t) not in first_use:
+                    first_use[id(t)] = idx
+        for idx in range(len(self.nodes) - 1, -1, -1):
+            n = self.nodes[idx]
+            gouts = [grads.pop(id(o), None) for o in n.outputs]
+            if all(g is None for g in gouts):
+                continue
+            gins = n.bwd(*gouts)
+            if not isinstance(gins, (tuple, list)):
+                gins = (gins,)
+            for t, g in zip(n.inputs, gins):
+                if g is None:
+                    continue
+                k = id(t)
+                grads[k] = g if k not in grads else grads[k] + g
+            if on_grad is not None:
+                for t in n.inputs:
+                    k = id(t)
+                    if first_use.get(k) == idx and k in grads:
+                        on_grad(t, grads.pop(k))
+        self.nodes.clear()
+        return {k: g for k, g in grads.items() if k in self.leaves}
+
+    def grad_of(self, grads: Dict[int, torch.Tensor], t: torch.Tensor) -> Optional[torch.Tensor]:
+        return grads.get(id(t))
+
+    # ---- checkpoint -----------------------------------------------------------------
+    def checkpoint(self, fn: Callable, *inputs: torch.Tensor,
+                   params: Sequence[torch.Tensor] = ()) -> torch.Tensor:
+        """Run ``fn(tape, *inputs)`` without recording and keep only its inputs;
+        backward replays it on a private tape.  ``params`` lists the watched leaves
+        ``fn`` reads through its closure so their gradients flow out of the segment."""
+        was = self.enabled
+        self.enabled = False
+        try:
+            out = fn(self, *inputs)
+        finally:
+            self.enabled = was
+        params = tuple(params)
+
+        def bwd(g):
+            sub = Tape(self.tp_group, self.tp_world)
+            for t in inputs + params:
+                sub.leaves[id(t)] = t
+            y = fn(sub, *inputs)
+            gs = sub.backward(y, g)
+            return tuple(gs.get(id(t)) for t in inputs + params)
+
+        self.record("checkpoint", inputs + params, (out,), bwd)
+        return out
+
+
+# ---- ops ---------------------------------------------------------------------------------
+def _nograd(fn):
+    def wrapped(*a, **k):
+        with torch.no_grad():
+            return fn(*a, **k)
+    wrapped.__name__ = fn.__name__
+    wrapped.__doc__ = fn.__doc__
+    return wrapped
+
+
+@_nograd
+def embedding(tape: Tape, table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    out = table[ids.long()].float()
+
+    def bwd(g):
+        gt = torch.zeros(table.shape, dtype=torch.float32, device=table.device)
+        gt.index_add_(0, ids.reshape(-1).long(), g.reshape(-1, g.shape[-1]).float())
+        return (gt,)
+
+    tape.record("embedding", (table,), (out,), bwd)
+    return out
+
+
+@_nograd
+def rmsnorm(tape: Tape, x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    rstd = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    xn = xf * rstd
+    out = xn * w.float()
+
+    def bwd(g):
+        g = g.float()
+        gw = (g * xn).reshape(-1, x.shape[-1]).sum(0)
+        gx = g * w.float()
+        dx = rstd * (gx - xn * (gx * xn).mean(-1, keepdim=True))
+        return dx, gw
+
+    tape.record("rmsnorm", (x, w), (out,), bwd)
+    return out
+
+
+@_nograd
+def linear(tape: Tape, x: torch.Tensor, w, frozen: bool = False) -> torch.Tensor:
+    """``y = x @ W^T``.  ``w`` is a dense master tensor (dX and dW) or a quantised
+    weight / ``frozen=True`` dense tensor (dX only, the LoRA-on-frozen-base mode)."""
+    dense = isinstance(w, torch.Tensor)
+    wf = w.float() if dense else w.dequant().to(x.device)
+    out = x.float() @ wf.t()
+
+    def bwd(g):
+        g = g.float()
+        dx = g @ wf
+        if dense and not frozen:
+            dw = g.reshape(-1, g.shape[-1]).t() @ x.float().reshape(-1, x.shape[-1])
+            return dx, dw
+        return (dx,)
+
+    tape.record("linear", (x, w) if dense and not frozen else (x,), (out,), bwd)
+    return out
+
+
+@_nograd
+def add(tape: Tape, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    out = a + b
+    tape.record("add", (a, b), (out,), lambda g: (g, g))
+    return out
+
+
+@_nograd
+def scale(tape: Tape, a: torch.Tensor, s: float) -> torch.Tensor:
+    out = a * s
+    tape.record("scale", (a,), (out,), lambda g: (g * s,))
+    return out
+
+
+@_nograd
+def swiglu(tape: Tape, gu: torch.Tensor) -> torch.Tensor:
+    g_, u_ = gu[..., 0::2].float(), gu[..., 1::2].float()
+    sig = torch.sigmoid(g_)
+    out = g_ * sig * u_
+
+    def bwd(g):
+        dg = g * u_ * sig * (1 + g_ * (1 - sig))
+        du = g * g_ * sig
+        return (torch.stack([dg, du], -1).flatten(-2),)
+
+    tape.record("swiglu", (gu,), (out,), bwd)
+    return out
+
+
+@_nograd
+def attention_block(tape: Tape, qkv: torch.Tensor, q_norm_w: torch.Tensor, k_norm_w: torch.Tensor,
+                    positions: torch.Tensor, *, n_q, n_kv, head_dim, rotary_dim, theta, eps,
+                    gated=True) -> torch.Tensor:
+    """Dense causal gated-GQA attention on ``qkv [B, T, rows]``: split, per-head q/k
+    RMSNorm, partial RoPE, softmax(QK^T)V, sigmoid gate.  Backward is derived by
+    hand (softmax Jacobian, RoPE transpose rotation, RMSNorm)."""
+    b, t, _ = qkv.shape
+    d, g = head_dim, n_q // n_kv
+    x = qkv.float()
+    q_rows = n_q * d * (2 if gated else 1)
+    if gated:
+        qg = x[..., :q_rows].view(b, t, n_q, 2, d)
+        q_raw, gate = qg[..., 0, :], qg[..., 1, :]
+    else:
+        q_raw, gate = x[..., :q_rows].view(b, t, n_q, d), None
+    k_raw = x[..., q_rows:q_rows + n_kv * d].view(b, t, n_kv, d)
+    v = x[..., q_rows + n_kv * d:].view(b, t, n_kv, d)
+
+    def norm(z, w):
+        rstd = torch.rsqrt(z.pow(2).mean(-1, keepdim=True) + eps)
+        return z * rstd, rstd
+
+    qn, q_rstd = norm(q_raw, q_norm_w)
+    kn, k_rstd = norm(k_raw, k_norm_w)
+    half = rotary_dim // 2
+    inv = theta ** (-torch.arange(half, dtype=torch.float64, device=x.device) * 2.0 / rotary_dim)
+    ang = positions.to(torch.float64)[..., None] * inv
+    cos, sin = ang.cos().float(), ang.sin().float()
+    if cos.dim() == 2:
+        cos, sin = cos[None], sin[None]
+    cos, sin = cos[:, :, None, :], sin[:, :, None, :]
+
+    def rope(z, sgn=1.0):
+        o = z.clone()
+        z1, z2 = z[..., :half], z[..., half:rotary_dim]
+        o[..., :half] = z1 * cos - sgn * z2 * sin
+        o[..., half:rotary_dim] = z2 * cos + sgn * z1 * sin
+        return o
+
+    q = rope(qn * q_norm_w.float())
+    k = rope(kn * k_norm_w.float())
+    sc = 1.0 / math.sqrt(d)
+    qq = q.view(b, t, n_kv, g, d)
+    s = torch.einsum("bthgd,bshd->bhgts", qq, k) * sc
+    pos = positions if positions.dim() == 2 else positions[None].expand(b, -1)
+    mask = pos[:, None, :] <= pos[:, :, None]                     # [b, t, s]
+    s = s.masked_fill(~mask[:, None, None], float("-inf"))
+    p = torch.softmax(s, -1)
+    o = torch.einsum("bhgts,bshd->bthgd", p, v).reshape(b, t, n_q, d)
+    sig = torch.sigmoid(gate) if gated else None
+    out = (o * sig if gated else o).reshape(b, t, n_q * d)
+
+    def bwd(gout):
+        go = gout.float().view(b, t, n_q, d)
+        if gated:
+            dgate = go * o * sig * (1 - sig)
+            go = go * sig
+        gog = go.view(b, t, n_kv, g, d)
+        dv = torch.einsum("bhgts,bthgd->bshd", p, gog)
+        dp = torch.einsum("bthgd,bshd->bhgts", gog, v)
+        ds = p * (dp - (dp * p).sum(-1, keepdim=True))
+        dq = torch.einsum("bhgts,bshd->bthgd", ds, k).reshape(b, t, n_q, d) * sc
+        dk = torch.einsum("bhgts,bthgd->bshd", ds, qq) * sc
+        dq, dk = rope(dq, -1.0), rope(dk, -1.0)   # transpose of a rotation = inverse rotation
+
+        def norm_bwd(gz, zn, rstd, w):
+            gw = (gz * zn).reshape(-1, d).sum(0)
+            gx = gz * w.float()
+            return rstd * (gx - zn * (gx * zn).mean(-1, keepdim=True)), gw
+
+        dq_raw, gqw = norm_bwd(dq, qn, q_rstd, q_norm_w)
+        dk_raw, gkw = norm_bwd(dk, kn, k_rstd, k_norm_w)
+        parts = []
+        if gated:
+            parts.append(torch.stack([dq_raw, dgate], 3).reshape(b, t, q_rows))
+        else:
+            parts.append(dq_raw.reshape(b, t, q_rows))
+        parts += [dk_raw.reshape(b, t, -1), dv.reshape(b, t, -1)]
+        return torch.cat(parts, -1), gqw, gkw
+
+    tape.record("attention", (qkv, q_norm_w, k_norm_w), (out,), bwd)
+    return out
+
+
+def gdn_block_torch(inp, conv_w, dt_bias, a_log, norm_w, *, nk, nv, dk, dv, eps, chunk=64,
+                    state=None):
+    """Differentiable dense GDN block on ``inp [B, T, rows]`` (zero initial state
+    and zero conv history): the autograd twin of the serving kernels."""
+    b, t, _ = inp.shape
+    q_raw, k_raw, v_raw, z, a, bb = ref.gdn_split(inp.float(), nk=nk, nv=nv, dk=dk, dv=dv)
+    qkv = torch.cat([q_raw, k_raw, v_raw], -1)
+    kw = conv_w.shape[1]
+    xp = F.pad(qkv, (0, 0, kw - 1, 0))
+    conv = sum(xp[:, j:j + t] * conv_w.float()[:, j] for j in range(kw))
+    c = F.silu(conv)
+    qc = c[..., :nk * dk].view(b, t, nk, dk)
+    kc = c[..., nk * dk:2 * nk * dk].view(b, t, nk, dk)
+    vc = c[..., 2 * nk * dk:].view(b, t, nv, dv)
+    rep = nv // nk
+    qn = (ref.l2norm(qc) / math.sqrt(dk)).repeat_interleave(rep, 2)
+    kn = ref.l2norm(kc).repeat_interleave(rep, 2)
+    g, beta = ref.gdn_gates(a, bb, a_log, dt_bias)
+    s0 = torch.zeros(b, nv, dk, dv, dtype=torch.float32, device=inp.device) if state is None else state
+    if chunk and t > 1:
+        o, _ = ref.gdn_chunked(qn, kn, vc, g, beta, s0, chunk=min(chunk, max(1, t)))
+    else:
+        o, _ = ref.gdn_recurrent_batched(qn, kn, vc, g, beta, s0)
+    out = ref.gdn_gated_norm(o, z.reshape(b, t, nv, dv), norm_w, eps)
+    return out.reshape(b, t, nv * dv)
+
+
+def gdn_block(tape: Tape, inp: torch.Tensor, conv_w, dt_bias, a_log, norm_w, **kw) -> torch.Tensor:
+    """GDN block as one tape op.  Forward runs without a graph; backward recomputes
+    the block (activation checkpointing at block granularity) and differentiates
+    the chunked form locally."""
+    with torch.no_grad():
+        out = gdn_block_torch(inp, conv_w, dt_bias, a_log, norm_w, **kw)
+    params = (conv_w, dt_bias, a_log, norm_w)
+
+    def bwd(g):
+        with torch.enable_grad():
+            leaves = [t.detach().float().requires_grad_(True) for t in (inp,) + params]
+            y = gdn_block_torch(*leaves, **kw)
+            gs = torch.autograd.grad(y, leaves, g.float(), allow_unused=True)
+        return tuple(gs)
+
+    tape.record("gdn", (inp,) + params, (out,), bwd)
+    return out
+
+
+@_nograd
+def cross_entropy(tape: Tape, logits: torch.Tensor, targets: torch.Tensor,
+                  weights: torch.Tensor) -> torch.Tensor:
+    """``sum_i w_i * nll_i`` over flattened rows; the gradient is produced together
+    with the loss (the form used by SFT and by the policy-gradient step)."""
+    lg = logits.reshape(-1, logits.shape[-1])
+    loss, grad = ref.cross_entropy_grad(lg, targets.reshape(-1), weights.reshape(-1).float())
+    grad = grad.view_as(logits)
+    tape.record("cross_entropy", (logits,), (loss,), lambda g: (grad * g,))
+    return loss
+
+
+@_nograd
+def tp_fork(tape: Tape, x: torch.Tensor) -> torch.Tensor:
+    """Identity forward; all-reduce of the gradient in backward (entry of a
+    column-parallel region)."""
+    out = x.view_as(x)
+
+    def bwd(g):
+        if tape.tp_world > 1:
+            import torch.distributed as dist
+            g = g.contiguous()
+            dist.all_reduce(g, group=tape.tp_group)
+        return (g,)
+
+    tape.record("tp_fork", (x,), (out,), bwd)
+    return out
+
+
+@_nograd
+def all_reduce(tape: Tape, x: torch.Tensor) -> torch.Tensor:
+    """All-reduce forward (exit of a row-parallel region); identity backward."""
+    out = x.clone()
+    if tape.tp_world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(out, group=tape.tp_group)
+    tape.record("all_reduce", (x,), (out,), lambda g: (g,))
+    return out
+
+
+@_nograd
+def lora(tape: Tape, y: torch.Tensor, x: torch.Tensor, a: torch.Tensor, b: torch.Tensor,
+         s: float) -> torch.Tensor:
+    """``y + s * (x A^T) B^T`` with gradients for x, A and B."""
+    xa = x.float() @ a.float().t()
+    out = y + (xa @ b.float().t()) * s
+
+    def bwd(g):
+        g = g.float()
+        g2 = g.reshape(-1, g.shape[-1])
+        db = (g2.t() @ xa.reshape(-1, xa.shape[-1])) * s
+        dxa = (g @ b.float()) * s
+        da = dxa.reshape(-1, dxa.shape[-1]).t() @ x.float().reshape(-1, x.shape[-1])
+        return g, dxa @ a.float(), da, db
+
+    tape.record("lora", (y, x, a, b), (out,), bwd)
+    return out
