@@ -1,0 +1,155 @@
+// Shared device helpers for the sm_100a kernels.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define TRL_API extern "C" __attribute__((visibility("default")))
+
+typedef __nv_bfloat16 bf16;
+typedef __nv_bfloat162 bf162;
+
+// ---- error word ------------------------------------------------------------------
+// Kernels never trap.  A bounded wait that runs out (or a debug bounds check that
+// fails) records {code, a, b, c} in this device-global word set and returns; the
+// host reads it with trl_error_read() after the step.
+struct TrlError {
+  int code;
+  int a, b, c;
+};
+enum { TRL_OK = 0, TRL_ERR_WAIT_TIMEOUT = 1, TRL_ERR_BOUNDS = 2, TRL_ERR_MBAR_TIMEOUT = 3 };
+extern __device__ TrlError g_trl_error;
+
+__device__ __forceinline__ void trl_set_error(int code, int a, int b, int c) {
+  if (atomicCAS(&g_trl_error.code, 0, code) == 0) {
+    g_trl_error.a = a;
+    g_trl_error.b = b;
+    g_trl_error.c = c;
+  }
+}
+
+// ---- programmatic dependent launch ----------------------------------------------------
+// Every kernel calls pdl_launch_dependents() first (the next kernel in the stream
+// may begin its own prologue) and pdl_wait() before touching anything a
+// predecessor wrote.  Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// ---- small math --------------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Block-wide sum / max through `red` (>= 32 floats of shared memory).  All threads
+// must call; result is broadcast.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float r = (lane < nw) ? red[lane] : 0.f;
+  return warp_sum(r);
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float r = (lane < nw) ? red[lane] : -INFINITY;
+  return warp_max(r);
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
+
+// ---- streaming loads -----------------------------------------------------------------------
+__device__ __forceinline__ uint4 ldg_stream_16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint2 ldg_stream_8(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ldg_stream_4(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint16_t ldg_stream_2(const void* p) {
+  uint16_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
+  return v;
+}
+
+// ---- narrow float decode --------------------------------------------------------------------
+// Four bytes of packed e2m1 (low nibble = even element) -> four f16x2 registers.
+__device__ __forceinline__ void cvt_e2m1x8_to_h2x4(uint32_t w, uint32_t (&h)[4]) {
+  asm("{ .reg .b8 b0, b1, b2, b3;\n"
+      "  mov.b32 {b0, b1, b2, b3}, %4;\n"
+      "  cvt.rn.f16x2.e2m1x2 %0, b0;\n"
+      "  cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+      "  cvt.rn.f16x2.e2m1x2 %2, b2;\n"
+      "  cvt.rn.f16x2.e2m1x2 %3, b3; }\n"
+      : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+      : "r"(w));
+}
+// Two e4m3 bytes -> f16x2.
+__device__ __forceinline__ uint32_t cvt_e4m3x2_to_h2(uint16_t s) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(s));
+  return r;
+}
+__device__ __forceinline__ float2 h2_to_f2(uint32_t h) {
+  __half2 v = *reinterpret_cast<__half2*>(&h);
+  return __half22float2(v);
+}
+__device__ __forceinline__ uint32_t hfma2_u(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ float bf16_bits_to_f(uint16_t b) { return __uint_as_float(((uint32_t)b) << 16); }
+__device__ __forceinline__ float2 bf162_bits_to_f2(uint32_t v) {
+  return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+}
+__device__ __forceinline__ uint32_t f2_to_bf162_bits(float a, float b) {
+  bf162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// ---- launch helper (host) ---------------------------------------------------------------------
+// Launch with the programmatic-stream-serialization attribute so consecutive
+// kernels of a tick overlap their tails/prologues (also inside CUDA graphs).
+extern int g_trl_use_pdl;
+template <typename... KArgs, typename... Args>
+static inline cudaError_t trl_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_trl_use_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}

@@ -1,0 +1,252 @@
+// Gated DeltaNet: token-parallel prep + per-head recurrent scan.
+//
+// Input is the fused projection row [q nk*dk ; k nk*dk ; v nv*dv ; z nv*dv ; a nv ; b nv]
+// (bf16).  D = dk = dv in {64, 128}.
+//
+//   gdn_prep  (grid = tokens): depthwise causal conv (taps read from this tick's rows
+//             or, before the tick's first token, from the per-slot ring of raw rows
+//             indexed by position % 16) + SiLU, L2-norm of q (with 1/sqrt(dk)) and k,
+//             g = -exp(A_log) * softplus(a + dt_bias), beta = sigmoid(b).
+//   gdn_recur (grid = (value head, sequence)): the decay-first delta rule
+//                 S <- e^g S;  d = beta (v - S^T k);  S <- S + k d^T;  o = S^T q
+//             with S[dk, dv] held in registers (thread = (column, k-quarter)), one
+//             block-level reduction per token, raw o to an fp32 scratch; then a
+//             token-parallel epilogue: RMSNorm over dv, * weight, * silu(z) -> bf16.
+//             Also refreshes the ring with the tick's last raw rows, and in "keep"
+//             mode stores the state after each token in planes 0..T-1 (speculative
+//             verify); otherwise the final state goes back to the live plane.
+//
+// State pool: [slots, layers, planes, nv, D, D] fp32; cur[slot] = live plane.
+// Reference parity: kernels_gdn.py:21-126 (prep), :539-744 (fused decode), :746-939
+// (serial-scan prefill) of packages/tilerl-kernels/src/tilerl_kernels; maths
+// reference.py:1142-1277.
+#include "common.cuh"
+
+namespace {
+
+constexpr int RING = 16;
+
+__global__ void __launch_bounds__(256)
+gdn_prep_kernel(const bf16* __restrict__ inp, int ld, const float* __restrict__ conv_w,
+                const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                const bf16* __restrict__ ring, const int* __restrict__ positions,
+                const int* __restrict__ seq_ids, const int* __restrict__ q_start,
+                const int* __restrict__ state_slots, long ring_slot_stride,
+                float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ vc,
+                float* __restrict__ gout, float* __restrict__ bout, int nk, int nv, int D, int KW) {
+  extern __shared__ float sm[];  // [conv_dim] conv+silu result, then [2*nk] norms
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int C = 2 * nk * D + nv * D;
+  const int pos = positions[t];
+  const int seq = seq_ids[t];
+  const int t0 = q_start[seq];
+  const bf16* rg = ring + (size_t)state_slots[seq] * ring_slot_stride;
+  float* cv = sm;
+  float* nrm = sm + C;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < KW; ++j) {  // tap KW-1 multiplies the newest row
+      const int back = KW - 1 - j;
+      const int pj = pos - back;
+      float v = 0.f;
+      if (pj >= 0) {
+        if (t - back >= t0)
+          v = __bfloat162float(inp[(size_t)(t - back) * ld + c]);
+        else
+          v = __bfloat162float(rg[(size_t)(pj % RING) * C + c]);
+      }
+      acc = fmaf(v, conv_w[(size_t)c * KW + j], acc);
+    }
+    cv[c] = silu_f(acc);
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int h = warp; h < 2 * nk; h += nw) {
+    float ss = 0.f;
+    for (int d = lane; d < D; d += 32) {
+      const float v = cv[(size_t)h * D + d];
+      ss += v * v;
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) nrm[h] = rsqrtf(ss + 1e-12f) * (h < nk ? rsqrtf((float)D) : 1.f);
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    if (c < nk * D)
+      qn[(size_t)t * nk * D + c] = cv[c] * nrm[c / D];
+    else if (c < 2 * nk * D)
+      kn[(size_t)t * nk * D + (c - nk * D)] = cv[c] * nrm[c / D];
+    else
+      vc[(size_t)t * nv * D + (c - 2 * nk * D)] = cv[c];
+  }
+  const bf16* ab = inp + (size_t)t * ld + C + nv * D;
+  for (int h = threadIdx.x; h < nv; h += blockDim.x) {
+    const float a = __bfloat162float(ab[h]), b = __bfloat162float(ab[nv + h]);
+    gout[(size_t)t * nv + h] = -__expf(a_log[h]) * softplus_f(a + dt_bias[h]);
+    bout[(size_t)t * nv + h] = sigmoid_f(b);
+  }
+}
+
+// Thread (col, kq): col = tid % D, kq = tid / D in 0..3 owns S[kq*D/4 .. +D/4][col].
+template <int D>
+__global__ void __launch_bounds__(D * 4)
+gdn_recur_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
+                 const float* __restrict__ vc, const float* __restrict__ gin,
+                 const float* __restrict__ bin, const bf16* __restrict__ inp, int ld,
+                 float* __restrict__ states, int* __restrict__ cur, bf16* __restrict__ ring,
+                 const int* __restrict__ q_start, const int* __restrict__ q_len,
+                 const int* __restrict__ positions, const int* __restrict__ state_slots,
+                 const int* __restrict__ keep_flags, long state_slot_stride, long plane_stride,
+                 long ring_slot_stride, const float* __restrict__ norm_w, float eps,
+                 float* __restrict__ o_scratch, bf16* __restrict__ out, int nk, int nv, int planes) {
+  constexpr int KQ = D / 4;
+  __shared__ float s_q[2][D], s_k[2][D];
+  __shared__ float s_part[4][2][D];
+  __shared__ float s_sc[2][4];  // v unused; [buf][g, beta, qk]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int h = blockIdx.x, seq = blockIdx.y;
+  const int col = threadIdx.x % D, kq = threadIdx.x / D;
+  const int T = q_len[seq], t0 = q_start[seq];
+  if (T == 0) return;
+  const int slot = state_slots[seq];
+  const int keep = keep_flags ? keep_flags[seq] : 0;
+  const int kh = h * nk / nv;
+  const int live = cur[slot];
+  float* sbase = states + (size_t)slot * state_slot_stride + (size_t)h * D * D;
+  const float* sin_ = sbase + (size_t)live * plane_stride;
+  float S[KQ];
+#pragma unroll
+  for (int i = 0; i < KQ; ++i) S[i] = sin_[(size_t)(kq * KQ + i) * D + col];
+
+  // prefetch token 0
+  auto load_tok = [&](int i, int b) {
+    const int t = t0 + i;
+    if (threadIdx.x < D) s_q[b][threadIdx.x] = qn[((size_t)t * nk + kh) * D + threadIdx.x];
+    else if (threadIdx.x < 2 * D) s_k[b][threadIdx.x - D] = kn[((size_t)t * nk + kh) * D + threadIdx.x - D];
+  };
+  load_tok(0, 0);
+  __syncthreads();
+  for (int i = 0; i < T; ++i) {
+    const int b = i & 1;
+    const int t = t0 + i;
+    if (i + 1 < T) load_tok(i + 1, b ^ 1);
+    const float g = gin[(size_t)t * nv + h], beta = bin[(size_t)t * nv + h];
+    const float v = vc[((size_t)t * nv + h) * D + col];
+    const float eg = __expf(g);
+    float ks = 0.f, qs = 0.f, qk = 0.f;
+#pragma unroll
+    for (int j = 0; j < KQ; ++j) {
+      const float kk = s_k[b][kq * KQ + j], qq = s_q[b][kq * KQ + j];
+      ks = fmaf(kk, S[j], ks);
+      qs = fmaf(qq, S[j], qs);
+      qk = fmaf(qq, kk, qk);
+    }
+    s_part[kq][0][col] = ks;
+    s_part[kq][1][col] = qs;
+    if (col == 0) s_sc[b][kq] = qk;
+    __syncthreads();
+    const float ksum = s_part[0][0][col] + s_part[1][0][col] + s_part[2][0][col] + s_part[3][0][col];
+    const float qsum = s_part[0][1][col] + s_part[1][1][col] + s_part[2][1][col] + s_part[3][1][col];
+    const float qkd = s_sc[b][0] + s_sc[b][1] + s_sc[b][2] + s_sc[b][3];
+    const float d = beta * (v - eg * ksum);
+#pragma unroll
+    for (int j = 0; j < KQ; ++j) S[j] = fmaf(s_k[b][kq * KQ + j], d, eg * S[j]);
+    if (kq == 0) o_scratch[((size_t)t * nv + h) * D + col] = fmaf(eg, qsum, qkd * d);
+    if (keep && i < planes) {
+      float* sp = sbase + (size_t)i * plane_stride;
+#pragma unroll
+      for (int j = 0; j < KQ; ++j) sp[(size_t)(kq * KQ + j) * D + col] = S[j];
+    }
+    __syncthreads();  // s_part / next token buffers
+  }
+  if (!keep) {
+    float* sp = sbase + (size_t)live * plane_stride;
+#pragma unroll
+    for (int j = 0; j < KQ; ++j) sp[(size_t)(kq * KQ + j) * D + col] = S[j];
+  }
+  // ring refresh: raw q/k rows by the first value head of each key head, v rows by
+  // every head, for the last min(T, RING) tokens of the tick
+  {
+    bf16* rg = ring + (size_t)slot * ring_slot_stride;
+    const int C = 2 * nk * D + nv * D;
+    const int first = max(0, T - RING);
+    const int rep = nv / nk;
+    for (int i = first; i < T; ++i) {
+      const int t = t0 + i;
+      const int rrow = positions[t] % RING;
+      const bf16* src = inp + (size_t)t * ld;
+      bf16* dst = rg + (size_t)rrow * C;
+      if (h % rep == 0) {
+        for (int c = threadIdx.x; c < 2 * D; c += blockDim.x) {
+          const int cc = (c < D) ? kh * D + c : nk * D + kh * D + (c - D);
+          dst[cc] = src[cc];
+        }
+      }
+      for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        const int cc = 2 * nk * D + h * D + c;
+        dst[cc] = src[cc];
+      }
+    }
+  }
+  __syncthreads();
+  __threadfence_block();
+  // epilogue: gated RMSNorm per token, one warp per token
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int C = 2 * nk * D + nv * D;
+  for (int i = warp; i < T; i += nw) {
+    const int t = t0 + i;
+    const float* o = o_scratch + ((size_t)t * nv + h) * D;
+    float ov[D / 32], ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < D / 32; ++j) {
+      ov[j] = o[lane + 32 * j];
+      ss += ov[j] * ov[j];
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)D + eps);
+    const bf16* z = inp + (size_t)t * ld + C + (size_t)h * D;
+#pragma unroll
+    for (int j = 0; j < D / 32; ++j) {
+      const int c = lane + 32 * j;
+      out[((size_t)t * nv + h) * D + c] =
+          __float2bfloat16(ov[j] * rstd * norm_w[c] * silu_f(__bfloat162float(z[c])));
+    }
+  }
+}
+
+}  // namespace
+
+// Scratch (fp32): qn, kn [T*nk*D]; vc, o_scratch [T*nv*D]; g, beta [T*nv].
+TRL_API int trl_gdn(const void* inp, int ld, const void* conv_w, const void* dt_bias, const void* a_log,
+                    const void* norm_w, void* states, void* cur, void* ring, const void* positions,
+                    const void* seq_ids, const void* q_start, const void* q_len,
+                    const void* state_slots, const void* keep_flags, long state_slot_stride,
+                    long plane_stride, long ring_slot_stride, void* qn, void* kn, void* vc, void* g,
+                    void* beta, void* o_scratch, void* out, int T, int B, int nk, int nv, int D, int KW,
+                    int planes, float eps, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  const int C = 2 * nk * D + nv * D;
+  const size_t smem = (size_t)(C + 2 * nk) * sizeof(float);
+  cudaFuncSetAttribute(gdn_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = trl_launch(gdn_prep_kernel, dim3(T), dim3(256), smem, st, (const bf16*)inp, ld,
+                             (const float*)conv_w, (const float*)dt_bias, (const float*)a_log,
+                             (const bf16*)ring, (const int*)positions, (const int*)seq_ids,
+                             (const int*)q_start, (const int*)state_slots, ring_slot_stride,
+                             (float*)qn, (float*)kn, (float*)vc, (float*)g, (float*)beta, nk, nv, D, KW);
+  if (e != cudaSuccess) return (int)e;
+#define RECUR(DD)                                                                                   \
+  e = trl_launch(gdn_recur_kernel<DD>, dim3(nv, B), dim3(DD * 4), 0, st, (const float*)qn,          \
+                 (const float*)kn, (const float*)vc, (const float*)g, (const float*)beta,           \
+                 (const bf16*)inp, ld, (float*)states, (int*)cur, (bf16*)ring, (const int*)q_start, \
+                 (const int*)q_len, (const int*)positions, (const int*)state_slots,                 \
+                 (const int*)keep_flags, state_slot_stride, plane_stride, ring_slot_stride,         \
+                 (const float*)norm_w, eps, (float*)o_scratch, (bf16*)out, nk, nv, planes)
+  if (D == 128) RECUR(128);
+  else if (D == 64) RECUR(64);
+  else return (int)cudaErrorInvalidValue;
+#undef RECUR
+  return (int)e;
+}

@@ -1,0 +1,423 @@
+// Skinny (M <= 4 rows per pass) weight-streaming linears for the decode tick.
+//
+//   y[m, n] = epi( tscale * sum_k x'[m, k] * W[n, k] )
+//
+// * W is NVFP4 in the checkpoint layout: e2m1 nibbles [N, K/2] (low nibble = even
+//   k), one e4m3 scale per 16 k [N, K/16], one fp32 tensor scale -- or bf16 [N, K].
+// * x' = x, or RMSNorm(x) * norm_w when norm_w != nullptr: the norm is folded into
+//   the prologue, every CTA recomputes it from the (L2-resident) activation row.
+// * epi: plain store | + residual | SwiGLU on interleaved (gate, up) row pairs.
+//
+// The kernel is HBM-bound by construction: each warp owns R consecutive weight
+// rows and walks K in 32-weight chunks with 128-bit streaming loads (R*U loads
+// in flight per lane).  The activation lives in shared memory as f16, pre-scaled
+// by a per-row power of two so that a 16-element block sum cannot overflow, in a
+// chunk-interleaved layout that makes the four 16-byte reads per chunk
+// bank-conflict free.  e2m1 -> f16x2 uses the native cvt; products accumulate in
+// f16x2 within one 16-element scale block (exact products: 2-bit x 8-bit
+// mantissas), then promote to fp32 with the block scale.
+//
+// Reference parity: `linear_fp4_gemv` / `linear_bf16_gemv` of
+// packages/tilerl-kernels/src/tilerl_kernels/kernels_linear.py:924-1097.
+#include "common.cuh"
+
+__device__ TrlError g_trl_error = {0, 0, 0, 0};
+int g_trl_use_pdl = 1;
+
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_STORE_F32 = 3 };
+
+namespace {
+
+constexpr int GEMV_THREADS = 512;
+
+// Stage x (bf16 [M, K], optional RMSNorm) into shared memory as scaled f16.
+// Layout per row m: piece p (8 halves) of 32-element chunk c sits at
+// ((p * nchunks + c) * 8) halves.  Returns nothing; xs_inv[m] = 1 / applied scale.
+template <int M>
+__device__ __forceinline__ void stage_x(const bf16* __restrict__ x, int ldx, int K,
+                                        const float* __restrict__ norm_w, float eps,
+                                        __half* xs, float* xs_inv, float* red) {
+  const int nchunks = K >> 5;
+#pragma unroll
+  for (int m = 0; m < M; ++m) {
+    const bf16* xr = x + (size_t)m * ldx;
+    float rstd = 1.f;
+    if (norm_w != nullptr) {
+      float ss = 0.f;
+      for (int k = threadIdx.x * 2; k < K; k += blockDim.x * 2) {
+        float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(xr + k));
+        ss += v.x * v.x + v.y * v.y;
+      }
+      ss = block_sum(ss, red);
+      rstd = rsqrtf(ss / (float)K + eps);
+    }
+    float amax = 0.f;
+    for (int k = threadIdx.x * 2; k < K; k += blockDim.x * 2) {
+      float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(xr + k));
+      if (norm_w != nullptr) {
+        // the unfused path rounds the normalised row to bf16; do the same
+        v.x = __bfloat162float(__float2bfloat16(v.x * rstd * norm_w[k]));
+        v.y = __bfloat162float(__float2bfloat16(v.y * rstd * norm_w[k + 1]));
+      }
+      amax = fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y)));
+    }
+    amax = block_max(amax, red);
+    // power-of-two scale s with amax * s <= 256: 16 products of |w| <= 6 stay < 65504
+    int e = 0;
+    if (amax > 0.f) {
+      frexpf(amax, &e);  // amax = f * 2^e, f in [0.5, 1)
+    }
+    const float s = exp2f((float)(8 - e));
+    if (threadIdx.x == 0) xs_inv[m] = exp2f((float)(e - 8));
+    __half* dst = xs + (size_t)m * K;
+    for (int k = threadIdx.x * 2; k < K; k += blockDim.x * 2) {
+      float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(xr + k));
+      if (norm_w != nullptr) {
+        v.x = __bfloat162float(__float2bfloat16(v.x * rstd * norm_w[k]));
+        v.y = __bfloat162float(__float2bfloat16(v.y * rstd * norm_w[k + 1]));
+      }
+      const int c = k >> 5, p = (k >> 3) & 3, o = k & 7;
+      *reinterpret_cast<__half2*>(dst + ((size_t)(p * nchunks + c) << 3) + o) =
+          __floats2half2_rn(v.x * s, v.y * s);
+    }
+  }
+  __syncthreads();
+}
+
+template <int M, int R, int EPI>
+__global__ void __launch_bounds__(GEMV_THREADS, 1)
+gemv_nvfp4_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ wq,
+                  const uint8_t* __restrict__ wscale, const float* __restrict__ tscale,
+                  const float* __restrict__ norm_w, float eps, const bf16* __restrict__ residual,
+                  int ldr, void* __restrict__ yout, int ldy, int N, int K) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __half* xs = reinterpret_cast<__half*>(smem_raw);
+  float* xs_inv = reinterpret_cast<float*>(smem_raw + (size_t)M * K * sizeof(__half));
+  float* red = xs_inv + 8;
+  pdl_launch_dependents();
+  pdl_wait();
+  stage_x<M>(x, ldx, K, norm_w, eps, xs, xs_inv, red);
+
+  const int lane = threadIdx.x & 31;
+  const int warp = blockIdx.x * (GEMV_THREADS / 32) + (threadIdx.x >> 5);
+  const int nwarps = gridDim.x * (GEMV_THREADS / 32);
+  const int nchunks = K >> 5;
+  const size_t row_bytes = (size_t)K >> 1, srow_bytes = (size_t)K >> 4;
+  const float ts = *tscale;
+
+  for (int r0 = warp * R; r0 < N; r0 += nwarps * R) {
+    float acc[R][M];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
+    const uint8_t* wrow[R];
+    const uint8_t* srow[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int rr = min(r0 + r, N - 1);
+      wrow[r] = wq + (size_t)rr * row_bytes;
+      srow[r] = wscale + (size_t)rr * srow_bytes;
+    }
+    // software pipeline: the loads of chunk c+32 are in flight while chunk c is consumed
+    uint4 wv[R], wn[R];
+    uint16_t sv[R], sn[R];
+    if (lane < nchunks) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        wv[r] = ldg_stream_16(wrow[r] + ((size_t)lane << 4));
+        sv[r] = ldg_stream_2(srow[r] + ((size_t)lane << 1));
+      }
+    }
+    for (int c = lane; c < nchunks; c += 32) {
+      const int cn = c + 32;
+      if (cn < nchunks) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          wn[r] = ldg_stream_16(wrow[r] + ((size_t)cn << 4));
+          sn[r] = ldg_stream_2(srow[r] + ((size_t)cn << 1));
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        uint32_t xh[16];
+        const __half* xm = xs + (size_t)m * K;
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          uint4 t = *reinterpret_cast<const uint4*>(xm + ((size_t)(p * nchunks + c) << 3));
+          xh[p * 4 + 0] = t.x, xh[p * 4 + 1] = t.y, xh[p * 4 + 2] = t.z, xh[p * 4 + 3] = t.w;
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const float2 sc = h2_to_f2(cvt_e4m3x2_to_h2(sv[r]));
+          const uint32_t w4[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
+#pragma unroll
+          for (int blk = 0; blk < 2; ++blk) {
+            uint32_t a = 0u;  // f16x2 zero
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              uint32_t h[4];
+              cvt_e2m1x8_to_h2x4(w4[blk * 2 + q], h);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) a = hfma2_u(h[i], xh[(blk * 2 + q) * 4 + i], a);
+            }
+            const float2 af = h2_to_f2(a);
+            acc[r][m] = fmaf(blk == 0 ? sc.x : sc.y, af.x + af.y, acc[r][m]);
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < R; ++r) wv[r] = wn[r], sv[r] = sn[r];
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]) * ts * xs_inv[m];
+
+    if (EPI == EPI_SWIGLU) {
+      // rows (2j, 2j+1) = (gate_j, up_j); R is even and r0 is a multiple of R
+      if (lane < (R / 2) * M) {
+        const int j = lane / M, m = lane % M;
+        float g = 0.f, u = 0.f;
+#pragma unroll
+        for (int r = 0; r < R; r += 2)
+#pragma unroll
+          for (int mm = 0; mm < M; ++mm)
+            if (r / 2 == j && mm == m) g = acc[r][mm], u = acc[r + 1][mm];
+        const int n = r0 + 2 * j;
+        if (n + 1 < N)
+          reinterpret_cast<bf16*>(yout)[(size_t)m * ldy + (n >> 1)] = __float2bfloat16(silu_f(g) * u);
+      }
+    } else {
+      if (lane < R * M) {
+        const int r = lane / M, m = lane % M;
+        float v = 0.f;
+#pragma unroll
+        for (int rr = 0; rr < R; ++rr)
+#pragma unroll
+          for (int mm = 0; mm < M; ++mm)
+            if (rr == r && mm == m) v = acc[rr][mm];
+        const int n = r0 + r;
+        if (n < N) {
+          if (EPI == EPI_RESIDUAL) v += __bfloat162float(residual[(size_t)m * ldr + n]);
+          if (EPI == EPI_STORE_F32)
+            reinterpret_cast<float*>(yout)[(size_t)m * ldy + n] = v;
+          else
+            reinterpret_cast<bf16*>(yout)[(size_t)m * ldy + n] = __float2bfloat16(v);
+        }
+      }
+    }
+  }
+}
+
+// bf16 weights [N, K]: fp32 FMA, 8 weights per 16-byte load.  x staged as fp32.
+template <int M, int R, int EPI>
+__global__ void __launch_bounds__(GEMV_THREADS, 1)
+gemv_bf16_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w,
+                 const float* __restrict__ norm_w, float eps, const bf16* __restrict__ residual,
+                 int ldr, void* __restrict__ yout, int ldy, int N, int K) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* xs = reinterpret_cast<float*>(smem_raw);
+  float* red = xs + (size_t)M * K;
+  pdl_launch_dependents();
+  pdl_wait();
+#pragma unroll
+  for (int m = 0; m < M; ++m) {
+    const bf16* xr = x + (size_t)m * ldx;
+    float rstd = 1.f;
+    if (norm_w != nullptr) {
+      float ss = 0.f;
+      for (int k = threadIdx.x; k < K; k += blockDim.x) {
+        float v = __bfloat162float(xr[k]);
+        ss += v * v;
+      }
+      ss = block_sum(ss, red);
+      rstd = rsqrtf(ss / (float)K + eps);
+    }
+    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+      float v = __bfloat162float(xr[k]);
+      if (norm_w != nullptr) v = __bfloat162float(__float2bfloat16(v * rstd * norm_w[k]));
+      xs[(size_t)m * K + k] = v;
+    }
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int warp = blockIdx.x * (GEMV_THREADS / 32) + (threadIdx.x >> 5);
+  const int nwarps = gridDim.x * (GEMV_THREADS / 32);
+  const int nvec = K >> 3;
+  for (int r0 = warp * R; r0 < N; r0 += nwarps * R) {
+    float acc[R][M];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
+    for (int c = lane; c < nvec; c += 32) {
+      uint4 wv[R];
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+        wv[r] = ldg_stream_16(w + (size_t)min(r0 + r, N - 1) * K + ((size_t)c << 3));
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        const float4 x0 = *reinterpret_cast<const float4*>(xs + (size_t)m * K + (c << 3));
+        const float4 x1 = *reinterpret_cast<const float4*>(xs + (size_t)m * K + (c << 3) + 4);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          float2 a = bf162_bits_to_f2(wv[r].x), b = bf162_bits_to_f2(wv[r].y);
+          float2 cc = bf162_bits_to_f2(wv[r].z), d = bf162_bits_to_f2(wv[r].w);
+          float s = acc[r][m];
+          s = fmaf(a.x, x0.x, s), s = fmaf(a.y, x0.y, s), s = fmaf(b.x, x0.z, s), s = fmaf(b.y, x0.w, s);
+          s = fmaf(cc.x, x1.x, s), s = fmaf(cc.y, x1.y, s), s = fmaf(d.x, x1.z, s), s = fmaf(d.y, x1.w, s);
+          acc[r][m] = s;
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]);
+    if (lane < R * M) {
+      const int r = lane / M, m = lane % M;
+      float v = 0.f;
+#pragma unroll
+      for (int rr = 0; rr < R; ++rr)
+#pragma unroll
+        for (int mm = 0; mm < M; ++mm)
+          if (rr == r && mm == m) v = acc[rr][mm];
+      const int n = r0 + r;
+      if (n < N) {
+        if (EPI == EPI_RESIDUAL) v += __bfloat162float(residual[(size_t)m * ldr + n]);
+        if (EPI == EPI_STORE_F32)
+          reinterpret_cast<float*>(yout)[(size_t)m * ldy + n] = v;
+        else
+          reinterpret_cast<bf16*>(yout)[(size_t)m * ldy + n] = __float2bfloat16(v);
+      }
+    }
+  }
+}
+
+int g_num_sms = 0;
+int num_sms() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return g_num_sms;
+}
+
+template <int M, int R, int EPI>
+cudaError_t launch_nvfp4(const bf16* x, int ldx, const uint8_t* wq, const uint8_t* ws, const float* ts,
+                         const float* norm_w, float eps, const bf16* res, int ldr, void* y, int ldy,
+                         int N, int K, cudaStream_t st) {
+  const size_t smem = (size_t)M * K * sizeof(__half) + 8 * sizeof(float) + 32 * sizeof(float);
+  auto kern = gemv_nvfp4_kernel<M, R, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    configured = true;
+  }
+  const int warps_needed = (N + R - 1) / R;
+  int grid = min(num_sms(), (warps_needed + GEMV_THREADS / 32 - 1) / (GEMV_THREADS / 32));
+  return trl_launch(kern, dim3(grid), dim3(GEMV_THREADS), smem, st, x, ldx, wq, ws, ts, norm_w, eps,
+                    res, ldr, y, ldy, N, K);
+}
+
+template <int M, int EPI>
+cudaError_t dispatch_r(const bf16* x, int ldx, const uint8_t* wq, const uint8_t* ws, const float* ts,
+                       const float* norm_w, float eps, const bf16* res, int ldr, void* y, int ldy,
+                       int N, int K, cudaStream_t st) {
+  // enough row blocks to give every warp of a full grid at least two -> R = 4
+  const int full_warps = num_sms() * (GEMV_THREADS / 32);
+  if (N >= full_warps * 4 * 2)
+    return launch_nvfp4<M, 4, EPI>(x, ldx, wq, ws, ts, norm_w, eps, res, ldr, y, ldy, N, K, st);
+  return launch_nvfp4<M, 2, EPI>(x, ldx, wq, ws, ts, norm_w, eps, res, ldr, y, ldy, N, K, st);
+}
+
+template <int EPI>
+cudaError_t dispatch_m(int M, const bf16* x, int ldx, const uint8_t* wq, const uint8_t* ws,
+                       const float* ts, const float* norm_w, float eps, const bf16* res, int ldr,
+                       void* y, int ldy, int N, int K, cudaStream_t st) {
+  switch (M) {
+    case 1: return dispatch_r<1, EPI>(x, ldx, wq, ws, ts, norm_w, eps, res, ldr, y, ldy, N, K, st);
+    case 2: return dispatch_r<2, EPI>(x, ldx, wq, ws, ts, norm_w, eps, res, ldr, y, ldy, N, K, st);
+    case 3: return dispatch_r<3, EPI>(x, ldx, wq, ws, ts, norm_w, eps, res, ldr, y, ldy, N, K, st);
+    case 4: return dispatch_r<4, EPI>(x, ldx, wq, ws, ts, norm_w, eps, res, ldr, y, ldy, N, K, st);
+  }
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+// y: bf16 (or fp32 for EPI_STORE_F32).  M up to 4 per pass; larger M is looped.
+// K must be a multiple of 32 and M*K*2 bytes must fit in shared memory (<= ~190 KB).
+TRL_API int trl_gemv_nvfp4(const void* x, int ldx, const void* wq, const void* wscale, const void* tscale,
+                           const void* norm_w, float eps, const void* residual, int ldr, void* y, int ldy,
+                           int M, int N, int K, int epi, void* stream) {
+  if (K % 32 != 0 || N <= 0 || M <= 0) return (int)cudaErrorInvalidValue;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t ysz = (epi == EPI_STORE_F32) ? 4 : 2;
+  int per = 4;
+  while (per > 1 && (size_t)per * K * 2 > 190 * 1024) --per;
+  for (int m0 = 0; m0 < M; m0 += per) {
+    const int mm = min(per, M - m0);
+    const bf16* xp = (const bf16*)x + (size_t)m0 * ldx;
+    const bf16* rp = residual ? (const bf16*)residual + (size_t)m0 * ldr : nullptr;
+    void* yp = (char*)y + (size_t)m0 * ldy * ysz;
+    cudaError_t e;
+    switch (epi) {
+      case EPI_STORE: e = dispatch_m<EPI_STORE>(mm, xp, ldx, (const uint8_t*)wq, (const uint8_t*)wscale, (const float*)tscale, (const float*)norm_w, eps, rp, ldr, yp, ldy, N, K, st); break;
+      case EPI_RESIDUAL: e = dispatch_m<EPI_RESIDUAL>(mm, xp, ldx, (const uint8_t*)wq, (const uint8_t*)wscale, (const float*)tscale, (const float*)norm_w, eps, rp, ldr, yp, ldy, N, K, st); break;
+      case EPI_SWIGLU: e = dispatch_m<EPI_SWIGLU>(mm, xp, ldx, (const uint8_t*)wq, (const uint8_t*)wscale, (const float*)tscale, (const float*)norm_w, eps, rp, ldr, yp, ldy, N, K, st); break;
+      case EPI_STORE_F32: e = dispatch_m<EPI_STORE_F32>(mm, xp, ldx, (const uint8_t*)wq, (const uint8_t*)wscale, (const float*)tscale, (const float*)norm_w, eps, rp, ldr, yp, ldy, N, K, st); break;
+      default: return (int)cudaErrorInvalidValue;
+    }
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
+}
+
+TRL_API int trl_gemv_bf16(const void* x, int ldx, const void* w, const void* norm_w, float eps,
+                          const void* residual, int ldr, void* y, int ldy, int M, int N, int K, int epi,
+                          void* stream) {
+  if (K % 8 != 0 || N <= 0 || M <= 0) return (int)cudaErrorInvalidValue;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t ysz = (epi == EPI_STORE_F32) ? 4 : 2;
+  int per = 4;
+  while (per > 1 && (size_t)per * K * 4 > 190 * 1024) --per;
+  for (int m0 = 0; m0 < M; m0 += per) {
+    const int mm = min(per, M - m0);
+    const bf16* xp = (const bf16*)x + (size_t)m0 * ldx;
+    const bf16* rp = residual ? (const bf16*)residual + (size_t)m0 * ldr : nullptr;
+    void* yp = (char*)y + (size_t)m0 * ldy * ysz;
+    const size_t smem = (size_t)mm * K * 4 + 32 * 4;
+    const int grid = min(num_sms(), (N / 2 + GEMV_THREADS / 32 - 1) / (GEMV_THREADS / 32) + 1);
+    cudaError_t e = cudaErrorInvalidValue;
+#define BF16_CASE(MM, EP)                                                                          \
+  if (mm == MM && epi == EP) {                                                                     \
+    auto kern = gemv_bf16_kernel<MM, 2, EP>;                                                       \
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);           \
+    e = trl_launch(kern, dim3(grid), dim3(GEMV_THREADS), smem, st, xp, ldx, (const bf16*)w,        \
+                   (const float*)norm_w, eps, rp, ldr, yp, ldy, N, K);                             \
+  }
+    BF16_CASE(1, EPI_STORE) BF16_CASE(2, EPI_STORE) BF16_CASE(3, EPI_STORE) BF16_CASE(4, EPI_STORE)
+    BF16_CASE(1, EPI_STORE_F32) BF16_CASE(2, EPI_STORE_F32) BF16_CASE(3, EPI_STORE_F32) BF16_CASE(4, EPI_STORE_F32)
+    BF16_CASE(1, EPI_RESIDUAL) BF16_CASE(2, EPI_RESIDUAL) BF16_CASE(3, EPI_RESIDUAL) BF16_CASE(4, EPI_RESIDUAL)
+#undef BF16_CASE
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
+}
+
+TRL_API void trl_set_pdl(int on) { g_trl_use_pdl = on; }
+
+TRL_API int trl_error_read(int* out4, int clear) {
+  TrlError h;
+  cudaError_t e = cudaMemcpyFromSymbol(&h, g_trl_error, sizeof(h));
+  if (e != cudaSuccess) return (int)e;
+  out4[0] = h.code, out4[1] = h.a, out4[2] = h.b, out4[3] = h.c;
+  if (clear && h.code != 0) {
+    TrlError z = {0, 0, 0, 0};
+    cudaMemcpyToSymbol(g_trl_error, &z, sizeof(z));
+  }
+  return 0;
+}

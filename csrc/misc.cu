@@ -1,0 +1,286 @@
+// Small memory-bound ops: embedding gather, standalone RMSNorm, SwiGLU on interleaved
+// (gate, up) columns, row argmax, gather of rows, fused AdamW, NVFP4 (re)quantisation.
+// Reference parity: kernels.py:30-200 (rmsnorm), :361-403 (silu_mul), :464-509
+// (embedding) of packages/tilerl-kernels/src/tilerl_kernels; AdamW src/tilerl/autograd.py:466;
+// requantize_fp4 src/tilerl/model.py:1255-1296.
+#include "common.cuh"
+
+namespace {
+
+__global__ void embedding_kernel(const bf16* __restrict__ table, const int* __restrict__ ids,
+                                 bf16* __restrict__ out, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)ids[t] * H);
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)t * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+__global__ void gather_rows_kernel(const bf16* __restrict__ x, const int* __restrict__ idx,
+                                   bf16* __restrict__ out, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)idx[t] * H);
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)t * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(const bf16* __restrict__ x, const float* __restrict__ w, bf16* __restrict__ out, int H,
+               float eps) {
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const bf16* xr = x + (size_t)blockIdx.x * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
+    float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(xr + i));
+    ss += v.x * v.x + v.y * v.y;
+  }
+  ss = block_sum(ss, red);
+  const float rstd = rsqrtf(ss / (float)H + eps);
+  bf16* o = out + (size_t)blockIdx.x * H;
+  for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
+    float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(xr + i));
+    *reinterpret_cast<bf162*>(o + i) = __floats2bfloat162_rn(v.x * rstd * w[i], v.y * rstd * w[i + 1]);
+  }
+}
+
+__global__ void swiglu_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, long n_out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n_out; i += (long)gridDim.x * blockDim.x) {
+    float2 v = __bfloat1622float2(reinterpret_cast<const bf162*>(gu)[i]);
+    out[i] = __float2bfloat16(silu_f(v.x) * v.y);
+  }
+}
+
+__global__ void __launch_bounds__(1024)
+argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__ out) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const float* row = logits + (size_t)blockIdx.x * ld;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = row[i];
+    if (v > best) best = v, bi = i;  // strided scan keeps the lowest index on ties per thread
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) best = ov, bi = oi;
+  }
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (lane == 0) sv[w] = best, si[w] = bi;
+  __syncthreads();
+  if (w == 0) {
+    best = lane < (blockDim.x >> 5) ? sv[lane] : -INFINITY;
+    bi = lane < (blockDim.x >> 5) ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) best = ov, bi = oi;
+    }
+    if (lane == 0) out[blockIdx.x] = bi;
+  }
+}
+
+// Fused AdamW on fp32 master + moments; optionally refreshes a bf16 copy.
+__global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
+                             const float* __restrict__ g, bf16* __restrict__ p_bf16, long n, float lr,
+                             float b1, float b2, float eps, float wd, float c1, float c2, float gscale) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    const float gi = g[i] * gscale;
+    const float mi = b1 * m[i] + (1.f - b1) * gi;
+    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+    m[i] = mi, v[i] = vi;
+    float w = p[i] * (1.f - lr * wd);
+    w -= lr * (mi / c1) / (sqrtf(vi / c2) + eps);
+    p[i] = w;
+    if (p_bf16) p_bf16[i] = __float2bfloat16(w);
+  }
+}
+
+// NVFP4 quantisation of a dense [N, K] matrix with a given tensor scale: one thread
+// per 16-element block; writes 8 packed bytes + 1 e4m3 scale.
+template <typename T>
+__global__ void quant_nvfp4_kernel(const T* __restrict__ w, const float* __restrict__ tscale,
+                                   uint8_t* __restrict__ wq, uint8_t* __restrict__ sc, long nblocks) {
+  const float ts = *tscale;
+  for (long b = blockIdx.x * (long)blockDim.x + threadIdx.x; b < nblocks; b += (long)gridDim.x * blockDim.x) {
+    float x[16];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      x[i] = (float)w[b * 16 + i];
+      amax = fmaxf(amax, fabsf(x[i]));
+    }
+    float s = fminf(amax / 6.f / ts, 448.f);
+    // round the block scale to e4m3 and read it back
+    uint16_t s8;
+    asm("{ .reg .b16 t; cvt.rn.satfinite.e4m3x2.f32 t, %1, %2; mov.b16 %0, t; }" : "=h"(s8) : "f"(0.f), "f"(s));
+    const float sf = h2_to_f2(cvt_e4m3x2_to_h2(s8)).x;
+    const float denom = sf * ts;
+    uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
+      const float a = denom > 0.f ? x[i] / denom : 0.f, c = denom > 0.f ? x[i + 1] / denom : 0.f;
+      uint16_t byte;
+      asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u16.u8 %0, t; }" : "=h"(byte) : "f"(c), "f"(a));
+      packed[i / 8] |= ((uint32_t)(byte & 0xff)) << ((i % 8) * 4);
+    }
+    reinterpret_cast<uint2*>(wq)[b] = make_uint2(packed[0], packed[1]);
+    sc[b] = (uint8_t)(s8 & 0xff);
+  }
+}
+
+// NVFP4 -> bf16 dense matrix (8 elements per thread).
+__global__ void dequant_nvfp4_kernel(const uint8_t* __restrict__ wq, const uint8_t* __restrict__ sc,
+                                     const float* __restrict__ tscale, bf16* __restrict__ out, long n8) {
+  const float ts = *tscale;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    const uint32_t w = reinterpret_cast<const uint32_t*>(wq)[i];
+    const uint16_t s2 = (uint16_t)sc[i >> 1];
+    const float s = h2_to_f2(cvt_e4m3x2_to_h2(s2)).x * ts;
+    uint32_t h[4];
+    cvt_e2m1x8_to_h2x4(w, h);
+    uint4 o;
+    float2 f;
+    f = h2_to_f2(h[0]); o.x = f2_to_bf162_bits(f.x * s, f.y * s);
+    f = h2_to_f2(h[1]); o.y = f2_to_bf162_bits(f.x * s, f.y * s);
+    f = h2_to_f2(h[2]); o.z = f2_to_bf162_bits(f.x * s, f.y * s);
+    f = h2_to_f2(h[3]); o.w = f2_to_bf162_bits(f.x * s, f.y * s);
+    reinterpret_cast<uint4*>(out)[i] = o;
+  }
+}
+
+// out[i] = a[i] + b[i] (bf16), used by the large-M path where the residual add is
+// not folded into a GEMV epilogue.
+__global__ void add_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, bf16* __restrict__ out, long n2) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n2; i += (long)gridDim.x * blockDim.x) {
+    float2 x = __bfloat1622float2(reinterpret_cast<const bf162*>(a)[i]);
+    float2 y = __bfloat1622float2(reinterpret_cast<const bf162*>(b)[i]);
+    reinterpret_cast<bf162*>(out)[i] = __floats2bfloat162_rn(x.x + y.x, x.y + y.y);
+  }
+}
+
+// Device-side tick advance: feed each row's sampled token back as the next input,
+// bump position / KV length, recompute the KV write slot from the block table and
+// append the token to a history row.  Lets a captured decode tick be replayed
+// back to back with no host round trip.
+__global__ void decode_advance_kernel(const int* __restrict__ tok, int* __restrict__ ids,
+                                      int* __restrict__ pos, int* __restrict__ smap,
+                                      int* __restrict__ kvlen, const int* __restrict__ table, int B,
+                                      int max_blocks, int* __restrict__ hist, int hist_cap,
+                                      int* __restrict__ hist_n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r < B) {
+    const int p = pos[r] + 1;
+    ids[r] = tok[r];
+    pos[r] = p;
+    kvlen[r] = p + 1;
+    const int pg = min(p / 16, max_blocks - 1);
+    smap[r] = table[(size_t)r * max_blocks + pg] * 16 + (p % 16);
+    const int n = *hist_n;
+    if (hist && n < hist_cap) hist[(size_t)r * hist_cap + n] = tok[r];
+  }
+  __syncthreads();
+  if (r == 0) *hist_n = min(*hist_n + 1, hist_cap);
+}
+
+template <typename T>
+__global__ void absmax_kernel(const T* __restrict__ w, long n, float* __restrict__ out) {
+  __shared__ float red[32];
+  float a = 0.f;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x)
+    a = fmaxf(a, fabsf((float)w[i]));
+  a = block_max(a, red);
+  if (threadIdx.x == 0) atomicMax(reinterpret_cast<int*>(out), __float_as_int(a));  // a >= 0
+}
+
+__global__ void tscale_kernel(const float* amax, float* ts) { *ts = fmaxf(*amax, 1e-30f) / (6.f * 448.f); }
+
+}  // namespace
+
+TRL_API int trl_embedding(const void* table, const void* ids, void* out, int T, int H, void* stream) {
+  return (int)trl_launch(embedding_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream,
+                         (const bf16*)table, (const int*)ids, (bf16*)out, H);
+}
+TRL_API int trl_gather_rows(const void* x, const void* idx, void* out, int T, int H, void* stream) {
+  return (int)trl_launch(gather_rows_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream,
+                         (const bf16*)x, (const int*)idx, (bf16*)out, H);
+}
+TRL_API int trl_rmsnorm(const void* x, const void* w, void* out, int T, int H, float eps, void* stream) {
+  return (int)trl_launch(rmsnorm_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, (const bf16*)x,
+                         (const float*)w, (bf16*)out, H, eps);
+}
+TRL_API int trl_swiglu(const void* gu, void* out, long n_out, void* stream) {
+  const int grid = (int)min((n_out + 255) / 256, (long)148 * 8);
+  return (int)trl_launch(swiglu_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const bf16*)gu,
+                         (bf16*)out, n_out);
+}
+TRL_API int trl_argmax(const void* logits, int ld, int M, int V, void* out, void* stream) {
+  return (int)trl_launch(argmax_kernel, dim3(M), dim3(1024), 0, (cudaStream_t)stream,
+                         (const float*)logits, ld, V, (int*)out);
+}
+TRL_API int trl_adamw(void* p, void* m, void* v, const void* g, void* p_bf16, long n, float lr, float b1,
+                      float b2, float eps, float wd, int step, float gscale, void* stream) {
+  const float c1 = 1.f - powf(b1, (float)step), c2 = 1.f - powf(b2, (float)step);
+  const int grid = (int)min((n + 255) / 256, (long)148 * 16);
+  adamw_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((float*)p, (float*)m, (float*)v, (const float*)g,
+                                                       (bf16*)p_bf16, n, lr, b1, b2, eps, wd, c1, c2, gscale);
+  return (int)cudaGetLastError();
+}
+// dtype: 0 = fp32, 1 = bf16.  amax_tmp: one fp32 of scratch (zeroed here).  If
+// fixed_tscale != 0 the tensor scale in `tscale` is kept, else it is recomputed.
+TRL_API int trl_quant_nvfp4(const void* w, int dtype, long N, long K, void* wq, void* scale, void* tscale,
+                            void* amax_tmp, int fixed_tscale, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  const long n = N * K, nb = n / 16;
+  const int grid = (int)min((nb + 255) / 256, (long)148 * 16);
+  if (!fixed_tscale) {
+    cudaMemsetAsync(amax_tmp, 0, 4, st);
+    if (dtype == 0) absmax_kernel<float><<<grid, 256, 0, st>>>((const float*)w, n, (float*)amax_tmp);
+    else absmax_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)w, n, (float*)amax_tmp);
+    tscale_kernel<<<1, 1, 0, st>>>((const float*)amax_tmp, (float*)tscale);
+  }
+  if (dtype == 0)
+    quant_nvfp4_kernel<float><<<grid, 256, 0, st>>>((const float*)w, (const float*)tscale, (uint8_t*)wq, (uint8_t*)scale, nb);
+  else
+    quant_nvfp4_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)w, (const float*)tscale, (uint8_t*)wq, (uint8_t*)scale, nb);
+  return (int)cudaGetLastError();
+}
+
+TRL_API int trl_dequant_nvfp4(const void* wq, const void* scale, const void* tscale, void* out, long N,
+                              long K, void* stream) {
+  const long n8 = N * K / 8;
+  const int grid = (int)min((n8 + 255) / 256, (long)148 * 32);
+  dequant_nvfp4_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)wq, (const uint8_t*)scale,
+                                                               (const float*)tscale, (bf16*)out, n8);
+  return (int)cudaGetLastError();
+}
+TRL_API int trl_add(const void* a, const void* b, void* out, long n, void* stream) {
+  const long n2 = n / 2;
+  const int grid = (int)min((n2 + 255) / 256, (long)148 * 16);
+  return (int)trl_launch(add_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const bf16*)a,
+                         (const bf16*)b, (bf16*)out, n2);
+}
+
+TRL_API int trl_decode_advance(const void* tok, void* ids, void* pos, void* smap, void* kvlen,
+                               const void* table, int B, int max_blocks, void* hist, int hist_cap,
+                               void* hist_n, void* stream) {
+  return (int)trl_launch(decode_advance_kernel, dim3((B + 127) / 128), dim3(128), 0, (cudaStream_t)stream,
+                         (const int*)tok, (int*)ids, (int*)pos, (int*)smap, (int*)kvlen, (const int*)table,
+                         B, max_blocks, (int*)hist, hist_cap, (int*)hist_n);
+}

@@ -1,0 +1,180 @@
+"""Per-kernel parity on a B200: each sm_100a kernel against the fp32 torch oracle of
+the same op (``tilerl_b200.ops.ref``), at small shapes that hit every tail and at
+the 27B's real shapes."""
+import math
+
+import pytest
+import torch
+
+from tilerl_b200 import formats as F
+from tilerl_b200.ops import ref
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from tilerl_b200.ops.cuda import CudaOps
+    return CudaOps(DEV)
+
+
+def _q(n, k, seed=0, std=0.02):
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randn(n, k, generator=g) * std
+    return F.quantize_nvfp4(w).to(DEV)
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-9))
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 7, 8])
+@pytest.mark.parametrize("n,k", [(96, 256), (130, 1024), (5120, 6144), (1031, 17408)])
+def test_gemv_nvfp4_plain(ops, m, n, k):
+    w = _q(n, k, seed=n + k)
+    x = (torch.randn(m, k, generator=torch.Generator().manual_seed(m)) * 2).to(DEV, torch.bfloat16)
+    y = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops._gemv(x, w, y)
+    want = ref.linear(x, w)
+    assert _rel(y, want) < 6e-3
+    from tilerl_b200.ops import native
+    assert native.read_error()[0] == 0
+
+
+def test_gemv_nvfp4_fused_norm_residual_swiglu_f32(ops):
+    n, k, m = 1024, 5120, 3
+    w = _q(n, k, seed=5)
+    g = torch.Generator().manual_seed(9)
+    x = (torch.randn(m, k, generator=g) * 30).to(DEV, torch.bfloat16)   # large activations: range scaling
+    nw = (1 + 0.1 * torch.randn(k, generator=g)).to(DEV)
+    y = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops._gemv(x, w, y, norm_w=nw, eps=1e-6)
+    h = ref.rmsnorm(x, nw, 1e-6).to(torch.bfloat16)
+    assert _rel(y, ref.linear(h, w)) < 6e-3
+    res = torch.randn(m, n, generator=g).to(DEV, torch.bfloat16)
+    out = res.clone()
+    ops._gemv(x, w, out, residual=out, epi=1)
+    assert _rel(out, ref.linear(x, w, res)) < 6e-3
+    act = torch.empty(m, n // 2, dtype=torch.bfloat16, device=DEV)
+    ops._gemv(x, w, act, norm_w=nw, eps=1e-6, epi=2)
+    assert _rel(act, ref.swiglu(ref.linear(h, w))) < 1e-2
+    yf = torch.empty(m, n, dtype=torch.float32, device=DEV)
+    ops._gemv(x, w, yf, epi=3)
+    assert _rel(yf, ref.linear(x, w)) < 3e-3
+
+
+def test_gemv_bf16_lm_head_shape(ops):
+    g = torch.Generator().manual_seed(1)
+    n, k = 4099, 5120
+    w = (torch.randn(n, k, generator=g) * 0.02).to(DEV, torch.bfloat16)
+    x = torch.randn(2, k, generator=g).to(DEV, torch.bfloat16)
+    nw = torch.ones(k, device=DEV)
+    y = torch.empty(2, n, dtype=torch.float32, device=DEV)
+    ops._gemv(x, w, y, norm_w=nw, eps=1e-6, epi=3)
+    want = ref.linear(ref.rmsnorm(x, nw, 1e-6).to(torch.bfloat16), w)
+    assert _rel(y, want) < 2e-3
+    tok = ops.argmax(y)
+    assert tok.tolist() == want.argmax(-1).tolist()
+
+
+def test_quant_kernel_bit_exact_and_dequant(ops):
+    g = torch.Generator().manual_seed(3)
+    for dtype in (torch.float32, torch.bfloat16):
+        w = (torch.randn(257, 512, generator=g) * 0.02).to(DEV, dtype)
+        want = F.quantize_nvfp4(w.float())
+        got = F.NVFP4Tensor(torch.empty_like(want.wq), torch.empty_like(want.scale), torch.zeros(1, device=DEV))
+        ops.quantize_nvfp4_(w, got)
+        torch.cuda.synchronize()
+        assert torch.equal(got.tscale.cpu(), want.tscale.cpu())
+        assert torch.equal(got.scale.view(torch.uint8).cpu(), want.scale.view(torch.uint8).cpu())
+        assert torch.equal(got.wq.cpu(), want.wq.cpu())
+        d = ops.dequantize_nvfp4(got)
+        assert torch.allclose(d.float().cpu(), want.dequant().cpu().to(torch.bfloat16).float(), rtol=0, atol=0)
+
+
+def test_small_ops(ops):
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(5, 1024, generator=g).to(DEV, torch.bfloat16)
+    w = torch.rand(1024, generator=g).to(DEV)
+    assert _rel(ops._rmsnorm(x, w, 1e-6), ref.rmsnorm(x, w, 1e-6)) < 5e-3
+    table = torch.randn(100, 1024, generator=g).to(DEV, torch.bfloat16)
+    ids = torch.tensor([3, 99, 0], dtype=torch.int32, device=DEV)
+    assert torch.equal(ops.embed(table, ids), table[ids.long()])
+    gu = torch.randn(4, 512, generator=g).to(DEV, torch.bfloat16)
+    act = torch.empty(4, 256, dtype=torch.bfloat16, device=DEV)
+    ops.lib.trl_swiglu(gu.data_ptr(), act.data_ptr(), act.numel(), torch.cuda.current_stream().cuda_stream)
+    assert _rel(act, ref.swiglu(gu)) < 5e-3
+
+
+@pytest.mark.parametrize("d,n_q,n_kv,rot", [(256, 6, 1, 64), (256, 24, 4, 64), (64, 4, 2, 64), (128, 8, 2, 32)])
+def test_attention_prep_and_paged(ops, d, n_q, n_kv, rot):
+    from tilerl_b200.batch import Batch
+    from tilerl_b200.config import ModelConfig, ATTN
+    cfg = ModelConfig("t", hidden=64, ffn=64, vocab=64, layer_types=(ATTN,), n_q_heads=n_q, n_kv_heads=n_kv,
+                      head_dim=d, rotary_dim=rot, rope_theta=1e7)
+    g = torch.Generator().manual_seed(d + n_q)
+    # two sequences: a decode row with 37 cached tokens, and a 21-token prefill chunk starting at 5
+    seqs = [dict(tokens=[1], start=37, blocks=[3, 7, 2], slot=1),
+            dict(tokens=list(range(21)), start=5, blocks=[4, 9], slot=2)]
+    batch = Batch.build(seqs, DEV)
+    t = batch.n_tokens
+    qkv = torch.randn(t, cfg.qkv_rows, generator=g).to(DEV, torch.bfloat16)
+    qw = (1 + 0.1 * torch.randn(d, generator=g)).to(DEV)
+    kw = (1 + 0.1 * torch.randn(d, generator=g)).to(DEV)
+    blocks = 12
+    kc0 = (torch.randn(blocks, n_kv, 16, d, generator=g)).to(DEV, torch.bfloat16)
+    vc0 = (torch.randn(blocks, n_kv, 16, d, generator=g)).to(DEV, torch.bfloat16)
+
+    class Pool:
+        def __init__(self, k, v):
+            self.k, self.v = k, v
+
+        def layer(self, i):
+            return self.k, self.v
+
+    lp = dict(q_norm=qw, k_norm=kw)
+    pool_ref = Pool(kc0.float().clone(), vc0.float().clone())
+    from tilerl_b200.ops.backend import RefOps
+    want = RefOps().attention(qkv, lp, batch, pool_ref, 0, cfg, n_q, n_kv)
+    for splits in (1, 4):
+        pool = Pool(kc0.clone(), vc0.clone())
+        ops.attn_splits = splits
+        got = ops.attention(qkv, lp, batch, pool, 0, cfg, n_q, n_kv)
+        ops.attn_splits = 0
+        assert _rel(got, want) < 2e-2, splits
+        assert _rel(pool.k, pool_ref.k) < 1e-2 and torch.equal(pool.v.float(), pool_ref.v.to(torch.bfloat16).float())
+
+
+@pytest.mark.parametrize("d,nk,nv", [(128, 2, 6), (64, 4, 4), (128, 16, 48)])
+def test_gdn_kernel(ops, d, nk, nv):
+    from tilerl_b200.batch import Batch
+    from tilerl_b200.config import ModelConfig, GDN
+    from tilerl_b200.kv import GdnStatePool
+    from tilerl_b200.ops.backend import RefOps
+    cfg = ModelConfig("t", hidden=64, ffn=64, vocab=64, layer_types=(GDN,), n_q_heads=2, n_kv_heads=1,
+                      head_dim=64, rotary_dim=64, rope_theta=1e6, gdn_k_heads=nk, gdn_v_heads=nv,
+                      gdn_head_dim=d)
+    g = torch.Generator().manual_seed(d + nv)
+    lp = dict(conv=(torch.randn(cfg.gdn_conv_dim, 4, generator=g) * 0.3).to(DEV),
+              dt_bias=torch.rand(nv, generator=g).to(DEV), a_log=torch.log(1 + 3 * torch.rand(nv, generator=g)).to(DEV),
+              gdn_norm=(1 + 0.1 * torch.randn(d, generator=g)).to(DEV))
+    pools = [GdnStatePool(cfg, 4, DEV, planes=4, ring_dtype=torch.bfloat16) for _ in range(2)]
+    # tick 1: prefill 19 tokens on slot 1, 3 tokens on slot 2; tick 2: decode; tick 3: verify (keep)
+    ticks = [
+        ([dict(tokens=list(range(19)), start=0, blocks=[1, 2], slot=1), dict(tokens=[1, 2, 3], start=0, blocks=[3], slot=2)], 0),
+        ([dict(tokens=[5], start=19, blocks=[1, 2], slot=1), dict(tokens=[6], start=3, blocks=[3], slot=2)], 0),
+        ([dict(tokens=[5, 6, 7], start=20, blocks=[1, 2], slot=1, keep=True)], 3),
+    ]
+    for seqs, keep in ticks:
+        batch = Batch.build(seqs, DEV, keep_steps=keep)
+        inp = (torch.randn(batch.n_tokens, cfg.gdn_in_rows, generator=g)).to(DEV, torch.bfloat16)
+        want = RefOps().gdn(inp, lp, batch, pools[0], 0, cfg, nk, nv)
+        got = ops.gdn(inp, lp, batch, pools[1], 0, cfg, nk, nv)
+        assert _rel(got, want) < 2e-2
+        assert _rel(pools[1].states, pools[0].states) < 1e-3
+        assert torch.equal(pools[1].ring, pools[0].ring)
+        if keep:
+            for p in pools:
+                p.select_step(1, 1)

@@ -39,6 +39,7 @@ class Batch:
     host_kv_len: List[int] = field(default_factory=list)
     keep_rows: List[bool] = field(default_factory=list)   # per sequence: store per-token GDN states
     keep_flags: Optional[torch.Tensor] = None             # [B] int32 device copy of keep_rows
+    h2d_bytes: int = 0
 
     @staticmethod
     def build(seqs: Sequence[dict], device, max_blocks: Optional[int] = None,
@@ -66,11 +67,49 @@ class Batch:
             keep.append(bool(s.get("keep", False)) and keep_steps > 0)
             if blocks:
                 table[r, :len(blocks)] = torch.tensor(blocks, dtype=torch.int32)
-        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
+        device = torch.device(device)
+        arrays = [ids, pos, sid, smap, qs, ql, kl, slots, last, [int(k) for k in keep]]
+        sizes = [len(a) for a in arrays]
+        total = sum(sizes) + table.numel()
+        if device.type == "cuda":
+            # one pinned staging block, one async H2D copy for the whole descriptor
+            host = _pinned(total)
+            flat = host[:total]
+            o = 0
+            for a, n in zip(arrays, sizes):
+                flat[o:o + n] = torch.tensor(a, dtype=torch.int32)
+                o += n
+            flat[o:] = table.reshape(-1)
+            dev = torch.empty(total, dtype=torch.int32, device=device)
+            dev.copy_(flat, non_blocking=True)
+            _PIN["event"].record()
+            views, o = [], 0
+            for n in sizes:
+                views.append(dev[o:o + n])
+                o += n
+            tbl = dev[o:].view(len(seqs), mb)
+        else:
+            views = [torch.tensor(a, dtype=torch.int32) for a in arrays]
+            tbl = table
+        v_ids, v_pos, v_sid, v_smap, v_qs, v_ql, v_kl, v_slots, v_last, v_keep = views
         return Batch(
-            token_ids=i32(ids), positions=i32(pos), seq_ids=i32(sid), slot_mapping=i32(smap),
-            q_start=i32(qs), q_len=i32(ql), kv_len=i32(kl), state_slots=i32(slots),
-            block_table=table.to(device), last_idx=i32(last), n_seqs=len(seqs), n_tokens=t,
+            token_ids=v_ids, positions=v_pos, seq_ids=v_sid, slot_mapping=v_smap,
+            q_start=v_qs, q_len=v_ql, kv_len=v_kl, state_slots=v_slots,
+            block_table=tbl, last_idx=v_last, n_seqs=len(seqs), n_tokens=t,
             max_q_len=max(ql), keep_steps=keep_steps, host_q_len=ql, host_kv_len=kl,
-            keep_rows=keep, keep_flags=i32([int(k) for k in keep]),
+            keep_rows=keep, keep_flags=v_keep, h2d_bytes=total * 4,
         )
+
+
+_PIN = {"buf": None, "event": None}
+
+
+def _pinned(n: int) -> torch.Tensor:
+    """Grow-only pinned staging buffer; waits for the previous copy out of it."""
+    if _PIN["event"] is None:
+        _PIN["event"] = torch.cuda.Event()
+    else:
+        _PIN["event"].synchronize()
+    if _PIN["buf"] is None or _PIN["buf"].numel() < n:
+        _PIN["buf"] = torch.empty(max(n, 1 << 16), dtype=torch.int32).pin_memory()
+    return _PIN["buf"]

@@ -162,6 +162,8 @@ class Engine:
                              finished=0, preempted=0)
         self.timing = os.environ.get("TRL_STEP_TIMING") == "1"
         self.last_tick_ms: Dict[str, float] = {}
+        self.io_h2d = 0   # bytes copied host->device for tick inputs (eager ticks)
+        self.io_d2h = 0   # bytes read back (sampled tokens / logits rows)
 
     # ---- public API -------------------------------------------------------------
     def submit(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
@@ -245,6 +247,12 @@ class Engine:
         idle = not self.has_work()
         return dict(last_progress_age_s=0.0 if idle else time.monotonic() - self._last_progress,
                     degraded=self._degraded, running=len(self._running), waiting=len(self._waiting))
+
+    def io_bytes(self) -> Tuple[int, int]:
+        """(host->device, device->host) bytes moved for tick inputs / sampled tokens."""
+        g = self.graph
+        return (self.io_h2d + (g.h2d_bytes if g is not None else 0),
+                self.io_d2h + (g.d2h_bytes if g is not None else 0))
 
     def stats(self) -> Dict[str, object]:
         return dict(
@@ -404,9 +412,15 @@ class Engine:
             if logits is not None:
                 self.counters["graph_ticks"] += 1
         taps = hidden = None
-        if logits is None:
+        amax = None
+        if logits is not None:
+            logits, amax = logits.logits, logits.argmax
+            if not all(self._is_plain_greedy(r) for r, _, _ in plan):
+                amax = None
+        else:
             keep = max(len(t) for _, t, _ in plan) if verify else 0
             batch = Batch.build(seqs, self.device, keep_steps=keep)
+            self.io_h2d += batch.h2d_bytes
             if self.sparse is not None:
                 batch.sparse = self.sparse.for_batch(batch, [r.rid for r, _, _ in plan])
             aux = tuple(self.drafter.aux_layers) if self.drafter is not None else ()
@@ -416,46 +430,54 @@ class Engine:
                 logits, hidden, taps = res
             else:
                 logits = res
+            if all(self._is_plain_greedy(r) for r, _, _ in plan):
+                amax = [int(v) for v in self.ops.argmax(logits).tolist()]  # one device sync per tick
+                self.io_d2h += 4 * len(amax)
         kinds = {r.state for r, _, _ in plan}
         key = "mixed_ticks" if len(kinds) > 1 else ("decode_ticks" if DECODE in kinds else "prefill_ticks")
         self.counters[key] += 1
-        row = 0  # row of `logits` when last_only; token offset otherwise
         tok_off = 0
         for i, (r, toks, start) in enumerate(plan):
             n = len(toks)
-            if verify:
-                lrows = logits[tok_off:tok_off + n]
-            else:
-                lrows = logits[i:i + 1]
+            base = tok_off if verify else i        # first logits row of this sequence
+            last = base + n - 1 if verify else i   # row of its last token
             if r.state == PREFILL:
                 r.n_computed = start + n
                 self._maybe_publish(r)
                 if r.n_computed == len(r.prompt):
                     r.state = DECODE
                     r.t_first = time.monotonic()
-                    self._commit(r, [self._sample(r, lrows[-1], 0)])
+                    self._commit(r, [self._sample(r, logits, last, 0, amax)])
                     self._offer_draft(r, taps, tok_off, n)
             else:
-                self._verify_commit(r, toks, lrows, verify)
+                self._verify_commit(r, toks, logits, base, verify, amax)
                 self._offer_draft(r, taps, tok_off, n)
             tok_off += n
 
     # ---- sampling / commit ------------------------------------------------------------------------
-    def _sample(self, r: _Req, logits_row: torch.Tensor, k: int) -> Tuple[int, float]:
+    @staticmethod
+    def _is_plain_greedy(r: _Req) -> bool:
+        p = r.params
+        return p.temperature <= 0.0 and p.allowed_ids is None and not p.logprobs \
+            and p.max_think_tokens is None
+
+    def _sample(self, r: _Req, logits: torch.Tensor, row: int, k: int, amax=None) -> Tuple[int, float]:
         p = r.params
         idx = len(r.out) + k
         if self.think_ids and p.max_think_tokens is not None and r.in_think \
                 and r.think_tokens + k >= p.max_think_tokens:
             return self.think_ids[1], 0.0  # forced </think>
+        if amax is not None:
+            return amax[row], 0.0
         allowed = None if p.allowed_ids is None else torch.tensor(p.allowed_ids)
         if p.temperature <= 0.0 and allowed is None and not p.logprobs:
-            return int(torch.argmax(logits_row)), 0.0
-        return ref.sample(logits_row.detach().float().cpu(), p.temperature, p.top_p, p.top_k,
+            return int(torch.argmax(logits[row])), 0.0
+        return ref.sample(logits[row].detach().float().cpu(), p.temperature, p.top_p, p.top_k,
                           ref.sample_seed(p.seed, idx), allowed)
 
-    def _verify_commit(self, r: _Req, chain: List[int], lrows: torch.Tensor, verify: bool) -> None:
+    def _verify_commit(self, r: _Req, chain: List[int], logits, base: int, verify: bool, amax=None) -> None:
         if not verify or len(chain) == 1:
-            self._commit(r, [self._sample(r, lrows[-1] if not verify else lrows[0], 0)])
+            self._commit(r, [self._sample(r, logits, base, 0, amax)])
             if verify:
                 self.states.select_step(r.slot, 0)
             return
@@ -463,7 +485,7 @@ class Engine:
         accepted: List[Tuple[int, float]] = []
         n_ok = 0
         for k in range(len(chain)):
-            tok = self._sample(r, lrows[k], k)
+            tok = self._sample(r, logits, base + k, k, amax)
             accepted.append(tok)
             if k < len(drafts) and tok[0] == drafts[k]:
                 n_ok += 1

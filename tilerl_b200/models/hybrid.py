@@ -210,7 +210,7 @@ class HybridModel:
                                          self._lora(p + "gate_up"))
             x = ops.linear_residual(act, P[p + "down"], x, self._lora(p + "down"))
             if i in aux_layers:
-                taps[i] = x
+                taps[i] = x.clone()  # the residual stream is updated in place
         xs = x[batch.last_idx.long()] if last_only else x
         head = P["embed"] if cfg.tie_embeddings else P["lm_head"]
         logits = ops.lm_head(xs, P["final_norm"], head, eps)[..., :cfg.vocab]

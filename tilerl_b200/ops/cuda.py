@@ -1,0 +1,273 @@
+"""B200 implementation of the model's op surface on the hand-written kernels.
+
+Shapes decide the kernel, not flags: up to ``GEMV_MAX_M`` tokens a projection
+is a weight-streaming NVFP4 GEMV with RMSNorm folded into its prologue and the
+residual add / SwiGLU folded into its epilogue; above that it is the tcgen05
+block-scaled GEMM (:mod:`tilerl_b200.ops.gemm`).  All intermediate buffers live
+in a workspace allocated once per ``max_tokens`` so every launch of a decode tick
+sees fixed addresses and the tick can be captured in a CUDA graph.
+
+With a tensor-parallel group the row-parallel projections end in the fused
+one-shot all-reduce of :mod:`tilerl_b200.parallel.symm` instead of a separate
+collective.
+
+Parity: the ``Backend`` op surface of reference
+``packages/tilerl-kernels/src/tilerl_kernels/backend.py:559-1797`` (dispatch by
+launch M ``:733-905``).
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+
+from ..formats import FP8BlockTensor, NVFP4Tensor
+from . import native as N
+
+EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU, EPI_STORE_F32 = 0, 1, 2, 3
+GEMV_MAX_M = 8
+
+
+class Workspace:
+    """Named, lazily created, fixed-address device buffers."""
+
+    def __init__(self, device):
+        self.device = device
+        self.bufs: Dict[str, torch.Tensor] = {}
+
+    def get(self, name: str, shape, dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        t = self.bufs.get(name)
+        if t is None or t.numel() < n or t.dtype != dtype:
+            if t is not None and torch.cuda.is_current_stream_capturing():
+                raise RuntimeError(f"workspace buffer {name!r} would be reallocated during graph capture")
+            t = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self.bufs[name] = t
+        return t[:n].view(*shape)
+
+
+class CudaOps:
+    name = "cuda"
+
+    def __init__(self, device="cuda", tp=None, comm=None, attn_splits: int = 0, use_tc_gemm: bool = True):
+        if not torch.cuda.is_available():
+            raise RuntimeError("CudaOps needs a CUDA device")
+        self.lib = N.lib()
+        self.device = torch.device(device)
+        self.ws = Workspace(self.device)
+        self.tp = tp
+        self.comm = comm          # parallel.symm.SymmComm or None
+        self.attn_splits = attn_splits
+        self.use_tc_gemm = use_tc_gemm
+        self.act_dtype = torch.bfloat16
+        self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+
+    # ---- helpers ------------------------------------------------------------------
+    def _f32(self, t: torch.Tensor) -> torch.Tensor:
+        assert t.dtype == torch.float32 and t.is_cuda, "norm/vector parameters must be fp32 on device"
+        return t
+
+    def _gemv(self, x, w, y, *, norm_w=None, eps=0.0, residual=None, epi=EPI_STORE):
+        m, k = x.shape
+        if isinstance(w, NVFP4Tensor):
+            n = w.wq.shape[0]
+            N.check(self.lib.trl_gemv_nvfp4(
+                x.data_ptr(), x.stride(0), w.wq.data_ptr(), w.scale.data_ptr(), w.tscale.data_ptr(),
+                N.ptr(norm_w), eps, N.ptr(residual), residual.stride(0) if residual is not None else 0,
+                y.data_ptr(), y.stride(0), m, n, k, epi, N.stream()), "gemv_nvfp4")
+            N.count((m + 3) // 4)
+        elif isinstance(w, torch.Tensor) and w.dtype == torch.bfloat16:
+            n = w.shape[0]
+            assert epi != EPI_SWIGLU
+            N.check(self.lib.trl_gemv_bf16(
+                x.data_ptr(), x.stride(0), w.data_ptr(), N.ptr(norm_w), eps, N.ptr(residual),
+                residual.stride(0) if residual is not None else 0, y.data_ptr(), y.stride(0),
+                m, n, k, epi, N.stream()), "gemv_bf16")
+            N.count((m + 3) // 4)
+        else:
+            raise TypeError(f"no GEMV for weight type {type(w)}")
+
+    def _gemm(self, x, w, out_name: str):
+        """Large-M projection ``[T, K] x W^T -> [T, N]`` bf16."""
+        from . import gemm
+        t = x.shape[0]
+        n = w.shape[0]
+        y = self.ws.get(out_name, (t, n), torch.bfloat16)
+        gemm.linear(self, x, w, y)
+        return y
+
+    def _rmsnorm(self, x, w, eps, name="h"):
+        t, h = x.shape
+        out = self.ws.get(name, (t, h), torch.bfloat16)
+        N.check(self.lib.trl_rmsnorm(x.data_ptr(), w.data_ptr(), out.data_ptr(), t, h, eps, N.stream()), "rmsnorm")
+        N.count()
+        return out
+
+    def _lora_add(self, y, x, lora):
+        if lora is not None:
+            a, b, s = lora
+            y.add_(((x.float() @ a.float().t()) @ b.float().t() * s).to(y.dtype))
+        return y
+
+    # ---- op surface --------------------------------------------------------------------
+    def embed(self, table, ids):
+        t, h = ids.shape[0], table.shape[1]
+        x = self.ws.get("x", (t, h), torch.bfloat16)
+        N.check(self.lib.trl_embedding(table.data_ptr(), ids.data_ptr(), x.data_ptr(), t, h, N.stream()), "embedding")
+        N.count()
+        return x
+
+    def norm_linear(self, x, norm_w, w, eps, lora=None):
+        t = x.shape[0]
+        n = w.shape[0]
+        if t <= GEMV_MAX_M:
+            y = self.ws.get("proj", (t, n), torch.bfloat16)
+            self._gemv(x, w, y, norm_w=self._f32(norm_w), eps=eps)
+            if lora is not None:
+                h = self._rmsnorm(x, norm_w, eps)
+                self._lora_add(y, h, lora)
+            return y
+        h = self._rmsnorm(x, norm_w, eps)
+        return self._lora_add(self._gemm(h, w, "proj"), h, lora)
+
+    def norm_linear_swiglu(self, x, norm_w, w, eps, lora=None):
+        t = x.shape[0]
+        n = w.shape[0]
+        act = self.ws.get("act", (t, n // 2), torch.bfloat16)
+        if t <= GEMV_MAX_M and lora is None:
+            self._gemv(x, w, act, norm_w=self._f32(norm_w), eps=eps, epi=EPI_SWIGLU)
+            return act
+        h = self._rmsnorm(x, norm_w, eps)
+        gu = self._lora_add(self._gemm(h, w, "proj"), h, lora)
+        N.check(self.lib.trl_swiglu(gu.data_ptr(), act.data_ptr(), act.numel(), N.stream()), "swiglu")
+        N.count()
+        return act
+
+    def linear_residual(self, a, w, residual, lora=None):
+        """``residual += a @ W^T`` (in place on the residual stream).  Under TP the
+        partial products are summed across ranks inside the fused kernel."""
+        t = a.shape[0]
+        if self.comm is not None and self.comm.world > 1:
+            return self.comm.linear_allreduce_residual(self, a, w, residual, lora)
+        if t <= GEMV_MAX_M and lora is None:
+            self._gemv(a, w, residual, residual=residual, epi=EPI_RESIDUAL)
+            return residual
+        y = self._lora_add(self._gemm(a, w, "rowout"), a, lora)
+        N.check(self.lib.trl_add(y.data_ptr(), residual.data_ptr(), residual.data_ptr(), y.numel(), N.stream()), "add")
+        N.count()
+        return residual
+
+    def attention(self, qkv, lp, batch, pool, attn_idx, cfg, n_q, n_kv):
+        t = qkv.shape[0]
+        d = cfg.head_dim
+        q = self.ws.get("q", (t, n_q, d), torch.bfloat16)
+        out = self.ws.get("act", (t, n_q * d), torch.bfloat16)
+        kc, vc = pool.layer(attn_idx)
+        st = N.stream()
+        N.check(self.lib.trl_attn_prep(
+            qkv.data_ptr(), qkv.stride(0), self._f32(lp["q_norm"]).data_ptr(),
+            self._f32(lp["k_norm"]).data_ptr(), batch.positions.data_ptr(),
+            batch.slot_mapping.data_ptr(), q.data_ptr(), kc.data_ptr(), vc.data_ptr(), t, n_q, n_kv, d,
+            cfg.rotary_dim, float(cfg.rope_theta), cfg.rms_eps, int(cfg.attn_gated), st), "attn_prep")
+        splits = self.attn_splits or self._pick_splits(batch, t, n_kv)
+        po = self.ws.get("attn_po", (t * n_q * splits * d,), torch.float32)
+        pm = self.ws.get("attn_pm", (t * n_q * splits,), torch.float32)
+        pl = self.ws.get("attn_pl", (t * n_q * splits,), torch.float32)
+        N.check(self.lib.trl_attn_paged(
+            q.data_ptr(), qkv.data_ptr(), qkv.stride(0), kc.data_ptr(), vc.data_ptr(),
+            batch.block_table.data_ptr(), batch.block_table.stride(0), batch.seq_ids.data_ptr(),
+            batch.positions.data_ptr(), po.data_ptr(), pm.data_ptr(), pl.data_ptr(), out.data_ptr(),
+            t, n_q, n_kv, d, splits, 1.0 / math.sqrt(d), int(cfg.attn_gated), st), "attn_paged")
+        N.count(2 + (1 if splits > 1 else 0))
+        return out
+
+    def _pick_splits(self, batch, t: int, n_kv: int) -> int:
+        """Enough CTAs to fill the GPU when few tokens attend to long contexts."""
+        if t * n_kv >= self.sms:
+            return 1
+        longest = max(batch.host_kv_len) if batch.host_kv_len else 1
+        want = max(1, self.sms // max(1, t * n_kv))
+        return max(1, min(want, 32, (longest + 127) // 128))
+
+    def gdn(self, inp, lp, batch, spool, gdn_idx, cfg, nk, nv):
+        t = inp.shape[0]
+        d = cfg.gdn_head_dim
+        f32 = torch.float32
+        qn = self.ws.get("gdn_qn", (t * nk * d,), f32)
+        kn = self.ws.get("gdn_kn", (t * nk * d,), f32)
+        vc = self.ws.get("gdn_vc", (t * nv * d,), f32)
+        g = self.ws.get("gdn_g", (t * nv,), f32)
+        beta = self.ws.get("gdn_b", (t * nv,), f32)
+        osc = self.ws.get("gdn_o", (t * nv * d,), f32)
+        out = self.ws.get("act", (t, nv * d), torch.bfloat16)
+        states, ring = spool.states, spool.ring
+        s_l = states[:, gdn_idx]
+        r_l = ring[:, gdn_idx]
+        keep = batch.keep_flags if batch.keep_steps else None
+        N.check(self.lib.trl_gdn(
+            inp.data_ptr(), inp.stride(0), self._f32(lp["conv"]).data_ptr(),
+            self._f32(lp["dt_bias"]).data_ptr(), self._f32(lp["a_log"]).data_ptr(),
+            self._f32(lp["gdn_norm"]).data_ptr(), s_l.data_ptr(), spool.cur.data_ptr(), r_l.data_ptr(),
+            batch.positions.data_ptr(), batch.seq_ids.data_ptr(), batch.q_start.data_ptr(),
+            batch.q_len.data_ptr(), batch.state_slots.data_ptr(), N.ptr(keep),
+            states.stride(0), states.stride(2), ring.stride(0),
+            qn.data_ptr(), kn.data_ptr(), vc.data_ptr(), g.data_ptr(), beta.data_ptr(), osc.data_ptr(),
+            out.data_ptr(), t, batch.n_seqs, nk, nv, d, cfg.gdn_conv, spool.planes, cfg.rms_eps,
+            N.stream()), "gdn")
+        N.count(2)
+        return out
+
+    def lm_head(self, x, norm_w, w, eps):
+        m = x.shape[0]
+        n = w.shape[0]
+        logits = self.ws.get("logits", (m, n), torch.float32)
+        if m <= GEMV_MAX_M:
+            self._gemv(x.contiguous(), w, logits, norm_w=self._f32(norm_w), eps=eps, epi=EPI_STORE_F32)
+        else:
+            h = self._rmsnorm(x.contiguous(), norm_w, eps, name="h_head")
+            wt = w if isinstance(w, torch.Tensor) else None
+            if wt is None:
+                from . import gemm
+                y = self._gemm(h, w, "head_bf16")
+                logits.copy_(y)
+            else:
+                torch.matmul(h, wt.t(), out=self.ws.get("head_bf16", (m, n), torch.bfloat16))
+                logits.copy_(self.ws.get("head_bf16", (m, n), torch.bfloat16))
+        if self.comm is not None and self.comm.world > 1:
+            return self.comm.all_gather_logits(logits)
+        return logits
+
+    def argmax(self, logits):
+        m, v = logits.shape
+        out = self.ws.get("argmax", (m,), torch.int32)
+        N.check(self.lib.trl_argmax(logits.data_ptr(), logits.stride(0), m, v, out.data_ptr(), N.stream()), "argmax")
+        N.count()
+        return out
+
+    # ---- training / maintenance kernels ------------------------------------------------------
+    def quantize_nvfp4_(self, w: torch.Tensor, dst: NVFP4Tensor, keep_tscale: bool = False) -> None:
+        """Re-pack ``w`` (fp32 or bf16 ``[N, K]``) into ``dst`` in place."""
+        n, k = w.shape
+        tmp = self.ws.get("amax_tmp", (1,), torch.float32)
+        dt = {torch.float32: 0, torch.bfloat16: 1}[w.dtype]
+        N.check(self.lib.trl_quant_nvfp4(w.data_ptr(), dt, n, k, dst.wq.data_ptr(), dst.scale.data_ptr(),
+                                         dst.tscale.data_ptr(), tmp.data_ptr(), int(keep_tscale), N.stream()),
+                "quant_nvfp4")
+        N.count(4)
+
+    def dequantize_nvfp4(self, w: NVFP4Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        n, k = w.shape
+        if out is None:
+            out = torch.empty(n, k, dtype=torch.bfloat16, device=self.device)
+        N.check(self.lib.trl_dequant_nvfp4(w.wq.data_ptr(), w.scale.data_ptr(), w.tscale.data_ptr(),
+                                           out.data_ptr(), n, k, N.stream()), "dequant_nvfp4")
+        N.count()
+        return out
+
+    def adamw_step(self, p, m, v, g, *, lr, betas, eps, wd, step, gscale=1.0, p_bf16=None) -> None:
+        N.check(self.lib.trl_adamw(p.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), N.ptr(p_bf16),
+                                   p.numel(), lr, betas[0], betas[1], eps, wd, step, gscale, N.stream()), "adamw")
+        N.count()

@@ -1,0 +1,106 @@
+"""ctypes binding of ``tilerl_b200/_C.so`` (the sm_100a kernels and the C++ runtime).
+
+Every entry point takes raw device pointers plus the CUDA stream handle and
+returns a ``cudaError_t`` as int; :func:`check` turns a non-zero code into an
+exception.  Launches go to ``torch.cuda.current_stream()``, so they are captured
+by ``torch.cuda.graph`` like any torch op.  There is no silent fallback: asking for
+the library on a machine where it cannot be loaded raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_long, c_void_p
+from typing import Optional
+
+import torch
+
+_LIB: Optional[ctypes.CDLL] = None
+_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "_C.so")
+
+P, I, L, F = c_void_p, c_int, c_long, c_float
+
+_SIGS = {
+    "trl_gemv_nvfp4": [P, I, P, P, P, P, F, P, I, P, I, I, I, I, I, P],
+    "trl_gemv_bf16": [P, I, P, P, F, P, I, P, I, I, I, I, I, P],
+    "trl_set_pdl": [I],
+    "trl_error_read": [P, I],
+    "trl_attn_prep": [P, I, P, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P],
+    "trl_attn_paged": [P, P, I, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, F, I, P],
+    "trl_gdn": [P, I, P, P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, P, P, P, P, P, P, P,
+                I, I, I, I, I, I, I, F, P],
+    "trl_embedding": [P, P, P, I, I, P],
+    "trl_gather_rows": [P, P, P, I, I, P],
+    "trl_rmsnorm": [P, P, P, I, I, F, P],
+    "trl_swiglu": [P, P, L, P],
+    "trl_argmax": [P, I, I, I, P, P],
+    "trl_adamw": [P, P, P, P, P, L, F, F, F, F, F, I, F, P],
+    "trl_quant_nvfp4": [P, I, L, L, P, P, P, P, I, P],
+    "trl_dequant_nvfp4": [P, P, P, P, L, L, P],
+    "trl_add": [P, P, P, L, P],
+    "trl_decode_advance": [P, P, P, P, P, P, I, I, P, I, P, P],
+}
+
+
+def lib_path() -> str:
+    return _PATH
+
+
+def available() -> bool:
+    return os.path.exists(_PATH) and torch.cuda.is_available()
+
+
+def lib() -> ctypes.CDLL:
+    global _LIB
+    if _LIB is None:
+        if not os.path.exists(_PATH):
+            raise RuntimeError(f"{_PATH} is missing: run `python -m tilerl_b200.build`")
+        _LIB = ctypes.CDLL(_PATH)
+        for name, sig in _SIGS.items():
+            fn = getattr(_LIB, name, None)
+            if fn is None:
+                continue
+            fn.argtypes = sig
+            fn.restype = c_int if name != "trl_set_pdl" else None
+    return _LIB
+
+
+def register(name: str, sig) -> None:
+    """Declare the signature of an entry point defined by another source file."""
+    _SIGS[name] = sig
+    if _LIB is not None and hasattr(_LIB, name):
+        fn = getattr(_LIB, name)
+        fn.argtypes = sig
+        fn.restype = c_int
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def check(code: int, what: str = "") -> None:
+    if code != 0:
+        raise KernelError(f"{what or 'kernel'} failed with cudaError {code}")
+
+
+def ptr(t) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def read_error(clear: bool = True):
+    """(code, a, b, c) of the device error word; code 0 = none."""
+    out = (c_int * 4)()
+    check(lib().trl_error_read(out, int(clear)), "trl_error_read")
+    return tuple(out)
+
+
+launch_count = 0
+
+
+def count(n: int = 1) -> None:
+    global launch_count
+    launch_count += n
