@@ -3,7 +3,7 @@
 // Input is the fused projection row [q nk*dk ; k nk*dk ; v nv*dv ; z nv*dv ; a nv ; b nv]
 // (bf16).  D = dk = dv in {64, 128}.
 //
-//   gdn_prep  (grid = tokens): depthwise causal conv (taps read from this tick's rows
+//   gdn_prep  (grid = tokens x heads): depthwise causal conv (taps read from this tick's rows
 //             or, before the tick's first token, from the per-slot ring of raw rows
 //             indexed by position % 16) + SiLU, L2-norm of q (with 1/sqrt(dk)) and k,
 //             g = -exp(A_log) * softplus(a + dt_bias), beta = sigmoid(b).
@@ -26,7 +26,9 @@ namespace {
 
 constexpr int RING = 16;
 
-__global__ void __launch_bounds__(256)
+// grid = (tokens, 2*nk + nv): one CTA of D threads per (token, head); q/k heads also
+// L2-normalise, the first CTA of a token also emits the gates.
+__global__ void __launch_bounds__(128)
 gdn_prep_kernel(const bf16* __restrict__ inp, int ld, const float* __restrict__ conv_w,
                 const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                 const bf16* __restrict__ ring, const int* __restrict__ positions,
@@ -34,58 +36,48 @@ gdn_prep_kernel(const bf16* __restrict__ inp, int ld, const float* __restrict__ 
                 const int* __restrict__ state_slots, long ring_slot_stride,
                 float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ vc,
                 float* __restrict__ gout, float* __restrict__ bout, int nk, int nv, int D, int KW) {
-  extern __shared__ float sm[];  // [conv_dim] conv+silu result, then [2*nk] norms
+  __shared__ float red[32];
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x;
+  const int t = blockIdx.x, head = blockIdx.y;
   const int C = 2 * nk * D + nv * D;
   const int pos = positions[t];
   const int seq = seq_ids[t];
   const int t0 = q_start[seq];
   const bf16* rg = ring + (size_t)state_slots[seq] * ring_slot_stride;
-  float* cv = sm;
-  float* nrm = sm + C;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    float acc = 0.f;
-    for (int j = 0; j < KW; ++j) {  // tap KW-1 multiplies the newest row
-      const int back = KW - 1 - j;
-      const int pj = pos - back;
-      float v = 0.f;
-      if (pj >= 0) {
-        if (t - back >= t0)
-          v = __bfloat162float(inp[(size_t)(t - back) * ld + c]);
-        else
-          v = __bfloat162float(rg[(size_t)(pj % RING) * C + c]);
-      }
-      acc = fmaf(v, conv_w[(size_t)c * KW + j], acc);
+  const int d = threadIdx.x;
+  const int c = head * D + d;
+  float acc = 0.f;
+  for (int j = 0; j < KW; ++j) {  // tap KW-1 multiplies the newest row
+    const int back = KW - 1 - j;
+    const int pj = pos - back;
+    float v = 0.f;
+    if (pj >= 0) {
+      if (t - back >= t0)
+        v = __bfloat162float(inp[(size_t)(t - back) * ld + c]);
+      else
+        v = __bfloat162float(rg[(size_t)(pj % RING) * C + c]);
     }
-    cv[c] = silu_f(acc);
+    acc = fmaf(v, conv_w[(size_t)c * KW + j], acc);
   }
-  __syncthreads();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  for (int h = warp; h < 2 * nk; h += nw) {
-    float ss = 0.f;
-    for (int d = lane; d < D; d += 32) {
-      const float v = cv[(size_t)h * D + d];
-      ss += v * v;
-    }
-    ss = warp_sum(ss);
-    if (lane == 0) nrm[h] = rsqrtf(ss + 1e-12f) * (h < nk ? rsqrtf((float)D) : 1.f);
-  }
-  __syncthreads();
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    if (c < nk * D)
-      qn[(size_t)t * nk * D + c] = cv[c] * nrm[c / D];
-    else if (c < 2 * nk * D)
-      kn[(size_t)t * nk * D + (c - nk * D)] = cv[c] * nrm[c / D];
+  const float val = silu_f(acc);
+  if (head < 2 * nk) {
+    const float ss = block_sum(val * val, red);
+    const float nrm = rsqrtf(ss + 1e-12f) * (head < nk ? rsqrtf((float)D) : 1.f);
+    if (head < nk)
+      qn[((size_t)t * nk + head) * D + d] = val * nrm;
     else
-      vc[(size_t)t * nv * D + (c - 2 * nk * D)] = cv[c];
+      kn[((size_t)t * nk + (head - nk)) * D + d] = val * nrm;
+  } else {
+    vc[((size_t)t * nv + (head - 2 * nk)) * D + d] = val;
   }
-  const bf16* ab = inp + (size_t)t * ld + C + nv * D;
-  for (int h = threadIdx.x; h < nv; h += blockDim.x) {
-    const float a = __bfloat162float(ab[h]), b = __bfloat162float(ab[nv + h]);
-    gout[(size_t)t * nv + h] = -__expf(a_log[h]) * softplus_f(a + dt_bias[h]);
-    bout[(size_t)t * nv + h] = sigmoid_f(b);
+  if (head == 0) {
+    const bf16* ab = inp + (size_t)t * ld + C + nv * D;
+    for (int h = threadIdx.x; h < nv; h += blockDim.x) {
+      const float a = __bfloat162float(ab[h]), b = __bfloat162float(ab[nv + h]);
+      gout[(size_t)t * nv + h] = -__expf(a_log[h]) * softplus_f(a + dt_bias[h]);
+      bout[(size_t)t * nv + h] = sigmoid_f(b);
+    }
   }
 }
 
@@ -228,10 +220,7 @@ TRL_API int trl_gdn(const void* inp, int ld, const void* conv_w, const void* dt_
                     void* beta, void* o_scratch, void* out, int T, int B, int nk, int nv, int D, int KW,
                     int planes, float eps, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
-  const int C = 2 * nk * D + nv * D;
-  const size_t smem = (size_t)(C + 2 * nk) * sizeof(float);
-  cudaFuncSetAttribute(gdn_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  cudaError_t e = trl_launch(gdn_prep_kernel, dim3(T), dim3(256), smem, st, (const bf16*)inp, ld,
+  cudaError_t e = trl_launch(gdn_prep_kernel, dim3(T, 2 * nk + nv), dim3(D), 0, st, (const bf16*)inp, ld,
                              (const float*)conv_w, (const float*)dt_bias, (const float*)a_log,
                              (const bf16*)ring, (const int*)positions, (const int*)seq_ids,
                              (const int*)q_start, (const int*)state_slots, ring_slot_stride,

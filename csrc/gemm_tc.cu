@@ -1,0 +1,675 @@
+// tcgen05 block-scaled NVFP4 GEMM (and its activation quantiser).
+//
+//   Y[tok, n] = epi( tscale * sum_j rs[col] * sum_k Xq[col, k] sfx[col, k/16] * Wq[n, k] sfw[n, k/16] )
+//
+// The *weight* is the MMA "A" operand (128 rows per tile -> TMEM lanes), the
+// activation columns are the "B" operand (BN in {16..256} -> TMEM columns): a decode
+// tick with a handful of tokens still fills the 128-lane datapath, and the weight
+// stream -- the only large operand -- is read exactly once by TMA straight into
+// 128B-swizzled shared memory with no ALU decode at all.
+//
+// Activation precision is a *column count* here: token t occupies J consecutive
+// columns holding successive NVFP4 residual terms x ~= x1 + x2 + ... (each with its
+// own per-16 e4m3 scales and fp32 row scale), summed in the epilogue.  J = 1 is plain
+// W4A4; J = 4 reproduces a bf16 activation to ~2^-9 while still running entirely on
+// the FP4 tensor cores -- that is how the B = 1 decode tick reads its weights at
+// HBM speed with bf16-accurate activations.
+//
+// Schedule: stream-K.  The (tile, k-tile) units are split evenly over one CTA per
+// SM; a CTA whose range covers a whole tile finishes it from TMEM, otherwise partial
+// tiles are reduced with fp32 red.global.add into a scratch buffer and the last
+// arriving CTA of the tile (atomic counter) runs the epilogue and re-zeroes the
+// scratch.  Small-N / large-K projections (down_proj, o_proj) therefore use every SM.
+//
+// Warp roles (192 threads): warp 0 = TMA producer (weight tiles are prefetched
+// *before* griddepcontrol.wait, since they do not depend on the previous kernel),
+// warp 1 = TMEM owner + MMA issuer (one elected lane), warps 2-5 = epilogue
+// (tcgen05.ld, scale, residual / SwiGLU, store).  Every mbarrier wait is bounded: on
+// expiry the CTA records an error word, raises a shared abort flag, frees its TMEM
+// and returns.
+//
+// Scale factors use the 128x4 tiled layout the tensor core reads:
+//   byte offset = ((row/128) * KT4 + k64) * 512 + (row%32)*16 + ((row%128)/32)*4 + (k16%4)
+// so that one k-tile of a 128-row atom is 2 KB contiguous.
+//
+// No counterpart exists in the reference: its Blackwell kernel cell is empty
+// (packages/tilerl-kernels/src/tilerl_kernels/registry.py:188-189); functionally this
+// replaces linear_fp4_fp8 / linear_fp4_gemv / linear_fp4_mma8 (kernels_linear.py:924-1687).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int TILE_N = 128;
+constexpr int KT_BYTES = 128;   // bytes of K per row per k-tile (= 256 e2m1)
+constexpr int KT_ELEMS = 256;
+constexpr int GEMM_THREADS = 192;
+constexpr int SF_ATOM = 512;    // bytes: 128 rows x 4 scales
+constexpr long long WAIT_CYCLES = 4000000000LL;  // ~2 s at 1.9 GHz
+
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_STORE_F32 = 3 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{ .reg .pred p;\n"
+      "  mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "  selp.u32 %0, 1, 0, p; }\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait.  Returns false when the wait ran out or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 31) == 31) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > WAIT_CYCLES) {
+        *abort_flag = 1;
+        trl_set_error(TRL_ERR_MBAR_TIMEOUT, (int)blockIdx.x, (int)bar, (int)parity);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_nvfp4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{ .reg .pred p;\n"
+      "  setp.ne.b32 p, %4, 0;\n"
+      "  tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p; }\n"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, 128B-swizzled operand tile: rows 128 B apart, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
+  uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;            // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset
+  d |= (uint64_t)1 << 46;            // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;            // SWIZZLE_128B
+  return d;
+}
+// Scale-factor atom for tcgen05.cp.32x128b: 32 rows of 16 B, no swizzle.
+__device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
+  uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(128 >> 4) << 32;   // 8-row core matrices 128 B apart
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+
+struct GemmParams {
+  const uint8_t* sfw;    // weight scales, tiled
+  const uint8_t* sfx;    // activation scales, tiled
+  const float* tscale;   // weight tensor scale
+  const float* rs;       // per-column activation scale [cols]
+  const bf16* residual;  // [tokens, ldr]
+  void* out;
+  float* partial;        // [tiles, max_seg, BN/J, 128] fp32 split-K slots (no init needed)
+  int* counters;         // [tiles], zero on entry, zero on exit
+  int N, K, cols, tokens, J;
+  int ldr, ldo;
+  int n_tiles, c_tiles, nk, kt4;
+  int max_seg;
+  int split;   // 1: stream-K over (tile, k-tile) units; 0: whole tiles per CTA
+  int epi;
+};
+
+__device__ __forceinline__ int owner_of(long long unit, long long U, int G) {
+  int i = (int)((unit * G) / U);
+  while ((long long)(i + 1) * U / G <= unit) ++i;
+  while ((long long)i * U / G > unit) --i;
+  return i;
+}
+
+template <int BN>
+struct Cfg {
+  static constexpr int SFB_ATOMS = BN > 128 ? 2 : 1;
+  static constexpr int A_BYTES = TILE_N * KT_BYTES;
+  static constexpr int B_BYTES = BN * KT_BYTES;
+  static constexpr int B_ALLOC = (B_BYTES + 1023) / 1024 * 1024;
+  static constexpr int SFA_BYTES = 4 * SF_ATOM;
+  static constexpr int SFB_BYTES = SFB_ATOMS * 4 * SF_ATOM;
+  static constexpr int STAGE = A_BYTES + B_ALLOC + SFA_BYTES + SFB_BYTES;
+  // small-BN (decode) tiles: 4 stages and half the TMEM, so that the next kernel's CTA can
+  // become resident (and prefetch its weights) while this one drains
+  static constexpr int STAGES = BN <= 64 ? 4 : ((200 * 1024) / STAGE > 8 ? 8 : (200 * 1024) / STAGE);
+  static constexpr int TMEM_COLS = BN <= 64 ? 256 : 512;
+  static constexpr int SF_COL0 = BN <= 64 ? 128 : 256;
+  static constexpr int SMEM = STAGES * STAGE + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                  const GemmParams p) {
+  using C = Cfg<BN>;
+  constexpr int S = C::STAGES;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)S * C::STAGE);
+  // bars[0..S) full, [S..2S) empty, [2S] accum_full, [2S+1] accum_empty
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* last_flag = const_cast<int*>(abort_flag) + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
+  const uint32_t accum_full = bar0 + 8u * (2 * S), accum_empty = bar0 + 8u * (2 * S + 1);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) mbar_init(full_bar(s), 1), mbar_init(empty_bar(s), 1);
+    mbar_init(accum_full, 1);
+    mbar_init(accum_empty, 128);
+    *abort_flag = 0;
+    *last_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(C::TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+
+  const long long U = (long long)p.n_tiles * p.c_tiles * p.nk;
+  const int G = gridDim.x;
+  long long u0 = (long long)blockIdx.x * U / G, u1 = (long long)(blockIdx.x + 1) * U / G;
+  if (!p.split) {
+    const long long T = (long long)p.n_tiles * p.c_tiles;
+    u0 = ((long long)blockIdx.x * T / G) * p.nk, u1 = ((long long)(blockIdx.x + 1) * T / G) * p.nk;
+  }
+  const uint32_t stage_bytes = C::A_BYTES + C::B_BYTES + C::SFA_BYTES + C::SFB_BYTES;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      long long u = u0;
+      int it = 0;
+      // prologue: weight tiles of the first S units do not depend on the previous kernel
+      const int pre = (int)min((long long)S, u1 - u0);
+      for (int i = 0; i < pre; ++i) {
+        const long long uu = u0 + i;
+        const int tile = (int)(uu / p.nk), kt = (int)(uu % p.nk);
+        const int nt = tile / p.c_tiles;
+        unsigned char* st = smem + (size_t)i * C::STAGE;
+        mbar_expect_tx(full_bar(i), stage_bytes);
+        tma_load_2d(smem_u32(st), &map_w, kt * KT_BYTES, nt * TILE_N, full_bar(i));
+        bulk_load(smem_u32(st + C::A_BYTES + C::B_ALLOC), p.sfw + ((size_t)nt * p.kt4 + (size_t)kt * 4) * SF_ATOM,
+                  C::SFA_BYTES, full_bar(i));
+      }
+      pdl_wait();
+      bool ok = true;
+      for (; ok && u < u1; ++u, ++it) {
+        const int s = it % S;
+        const uint32_t ph = (uint32_t)(it / S) & 1u;
+        const int tile = (int)(u / p.nk), kt = (int)(u % p.nk);
+        const int nt = tile / p.c_tiles, ct = tile % p.c_tiles;
+        unsigned char* st = smem + (size_t)s * C::STAGE;
+        if (it >= pre) {
+          ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag);
+          if (!ok) break;
+          mbar_expect_tx(full_bar(s), stage_bytes);
+          tma_load_2d(smem_u32(st), &map_w, kt * KT_BYTES, nt * TILE_N, full_bar(s));
+          bulk_load(smem_u32(st + C::A_BYTES + C::B_ALLOC), p.sfw + ((size_t)nt * p.kt4 + (size_t)kt * 4) * SF_ATOM,
+                    C::SFA_BYTES, full_bar(s));
+        }
+        tma_load_2d(smem_u32(st + C::A_BYTES), &map_x, kt * KT_BYTES, ct * BN, full_bar(s));
+#pragma unroll
+        for (int j = 0; j < C::SFB_ATOMS; ++j) {
+          const size_t atom_row = (size_t)(ct * BN) / 128 + j;
+          bulk_load(smem_u32(st + C::A_BYTES + C::B_ALLOC + C::SFA_BYTES + j * 4 * SF_ATOM),
+                    p.sfx + (atom_row * p.kt4 + (size_t)kt * 4) * SF_ATOM, 4 * SF_ATOM, full_bar(s));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    pdl_wait();
+    if (lane == 0) {
+      constexpr uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TILE_N >> 4) << 24);
+      long long u = u0;
+      int it = 0, seg = 0;
+      bool ok = true;
+      while (ok && u < u1) {
+        const int k0 = (int)(u % p.nk);
+        const int len = (int)min((long long)(p.nk - k0), u1 - u);
+        if (seg > 0) {
+          ok = mbar_wait(accum_empty, (uint32_t)(seg - 1) & 1u, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        for (int i = 0; ok && i < len; ++i, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (uint32_t)(it / S) & 1u;
+          ok = mbar_wait(full_bar(s), ph, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          unsigned char* st = smem + (size_t)s * C::STAGE;
+          const uint32_t sf_cols = tmem_base + C::SF_COL0 + (uint32_t)(it & 1) * 64;  // double-buffered by parity
+          const uint32_t sfa_s = smem_u32(st + C::A_BYTES + C::B_ALLOC);
+          const uint32_t sfb_s = sfa_s + C::SFA_BYTES;
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb) {
+            tc_cp_sf(sf_cols + kb * 4, desc_sf(sfa_s + kb * SF_ATOM));
+#pragma unroll
+            for (int j = 0; j < C::SFB_ATOMS; ++j)
+              tc_cp_sf(sf_cols + 16 + kb * 8 + j * 4, desc_sf(sfb_s + j * 4 * SF_ATOM + kb * SF_ATOM));
+          }
+          const uint64_t ad = desc_sw128(smem_u32(st)), bd = desc_sw128(smem_u32(st + C::A_BYTES));
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb)
+            tc_mma_nvfp4(tmem_base, ad + (uint64_t)(kb * 2), bd + (uint64_t)(kb * 2), idesc, sf_cols + kb * 4,
+                         sf_cols + 16 + kb * 8, (i | kb) ? 1u : 0u);
+          tc_commit(empty_bar(s));
+        }
+        if (ok) tc_commit(accum_full);
+        u += len;
+        ++seg;
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    pdl_wait();
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const float ts = *p.tscale;
+    const int J = p.J;
+    long long u = u0;
+    int seg = 0;
+    bool ok = true;
+    while (ok && u < u1) {
+      const int tile = (int)(u / p.nk);
+      const int k0 = (int)(u % p.nk);
+      const int len = (int)min((long long)(p.nk - k0), u1 - u);
+      const bool whole = (k0 == 0 && len == p.nk);
+      const int nt = tile / p.c_tiles, ct = tile % p.c_tiles;
+      const int n = nt * TILE_N + row;
+      const int tok0 = (ct * BN) / J;
+      // split tiles: this CTA's private slot (deterministic, order-independent reduction)
+      const long long t_lo = (long long)tile * p.nk;
+      const int first_owner = whole ? 0 : owner_of(t_lo, U, G);
+      float* tile_slots = p.partial + (size_t)tile * p.max_seg * (BN / J) * TILE_N;
+      float* slot = tile_slots + (size_t)((int)blockIdx.x - first_owner) * (BN / J) * TILE_N;
+      ok = mbar_wait(accum_full, (uint32_t)seg & 1u, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      // finishing one (token, row) value
+      auto finish = [&](int tok, float v) {
+        if (p.epi == EPI_SWIGLU) {
+          const float other = __shfl_xor_sync(0xffffffffu, v, 1);
+          if ((lane & 1) == 0 && tok < p.tokens && n + 1 < p.N)
+            reinterpret_cast<bf16*>(p.out)[(size_t)tok * p.ldo + (n >> 1)] = __float2bfloat16(silu_f(v) * other);
+        } else if (tok < p.tokens && n < p.N) {
+          if (p.epi == EPI_RESIDUAL) v += __bfloat162float(p.residual[(size_t)tok * p.ldr + n]);
+          if (p.epi == EPI_STORE_F32)
+            reinterpret_cast<float*>(p.out)[(size_t)tok * p.ldo + n] = v;
+          else
+            reinterpret_cast<bf16*>(p.out)[(size_t)tok * p.ldo + n] = __float2bfloat16(v);
+        }
+      };
+      constexpr int CH = BN >= 32 ? 32 : 16;
+#pragma unroll 1
+      for (int c = 0; c < BN / CH; ++c) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * CH);
+        if (CH == 32) tc_ld32(taddr, r); else tc_ld16(taddr, r);
+        tc_wait_ld();
+        float v = 0.f;
+#pragma unroll
+        for (int idx = 0; idx < CH; ++idx) {  // static register indices; J divides CH
+          const int col = ct * BN + c * CH + idx;
+          const float cs = col < p.cols ? p.rs[col] : 0.f;
+          v = fmaf(__uint_as_float(r[idx]), cs, v);
+          if ((idx + 1) % J == 0) {
+            const int tok = col / J;
+            v *= ts;
+            if (whole) {
+              finish(tok, v);
+            } else {
+              slot[(size_t)(tok - tok0) * TILE_N + row] = v;
+            }
+            v = 0.f;
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(accum_empty);
+      if (!whole) {
+        // split tile: the last CTA to arrive finishes it from the per-segment slots
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // all slot stores of this CTA issued
+        const int nseg = owner_of(t_lo + p.nk - 1, U, G) - first_owner + 1;
+        if (threadIdx.x == 64) {
+          __threadfence();                                // publish them (cumulative over the barrier)
+          const int prev = atomicAdd(p.counters + tile, 1);
+          *last_flag = (prev == nseg - 1);
+          if (prev == nseg - 1) p.counters[tile] = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*last_flag) {
+          __threadfence();
+          for (int g = 0; g < BN / J; ++g) {
+            float part[8];
+#pragma unroll
+            for (int sg = 0; sg < 8; ++sg)   // issue every load before the first use
+              part[sg] = sg < nseg ? __ldcg(tile_slots + ((size_t)sg * (BN / J) + g) * TILE_N + row) : 0.f;
+            float v = 0.f;
+#pragma unroll
+            for (int sg = 0; sg < 8; ++sg) v += part[sg];   // fixed order: bitwise reproducible
+            for (int sg = 8; sg < nseg; ++sg)
+              v += __ldcg(tile_slots + ((size_t)sg * (BN / J) + g) * TILE_N + row);
+            finish(tok0 + g, v);
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      u += len;
+      ++seg;
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (*abort_flag) {
+    // give copies that are still in flight time to land before the CTA's memory goes away
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) {
+    }
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Activation quantiser: optional RMSNorm (or SwiGLU of an interleaved gate/up row), then
+// J NVFP4 residual terms per token.  column (tok*J + j): xq [cols, K/2], sf tiled (see
+// header), rs[col] fp32.
+//
+// Grid = (tokens, K/4096): every CTA first reduces the whole (L2-resident) row for the
+// norm statistics and the row maximum, then each thread owns one 16-element block and
+// runs all J terms in registers.  The row scale of term j is rs_0 / 4^j -- a bound, not a
+// reduction: one e2m1 term leaves a remainder of at most 1/4 of the block maximum it
+// encoded (worst gap 4..6 of 6 plus the e4m3 scale rounding) -- so no second pass over
+// the row is needed.
+__global__ void __launch_bounds__(256)
+quant_act_kernel(const bf16* __restrict__ x, int ldx, const float* __restrict__ norm_w, float eps,
+                 uint8_t* __restrict__ xq, uint8_t* __restrict__ sf, float* __restrict__ rs, int K, int J,
+                 int kt4, int swiglu_in) {
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tok = blockIdx.x;
+  const bf16* xr = x + (size_t)tok * ldx;
+  // four consecutive elements starting at k (k % 4 == 0)
+  auto load4 = [&](int k, float (&v)[4]) {
+    if (swiglu_in) {  // interleaved (gate, up) pairs: K outputs from 2K inputs
+      const uint4 u = *reinterpret_cast<const uint4*>(xr + 2 * k);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 gu = bf162_bits_to_f2(w[i]);
+        v[i] = __bfloat162float(__float2bfloat16(silu_f(gu.x) * gu.y));
+      }
+    } else {
+      const uint2 u = *reinterpret_cast<const uint2*>(xr + k);
+      const float2 a = bf162_bits_to_f2(u.x), b = bf162_bits_to_f2(u.y);
+      v[0] = a.x, v[1] = a.y, v[2] = b.x, v[3] = b.y;
+    }
+  };
+  float rstd = 1.f;
+  if (norm_w != nullptr) {
+    float ss = 0.f;
+    for (int k = threadIdx.x * 4; k < K; k += blockDim.x * 4) {
+      float v[4];
+      load4(k, v);
+      ss += v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+    }
+    ss = block_sum(ss, red);
+    rstd = rsqrtf(ss / (float)K + eps);
+  }
+  float amax = 0.f;
+  for (int k = threadIdx.x * 4; k < K; k += blockDim.x * 4) {
+    float v[4];
+    load4(k, v);
+    if (norm_w != nullptr) {
+      const float4 w = *reinterpret_cast<const float4*>(norm_w + k);
+      v[0] = __bfloat162float(__float2bfloat16(v[0] * rstd * w.x));
+      v[1] = __bfloat162float(__float2bfloat16(v[1] * rstd * w.y));
+      v[2] = __bfloat162float(__float2bfloat16(v[2] * rstd * w.z));
+      v[3] = __bfloat162float(__float2bfloat16(v[3] * rstd * w.w));
+    }
+    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))));
+  }
+  amax = block_max(amax, red);
+  const float rs0 = fmaxf(amax, 1e-30f) * (1.f / (6.f * 448.f));
+  if (blockIdx.y == 0 && threadIdx.x < J) rs[tok * J + threadIdx.x] = rs0 * exp2f(-2.f * (float)threadIdx.x);
+  // this thread's quarter block
+  const int q4 = blockIdx.y * blockDim.x + threadIdx.x;  // index of the 4-element group
+  const int k = q4 * 4;
+  const int b = q4 >> 2;                                  // 16-element block
+  if (b >= kt4 * 4) return;
+  float r[4] = {0.f, 0.f, 0.f, 0.f};
+  if (k < K) {
+    load4(k, r);
+    if (norm_w != nullptr) {
+      const float4 w = *reinterpret_cast<const float4*>(norm_w + k);
+      r[0] = __bfloat162float(__float2bfloat16(r[0] * rstd * w.x));
+      r[1] = __bfloat162float(__float2bfloat16(r[1] * rstd * w.y));
+      r[2] = __bfloat162float(__float2bfloat16(r[2] * rstd * w.z));
+      r[3] = __bfloat162float(__float2bfloat16(r[3] * rstd * w.w));
+    }
+  }
+  float rscale = rs0;
+  for (int j = 0; j < J; ++j, rscale *= 0.25f) {
+    const int col = tok * J + j;
+    float bm = fmaxf(fmaxf(fabsf(r[0]), fabsf(r[1])), fmaxf(fabsf(r[2]), fabsf(r[3])));
+    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+    const float s = fminf(__fdividef(bm, 6.f * rscale), 448.f);
+    uint16_t s16;
+    asm("{ .reg .b16 t; cvt.rn.satfinite.e4m3x2.f32 t, %1, %2; mov.b16 %0, t; }" : "=h"(s16) : "f"(0.f), "f"(s));
+    const float sfv = h2_to_f2(cvt_e4m3x2_to_h2(s16)).x;
+    const float denom = sfv * rscale;
+    const float inv = denom > 0.f ? __frcp_rn(denom) : 0.f;
+    uint16_t lo, hi;
+    asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u16.u8 %0, t; }" : "=h"(lo) : "f"(r[1] * inv), "f"(r[0] * inv));
+    asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u16.u8 %0, t; }" : "=h"(hi) : "f"(r[3] * inv), "f"(r[2] * inv));
+    uint32_t h0, h1;
+    asm("{ .reg .b8 t; cvt.u8.u16 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(h0) : "h"(lo));
+    asm("{ .reg .b8 t; cvt.u8.u16 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(h1) : "h"(hi));
+    const float2 d0 = h2_to_f2(h0), d1 = h2_to_f2(h1);
+    r[0] = fmaf(-d0.x, denom, r[0]);   // the next term encodes the remainder
+    r[1] = fmaf(-d0.y, denom, r[1]);
+    r[2] = fmaf(-d1.x, denom, r[2]);
+    r[3] = fmaf(-d1.y, denom, r[3]);
+    if (k < K)
+      reinterpret_cast<uint16_t*>(xq + (size_t)col * (K >> 1))[q4] = (uint16_t)((lo & 0xff) | ((hi & 0xff) << 8));
+    if ((threadIdx.x & 3) == 0)  // scale byte (zero for the K padding)
+      sf[((size_t)(col >> 7) * kt4 + (b >> 2)) * SF_ATOM + (col & 31) * 16 + ((col & 127) >> 5) * 4 + (b & 3)] =
+          (k < K) ? (uint8_t)(s16 & 0xff) : (uint8_t)0;
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) return 1;
+    g_encode = (EncodeTiledFn)fn;
+  }
+  cuuint64_t dims[2] = {row_bytes, rows};
+  cuuint64_t strides[1] = {row_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)KT_BYTES, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 2;
+}
+
+template <int BN>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, int grid, cudaStream_t st) {
+  auto kern = gemm_nvfp4_kernel<BN>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM) != cudaSuccess) return 3;
+    configured = true;
+  }
+  return (int)trl_launch(kern, dim3(grid), dim3(GEMM_THREADS), (size_t)Cfg<BN>::SMEM, st, mw, mx, p);
+}
+
+}  // namespace
+
+// Quantise activations for the GEMM.  xq: [tokens*J, K/2]; sf: tiled, (ceil(tokens*J/256)*2) atoms
+// of rows x kt4 atoms of K; rs: [tokens*J].  K % 16 == 0.
+TRL_API int trl_quant_act_nvfp4(const void* x, int ldx, const void* norm_w, float eps, void* xq, void* sf,
+                                void* rs, int tokens, int K, int J, int swiglu_in, void* stream) {
+  if (K % 16 != 0 || J < 1 || J > 16) return (int)cudaErrorInvalidValue;
+  const int nk = (K + KT_ELEMS - 1) / KT_ELEMS;
+  const int slices = (nk * KT_ELEMS / 4 + 255) / 256;  // 4 elements per thread
+  return (int)trl_launch(quant_act_kernel, dim3(tokens, slices), dim3(256), 0, (cudaStream_t)stream, (const bf16*)x,
+                         ldx, (const float*)norm_w, eps, (uint8_t*)xq, (uint8_t*)sf, (float*)rs, K, J, nk * 4,
+                         swiglu_in);
+}
+
+// Largest number of CTAs that share one output tile under the even stream-K split.
+static int max_segments(long long U, int G, int nk) {
+  // a tile spans nk consecutive units; CTA ranges are ~U/G long
+  const long long per = U / G;
+  if (per >= nk && U % G == 0 && per % nk == 0) return 1;
+  return (int)min((long long)G, (long long)nk / (per > 0 ? per : 1) + 2);
+}
+
+static int pick_bn(int cols) {
+  int bn = 16;
+  while (bn < cols && bn < 256) bn <<= 1;
+  return bn;
+}
+
+// Bytes of split-K scratch trl_gemm_nvfp4 needs for this problem (0 if no tile is split).
+TRL_API long trl_gemm_nvfp4_scratch_bytes(int tokens, int J, int N, int K, int max_ctas) {
+  const int cols = tokens * J, BN = pick_bn(cols);
+  const int n_tiles = (N + TILE_N - 1) / TILE_N, c_tiles = (cols + BN - 1) / BN, nk = (K + KT_ELEMS - 1) / KT_ELEMS;
+  int sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (max_ctas > 0) sms = min(sms, max_ctas);
+  const long long U = (long long)n_tiles * c_tiles * nk;
+  const int grid = (int)min((long long)sms, U);
+  return (long)n_tiles * c_tiles * max_segments(U, grid, nk) * (BN / J) * TILE_N * (long)sizeof(float);
+}
+
+// out[tok, n] = epi(...).  wq [N, K/2] packed e2m1; sfw / sfx tiled scales; partial: fp32
+// split-K slots of at least trl_gemm_nvfp4_scratch_bytes() bytes (contents irrelevant);
+// counters: int32 [n_tiles * c_tiles], zero on entry and zero again on exit.
+TRL_API int trl_gemm_nvfp4(const void* wq, const void* sfw, const void* tscale, const void* xq, const void* sfx,
+                           const void* rs, const void* residual, int ldr, void* out, int ldo, void* partial,
+                           void* counters, long partial_bytes, int tokens, int J, int N, int K, int epi, int max_ctas,
+                           int split, void* stream) {
+  if (K % 32 != 0 || J < 1 || (32 % J) != 0 || J > 16) return (int)cudaErrorInvalidValue;
+  const int cols = tokens * J;
+  const int BN = pick_bn(cols);
+  CUtensorMap mw, mx;
+  if (make_map(&mw, wq, (uint64_t)N, (uint64_t)K / 2, TILE_N)) return (int)cudaErrorInvalidValue;
+  if (make_map(&mx, xq, (uint64_t)cols, (uint64_t)K / 2, (uint32_t)BN)) return (int)cudaErrorInvalidValue;
+  GemmParams p;
+  p.sfw = (const uint8_t*)sfw, p.sfx = (const uint8_t*)sfx, p.tscale = (const float*)tscale, p.rs = (const float*)rs;
+  p.residual = (const bf16*)residual, p.out = out, p.partial = (float*)partial, p.counters = (int*)counters;
+  p.N = N, p.K = K, p.cols = cols, p.tokens = tokens, p.J = J, p.ldr = ldr, p.ldo = ldo;
+  p.n_tiles = (N + TILE_N - 1) / TILE_N;
+  p.c_tiles = (cols + BN - 1) / BN;
+  p.nk = (K + KT_ELEMS - 1) / KT_ELEMS;
+  p.kt4 = p.nk * 4;
+  p.epi = epi;
+  int sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (max_ctas > 0) sms = min(sms, max_ctas);
+  const long long U = (long long)p.n_tiles * p.c_tiles * p.nk;
+  p.split = split;
+  const int grid = split ? (int)min((long long)sms, U) : min(sms, p.n_tiles * p.c_tiles);
+  p.max_seg = split ? max_segments(U, grid, p.nk) : 1;
+  if (split && (size_t)p.n_tiles * p.c_tiles * p.max_seg * (BN / J) * TILE_N * sizeof(float) > (size_t)partial_bytes)
+    return (int)cudaErrorMemoryAllocation;
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (BN) {
+    case 16: return launch<16>(mw, mx, p, grid, st);
+    case 32: return launch<32>(mw, mx, p, grid, st);
+    case 64: return launch<64>(mw, mx, p, grid, st);
+    case 128: return launch<128>(mw, mx, p, grid, st);
+    default: return launch<256>(mw, mx, p, grid, st);
+  }
+}

@@ -57,38 +57,55 @@ __global__ void swiglu_kernel(const bf16* __restrict__ gu, bf16* __restrict__ ou
   }
 }
 
-__global__ void __launch_bounds__(1024)
-argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__ out) {
-  __shared__ float sv[32];
-  __shared__ int si[32];
+// Row argmax in two stages: (row, chunk) partial maxima, then one warp-level merge per row.
+// Ties resolve to the lowest index.
+constexpr int ARGMAX_CHUNKS = 64;
+__device__ __forceinline__ void argmax_merge(float& best, int& bi, float ov, int oi) {
+  if (ov > best || (ov == best && oi < bi)) best = ov, bi = oi;
+}
+__global__ void __launch_bounds__(256)
+argmax_stage1_kernel(const float* __restrict__ logits, int ld, int V, float* __restrict__ pv,
+                     int* __restrict__ pi) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
   pdl_launch_dependents();
   pdl_wait();
-  const float* row = logits + (size_t)blockIdx.x * ld;
+  const int row = blockIdx.x, chunk = blockIdx.y;
+  const int per = (V + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
+  const int lo = chunk * per, hi = min(V, lo + per);
+  const float* r = logits + (size_t)row * ld;
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = row[i];
-    if (v > best) best = v, bi = i;  // strided scan keeps the lowest index on ties per thread
-  }
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) argmax_merge(best, bi, r[i], i);
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > best || (ov == best && oi < bi)) best = ov, bi = oi;
-  }
+  for (int o = 16; o > 0; o >>= 1)
+    argmax_merge(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   if (lane == 0) sv[w] = best, si[w] = bi;
   __syncthreads();
-  if (w == 0) {
-    best = lane < (blockDim.x >> 5) ? sv[lane] : -INFINITY;
-    bi = lane < (blockDim.x >> 5) ? si[lane] : 0x7fffffff;
+  if (threadIdx.x == 0) {
+    for (int k = 1; k < 8; ++k) argmax_merge(best, bi, sv[k], si[k]);
+    pv[row * ARGMAX_CHUNKS + chunk] = best;
+    pi[row * ARGMAX_CHUNKS + chunk] = bi;
+  }
+}
+__global__ void __launch_bounds__(64)
+argmax_stage2_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x;
+  float best = pv[row * ARGMAX_CHUNKS + threadIdx.x];
+  int bi = pi[row * ARGMAX_CHUNKS + threadIdx.x];
+  __shared__ float sv[2];
+  __shared__ int si[2];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) best = ov, bi = oi;
-    }
-    if (lane == 0) out[blockIdx.x] = bi;
+  for (int o = 16; o > 0; o >>= 1)
+    argmax_merge(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
+  if ((threadIdx.x & 31) == 0) sv[threadIdx.x >> 5] = best, si[threadIdx.x >> 5] = bi;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    argmax_merge(best, bi, sv[1], si[1]);
+    out[row] = bi;
   }
 }
 
@@ -230,9 +247,15 @@ TRL_API int trl_swiglu(const void* gu, void* out, long n_out, void* stream) {
   return (int)trl_launch(swiglu_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const bf16*)gu,
                          (bf16*)out, n_out);
 }
-TRL_API int trl_argmax(const void* logits, int ld, int M, int V, void* out, void* stream) {
-  return (int)trl_launch(argmax_kernel, dim3(M), dim3(1024), 0, (cudaStream_t)stream,
-                         (const float*)logits, ld, V, (int*)out);
+// scratch: M * 64 floats followed by M * 64 ints.
+TRL_API int trl_argmax(const void* logits, int ld, int M, int V, void* out, void* scratch, void* stream) {
+  float* pv = (float*)scratch;
+  int* pi = (int*)(pv + (size_t)M * ARGMAX_CHUNKS);
+  cudaError_t e = trl_launch(argmax_stage1_kernel, dim3(M, ARGMAX_CHUNKS), dim3(256), 0, (cudaStream_t)stream,
+                             (const float*)logits, ld, V, pv, pi);
+  if (e != cudaSuccess) return (int)e;
+  return (int)trl_launch(argmax_stage2_kernel, dim3(M), dim3(64), 0, (cudaStream_t)stream, (const float*)pv,
+                         (const int*)pi, (int*)out);
 }
 TRL_API int trl_adamw(void* p, void* m, void* v, const void* g, void* p_bf16, long n, float lr, float b1,
                       float b2, float eps, float wd, int step, float gscale, void* stream) {

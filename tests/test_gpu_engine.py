@@ -12,6 +12,9 @@ def setup():
     from tilerl_b200.factory import build_model, make_ops
     cfg = small_gpu()
     ops = make_ops("cuda")
+    # same activation precision for every token count, so a token's numerics do not depend on
+    # how the scheduler batched it (chunked prefill == one shot == single)
+    ops.terms_small = ops.terms_large = 4
     model = build_model(cfg, "cuda", seed=0, ops=ops)
     return cfg, ops, model
 

@@ -93,11 +93,13 @@ def quantize_nvfp4(w: torch.Tensor, tscale: torch.Tensor | None = None) -> NVFP4
     n, k = w.shape
     if tscale is None:
         amax = w.abs().max().clamp_min(1e-30)
-        tscale = (amax / (E2M1_MAX * E4M3_MAX)).reshape(1)
+        # tensor / tensor: a true IEEE division (tensor / python-scalar may be lowered
+        # to a multiply by the reciprocal, which differs in the last bit)
+        tscale = (amax / torch.tensor(E2M1_MAX * E4M3_MAX, device=w.device)).reshape(1)
     tscale = tscale.float().reshape(1)
     blocks = w.view(n, k // FP4_BLOCK, FP4_BLOCK)
     bmax = blocks.abs().amax(-1)
-    s = (bmax / E2M1_MAX / tscale).clamp(max=E4M3_MAX)
+    s = (bmax / torch.tensor(E2M1_MAX, device=w.device) / tscale).clamp(max=E4M3_MAX)
     s8 = s.to(torch.float8_e4m3fn)
     sf = s8.float()
     denom = (sf * tscale).unsqueeze(-1)

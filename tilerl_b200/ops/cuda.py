@@ -18,6 +18,7 @@ launch M ``:733-905``).
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, Optional
 
 import torch
@@ -52,7 +53,8 @@ class Workspace:
 class CudaOps:
     name = "cuda"
 
-    def __init__(self, device="cuda", tp=None, comm=None, attn_splits: int = 0, use_tc_gemm: bool = True):
+    def __init__(self, device="cuda", tp=None, comm=None, attn_splits: int = 0, use_tc_gemm: bool = True,
+                 decode_tc: Optional[bool] = None, terms_small: int = 4, terms_large: int = 2):
         if not torch.cuda.is_available():
             raise RuntimeError("CudaOps needs a CUDA device")
         self.lib = N.lib()
@@ -61,7 +63,12 @@ class CudaOps:
         self.tp = tp
         self.comm = comm          # parallel.symm.SymmComm or None
         self.attn_splits = attn_splits
-        self.use_tc_gemm = use_tc_gemm
+        self.use_tc_gemm = use_tc_gemm and os.environ.get("TRL_GEMM", "tc") == "tc"
+        # small-M projections: tcgen05 GEMM with `terms_small` residual terms (bf16-accurate
+        # activations at HBM speed) or the SIMT GEMV (TRL_DECODE=simt)
+        self.decode_tc = (os.environ.get("TRL_DECODE", "tc") == "tc") if decode_tc is None else decode_tc
+        self.terms_small = int(os.environ.get("TRL_TERMS_SMALL", terms_small))
+        self.terms_large = int(os.environ.get("TRL_TERMS_LARGE", terms_large))
         self.act_dtype = torch.bfloat16
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
 
@@ -90,14 +97,33 @@ class CudaOps:
         else:
             raise TypeError(f"no GEMV for weight type {type(w)}")
 
-    def _gemm(self, x, w, out_name: str):
-        """Large-M projection ``[T, K] x W^T -> [T, N]`` bf16."""
-        from . import gemm
+    def _tc(self, w, t: int) -> bool:
+        return isinstance(w, NVFP4Tensor) and self.use_tc_gemm and (t > GEMV_MAX_M or self.decode_tc)
+
+    def _linear(self, x, w, y, *, norm_w=None, eps=0.0, residual=None, epi=EPI_STORE):
+        """``y = epi(norm(x) @ W^T)`` with everything fused into one or two kernels."""
         t = x.shape[0]
+        if self._tc(w, t):
+            from .gemm_tc import gemm_nvfp4
+            terms = self.terms_small if t <= GEMV_MAX_M else self.terms_large
+            gemm_nvfp4(self, x, w, y, terms=terms, norm_w=norm_w, eps=eps, residual=residual, epi=epi)
+            return
+        if t <= GEMV_MAX_M:
+            self._gemv(x, w, y, norm_w=norm_w, eps=eps, residual=residual, epi=epi)
+            return
+        # unfused large-M path (non-NVFP4 weights, or TRL_GEMM=dequant for bisecting numerics)
+        from . import gemm
+        h = self._rmsnorm(x, norm_w, eps) if norm_w is not None else x
         n = w.shape[0]
-        y = self.ws.get(out_name, (t, n), torch.bfloat16)
-        gemm.linear(self, x, w, y)
-        return y
+        tmp = self.ws.get("gemm_tmp", (t, n), torch.bfloat16)
+        gemm.linear(self, h, w, tmp)
+        if epi == EPI_SWIGLU:
+            N.check(self.lib.trl_swiglu(tmp.data_ptr(), y.data_ptr(), y.numel(), N.stream()), "swiglu")
+        elif epi == EPI_RESIDUAL:
+            N.check(self.lib.trl_add(tmp.data_ptr(), residual.data_ptr(), y.data_ptr(), tmp.numel(), N.stream()), "add")
+        else:
+            y.copy_(tmp)
+        N.count()
 
     def _rmsnorm(self, x, w, eps, name="h"):
         t, h = x.shape
@@ -121,27 +147,22 @@ class CudaOps:
         return x
 
     def norm_linear(self, x, norm_w, w, eps, lora=None):
-        t = x.shape[0]
-        n = w.shape[0]
-        if t <= GEMV_MAX_M:
-            y = self.ws.get("proj", (t, n), torch.bfloat16)
-            self._gemv(x, w, y, norm_w=self._f32(norm_w), eps=eps)
-            if lora is not None:
-                h = self._rmsnorm(x, norm_w, eps)
-                self._lora_add(y, h, lora)
-            return y
-        h = self._rmsnorm(x, norm_w, eps)
-        return self._lora_add(self._gemm(h, w, "proj"), h, lora)
+        t, n = x.shape[0], w.shape[0]
+        y = self.ws.get("proj", (t, n), torch.bfloat16)
+        self._linear(x, w, y, norm_w=self._f32(norm_w), eps=eps)
+        if lora is not None:
+            self._lora_add(y, self._rmsnorm(x, norm_w, eps), lora)
+        return y
 
     def norm_linear_swiglu(self, x, norm_w, w, eps, lora=None):
-        t = x.shape[0]
-        n = w.shape[0]
+        t, n = x.shape[0], w.shape[0]
         act = self.ws.get("act", (t, n // 2), torch.bfloat16)
-        if t <= GEMV_MAX_M and lora is None:
-            self._gemv(x, w, act, norm_w=self._f32(norm_w), eps=eps, epi=EPI_SWIGLU)
+        if lora is None:
+            self._linear(x, w, act, norm_w=self._f32(norm_w), eps=eps, epi=EPI_SWIGLU)
             return act
-        h = self._rmsnorm(x, norm_w, eps)
-        gu = self._lora_add(self._gemm(h, w, "proj"), h, lora)
+        gu = self.ws.get("proj", (t, n), torch.bfloat16)
+        self._linear(x, w, gu, norm_w=self._f32(norm_w), eps=eps)
+        self._lora_add(gu, self._rmsnorm(x, norm_w, eps), lora)
         N.check(self.lib.trl_swiglu(gu.data_ptr(), act.data_ptr(), act.numel(), N.stream()), "swiglu")
         N.count()
         return act
@@ -149,15 +170,12 @@ class CudaOps:
     def linear_residual(self, a, w, residual, lora=None):
         """``residual += a @ W^T`` (in place on the residual stream).  Under TP the
         partial products are summed across ranks inside the fused kernel."""
-        t = a.shape[0]
         if self.comm is not None and self.comm.world > 1:
             return self.comm.linear_allreduce_residual(self, a, w, residual, lora)
-        if t <= GEMV_MAX_M and lora is None:
-            self._gemv(a, w, residual, residual=residual, epi=EPI_RESIDUAL)
-            return residual
-        y = self._lora_add(self._gemm(a, w, "rowout"), a, lora)
-        N.check(self.lib.trl_add(y.data_ptr(), residual.data_ptr(), residual.data_ptr(), y.numel(), N.stream()), "add")
-        N.count()
+        self._linear(a, w, residual, residual=residual, epi=EPI_RESIDUAL)
+        if lora is not None:
+            zero = torch.zeros_like(residual)
+            residual.add_(self._lora_add(zero, a, lora))
         return residual
 
     def attention(self, qkv, lp, batch, pool, attn_idx, cfg, n_q, n_kv):
@@ -227,15 +245,14 @@ class CudaOps:
         if m <= GEMV_MAX_M:
             self._gemv(x.contiguous(), w, logits, norm_w=self._f32(norm_w), eps=eps, epi=EPI_STORE_F32)
         else:
-            h = self._rmsnorm(x.contiguous(), norm_w, eps, name="h_head")
-            wt = w if isinstance(w, torch.Tensor) else None
-            if wt is None:
-                from . import gemm
-                y = self._gemm(h, w, "head_bf16")
-                logits.copy_(y)
+            xc = x.contiguous()
+            if isinstance(w, NVFP4Tensor) and self.use_tc_gemm:
+                self._linear(xc, w, logits, norm_w=self._f32(norm_w), eps=eps, epi=EPI_STORE_F32)
             else:
-                torch.matmul(h, wt.t(), out=self.ws.get("head_bf16", (m, n), torch.bfloat16))
-                logits.copy_(self.ws.get("head_bf16", (m, n), torch.bfloat16))
+                h = self._rmsnorm(xc, norm_w, eps, name="h_head")
+                hb = self.ws.get("head_bf16", (m, n), torch.bfloat16)
+                torch.matmul(h, (w if isinstance(w, torch.Tensor) else w.dequant().to(torch.bfloat16)).t(), out=hb)
+                logits.copy_(hb)
         if self.comm is not None and self.comm.world > 1:
             return self.comm.all_gather_logits(logits)
         return logits
@@ -243,8 +260,10 @@ class CudaOps:
     def argmax(self, logits):
         m, v = logits.shape
         out = self.ws.get("argmax", (m,), torch.int32)
-        N.check(self.lib.trl_argmax(logits.data_ptr(), logits.stride(0), m, v, out.data_ptr(), N.stream()), "argmax")
-        N.count()
+        scratch = self.ws.get("argmax_scratch", (m * 128,), torch.float32)
+        N.check(self.lib.trl_argmax(logits.data_ptr(), logits.stride(0), m, v, out.data_ptr(), scratch.data_ptr(),
+                                    N.stream()), "argmax")
+        N.count(2)
         return out
 
     # ---- training / maintenance kernels ------------------------------------------------------

@@ -31,7 +31,7 @@ def linear(ops, x: torch.Tensor, w, y: torch.Tensor) -> None:
     if isinstance(w, NVFP4Tensor):
         if has_tc(ops):
             from .gemm_tc import gemm_nvfp4
-            return gemm_nvfp4(ops, x, w, y)
+            return gemm_nvfp4(ops, x, w, y, terms=ops.terms_large)
         n, k = w.shape
         wd = ops.ws.get("dequant_w", (n, k), torch.bfloat16)
         ops.dequantize_nvfp4(w, wd)

@@ -1,0 +1,115 @@
+"""Python side of the tcgen05 NVFP4 GEMM: scale-factor tiling, scratch buffers, launch.
+
+``gemm_nvfp4(ops, x, w, y, ...)`` runs ``y = epi(x' @ W^T)`` for any token count:
+
+* ``terms`` (J) NVFP4 residual terms per token decide the activation precision
+  (1 = W4A4, 2 ~ FP8-class, 4 ~ bf16); ``norm_w`` folds RMSNorm and ``swiglu_in``
+  folds SwiGLU of an interleaved gate/up row into the quantiser.
+* the weight's e4m3 scales are re-tiled once into the 128x4 layout the tensor core
+  reads (``w.sf_tiled``), next to the checkpoint-layout scales the GEMV uses.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..formats import NVFP4Tensor
+from . import native as N
+
+N.register("trl_quant_act_nvfp4", [N.P, N.I, N.P, N.F, N.P, N.P, N.P, N.I, N.I, N.I, N.I, N.P])
+N.register("trl_gemm_nvfp4", [N.P, N.P, N.P, N.P, N.P, N.P, N.P, N.I, N.P, N.I, N.P, N.P, N.L,
+                              N.I, N.I, N.I, N.I, N.I, N.I, N.I, N.P])
+N.register("trl_gemm_nvfp4_scratch_bytes", [N.I, N.I, N.I, N.I, N.I])
+
+KT = 256  # K elements per k-tile
+
+
+def tile_scales(scale: torch.Tensor, K: int) -> torch.Tensor:
+    """``[R, K/16]`` e4m3 (any device) -> tiled bytes ``[ceil(R/128), nk*4, 32, 4, 4]`` with
+    byte (r, k16) at ``((r//128)*kt4 + k16//4)*512 + (r%32)*16 + ((r%128)//32)*4 + k16%4``;
+    padding rows / k-blocks are zero."""
+    r, kb = scale.shape
+    nk = (K + KT - 1) // KT
+    rp, kp = (r + 127) // 128 * 128, nk * 16
+    s = torch.zeros(rp, kp, dtype=torch.uint8, device=scale.device)
+    s[:r, :kb] = scale.view(torch.uint8)
+    s = s.view(rp // 128, 4, 32, kp // 4, 4)        # [atom, r/32, r%32, k64, k16%4]
+    return s.permute(0, 3, 2, 1, 4).contiguous()      # [atom, k64, r%32, r/32, k16%4]
+
+
+def sf_tiled(w: NVFP4Tensor) -> torch.Tensor:
+    t = getattr(w, "sf_tiled", None)
+    if t is None or getattr(w, "sf_version", None) is not w.scale._version:
+        t = tile_scales(w.scale, w.shape[1])
+        w.sf_tiled = t
+        w.sf_version = w.scale._version
+    return t
+
+
+def quant_act(ops, x: torch.Tensor, K: int, terms: int, *, norm_w=None, eps: float = 0.0,
+              swiglu_in: bool = False):
+    """Quantise ``x [T, K]`` (or ``[T, 2K]`` interleaved gate/up when ``swiglu_in``).
+    Returns (xq, sfx, rs) workspace views."""
+    t = x.shape[0]
+    cols = t * terms
+    nk = (K + KT - 1) // KT
+    atoms = (cols + 255) // 256 * 2
+    xq = ops.ws.get("tc_xq", (cols, K // 2), torch.uint8)
+    sfx = ops.ws.get("tc_sfx", (atoms * nk * 4 * 512,), torch.uint8)
+    rs = ops.ws.get("tc_rs", (cols,), torch.float32)
+    N.check(ops.lib.trl_quant_act_nvfp4(x.data_ptr(), x.stride(0), N.ptr(norm_w), eps, xq.data_ptr(),
+                                        sfx.data_ptr(), rs.data_ptr(), t, K, terms, int(swiglu_in), N.stream()),
+            "quant_act_nvfp4")
+    N.count()
+    return xq, sfx, rs
+
+
+def _scratch(ops, nbytes: int, tiles: int):
+    """Split-K slot buffer (contents irrelevant) and the zero-initialised tile counters
+    (the kernel resets each counter it used)."""
+    buf = ops.ws.get("tc_partial", (max(nbytes // 4, 1),), torch.float32)
+    cnt = ops.ws.bufs.get("tc_counters")
+    if cnt is None or cnt.numel() < tiles:
+        if cnt is not None and torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("tile counters would be reallocated during graph capture")
+        ops.ws.bufs["tc_counters"] = torch.zeros(max(tiles, 8192), dtype=torch.int32, device=ops.device)
+    return buf, ops.ws.bufs["tc_counters"]
+
+
+def _want_split(ops, n: int, k: int, cols: int) -> bool:
+    """Split tiles along K only when whole tiles cannot occupy the SMs."""
+    import os
+    mode = os.environ.get("TRL_SPLITK", "auto")
+    if mode in ("0", "1"):
+        return mode == "1"
+    tiles = ((n + 127) // 128) * ((cols + 255) // 256 if cols > 256 else 1)
+    return tiles < ops.sms
+
+
+def gemm_nvfp4(ops, x: torch.Tensor, w: NVFP4Tensor, y: torch.Tensor, *, terms: int = 1, norm_w=None,
+               eps: float = 0.0, residual: Optional[torch.Tensor] = None, epi: int = 0,
+               swiglu_in: bool = False, max_ctas: int = 0, split: Optional[bool] = None) -> None:
+    n, k = w.shape
+    t = x.shape[0]
+    xq, sfx, rs = quant_act(ops, x, k, terms, norm_w=norm_w, eps=eps, swiglu_in=swiglu_in)
+    cols = t * terms
+    bn = 16
+    while bn < cols and bn < 256:
+        bn *= 2
+    c_tiles = (cols + bn - 1) // bn
+    n_tiles = (n + 127) // 128
+    ops.lib.trl_gemm_nvfp4_scratch_bytes.restype = __import__("ctypes").c_long
+    nbytes = ops.lib.trl_gemm_nvfp4_scratch_bytes(t, terms, n, k, max_ctas)
+    partial, counters = _scratch(ops, nbytes, n_tiles * c_tiles)
+    N.check(ops.lib.trl_gemm_nvfp4(
+        w.wq.data_ptr(), sf_tiled(w).data_ptr(), w.tscale.data_ptr(), xq.data_ptr(), sfx.data_ptr(),
+        rs.data_ptr(), N.ptr(residual), residual.stride(0) if residual is not None else 0,
+        y.data_ptr(), y.stride(0), partial.data_ptr(), counters.data_ptr(), partial.numel() * 4, t, terms, n, k,
+        epi, max_ctas, int(_want_split(ops, n, k, cols) if split is None else split),
+        N.stream()), "gemm_nvfp4")
+    N.count()
+
+
+def gemm_bf16(ops, x, w, y):
+    torch.matmul(x, w.t(), out=y)

@@ -1,0 +1,106 @@
+"""Time individual kernels at the 27B's projection shapes with CUDA events.
+
+    python -m tilerl_b200.utils.kernel_bench [--m 1] [--only gemm|gemv|quant] [--reps 20]
+
+Each measurement rotates over enough distinct weight copies to exceed the 126 MB L2,
+so every launch streams its weights from HBM; the figure printed is achieved weight
+bytes per second of the launch (or launch pair) named.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+SHAPES = {"gate_up": (34816, 5120), "down": (5120, 17408), "gdn_in": (16480, 5120),
+          "qkv": (14336, 5120), "o": (5120, 6144)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--terms", type=int, default=4)
+    ap.add_argument("--only", default="")
+    ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--shapes", default="")
+    ap.add_argument("--max-ctas", type=int, default=0)
+    ap.add_argument("--split", type=int, default=1)
+    args = ap.parse_args()
+    from tilerl_b200.formats import NVFP4Tensor
+    from tilerl_b200.ops.cuda import CudaOps
+    from tilerl_b200.ops.gemm_tc import gemm_nvfp4, quant_act, sf_tiled
+    from tilerl_b200.ops import native
+    dev = torch.device("cuda", 0)
+    ops = CudaOps(dev)
+    out = {}
+    names = [s for s in args.shapes.split(",") if s] or list(SHAPES)
+    for name in names:
+        n, k = SHAPES[name]
+        wbytes = n * k // 2 + n * k // 16
+        copies = max(2, int(400e6 // wbytes) + 1)
+        ws = []
+        for c in range(copies):
+            w = NVFP4Tensor(torch.randint(0, 255, (n, k // 2), dtype=torch.uint8, device=dev),
+                            (torch.rand(n, k // 16, device=dev) + 0.5).to(torch.float8_e4m3fn),
+                            torch.ones(1, device=dev))
+            sf_tiled(w)
+            ws.append(w)
+        x = torch.randn(args.m, k, device=dev).to(torch.bfloat16)
+        y = torch.zeros(args.m, n, dtype=torch.bfloat16, device=dev)
+        res = {}
+
+        def timeit(fn):
+            """Device time per launch: the launches are captured in one CUDA graph so the
+            host launch path is not part of the figure."""
+            for i in range(3):
+                fn(ws[i % copies])
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for i in range(args.reps):
+                    fn(ws[i % copies])
+            g.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / args.reps * 1e3  # us
+
+        if args.only in ("", "gemv") and args.m <= 8:
+            us = timeit(lambda w: ops._gemv(x, w, y))
+            res["gemv_simt_us"] = round(us, 2)
+            res["gemv_simt_TBs"] = round(wbytes / us / 1e6, 3)
+        if args.only in ("", "gemm"):
+            us = timeit(lambda w: gemm_nvfp4(ops, x, w, y, terms=args.terms, max_ctas=args.max_ctas, split=bool(args.split)))
+            res["quant+gemm_tc_us"] = round(us, 2)
+            res["quant+gemm_tc_TBs"] = round(wbytes / us / 1e6, 3)
+            xq, sfx, rs = quant_act(ops, x, k, args.terms)
+            from tilerl_b200.ops.gemm_tc import _scratch
+            import ctypes
+            ops.lib.trl_gemm_nvfp4_scratch_bytes.restype = ctypes.c_long
+            nb = ops.lib.trl_gemm_nvfp4_scratch_bytes(args.m, args.terms, n, k, args.max_ctas)
+            partial, counters = _scratch(ops, nb, 8192)
+
+            def gemm_only(w):
+                native.check(ops.lib.trl_gemm_nvfp4(
+                    w.wq.data_ptr(), w.sf_tiled.data_ptr(), w.tscale.data_ptr(), xq.data_ptr(), sfx.data_ptr(),
+                    rs.data_ptr(), None, 0, y.data_ptr(), y.stride(0), partial.data_ptr(), counters.data_ptr(),
+                    partial.numel() * 4, args.m, args.terms, n, k, 0, args.max_ctas, args.split, native.stream()))
+            us = timeit(gemm_only)
+            res["gemm_tc_us"] = round(us, 2)
+            res["gemm_tc_TBs"] = round(wbytes / us / 1e6, 3)
+        if args.only in ("", "quant"):
+            us = timeit(lambda w: quant_act(ops, x, k, args.terms))
+            res["quant_us"] = round(us, 2)
+        out[name] = res
+        del ws
+        torch.cuda.empty_cache()
+    print(json.dumps(out, indent=1))
+    print("kernel_bench done")
+
+
+if __name__ == "__main__":
+    main()
