@@ -36,6 +36,7 @@
 // (packages/tilerl-kernels/src/tilerl_kernels/registry.py:188-189); functionally this
 // replaces linear_fp4_fp8 / linear_fp4_gemv / linear_fp4_mma8 (kernels_linear.py:924-1687).
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -118,6 +119,24 @@ __device__ __forceinline__ void tc_mma_nvfp4(uint32_t d_tmem, uint64_t adesc, ui
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
       : "memory");
 }
+// Same instructions with the 64-bit shared-memory descriptor given as (low, high) words: the
+// high word is loop invariant and the low word is an affine function of stage and k-block,
+// which keeps the single issuing thread's instruction stream short.
+__device__ __forceinline__ void tc_cp_sf_lh(uint32_t taddr, uint32_t lo, uint32_t hi) {
+  asm volatile("{ .reg .b64 d; mov.b64 d, {%1, %2}; tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d; }"
+               ::"r"(taddr), "r"(lo), "r"(hi) : "memory");
+}
+__device__ __forceinline__ void tc_mma_nvfp4_lh(uint32_t d_tmem, uint32_t alo, uint32_t blo, uint32_t hi,
+                                                uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{ .reg .pred p; .reg .b64 da, db;\n"
+      "  mov.b64 da, {%1, %3}; mov.b64 db, {%2, %3};\n"
+      "  setp.ne.b32 p, %5, 0;\n"
+      "  tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], da, db, %4, [%6], [%7], p; }\n"
+      ::"r"(d_tmem), "r"(alo), "r"(blo), "r"(hi), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -171,6 +190,8 @@ struct GemmParams {
   int ldr, ldo;
   int n_tiles, c_tiles, nk, kt4;
   int max_seg;
+  int w_tiled; // weights stored tile-contiguous [n_tiles, nk, 128 rows, 128 B]
+  int dbg;     // timing experiments only: bit0 skip SF copies, bit1 skip MMAs, bit2 skip activation loads
   int split;   // 1: stream-K over (tile, k-tile) units; 0: whole tiles per CTA
   int epi;
 };
@@ -191,9 +212,8 @@ struct Cfg {
   static constexpr int SFA_BYTES = 4 * SF_ATOM;
   static constexpr int SFB_BYTES = SFB_ATOMS * 4 * SF_ATOM;
   static constexpr int STAGE = A_BYTES + B_ALLOC + SFA_BYTES + SFB_BYTES;
-  // small-BN (decode) tiles: 4 stages and half the TMEM, so that the next kernel's CTA can
-  // become resident (and prefetch its weights) while this one drains
-  static constexpr int STAGES = BN <= 64 ? 4 : ((200 * 1024) / STAGE > 8 ? 8 : (200 * 1024) / STAGE);
+  // as many stages as fit: the weight stream is latency-bound below ~150 KB in flight per SM
+  static constexpr int STAGES = (200 * 1024) / STAGE > 8 ? 8 : (200 * 1024) / STAGE;
   static constexpr int TMEM_COLS = BN <= 64 ? 256 : 512;
   static constexpr int SF_COL0 = BN <= 64 ? 128 : 256;
   static constexpr int SMEM = STAGES * STAGE + 1024 /*align*/ + 256 /*barriers*/;
@@ -249,43 +269,54 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      long long u = u0;
-      int it = 0;
+      // running (tile, k-tile) coordinates: no division on the per-unit path
+      const int n_units = (int)(u1 - u0);
+      int tile0 = (int)(u0 / p.nk), kt = (int)(u0 % p.nk);
+      int nt = tile0 / p.c_tiles, ct = tile0 % p.c_tiles;
+      const uint32_t smem0 = smem_u32(smem);
+      auto load_w = [&](int s_, int nt_, int kt_) {
+        const uint32_t st = smem0 + (uint32_t)s_ * C::STAGE;
+        mbar_expect_tx(full_bar(s_), stage_bytes);
+        tma_load_2d(st, &map_w, p.w_tiled ? 0 : kt_ * KT_BYTES,
+                    p.w_tiled ? (nt_ * p.nk + kt_) * TILE_N : nt_ * TILE_N, full_bar(s_));
+        bulk_load(st + C::A_BYTES + C::B_ALLOC, p.sfw + ((size_t)(nt_ * p.kt4 + kt_ * 4)) * SF_ATOM, C::SFA_BYTES,
+                  full_bar(s_));
+      };
       // prologue: weight tiles of the first S units do not depend on the previous kernel
-      const int pre = (int)min((long long)S, u1 - u0);
-      for (int i = 0; i < pre; ++i) {
-        const long long uu = u0 + i;
-        const int tile = (int)(uu / p.nk), kt = (int)(uu % p.nk);
-        const int nt = tile / p.c_tiles;
-        unsigned char* st = smem + (size_t)i * C::STAGE;
-        mbar_expect_tx(full_bar(i), stage_bytes);
-        tma_load_2d(smem_u32(st), &map_w, kt * KT_BYTES, nt * TILE_N, full_bar(i));
-        bulk_load(smem_u32(st + C::A_BYTES + C::B_ALLOC), p.sfw + ((size_t)nt * p.kt4 + (size_t)kt * 4) * SF_ATOM,
-                  C::SFA_BYTES, full_bar(i));
+      const int pre = min(S, n_units);
+      {
+        int nt_ = nt, ct_ = ct, kt_ = kt;
+        for (int i = 0; i < pre; ++i) {
+          load_w(i, nt_, kt_);
+          if (++kt_ == p.nk) {
+            kt_ = 0;
+            if (++ct_ == p.c_tiles) ct_ = 0, ++nt_;
+          }
+        }
       }
       pdl_wait();
       bool ok = true;
-      for (; ok && u < u1; ++u, ++it) {
-        const int s = it % S;
-        const uint32_t ph = (uint32_t)(it / S) & 1u;
-        const int tile = (int)(u / p.nk), kt = (int)(u % p.nk);
-        const int nt = tile / p.c_tiles, ct = tile % p.c_tiles;
-        unsigned char* st = smem + (size_t)s * C::STAGE;
+      int st_i = 0;
+      uint32_t st_ph = 0;
+      for (int it = 0; ok && it < n_units; ++it) {
+        const uint32_t st = smem0 + (uint32_t)st_i * C::STAGE;
         if (it >= pre) {
-          ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag);
+          ok = mbar_wait(empty_bar(st_i), st_ph ^ 1u, abort_flag);
           if (!ok) break;
-          mbar_expect_tx(full_bar(s), stage_bytes);
-          tma_load_2d(smem_u32(st), &map_w, kt * KT_BYTES, nt * TILE_N, full_bar(s));
-          bulk_load(smem_u32(st + C::A_BYTES + C::B_ALLOC), p.sfw + ((size_t)nt * p.kt4 + (size_t)kt * 4) * SF_ATOM,
-                    C::SFA_BYTES, full_bar(s));
+          load_w(st_i, nt, kt);
         }
-        tma_load_2d(smem_u32(st + C::A_BYTES), &map_x, kt * KT_BYTES, ct * BN, full_bar(s));
+        tma_load_2d(st + C::A_BYTES, &map_x, kt * KT_BYTES, ct * BN, full_bar(st_i));
 #pragma unroll
         for (int j = 0; j < C::SFB_ATOMS; ++j) {
-          const size_t atom_row = (size_t)(ct * BN) / 128 + j;
-          bulk_load(smem_u32(st + C::A_BYTES + C::B_ALLOC + C::SFA_BYTES + j * 4 * SF_ATOM),
-                    p.sfx + (atom_row * p.kt4 + (size_t)kt * 4) * SF_ATOM, 4 * SF_ATOM, full_bar(s));
+          const int atom_row = (ct * BN) / 128 + j;
+          bulk_load(st + C::A_BYTES + C::B_ALLOC + C::SFA_BYTES + j * 4 * SF_ATOM,
+                    p.sfx + ((size_t)(atom_row * p.kt4 + kt * 4)) * SF_ATOM, 4 * SF_ATOM, full_bar(st_i));
         }
+        if (++kt == p.nk) {
+          kt = 0;
+          if (++ct == p.c_tiles) ct = 0, ++nt;
+        }
+        if (++st_i == S) st_i = 0, st_ph ^= 1u;
       }
     }
   } else if (warp == 1) {
@@ -294,8 +325,14 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     if (lane == 0) {
       constexpr uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TILE_N >> 4) << 24);
       long long u = u0;
-      int it = 0, seg = 0;
+      int it = 0, seg = 0, st_i = 0;
+      uint32_t st_ph = 0;
       bool ok = true;
+      // descriptor words of stage 0 / k-block 0; everything else is an affine offset
+      const uint64_t d_a = desc_sw128(smem_u32(smem)), d_b = desc_sw128(smem_u32(smem + C::A_BYTES));
+      const uint64_t d_sfa = desc_sf(smem_u32(smem + C::A_BYTES + C::B_ALLOC));
+      const uint32_t a_lo = (uint32_t)d_a, b_lo = (uint32_t)d_b, op_hi = (uint32_t)(d_a >> 32);
+      const uint32_t sfa_lo = (uint32_t)d_sfa, sfb_lo = sfa_lo + (C::SFA_BYTES >> 4), sf_hi = (uint32_t)(d_sfa >> 32);
       while (ok && u < u1) {
         const int k0 = (int)(u % p.nk);
         const int len = (int)min((long long)(p.nk - k0), u1 - u);
@@ -305,28 +342,24 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
           tc_fence_after();
         }
         for (int i = 0; ok && i < len; ++i, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (uint32_t)(it / S) & 1u;
-          ok = mbar_wait(full_bar(s), ph, abort_flag);
+          ok = mbar_wait(full_bar(st_i), st_ph, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          unsigned char* st = smem + (size_t)s * C::STAGE;
+          const uint32_t soff = (uint32_t)st_i * (uint32_t)(C::STAGE >> 4);
           const uint32_t sf_cols = tmem_base + C::SF_COL0 + (uint32_t)(it & 1) * 64;  // double-buffered by parity
-          const uint32_t sfa_s = smem_u32(st + C::A_BYTES + C::B_ALLOC);
-          const uint32_t sfb_s = sfa_s + C::SFA_BYTES;
 #pragma unroll
-          for (int kb = 0; kb < 4; ++kb) {
-            tc_cp_sf(sf_cols + kb * 4, desc_sf(sfa_s + kb * SF_ATOM));
+          for (int kb = 0; kb < 4 && !(p.dbg & 1); ++kb) {
+            tc_cp_sf_lh(sf_cols + kb * 4, sfa_lo + soff + kb * (SF_ATOM >> 4), sf_hi);
 #pragma unroll
             for (int j = 0; j < C::SFB_ATOMS; ++j)
-              tc_cp_sf(sf_cols + 16 + kb * 8 + j * 4, desc_sf(sfb_s + j * 4 * SF_ATOM + kb * SF_ATOM));
+              tc_cp_sf_lh(sf_cols + 16 + kb * 8 + j * 4, sfb_lo + soff + (j * 4 + kb) * (SF_ATOM >> 4), sf_hi);
           }
-          const uint64_t ad = desc_sw128(smem_u32(st)), bd = desc_sw128(smem_u32(st + C::A_BYTES));
 #pragma unroll
-          for (int kb = 0; kb < 4; ++kb)
-            tc_mma_nvfp4(tmem_base, ad + (uint64_t)(kb * 2), bd + (uint64_t)(kb * 2), idesc, sf_cols + kb * 4,
-                         sf_cols + 16 + kb * 8, (i | kb) ? 1u : 0u);
-          tc_commit(empty_bar(s));
+          for (int kb = 0; kb < 4 && !(p.dbg & 2); ++kb)
+            tc_mma_nvfp4_lh(tmem_base, a_lo + soff + kb * 2, b_lo + soff + kb * 2, op_hi, idesc, sf_cols + kb * 4,
+                            sf_cols + 16 + kb * 8, (i | kb) ? 1u : 0u);
+          tc_commit(empty_bar(st_i));
+          if (++st_i == S) st_i = 0, st_ph ^= 1u;
         }
         if (ok) tc_commit(accum_full);
         u += len;
@@ -638,12 +671,17 @@ TRL_API long trl_gemm_nvfp4_scratch_bytes(int tokens, int J, int N, int K, int m
 TRL_API int trl_gemm_nvfp4(const void* wq, const void* sfw, const void* tscale, const void* xq, const void* sfx,
                            const void* rs, const void* residual, int ldr, void* out, int ldo, void* partial,
                            void* counters, long partial_bytes, int tokens, int J, int N, int K, int epi, int max_ctas,
-                           int split, void* stream) {
+                           int split, int w_tiled, void* stream) {
   if (K % 32 != 0 || J < 1 || (32 % J) != 0 || J > 16) return (int)cudaErrorInvalidValue;
   const int cols = tokens * J;
   const int BN = pick_bn(cols);
   CUtensorMap mw, mx;
-  if (make_map(&mw, wq, (uint64_t)N, (uint64_t)K / 2, TILE_N)) return (int)cudaErrorInvalidValue;
+  {
+    const uint64_t nt = (N + TILE_N - 1) / TILE_N, nkk = (K + KT_ELEMS - 1) / KT_ELEMS;
+    const int rc = w_tiled ? make_map(&mw, wq, nt * nkk * TILE_N, KT_BYTES, TILE_N)
+                           : make_map(&mw, wq, (uint64_t)N, (uint64_t)K / 2, TILE_N);
+    if (rc) return (int)cudaErrorInvalidValue;
+  }
   if (make_map(&mx, xq, (uint64_t)cols, (uint64_t)K / 2, (uint32_t)BN)) return (int)cudaErrorInvalidValue;
   GemmParams p;
   p.sfw = (const uint8_t*)sfw, p.sfx = (const uint8_t*)sfx, p.tscale = (const float*)tscale, p.rs = (const float*)rs;
@@ -660,6 +698,11 @@ TRL_API int trl_gemm_nvfp4(const void* wq, const void* sfw, const void* tscale, 
   if (max_ctas > 0) sms = min(sms, max_ctas);
   const long long U = (long long)p.n_tiles * p.c_tiles * p.nk;
   p.split = split;
+  {
+    const char* e = getenv("TRL_GEMM_DBG");
+    p.dbg = e ? atoi(e) : 0;
+  }
+  p.w_tiled = w_tiled;
   const int grid = split ? (int)min((long long)sms, U) : min(sms, p.n_tiles * p.c_tiles);
   p.max_seg = split ? max_segments(U, grid, p.nk) : 1;
   if (split && (size_t)p.n_tiles * p.c_tiles * p.max_seg * (BN / J) * TILE_N * sizeof(float) > (size_t)partial_bytes)

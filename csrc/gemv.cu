@@ -119,55 +119,65 @@ gemv_nvfp4_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict
       wrow[r] = wq + (size_t)rr * row_bytes;
       srow[r] = wscale + (size_t)rr * srow_bytes;
     }
-    // software pipeline: the loads of chunk c+32 are in flight while chunk c is consumed
-    uint4 wv[R], wn[R];
-    uint16_t sv[R], sn[R];
-    if (lane < nchunks) {
+    // D-deep register ring: while chunk c is consumed, the loads of the next D-1 chunks of
+    // every row are in flight (the loop is bound by memory latency / D, not by latency)
+    constexpr int D = (R * M <= 4) ? 4 : 2;
+    uint4 wv[D][R];
+    uint16_t sv[D][R];
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        wv[r] = ldg_stream_16(wrow[r] + ((size_t)lane << 4));
-        sv[r] = ldg_stream_2(srow[r] + ((size_t)lane << 1));
+    for (int d = 0; d < D; ++d) {
+      const int c = lane + 32 * d;
+      if (c < nchunks) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          wv[d][r] = ldg_stream_16(wrow[r] + ((size_t)c << 4));
+          sv[d][r] = ldg_stream_2(srow[r] + ((size_t)c << 1));
+        }
       }
     }
-    for (int c = lane; c < nchunks; c += 32) {
-      const int cn = c + 32;
-      if (cn < nchunks) {
+    for (int base = lane; base < nchunks; base += 32 * D) {
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-          wn[r] = ldg_stream_16(wrow[r] + ((size_t)cn << 4));
-          sn[r] = ldg_stream_2(srow[r] + ((size_t)cn << 1));
-        }
-      }
+      for (int d = 0; d < D; ++d) {
+        const int c = base + 32 * d;
+        if (c < nchunks) {
 #pragma unroll
-      for (int m = 0; m < M; ++m) {
-        uint32_t xh[16];
-        const __half* xm = xs + (size_t)m * K;
+          for (int m = 0; m < M; ++m) {
+            uint32_t xh[16];
+            const __half* xm = xs + (size_t)m * K;
 #pragma unroll
-        for (int p = 0; p < 4; ++p) {
-          uint4 t = *reinterpret_cast<const uint4*>(xm + ((size_t)(p * nchunks + c) << 3));
-          xh[p * 4 + 0] = t.x, xh[p * 4 + 1] = t.y, xh[p * 4 + 2] = t.z, xh[p * 4 + 3] = t.w;
-        }
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-          const float2 sc = h2_to_f2(cvt_e4m3x2_to_h2(sv[r]));
-          const uint32_t w4[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
-#pragma unroll
-          for (int blk = 0; blk < 2; ++blk) {
-            uint32_t a = 0u;  // f16x2 zero
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-              uint32_t h[4];
-              cvt_e2m1x8_to_h2x4(w4[blk * 2 + q], h);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) a = hfma2_u(h[i], xh[(blk * 2 + q) * 4 + i], a);
+            for (int p = 0; p < 4; ++p) {
+              uint4 t = *reinterpret_cast<const uint4*>(xm + ((size_t)(p * nchunks + c) << 3));
+              xh[p * 4 + 0] = t.x, xh[p * 4 + 1] = t.y, xh[p * 4 + 2] = t.z, xh[p * 4 + 3] = t.w;
             }
-            const float2 af = h2_to_f2(a);
-            acc[r][m] = fmaf(blk == 0 ? sc.x : sc.y, af.x + af.y, acc[r][m]);
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+              const float2 sc = h2_to_f2(cvt_e4m3x2_to_h2(sv[d][r]));
+              const uint32_t w4[4] = {wv[d][r].x, wv[d][r].y, wv[d][r].z, wv[d][r].w};
+#pragma unroll
+              for (int blk = 0; blk < 2; ++blk) {
+                uint32_t a = 0u;  // f16x2 zero
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                  uint32_t h[4];
+                  cvt_e2m1x8_to_h2x4(w4[blk * 2 + q], h);
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) a = hfma2_u(h[i], xh[(blk * 2 + q) * 4 + i], a);
+                }
+                const float2 af = h2_to_f2(a);
+                acc[r][m] = fmaf(blk == 0 ? sc.x : sc.y, af.x + af.y, acc[r][m]);
+              }
+            }
+          }
+          const int cn = c + 32 * D;
+          if (cn < nchunks) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+              wv[d][r] = ldg_stream_16(wrow[r] + ((size_t)cn << 4));
+              sv[d][r] = ldg_stream_2(srow[r] + ((size_t)cn << 1));
+            }
           }
         }
       }
-#pragma unroll
-      for (int r = 0; r < R; ++r) wv[r] = wn[r], sv[r] = sn[r];
     }
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -328,7 +338,7 @@ cudaError_t dispatch_r(const bf16* x, int ldx, const uint8_t* wq, const uint8_t*
                        int N, int K, cudaStream_t st) {
   // enough row blocks to give every warp of a full grid at least two -> R = 4
   const int full_warps = num_sms() * (GEMV_THREADS / 32);
-  if (N >= full_warps * 4 * 2)
+  if (M > 2 && N >= full_warps * 4 * 2)
     return launch_nvfp4<M, 4, EPI>(x, ldx, wq, ws, ts, norm_w, eps, res, ldr, y, ldy, N, K, st);
   return launch_nvfp4<M, 2, EPI>(x, ldx, wq, ws, ts, norm_w, eps, res, ldr, y, ldy, N, K, st);
 }

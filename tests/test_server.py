@@ -1,0 +1,231 @@
+"""API surface over the tiny engine (CPU): raw HTTP through the ASGI app, then the real
+``openai`` and ``anthropic`` SDK clients pointed at it."""
+import asyncio
+import json
+
+import httpx
+import pytest
+
+from helpers import make_engine
+from tilerl_b200.config import tiny
+from tilerl_b200.server.app import create_app
+from tilerl_b200.server import prompt as P
+from tilerl_b200.tokenizer import ByteTokenizer
+
+
+@pytest.fixture()
+def served():
+    eng = make_engine(tiny(max_ctx=2048), blocks=300, slots=6)
+    tok = ByteTokenizer()
+    eng.eos_id = tok.eos_id
+    eng.detok = tok.decode
+    eng.think_ids = tok.think_ids
+    eng.run(batching_window_s=0.0)
+    app = create_app(eng, tok, "tiny-test")
+    yield eng, app
+    eng.stop()
+
+
+def _client(app):
+    return httpx.AsyncClient(transport=httpx.ASGITransport(app=app), base_url="http://test")
+
+
+def run(coro):
+    return asyncio.run(coro)
+
+
+def test_prompt_rendering_and_tool_parsing():
+    text = P.render_chat([{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi"}],
+                         enable_thinking=False)
+    assert text.startswith("<|im_start|>system\nbe brief<|im_end|>") and text.endswith("<think>\n\n</think>\n\n")
+    assert P.render_chat([{"role": "user", "content": "x"}]).endswith("<|im_start|>assistant\n<think>\n")
+    tools = [{"type": "function", "function": {"name": "add", "parameters": {
+        "type": "object", "properties": {"a": {"type": "integer"}, "b": {"type": "number"}, "s": {"type": "string"}}}}}]
+    assert "<tools>" in P.render_chat([{"role": "user", "content": "x"}], tools=tools)
+    out = "ok <tool_call>\n<function=add>\n<parameter=a>\n2\n</parameter>\n<parameter=b>\n1.5\n</parameter>\n" \
+          "<parameter=s>\nhey\n</parameter>\n</function>\n</tool_call>"
+    rest, calls = P.parse_tool_calls(out, tools)
+    assert rest == "ok" and calls == [{"name": "add", "arguments": {"a": 2, "b": 1.5, "s": "hey"}}]
+    assert P.split_think("abc</think>\n\nanswer", True) == ("abc", "answer")
+    assert P.split_think("still thinking", True) == ("still thinking", "")
+    assert P.holdback("hello </thi", ["</think>"]) == 5
+    assert P.sampling({}, True)["top_k"] == 20 and P.sampling({"temperature": 0.1}, False)["temperature"] == 0.1
+    assert P.think_cap("low") == 512
+    with pytest.raises(P.BadRequest):
+        P.refuse_unknown({"bogus": 1}, {"model"})
+
+
+def test_chat_completion_json_health_models(served):
+    eng, app = served
+
+    async def go():
+        async with _client(app) as c:
+            h = await c.get("/health")
+            assert h.status_code == 200 and h.json()["status"] == "ok" and "blocks_free" in h.json()["stats"]
+            m = await c.get("/v1/models")
+            assert m.json()["data"][0]["id"] == "tiny-test"
+            r = await c.post("/v1/chat/completions", json={
+                "model": "tiny-test", "messages": [{"role": "user", "content": "hello"}], "max_tokens": 12,
+                "temperature": 0.0, "top_p": 1.0, "seed": 1, "logprobs": True, "enable_thinking": False})
+            assert r.status_code == 200, r.text
+            j = r.json()
+            ch = j["choices"][0]
+            assert j["object"] == "chat.completion" and ch["finish_reason"] in ("stop", "length")
+            assert j["usage"]["completion_tokens"] <= 12 and j["usage"]["prompt_tokens"] > 5
+            assert len(ch["logprobs"]["content"]) == j["usage"]["completion_tokens"]
+            bad = await c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "bogus": 1})
+            assert bad.status_code == 400 and "bogus" in bad.json()["error"]["message"]
+            bad2 = await c.post("/v1/chat/completions", json={"messages": []})
+            assert bad2.status_code == 400
+            about = await c.get("/about")
+            assert about.json()["layers"] == 2
+            assert (await c.get("/chat")).status_code == 200
+    run(go())
+    assert eng.kv.used_blocks == 0
+
+
+def test_chat_completion_sse_stream(served):
+    eng, app = served
+
+    async def go():
+        async with _client(app) as c:
+            async with c.stream("POST", "/v1/chat/completions", json={
+                    "messages": [{"role": "user", "content": "hi"}], "max_tokens": 10, "stream": True,
+                    "stream_options": {"include_usage": True}, "temperature": 0.0}) as r:
+                assert r.status_code == 200
+                lines = [ln async for ln in r.aiter_lines() if ln.startswith("data: ")]
+        assert lines[-1] == "data: [DONE]"
+        chunks = [json.loads(ln[6:]) for ln in lines[:-1]]
+        assert chunks[0]["choices"][0]["delta"]["role"] == "assistant"
+        finishes = [c["choices"][0]["finish_reason"] for c in chunks if c["choices"]]
+        assert finishes[-1] in ("stop", "length")
+        assert chunks[-1]["usage"]["completion_tokens"] <= 10 and chunks[-1]["choices"] == []
+    run(go())
+
+
+def test_overload_returns_503(served):
+    eng, app = served
+    eng.limits.max_inflight = 0
+
+    async def go():
+        async with _client(app) as c:
+            r = await c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}]})
+            assert r.status_code == 503 and r.json()["error"]["type"] == "overloaded_error"
+            r2 = await c.post("/v1/messages", json={"model": "m", "max_tokens": 4, "messages": [{"role": "user", "content": "x"}]})
+            assert r2.status_code == 529 and r2.json()["error"]["type"] == "overloaded_error"
+    run(go())
+
+
+def test_health_reports_stuck_engine(served):
+    eng, app = served
+    eng.stop()
+    eng.submit([1, 2, 3])
+    eng._last_progress -= 1000
+
+    async def go():
+        async with _client(app) as c:
+            r = await c.get("/health")
+            assert r.status_code == 503 and r.json()["status"] == "stuck"
+    run(go())
+
+
+def test_anthropic_messages_json_and_sse(served):
+    eng, app = served
+
+    async def go():
+        async with _client(app) as c:
+            r = await c.post("/v1/messages", json={
+                "model": "tiny-test", "max_tokens": 8, "system": "s",
+                "messages": [{"role": "user", "content": [{"type": "text", "text": "hi"}]}], "temperature": 0.0})
+            assert r.status_code == 200, r.text
+            j = r.json()
+            assert j["type"] == "message" and j["content"][-1]["type"] == "text"
+            assert j["stop_reason"] in ("end_turn", "max_tokens") and j["usage"]["output_tokens"] <= 8
+            async with c.stream("POST", "/v1/messages", json={
+                    "model": "m", "max_tokens": 8, "stream": True, "thinking": {"type": "enabled", "budget_tokens": 3},
+                    "messages": [{"role": "user", "content": "hi"}]}) as s:
+                events = [ln[7:] async for ln in s.aiter_lines() if ln.startswith("event: ")]
+            assert events[0] == "message_start" and events[-1] == "message_stop" and "message_delta" in events
+            assert events.count("content_block_start") == events.count("content_block_stop")
+            r3 = await c.post("/v1/messages", json={"model": "m", "messages": [{"role": "user", "content": "x"}]})
+            assert r3.status_code == 400 and "max_tokens" in r3.json()["error"]["message"]
+    run(go())
+
+
+def test_responses_api(served):
+    eng, app = served
+
+    async def go():
+        async with _client(app) as c:
+            r = await c.post("/v1/responses", json={"model": "tiny-test", "input": "hello", "max_output_tokens": 8,
+                                                    "instructions": "be brief", "reasoning": {"effort": "none"}})
+            assert r.status_code == 200, r.text
+            j = r.json()
+            assert j["object"] == "response" and j["output"][-1]["type"] == "message"
+            assert j["usage"]["output_tokens"] <= 8
+            async with c.stream("POST", "/v1/responses", json={"input": [{"type": "message", "role": "user",
+                                "content": [{"type": "input_text", "text": "hi"}]}], "max_output_tokens": 6,
+                                "stream": True}) as s:
+                datas = [json.loads(ln[6:]) async for ln in s.aiter_lines() if ln.startswith("data: ")]
+            assert datas[0]["type"] == "response.created" and datas[-1]["type"] == "response.completed"
+            assert [d["sequence_number"] for d in datas] == list(range(len(datas)))
+    run(go())
+
+
+def test_real_sdk_clients(served):
+    eng, app = served
+    import anthropic
+    import openai
+
+    async def go():
+        http = _client(app)
+        oa = openai.AsyncOpenAI(api_key="x", base_url="http://test/v1", http_client=http)
+        r = await oa.chat.completions.create(model="tiny-test", messages=[{"role": "user", "content": "hi"}],
+                                             max_tokens=6, temperature=0.0)
+        assert r.choices[0].finish_reason in ("stop", "length") and r.usage.completion_tokens <= 6
+        stream = await oa.chat.completions.create(model="tiny-test", messages=[{"role": "user", "content": "hi"}],
+                                                  max_tokens=6, stream=True)
+        n = 0
+        async for ch in stream:
+            n += 1
+        assert n >= 2
+        models = await oa.models.list()
+        assert models.data[0].id == "tiny-test"
+        an = anthropic.AsyncAnthropic(api_key="x", base_url="http://test", http_client=_client(app))
+        m = await an.messages.create(model="tiny-test", max_tokens=6, messages=[{"role": "user", "content": "hi"}])
+        assert m.role == "assistant" and m.usage.output_tokens <= 6
+        async with an.messages.stream(model="tiny-test", max_tokens=6,
+                                      messages=[{"role": "user", "content": "hi"}]) as st:
+            final = await st.get_final_message()
+        assert final.stop_reason in ("end_turn", "max_tokens")
+    run(go())
+
+
+def test_websocket_chat(served):
+    eng, app = served
+    from starlette.testclient import TestClient
+    with TestClient(app) as tc:
+        with tc.websocket_connect("/ws/chat") as ws:
+            ws.send_text(json.dumps({"messages": [{"role": "user", "content": "hi"}], "max_tokens": 5}))
+            frames = []
+            while True:
+                f = json.loads(ws.receive_text())
+                frames.append(f)
+                if f["type"] in ("done", "error"):
+                    break
+        assert frames[-1]["type"] == "done" and frames[-1]["usage"]["completion_tokens"] <= 5
+
+
+def test_stream_pacing():
+    from tilerl_b200.server.pacing import Pacer
+    t = [0.0]
+    p = Pacer(enabled=True, max_delay_s=0.5, clock=lambda: t[0])
+    p.push(["a"])
+    assert p.pop_ready() == ["a"]
+    t[0] = 0.1
+    p.push(["b", "c", "d", "e"])          # a burst of 4 in 0.1 s -> 40/s
+    first = p.pop_ready()
+    assert 1 <= len(first) < 4            # not all at once
+    t[0] = 1.0
+    assert "".join(first + p.pop_ready()) == "bcde"
+    assert Pacer(enabled=False).pop_ready() == []

@@ -64,9 +64,9 @@ class CudaOps:
         self.comm = comm          # parallel.symm.SymmComm or None
         self.attn_splits = attn_splits
         self.use_tc_gemm = use_tc_gemm and os.environ.get("TRL_GEMM", "tc") == "tc"
-        # small-M projections: tcgen05 GEMM with `terms_small` residual terms (bf16-accurate
-        # activations at HBM speed) or the SIMT GEMV (TRL_DECODE=simt)
-        self.decode_tc = (os.environ.get("TRL_DECODE", "tc") == "tc") if decode_tc is None else decode_tc
+        # small-M projections: the SIMT weight-streaming GEMV (default; measured faster at
+        # B=1) or the tcgen05 GEMM with `terms_small` residual terms (TRL_DECODE=tc)
+        self.decode_tc = (os.environ.get("TRL_DECODE", "simt") == "tc") if decode_tc is None else decode_tc
         self.terms_small = int(os.environ.get("TRL_TERMS_SMALL", terms_small))
         self.terms_large = int(os.environ.get("TRL_TERMS_LARGE", terms_large))
         self.act_dtype = torch.bfloat16

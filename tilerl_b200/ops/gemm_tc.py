@@ -19,7 +19,7 @@ from . import native as N
 
 N.register("trl_quant_act_nvfp4", [N.P, N.I, N.P, N.F, N.P, N.P, N.P, N.I, N.I, N.I, N.I, N.P])
 N.register("trl_gemm_nvfp4", [N.P, N.P, N.P, N.P, N.P, N.P, N.P, N.I, N.P, N.I, N.P, N.P, N.L,
-                              N.I, N.I, N.I, N.I, N.I, N.I, N.I, N.P])
+                              N.I, N.I, N.I, N.I, N.I, N.I, N.I, N.I, N.P])
 N.register("trl_gemm_nvfp4_scratch_bytes", [N.I, N.I, N.I, N.I, N.I])
 
 KT = 256  # K elements per k-tile
@@ -36,6 +36,30 @@ def tile_scales(scale: torch.Tensor, K: int) -> torch.Tensor:
     s[:r, :kb] = scale.view(torch.uint8)
     s = s.view(rp // 128, 4, 32, kp // 4, 4)        # [atom, r/32, r%32, k64, k16%4]
     return s.permute(0, 3, 2, 1, 4).contiguous()      # [atom, k64, r%32, r/32, k16%4]
+
+
+def tile_weight(wq: torch.Tensor, K: int) -> torch.Tensor:
+    """Packed nibbles ``[N, K/2]`` -> tile-contiguous ``[ceil(N/128), nk, 128, 128]`` bytes:
+    every (128 rows x 256 k) operand tile is one contiguous 16 KB run, so a TMA box is a
+    single DRAM burst instead of 128 strided 128-byte reads.  Tails are zero-padded."""
+    n, kb = wq.shape
+    nk = (K + KT - 1) // KT
+    np_, kp = (n + 127) // 128 * 128, nk * 128
+    if (np_, kp) != (n, kb):
+        t = torch.zeros(np_, kp, dtype=torch.uint8, device=wq.device)
+        t[:n, :kb] = wq
+    else:
+        t = wq
+    return t.view(np_ // 128, 128, nk, 128).permute(0, 2, 1, 3).contiguous()
+
+
+def wq_tiled(w: NVFP4Tensor) -> torch.Tensor:
+    t = getattr(w, "wq_tiled", None)
+    if t is None or getattr(w, "wq_version", None) is not w.wq._version:
+        t = tile_weight(w.wq, w.shape[1])
+        w.wq_tiled = t
+        w.wq_version = w.wq._version
+    return t
 
 
 def sf_tiled(w: NVFP4Tensor) -> torch.Tensor:
@@ -102,11 +126,12 @@ def gemm_nvfp4(ops, x: torch.Tensor, w: NVFP4Tensor, y: torch.Tensor, *, terms: 
     ops.lib.trl_gemm_nvfp4_scratch_bytes.restype = __import__("ctypes").c_long
     nbytes = ops.lib.trl_gemm_nvfp4_scratch_bytes(t, terms, n, k, max_ctas)
     partial, counters = _scratch(ops, nbytes, n_tiles * c_tiles)
+    tiled = getattr(ops, "tile_weights", True)
     N.check(ops.lib.trl_gemm_nvfp4(
-        w.wq.data_ptr(), sf_tiled(w).data_ptr(), w.tscale.data_ptr(), xq.data_ptr(), sfx.data_ptr(),
+        (wq_tiled(w) if tiled else w.wq).data_ptr(), sf_tiled(w).data_ptr(), w.tscale.data_ptr(), xq.data_ptr(), sfx.data_ptr(),
         rs.data_ptr(), N.ptr(residual), residual.stride(0) if residual is not None else 0,
         y.data_ptr(), y.stride(0), partial.data_ptr(), counters.data_ptr(), partial.numel() * 4, t, terms, n, k,
-        epi, max_ctas, int(_want_split(ops, n, k, cols) if split is None else split),
+        epi, max_ctas, int(_want_split(ops, n, k, cols) if split is None else split), int(tiled),
         N.stream()), "gemm_nvfp4")
     N.count()
 

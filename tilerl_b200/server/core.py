@@ -1,0 +1,186 @@
+"""Shared serving plumbing: engine submission, incremental detokenisation, delta streams.
+
+All three API dialects (OpenAI chat, Anthropic messages, Responses) render a prompt,
+submit it to the engine, and consume the same stream of ``(channel, text)`` deltas where
+channel is ``reasoning`` or ``content``; tool-call XML is held back from the content
+channel and parsed at the end.
+
+Parity: reference ``src/tilerl/server.py`` -- ``_submit:526``, ``await_or_cancel:313``,
+``stream_or_cancel:397``, ``_deltas:794``.
+"""
+from __future__ import annotations
+
+import asyncio
+import os
+import time
+import uuid
+from dataclasses import dataclass, field
+from typing import Any, AsyncIterator, Dict, List, Optional, Tuple
+
+from ..engine import Engine, EngineOverloaded, SamplingParams
+from . import prompt as P
+
+
+@dataclass
+class ServeContext:
+    engine: Engine
+    tokenizer: Any
+    model_name: str = "tilerl-b200"
+    completion_timeout_s: float = float(os.environ.get("TRL_COMPLETION_TIMEOUT_S", "600"))
+    health_stuck_s: float = float(os.environ.get("TRL_HEALTH_STUCK_S", "30"))
+    pace: bool = False
+    started: float = field(default_factory=time.time)
+
+
+def overloaded_body(msg: str = "engine overloaded, retry later") -> Dict[str, Any]:
+    return {"error": {"message": msg, "type": "overloaded_error", "code": "overloaded"}}
+
+
+def error_body(msg: str, typ: str = "invalid_request_error", param: Optional[str] = None) -> Dict[str, Any]:
+    return {"error": {"message": msg, "type": typ, "param": param, "code": None}}
+
+
+def new_id(prefix: str) -> str:
+    return f"{prefix}-{uuid.uuid4().hex[:24]}"
+
+
+@dataclass
+class Job:
+    rid: int
+    prompt_tokens: int
+    thinking: bool
+    stop_texts: Tuple[str, ...]
+    tools: Optional[List[Dict[str, Any]]]
+    want_logprobs: bool = False
+
+
+def submit(ctx: ServeContext, messages: List[Dict[str, Any]], *, tools=None, thinking: bool = True,
+           max_tokens: int = 512, body: Optional[Dict[str, Any]] = None, stop=None, seed: Optional[int] = None,
+           logprobs: bool = False, think_cap: Optional[int] = None) -> Job:
+    text = P.render_chat(messages, tools=tools, enable_thinking=thinking)
+    ids = ctx.tokenizer.encode(text)
+    s = P.sampling(body or {}, thinking)
+    stops = () if stop is None else ((stop,) if isinstance(stop, str) else tuple(stop))
+    sp = SamplingParams(max_tokens=int(max_tokens), temperature=s["temperature"], top_p=s["top_p"],
+                        top_k=s["top_k"], seed=int(seed) if seed is not None else int(time.time_ns() & 0x7FFFFFFF),
+                        stop_texts=stops, logprobs=logprobs, max_think_tokens=think_cap)
+    rid = ctx.engine.submit(ids, sp)
+    return Job(rid, len(ids), thinking, stops, tools, logprobs)
+
+
+def _stable_text(ctx: ServeContext, tokens: List[int]) -> str:
+    """Decode, holding back a trailing incomplete UTF-8 sequence."""
+    text = ctx.tokenizer.decode(tokens)
+    while text.endswith("�"):
+        text = text[:-1]
+    return text
+
+
+def _strip_specials(text: str) -> str:
+    for s in ("<|im_end|>", "<|endoftext|>"):
+        text = text.replace(s, "")
+    return text
+
+
+def _truncate_at_stop(text: str, stops: Tuple[str, ...]) -> Tuple[str, bool]:
+    cut = min((text.find(s) for s in stops if s in text), default=-1)
+    return (text[:cut], True) if cut >= 0 else (text, False)
+
+
+async def deltas(ctx: ServeContext, job: Job, *, disconnected=None, poll_s: float = 0.01
+                 ) -> AsyncIterator[Tuple[str, str]]:
+    """Yield ``(channel, new_text)`` as tokens arrive.  Channels: ``reasoning``, ``content``.
+    Text that could still turn into a stop string or a tool-call tag is held back."""
+    sent_r = sent_c = 0
+    t0 = time.monotonic()
+    markers = list(job.stop_texts) + ["</think>", "<tool_call>"]
+    while True:
+        toks, done = ctx.engine.peek(job.rid)
+        text = _strip_specials(_stable_text(ctx, toks))
+        text, stopped = _truncate_at_stop(text, job.stop_texts)
+        closed = "</think>" in text or not job.thinking
+        reasoning, answer = P.split_think(text, job.thinking)
+        if "<tool_call>" in answer:
+            answer = answer[:answer.index("<tool_call>")]
+        fin = done or stopped
+        if not fin:
+            if closed:
+                answer = answer[:len(answer) - P.holdback(answer, markers)]
+            else:
+                reasoning = reasoning[:len(reasoning) - P.holdback(reasoning, markers)]
+        if len(reasoning) > sent_r:
+            yield "reasoning", reasoning[sent_r:]
+            sent_r = len(reasoning)
+        if len(answer) > sent_c:
+            yield "content", answer[sent_c:]
+            sent_c = len(answer)
+        if fin:
+            if stopped and not done:
+                ctx.engine.cancel(job.rid)
+            return
+        if disconnected is not None and await disconnected():
+            ctx.engine.cancel(job.rid)
+            return
+        if time.monotonic() - t0 > ctx.completion_timeout_s:
+            ctx.engine.cancel(job.rid)
+            raise TimeoutError("completion timed out")
+        await asyncio.sleep(poll_s)
+
+
+@dataclass
+class Final:
+    reasoning: str
+    content: str
+    tool_calls: List[Dict[str, Any]]
+    finish_reason: str
+    prompt_tokens: int
+    completion_tokens: int
+    logprobs: List[float]
+    tokens: List[int]
+    cached_tokens: int = 0
+
+
+def finalize(ctx: ServeContext, job: Job, res) -> Final:
+    text = _strip_specials(ctx.tokenizer.decode(res.tokens))
+    text, stopped = _truncate_at_stop(text, job.stop_texts)
+    reasoning, answer = P.split_think(text, job.thinking)
+    answer, calls = P.parse_tool_calls(answer, job.tools)
+    reason = res.finish_reason
+    if reason == "error":
+        raise RuntimeError(res.error or "request failed")
+    if calls:
+        reason = "tool_calls"
+    elif stopped:
+        reason = "stop"
+    return Final(reasoning, answer, calls, reason, res.prompt_tokens, len(res.tokens), list(res.logprobs),
+                 list(res.tokens), res.cached_tokens)
+
+
+async def complete(ctx: ServeContext, job: Job, disconnected=None) -> Optional[Final]:
+    """Wait for the request; ``None`` if the client went away (request cancelled)."""
+    t0 = time.monotonic()
+    while True:
+        res = ctx.engine.take(job.rid)
+        if res is not None:
+            return finalize(ctx, job, res)
+        if disconnected is not None and await disconnected():
+            ctx.engine.cancel(job.rid)
+            ctx.engine.take(job.rid)
+            return None
+        if time.monotonic() - t0 > ctx.completion_timeout_s:
+            ctx.engine.cancel(job.rid)
+            ctx.engine.take(job.rid)
+            raise TimeoutError("completion timed out")
+        await asyncio.sleep(0.01)
+
+
+def health(ctx: ServeContext) -> Tuple[int, Dict[str, Any]]:
+    live = ctx.engine.liveness()
+    stats = ctx.engine.stats()
+    stuck = live["last_progress_age_s"] > ctx.health_stuck_s
+    degraded = live["degraded"] is not None
+    status = 503 if (stuck or degraded) else 200
+    body = {"status": "ok" if status == 200 else ("degraded" if degraded else "stuck"),
+            "model": ctx.model_name, "uptime_s": round(time.time() - ctx.started, 1),
+            "liveness": live, "stats": stats}
+    return status, body

@@ -26,13 +26,15 @@ def main():
     ap.add_argument("--shapes", default="")
     ap.add_argument("--max-ctas", type=int, default=0)
     ap.add_argument("--split", type=int, default=1)
+    ap.add_argument("--tiled", type=int, default=1)
     args = ap.parse_args()
     from tilerl_b200.formats import NVFP4Tensor
     from tilerl_b200.ops.cuda import CudaOps
-    from tilerl_b200.ops.gemm_tc import gemm_nvfp4, quant_act, sf_tiled
+    from tilerl_b200.ops.gemm_tc import gemm_nvfp4, quant_act, sf_tiled, wq_tiled
     from tilerl_b200.ops import native
     dev = torch.device("cuda", 0)
     ops = CudaOps(dev)
+    ops.tile_weights = bool(args.tiled)
     out = {}
     names = [s for s in args.shapes.split(",") if s] or list(SHAPES)
     for name in names:
@@ -45,6 +47,7 @@ def main():
                             (torch.rand(n, k // 16, device=dev) + 0.5).to(torch.float8_e4m3fn),
                             torch.ones(1, device=dev))
             sf_tiled(w)
+            wq_tiled(w)
             ws.append(w)
         x = torch.randn(args.m, k, device=dev).to(torch.bfloat16)
         y = torch.zeros(args.m, n, dtype=torch.bfloat16, device=dev)
@@ -86,9 +89,9 @@ def main():
 
             def gemm_only(w):
                 native.check(ops.lib.trl_gemm_nvfp4(
-                    w.wq.data_ptr(), w.sf_tiled.data_ptr(), w.tscale.data_ptr(), xq.data_ptr(), sfx.data_ptr(),
+                    (w.wq_tiled if args.tiled else w.wq).data_ptr(), w.sf_tiled.data_ptr(), w.tscale.data_ptr(), xq.data_ptr(), sfx.data_ptr(),
                     rs.data_ptr(), None, 0, y.data_ptr(), y.stride(0), partial.data_ptr(), counters.data_ptr(),
-                    partial.numel() * 4, args.m, args.terms, n, k, 0, args.max_ctas, args.split, native.stream()))
+                    partial.numel() * 4, args.m, args.terms, n, k, 0, args.max_ctas, args.split, args.tiled, native.stream()))
             us = timeit(gemm_only)
             res["gemm_tc_us"] = round(us, 2)
             res["gemm_tc_TBs"] = round(wbytes / us / 1e6, 3)
