@@ -29,6 +29,14 @@ __device__ __forceinline__ void trl_set_error(int code, int a, int b, int c) {
   }
 }
 
+// ---- tensor-parallel push target (see comm.cu) --------------------------------------------
+// Peer workspace pointers for the row-parallel GEMV epilogue that writes its fp32 partial
+// rows into every rank's one-shot all-reduce slot.
+struct TrlPushArgs {
+  unsigned char* ws[8];
+  int rank, world, hmax, row0;
+};
+
 // ---- programmatic dependent launch ----------------------------------------------------
 // Every kernel calls pdl_launch_dependents() first (the next kernel in the stream
 // may begin its own prologue) and pdl_wait() before touching anything a

@@ -24,7 +24,7 @@
 __device__ TrlError g_trl_error = {0, 0, 0, 0};
 int g_trl_use_pdl = 1;
 
-enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_STORE_F32 = 3 };
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_STORE_F32 = 3, EPI_PUSH = 4 };
 
 namespace {
 
@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1)
 gemv_nvfp4_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ wq,
                   const uint8_t* __restrict__ wscale, const float* __restrict__ tscale,
                   const float* __restrict__ norm_w, float eps, const bf16* __restrict__ residual,
-                  int ldr, void* __restrict__ yout, int ldy, int N, int K) {
+                  int ldr, void* __restrict__ yout, int ldy, int N, int K, const TrlPushArgs push) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __half* xs = reinterpret_cast<__half*>(smem_raw);
   float* xs_inv = reinterpret_cast<float*>(smem_raw + (size_t)M * K * sizeof(__half));
@@ -209,12 +209,35 @@ gemv_nvfp4_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict
             if (rr == r && mm == m) v = acc[rr][mm];
         const int n = r0 + r;
         if (n < N) {
-          if (EPI == EPI_RESIDUAL) v += __bfloat162float(residual[(size_t)m * ldr + n]);
-          if (EPI == EPI_STORE_F32)
-            reinterpret_cast<float*>(yout)[(size_t)m * ldy + n] = v;
-          else
-            reinterpret_cast<bf16*>(yout)[(size_t)m * ldy + n] = __float2bfloat16(v);
+          if (EPI == EPI_PUSH) {
+            // fp32 partial row straight into every rank's all-reduce slot (NVLink stores)
+            const uint32_t epoch = *reinterpret_cast<const uint32_t*>(push.ws[push.rank]) + 1;
+            const size_t off = 65536 + ((size_t)(((epoch & 1) * 8 + push.rank) * 8 + push.row0 + m) * push.hmax + n) * 4;
+            for (int p = 0; p < push.world; ++p) *reinterpret_cast<float*>(push.ws[p] + off) = v;
+          } else {
+            if (EPI == EPI_RESIDUAL) v += __bfloat162float(residual[(size_t)m * ldr + n]);
+            if (EPI == EPI_STORE_F32)
+              reinterpret_cast<float*>(yout)[(size_t)m * ldy + n] = v;
+            else
+              reinterpret_cast<bf16*>(yout)[(size_t)m * ldy + n] = __float2bfloat16(v);
+          }
         }
+      }
+    }
+  }
+  if (EPI == EPI_PUSH && ldy != 0) {
+    // ldy != 0 marks the last row chunk: when every CTA has pushed, publish the epoch flag
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      uint32_t* ctrl = reinterpret_cast<uint32_t*>(push.ws[push.rank]);
+      const uint32_t epoch = ctrl[0] + 1;
+      const uint32_t prev = atomicAdd(ctrl + 16, 1u);
+      if (prev == gridDim.x - 1) {
+        ctrl[16] = 0;
+        __threadfence_system();
+        for (int p = 0; p < push.world; ++p)
+          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(reinterpret_cast<uint32_t*>(push.ws[p] + 4096) + (epoch & 1) * 8 + push.rank), "r"(epoch) : "memory");
       }
     }
   }
@@ -318,7 +341,7 @@ int num_sms() {
 template <int M, int R, int EPI>
 cudaError_t launch_nvfp4(const bf16* x, int ldx, const uint8_t* wq, const uint8_t* ws, const float* ts,
                          const float* norm_w, float eps, const bf16* res, int ldr, void* y, int ldy,
-                         int N, int K, cudaStream_t st) {
+                         int N, int K, cudaStream_t st, const TrlPushArgs& push) {
   const size_t smem = (size_t)M * K * sizeof(__half) + 8 * sizeof(float) + 32 * sizeof(float);
   auto kern = gemv_nvfp4_kernel<M, R, EPI>;
   static bool configured = false;
@@ -329,29 +352,29 @@ cudaError_t launch_nvfp4(const bf16* x, int ldx, const uint8_t* wq, const uint8_
   const int warps_needed = (N + R - 1) / R;
   int grid = min(num_sms(), (warps_needed + GEMV_THREADS / 32 - 1) / (GEMV_THREADS / 32));
   return trl_launch(kern, dim3(grid), dim3(GEMV_THREADS), smem, st, x, ldx, wq, ws, ts, norm_w, eps,
-                    res, ldr, y, ldy, N, K);
+                    res, ldr, y, ldy, N, K, push);
 }
 
 template <int M, int EPI>
 cudaError_t dispatch_r(const bf16* x, int ldx, const uint8_t* wq, const uint8_t* ws, const float* ts,
                        const float* norm_w, float eps, const bf16* res, int ldr, void* y, int ldy,
-                       int N, int K, cudaStream_t st) {
+                       int N, int K, cudaStream_t st, const TrlPushArgs& push) {
   // enough row blocks to give every warp of a full grid at least two -> R = 4
   const int full_warps = num_sms() * (GEMV_THREADS / 32);
   if (M > 2 && N >= full_warps * 4 * 2)
-    return launch_nvfp4<M, 4, EPI>(x, ldx, wq, ws, ts, norm_w, eps, res, ldr, y, ldy, N, K, st);
-  return launch_nvfp4<M, 2, EPI>(x, ldx, wq, ws, ts, norm_w, eps, res, ldr, y, ldy, N, K, st);
+    return launch_nvfp4<M, 4, EPI>(x, ldx, wq, ws, ts, norm_w, eps, res, ldr, y, ldy, N, K, st, push);
+  return launch_nvfp4<M, 2, EPI>(x, ldx, wq, ws, ts, norm_w, eps, res, ldr, y, ldy, N, K, st, push);
 }
 
 template <int EPI>
 cudaError_t dispatch_m(int M, const bf16* x, int ldx, const uint8_t* wq, const uint8_t* ws,
                        const float* ts, const float* norm_w, float eps, const bf16* res, int ldr,
-                       void* y, int ldy, int N, int K, cudaStream_t st) {
+                       void* y, int ldy, int N, int K, cudaStream_t st, const TrlPushArgs& push = TrlPushArgs()) {
   switch (M) {
-    case 1: return dispatch_r<1, EPI>(x, ldx, wq, ws, ts, norm_w, eps, res, ldr, y, ldy, N, K, st);
-    case 2: return dispatch_r<2, EPI>(x, ldx, wq, ws, ts, norm_w, eps, res, ldr, y, ldy, N, K, st);
-    case 3: return dispatch_r<3, EPI>(x, ldx, wq, ws, ts, norm_w, eps, res, ldr, y, ldy, N, K, st);
-    case 4: return dispatch_r<4, EPI>(x, ldx, wq, ws, ts, norm_w, eps, res, ldr, y, ldy, N, K, st);
+    case 1: return dispatch_r<1, EPI>(x, ldx, wq, ws, ts, norm_w, eps, res, ldr, y, ldy, N, K, st, push);
+    case 2: return dispatch_r<2, EPI>(x, ldx, wq, ws, ts, norm_w, eps, res, ldr, y, ldy, N, K, st, push);
+    case 3: return dispatch_r<3, EPI>(x, ldx, wq, ws, ts, norm_w, eps, res, ldr, y, ldy, N, K, st, push);
+    case 4: return dispatch_r<4, EPI>(x, ldx, wq, ws, ts, norm_w, eps, res, ldr, y, ldy, N, K, st, push);
   }
   return cudaErrorInvalidValue;
 }
@@ -428,6 +451,27 @@ TRL_API int trl_error_read(int* out4, int clear) {
   if (clear && h.code != 0) {
     TrlError z = {0, 0, 0, 0};
     cudaMemcpyToSymbol(g_trl_error, &z, sizeof(z));
+  }
+  return 0;
+}
+
+// Row-parallel GEMV whose epilogue pushes fp32 partial rows into every rank's one-shot
+// all-reduce slot (see comm.cu); trl_allreduce_finish completes the sum on each rank.
+TRL_API int trl_gemv_nvfp4_push(const void* x, int ldx, const void* wq, const void* wscale, const void* tscale,
+                                void* const* ws, int rank, int world, int hmax, int M, int N, int K, void* stream) {
+  if (K % 32 != 0 || N <= 0 || M <= 0 || M > 8 || N > hmax) return (int)cudaErrorInvalidValue;
+  int per = 4;
+  while (per > 1 && (size_t)per * K * 2 > 190 * 1024) --per;
+  for (int m0 = 0; m0 < M; m0 += per) {
+    const int mm = min(per, M - m0);
+    TrlPushArgs push;
+    for (int i = 0; i < 8; ++i) push.ws[i] = i < world ? (unsigned char*)ws[i] : nullptr;
+    push.rank = rank, push.world = world, push.hmax = hmax, push.row0 = m0;
+    const int last = (m0 + mm >= M) ? 1 : 0;
+    cudaError_t e = dispatch_m<EPI_PUSH>(mm, (const bf16*)x + (size_t)m0 * ldx, ldx, (const uint8_t*)wq,
+                                         (const uint8_t*)wscale, (const float*)tscale, nullptr, 0.f, nullptr, 0,
+                                         nullptr, last, N, K, (cudaStream_t)stream, push);
+    if (e != cudaSuccess) return (int)e;
   }
   return 0;
 }

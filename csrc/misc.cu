@@ -257,6 +257,11 @@ TRL_API int trl_argmax(const void* logits, int ld, int M, int V, void* out, void
   return (int)trl_launch(argmax_stage2_kernel, dim3(M), dim3(64), 0, (cudaStream_t)stream, (const float*)pv,
                          (const int*)pi, (int*)out);
 }
+// Stage 1 only (per-row chunk maxima) for the vocab-parallel argmax: pv/pi are [M, 64].
+TRL_API int trl_argmax_stage1(const void* logits, int ld, int M, int V, void* pv, void* pi, void* stream) {
+  return (int)trl_launch(argmax_stage1_kernel, dim3(M, ARGMAX_CHUNKS), dim3(256), 0, (cudaStream_t)stream,
+                         (const float*)logits, ld, V, (float*)pv, (int*)pi);
+}
 TRL_API int trl_adamw(void* p, void* m, void* v, const void* g, void* p_bf16, long n, float lr, float b1,
                       float b2, float eps, float wd, int step, float gscale, void* stream) {
   const float c1 = 1.f - powf(b1, (float)step), c2 = 1.f - powf(b2, (float)step);

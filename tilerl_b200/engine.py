@@ -433,6 +433,8 @@ class Engine:
             if all(self._is_plain_greedy(r) for r, _, _ in plan):
                 amax = [int(v) for v in self.ops.argmax(logits).tolist()]  # one device sync per tick
                 self.io_d2h += 4 * len(amax)
+        if amax is None and hasattr(self.ops, "full_logits"):
+            logits = self.ops.full_logits(logits)   # sampling needs every vocab shard
         kinds = {r.state for r, _, _ in plan}
         key = "mixed_ticks" if len(kinds) > 1 else ("decode_ticks" if DECODE in kinds else "prefill_ticks")
         self.counters[key] += 1

@@ -53,15 +53,19 @@ def build_random_streaming(cfg: ModelConfig, device, seed: int = 0, tp_rank: int
     lin = set(linear_names(cfg))
     params: Dict[str, object] = {}
     for name, shape in param_shapes(cfg, 1).items():
-        w = shard_param(cfg, name, random_param(cfg, name, shape, seed, device), tp_rank, tp)
+        full = random_param(cfg, name, shape, seed, device)
+        w = shard_param(cfg, name, full, tp_rank, tp)
         if name in lin or (name == "lm_head" and cfg.lm_head_quant == "nvfp4"):
             if cfg.quant == "nvfp4" and device.type == "cuda" and ops is not None:
-                n, k = w.shape
+                # quantise the full tensor on the device, then cut the packed planes
+                n, k = full.shape
                 q = NVFP4Tensor(torch.empty(n, k // 2, dtype=torch.uint8, device=device),
                                 torch.empty(n, k // 16, dtype=torch.float8_e4m3fn, device=device),
                                 torch.empty(1, dtype=torch.float32, device=device))
-                ops.quantize_nvfp4_(w.contiguous(), q)
-                params[name] = q
+                ops.quantize_nvfp4_(full.contiguous(), q)
+                params[name] = shard_param(cfg, name, q, tp_rank, tp)
+            elif cfg.quant == "nvfp4":
+                params[name] = shard_param(cfg, name, quantize_weight(full.float(), "nvfp4"), tp_rank, tp)
             else:
                 params[name] = quantize_weight(w.float(), cfg.quant)
             if keep_master:
@@ -70,10 +74,23 @@ def build_random_streaming(cfg: ModelConfig, device, seed: int = 0, tp_rank: int
             params[name] = w.to(torch.bfloat16 if device.type == "cuda" else torch.float32)
         else:
             params[name] = w.float()
-        del w
+        del w, full
     if device.type == "cuda":
         torch.cuda.synchronize()
     return HybridModel(cfg, params, tp_rank, tp)
+
+
+def materialize(model: HybridModel, ops) -> None:
+    """Create the device-side operand layouts up front (tile-contiguous weight nibbles and
+    128x4-tiled scales for the tcgen05 GEMM) so the first request does not pay for them.
+    Reference: ``Backend.materialize`` (``backend.py:975-1021``)."""
+    if getattr(ops, "name", "") != "cuda" or not getattr(ops, "use_tc_gemm", False):
+        return
+    from .ops.gemm_tc import sf_tiled, wq_tiled
+    for v in model.params.values():
+        if isinstance(v, NVFP4Tensor):
+            sf_tiled(v)
+            wq_tiled(v)
 
 
 def build_model(model: str | ModelConfig, device="cpu", *, seed: int = 0, checkpoint: Optional[str] = None,
@@ -82,7 +99,10 @@ def build_model(model: str | ModelConfig, device="cpu", *, seed: int = 0, checkp
     if checkpoint:
         from .checkpoint import load_checkpoint
         return load_checkpoint(cfg, checkpoint, device=device, tp_rank=tp_rank, tp=tp, keep_master=keep_master)
-    return build_random_streaming(cfg, device, seed, tp_rank, tp, ops, keep_master)
+    m = build_random_streaming(cfg, device, seed, tp_rank, tp, ops, keep_master)
+    if ops is not None:
+        materialize(m, ops)
+    return m
 
 
 def fit_blocks(cfg: ModelConfig, free_bytes: int, slots: int, *, planes: int = 1, tp: int = 1,
@@ -114,6 +134,8 @@ def build_engine(model: HybridModel, ops=None, *, device=None, blocks: Optional[
         device = e.device
     device = torch.device(device)
     ops = ops or make_ops(device)
+    if hasattr(ops, "vocab"):
+        ops.vocab = cfg.vocab
     planes = max(1, spec_width)
     d = model.dims
     if blocks is None:

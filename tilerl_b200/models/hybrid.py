@@ -132,12 +132,16 @@ class HybridModel:
             ws = shard_param(cfg, name, w, tp_rank, tp)
             if device is not None:
                 ws = ws.to(device)
-            if name in lin:
-                params[name] = quantize_weight(ws.float(), quant)
-                if keep_master:
+            if name in lin or (name == "lm_head" and cfg.lm_head_quant == "nvfp4"):
+                if quant == "nvfp4" or name == "lm_head":
+                    # quantise the FULL tensor, then cut the packed planes: every TP degree
+                    # serves exactly the same quantised values
+                    q = shard_param(cfg, name, quantize_nvfp4(w.float()), tp_rank, tp)
+                    params[name] = q.to(device) if device is not None else q
+                else:
+                    params[name] = quantize_weight(ws.float(), quant)
+                if keep_master and name in lin:
                     params["master." + name] = ws.clone()
-            elif name == "lm_head" and cfg.lm_head_quant == "nvfp4":
-                params[name] = quantize_nvfp4(ws.float())
             elif ws.dim() == 2 and name in ("embed", "lm_head"):
                 params[name] = ws.to(act_dtype)
             else:

@@ -71,6 +71,9 @@ class CudaOps:
         self.terms_large = int(os.environ.get("TRL_TERMS_LARGE", terms_large))
         self.act_dtype = torch.bfloat16
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.vocab = None   # set by the engine builder: real vocabulary size (TP pads it)
+        if comm is not None:
+            comm.attach(self)
 
     # ---- helpers ------------------------------------------------------------------
     def _f32(self, t: torch.Tensor) -> torch.Tensor:
@@ -253,12 +256,20 @@ class CudaOps:
                 hb = self.ws.get("head_bf16", (m, n), torch.bfloat16)
                 torch.matmul(h, (w if isinstance(w, torch.Tensor) else w.dequant().to(torch.bfloat16)).t(), out=hb)
                 logits.copy_(hb)
+        return logits   # vocab-parallel under TP: [M, V_local]
+
+    def full_logits(self, logits):
+        """Full-vocabulary logits (gathers the vocab shards under TP)."""
         if self.comm is not None and self.comm.world > 1:
-            return self.comm.all_gather_logits(logits)
+            full = self.comm.all_gather_logits(logits)
+            return full[..., :self.vocab] if self.vocab else full
         return logits
 
     def argmax(self, logits):
         m, v = logits.shape
+        if self.comm is not None and self.comm.world > 1:
+            v_valid = (self.vocab or v * self.comm.world) - self.comm.rank * v
+            return self.comm.argmax(self, logits, v_valid)
         out = self.ws.get("argmax", (m,), torch.int32)
         scratch = self.ws.get("argmax_scratch", (m * 128,), torch.float32)
         N.check(self.lib.trl_argmax(logits.data_ptr(), logits.stride(0), m, v, out.data_ptr(), scratch.data_ptr(),

@@ -151,10 +151,6 @@ def check_alignment(cfg: ModelConfig, tp: int) -> None:
             raise ValueError(f"tp={tp}: reduction dim {k} of '{name}' is not a multiple of {need}")
 
 
-def _rows(w: torch.Tensor, a: int, b: int) -> torch.Tensor:
-    return w[a:b]
-
-
 def shard_dim(name: str) -> int | None:
     leaf = name.split(".")[-1]
     if leaf in COLUMN_PARALLEL or leaf in ("conv", "dt_bias", "a_log"):
@@ -168,59 +164,83 @@ def is_sharded(name: str) -> bool:
     return shard_dim(name) is not None
 
 
-def shard_param(cfg: ModelConfig, name: str, w: torch.Tensor, rank: int, tp: int) -> torch.Tensor:
-    """Slice the full parameter ``name`` for TP rank ``rank``."""
-    if tp == 1:
-        return w
+def shard_spec(cfg: ModelConfig, name: str, rank: int, tp: int):
+    """How rank ``rank`` cuts parameter ``name``: ``("full",)``, ``("rows", [(a, b), ...], pad_to)``
+    (row ranges concatenated, optionally zero-padded to ``pad_to`` source rows first) or
+    ``("cols", (a, b))``.  One description serves dense tensors and packed NVFP4 planes."""
     leaf = name.split(".")[-1]
+    if tp == 1 or leaf in REPLICATED:
+        return ("full",)
     d = tp_dims(cfg, tp)
     hd = cfg.head_dim
-    if leaf in REPLICATED:
-        return w
     if leaf == "lm_head":
-        pad = d.vocab_padded - w.shape[0]
-        if pad:
-            w = torch.cat([w, w.new_zeros(pad, w.shape[1])])
-        return _rows(w, rank * d.vocab_local, (rank + 1) * d.vocab_local).contiguous()
+        return ("rows", [(rank * d.vocab_local, (rank + 1) * d.vocab_local)], d.vocab_padded)
     if leaf == "qkv":
         per_q = hd * (2 if cfg.attn_gated else 1)
         q_all = cfg.n_q_heads * per_q
         kv_all = cfg.n_kv_heads * hd
         kv0 = (rank // d.kv_rep) * d.n_kv if tp > cfg.n_kv_heads else rank * d.n_kv
-        q = _rows(w, rank * d.n_q * per_q, (rank + 1) * d.n_q * per_q)
-        k = _rows(w, q_all + kv0 * hd, q_all + (kv0 + d.n_kv) * hd)
-        v = _rows(w, q_all + kv_all + kv0 * hd, q_all + kv_all + (kv0 + d.n_kv) * hd)
-        return torch.cat([q, k, v]).contiguous()
+        return ("rows", [(rank * d.n_q * per_q, (rank + 1) * d.n_q * per_q),
+                         (q_all + kv0 * hd, q_all + (kv0 + d.n_kv) * hd),
+                         (q_all + kv_all + kv0 * hd, q_all + kv_all + (kv0 + d.n_kv) * hd)], None)
     if leaf == "o":
         c = d.n_q * hd
-        return w[:, rank * c:(rank + 1) * c].contiguous()
+        return ("cols", (rank * c, (rank + 1) * c))
     gd = cfg.gdn_head_dim
     if leaf in ("in", "conv"):
         qd, vd = cfg.gdn_qk_dim, cfg.gdn_v_dim
         lk, lv = d.gdn_nk * gd, d.gdn_nv * gd
-        segs = [
-            _rows(w, rank * lk, (rank + 1) * lk),
-            _rows(w, qd + rank * lk, qd + (rank + 1) * lk),
-            _rows(w, 2 * qd + rank * lv, 2 * qd + (rank + 1) * lv),
-        ]
+        segs = [(rank * lk, (rank + 1) * lk), (qd + rank * lk, qd + (rank + 1) * lk),
+                (2 * qd + rank * lv, 2 * qd + (rank + 1) * lv)]
         if leaf == "in":
             base = 2 * qd + vd
-            segs.append(_rows(w, base + rank * lv, base + (rank + 1) * lv))
+            segs.append((base + rank * lv, base + (rank + 1) * lv))
             base += vd
             nv = cfg.gdn_v_heads
-            segs.append(_rows(w, base + rank * d.gdn_nv, base + (rank + 1) * d.gdn_nv))
-            segs.append(_rows(w, base + nv + rank * d.gdn_nv, base + nv + (rank + 1) * d.gdn_nv))
-        return torch.cat(segs).contiguous()
+            segs.append((base + rank * d.gdn_nv, base + (rank + 1) * d.gdn_nv))
+            segs.append((base + nv + rank * d.gdn_nv, base + nv + (rank + 1) * d.gdn_nv))
+        return ("rows", segs, None)
     if leaf == "out":
         c = d.gdn_nv * gd
-        return w[:, rank * c:(rank + 1) * c].contiguous()
+        return ("cols", (rank * c, (rank + 1) * c))
     if leaf in ("dt_bias", "a_log"):
-        return w[rank * d.gdn_nv:(rank + 1) * d.gdn_nv].contiguous()
+        return ("rows", [(rank * d.gdn_nv, (rank + 1) * d.gdn_nv)], None)
     if leaf == "gate_up":
-        return _rows(w, rank * 2 * d.ffn, (rank + 1) * 2 * d.ffn).contiguous()
+        return ("rows", [(rank * 2 * d.ffn, (rank + 1) * 2 * d.ffn)], None)
     if leaf == "down":
-        return w[:, rank * d.ffn:(rank + 1) * d.ffn].contiguous()
+        return ("cols", (rank * d.ffn, (rank + 1) * d.ffn))
     raise KeyError(f"no shard rule for parameter {name!r}")
+
+
+def apply_spec(w: torch.Tensor, spec, col_div: int = 1) -> torch.Tensor:
+    """Cut ``w`` by ``spec``; ``col_div`` maps logical column indices to stored ones (2 for
+    packed nibbles, 16 for per-16 scales)."""
+    kind = spec[0]
+    if kind == "full":
+        return w
+    if kind == "cols":
+        a, b = spec[1]
+        return w[:, a // col_div:b // col_div].contiguous()
+    segs, pad_to = spec[1], spec[2]
+    if pad_to is not None and pad_to > w.shape[0]:
+        w = torch.cat([w, w.new_zeros((pad_to - w.shape[0],) + tuple(w.shape[1:]))])
+    return torch.cat([w[a:b] for a, b in segs]).contiguous()
+
+
+def shard_param(cfg: ModelConfig, name: str, w, rank: int, tp: int):
+    """Slice the full parameter ``name`` for TP rank ``rank``.  A quantised weight is cut in
+    its packed form (nibbles, block scales; the tensor scale is shared), so every shard holds
+    exactly the values of the full quantised tensor."""
+    spec = shard_spec(cfg, name, rank, tp)
+    if spec[0] == "full":
+        return w
+    from ..formats import FP8BlockTensor, NVFP4Tensor
+    if isinstance(w, NVFP4Tensor):
+        sc = apply_spec(w.scale.view(torch.uint8), spec, 16).view(torch.float8_e4m3fn)
+        return NVFP4Tensor(apply_spec(w.wq, spec, 2), sc, w.tscale.clone())
+    if isinstance(w, FP8BlockTensor):
+        raise NotImplementedError("block-scaled FP8 weights are sharded before quantisation")
+    return apply_spec(w, spec)
 
 
 def shard_params(cfg: ModelConfig, params: Dict[str, torch.Tensor], rank: int, tp: int) -> Dict[str, torch.Tensor]:

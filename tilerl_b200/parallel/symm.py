@@ -1,0 +1,145 @@
+"""Symmetric peer memory and the tensor-parallel kernels that use it.
+
+``SymmComm.create(group, device)`` allocates one workspace per rank with ``cudaMalloc``
+(inside the extension, so it can be exported with CUDA IPC), exchanges the IPC handles
+over the process group (``all_gather_object``: bootstrap only) and opens every peer's
+workspace.  After that no library collective is on the decode path:
+
+* ``linear_allreduce_residual`` -- row-parallel projection + all-reduce + residual add.
+  Up to 8 tokens: the GEMV pushes fp32 partial rows into every peer's slot from its
+  epilogue and ``allreduce_finish`` sums them (one-shot).  More tokens: the GEMM writes
+  its partial into the symmetric ``big`` region and one two-shot kernel reduce-scatters
+  by peer loads and all-gathers by peer stores straight into every rank's residual stream.
+* ``argmax`` -- vocab-parallel argmax with a (max, index) exchange.
+* ``all_gather_logits`` -- full-vocab logits for sampling (NCCL; off the greedy path).
+
+The residual stream (workspace buffer ``x``) and the row-parallel GEMM output
+(``rowout``) are views of the symmetric workspace so peers can address them.
+
+Parity: the reference has only ``torch.distributed`` collectives
+(``packages/tilerl-kernels/src/tilerl_kernels/backend.py:165-364``); this replaces
+``Backend.all_reduce`` ``:260`` and the logits ``all_gather`` ``:272``.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native as N
+
+for _name, _sig in {
+    "trl_symm_bytes": [N.I, N.I], "trl_symm_big_offset": [N.I], "trl_symm_out_offset": [N.I, N.I],
+    "trl_symm_alloc": [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p)], "trl_symm_free": [N.P],
+    "trl_ipc_get": [N.P, N.P], "trl_ipc_open": [N.P, ctypes.POINTER(ctypes.c_void_p)], "trl_ipc_close": [N.P],
+    "trl_allreduce_finish": [N.P, N.I, N.I, N.I, N.P, N.I, N.P, N.I, N.I, N.I, N.P],
+    "trl_allreduce_twoshot": [N.P, N.I, N.I, N.I, N.I, N.P, N.I, N.I, N.I, N.I, N.P],
+    "trl_argmax_tp": [N.P, N.I, N.I, N.I, N.P, N.P, N.I, N.I, N.P, N.I, N.P],
+    "trl_gemv_nvfp4_push": [N.P, N.I, N.P, N.P, N.P, N.P, N.I, N.I, N.I, N.I, N.I, N.I, N.P],
+}.items():
+    N.register(_name, _sig)
+
+
+class _DevMem:
+    """Expose a raw device allocation to torch through __cuda_array_interface__."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+class SymmComm:
+    def __init__(self, rank: int, world: int, group, device, hmax: int, tmax: int):
+        self.rank, self.world, self.group, self.device = rank, world, group, torch.device(device)
+        self.hmax, self.tmax = hmax, tmax
+        self.lib = N.lib()
+        for fn in ("trl_symm_bytes", "trl_symm_big_offset", "trl_symm_out_offset"):
+            getattr(self.lib, fn).restype = ctypes.c_size_t
+        self.nbytes = self.lib.trl_symm_bytes(hmax, tmax)
+        p = ctypes.c_void_p()
+        N.check(self.lib.trl_symm_alloc(self.nbytes, ctypes.byref(p)), "symm_alloc")
+        self.local_ptr = p.value
+        handle = (ctypes.c_ubyte * 64)()
+        N.check(self.lib.trl_ipc_get(self.local_ptr, handle), "ipc_get")
+        handles: List[Optional[bytes]] = [None] * world
+        dist.all_gather_object(handles, bytes(handle), group=group)
+        self.ptrs: List[int] = []
+        for r, h in enumerate(handles):
+            if r == rank:
+                self.ptrs.append(self.local_ptr)
+                continue
+            q = ctypes.c_void_p()
+            buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+            N.check(self.lib.trl_ipc_open(buf, ctypes.byref(q)), "ipc_open")
+            self.ptrs.append(q.value)
+        self.table = (ctypes.c_void_p * 8)(*(self.ptrs + [None] * (8 - world)))
+        self.mem = torch.as_tensor(_DevMem(self.local_ptr, self.nbytes), device=self.device)
+        big0 = self.lib.trl_symm_big_offset(hmax)
+        out0 = self.lib.trl_symm_out_offset(hmax, tmax)
+        self.big = self.mem[big0:big0 + tmax * hmax * 2].view(torch.bfloat16)
+        self.xres = self.mem[out0:out0 + tmax * hmax * 2].view(torch.bfloat16)
+        dist.barrier(group=group)
+
+    @classmethod
+    def create(cls, group, device, hmax: int = 8192, tmax: int = 8192) -> "SymmComm":
+        return cls(dist.get_rank(group), dist.get_world_size(group), group, device, hmax, tmax)
+
+    # ---- workspace views handed to CudaOps ----------------------------------------------------
+    def attach(self, ops) -> None:
+        """Place the residual stream and the row-parallel GEMM output in symmetric memory."""
+        ops.ws.bufs["x"] = self.xres
+        ops.ws.bufs["rowout"] = self.big
+
+    # ---- fused ops ------------------------------------------------------------------------------
+    def linear_allreduce_residual(self, ops, a, w, residual, lora=None):
+        from ..formats import NVFP4Tensor
+        t, k = a.shape
+        n = w.shape[0]
+        st = N.stream()
+        if t <= 8 and isinstance(w, NVFP4Tensor) and lora is None:
+            N.check(self.lib.trl_gemv_nvfp4_push(a.data_ptr(), a.stride(0), w.wq.data_ptr(), w.scale.data_ptr(),
+                                                 w.tscale.data_ptr(), self.table, self.rank, self.world, self.hmax,
+                                                 t, n, k, st), "gemv_push")
+            N.check(self.lib.trl_allreduce_finish(self.table, self.rank, self.world, self.hmax, residual.data_ptr(),
+                                                  residual.stride(0), residual.data_ptr(), residual.stride(0),
+                                                  t, n, st), "allreduce_finish")
+            N.count((t + 3) // 4 + 1)
+            return residual
+        # large-M: local partial into the symmetric region, then one two-shot kernel
+        assert residual.data_ptr() == self.xres.data_ptr(), "residual stream must live in symmetric memory"
+        assert t <= self.tmax and n <= self.hmax
+        part = self.big[: t * n].view(t, n)
+        ops._linear(a, w, part)
+        if lora is not None:
+            ops._lora_add(part, a, lora)
+        N.check(self.lib.trl_allreduce_twoshot(self.table, self.rank, self.world, self.hmax, self.tmax,
+                                               residual.data_ptr(), residual.stride(0), residual.stride(0), t, n, st),
+                "allreduce_twoshot")
+        N.count()
+        return residual
+
+    def argmax(self, ops, logits, v_valid: int):
+        """Global argmax over vocab-parallel fp32 logits ``[M, V_local]``."""
+        m, v_local = logits.shape
+        out = ops.ws.get("argmax", (m,), torch.int32)
+        scratch = ops.ws.get("argmax_scratch", (m * 128,), torch.float32)
+        pv = scratch
+        pi = scratch[m * 64:]
+        N.check(ops.lib.trl_argmax_stage1(logits.data_ptr(), logits.stride(0), m, max(0, min(v_local, v_valid)),
+                                          pv.data_ptr(), pi.data_ptr(), N.stream()), "argmax_stage1")
+        N.check(self.lib.trl_argmax_tp(self.table, self.rank, self.world, self.hmax, pv.data_ptr(), pi.data_ptr(),
+                                       64, v_local, out.data_ptr(), m, N.stream()), "argmax_tp")
+        N.count(2)
+        return out
+
+    def all_gather_logits(self, logits: torch.Tensor) -> torch.Tensor:
+        parts = [torch.empty_like(logits) for _ in range(self.world)]
+        dist.all_gather(parts, logits.contiguous(), group=self.group)
+        return torch.cat(parts, dim=-1)
+
+    def close(self) -> None:
+        for r, p in enumerate(self.ptrs):
+            if r != self.rank and p:
+                self.lib.trl_ipc_close(p)
+        self.lib.trl_symm_free(self.local_ptr)
