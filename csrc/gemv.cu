@@ -41,27 +41,30 @@ __device__ __forceinline__ void stage_x(const bf16* __restrict__ x, int ldx, int
 #pragma unroll
   for (int m = 0; m < M; ++m) {
     const bf16* xr = x + (size_t)m * ldx;
+    // one pass: sum of squares and max |x * w| together (the max of the normalised row is
+    // rstd times the latter), one block reduction for both
     float rstd = 1.f;
-    if (norm_w != nullptr) {
-      float ss = 0.f;
-      for (int k = threadIdx.x * 2; k < K; k += blockDim.x * 2) {
-        float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(xr + k));
-        ss += v.x * v.x + v.y * v.y;
-      }
-      ss = block_sum(ss, red);
-      rstd = rsqrtf(ss / (float)K + eps);
-    }
-    float amax = 0.f;
+    float ss = 0.f, amax = 0.f;
     for (int k = threadIdx.x * 2; k < K; k += blockDim.x * 2) {
       float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(xr + k));
-      if (norm_w != nullptr) {
-        // the unfused path rounds the normalised row to bf16; do the same
-        v.x = __bfloat162float(__float2bfloat16(v.x * rstd * norm_w[k]));
-        v.y = __bfloat162float(__float2bfloat16(v.y * rstd * norm_w[k + 1]));
-      }
+      ss += v.x * v.x + v.y * v.y;
+      if (norm_w != nullptr) v.x *= norm_w[k], v.y *= norm_w[k + 1];
       amax = fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y)));
     }
-    amax = block_max(amax, red);
+    {
+      const int lane_ = threadIdx.x & 31, w_ = threadIdx.x >> 5, nw_ = (blockDim.x + 31) >> 5;
+      ss = warp_sum(ss);
+      amax = warp_max(amax);
+      __syncthreads();
+      if (lane_ == 0) red[w_] = ss, red[32 + w_] = amax;
+      __syncthreads();
+      ss = warp_sum(lane_ < nw_ ? red[lane_] : 0.f);
+      amax = warp_max(lane_ < nw_ ? red[32 + lane_] : 0.f);
+    }
+    if (norm_w != nullptr) {
+      rstd = rsqrtf(ss / (float)K + eps);
+      amax *= rstd * 1.01f;   // bf16 rounding of the normalised values can add < 0.4 %
+    }
     // power-of-two scale s with amax * s <= 256: 16 products of |w| <= 6 stay < 65504
     int e = 0;
     if (amax > 0.f) {
@@ -342,7 +345,7 @@ template <int M, int R, int EPI>
 cudaError_t launch_nvfp4(const bf16* x, int ldx, const uint8_t* wq, const uint8_t* ws, const float* ts,
                          const float* norm_w, float eps, const bf16* res, int ldr, void* y, int ldy,
                          int N, int K, cudaStream_t st, const TrlPushArgs& push) {
-  const size_t smem = (size_t)M * K * sizeof(__half) + 8 * sizeof(float) + 32 * sizeof(float);
+  const size_t smem = (size_t)M * K * sizeof(__half) + 8 * sizeof(float) + 64 * sizeof(float);
   auto kern = gemv_nvfp4_kernel<M, R, EPI>;
   static bool configured = false;
   if (!configured) {
