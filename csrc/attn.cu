@@ -279,3 +279,44 @@ TRL_API int trl_attn_paged(const void* q, const void* gate_src, int gate_ld, con
                    D, n_splits, gated);
   return (int)e;
 }
+
+// ---- allocation-free variant (declared in attn_static.h) --------------------------------------
+#include "attn_static.h"
+
+// Scratch for the split partials of trl_attn_paged_static.  In host code this name is only a
+// stand-in for the symbol, not a device address: the address is fetched per device below.
+static __device__ __align__(256) unsigned char g_attn_static_scratch[TRL_ATTN_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_ptr[kMaxDevices] = {nullptr};
+}  // namespace
+
+TRL_API size_t trl_attn_static_scratch_needed(int T, int n_q, int D, int n_splits) {
+  return (size_t)T * n_q * n_splits * ((size_t)D + 2) * sizeof(float);
+}
+
+TRL_API int trl_attn_paged_static(const void* q, const void* gate_src, int gate_ld, const void* kcache,
+                                  const void* vcache, const void* block_table, int max_blocks,
+                                  const void* seq_ids, const void* positions, void* out, int T, int n_q,
+                                  int n_kv, int D, int n_splits, float scale, int gated, void* stream) {
+  if (T <= 0 || n_q <= 0 || n_splits <= 0 || D <= 0) return (int)cudaErrorInvalidValue;
+  const size_t need = trl_attn_static_scratch_needed(T, n_q, D, n_splits);
+  if (need > (size_t)TRL_ATTN_STATIC_SCRATCH_BYTES) return (int)cudaErrorInvalidValue;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return (int)cudaErrorInvalidDevice;
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    // once per device, with that device current: the symbol's address on THIS device
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_attn_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_static_scratch_ptr[dev] = p;
+  }
+  float* po = reinterpret_cast<float*>(g_static_scratch_ptr[dev]);
+  float* pm = po + (size_t)T * n_q * n_splits * D;
+  float* pl = pm + (size_t)T * n_q * n_splits;
+  return trl_attn_paged(q, gate_src, gate_ld, kcache, vcache, block_table, max_blocks, seq_ids, positions, po,
+                        pm, pl, out, T, n_q, n_kv, D, n_splits, scale, gated, stream);
+}
