@@ -1,0 +1,66 @@
+import os
+
+import torch
+
+from helpers import make_engine, rand_prompts
+from tilerl_b200.config import tiny_hybrid
+from tilerl_b200.engine import SamplingParams
+from tilerl_b200.kv import PrefixStore
+from tilerl_b200.kv_tiers import ColdSsdFile, DramSnapshots, HostKvPages, KvBootStore, SpillWriteError
+
+
+def _page(seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(1, 2, 16, 8, generator=g), torch.randn(1, 2, 16, 8, generator=g)
+
+
+def test_host_pages_lru_sharing_and_ssd_spill(tmp_path):
+    k0, v0 = _page(0)
+    nb = k0.numel() * 4 * 2
+    cold = ColdSsdFile(str(tmp_path / "spill.bin"), slot_bytes=nb, slots=4)
+    host = HostKvPages(budget_bytes=2 * nb, cold=cold)
+    keys = [host.demote(*_page(i)) for i in range(4)]
+    assert host.demote(*_page(3)) == keys[3] and host.stats["shared"] == 1
+    assert len(host.pages) == 2 and host.stats["spilled"] == 2
+    for i, key in enumerate(keys):             # promote from host or from the spill file
+        k, v = host.promote(key)
+        assert torch.equal(k, _page(i)[0]) and torch.equal(v, _page(i)[1])
+    assert host.promote("nope") is None
+    try:
+        cold.put("big", b"x" * (nb + 1))
+        assert False
+    except SpillWriteError:
+        pass
+    cold.close()
+
+
+def test_dram_snapshots_budget():
+    d = DramSnapshots(budget_bytes=3000)
+    for i in range(4):
+        d.put(i, (torch.full((256,), float(i)), torch.zeros(4)))
+    assert d.get(0, "cpu") is None and float(d.get(3, "cpu")[0][0]) == 3.0
+
+
+def test_boot_store_roundtrip_fingerprint_and_crc(tmp_path):
+    cfg = tiny_hybrid()
+    eng = make_engine(cfg)
+    eng.prefix = PrefixStore(eng.kv)
+    p = rand_prompts(cfg, 1, 40, seed=9)[0]
+    sp = SamplingParams(max_tokens=5)
+    cold = eng.generate([p], sp)[0].tokens
+    store = KvBootStore(str(tmp_path / "boot"))
+    assert store.save(eng) == 1
+    fresh = make_engine(cfg, model=eng.model)
+    fresh.prefix = PrefixStore(fresh.kv)
+    assert store.boot(fresh)["loaded"] == 1
+    r = fresh.generate([p], sp)[0]
+    assert r.tokens == cold and r.cached_tokens == 32
+    other = make_engine(cfg, seed=77)            # different weights: the store is ignored
+    other.prefix = PrefixStore(other.kv)
+    assert store.boot(other)["skipped_fingerprint"] == 1
+    victim = [f for f in os.listdir(tmp_path / "boot") if f.endswith("_0.bin")][0]
+    with open(tmp_path / "boot" / victim, "r+b") as f:
+        f.write(b"\xff\xff\xff")
+    again = make_engine(cfg, model=eng.model)
+    again.prefix = PrefixStore(again.kv)
+    assert store.boot(again) == dict(loaded=0, skipped_fingerprint=0, corrupt=1)

@@ -109,6 +109,7 @@ class _Req:
     t_done: float = 0.0
     prefix_tokens: int = 0
     published: bool = False
+    n_last_commit: int = 1   # tokens committed by the last tick (valid tap rows for the drafter)
 
     @property
     def toks(self) -> List[int]:
@@ -501,6 +502,7 @@ class Engine:
 
     def _commit(self, r: _Req, toks: List[Tuple[int, float]]) -> None:
         p = r.params
+        r.n_last_commit = len(toks)
         for tok, lp in toks:
             r.out.append(tok)
             if p.logprobs:

@@ -81,14 +81,11 @@ class RefOps:
         kc, vc = pool.layer(attn_idx)
         ref.kv_write(kc, vc, k, v, batch.slot_mapping)
         scale = 1.0 / math.sqrt(cfg.head_dim)
+        table, pos = batch.block_table, batch.positions
         sp = batch.sparse
         if sp is not None and sp.active(attn_idx):
-            lists, counts = sp.page_lists(attn_idx, q, batch)
-            out = ref.sparse_paged_attention(q, gate, kc, vc, lists, counts, batch.seq_ids,
-                                             batch.positions, scale)
-        else:
-            out = ref.paged_attention(q, gate, kc, vc, batch.block_table, batch.seq_ids,
-                                      batch.positions, scale)
+            table, pos = sp.packed(attn_idx, q, kc)    # [selected pages ; trailing window]
+        out = ref.paged_attention(q, gate, kc, vc, table, batch.seq_ids, pos, scale)
         return out.to(self.act_dtype)
 
     def gdn(self, inp, lp, batch, spool, gdn_idx, cfg, nk, nv):

@@ -193,14 +193,18 @@ class CudaOps:
             self._f32(lp["k_norm"]).data_ptr(), batch.positions.data_ptr(),
             batch.slot_mapping.data_ptr(), q.data_ptr(), kc.data_ptr(), vc.data_ptr(), t, n_q, n_kv, d,
             cfg.rotary_dim, float(cfg.rope_theta), cfg.rms_eps, int(cfg.attn_gated), st), "attn_prep")
+        table, pos = batch.block_table, batch.positions
+        sp = batch.sparse
+        if sp is not None and sp.active(attn_idx):
+            table, pos = sp.packed(attn_idx, q, kc)    # same kernel on [selected pages ; trailing window]
         splits = self.attn_splits or self._pick_splits(batch, t, n_kv)
         po = self.ws.get("attn_po", (t * n_q * splits * d,), torch.float32)
         pm = self.ws.get("attn_pm", (t * n_q * splits,), torch.float32)
         pl = self.ws.get("attn_pl", (t * n_q * splits,), torch.float32)
         N.check(self.lib.trl_attn_paged(
             q.data_ptr(), qkv.data_ptr(), qkv.stride(0), kc.data_ptr(), vc.data_ptr(),
-            batch.block_table.data_ptr(), batch.block_table.stride(0), batch.seq_ids.data_ptr(),
-            batch.positions.data_ptr(), po.data_ptr(), pm.data_ptr(), pl.data_ptr(), out.data_ptr(),
+            table.data_ptr(), table.stride(0), batch.seq_ids.data_ptr(),
+            pos.data_ptr(), po.data_ptr(), pm.data_ptr(), pl.data_ptr(), out.data_ptr(),
             t, n_q, n_kv, d, splits, 1.0 / math.sqrt(d), int(cfg.attn_gated), st), "attn_paged")
         N.count(2 + (1 if splits > 1 else 0))
         return out

@@ -1,0 +1,235 @@
+"""Speculative decoding: drafters and the verify bookkeeping.
+
+The engine verifies a width-W chain ``[last committed token, d1 .. d_{W-1}]`` in ONE trunk
+forward (W-wide attention over the paged KV, W recurrent GDN steps with the state after
+every step kept in its own plane), samples the trunk's own token at every position with
+the same per-position seeds plain decoding would use, accepts the leading run where
+sample == draft, and adopts the GDN state plane of the last accepted token.  Greedy and
+seeded-sampling outputs are therefore identical with and without a drafter.
+
+Drafters (all expose ``aux_layers`` and ``propose``):
+
+* :class:`BlockDrafter` -- W-wide block drafter: reads three trunk hidden taps, keeps an
+  incrementally projected context K/V per request, runs a block of ``[embed(last), mask x
+  (W-1)]`` through ``n_layers`` non-causal GQA layers of trunk width and scores every slot
+  with the trunk's own lm_head (shared embedding and head).
+* :class:`ChainDrafter` -- NextN / MTP style: ``fc([norm(embed(tok)), norm(h_trunk)])`` ->
+  one causal layer over its own short cache -> trunk lm_head, unrolled greedily.
+* :class:`OracleDrafter` / :class:`ConstantDrafter` -- test and benchmark seams: forced
+  full acceptance (drafts = the trunk's greedy continuation, precomputed) and zero
+  acceptance.
+
+Parity: reference ``src/tilerl/spec.py`` -- ``verify_lens:133``, ``DraftHead:351``,
+``DFlash2Config:903``, ``DFlash2Head:954`` (``step:986``, ``context_kv:1031``,
+``block_hidden:1045``, ``paths:1071``); engine ``_verify`` ``src/tilerl/engine.py:2625``.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import torch
+import torch.nn.functional as F
+
+from .ops import ref
+
+
+def verify_lens(drafts: Sequence[int], sampled: Sequence[int]) -> int:
+    """Length of the leading run where the trunk's sampled token equals the draft."""
+    n = 0
+    for d, s in zip(drafts, sampled):
+        if d != s:
+            break
+        n += 1
+    return n
+
+
+def expected_goodput(accept_rate: float, width: int) -> float:
+    """Expected committed tokens per verify tick for i.i.d. per-slot acceptance."""
+    a = min(max(accept_rate, 0.0), 1.0)
+    return sum(a ** k for k in range(width))
+
+
+@dataclass
+class BlockDrafterConfig:
+    width: int = 8
+    n_layers: int = 2
+    n_heads: int = 8
+    n_kv_heads: int = 2
+    taps: int = 3
+    window: int = 64          # context positions the block attends to
+    ffn_mult: float = 2.0
+
+
+class BlockDrafter:
+    """Random-init or loaded block drafter.  Everything here is small-M work on the
+    trunk's width; it runs as torch ops on the engine's device."""
+
+    def __init__(self, model, cfg: Optional[BlockDrafterConfig] = None, seed: int = 0, dtype=torch.float32):
+        self.cfg = cfg or BlockDrafterConfig()
+        self.model = model
+        mc = model.cfg
+        h = mc.hidden
+        n = mc.n_layers
+        self.aux_layers = tuple(sorted({max(0, n // 4 - 1), max(0, n // 2 - 1), n - 1}))[-self.cfg.taps:]
+        dev = model.params["embed"].device
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        c = self.cfg
+        self.hd = h // c.n_heads
+        ffn = int(h * c.ffn_mult)
+
+        def w(*shape, s=0.02):
+            return (torch.randn(*shape, generator=g) * s).to(dev, dtype)
+        self.p: Dict[str, torch.Tensor] = {"fc": w(h, len(self.aux_layers) * h), "mask": w(h), "pos": w(c.width, h),
+                                           "ctx_norm": torch.ones(h, device=dev, dtype=dtype),
+                                           "out_norm": torch.ones(h, device=dev, dtype=dtype)}
+        for i in range(c.n_layers):
+            q = f"l{i}."
+            self.p[q + "norm1"] = torch.ones(h, device=dev, dtype=dtype)
+            self.p[q + "norm2"] = torch.ones(h, device=dev, dtype=dtype)
+            self.p[q + "q"] = w(c.n_heads * self.hd, h)
+            self.p[q + "kv"] = w(2 * c.n_kv_heads * self.hd, h)
+            self.p[q + "o"] = w(h, c.n_heads * self.hd)
+            self.p[q + "gate_up"] = w(2 * ffn, h)
+            self.p[q + "down"] = w(h, ffn)
+        self.ctx: Dict[int, List[torch.Tensor]] = {}   # rid -> per-layer context features [n, H]
+
+    # ---- engine hooks -------------------------------------------------------------------
+    def release(self, rid: int) -> None:
+        self.ctx.pop(rid, None)
+
+    def invalidate(self) -> None:
+        self.ctx.clear()
+
+    def _embed(self, tok: int) -> torch.Tensor:
+        return self.model.params["embed"][tok].to(self.p["fc"].dtype)
+
+    def _head(self, x: torch.Tensor) -> torch.Tensor:
+        head = self.model.params["embed" if self.model.cfg.tie_embeddings else "lm_head"]
+        w = head if isinstance(head, torch.Tensor) else head.dequant()
+        return ref.rmsnorm(x, self.p["out_norm"], 1e-6) @ w.float().t().to(x.device)
+
+    def context_features(self, taps: Dict[int, torch.Tensor], rows: slice) -> torch.Tensor:
+        """Project the concatenated trunk taps of the given token rows: [n, H]."""
+        cat = torch.cat([taps[l][rows].to(self.p["fc"].dtype) for l in self.aux_layers], dim=-1)
+        return ref.rmsnorm(cat @ self.p["fc"].t(), self.p["ctx_norm"], 1e-6).to(self.p["fc"].dtype)
+
+    def _attend(self, q, k, v):
+        """Non-causal GQA: q [W, nh, d], k/v [S, nkv, d]."""
+        c = self.cfg
+        g = c.n_heads // c.n_kv_heads
+        qq = q.view(q.shape[0], c.n_kv_heads, g, self.hd)
+        s = torch.einsum("whgd,shd->hgws", qq.float(), k.float()) / math.sqrt(self.hd)
+        p = torch.softmax(s, -1)
+        return torch.einsum("hgws,shd->whgd", p, v.float()).reshape(q.shape[0], -1)
+
+    def block_hidden(self, last_tok: int, ctx: torch.Tensor) -> torch.Tensor:
+        """Run the mask-token block over the context features; returns [W, H]."""
+        c = self.cfg
+        x = torch.stack([self._embed(last_tok)] + [self.p["mask"]] * (c.width - 1)) + self.p["pos"]
+        ctx = ctx[-c.window:]
+        for i in range(c.n_layers):
+            q_ = f"l{i}."
+            hx = ref.rmsnorm(x, self.p[q_ + "norm1"], 1e-6).to(x.dtype)
+            src = torch.cat([ctx, hx])                      # context rows first, then the block itself
+            kv = (src @ self.p[q_ + "kv"].t()).view(src.shape[0], 2, c.n_kv_heads, self.hd)
+            q = (hx @ self.p[q_ + "q"].t()).view(c.width, c.n_heads, self.hd)
+            a = self._attend(q, kv[:, 0], kv[:, 1]).to(x.dtype)
+            x = x + a @ self.p[q_ + "o"].t()
+            hx = ref.rmsnorm(x, self.p[q_ + "norm2"], 1e-6).to(x.dtype)
+            gu = hx @ self.p[q_ + "gate_up"].t()
+            f = gu.shape[-1] // 2
+            x = x + (F.silu(gu[:, :f]) * gu[:, f:]) @ self.p[q_ + "down"].t()
+        return x
+
+    def propose(self, engine, req, taps, tok_off: int, n_run: int, k: int) -> List[int]:
+        """Drafts for the next verify tick.  ``taps``: trunk residual-stream taps of this tick's
+        tokens; rows ``tok_off .. tok_off + n_valid`` belong to tokens that were really
+        committed to the sequence."""
+        if taps is None or k <= 0:
+            return []
+        n_valid = min(n_run, max(1, getattr(req, "n_last_commit", n_run))) if req.state == "decode" and n_run <= \
+            engine.spec_width else n_run
+        feats = self.context_features(taps, slice(tok_off, tok_off + n_valid))
+        old = self.ctx.get(req.rid)
+        ctx = feats if old is None else torch.cat([old, feats])[-self.cfg.window:]
+        self.ctx[req.rid] = ctx
+        hid = self.block_hidden(req.toks[-1], ctx)
+        logits = self._head(hid[1:1 + k] if hid.shape[0] > k else hid[-k:])
+        return [int(t) for t in logits.argmax(-1).tolist()][:k]
+
+
+class ChainDrafter:
+    """NextN-style chain drafter sharing the trunk's embedding and lm_head."""
+
+    def __init__(self, model, seed: int = 0, dtype=torch.float32):
+        self.model = model
+        h = model.cfg.hidden
+        self.aux_layers = (model.cfg.n_layers - 1,)
+        dev = model.params["embed"].device
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        self.fc = (torch.randn(h, 2 * h, generator=g) * 0.02).to(dev, dtype)
+        self.mix = (torch.randn(h, h, generator=g) * 0.02).to(dev, dtype)
+        self.n1 = torch.ones(h, device=dev, dtype=dtype)
+        self.n2 = torch.ones(h, device=dev, dtype=dtype)
+        self.hidden: Dict[int, torch.Tensor] = {}
+
+    def release(self, rid: int) -> None:
+        self.hidden.pop(rid, None)
+
+    def invalidate(self) -> None:
+        self.hidden.clear()
+
+    def step(self, tok: int, h_prev: torch.Tensor) -> torch.Tensor:
+        e = self.model.params["embed"][tok].to(self.fc.dtype)
+        z = torch.cat([ref.rmsnorm(e, self.n1, 1e-6), ref.rmsnorm(h_prev, self.n2, 1e-6)]).to(self.fc.dtype)
+        x = z @ self.fc.t()
+        return x + F.silu(x @ self.mix.t())
+
+    def propose(self, engine, req, taps, tok_off: int, n_run: int, k: int) -> List[int]:
+        if taps is None or k <= 0:
+            return []
+        n_valid = min(n_run, max(1, getattr(req, "n_last_commit", n_run)))
+        h = taps[self.aux_layers[0]][tok_off + n_valid - 1].to(self.fc.dtype)
+        head = self.model.params["embed" if self.model.cfg.tie_embeddings else "lm_head"]
+        w = (head if isinstance(head, torch.Tensor) else head.dequant()).float().to(h.device)
+        out, tok = [], req.toks[-1]
+        for _ in range(k):
+            h = self.step(tok, h)
+            tok = int((h.float() @ w.t()).argmax())
+            out.append(tok)
+        return out
+
+
+class OracleDrafter:
+    """Forced full acceptance: proposes the continuation recorded for each prompt (the
+    trunk's own greedy output).  Used to time the verify tick at acceptance = 1."""
+    aux_layers: tuple = ()
+
+    def __init__(self, continuations: Dict[tuple, List[int]]):
+        self.cont = continuations
+
+    def propose(self, engine, req, taps, tok_off, n_run, k) -> List[int]:
+        c = self.cont.get(tuple(req.prompt))
+        if c is None:
+            return []
+        i = len(req.out)
+        return list(c[i:i + k])
+
+    def release(self, rid: int) -> None:
+        pass
+
+
+class ConstantDrafter:
+    """Zero acceptance (with overwhelming probability): always proposes the same token."""
+    aux_layers: tuple = ()
+
+    def __init__(self, token: int = 0):
+        self.token = token
+
+    def propose(self, engine, req, taps, tok_off, n_run, k) -> List[int]:
+        return [self.token] * k
+
+    def release(self, rid: int) -> None:
+        pass
