@@ -1,0 +1,56 @@
+"""CLI smoke on CPU: every verb parses and runs its smallest case."""
+import json
+import os
+
+import pytest
+
+from tilerl_b200 import cli
+
+
+def test_serve_dry_run_prints_ledger(capsys):
+    assert cli.main(["serve", "--model", "qwen38-27b", "--dry-run", "--slots", "16"]) == 0
+    out = capsys.readouterr().out
+    assert "weights" in out and "kv pool" in out
+
+
+def test_bench_kernels_table(capsys):
+    assert cli.main(["bench", "--model", "qwen38-27b", "--kernels"]) == 0
+    out = capsys.readouterr().out
+    assert "gate_up" in out and "bound" in out.lower()
+
+
+def test_bench_runs_tiny(capsys):
+    assert cli.main(["bench", "--model", "tiny", "--device", "cpu", "--prompt-len", "16", "--gen", "4"]) == 0
+    rec = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rec[0]["batch"] == 1 and rec[0]["decode_tok_s"] > 0
+
+
+def test_train_recipe_and_ledger(tmp_path, capsys):
+    runs = str(tmp_path / "runs")
+    assert cli.main(["train", "--recipe", "grpo-tiny-smoke", "--device", "cpu", "--steps", "1", "--max-tokens", "4",
+                     "--runs", runs, "--prompt-len", "6"]) == 0
+    lines = [l for l in capsys.readouterr().out.splitlines() if l.startswith("{")]
+    assert json.loads(lines[-1])["step"] == 0
+    assert cli.main(["ledger", "--runs", runs]) == 0
+    assert "done" in capsys.readouterr().out
+
+
+def test_train_sft_lora_saves_adapter(tmp_path, capsys):
+    out = str(tmp_path / "adapter")
+    assert cli.main(["train", "--model", "tiny", "--device", "cpu", "--steps", "1", "--lora-rank", "2",
+                     "--save-model", out, "--runs", str(tmp_path / "r"), "--prompt-len", "8"]) == 0
+    assert os.path.exists(out)
+
+
+def test_generate_and_merge(tmp_path, capsys):
+    p = tmp_path / "p.jsonl"
+    p.write_text('{"prompt": "hi"}\n{"prompt": "yo"}\n')
+    assert cli.main(["generate", "--model", "tiny", "--device", "cpu", "--prompts", str(p), "--out",
+                     str(tmp_path / "gen"), "--max-tokens", "3"]) == 0
+    files = json.loads(capsys.readouterr().out.strip().splitlines()[-1])["files"]
+    assert len(open(files[0]).read().splitlines()) == 2
+
+
+def test_unknown_recipe():
+    with pytest.raises(KeyError):
+        cli.main(["train", "--recipe", "nope", "--device", "cpu"])

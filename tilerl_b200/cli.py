@@ -1,0 +1,296 @@
+"""Command line: ``python -m tilerl_b200.cli {serve,train,bench,generate,merge,ledger}``.
+
+Parity: reference ``src/tilerl/cli.py`` -- ``cmd_serve:145``, ``_build_parser:507-1255``
+(same verbs; one ``TRL_*`` environment namespace instead of the reference's ``TILERL_*``).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+from typing import List, Optional
+
+
+def _add_model_flags(p: argparse.ArgumentParser) -> None:
+    p.add_argument("--model", default="tiny", help="model config name (see tilerl_b200.config)")
+    p.add_argument("--checkpoint", default=None, help="HF-style checkpoint directory")
+    p.add_argument("--tokenizer", default=None, help="tokenizer.json (default: byte tokenizer)")
+    p.add_argument("--device", default=None, help="cuda | cpu (default: cuda when available)")
+    p.add_argument("--seed", type=int, default=0)
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="tilerl_b200")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+
+    s = sub.add_parser("serve", help="OpenAI / Anthropic compatible HTTP server")
+    _add_model_flags(s)
+    s.add_argument("--host", default="127.0.0.1")
+    s.add_argument("--port", type=int, default=8000)
+    s.add_argument("--slots", type=int, default=8)
+    s.add_argument("--blocks", type=int, default=None)
+    s.add_argument("--max-ctx", type=int, default=4096)
+    s.add_argument("--max-batch", type=int, default=64)
+    s.add_argument("--max-batched-tokens", type=int, default=512)
+    s.add_argument("--max-inflight", type=int, default=1024)
+    s.add_argument("--decode-graph", dest="graph", action="store_true", default=True)
+    s.add_argument("--no-decode-graph", dest="graph", action="store_false")
+    s.add_argument("--no-prefix", action="store_true")
+    s.add_argument("--draft", default=None, choices=[None, "block", "chain"])
+    s.add_argument("--spec-width", type=int, default=8)
+    s.add_argument("--sparse-k", type=int, default=0)
+    s.add_argument("--sparse-min-tokens", type=int, default=4096)
+    s.add_argument("--sparse-window-tokens", type=int, default=128)
+    s.add_argument("--sparse-refresh-ticks", type=int, default=8)
+    s.add_argument("--kv-store", default=None, help="directory of the cold-start KV store")
+    s.add_argument("--completion-timeout-s", type=float, default=600.0)
+    s.add_argument("--stream-pace", action="store_true")
+    s.add_argument("--no-warmup", action="store_true")
+    s.add_argument("--dry-run", action="store_true", help="print the memory ledger and exit")
+
+    t = sub.add_parser("train", help="SFT / GRPO / on-policy distillation")
+    _add_model_flags(t)
+    t.add_argument("--recipe", default=None)
+    t.add_argument("--rl", action="store_true")
+    t.add_argument("--opd", action="store_true")
+    t.add_argument("--steps", type=int, default=None)
+    t.add_argument("--group", type=int, default=None)
+    t.add_argument("--prompts-per-step", type=int, default=None)
+    t.add_argument("--max-tokens", type=int, default=None)
+    t.add_argument("--micro", type=int, default=None)
+    t.add_argument("--lora-rank", type=int, default=None)
+    t.add_argument("--lr", type=float, default=None)
+    t.add_argument("--optim", default=None, choices=[None, "adamw", "adafactor", "iso"])
+    t.add_argument("--reward", default=None)
+    t.add_argument("--clip-eps", type=float, default=0.2)
+    t.add_argument("--kl-coef", type=float, default=0.0)
+    t.add_argument("--prompts", default=None, help="jsonl of prompts (default: random token prompts)")
+    t.add_argument("--prompt-len", type=int, default=16)
+    t.add_argument("--save-model", default=None)
+    t.add_argument("--load-adapter", default=None)
+    t.add_argument("--served-fp4", action="store_true")
+    t.add_argument("--runs", default="runs")
+
+    b = sub.add_parser("bench", help="prefill / decode throughput, kernel roofline table, calibration")
+    _add_model_flags(b)
+    b.add_argument("--prompt-len", type=int, default=512)
+    b.add_argument("--gen", type=int, default=64)
+    b.add_argument("--batches", default="1")
+    b.add_argument("--kernels", action="store_true", help="print the declared cost table and bounds")
+    b.add_argument("--calibrate", action="store_true", help="measure HBM / GEMM / H2D floors")
+    b.add_argument("--tp", type=int, default=1)
+    b.add_argument("--record", action="store_true", help="append results to the bench store")
+
+    g = sub.add_parser("generate", help="offline generation, one process per GPU")
+    _add_model_flags(g)
+    g.add_argument("--prompts", required=True)
+    g.add_argument("--out", required=True)
+    g.add_argument("--workers", type=int, default=1)
+    g.add_argument("--max-tokens", type=int, default=64)
+    g.add_argument("--temperature", type=float, default=0.0)
+
+    m = sub.add_parser("merge", help="merge fine-tuned checkpoints")
+    m.add_argument("--base", required=True)
+    m.add_argument("--tuned", nargs="+", required=True)
+    m.add_argument("--out", required=True)
+    m.add_argument("--method", default="average", choices=["average", "ties", "dare", "iso"])
+
+    lg = sub.add_parser("ledger", help="list runs, show lineage, list devices")
+    lg.add_argument("--runs", default="runs")
+    lg.add_argument("--show", default=None)
+    lg.add_argument("--devices", action="store_true")
+    return ap
+
+
+def _device(args) -> str:
+    if args.device:
+        return args.device
+    import torch
+    return "cuda" if torch.cuda.is_available() else "cpu"
+
+
+def cmd_serve(args) -> int:
+    from . import memory
+    from .config import get_config
+    cfg = get_config(args.model)
+    if args.dry_run:
+        p = memory.plan(cfg, slots=args.slots, blocks=args.blocks, max_batched_tokens=args.max_batched_tokens,
+                        planes=args.spec_width if args.draft else 1)
+        print(memory.memory_table(p))
+        return 0
+    from .engine import StepLimits
+    from .factory import build_engine, build_model, make_ops
+    from .server.app import create_app
+    from .tokenizer import load_tokenizer
+    dev = _device(args)
+    ops = make_ops(dev)
+    model = build_model(cfg, dev, seed=args.seed, checkpoint=args.checkpoint, ops=ops if dev != "cpu" else None)
+    drafter = None
+    if args.draft:
+        from .spec import BlockDrafter, ChainDrafter
+        drafter = BlockDrafter(model) if args.draft == "block" else ChainDrafter(model)
+    sparse = None
+    if args.sparse_k:
+        from .sparse import SparseConfig, SparseKV
+        sparse = SparseKV(cfg, SparseConfig(args.sparse_k, max(1, args.sparse_window_tokens // 16),
+                                            args.sparse_refresh_ticks, args.sparse_min_tokens))
+    tok = load_tokenizer(args.tokenizer, cfg.vocab)
+    eng = build_engine(model, ops, device=dev, blocks=args.blocks, slots=args.slots, max_ctx=args.max_ctx,
+                       prefix=not args.no_prefix, graph=args.graph, spec_width=args.spec_width if drafter else 0,
+                       drafter=drafter, sparse=sparse,
+                       limits=StepLimits(args.max_batch, args.max_batched_tokens, max_inflight=args.max_inflight),
+                       eos_id=tok.eos_id, detokenize=tok.decode, think_ids=getattr(tok, "think_ids", None))
+    if args.kv_store:
+        from .kv_tiers import KvBootStore
+        print(json.dumps({"kv_boot": KvBootStore(args.kv_store).boot(eng)}))
+    if not args.no_warmup:
+        eng.precapture((1,))
+    eng.run()
+    app = create_app(eng, tok, cfg.name, pace=args.stream_pace, completion_timeout_s=args.completion_timeout_s)
+    import uvicorn
+    uvicorn.run(app, host=args.host, port=args.port, log_level="warning")
+    return 0
+
+
+def cmd_train(args) -> int:
+    import torch
+    from . import evals, rl
+    from .checkpoint import load_adapter, save_adapter, save_checkpoint
+    from .config import get_config
+    from .factory import build_engine, build_model, make_ops
+    from .ledger import Run
+    from .optim import make_optimizer
+    from .recipes import expand
+    over = {k: getattr(args, k) for k in ("steps", "group", "prompts_per_step", "max_tokens", "micro", "lora_rank",
+                                          "lr", "optim", "reward")}
+    if args.rl:
+        over["rl"] = True
+    if args.opd:
+        over["opd"] = True
+    flags = expand(args.recipe, over) if args.recipe else {**dict(model=args.model, steps=2, group=4, prompts_per_step=2,
+                                                                  max_tokens=8, micro=0, lora_rank=0, lr=1e-5,
+                                                                  optim="adamw", reward="even", rl=args.rl,
+                                                                  opd=args.opd),
+                                                           **{k: v for k, v in over.items() if v is not None}}
+    cfg = get_config(flags.get("model", args.model))
+    dev = _device(args)
+    ops = make_ops(dev)
+    model = build_model(cfg, dev, seed=args.seed, checkpoint=args.checkpoint, ops=ops if dev != "cpu" else None,
+                        keep_master=not flags.get("lora_rank"))
+    if flags.get("lora_rank"):
+        model.add_lora(rank=flags["lora_rank"])
+        if args.load_adapter:
+            load_adapter(model, args.load_adapter)
+    opt = make_optimizer(flags.get("optim", "adamw"), model.trainable(), flags["lr"])
+    run = Run({"cmd": "train", **flags}, root=args.runs)
+    eng = build_engine(model, ops, device=dev, slots=flags["group"] * flags["prompts_per_step"] + 1,
+                       max_ctx=args.prompt_len + flags["max_tokens"] + 32, prefix=False, graph=False)
+    g = torch.Generator().manual_seed(args.seed)
+    prompts = [torch.randint(0, cfg.vocab, (args.prompt_len,), generator=g).tolist() for _ in range(64)]
+    post = (lambda m: m.requantize_()) if not flags.get("lora_rank") else None
+    if flags.get("opd"):
+        loop = rl.opd_loop(eng, model, prompts, opt, steps=flags["steps"], max_tokens=flags["max_tokens"],
+                           prompts_per_step=flags["prompts_per_step"])
+    elif flags.get("rl"):
+        loop = rl.grpo_loop(eng, model, prompts, evals.REWARDS.get(flags["reward"], evals.reward_even), opt,
+                            steps=flags["steps"], group=flags["group"], prompts_per_step=flags["prompts_per_step"],
+                            max_tokens=flags["max_tokens"], clip_eps=args.clip_eps, kl_coef=args.kl_coef,
+                            micro=flags.get("micro") or 0, post_step=post)
+    else:
+        data = iter(lambda: torch.randint(0, cfg.vocab, (2, args.prompt_len), generator=g), None)
+        loop = iter(rl.pretrain(model, data, opt, steps=flags["steps"], lr=flags["lr"]))
+    for m in loop:
+        run.log(**{k: v for k, v in m.items() if not isinstance(v, dict)})
+        print(json.dumps(m, default=str), flush=True)
+    if args.save_model:
+        if flags.get("lora_rank"):
+            save_adapter(model, args.save_model)
+        else:
+            save_checkpoint(model, args.save_model)
+        run.artifacts["model"] = args.save_model
+    run.finish()
+    return 0
+
+
+def cmd_bench(args) -> int:
+    from . import kernel_cost as kc
+    from .calibration import calibrate, load_peaks
+    from .config import get_config
+    cfg = get_config(args.model)
+    if args.calibrate:
+        import dataclasses
+        print(json.dumps(dataclasses.asdict(calibrate(_device(args)))))
+        return 0
+    pk = load_peaks()
+    if args.kernels:
+        rows = kc.tick_rows(cfg, kc.TickShape(batch=int(args.batches.split(",")[0]), ctx=args.prompt_len, tp=args.tp))
+        print(kc.table(rows, pk.hbm_gbs, pk.bf16_tflops, pk.nvlink_gbs))
+        print(kc.table(kc.prefill_rows(cfg, args.prompt_len, args.tp), pk.hbm_gbs, 4 * pk.bf16_tflops, pk.nvlink_gbs))
+        return 0
+    import time
+    import torch
+    from .engine import SamplingParams
+    from .factory import build_engine, build_model, make_ops
+    dev = _device(args)
+    ops = make_ops(dev)
+    model = build_model(cfg, dev, seed=args.seed, checkpoint=args.checkpoint, ops=ops if dev != "cpu" else None)
+    out = []
+    for b in [int(x) for x in args.batches.split(",")]:
+        eng = build_engine(model, ops, device=dev, slots=b + 1, max_ctx=args.prompt_len + args.gen + 32, prefix=False)
+        g = torch.Generator().manual_seed(1)
+        prompts = [torch.randint(0, cfg.vocab, (args.prompt_len,), generator=g).tolist() for _ in range(b)]
+        for _ in range(3):
+            eng.generate(prompts, SamplingParams(max_tokens=min(4, args.gen), ignore_eos=True))
+        t0 = time.perf_counter()
+        res = eng.generate(prompts, SamplingParams(max_tokens=args.gen, ignore_eos=True))
+        dt = time.perf_counter() - t0
+        ttft = sum(r.ttft_s for r in res) / b
+        rec = {"batch": b, "prefill_tok_s": round(b * args.prompt_len / max(ttft, 1e-9), 1),
+               "decode_tok_s": round(b * (args.gen - 1) / max(dt - ttft, 1e-9), 1)}
+        out.append(rec)
+        if args.record:
+            from . import benchrec
+            benchrec.append(benchrec.make_record("decode_tok_s", rec["decode_tok_s"],
+                                                 dict(model=cfg.name, batch=b, ctx=args.prompt_len, tp=args.tp)))
+    print(json.dumps(out))
+    return 0
+
+
+def cmd_generate(args) -> int:
+    from .generate import generate
+    files = generate(args.model, args.prompts, args.out, workers=args.workers, device=_device(args),
+                     max_tokens=args.max_tokens, temperature=args.temperature, checkpoint=args.checkpoint,
+                     tokenizer_path=args.tokenizer, seed=args.seed)
+    print(json.dumps({"files": files}))
+    return 0
+
+
+def cmd_merge(args) -> int:
+    from .merge import merge_checkpoints
+    n = merge_checkpoints(args.base, args.tuned, args.out, args.method)
+    print(json.dumps({"tensors": n, "out": args.out}))
+    return 0
+
+
+def cmd_ledger(args) -> int:
+    from . import ledger
+    if args.devices:
+        print(json.dumps(ledger.devices(), indent=1))
+        return 0
+    if args.show:
+        print(json.dumps({"run": ledger.load_run(args.show, args.runs), "lineage": ledger.lineage(args.show, args.runs)},
+                         indent=1))
+        return 0
+    for r in ledger.list_runs(args.runs):
+        print(f"{r['id']}  {r['status']:12s} {r['seconds']:8.1f}s  {r['inputs'].get('recipe') or r['inputs'].get('cmd', '')}")
+    return 0
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    args = build_parser().parse_args(argv)
+    return {"serve": cmd_serve, "train": cmd_train, "bench": cmd_bench, "generate": cmd_generate,
+            "merge": cmd_merge, "ledger": cmd_ledger}[args.cmd](args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

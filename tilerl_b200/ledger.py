@@ -1,0 +1,143 @@
+"""Run ledger: every training / eval run gets ``runs/<id>/manifest.json`` whose id is a hash
+of its inputs (flags, model, data, parent run), with gates, lineage and early stopping.
+
+Parity: reference ``src/tilerl/ledger.py:245,299,549`` (manifest, gates, ``EarlyStop``,
+``time_to_score``, ``ledger --devices``).
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+import time
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+RUNS_DIR = os.environ.get("TRL_RUNS", "runs")
+
+
+def run_id(inputs: Dict[str, Any]) -> str:
+    blob = json.dumps(inputs, sort_keys=True, default=str).encode()
+    return hashlib.sha256(blob).hexdigest()[:12]
+
+
+@dataclass
+class Gate:
+    name: str
+    value: float
+    threshold: float
+    higher_is_better: bool = True
+
+    @property
+    def passed(self) -> bool:
+        return self.value >= self.threshold if self.higher_is_better else self.value <= self.threshold
+
+
+@dataclass
+class Run:
+    inputs: Dict[str, Any]
+    root: str = RUNS_DIR
+    parent: Optional[str] = None
+    id: str = ""
+    metrics: List[Dict[str, Any]] = field(default_factory=list)
+    gates: List[Gate] = field(default_factory=list)
+    artifacts: Dict[str, str] = field(default_factory=dict)
+    started: float = field(default_factory=time.time)
+    status: str = "running"
+
+    def __post_init__(self):
+        self.id = self.id or run_id({**self.inputs, "parent": self.parent})
+        os.makedirs(self.dir, exist_ok=True)
+        self.write()
+
+    @property
+    def dir(self) -> str:
+        return os.path.join(self.root, self.id)
+
+    def log(self, **m) -> None:
+        self.metrics.append({"t": round(time.time() - self.started, 3), **m})
+
+    def gate(self, name: str, value: float, threshold: float, higher_is_better: bool = True) -> bool:
+        g = Gate(name, float(value), float(threshold), higher_is_better)
+        self.gates.append(g)
+        return g.passed
+
+    def finish(self, status: str = "done") -> None:
+        self.status = status if all(g.passed for g in self.gates) else "gate_failed"
+        self.write()
+
+    def write(self) -> None:
+        man = {"id": self.id, "parent": self.parent, "inputs": self.inputs, "status": self.status,
+               "started": self.started, "seconds": round(time.time() - self.started, 3), "metrics": self.metrics,
+               "gates": [{"name": g.name, "value": g.value, "threshold": g.threshold, "passed": g.passed}
+                         for g in self.gates], "artifacts": self.artifacts}
+        tmp = os.path.join(self.dir, "manifest.json.tmp")
+        with open(tmp, "w") as f:
+            json.dump(man, f, indent=1, default=str)
+        os.replace(tmp, os.path.join(self.dir, "manifest.json"))
+
+
+def load_run(rid: str, root: str = RUNS_DIR) -> Dict[str, Any]:
+    with open(os.path.join(root, rid, "manifest.json")) as f:
+        return json.load(f)
+
+
+def lineage(rid: str, root: str = RUNS_DIR) -> List[str]:
+    chain = []
+    cur: Optional[str] = rid
+    while cur and cur not in chain:
+        chain.append(cur)
+        try:
+            cur = load_run(cur, root).get("parent")
+        except OSError:
+            break
+    return chain
+
+
+def list_runs(root: str = RUNS_DIR) -> List[Dict[str, Any]]:
+    out = []
+    if os.path.isdir(root):
+        for d in sorted(os.listdir(root)):
+            try:
+                out.append(load_run(d, root))
+            except (OSError, json.JSONDecodeError):
+                continue
+    return out
+
+
+def time_to_score(run: Dict[str, Any], key: str, target: float) -> Optional[float]:
+    for m in run.get("metrics", []):
+        if key in m and m[key] >= target:
+            return m["t"]
+    return None
+
+
+class EarlyStop:
+    """Stop when the monitored score has not improved by ``min_delta`` for ``patience`` evals."""
+
+    def __init__(self, patience: int = 3, min_delta: float = 0.0):
+        self.patience, self.min_delta = patience, min_delta
+        self.best: Optional[float] = None
+        self.best_step = -1
+        self.bad = 0
+
+    def update(self, score: float, step: int) -> bool:
+        """Returns True when training should stop; ``improved`` tells whether to save."""
+        self.improved = self.best is None or score > self.best + self.min_delta
+        if self.improved:
+            self.best, self.best_step, self.bad = score, step, 0
+        else:
+            self.bad += 1
+        return self.bad >= self.patience
+
+
+def devices() -> List[Dict[str, Any]]:
+    """What ``ledger --devices`` prints: one row per visible GPU (read-only queries)."""
+    try:
+        import torch
+        return [{"index": i, "name": torch.cuda.get_device_name(i),
+                 "total_gib": round(torch.cuda.get_device_properties(i).total_memory / 2 ** 30, 1),
+                 "sms": torch.cuda.get_device_properties(i).multi_processor_count}
+                for i in range(torch.cuda.device_count())]
+    except Exception:  # noqa: BLE001
+        return []
