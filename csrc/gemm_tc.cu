@@ -191,7 +191,7 @@ struct GemmParams {
   int n_tiles, c_tiles, nk, kt4;
   int max_seg;
   int w_tiled; // weights stored tile-contiguous [n_tiles, nk, 128 rows, 128 B]
-  int dbg;     // timing experiments only: bit0 skip SF copies, bit1 skip MMAs, bit2 skip activation loads
+  int dbg;     // timing experiments only: bit0 skip SF copies, bit1 skip MMAs, bit2 skip activation loads, bit3 skip the epilogue body
   int split;   // 1: stream-K over (tile, k-tile) units; 0: whole tiles per CTA
   int epi;
 };
@@ -201,6 +201,72 @@ __device__ __forceinline__ int owner_of(long long unit, long long U, int G) {
   while ((long long)(i + 1) * U / G <= unit) ++i;
   while ((long long)i * U / G > unit) --i;
   return i;
+}
+
+
+// One finished (token, row) value of a whole tile.  Compile-time epilogue kind: the caller's
+// unrolled loops stay free of branches, so the few epilogue warps overlap the tokens of a chunk.
+template <int EPI>
+__device__ __forceinline__ void epi_store(const GemmParams& p, int tok, int n, int lane, float v, float res) {
+  if (EPI == EPI_SWIGLU) {
+    const float other = __shfl_xor_sync(0xffffffffu, v, 1);
+    const float y = __fdividef(v, 1.f + __expf(-v)) * other;
+    if ((lane & 1) == 0 && tok < p.tokens && n + 1 < p.N)
+      reinterpret_cast<bf16*>(p.out)[(size_t)tok * p.ldo + (n >> 1)] = __float2bfloat16(y);
+  } else {
+    v += res;
+    if (tok < p.tokens && n < p.N) {
+      if (EPI == EPI_STORE_F32)
+        reinterpret_cast<float*>(p.out)[(size_t)tok * p.ldo + n] = v;
+      else
+        reinterpret_cast<bf16*>(p.out)[(size_t)tok * p.ldo + n] = __float2bfloat16(v);
+    }
+  }
+}
+
+// Epilogue of one accumulator tile: TMEM -> registers in chunks of CH columns, J columns summed
+// per token with their activation scales, then either the final store (WHOLE) or this CTA's
+// split-K slot.  tok_first = first token of the tile; slot_row = slot + row.
+template <int BN, int J, int EPI, bool WHOLE>
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t taddr0, const float* rs_s, float ts,
+                                              int tok_first, int n, int lane, float* slot_row) {
+  constexpr int CH = BN >= 32 ? 32 : 16;
+  constexpr int TPC = CH / J;
+#pragma unroll 1
+  for (int c = 0; c < BN / CH; ++c) {
+    uint32_t r[32];
+    if (CH == 32) tc_ld32(taddr0 + (uint32_t)(c * CH), r); else tc_ld16(taddr0 + (uint32_t)(c * CH), r);
+    const int tokc = tok_first + c * TPC;
+    float res[TPC];
+#pragma unroll
+    for (int t = 0; t < TPC; ++t)   // issued before the wait and before any store of this chunk
+      res[t] = (WHOLE && EPI == EPI_RESIDUAL && tokc + t < p.tokens && n < p.N)
+                   ? __bfloat162float(p.residual[(size_t)(tokc + t) * p.ldr + n]) : 0.f;
+    tc_wait_ld();
+    float v[TPC];
+#pragma unroll
+    for (int t = 0; t < TPC; ++t) {
+      float a = 0.f;
+#pragma unroll
+      for (int j = 0; j < J; ++j) a = fmaf(__uint_as_float(r[t * J + j]), rs_s[c * CH + t * J + j], a);
+      v[t] = a * ts;
+    }
+#pragma unroll
+    for (int t = 0; t < TPC; ++t) {
+      if (WHOLE) epi_store<EPI>(p, tokc + t, n, lane, v[t], res[t]);
+      else slot_row[(size_t)(c * TPC + t) * TILE_N] = v[t];
+    }
+  }
+}
+
+template <int BN, int J>
+__device__ __forceinline__ void epilogue_dispatch(const GemmParams& p, bool whole, uint32_t taddr0, const float* rs_s,
+                                                  float ts, int tok_first, int n, int lane, float* slot_row) {
+  if (!whole) epilogue_tile<BN, J, EPI_STORE, false>(p, taddr0, rs_s, ts, tok_first, n, lane, slot_row);
+  else if (p.epi == EPI_SWIGLU) epilogue_tile<BN, J, EPI_SWIGLU, true>(p, taddr0, rs_s, ts, tok_first, n, lane, slot_row);
+  else if (p.epi == EPI_RESIDUAL) epilogue_tile<BN, J, EPI_RESIDUAL, true>(p, taddr0, rs_s, ts, tok_first, n, lane, slot_row);
+  else if (p.epi == EPI_STORE_F32) epilogue_tile<BN, J, EPI_STORE_F32, true>(p, taddr0, rs_s, ts, tok_first, n, lane, slot_row);
+  else epilogue_tile<BN, J, EPI_STORE, true>(p, taddr0, rs_s, ts, tok_first, n, lane, slot_row);
 }
 
 template <int BN>
@@ -216,7 +282,7 @@ struct Cfg {
   static constexpr int STAGES = (200 * 1024) / STAGE > 8 ? 8 : (200 * 1024) / STAGE;
   static constexpr int TMEM_COLS = BN <= 64 ? 256 : 512;
   static constexpr int SF_COL0 = BN <= 64 ? 128 : 256;
-  static constexpr int SMEM = STAGES * STAGE + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int SMEM = STAGES * STAGE + 1024 /*align*/ + 256 /*barriers*/ + 1024 /*column scales*/;
 };
 
 template <int BN>
@@ -232,6 +298,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* last_flag = const_cast<int*>(abort_flag) + 1;
+  float* rs_s = reinterpret_cast<float*>(bars) + 64;   // [BN] activation column scales of the current tile
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t bar0 = smem_u32(bars);
@@ -264,7 +331,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     const long long T = (long long)p.n_tiles * p.c_tiles;
     u0 = ((long long)blockIdx.x * T / G) * p.nk, u1 = ((long long)(blockIdx.x + 1) * T / G) * p.nk;
   }
-  const uint32_t stage_bytes = C::A_BYTES + C::B_BYTES + C::SFA_BYTES + C::SFB_BYTES;
+  const uint32_t stage_bytes = (p.dbg & 4) ? C::A_BYTES + C::SFA_BYTES : C::A_BYTES + C::B_BYTES + C::SFA_BYTES + C::SFB_BYTES;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -305,9 +372,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
           if (!ok) break;
           load_w(st_i, nt, kt);
         }
-        tma_load_2d(st + C::A_BYTES, &map_x, kt * KT_BYTES, ct * BN, full_bar(st_i));
+        if (!(p.dbg & 4)) tma_load_2d(st + C::A_BYTES, &map_x, kt * KT_BYTES, ct * BN, full_bar(st_i));
 #pragma unroll
-        for (int j = 0; j < C::SFB_ATOMS; ++j) {
+        for (int j = 0; j < C::SFB_ATOMS && !(p.dbg & 4); ++j) {
           const int atom_row = (ct * BN) / 128 + j;
           bulk_load(st + C::A_BYTES + C::B_ALLOC + C::SFA_BYTES + j * 4 * SF_ATOM,
                     p.sfx + ((size_t)(atom_row * p.kt4 + kt * 4)) * SF_ATOM, 4 * SF_ATOM, full_bar(st_i));
@@ -389,47 +456,43 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
       const int first_owner = whole ? 0 : owner_of(t_lo, U, G);
       float* tile_slots = p.partial + (size_t)tile * p.max_seg * (BN / J) * TILE_N;
       float* slot = tile_slots + (size_t)((int)blockIdx.x - first_owner) * (BN / J) * TILE_N;
+      // per-column activation scales of this tile: staged once in shared memory (while the
+      // mainloop still runs), so the value loop below has no global load between its stores
+      asm volatile("bar.sync 1, 128;" ::: "memory");   // previous tile's readers are done
+      for (int i = threadIdx.x - 64; i < BN; i += 128) {
+        const int col = ct * BN + i;
+        rs_s[i] = col < p.cols ? __ldg(p.rs + col) : 0.f;
+      }
       ok = mbar_wait(accum_full, (uint32_t)seg & 1u, abort_flag);
+      {
+        // one decision for all four epilogue warps (they meet at named barriers below), which
+        // also publishes the staged scales
+        uint32_t all;
+        asm volatile(
+            "{ .reg .pred p, q;\n"
+            "  setp.ne.u32 q, %1, 0;\n"
+            "  bar.red.and.pred p, 1, 128, q;\n"
+            "  selp.u32 %0, 1, 0, p; }\n"
+            : "=r"(all) : "r"((uint32_t)ok) : "memory");
+        ok = all != 0;
+      }
       if (!ok) break;
       tc_fence_after();
-      // finishing one (token, row) value
-      auto finish = [&](int tok, float v) {
-        if (p.epi == EPI_SWIGLU) {
-          const float other = __shfl_xor_sync(0xffffffffu, v, 1);
-          if ((lane & 1) == 0 && tok < p.tokens && n + 1 < p.N)
-            reinterpret_cast<bf16*>(p.out)[(size_t)tok * p.ldo + (n >> 1)] = __float2bfloat16(silu_f(v) * other);
-        } else if (tok < p.tokens && n < p.N) {
-          if (p.epi == EPI_RESIDUAL) v += __bfloat162float(p.residual[(size_t)tok * p.ldr + n]);
-          if (p.epi == EPI_STORE_F32)
-            reinterpret_cast<float*>(p.out)[(size_t)tok * p.ldo + n] = v;
-          else
-            reinterpret_cast<bf16*>(p.out)[(size_t)tok * p.ldo + n] = __float2bfloat16(v);
-        }
+      // finishing one (token, row) value of a split tile (run-time epilogue kind)
+      auto finish = [&](int tok, float v, float res) {
+        if (p.epi == EPI_SWIGLU) epi_store<EPI_SWIGLU>(p, tok, n, lane, v, res);
+        else if (p.epi == EPI_STORE_F32) epi_store<EPI_STORE_F32>(p, tok, n, lane, v, res);
+        else epi_store<EPI_STORE>(p, tok, n, lane, v, res);
       };
-      constexpr int CH = BN >= 32 ? 32 : 16;
-#pragma unroll 1
-      for (int c = 0; c < BN / CH; ++c) {
-        uint32_t r[32];
-        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * CH);
-        if (CH == 32) tc_ld32(taddr, r); else tc_ld16(taddr, r);
-        tc_wait_ld();
-        float v = 0.f;
-#pragma unroll
-        for (int idx = 0; idx < CH; ++idx) {  // static register indices; J divides CH
-          const int col = ct * BN + c * CH + idx;
-          const float cs = col < p.cols ? p.rs[col] : 0.f;
-          v = fmaf(__uint_as_float(r[idx]), cs, v);
-          if ((idx + 1) % J == 0) {
-            const int tok = col / J;
-            v *= ts;
-            if (whole) {
-              finish(tok, v);
-            } else {
-              slot[(size_t)(tok - tok0) * TILE_N + row] = v;
-            }
-            v = 0.f;
-          }
-        }
+      auto load_res = [&](int tok) -> float {
+        return (p.epi == EPI_RESIDUAL && tok < p.tokens && n < p.N)
+                   ? __bfloat162float(p.residual[(size_t)tok * p.ldr + n]) : 0.f;
+      };
+      if (!(p.dbg & 8)) {
+        const uint32_t taddr0 = tmem_base + ((uint32_t)(quad * 32) << 16);
+        if (J == 4) epilogue_dispatch<BN, 4>(p, whole, taddr0, rs_s, ts, tok0, n, lane, slot + row);
+        else if (J == 2) epilogue_dispatch<BN, 2>(p, whole, taddr0, rs_s, ts, tok0, n, lane, slot + row);
+        else epilogue_dispatch<BN, 1>(p, whole, taddr0, rs_s, ts, tok0, n, lane, slot + row);
       }
       tc_fence_before();
       mbar_arrive(accum_empty);
@@ -446,17 +509,29 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (*last_flag) {
           __threadfence();
-          for (int g = 0; g < BN / J; ++g) {
-            float part[8];
+          constexpr int GB = 4;   // tokens per batch: 4 x 8 slot loads + 4 residual loads in flight
+          for (int g0 = 0; g0 < BN / J; g0 += GB) {
+            float part[GB][8], res[GB];
 #pragma unroll
-            for (int sg = 0; sg < 8; ++sg)   // issue every load before the first use
-              part[sg] = sg < nseg ? __ldcg(tile_slots + ((size_t)sg * (BN / J) + g) * TILE_N + row) : 0.f;
-            float v = 0.f;
+            for (int gi = 0; gi < GB; ++gi) {
+              const int g = g0 + gi;
 #pragma unroll
-            for (int sg = 0; sg < 8; ++sg) v += part[sg];   // fixed order: bitwise reproducible
-            for (int sg = 8; sg < nseg; ++sg)
-              v += __ldcg(tile_slots + ((size_t)sg * (BN / J) + g) * TILE_N + row);
-            finish(tok0 + g, v);
+              for (int sg = 0; sg < 8; ++sg)
+                part[gi][sg] = (sg < nseg && g < BN / J)
+                                   ? __ldcg(tile_slots + ((size_t)sg * (BN / J) + g) * TILE_N + row) : 0.f;
+              res[gi] = g < BN / J ? load_res(tok0 + g) : 0.f;
+            }
+#pragma unroll
+            for (int gi = 0; gi < GB; ++gi) {
+              const int g = g0 + gi;
+              if (g >= BN / J) break;
+              float v = 0.f;
+#pragma unroll
+              for (int sg = 0; sg < 8; ++sg) v += part[gi][sg];   // fixed order: bitwise reproducible
+              for (int sg = 8; sg < nseg; ++sg)
+                v += __ldcg(tile_slots + ((size_t)sg * (BN / J) + g) * TILE_N + row);
+              finish(tok0 + g, v, res[gi]);
+            }
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");

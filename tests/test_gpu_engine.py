@@ -76,3 +76,56 @@ def test_prefix_hit_on_gpu(setup):
     cold = eng.generate([p], SamplingParams(max_tokens=6))[0]
     warm = eng.generate([p], SamplingParams(max_tokens=6))[0]
     assert warm.tokens == cold.tokens and warm.cached_tokens == 48
+
+
+def test_spec_decode_matches_plain_on_gpu(setup):
+    """Verify ticks (W-wide attention + per-step GDN planes) commit exactly the plain greedy
+    tokens, for a drafter that is always right, one that never is, and a random block drafter."""
+    from tilerl_b200.engine import SamplingParams
+    from tilerl_b200.factory import build_engine
+    from tilerl_b200.spec import BlockDrafter, BlockDrafterConfig, ConstantDrafter, OracleDrafter
+    cfg, ops, model = setup
+    prompts = _prompts(cfg, 2, 30, 11)
+    sp = SamplingParams(max_tokens=14)
+    plain = build_engine(model, ops, slots=4, max_ctx=256, graph=False, prefix=False)
+    want = [r.tokens for r in plain.generate(prompts, sp)]
+    oracle = OracleDrafter({tuple(p): w for p, w in zip(prompts, want)})
+    for drafter in (oracle, ConstantDrafter(3), BlockDrafter(model, BlockDrafterConfig(width=4, n_heads=4, n_kv_heads=2))):
+        eng = build_engine(model, ops, slots=4, max_ctx=256, graph=False, prefix=False, spec_width=4, drafter=drafter)
+        got = [r.tokens for r in eng.generate(prompts, sp)]
+        assert got == want, type(drafter).__name__
+    assert eng.stats()["spec_drafted"] > 0
+
+
+def test_sparse_decode_runs_on_gpu(setup):
+    """Top-k page selection with k >= pages is exactly dense; with a small k it still runs the
+    packed table through the same kernel and stays finite."""
+    from tilerl_b200.engine import SamplingParams
+    from tilerl_b200.factory import build_engine
+    from tilerl_b200.sparse import SparseConfig, SparseKV
+    cfg, ops, model = setup
+    p = _prompts(cfg, 1, 200, 13)
+    sp = SamplingParams(max_tokens=8)
+    dense = build_engine(model, ops, slots=2, max_ctx=512, graph=False, prefix=False)
+    want = dense.generate(p, sp)[0].tokens
+    full = SparseKV(cfg, SparseConfig(top_k=64, window=2, refresh_ticks=2, min_tokens=64))
+    eng = build_engine(model, ops, slots=2, max_ctx=512, graph=False, prefix=False, sparse=full)
+    assert eng.generate(p, sp)[0].tokens == want
+    assert full.stats["sparse_ticks"] > 0
+    small = SparseKV(cfg, SparseConfig(top_k=3, window=2, refresh_ticks=2, min_tokens=64))
+    eng = build_engine(model, ops, slots=2, max_ctx=512, graph=False, prefix=False, sparse=small)
+    got = eng.generate(p, sp)[0].tokens
+    assert len(got) == 8 and small.stats["sparse_ticks"] > 0
+
+
+def test_seeded_sampling_is_reproducible_on_gpu(setup):
+    from tilerl_b200.engine import SamplingParams
+    from tilerl_b200.factory import build_engine
+    cfg, ops, model = setup
+    p = _prompts(cfg, 2, 20, 17)
+    sp = SamplingParams(max_tokens=10, temperature=1.0, top_p=0.9, top_k=50, seed=5, logprobs=True)
+    eng = build_engine(model, ops, slots=4, max_ctx=256, graph=False, prefix=False)
+    a = eng.generate(p, sp)
+    b = eng.generate(p, sp)
+    assert [r.tokens for r in a] == [r.tokens for r in b]
+    assert all(len(r.logprobs) == len(r.tokens) and all(l <= 0 for l in r.logprobs) for r in a)
