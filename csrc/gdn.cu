@@ -20,6 +20,8 @@
 // Reference parity: kernels_gdn.py:21-126 (prep), :539-744 (fused decode), :746-939
 // (serial-scan prefill) of packages/tilerl-kernels/src/tilerl_kernels; maths
 // reference.py:1142-1277.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace {
@@ -209,6 +211,210 @@ gdn_recur_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
   }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Column-sliced scan.  The delta rule never mixes state columns, so one (sequence, value
+// head) is cut into D/32 CTAs of 32 columns each; a warp owns 4 columns and its lanes split
+// the dk rows in eight groups (lane = group * 4 + column), so a step needs two 3-level
+// shuffles and no block barrier; eight warps per CTA keep every scheduler busy while each
+// warp waits on its own dependent FMA chain.  q / k / v / gates of 16 tokens at a time are staged in
+// shared memory with cp.async one chunk ahead, so no step waits on global memory.  The raw
+// outputs of a chunk go out coalesced; the last CTA of a head to finish (device counter)
+// runs the gated RMSNorm over the whole head.
+constexpr int SCAN_TC = 16;
+constexpr int GDN_DONE_CAP = 16384;
+__device__ int g_gdn_done[GDN_DONE_CAP];   // [seq * nv + head] arrival counters, self-resetting
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int D>
+__global__ void __launch_bounds__(256)
+gdn_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
+                const float* __restrict__ vc, const float* __restrict__ gin,
+                const float* __restrict__ bin, const bf16* __restrict__ inp, int ld,
+                float* __restrict__ states, int* __restrict__ cur, bf16* __restrict__ ring,
+                const int* __restrict__ q_start, const int* __restrict__ q_len,
+                const int* __restrict__ positions, const int* __restrict__ state_slots,
+                const int* __restrict__ keep_flags, long state_slot_stride, long plane_stride,
+                long ring_slot_stride, const float* __restrict__ norm_w, float eps,
+                float* __restrict__ o_scratch, bf16* __restrict__ out, int nk, int nv, int planes) {
+  constexpr int Q = 8;            // row groups (lanes that share a column)
+  constexpr int R = D / Q;        // state rows per thread
+  constexpr int NS = D / 32;      // column slices (CTAs) per head
+  constexpr int KP = R + 4;       // padded group stride: the eight groups hit different banks
+  constexpr int NT = 256, NW = NT / 32, CW = 32 / Q;   // threads, warps, columns per warp
+  constexpr int TC = SCAN_TC;
+  __shared__ __align__(16) float s_q[2][TC][Q * KP];
+  __shared__ __align__(16) float s_k[2][TC][Q * KP];
+  __shared__ __align__(16) float s_v[2][TC][32];
+  __shared__ float s_g[2][TC], s_b[2][TC], s_qk[2][TC];
+  __shared__ __align__(16) float s_o[TC][32];
+  __shared__ int s_last;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int h = blockIdx.x / NS, slice = blockIdx.x % NS, seq = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int r = lane / CW, cl = warp * CW + (lane % CW), col = slice * 32 + cl;
+  const int T = q_len[seq], t0 = q_start[seq];
+  if (T == 0) return;
+  const int slot = state_slots[seq];
+  const int keep = keep_flags ? keep_flags[seq] : 0;
+  const int kh = h * nk / nv;
+  const int live = cur[slot];
+  float* sbase = states + (size_t)slot * state_slot_stride + (size_t)h * D * D;
+  const float* sin_ = sbase + (size_t)live * plane_stride;
+  float S[R];
+#pragma unroll
+  for (int j = 0; j < R; ++j) S[j] = sin_[(size_t)(r * R + j) * D + col];
+
+  auto stage = [&](int i0, int b) {
+    const int n = min(TC, T - i0);
+    // q and k rows: D/4 pieces of 16 B per token each; v: 8 pieces; gates: scalars
+    for (int x = tid; x < n * (D / 4); x += NT) {
+      const int tt = x / (D / 4), pc = x % (D / 4);
+      const int e = pc * 4, dst = (e / R) * KP + (e % R);
+      const size_t src = ((size_t)(t0 + i0 + tt) * nk + kh) * D + e;
+      cp_async16(&s_q[b][tt][dst], qn + src);
+      cp_async16(&s_k[b][tt][dst], kn + src);
+    }
+    for (int x = tid; x < n * 8; x += NT) {
+      const int tt = x >> 3, pc = x & 7;
+      cp_async16(&s_v[b][tt][pc * 4], vc + ((size_t)(t0 + i0 + tt) * nv + h) * D + slice * 32 + pc * 4);
+    }
+    if (tid < n) {
+      s_g[b][tid] = gin[(size_t)(t0 + i0 + tid) * nv + h];
+      s_b[b][tid] = bin[(size_t)(t0 + i0 + tid) * nv + h];
+    }
+    cp_async_commit();
+  };
+
+  stage(0, 0);
+  int b = 0;
+  for (int i0 = 0; i0 < T; i0 += TC, b ^= 1) {
+    const int n = min(TC, T - i0);
+    cp_async_wait<0>();
+    __syncthreads();                       // chunk b landed; every thread left the previous chunk
+    if (i0 > 0) {                          // raw outputs of the previous chunk, 128 B rows
+      const int pn = TC;
+      for (int x = tid; x < pn * 32; x += NT)
+        o_scratch[((size_t)(t0 + i0 - TC + (x >> 5)) * nv + h) * D + slice * 32 + (x & 31)] = s_o[x >> 5][x & 31];
+    }
+    if (i0 + TC < T) stage(i0 + TC, b ^ 1);
+    for (int tt = warp; tt < n; tt += NW) { // q.k of this chunk's tokens
+      float a = 0.f;
+      for (int e = lane; e < D; e += 32) {
+        const int o = (e / R) * KP + (e % R);
+        a = fmaf(s_q[b][tt][o], s_k[b][tt][o], a);
+      }
+      a = warp_sum(a);
+      if (lane == 0) s_qk[b][tt] = a;
+    }
+    __syncthreads();                       // s_qk visible, s_o flushed
+    for (int tt = 0; tt < n; ++tt) {
+      const float eg = __expf(s_g[b][tt]), beta = s_b[b][tt], v = s_v[b][tt][cl], qk = s_qk[b][tt];
+      const float4* k4 = reinterpret_cast<const float4*>(&s_k[b][tt][r * KP]);
+      const float4* q4 = reinterpret_cast<const float4*>(&s_q[b][tt][r * KP]);
+      float kreg[R];
+      float ks0 = 0.f, ks1 = 0.f, qs0 = 0.f, qs1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < R / 4; ++j) {
+        const float4 kk = k4[j], qq = q4[j];
+        kreg[4 * j] = kk.x, kreg[4 * j + 1] = kk.y, kreg[4 * j + 2] = kk.z, kreg[4 * j + 3] = kk.w;
+        ks0 = fmaf(kk.x, S[4 * j], ks0), ks1 = fmaf(kk.y, S[4 * j + 1], ks1);
+        ks0 = fmaf(kk.z, S[4 * j + 2], ks0), ks1 = fmaf(kk.w, S[4 * j + 3], ks1);
+        qs0 = fmaf(qq.x, S[4 * j], qs0), qs1 = fmaf(qq.y, S[4 * j + 1], qs1);
+        qs0 = fmaf(qq.z, S[4 * j + 2], qs0), qs1 = fmaf(qq.w, S[4 * j + 3], qs1);
+      }
+      float ks = ks0 + ks1, qs = qs0 + qs1;
+#pragma unroll
+      for (int m = CW; m < 32; m <<= 1) {
+        ks += __shfl_xor_sync(0xffffffffu, ks, m);
+        qs += __shfl_xor_sync(0xffffffffu, qs, m);
+      }
+      const float d = beta * (v - eg * ks);
+#pragma unroll
+      for (int j = 0; j < R; ++j) S[j] = fmaf(kreg[j], d, eg * S[j]);
+      if (r == 0) s_o[tt][cl] = fmaf(eg, qs, qk * d);
+      if (keep && i0 + tt < planes) {
+        float* sp = sbase + (size_t)(i0 + tt) * plane_stride;
+#pragma unroll
+        for (int j = 0; j < R; ++j) sp[(size_t)(r * R + j) * D + col] = S[j];
+      }
+    }
+  }
+  __syncthreads();
+  {                                        // raw outputs of the last chunk
+    const int i0 = ((T - 1) / TC) * TC, n = T - i0;
+    for (int x = tid; x < n * 32; x += NT)
+      o_scratch[((size_t)(t0 + i0 + (x >> 5)) * nv + h) * D + slice * 32 + (x & 31)] = s_o[x >> 5][x & 31];
+  }
+  if (!keep) {
+    float* sp = sbase + (size_t)live * plane_stride;
+#pragma unroll
+    for (int j = 0; j < R; ++j) sp[(size_t)(r * R + j) * D + col] = S[j];
+  }
+  const int C = 2 * nk * D + nv * D;
+  if (slice == 0) {
+    // ring refresh: raw q/k rows by the first value head of each key head, v rows by every
+    // head, for the last min(T, RING) tokens of the tick
+    bf16* rg = ring + (size_t)slot * ring_slot_stride;
+    const int first = max(0, T - RING);
+    const int rep = nv / nk;
+    for (int i = first; i < T; ++i) {
+      const int t = t0 + i;
+      const int rrow = positions[t] % RING;
+      const bf16* src = inp + (size_t)t * ld;
+      bf16* dst = rg + (size_t)rrow * C;
+      if (h % rep == 0) {
+        for (int c = tid; c < 2 * D; c += NT) {
+          const int cc = (c < D) ? kh * D + c : nk * D + kh * D + (c - D);
+          dst[cc] = src[cc];
+        }
+      }
+      for (int c = tid; c < D; c += NT) {
+        const int cc = 2 * nk * D + h * D + c;
+        dst[cc] = src[cc];
+      }
+    }
+  }
+  // the last slice of this head to get here normalises the head
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    int* ctr = g_gdn_done + (size_t)seq * nv + h;
+    const int prev = atomicAdd(ctr, 1);
+    s_last = (prev == NS - 1);
+    if (prev == NS - 1) *ctr = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int i = warp; i < T; i += NW) {     // gated RMSNorm per token, one warp per token
+    const int t = t0 + i;
+    const float* o = o_scratch + ((size_t)t * nv + h) * D;
+    float ov[D / 32], ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < D / 32; ++j) {
+      ov[j] = __ldcg(o + lane + 32 * j);
+      ss += ov[j] * ov[j];
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)D + eps);
+    const bf16* z = inp + (size_t)t * ld + C + (size_t)h * D;
+#pragma unroll
+    for (int j = 0; j < D / 32; ++j) {
+      const int c = lane + 32 * j;
+      out[((size_t)t * nv + h) * D + c] =
+          __float2bfloat16(ov[j] * rstd * norm_w[c] * silu_f(__bfloat162float(z[c])));
+    }
+  }
+}
+
 }  // namespace
 
 // Scratch (fp32): qn, kn [T*nk*D]; vc, o_scratch [T*nv*D]; g, beta [T*nv].
@@ -233,9 +439,19 @@ TRL_API int trl_gdn(const void* inp, int ld, const void* conv_w, const void* dt_
                  (const int*)q_len, (const int*)positions, (const int*)state_slots,                 \
                  (const int*)keep_flags, state_slot_stride, plane_stride, ring_slot_stride,         \
                  (const float*)norm_w, eps, (float*)o_scratch, (bf16*)out, nk, nv, planes)
-  if (D == 128) RECUR(128);
-  else if (D == 64) RECUR(64);
+#define SCAN(DD)                                                                                    \
+  e = trl_launch(gdn_scan_kernel<DD>, dim3(nv * (DD / 32), B), dim3(256), 0, st, (const float*)qn,  \
+                 (const float*)kn, (const float*)vc, (const float*)g, (const float*)beta,           \
+                 (const bf16*)inp, ld, (float*)states, (int*)cur, (bf16*)ring, (const int*)q_start, \
+                 (const int*)q_len, (const int*)positions, (const int*)state_slots,                 \
+                 (const int*)keep_flags, state_slot_stride, plane_stride, ring_slot_stride,         \
+                 (const float*)norm_w, eps, (float*)o_scratch, (bf16*)out, nk, nv, planes)
+  static const bool legacy = getenv("TRL_GDN_LEGACY") != nullptr;
+  const bool scan = !legacy && (long)B * nv <= GDN_DONE_CAP;
+  if (D == 128) { if (scan) SCAN(128); else RECUR(128); }
+  else if (D == 64) { if (scan) SCAN(64); else RECUR(64); }
   else return (int)cudaErrorInvalidValue;
 #undef RECUR
+#undef SCAN
   return (int)e;
 }

@@ -193,6 +193,7 @@ struct GemmParams {
   int w_tiled; // weights stored tile-contiguous [n_tiles, nk, 128 rows, 128 B]
   int dbg;     // timing experiments only: bit0 skip SF copies, bit1 skip MMAs, bit2 skip activation loads, bit3 skip the epilogue body
   int split;   // 1: stream-K over (tile, k-tile) units; 0: whole tiles per CTA
+  int sa, sb;  // stages of the weight ring and of the activation ring
   int epi;
 };
 
@@ -277,12 +278,19 @@ struct Cfg {
   static constexpr int B_ALLOC = (B_BYTES + 1023) / 1024 * 1024;
   static constexpr int SFA_BYTES = 4 * SF_ATOM;
   static constexpr int SFB_BYTES = SFB_ATOMS * 4 * SF_ATOM;
-  static constexpr int STAGE = A_BYTES + B_ALLOC + SFA_BYTES + SFB_BYTES;
-  // as many stages as fit: the weight stream is latency-bound below ~150 KB in flight per SM
-  static constexpr int STAGES = (200 * 1024) / STAGE > 8 ? 8 : (200 * 1024) / STAGE;
+  // Two rings: the weight tile + its scales (A stage) and the activation tile + its scales
+  // (B stage).  The weight stream needs many loads in flight (load latency ~2 us), so it gets
+  // most of the shared memory; the stage counts are launch parameters.
+  static constexpr int A_STAGE = A_BYTES + SFA_BYTES;
+  static constexpr int B_STAGE = B_ALLOC + SFB_BYTES;
+  static constexpr int MAX_STAGES = 8;
+  static constexpr int RING_BYTES = 216 * 1024;
+  static constexpr int BAR_BYTES = 512;
   static constexpr int TMEM_COLS = BN <= 64 ? 256 : 512;
   static constexpr int SF_COL0 = BN <= 64 ? 128 : 256;
-  static constexpr int SMEM = STAGES * STAGE + 1024 /*align*/ + 256 /*barriers*/ + 1024 /*column scales*/;
+  static constexpr int smem_bytes(int sa, int sb) {
+    return sa * A_STAGE + sb * B_STAGE + 1024 /*align*/ + BAR_BYTES + 1024 /*column scales*/;
+  }
 };
 
 template <int BN>
@@ -290,24 +298,31 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                   const GemmParams p) {
   using C = Cfg<BN>;
-  constexpr int S = C::STAGES;
+  constexpr int MS = C::MAX_STAGES;
+  const int SA = p.sa, SB = p.sb;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)S * C::STAGE);
-  // bars[0..S) full, [S..2S) empty, [2S] accum_full, [2S+1] accum_empty
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 2);
+  unsigned char* smem_b = smem + (size_t)SA * C::A_STAGE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_b + (size_t)SB * C::B_STAGE);
+  // bars: [0,MS) full_a, [MS,2MS) empty_a, [2MS,3MS) full_b, [3MS,4MS) empty_b, accum_full, accum_empty
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * MS + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* last_flag = const_cast<int*>(abort_flag) + 1;
-  float* rs_s = reinterpret_cast<float*>(bars) + 64;   // [BN] activation column scales of the current tile
+  float* rs_s = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(bars) + C::BAR_BYTES);  // [BN] column scales
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t bar0 = smem_u32(bars);
-  auto full_bar = [&](int s) { return bar0 + 8u * s; };
-  auto empty_bar = [&](int s) { return bar0 + 8u * (S + s); };
-  const uint32_t accum_full = bar0 + 8u * (2 * S), accum_empty = bar0 + 8u * (2 * S + 1);
+  auto full_a = [&](int s) { return bar0 + 8u * s; };
+  auto empty_a = [&](int s) { return bar0 + 8u * (MS + s); };
+  auto full_b = [&](int s) { return bar0 + 8u * (2 * MS + s); };
+  auto empty_b = [&](int s) { return bar0 + 8u * (3 * MS + s); };
+  const uint32_t accum_full = bar0 + 8u * (4 * MS), accum_empty = bar0 + 8u * (4 * MS + 1);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < S; ++s) mbar_init(full_bar(s), 1), mbar_init(empty_bar(s), 1);
+    for (int s = 0; s < MS; ++s) {
+      mbar_init(full_a(s), 1), mbar_init(empty_a(s), 1);
+      mbar_init(full_b(s), 1), mbar_init(empty_b(s), 1);
+    }
     mbar_init(accum_full, 1);
     mbar_init(accum_empty, 128);
     *abort_flag = 0;
@@ -331,59 +346,64 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     const long long T = (long long)p.n_tiles * p.c_tiles;
     u0 = ((long long)blockIdx.x * T / G) * p.nk, u1 = ((long long)(blockIdx.x + 1) * T / G) * p.nk;
   }
-  const uint32_t stage_bytes = (p.dbg & 4) ? C::A_BYTES + C::SFA_BYTES : C::A_BYTES + C::B_BYTES + C::SFA_BYTES + C::SFB_BYTES;
+  const uint32_t a_tx = C::A_BYTES + C::SFA_BYTES, b_tx = C::B_BYTES + C::SFB_BYTES;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      // running (tile, k-tile) coordinates: no division on the per-unit path
       const int n_units = (int)(u1 - u0);
-      int tile0 = (int)(u0 / p.nk), kt = (int)(u0 % p.nk);
-      int nt = tile0 / p.c_tiles, ct = tile0 % p.c_tiles;
-      const uint32_t smem0 = smem_u32(smem);
-      auto load_w = [&](int s_, int nt_, int kt_) {
-        const uint32_t st = smem0 + (uint32_t)s_ * C::STAGE;
-        mbar_expect_tx(full_bar(s_), stage_bytes);
-        tma_load_2d(st, &map_w, p.w_tiled ? 0 : kt_ * KT_BYTES,
-                    p.w_tiled ? (nt_ * p.nk + kt_) * TILE_N : nt_ * TILE_N, full_bar(s_));
-        bulk_load(st + C::A_BYTES + C::B_ALLOC, p.sfw + ((size_t)(nt_ * p.kt4 + kt_ * 4)) * SF_ATOM, C::SFA_BYTES,
-                  full_bar(s_));
-      };
-      // prologue: weight tiles of the first S units do not depend on the previous kernel
-      const int pre = min(S, n_units);
-      {
-        int nt_ = nt, ct_ = ct, kt_ = kt;
-        for (int i = 0; i < pre; ++i) {
-          load_w(i, nt_, kt_);
-          if (++kt_ == p.nk) {
-            kt_ = 0;
-            if (++ct_ == p.c_tiles) ct_ = 0, ++nt_;
-          }
+      const uint32_t smem_a0 = smem_u32(smem), smem_b0 = smem_u32(smem_b);
+      // two cursors over the same unit sequence: weights run up to SA units ahead of the MMA,
+      // activations up to SB; running (tile, k-tile) coordinates, no division per unit
+      struct Cur { int nt, ct, kt, st; uint32_t ph; };
+      auto advance = [&](Cur& c, int ring) {
+        if (++c.kt == p.nk) {
+          c.kt = 0;
+          if (++c.ct == p.c_tiles) c.ct = 0, ++c.nt;
         }
-      }
+        if (++c.st == ring) c.st = 0, c.ph ^= 1u;
+      };
+      const int tile0 = (int)(u0 / p.nk);
+      Cur ca{tile0 / p.c_tiles, tile0 % p.c_tiles, (int)(u0 % p.nk), 0, 0u};
+      Cur cb = ca;
+      auto load_a = [&](const Cur& c) {
+        const uint32_t st = smem_a0 + (uint32_t)c.st * C::A_STAGE;
+        mbar_expect_tx(full_a(c.st), a_tx);
+        tma_load_2d(st, &map_w, p.w_tiled ? 0 : c.kt * KT_BYTES,
+                    p.w_tiled ? (c.nt * p.nk + c.kt) * TILE_N : c.nt * TILE_N, full_a(c.st));
+        bulk_load(st + C::A_BYTES, p.sfw + ((size_t)(c.nt * p.kt4 + c.kt * 4)) * SF_ATOM, C::SFA_BYTES, full_a(c.st));
+      };
+      auto load_b = [&](const Cur& c) {
+        const uint32_t st = smem_b0 + (uint32_t)c.st * C::B_STAGE;
+        mbar_expect_tx(full_b(c.st), b_tx);
+        tma_load_2d(st, &map_x, c.kt * KT_BYTES, c.ct * BN, full_b(c.st));
+#pragma unroll
+        for (int j = 0; j < C::SFB_ATOMS; ++j) {
+          const int atom_row = (c.ct * BN) / 128 + j;
+          bulk_load(st + C::B_ALLOC + j * 4 * SF_ATOM, p.sfx + ((size_t)(atom_row * p.kt4 + c.kt * 4)) * SF_ATOM,
+                    4 * SF_ATOM, full_b(c.st));
+        }
+      };
+      // prologue: the first SA weight tiles do not depend on the previous kernel
+      int a_issued = 0, b_issued = 0;
+      for (; a_issued < min(SA, n_units); ++a_issued) load_a(ca), advance(ca, SA);
       pdl_wait();
       bool ok = true;
-      int st_i = 0;
-      uint32_t st_ph = 0;
-      for (int it = 0; ok && it < n_units; ++it) {
-        const uint32_t st = smem0 + (uint32_t)st_i * C::STAGE;
-        if (it >= pre) {
-          ok = mbar_wait(empty_bar(st_i), st_ph ^ 1u, abort_flag);
+      while (ok && b_issued < n_units) {
+        if (b_issued >= SB) ok = mbar_wait(empty_b(cb.st), cb.ph ^ 1u, abort_flag);
+        if (!ok) break;
+        load_b(cb), advance(cb, SB), ++b_issued;
+        // weight unit (b_issued - 1 + SA) may go once the MMA of unit (b_issued - 1) has retired
+        if (a_issued < n_units && a_issued < b_issued + SA - 1) {
+          ok = mbar_wait(empty_a(ca.st), ca.ph ^ 1u, abort_flag);
           if (!ok) break;
-          load_w(st_i, nt, kt);
+          load_a(ca), advance(ca, SA), ++a_issued;
         }
-        if (!(p.dbg & 4)) tma_load_2d(st + C::A_BYTES, &map_x, kt * KT_BYTES, ct * BN, full_bar(st_i));
-#pragma unroll
-        for (int j = 0; j < C::SFB_ATOMS && !(p.dbg & 4); ++j) {
-          const int atom_row = (ct * BN) / 128 + j;
-          bulk_load(st + C::A_BYTES + C::B_ALLOC + C::SFA_BYTES + j * 4 * SF_ATOM,
-                    p.sfx + ((size_t)(atom_row * p.kt4 + kt * 4)) * SF_ATOM, 4 * SF_ATOM, full_bar(st_i));
-        }
-        if (++kt == p.nk) {
-          kt = 0;
-          if (++ct == p.c_tiles) ct = 0, ++nt;
-        }
-        if (++st_i == S) st_i = 0, st_ph ^= 1u;
+      }
+      while (ok && a_issued < n_units) {   // not reached when SA <= n_units bookkeeping holds; kept for safety
+        ok = mbar_wait(empty_a(ca.st), ca.ph ^ 1u, abort_flag);
+        if (!ok) break;
+        load_a(ca), advance(ca, SA), ++a_issued;
       }
     }
   } else if (warp == 1) {
@@ -392,14 +412,14 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     if (lane == 0) {
       constexpr uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TILE_N >> 4) << 24);
       long long u = u0;
-      int it = 0, seg = 0, st_i = 0;
-      uint32_t st_ph = 0;
+      int it = 0, seg = 0, sa_i = 0, sb_i = 0;
+      uint32_t sa_ph = 0, sb_ph = 0;
       bool ok = true;
       // descriptor words of stage 0 / k-block 0; everything else is an affine offset
-      const uint64_t d_a = desc_sw128(smem_u32(smem)), d_b = desc_sw128(smem_u32(smem + C::A_BYTES));
-      const uint64_t d_sfa = desc_sf(smem_u32(smem + C::A_BYTES + C::B_ALLOC));
+      const uint64_t d_a = desc_sw128(smem_u32(smem)), d_b = desc_sw128(smem_u32(smem_b));
+      const uint64_t d_sfa = desc_sf(smem_u32(smem + C::A_BYTES)), d_sfb = desc_sf(smem_u32(smem_b + C::B_ALLOC));
       const uint32_t a_lo = (uint32_t)d_a, b_lo = (uint32_t)d_b, op_hi = (uint32_t)(d_a >> 32);
-      const uint32_t sfa_lo = (uint32_t)d_sfa, sfb_lo = sfa_lo + (C::SFA_BYTES >> 4), sf_hi = (uint32_t)(d_sfa >> 32);
+      const uint32_t sfa_lo = (uint32_t)d_sfa, sfb_lo = (uint32_t)d_sfb, sf_hi = (uint32_t)(d_sfa >> 32);
       while (ok && u < u1) {
         const int k0 = (int)(u % p.nk);
         const int len = (int)min((long long)(p.nk - k0), u1 - u);
@@ -409,24 +429,27 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
           tc_fence_after();
         }
         for (int i = 0; ok && i < len; ++i, ++it) {
-          ok = mbar_wait(full_bar(st_i), st_ph, abort_flag);
+          ok = mbar_wait(full_a(sa_i), sa_ph, abort_flag) && mbar_wait(full_b(sb_i), sb_ph, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t soff = (uint32_t)st_i * (uint32_t)(C::STAGE >> 4);
+          const uint32_t aoff = (uint32_t)sa_i * (uint32_t)(C::A_STAGE >> 4);
+          const uint32_t boff = (uint32_t)sb_i * (uint32_t)(C::B_STAGE >> 4);
           const uint32_t sf_cols = tmem_base + C::SF_COL0 + (uint32_t)(it & 1) * 64;  // double-buffered by parity
 #pragma unroll
           for (int kb = 0; kb < 4 && !(p.dbg & 1); ++kb) {
-            tc_cp_sf_lh(sf_cols + kb * 4, sfa_lo + soff + kb * (SF_ATOM >> 4), sf_hi);
+            tc_cp_sf_lh(sf_cols + kb * 4, sfa_lo + aoff + kb * (SF_ATOM >> 4), sf_hi);
 #pragma unroll
             for (int j = 0; j < C::SFB_ATOMS; ++j)
-              tc_cp_sf_lh(sf_cols + 16 + kb * 8 + j * 4, sfb_lo + soff + (j * 4 + kb) * (SF_ATOM >> 4), sf_hi);
+              tc_cp_sf_lh(sf_cols + 16 + kb * 8 + j * 4, sfb_lo + boff + (j * 4 + kb) * (SF_ATOM >> 4), sf_hi);
           }
 #pragma unroll
           for (int kb = 0; kb < 4 && !(p.dbg & 2); ++kb)
-            tc_mma_nvfp4_lh(tmem_base, a_lo + soff + kb * 2, b_lo + soff + kb * 2, op_hi, idesc, sf_cols + kb * 4,
+            tc_mma_nvfp4_lh(tmem_base, a_lo + aoff + kb * 2, b_lo + boff + kb * 2, op_hi, idesc, sf_cols + kb * 4,
                             sf_cols + 16 + kb * 8, (i | kb) ? 1u : 0u);
-          tc_commit(empty_bar(st_i));
-          if (++st_i == S) st_i = 0, st_ph ^= 1u;
+          tc_commit(empty_a(sa_i));
+          tc_commit(empty_b(sb_i));
+          if (++sa_i == SA) sa_i = 0, sa_ph ^= 1u;
+          if (++sb_i == SB) sb_i = 0, sb_ph ^= 1u;
         }
         if (ok) tc_commit(accum_full);
         u += len;
@@ -689,14 +712,27 @@ int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t row_bytes
 }
 
 template <int BN>
-int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, int grid, cudaStream_t st) {
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, int grid, cudaStream_t st) {
+  using C = Cfg<BN>;
   auto kern = gemm_nvfp4_kernel<BN>;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM) != cudaSuccess) return 3;
-    configured = true;
+  // default split of the ring budget: weights first (up to 8 stages, at least 2 activation stages)
+  int sb_min = 2;
+  int sa = (C::RING_BYTES - sb_min * C::B_STAGE) / C::A_STAGE;
+  sa = sa > C::MAX_STAGES ? C::MAX_STAGES : sa;
+  int sb = (C::RING_BYTES - sa * C::A_STAGE) / C::B_STAGE;
+  sb = sb > C::MAX_STAGES ? C::MAX_STAGES : sb;
+  if (const char* e = getenv("TRL_GEMM_SA")) sa = atoi(e);
+  if (const char* e = getenv("TRL_GEMM_SB")) sb = atoi(e);
+  if (sa < 1 || sb < 1 || sa > C::MAX_STAGES || sb > C::MAX_STAGES || C::smem_bytes(sa, sb) > 227 * 1024)
+    return (int)cudaErrorInvalidValue;
+  p.sa = sa, p.sb = sb;
+  static int configured = 0;
+  const int smem = C::smem_bytes(sa, sb);
+  if (configured < smem) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return 3;
+    configured = smem;
   }
-  return (int)trl_launch(kern, dim3(grid), dim3(GEMM_THREADS), (size_t)Cfg<BN>::SMEM, st, mw, mx, p);
+  return (int)trl_launch(kern, dim3(grid), dim3(GEMM_THREADS), (size_t)smem, st, mw, mx, p);
 }
 
 }  // namespace
