@@ -19,6 +19,8 @@
 //
 // Reference parity: `linear_fp4_gemv` / `linear_bf16_gemv` of
 // packages/tilerl-kernels/src/tilerl_kernels/kernels_linear.py:924-1097.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 __device__ TrlError g_trl_error = {0, 0, 0, 0};
@@ -246,6 +248,195 @@ gemv_nvfp4_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict
   }
 }
 
+// Balanced variant.  A CTA owns a contiguous block of row PAIRS and its 16 warps split that
+// block's (pair, 32-chunk step) units evenly, whatever the row count: a 5120-row projection
+// on 148 x 16 warps no longer runs two rounds with the second almost empty.  A pair that is
+// cut between warps is summed through shared-memory slots in a fixed order (bitwise
+// reproducible); the epilogue then runs block-wide with coalesced stores.
+__device__ __forceinline__ int sk_owner(int unit, int U, int W) {
+  int w = (int)(((long long)unit * W) / U);
+  while (w + 1 < W && (int)(((long long)(w + 1) * U) / W) <= unit) ++w;
+  while (w > 0 && (int)(((long long)w * U) / W) > unit) --w;
+  return w;
+}
+
+template <int M, int EPI>
+__global__ void __launch_bounds__(GEMV_THREADS, 1)
+gemv_nvfp4_sk_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ wq,
+                     const uint8_t* __restrict__ wscale, const float* __restrict__ tscale,
+                     const float* __restrict__ norm_w, float eps, const bf16* __restrict__ residual,
+                     int ldr, void* __restrict__ yout, int ldy, int N, int K, int nslot,
+                     const TrlPushArgs push) {
+  constexpr int W = GEMV_THREADS / 32;
+  constexpr int D = 4;   // units in flight per lane: 4 x 2 rows x 16 B
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __half* xs = reinterpret_cast<__half*>(smem_raw);
+  float* xs_inv = reinterpret_cast<float*>(smem_raw + (size_t)M * K * sizeof(__half));
+  float* red = xs_inv + 8;
+  float* slots = red + 64;   // [pairs_local][2 rows][nslot][M]
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int npairs = N >> 1;
+  const int p_lo = (int)(((long long)blockIdx.x * npairs) / gridDim.x);
+  const int p_hi = (int)(((long long)(blockIdx.x + 1) * npairs) / gridDim.x);
+  const int pl = p_hi - p_lo;
+  for (int i = threadIdx.x; i < pl * 2 * nslot * M; i += GEMV_THREADS) slots[i] = 0.f;
+  pdl_wait();
+  stage_x<M>(x, ldx, K, norm_w, eps, xs, xs_inv, red);   // ends with a block barrier
+
+  const int nchunks = K >> 5;
+  const int nsteps = (nchunks + 31) >> 5;
+  const size_t row_bytes = (size_t)K >> 1, srow_bytes = (size_t)K >> 4;
+  const int U = pl * nsteps;
+  const int u0 = (int)(((long long)warp * U) / W), u1 = (int)(((long long)(warp + 1) * U) / W);
+
+  if (u0 < u1) {
+    uint4 wv[D][2];
+    uint16_t sv[D][2];
+    // loader cursor
+    // byte offsets from this CTA's first row (32-bit: a CTA's block is a few MB), advanced
+    // incrementally: 32 chunks per step, two rows per pair
+    int ls = u0 % nsteps;
+    const uint8_t* wbase = wq + (size_t)p_lo * 2 * row_bytes;
+    const uint8_t* sbase = wscale + (size_t)p_lo * 2 * srow_bytes;
+    uint32_t woff = (uint32_t)(u0 / nsteps) * 2u * (uint32_t)row_bytes + (uint32_t)(ls * 32 + lane) * 16u;
+    uint32_t soff = (uint32_t)(u0 / nsteps) * 2u * (uint32_t)srow_bytes + (uint32_t)(ls * 32 + lane) * 2u;
+    const uint32_t wwrap = 2u * (uint32_t)row_bytes - (uint32_t)nsteps * 512u;
+    const uint32_t swrap = 2u * (uint32_t)srow_bytes - (uint32_t)nsteps * 64u;
+    auto load = [&](int d) {
+      if (ls * 32 + lane < nchunks) {
+        wv[d][0] = ldg_stream_16(wbase + woff);
+        wv[d][1] = ldg_stream_16(wbase + woff + (uint32_t)row_bytes);
+        sv[d][0] = ldg_stream_2(sbase + soff);
+        sv[d][1] = ldg_stream_2(sbase + soff + (uint32_t)srow_bytes);
+      }
+      woff += 512u, soff += 64u;
+      if (++ls == nsteps) ls = 0, woff += wwrap, soff += swrap;
+    };
+#pragma unroll
+    for (int d = 0; d < D; ++d)
+      if (u0 + d < u1) load(d);
+    // consumer cursor
+    int cp = u0 / nsteps, cs = u0 % nsteps;
+    float acc[2][M];
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+      for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
+    auto flush = [&](int pair_local) {
+      // two-slot mode: slot 0 belongs to the warp that holds the pair's first unit
+      const int slot = nslot == 2 ? (pair_local * nsteps >= u0 ? 0 : 1) : warp - sk_owner(pair_local * nsteps, U, W);
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          const float v = warp_sum(acc[r][m]);
+          if (lane == 0) slots[((size_t)(pair_local * 2 + r) * nslot + slot) * M + m] = v;
+          acc[r][m] = 0.f;
+        }
+    };
+    for (int ub = u0; ub < u1; ub += D) {
+#pragma unroll
+      for (int d = 0; d < D; ++d) {
+        const int uc = ub + d;
+        if (uc < u1) {
+          const int c = cs * 32 + lane;
+          if (c < nchunks) {
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+              uint32_t xh[16];
+              const __half* xm = xs + (size_t)m * K;
+#pragma unroll
+              for (int p = 0; p < 4; ++p) {
+                uint4 t = *reinterpret_cast<const uint4*>(xm + ((size_t)(p * nchunks + c) << 3));
+                xh[p * 4 + 0] = t.x, xh[p * 4 + 1] = t.y, xh[p * 4 + 2] = t.z, xh[p * 4 + 3] = t.w;
+              }
+#pragma unroll
+              for (int r = 0; r < 2; ++r) {
+                const float2 sc = h2_to_f2(cvt_e4m3x2_to_h2(sv[d][r]));
+                const uint32_t w4[4] = {wv[d][r].x, wv[d][r].y, wv[d][r].z, wv[d][r].w};
+#pragma unroll
+                for (int blk = 0; blk < 2; ++blk) {
+                  uint32_t a = 0u;  // f16x2 zero
+#pragma unroll
+                  for (int q = 0; q < 2; ++q) {
+                    uint32_t h[4];
+                    cvt_e2m1x8_to_h2x4(w4[blk * 2 + q], h);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) a = hfma2_u(h[i], xh[(blk * 2 + q) * 4 + i], a);
+                  }
+                  const float2 af = h2_to_f2(a);
+                  acc[r][m] = fmaf(blk == 0 ? sc.x : sc.y, af.x + af.y, acc[r][m]);
+                }
+              }
+            }
+          }
+          if (uc + D < u1) load(d);
+          if (++cs == nsteps) {
+            flush(cp);
+            cs = 0, ++cp;
+          }
+        }
+      }
+    }
+    if (cs != 0) flush(cp);   // range ended inside a pair
+  }
+  __syncthreads();
+
+  // block-wide epilogue over this CTA's rows
+  const float ts = *tscale;
+  if (EPI == EPI_SWIGLU) {
+    for (int i = threadIdx.x; i < pl * M; i += GEMV_THREADS) {
+      const int pr = i / M, m = i % M;
+      float g = 0.f, u = 0.f;
+      for (int sl = 0; sl < nslot; ++sl) {
+        g += slots[((size_t)(pr * 2) * nslot + sl) * M + m];
+        u += slots[((size_t)(pr * 2 + 1) * nslot + sl) * M + m];
+      }
+      const float sc = ts * xs_inv[m];
+      const int n = (p_lo + pr) * 2;
+      if (n + 1 < N)
+        reinterpret_cast<bf16*>(yout)[(size_t)m * ldy + (n >> 1)] = __float2bfloat16(silu_f(g * sc) * (u * sc));
+    }
+  } else {
+    for (int i = threadIdx.x; i < pl * 2 * M; i += GEMV_THREADS) {
+      const int rl = i / M, m = i % M;
+      const int n = p_lo * 2 + rl;
+      if (n >= N) continue;
+      float v = 0.f;
+      for (int sl = 0; sl < nslot; ++sl) v += slots[((size_t)rl * nslot + sl) * M + m];
+      v *= ts * xs_inv[m];
+      if (EPI == EPI_PUSH) {
+        const uint32_t epoch = *reinterpret_cast<const uint32_t*>(push.ws[push.rank]) + 1;
+        const size_t off = 65536 + ((size_t)(((epoch & 1) * 8 + push.rank) * 8 + push.row0 + m) * push.hmax + n) * 4;
+        for (int p = 0; p < push.world; ++p) *reinterpret_cast<float*>(push.ws[p] + off) = v;
+      } else {
+        if (EPI == EPI_RESIDUAL) v += __bfloat162float(residual[(size_t)m * ldr + n]);
+        if (EPI == EPI_STORE_F32)
+          reinterpret_cast<float*>(yout)[(size_t)m * ldy + n] = v;
+        else
+          reinterpret_cast<bf16*>(yout)[(size_t)m * ldy + n] = __float2bfloat16(v);
+      }
+    }
+  }
+  if (EPI == EPI_PUSH && ldy != 0) {
+    // ldy != 0 marks the last row chunk: when every CTA has pushed, publish the epoch flag
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      uint32_t* ctrl = reinterpret_cast<uint32_t*>(push.ws[push.rank]);
+      const uint32_t epoch = ctrl[0] + 1;
+      const uint32_t prev = atomicAdd(ctrl + 16, 1u);
+      if (prev == gridDim.x - 1) {
+        ctrl[16] = 0;
+        __threadfence_system();
+        for (int p = 0; p < push.world; ++p)
+          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(reinterpret_cast<uint32_t*>(push.ws[p] + 4096) + (epoch & 1) * 8 + push.rank), "r"(epoch) : "memory");
+      }
+    }
+  }
+}
+
 // bf16 weights [N, K]: fp32 FMA, 8 weights per 16-byte load.  x staged as fp32.
 template <int M, int R, int EPI>
 __global__ void __launch_bounds__(GEMV_THREADS, 1)
@@ -359,9 +550,45 @@ cudaError_t launch_nvfp4(const bf16* x, int ldx, const uint8_t* wq, const uint8_
 }
 
 template <int M, int EPI>
+cudaError_t launch_nvfp4_sk(const bf16* x, int ldx, const uint8_t* wq, const uint8_t* ws, const float* ts,
+                            const float* norm_w, float eps, const bf16* res, int ldr, void* y, int ldy,
+                            int N, int K, cudaStream_t st, const TrlPushArgs& push) {
+  constexpr int W = GEMV_THREADS / 32;
+  if (N % 2 != 0) return cudaErrorInvalidValue;   // the older kernel handles odd row counts
+  const int npairs = N / 2;
+  const int grid = min(num_sms(), npairs);
+  const int pl_max = (npairs + grid - 1) / grid;
+  // a pair is shared by at most two warps once every CTA's warp share is at least one pair
+  const int nslot = (npairs / grid) >= W ? 2 : W;
+  const size_t smem = (size_t)M * K * sizeof(__half) + 8 * sizeof(float) + 64 * sizeof(float) +
+                      (size_t)pl_max * 2 * nslot * M * sizeof(float);
+  if (smem > 200 * 1024) return cudaErrorInvalidValue;
+  auto kern = gemv_nvfp4_sk_kernel<M, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    configured = true;
+  }
+  return trl_launch(kern, dim3(grid), dim3(GEMV_THREADS), smem, st, x, ldx, wq, ws, ts, norm_w, eps,
+                    res, ldr, y, ldy, N, K, nslot, push);
+}
+
+template <int M, int EPI>
 cudaError_t dispatch_r(const bf16* x, int ldx, const uint8_t* wq, const uint8_t* ws, const float* ts,
                        const float* norm_w, float eps, const bf16* res, int ldr, void* y, int ldy,
                        int N, int K, cudaStream_t st, const TrlPushArgs& push) {
+  // The balanced kernel pays a block-wide epilogue; it wins where whole-row rounds leave warps
+  // idle: rounds * R row-times against the ideal N / warps.
+  static const char* mode = getenv("TRL_GEMV_BALANCED");   // "0" never, "1" always, unset: by shape
+  const int all_warps = num_sms() * (GEMV_THREADS / 32);
+  const int R0 = (M > 2 && N >= all_warps * 4 * 2) ? 4 : 2;
+  const float ideal = (float)N / (float)all_warps;
+  const float rounds = (float)(((N + R0 - 1) / R0 + all_warps - 1) / all_warps) * (float)R0;
+  const bool balanced = mode ? (mode[0] == '1') : (ideal / rounds < 0.7f);
+  if (balanced) {
+    const cudaError_t e = launch_nvfp4_sk<M, EPI>(x, ldx, wq, ws, ts, norm_w, eps, res, ldr, y, ldy, N, K, st, push);
+    if (e != cudaErrorInvalidValue) return e;
+  }
   // enough row blocks to give every warp of a full grid at least two -> R = 4
   const int full_warps = num_sms() * (GEMV_THREADS / 32);
   if (M > 2 && N >= full_warps * 4 * 2)
