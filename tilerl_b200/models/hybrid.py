@@ -282,20 +282,27 @@ class HybridModel:
         return y
 
     def forward_dense(self, tape, ids: torch.Tensor, *, checkpoint_layers: bool = False,
-                      positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      positions: Optional[torch.Tensor] = None, hook=None) -> torch.Tensor:
         """Full-sequence forward on dense ``ids [B, T]`` with every op recorded on
         ``tape``; no KV cache, zero initial GDN state.  Returns this rank's logits
-        ``[B, T, vocab_local]`` (full vocab at TP=1)."""
+        ``[B, T, vocab_local]`` (full vocab at TP=1).  ``hook`` (a parameter sharder) is told
+        when the model starts (``pre_model``), when a layer is about to run -- in the forward
+        and again in its backward replay -- (``pre_layer``) and when a layer's forward is over
+        (``post_layer``)."""
         from .. import tape as T
         cfg, P, d = self.cfg, self.params, self.dims
         eps = cfg.rms_eps
         b, t = ids.shape
         pos = positions if positions is not None else torch.arange(t, device=ids.device)
+        if hook is not None:
+            hook.pre_model()
         x = T.embedding(tape, P["embed"], ids)
         tp = self.tp > 1
 
         def layer(tape, x, i=0):
             p = f"L{i}."
+            if hook is not None:
+                hook.pre_layer(i)
             h = T.rmsnorm(tape, x, P[p + "norm1"], eps)
             if tp:
                 h = T.tp_fork(tape, h)
@@ -332,6 +339,8 @@ class HybridModel:
                 x = tape.checkpoint(lambda tp_, x_, i=i: layer(tp_, x_, i), x, params=leaves)
             else:
                 x = layer(tape, x, i)
+            if hook is not None and checkpoint_layers:
+                hook.post_layer(i)
         h = T.rmsnorm(tape, x, P["final_norm"], eps)
         if tp:
             h = T.tp_fork(tape, h)

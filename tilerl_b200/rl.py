@@ -96,12 +96,12 @@ def _scored_mask(ids: torch.Tensor, prompt_lens, seq_lens) -> torch.Tensor:
 
 def forward_backward(model, ids: torch.Tensor, targets: torch.Tensor, weights_fn, *,
                      trainable: Dict[str, torch.Tensor], tp_group=None, tp_world: int = 1,
-                     checkpoint_layers: bool = False, on_grad=None):
+                     checkpoint_layers: bool = False, on_grad=None, hook=None):
     """One micro-batch: dense forward on a fresh tape, weights from ``weights_fn(logits)``,
     cross-entropy op, backward.  Returns (loss, named grads, logits)."""
     tp = T.Tape(tp_group, tp_world)
     tp.watch(*trainable.values())
-    logits = model.forward_dense(tp, ids, checkpoint_layers=checkpoint_layers)
+    logits = model.forward_dense(tp, ids, checkpoint_layers=checkpoint_layers, hook=hook)
     w = weights_fn(logits)
     loss = T.cross_entropy(tp, logits, targets, w)
     grads = tp.backward(loss, on_grad=on_grad)
