@@ -146,3 +146,42 @@ def test_zero3_world1_matches_adamw():
         rl.train_step(model, ids, z, max_norm=0.0, checkpoint_layers=True, on_grad=z.on_grad, hook=z)
     z.gather_all()
     assert _close(_snapshot(model), _single_step(1))
+
+
+def _resync_rank(rank, world):
+    """ZeRO-3 over `world` ranks trains; the same ranks serve a TP=`world` NVFP4 model.  After a
+    step + resync, every rank's shard must equal what quantising the updated full master and
+    cutting it for that rank gives."""
+    import torch.distributed as dist
+    from tilerl_b200 import rl
+    from tilerl_b200.formats import quantize_nvfp4
+    from tilerl_b200.models.hybrid import HybridModel, linear_names
+    from tilerl_b200.parallel.mesh import shard_param
+    from tilerl_b200.parallel.resync import resync
+    from tilerl_b200.parallel.zero3 import Zero3
+    cfg, trainer = _model()
+    rollout = HybridModel.build_random(cfg, seed=3, tp_rank=rank, tp=world)
+    addr = {k: (v.wq.data_ptr() if hasattr(v, "wq") else v.data_ptr()) for k, v in rollout.params.items()}
+    ids = _data(cfg, world)[2 * rank:2 * rank + 2]
+    z = Zero3(trainer, dist.group.WORLD, lr=1e-2, max_norm=1.0)
+    rl.train_step(trainer, ids, z, max_norm=0.0, checkpoint_layers=True, on_grad=z.on_grad, hook=z)
+    before = rollout.params["L0.gate_up"].wq.clone()
+    out = resync(z, rollout)
+    assert out["bytes"] > 0 and rollout.weights_version == 1
+    assert not torch.equal(before, rollout.params["L0.gate_up"].wq), "rollout weights did not change"
+    assert addr == {k: (v.wq.data_ptr() if hasattr(v, "wq") else v.data_ptr()) for k, v in rollout.params.items()}
+    z.gather_all()
+    bad = []
+    for name in linear_names(cfg):
+        want = shard_param(cfg, name, quantize_nvfp4(trainer.params["master." + name].float()), rank, world)
+        got = rollout.params[name]
+        if not (torch.equal(got.wq, want.wq) and torch.equal(got.scale.view(torch.uint8), want.scale.view(torch.uint8))
+                and torch.equal(got.tscale, want.tscale)):
+            bad.append(name)
+    norm_ok = torch.equal(rollout.params["L0.norm1"], trainer.params["L0.norm1"].float())
+    return bad, norm_ok
+
+
+def test_resync_writes_tp_shards_of_the_full_quantisation():
+    for bad, norm_ok in run_world(2, _resync_rank):
+        assert bad == [] and norm_ok

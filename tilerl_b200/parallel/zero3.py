@@ -121,8 +121,9 @@ class Zero3:
         self.t = 0
         with torch.no_grad():
             for u in self.units:
-                u.padded = (u.numel + self.world - 1) // self.world * self.world
-                flat = torch.zeros(max(u.padded, self.world), dtype=torch.float32, device=dev)
+                q = self.world * getattr(self.comm, "align", 1)
+                u.padded = (u.numel + q - 1) // q * q
+                flat = torch.zeros(max(u.padded, q), dtype=torch.float32, device=dev)
                 for name, off in zip(u.names, u.offsets):
                     p = self.params[name]
                     flat[off:off + p.numel()] = p.detach().float().reshape(-1)
@@ -292,3 +293,98 @@ class Zero3:
             for d, s in zip(dst, src):
                 d.copy_(s.to(d.device))
         self.drop_all()
+
+
+class P2PComm:
+    """ZeRO collectives by the kernels of ``csrc/zero.cu`` over NVLink peer memory.
+
+    One symmetric staging region per rank (``cap_bytes``: the largest unit's flat gradient in
+    the working dtype), exported with CUDA IPC.  Every collective is enqueued on this object's
+    own stream, in program order on every rank, so at most one of them runs per GPU and a
+    prefetch never meets a reduce-scatter half way; the caller's stream is joined before and
+    (unless the call is a prefetch issued from a side stream) after."""
+    align = 8          # elements: shards are moved in 16-byte vectors
+
+    def __init__(self, group, device, cap_bytes: int):
+        import ctypes
+
+        from ..ops import native as N
+        from .symm import _DevMem
+        self.group, self.device = group, torch.device(device)
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.backend = "p2p"
+        self.lib = N.lib()
+        for name, sig in {"trl_zero_allgather": [N.P, N.I, N.I, ctypes.c_long, N.P, N.P],
+                          "trl_zero_reduce_scatter": [N.P, N.I, N.I, ctypes.c_long, N.I, ctypes.c_float, N.P, N.I, N.P],
+                          }.items():
+            N.register(name, sig)
+        self.lib.trl_zero_data_offset.restype = ctypes.c_size_t
+        self.off = self.lib.trl_zero_data_offset()
+        self.cap = (cap_bytes + 255) // 256 * 256
+        self.nbytes = self.off + self.cap
+        p = ctypes.c_void_p()
+        N.check(self.lib.trl_symm_alloc(self.nbytes, ctypes.byref(p)), "symm_alloc")
+        self.local_ptr = p.value
+        handle = (ctypes.c_ubyte * 64)()
+        N.check(self.lib.trl_ipc_get(self.local_ptr, handle), "ipc_get")
+        handles: List[Optional[bytes]] = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle), group=group)
+        self.ptrs: List[int] = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.ptrs.append(self.local_ptr)
+                continue
+            q = ctypes.c_void_p()
+            N.check(self.lib.trl_ipc_open((ctypes.c_ubyte * 64).from_buffer_copy(h), ctypes.byref(q)), "ipc_open")
+            self.ptrs.append(q.value)
+        self.table = (ctypes.c_void_p * 8)(*(self.ptrs + [None] * (8 - self.world)))
+        self.mem = torch.as_tensor(_DevMem(self.local_ptr, self.nbytes), device=self.device)
+        self.stage = self.mem[self.off:]
+        self.stream = torch.cuda.Stream(device=self.device)
+        self._check = N.check
+        dist.barrier(group=group)
+
+    def _enter(self):
+        cur = torch.cuda.current_stream(self.device)
+        self.stream.wait_stream(cur)
+        return cur
+
+    def all_gather(self, shard: torch.Tensor, full: torch.Tensor, stream=None) -> None:
+        nb = shard.numel() * shard.element_size()
+        if nb > self.cap or nb % 16:
+            raise ValueError(f"shard of {nb} B does not fit the staging area ({self.cap} B) or is not 16-byte sized")
+        cur = self._enter()
+        with torch.cuda.stream(self.stream):
+            self.stage[:nb].copy_(shard.contiguous().view(torch.uint8))
+            self._check(self.lib.trl_zero_allgather(self.table, self.rank, self.world, nb, full.data_ptr(),
+                                                    self.stream.cuda_stream), "zero_allgather")
+        shard.record_stream(self.stream)
+        full.record_stream(self.stream)
+        cur.wait_stream(self.stream)
+
+    def reduce_scatter(self, full: torch.Tensor, shard_out: torch.Tensor, scale: float, accumulate: bool) -> None:
+        nb = full.numel() * full.element_size()
+        if nb > self.cap or shard_out.numel() % 8 or full.dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError("gradient does not fit the staging area, or shard not a multiple of 8 elements")
+        cur = self._enter()
+        with torch.cuda.stream(self.stream):
+            self.stage[:nb].copy_(full.contiguous().view(torch.uint8))
+            self._check(self.lib.trl_zero_reduce_scatter(self.table, self.rank, self.world, shard_out.numel(),
+                                                         int(full.dtype == torch.bfloat16), float(scale),
+                                                         shard_out.data_ptr(), int(accumulate),
+                                                         self.stream.cuda_stream), "zero_reduce_scatter")
+        full.record_stream(self.stream)
+        shard_out.record_stream(self.stream)
+        cur.wait_stream(self.stream)
+
+    def all_reduce_scalar(self, t: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            dist.all_reduce(t, group=self.group)
+        return t
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.device)
+        for r, p in enumerate(self.ptrs):
+            if r != self.rank:
+                self.lib.trl_ipc_close(p)
+        self.lib.trl_symm_free(self.local_ptr)
