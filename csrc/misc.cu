@@ -228,6 +228,97 @@ __global__ void absmax_kernel(const T* __restrict__ w, long n, float* __restrict
 
 __global__ void tscale_kernel(const float* amax, float* ts) { *ts = fmaxf(*amax, 1e-30f) / (6.f * 448.f); }
 
+
+// ---------------------------------------------------------------------------------------
+// Seeded temperature sampling of whole rows (top_p = 1, top_k = 0: the RL rollout setting):
+// softmax(logits / T) by two block reductions, then the inverse CDF at u = hash(seed).  Each
+// of the 1024 threads owns one contiguous chunk of the vocabulary; a block scan over the chunk
+// sums finds the chunk that holds u * total and its owner walks it.  One CTA per row, no host
+// round trip per row; the same (seed, logits) always give the same token.  Also returns the
+// log-probability of the token under the sampled distribution.
+// Parity: `sample_batch` of tilerl_kernels/reference.py:1656-1720 (there a torch multinomial
+// on the host generator); per-position seeds as in engine.py:206 of the reference.
+__device__ __forceinline__ float sample_u01(unsigned long long seed) {
+  unsigned long long z = seed + 0x9E3779B97F4A7C15ULL;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
+  z = z ^ (z >> 31);
+  return (float)(z >> 40) * (1.0f / 16777216.0f);
+}
+
+__global__ void __launch_bounds__(1024)
+sample_softmax_kernel(const float* __restrict__ logits, int ld, const int* __restrict__ rows,
+                      const long long* __restrict__ seeds, const float* __restrict__ inv_temp,
+                      int* __restrict__ out_tok, float* __restrict__ out_lp, int V) {
+  __shared__ float s_red[32];
+  __shared__ float s_sum[1024];
+  __shared__ float s_bcast[2];
+  __shared__ int s_pick;
+  const int b = blockIdx.x, tid = threadIdx.x;
+  const float* lg = logits + (size_t)rows[b] * ld;
+  const float it = inv_temp[b];
+  const int C = (V + 1023) / 1024;
+  const int lo = min(V, tid * C), hi = min(V, lo + C);
+  float mx = -INFINITY;
+  for (int i = lo; i < hi; ++i) mx = fmaxf(mx, lg[i] * it);
+  mx = warp_max(mx);
+  if ((tid & 31) == 0) s_red[tid >> 5] = mx;
+  __syncthreads();
+  if (tid < 32) {
+    float v = warp_max(s_red[tid]);
+    if (tid == 0) s_bcast[0] = v;
+  }
+  __syncthreads();
+  mx = s_bcast[0];
+  float sum = 0.f;
+  for (int i = lo; i < hi; ++i) sum += __expf(lg[i] * it - mx);
+  s_sum[tid] = sum;
+  __syncthreads();
+  // inclusive scan of the 1024 chunk sums by the first warp (32 values per lane)
+  if (tid < 32) {
+    float run = 0.f;
+    for (int j = 0; j < 32; ++j) run += s_sum[tid * 32 + j];
+    float incl = run;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (tid >= o) incl += n;
+    }
+    float acc = incl - run;   // exclusive prefix of this lane's 32 chunks
+    for (int j = 0; j < 32; ++j) {
+      const float v = s_sum[tid * 32 + j];
+      s_sum[tid * 32 + j] = acc;   // becomes the exclusive prefix of chunk tid*32+j
+      acc += v;
+    }
+    if (tid == 31) s_bcast[1] = acc;   // total
+  }
+  if (tid == 0) s_pick = -1;
+  __syncthreads();
+  const float total = s_bcast[1];
+  const float target = sample_u01((unsigned long long)seeds[b]) * total;
+  const float begin = s_sum[tid];
+  const float end = (tid == 1023) ? total : s_sum[tid + 1];
+  // the chunk whose [begin, end) holds the target; the last non-empty chunk takes rounding spill
+  if (hi > lo && target >= begin && (target < end || end >= total)) atomicMax(&s_pick, tid);
+  __syncthreads();
+  if (tid == max(s_pick, 0) && (s_pick >= 0 || tid == 0)) {
+    float acc = begin;
+    int tok = hi > lo ? hi - 1 : 0;
+    float e_tok = 0.f;
+    for (int i = lo; i < hi; ++i) {
+      const float e = __expf(lg[i] * it - mx);
+      acc += e;
+      if (acc > target && e > 0.f) {
+        tok = i, e_tok = e;
+        break;
+      }
+      if (e > 0.f) tok = i, e_tok = e;
+    }
+    out_tok[b] = tok;
+    out_lp[b] = logf(fmaxf(e_tok, 1e-45f)) - logf(total);
+  }
+}
+
 }  // namespace
 
 TRL_API int trl_embedding(const void* table, const void* ids, void* out, int T, int H, void* stream) {
@@ -311,4 +402,13 @@ TRL_API int trl_decode_advance(const void* tok, void* ids, void* pos, void* smap
   return (int)trl_launch(decode_advance_kernel, dim3((B + 127) / 128), dim3(128), 0, (cudaStream_t)stream,
                          (const int*)tok, (int*)ids, (int*)pos, (int*)smap, (int*)kvlen, (const int*)table,
                          B, max_blocks, (int*)hist, hist_cap, (int*)hist_n);
+}
+
+// rows[b]: logits row to sample; seeds[b]; inv_temp[b] = 1 / temperature.  One CTA per entry.
+TRL_API int trl_sample_softmax(const void* logits, int ld, const void* rows, const void* seeds,
+                               const void* inv_temp, void* out_tok, void* out_lp, int B, int V, void* stream) {
+  if (B <= 0) return 0;
+  return (int)trl_launch(sample_softmax_kernel, dim3(B), dim3(1024), 0, (cudaStream_t)stream, (const float*)logits,
+                         ld, (const int*)rows, (const long long*)seeds, (const float*)inv_temp, (int*)out_tok,
+                         (float*)out_lp, V);
 }

@@ -178,3 +178,31 @@ def test_gdn_kernel(ops, d, nk, nv):
         if keep:
             for p in pools:
                 p.select_step(1, 1)
+
+
+def test_sample_softmax_kernel_distribution_and_logprob():
+    """Device sampler: frequencies follow softmax(logits / T), the log-probability is the
+    sampled token's, equal seeds give equal tokens."""
+    from tilerl_b200.factory import make_ops
+    ops = make_ops("cuda")
+    g = torch.Generator().manual_seed(4)
+    v = 5003
+    logits = (torch.randn(3, v, generator=g) * 2.0).cuda()
+    temp = 0.8
+    n = 4096
+    rows = [1] * n
+    seeds = list(range(1000, 1000 + n))
+    toks, lps = ops.sample_rows(logits, rows, seeds, [temp] * n)
+    toks2, _ = ops.sample_rows(logits, rows, seeds, [temp] * n)
+    assert toks == toks2
+    p = torch.softmax(logits[1].double().cpu() / temp, -1)
+    lp_ref = torch.log(p)
+    t = torch.tensor(toks)
+    assert float((torch.tensor(lps).double() - lp_ref[t]).abs().max()) < 1e-3
+    top = torch.topk(p, 5).indices
+    for i in top.tolist():
+        freq = float((t == i).float().mean())
+        assert abs(freq - float(p[i])) < 4 * (float(p[i]) / n) ** 0.5 + 2e-3, (i, freq, float(p[i]))
+    # mean log-probability estimates the negative entropy
+    ent = -float((p * lp_ref).sum())
+    assert abs(-sum(lps) / n - ent) < 0.15

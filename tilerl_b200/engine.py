@@ -436,6 +436,7 @@ class Engine:
                 self.io_d2h += 4 * len(amax)
         if amax is None and hasattr(self.ops, "full_logits"):
             logits = self.ops.full_logits(logits)   # sampling needs every vocab shard
+        self._presampled = self._presample(plan, logits, verify) if amax is None else {}
         kinds = {r.state for r, _, _ in plan}
         key = "mixed_ticks" if len(kinds) > 1 else ("decode_ticks" if DECODE in kinds else "prefill_ticks")
         self.counters[key] += 1
@@ -464,6 +465,37 @@ class Engine:
         return p.temperature <= 0.0 and p.allowed_ids is None and not p.logprobs \
             and p.max_think_tokens is None
 
+    def _presample(self, plan, logits, verify: bool) -> Dict[int, Tuple[int, float]]:
+        """Rows that only need seeded temperature sampling (no top-k / top-p / allowed list) are
+        drawn on the device in one kernel when the backend offers it; everything else goes
+        through the per-row host sampler."""
+        if not hasattr(self.ops, "sample_rows"):
+            return {}
+        rows, seeds, temps = [], [], []
+        tok_off = 0
+        for i, (r, toks, start) in enumerate(plan):
+            n = len(toks)
+            p = r.params
+            base = tok_off if verify else i
+            tok_off += n
+            if p.temperature <= 0.0 or p.top_p < 1.0 or p.top_k or p.allowed_ids is not None:
+                continue
+            if r.state == PREFILL:
+                if start + n != len(r.prompt):
+                    continue
+                cand = [(base + n - 1 if verify else i, 0)]
+            else:
+                cand = [(base + k, k) for k in range(n)] if verify else [(i, 0)]
+            for row, k in cand:
+                rows.append(row)
+                seeds.append(ref.sample_seed(p.seed, len(r.out) + k))
+                temps.append(p.temperature)
+        if not rows:
+            return {}
+        toks_, lps = self.ops.sample_rows(logits, rows, seeds, temps)
+        self.io_d2h += 8 * len(rows)
+        return {row: (int(t), float(lp)) for row, t, lp in zip(rows, toks_, lps)}
+
     def _sample(self, r: _Req, logits: torch.Tensor, row: int, k: int, amax=None) -> Tuple[int, float]:
         p = r.params
         idx = len(r.out) + k
@@ -472,6 +504,9 @@ class Engine:
             return self.think_ids[1], 0.0  # forced </think>
         if amax is not None:
             return amax[row], 0.0
+        pre = getattr(self, "_presampled", None)
+        if pre and row in pre:
+            return pre[row]
         allowed = None if p.allowed_ids is None else torch.tensor(p.allowed_ids)
         if p.temperature <= 0.0 and allowed is None and not p.logprobs:
             return int(torch.argmax(logits[row])), 0.0

@@ -67,6 +67,9 @@ class CudaOps:
         # small-M projections: the SIMT weight-streaming GEMV (default; measured faster at
         # B=1) or the tcgen05 GEMM with `terms_small` residual terms (TRL_DECODE=tc)
         self.decode_tc = (os.environ.get("TRL_DECODE", "simt") == "tc") if decode_tc is None else decode_tc
+        self.gemv_tokens = int(os.environ.get("TRL_GEMV_TOKENS", GEMV_MAX_M))
+        from .. import tape as _tape
+        _tape.set_dequant(self.dequantize_nvfp4)   # frozen-base linears of the training forward
         self.terms_small = int(os.environ.get("TRL_TERMS_SMALL", terms_small))
         self.terms_large = int(os.environ.get("TRL_TERMS_LARGE", terms_large))
         self.act_dtype = torch.bfloat16
@@ -101,7 +104,11 @@ class CudaOps:
             raise TypeError(f"no GEMV for weight type {type(w)}")
 
     def _tc(self, w, t: int) -> bool:
-        return isinstance(w, NVFP4Tensor) and self.use_tc_gemm and (t > GEMV_MAX_M or self.decode_tc)
+        # the weight-streaming GEMV handles up to 8 tokens in passes of 4; `gemv_tokens = 4` sends
+        # 5..8 tokens to the tensor-core kernel's single pass instead (faster for batched decode,
+        # but its activation rounding differs from the GEMV's, so a speculative verify tick of
+        # width <= 8 keeps the GEMV by default and commits exactly what plain decode would)
+        return isinstance(w, NVFP4Tensor) and self.use_tc_gemm and (t > self.gemv_tokens or self.decode_tc)
 
     def _linear(self, x, w, y, *, norm_w=None, eps=0.0, residual=None, epi=EPI_STORE):
         """``y = epi(norm(x) @ W^T)`` with everything fused into one or two kernels."""
@@ -280,6 +287,25 @@ class CudaOps:
                                     N.stream()), "argmax")
         N.count(2)
         return out
+
+    def sample_rows(self, logits: torch.Tensor, rows, seeds, temps):
+        """Seeded temperature sampling of the listed logits rows on the device (one kernel, one
+        device-to-host copy).  Returns ``(tokens, logprobs)`` as Python lists."""
+        n = len(rows)
+        meta = torch.tensor([list(rows), [s & 0x7FFFFFFFFFFFFFFF for s in seeds]], dtype=torch.int64)
+        it = torch.tensor([1.0 / t for t in temps], dtype=torch.float32)
+        rows_d = meta[0].to(torch.int32).to(self.device, non_blocking=True)
+        seeds_d = meta[1].to(self.device, non_blocking=True)
+        it_d = it.to(self.device, non_blocking=True)
+        out = torch.empty(2, n, dtype=torch.float32, device=self.device)
+        tok = out[0].view(torch.int32)
+        lg = logits if logits.dtype == torch.float32 else logits.float()
+        N.check(self.lib.trl_sample_softmax(lg.data_ptr(), lg.stride(0), rows_d.data_ptr(), seeds_d.data_ptr(),
+                                            it_d.data_ptr(), tok.data_ptr(), out[1].data_ptr(), n, lg.shape[1],
+                                            N.stream()), "sample_softmax")
+        N.count()
+        host = out.cpu()
+        return host[0].view(torch.int32).tolist(), host[1].tolist()
 
     # ---- training / maintenance kernels ------------------------------------------------------
     def quantize_nvfp4_(self, w: torch.Tensor, dst: NVFP4Tensor, keep_tscale: bool = False) -> None:

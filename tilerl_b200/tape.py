@@ -132,7 +132,8 @@ def embedding(tape: Tape, table: torch.Tensor, ids: torch.Tensor) -> torch.Tenso
         gt.index_add_(0, ids.reshape(-1).long(), g.reshape(-1, g.shape[-1]).float())
         return (gt,)
 
-    tape.record("embedding", (table,), (out,), bwd)
+    if id(table) in tape.leaves:        # a frozen table needs no [vocab, hidden] gradient buffer
+        tape.record("embedding", (table,), (out,), bwd)
     return out
 
 
@@ -154,11 +155,43 @@ def rmsnorm(tape: Tape, x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.T
     return out
 
 
+# Device hook: a CUDA backend installs its NVFP4 -> bf16 dequantisation kernel here so the
+# frozen-base linears of the training forward do not run the torch decoder.
+DEQUANT_BF16: Optional[Callable] = None
+
+
+def set_dequant(fn: Optional[Callable]) -> None:
+    global DEQUANT_BF16
+    DEQUANT_BF16 = fn
+
+
 @_nograd
 def linear(tape: Tape, x: torch.Tensor, w, frozen: bool = False) -> torch.Tensor:
     """``y = x @ W^T``.  ``w`` is a dense master tensor (dX and dW) or a quantised
-    weight / ``frozen=True`` dense tensor (dX only, the LoRA-on-frozen-base mode)."""
+    weight / ``frozen=True`` dense tensor (dX only, the LoRA-on-frozen-base mode).
+    On CUDA the three GEMMs run in bf16 with fp32 accumulation; on CPU everything is fp32
+    (the oracle path)."""
     dense = isinstance(w, torch.Tensor)
+    if x.is_cuda:
+        if dense:
+            wf = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
+        elif DEQUANT_BF16 is not None and hasattr(w, "wq"):
+            wf = DEQUANT_BF16(w)
+        else:
+            wf = w.dequant().to(x.device, torch.bfloat16)
+        xb = x.to(torch.bfloat16)
+        out = (xb @ wf.t()).float()
+
+        def bwd(g):
+            gb = g.to(torch.bfloat16)
+            dx = (gb @ wf).float()
+            if dense and not frozen:
+                dw = (gb.reshape(-1, gb.shape[-1]).t() @ xb.reshape(-1, xb.shape[-1])).float()
+                return dx, dw
+            return (dx,)
+
+        tape.record("linear", (x, w) if dense and not frozen else (x,), (out,), bwd)
+        return out
     wf = w.float() if dense else w.dequant().to(x.device)
     out = x.float() @ wf.t()
 
