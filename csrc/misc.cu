@@ -319,6 +319,55 @@ sample_softmax_kernel(const float* __restrict__ logits, int ld, const int* __res
   }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// LoRA delta of a served projection, two small kernels instead of a chain of library calls:
+//   lora_a: t[tok, r] = sum_k xn[tok, k] * A[r, k]   (xn = x, or RMSNorm(x) * norm_w)
+//   lora_b: y[tok, n] += s * sum_r t[tok, r] * B[n, r]
+// grid (tokens, rank) and (tokens, ceil(N / 256)).  A, B are the fp32 trainable tensors.
+// Parity: `_linear` of src/tilerl/model.py:379-385 (two `linear` calls there).
+__global__ void __launch_bounds__(256)
+lora_a_kernel(const bf16* __restrict__ x, int ldx, const float* __restrict__ norm_w, float eps,
+              const float* __restrict__ A, float* __restrict__ t, int K, int R) {
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tok = blockIdx.x, r = blockIdx.y;
+  const bf16* xr = x + (size_t)tok * ldx;
+  const float* ar = A + (size_t)r * K;
+  float acc = 0.f, ss = 0.f;
+  for (int k = threadIdx.x * 2; k < K; k += blockDim.x * 2) {
+    const float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(xr + k));
+    ss += v.x * v.x + v.y * v.y;
+    if (norm_w != nullptr)
+      acc += v.x * norm_w[k] * ar[k] + v.y * norm_w[k + 1] * ar[k + 1];
+    else
+      acc += v.x * ar[k] + v.y * ar[k + 1];
+  }
+  acc = block_sum(acc, red);
+  __syncthreads();
+  ss = block_sum(ss, red);
+  if (threadIdx.x == 0) t[(size_t)tok * R + r] = norm_w != nullptr ? acc * rsqrtf(ss / (float)K + eps) : acc;
+}
+
+__global__ void __launch_bounds__(256)
+lora_b_kernel(const float* __restrict__ t, const float* __restrict__ B, bf16* __restrict__ y, int ldy, int N,
+              int R, float s) {
+  __shared__ float ts[64];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tok = blockIdx.x;
+  if (threadIdx.x < R) ts[threadIdx.x] = t[(size_t)tok * R + threadIdx.x];
+  __syncthreads();
+  const int n = blockIdx.y * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  const float* br = B + (size_t)n * R;
+  float acc = 0.f;
+  for (int r = 0; r < R; ++r) acc = fmaf(br[r], ts[r], acc);
+  bf16* yp = y + (size_t)tok * ldy + n;
+  *yp = __float2bfloat16(__bfloat162float(*yp) + s * acc);
+}
+
 }  // namespace
 
 TRL_API int trl_embedding(const void* table, const void* ids, void* out, int T, int H, void* stream) {
@@ -411,4 +460,16 @@ TRL_API int trl_sample_softmax(const void* logits, int ld, const void* rows, con
   return (int)trl_launch(sample_softmax_kernel, dim3(B), dim3(1024), 0, (cudaStream_t)stream, (const float*)logits,
                          ld, (const int*)rows, (const long long*)seeds, (const float*)inv_temp, (int*)out_tok,
                          (float*)out_lp, V);
+}
+
+// y[T, N] (bf16, in place) += s * (norm(x) A^T) B^T.  t: fp32 scratch [T, R]; R <= 64; K even.
+TRL_API int trl_lora_add(const void* x, int ldx, const void* norm_w, float eps, const void* A, const void* B,
+                         void* t, void* y, int ldy, int T, int N, int K, int R, float s, void* stream) {
+  if (R > 64 || R < 1 || (K & 1)) return (int)cudaErrorInvalidValue;
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e = trl_launch(lora_a_kernel, dim3(T, R), dim3(256), 0, st, (const bf16*)x, ldx, (const float*)norm_w,
+                             eps, (const float*)A, (float*)t, K, R);
+  if (e != cudaSuccess) return (int)e;
+  return (int)trl_launch(lora_b_kernel, dim3(T, (N + 255) / 256), dim3(256), 0, st, (const float*)t,
+                         (const float*)B, (bf16*)y, ldy, N, R, s);
 }

@@ -206,3 +206,23 @@ def test_sample_softmax_kernel_distribution_and_logprob():
     # mean log-probability estimates the negative entropy
     ent = -float((p * lp_ref).sum())
     assert abs(-sum(lps) / n - ent) < 0.15
+
+
+@pytest.mark.parametrize("norm", [False, True])
+def test_lora_add_kernel(norm):
+    from tilerl_b200.factory import make_ops
+    ops = make_ops("cuda")
+    g = torch.Generator().manual_seed(2)
+    t, k, n, r = 5, 1536, 777, 16
+    x = torch.randn(t, k, generator=g).cuda().to(torch.bfloat16)
+    a = (torch.randn(r, k, generator=g) * 0.1).cuda()
+    b = (torch.randn(n, r, generator=g) * 0.1).cuda()
+    nw = (1 + 0.1 * torch.randn(k, generator=g)).cuda()
+    y0 = torch.randn(t, n, generator=g).cuda().to(torch.bfloat16)
+    y = y0.clone()
+    ops._lora_add(y, x, (a, b, 2.0), nw if norm else None, 1e-6)
+    xf = x.float()
+    if norm:
+        xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * nw
+    want = y0.float() + 2.0 * (xf @ a.t()) @ b.t()
+    assert float((y.float() - want).abs().max()) < 0.03 * float(want.abs().max())

@@ -142,10 +142,23 @@ class CudaOps:
         N.count()
         return out
 
-    def _lora_add(self, y, x, lora):
+    def _lora_add(self, y, x, lora, norm_w=None, eps=0.0):
+        """``y += s * (norm(x) A^T) B^T`` in place (two small kernels; the norm is recomputed
+        inside the first, so no normalised copy of x is materialised)."""
         if lora is not None:
             a, b, s = lora
-            y.add_(((x.float() @ a.float().t()) @ b.float().t() * s).to(y.dtype))
+            t, k = x.shape
+            n, r = b.shape
+            if a.dtype == torch.float32 and b.dtype == torch.float32 and r <= 64 and k % 2 == 0 \
+                    and a.is_contiguous() and b.is_contiguous():
+                tmp = self.ws.get("lora_t", (t, r), torch.float32)
+                N.check(self.lib.trl_lora_add(x.data_ptr(), x.stride(0), N.ptr(self._f32(norm_w) if norm_w is not None else None),
+                                              eps, a.data_ptr(), b.data_ptr(), tmp.data_ptr(), y.data_ptr(), y.stride(0),
+                                              t, n, k, r, float(s), N.stream()), "lora_add")
+                N.count(2)
+            else:
+                xn = self._rmsnorm(x, norm_w, eps) if norm_w is not None else x
+                y.add_(((xn.float() @ a.float().t()) @ b.float().t() * s).to(y.dtype))
         return y
 
     # ---- op surface --------------------------------------------------------------------
@@ -161,7 +174,7 @@ class CudaOps:
         y = self.ws.get("proj", (t, n), torch.bfloat16)
         self._linear(x, w, y, norm_w=self._f32(norm_w), eps=eps)
         if lora is not None:
-            self._lora_add(y, self._rmsnorm(x, norm_w, eps), lora)
+            self._lora_add(y, x, lora, norm_w, eps)
         return y
 
     def norm_linear_swiglu(self, x, norm_w, w, eps, lora=None):
@@ -172,7 +185,7 @@ class CudaOps:
             return act
         gu = self.ws.get("proj", (t, n), torch.bfloat16)
         self._linear(x, w, gu, norm_w=self._f32(norm_w), eps=eps)
-        self._lora_add(gu, self._rmsnorm(x, norm_w, eps), lora)
+        self._lora_add(gu, x, lora, norm_w, eps)
         N.check(self.lib.trl_swiglu(gu.data_ptr(), act.data_ptr(), act.numel(), N.stream()), "swiglu")
         N.count()
         return act
@@ -184,8 +197,7 @@ class CudaOps:
             return self.comm.linear_allreduce_residual(self, a, w, residual, lora)
         self._linear(a, w, residual, residual=residual, epi=EPI_RESIDUAL)
         if lora is not None:
-            zero = torch.zeros_like(residual)
-            residual.add_(self._lora_add(zero, a, lora))
+            self._lora_add(residual, a, lora)
         return residual
 
     def attention(self, qkv, lp, batch, pool, attn_idx, cfg, n_q, n_kv):
