@@ -238,6 +238,11 @@ class Engine:
             self.prefix.clear()
             if self.drafter is not None and hasattr(self.drafter, "invalidate"):
                 self.drafter.invalidate()
+            refresh = getattr(self.ops, "refresh_weight", None)
+            if refresh is not None:      # derived device copies of rewritten weights, in place
+                for v in self.model.params.values():
+                    if hasattr(v, "wq"):
+                        refresh(v)
 
     def precapture(self, batches: Sequence[int] = (1,)) -> None:
         if self.graph is not None:

@@ -47,7 +47,9 @@ def random_param(cfg: ModelConfig, name: str, shape, seed: int, device) -> torch
 
 
 def build_random_streaming(cfg: ModelConfig, device, seed: int = 0, tp_rank: int = 0, tp: int = 1,
-                           ops=None, keep_master: bool = False) -> HybridModel:
+                           ops=None, keep_master: bool = False, master_only: bool = False) -> HybridModel:
+    """``master_only``: a trainer that never serves keeps just the master projections (no
+    quantised copy is built)."""
     from .parallel.mesh import shard_param
     device = torch.device(device)
     lin = set(linear_names(cfg))
@@ -55,7 +57,9 @@ def build_random_streaming(cfg: ModelConfig, device, seed: int = 0, tp_rank: int
     for name, shape in param_shapes(cfg, 1).items():
         full = random_param(cfg, name, shape, seed, device)
         w = shard_param(cfg, name, full, tp_rank, tp)
-        if name in lin or (name == "lm_head" and cfg.lm_head_quant == "nvfp4"):
+        if master_only and name in lin:
+            params["master." + name] = w.to(torch.bfloat16) if device.type == "cuda" else w.clone()
+        elif name in lin or (name == "lm_head" and cfg.lm_head_quant == "nvfp4"):
             if cfg.quant == "nvfp4" and device.type == "cuda" and ops is not None:
                 # quantise the full tensor on the device, then cut the packed planes
                 n, k = full.shape
@@ -94,13 +98,14 @@ def materialize(model: HybridModel, ops) -> None:
 
 
 def build_model(model: str | ModelConfig, device="cpu", *, seed: int = 0, checkpoint: Optional[str] = None,
-                tp_rank: int = 0, tp: int = 1, ops=None, keep_master: bool = False) -> HybridModel:
+                tp_rank: int = 0, tp: int = 1, ops=None, keep_master: bool = False,
+                master_only: bool = False) -> HybridModel:
     cfg = get_config(model) if isinstance(model, str) else model
     if checkpoint:
         from .checkpoint import load_checkpoint
         return load_checkpoint(cfg, checkpoint, device=device, tp_rank=tp_rank, tp=tp, keep_master=keep_master)
-    m = build_random_streaming(cfg, device, seed, tp_rank, tp, ops, keep_master)
-    if ops is not None:
+    m = build_random_streaming(cfg, device, seed, tp_rank, tp, ops, keep_master, master_only)
+    if ops is not None and not master_only:
         materialize(m, ops)
     return m
 

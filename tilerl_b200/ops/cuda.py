@@ -330,6 +330,23 @@ class CudaOps:
                 "quant_nvfp4")
         N.count(4)
 
+    def quantize_new(self, w: torch.Tensor) -> NVFP4Tensor:
+        """Quantise a full ``[N, K]`` fp32 / bf16 tensor into a fresh NVFP4 tensor (kernel)."""
+        n, k = w.shape
+        dst = NVFP4Tensor(torch.empty(n, k // 2, dtype=torch.uint8, device=self.device),
+                          torch.empty(n, k // 16, dtype=torch.float8_e4m3fn, device=self.device),
+                          torch.empty(1, dtype=torch.float32, device=self.device))
+        self.quantize_nvfp4_(w.contiguous(), dst)
+        return dst
+
+    def refresh_weight(self, w: NVFP4Tensor) -> None:
+        """Bring the GEMM's tile-contiguous copies of a rewritten weight up to date (in place)."""
+        from .gemm_tc import sf_tiled, wq_tiled
+        if getattr(w, "wq_tiled", None) is not None:
+            wq_tiled(w)
+        if getattr(w, "sf_tiled", None) is not None:
+            sf_tiled(w)
+
     def dequantize_nvfp4(self, w: NVFP4Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         n, k = w.shape
         if out is None:

@@ -55,18 +55,26 @@ def tile_weight(wq: torch.Tensor, K: int) -> torch.Tensor:
 
 def wq_tiled(w: NVFP4Tensor) -> torch.Tensor:
     t = getattr(w, "wq_tiled", None)
-    if t is None or getattr(w, "wq_version", None) is not w.wq._version:
+    if t is None:
         t = tile_weight(w.wq, w.shape[1])
         w.wq_tiled = t
+        w.wq_version = w.wq._version
+    elif getattr(w, "wq_version", None) != w.wq._version:
+        # the weight was rewritten in place (re-quantisation, resync): refresh the copy in place
+        # too, so kernels captured in CUDA graphs keep reading the right address
+        t.copy_(tile_weight(w.wq, w.shape[1]))
         w.wq_version = w.wq._version
     return t
 
 
 def sf_tiled(w: NVFP4Tensor) -> torch.Tensor:
     t = getattr(w, "sf_tiled", None)
-    if t is None or getattr(w, "sf_version", None) is not w.scale._version:
+    if t is None:
         t = tile_scales(w.scale, w.shape[1])
         w.sf_tiled = t
+        w.sf_version = w.scale._version
+    elif getattr(w, "sf_version", None) != w.scale._version:
+        t.copy_(tile_scales(w.scale, w.shape[1]))
         w.sf_version = w.scale._version
     return t
 

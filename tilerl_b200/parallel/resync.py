@@ -40,11 +40,11 @@ def _store(dst, src) -> int:
 def resync(zero, rollout, *, quantize: Optional[Callable] = None, refresh: Optional[Callable] = None,
            engine=None) -> Dict[str, float]:
     """Write the trainer's current weights into ``rollout`` (a served ``HybridModel`` of TP
-    degree ``rollout.tp``).  ``quantize(w_full_fp32) -> NVFP4Tensor`` defaults to the torch
+    degree ``rollout.tp``).  ``quantize(w_full) -> NVFP4Tensor`` defaults to the torch
     quantiser (a CUDA backend passes its kernel); ``refresh(param)`` is called for every
     rewritten quantised tensor (the CUDA backend re-tiles its GEMM copies there)."""
     cfg = rollout.cfg
-    quantize = quantize or quantize_nvfp4
+    quantize = quantize or (lambda w: quantize_nvfp4(w.float()))
     lin = set(linear_names(cfg))
     t0 = time.perf_counter()
     nbytes = 0
@@ -60,7 +60,7 @@ def resync(zero, rollout, *, quantize: Optional[Callable] = None, refresh: Optio
                 if dst is None:
                     continue
                 if base in lin and isinstance(dst, NVFP4Tensor):
-                    q = shard_param(cfg, base, quantize(w.float()), rollout.tp_rank, rollout.tp)
+                    q = shard_param(cfg, base, quantize(w), rollout.tp_rank, rollout.tp)
                     nbytes += _store(dst, q)
                     if refresh is not None:
                         refresh(dst)
