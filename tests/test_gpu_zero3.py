@@ -22,6 +22,15 @@ def _snapshot(model):
 
 
 def _worker(rank, world, port, out):
+    try:
+        _worker_body(rank, world, port, out)
+    except Exception:  # noqa: BLE001 - fail fast instead of letting the parent wait out its timeout
+        import traceback
+        out.put(dict(error=f"rank {rank}:\n{traceback.format_exc()}"))
+        raise
+
+
+def _worker_body(rank, world, port, out):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -106,6 +115,10 @@ def test_zero3_p2p_collectives_and_step(world):
     for p in procs:
         p.start()
     res = out.get(timeout=600)
+    if "error" in res:
+        for p in procs:
+            p.kill()
+        pytest.fail(res["error"])
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
