@@ -282,13 +282,15 @@ class HybridModel:
         return y
 
     def forward_dense(self, tape, ids: torch.Tensor, *, checkpoint_layers: bool = False,
-                      positions: Optional[torch.Tensor] = None, hook=None) -> torch.Tensor:
+                      positions: Optional[torch.Tensor] = None, hook=None, cp=None) -> torch.Tensor:
         """Full-sequence forward on dense ``ids [B, T]`` with every op recorded on
         ``tape``; no KV cache, zero initial GDN state.  Returns this rank's logits
         ``[B, T, vocab_local]`` (full vocab at TP=1).  ``hook`` (a parameter sharder) is told
         when the model starts (``pre_model``), when a layer is about to run -- in the forward
         and again in its backward replay -- (``pre_layer``) and when a layer's forward is over
-        (``post_layer``)."""
+        (``post_layer``).  ``cp`` (a ``parallel.cp.CPContext``): ``ids`` and ``positions`` hold this
+        rank's zigzag slice of the sequence; attention gathers K / V, the GDN layers exchange
+        chunk summaries and conv halos."""
         from .. import tape as T
         cfg, P, d = self.cfg, self.params, self.dims
         eps = cfg.rms_eps
@@ -311,13 +313,13 @@ class HybridModel:
                 a = T.attention_block(tape, qkv, P[p + "q_norm"], P[p + "k_norm"], pos,
                                       n_q=d.n_q, n_kv=d.n_kv, head_dim=cfg.head_dim,
                                       rotary_dim=cfg.rotary_dim, theta=cfg.rope_theta, eps=eps,
-                                      gated=cfg.attn_gated)
+                                      gated=cfg.attn_gated, cp=cp)
                 y = self._tlinear(tape, a, p + "o")
             else:
                 inp = self._tlinear(tape, h, p + "in")
                 a = T.gdn_block(tape, inp, P[p + "conv"], P[p + "dt_bias"], P[p + "a_log"],
                                 P[p + "gdn_norm"], nk=d.gdn_nk, nv=d.gdn_nv, dk=cfg.gdn_head_dim,
-                                dv=cfg.gdn_head_dim, eps=eps)
+                                dv=cfg.gdn_head_dim, eps=eps, cp=cp)
                 y = self._tlinear(tape, a, p + "out")
             if tp:
                 y = T.all_reduce(tape, y)

@@ -239,10 +239,12 @@ def swiglu(tape: Tape, gu: torch.Tensor) -> torch.Tensor:
 @_nograd
 def attention_block(tape: Tape, qkv: torch.Tensor, q_norm_w: torch.Tensor, k_norm_w: torch.Tensor,
                     positions: torch.Tensor, *, n_q, n_kv, head_dim, rotary_dim, theta, eps,
-                    gated=True) -> torch.Tensor:
+                    gated=True, cp=None) -> torch.Tensor:
     """Dense causal gated-GQA attention on ``qkv [B, T, rows]``: split, per-head q/k
     RMSNorm, partial RoPE, softmax(QK^T)V, sigmoid gate.  Backward is derived by
-    hand (softmax Jacobian, RoPE transpose rotation, RMSNorm)."""
+    hand (softmax Jacobian, RoPE transpose rotation, RMSNorm).  With a context-parallel
+    ``cp`` the rotated K, V and their absolute positions are all-gathered over the ranks
+    (the mask compares absolute positions) and dK / dV are reduce-scattered in backward."""
     b, t, _ = qkv.shape
     d, g = head_dim, n_q // n_kv
     x = qkv.float()
@@ -280,9 +282,16 @@ def attention_block(tape: Tape, qkv: torch.Tensor, q_norm_w: torch.Tensor, k_nor
     k = rope(kn * k_norm_w.float())
     sc = 1.0 / math.sqrt(d)
     qq = q.view(b, t, n_kv, g, d)
-    s = torch.einsum("bthgd,bshd->bhgts", qq, k) * sc
     pos = positions if positions.dim() == 2 else positions[None].expand(b, -1)
-    mask = pos[:, None, :] <= pos[:, :, None]                     # [b, t, s]
+    k_loc, v_loc = k, v
+    if cp is not None:
+        from .parallel.cp import gather_kv
+        k, v, pos_all = gather_kv(k_loc, v_loc, positions.reshape(-1)[:t].contiguous(), cp)
+        kpos = pos_all[None].expand(b, -1)
+    else:
+        kpos = pos
+    s = torch.einsum("bthgd,bshd->bhgts", qq, k) * sc
+    mask = kpos[:, None, :] <= pos[:, :, None]                    # [b, t, s]
     s = s.masked_fill(~mask[:, None, None], float("-inf"))
     p = torch.softmax(s, -1)
     o = torch.einsum("bhgts,bshd->bthgd", p, v).reshape(b, t, n_q, d)
@@ -300,6 +309,12 @@ def attention_block(tape: Tape, qkv: torch.Tensor, q_norm_w: torch.Tensor, k_nor
         ds = p * (dp - (dp * p).sum(-1, keepdim=True))
         dq = torch.einsum("bhgts,bshd->bthgd", ds, k).reshape(b, t, n_q, d) * sc
         dk = torch.einsum("bhgts,bthgd->bshd", ds, qq) * sc
+        if cp is not None:
+            # reduce-scatter: every rank holds gradients for all ranks' keys / values
+            import torch.distributed as dist
+            both = torch.stack([dk, dv]).contiguous()
+            dist.all_reduce(both, group=cp.group)
+            dk, dv = both[0][:, cp.rank * t:(cp.rank + 1) * t], both[1][:, cp.rank * t:(cp.rank + 1) * t]
         dq, dk = rope(dq, -1.0), rope(dk, -1.0)   # transpose of a rotation = inverse rotation
 
         def norm_bwd(gz, zn, rstd, w):
@@ -321,10 +336,53 @@ def attention_block(tape: Tape, qkv: torch.Tensor, q_norm_w: torch.Tensor, k_nor
     return out
 
 
+def _gdn_block_cp(inp, conv_w, dt_bias, a_log, norm_w, *, nk, nv, dk, dv, eps, chunk, cp):
+    """Context-parallel GDN block on this rank's two zigzag chunks ``inp [B, 2c, rows]``."""
+    from .parallel import cp as CP
+    b, t2, _ = inp.shape
+    c = t2 // 2
+    q_raw, k_raw, v_raw, z, a, bb = ref.gdn_split(inp.float(), nk=nk, nv=nv, dk=dk, dv=dv)
+    qkv = torch.cat([q_raw, k_raw, v_raw], -1)
+    kw = conv_w.shape[1]
+    halo = CP.conv_halo(qkv, kw, cp)                                  # [B, 2, kw-1, C]
+    outs = []
+    prepped = []
+    for i in range(2):
+        xp = torch.cat([halo[:, i], qkv[:, i * c:(i + 1) * c]], 1)
+        conv = sum(xp[:, j:j + c] * conv_w.float()[:, j] for j in range(kw))
+        cc = F.silu(conv)
+        qc = cc[..., :nk * dk].view(b, c, nk, dk)
+        kc = cc[..., nk * dk:2 * nk * dk].view(b, c, nk, dk)
+        vc = cc[..., 2 * nk * dk:].view(b, c, nv, dv)
+        rep = nv // nk
+        qn = (ref.l2norm(qc) / math.sqrt(dk)).repeat_interleave(rep, 2)
+        kn = ref.l2norm(kc).repeat_interleave(rep, 2)
+        g, beta = ref.gdn_gates(a[:, i * c:(i + 1) * c], bb[:, i * c:(i + 1) * c], a_log, dt_bias)
+        prepped.append((qn, kn, vc, g, beta))
+    # chunk summaries: B = state reached from zero, A = the map applied to an identity "state"
+    a_loc, b_loc = [], []
+    eye = torch.eye(dk, dtype=torch.float32, device=inp.device).expand(b, nv, dk, dk)
+    for qn, kn, vc, g, beta in prepped:
+        ck = min(chunk, c) if chunk else c
+        _, bs = ref.gdn_chunked(qn, kn, vc, g, beta, torch.zeros(b, nv, dk, dv, device=inp.device), chunk=ck)
+        _, as_ = ref.gdn_chunked(qn, kn, torch.zeros(b, c, nv, dk, device=inp.device), g, beta, eye, chunk=ck)
+        a_loc.append(as_)
+        b_loc.append(bs)
+    entry = CP.fold_entry_states(torch.stack(a_loc), torch.stack(b_loc), cp)
+    for i, (qn, kn, vc, g, beta) in enumerate(prepped):
+        ck = min(chunk, c) if chunk else c
+        o, _ = ref.gdn_chunked(qn, kn, vc, g, beta, entry[i], chunk=ck)
+        outs.append(ref.gdn_gated_norm(o, z[:, i * c:(i + 1) * c].reshape(b, c, nv, dv), norm_w, eps))
+    return torch.cat(outs, 1).reshape(b, t2, nv * dv)
+
+
 def gdn_block_torch(inp, conv_w, dt_bias, a_log, norm_w, *, nk, nv, dk, dv, eps, chunk=64,
-                    state=None):
+                    state=None, cp=None):
     """Differentiable dense GDN block on ``inp [B, T, rows]`` (zero initial state
     and zero conv history): the autograd twin of the serving kernels."""
+    if cp is not None:
+        return _gdn_block_cp(inp, conv_w, dt_bias, a_log, norm_w, nk=nk, nv=nv, dk=dk, dv=dv, eps=eps,
+                             chunk=chunk, cp=cp)
     b, t, _ = inp.shape
     q_raw, k_raw, v_raw, z, a, bb = ref.gdn_split(inp.float(), nk=nk, nv=nv, dk=dk, dv=dv)
     qkv = torch.cat([q_raw, k_raw, v_raw], -1)
