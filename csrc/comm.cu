@@ -34,7 +34,8 @@ namespace {
 
 constexpr int MAX_RANKS = 8;
 constexpr int ONESHOT_ROWS = 8;
-constexpr long long WAIT_CYCLES = 4000000000LL;
+// limit of every device-side wait, in SM clock cycles (~2 s by default; settable for tests)
+__device__ long long g_comm_wait_cycles = 4000000000LL;
 constexpr size_t OFF_FLAGS = 4096, OFF_AMAX = 8192, OFF_SLOTS = 65536;
 
 struct Peers {
@@ -56,7 +57,7 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t want, int 
   const long long t0 = clock64();
   for (uint32_t it = 0;; ++it) {
     if ((int32_t)(ld_acquire_sys(p) - want) >= 0) return true;
-    if ((it & 15) == 15 && clock64() - t0 > WAIT_CYCLES) {
+    if ((it & 15) == 15 && clock64() - t0 > g_comm_wait_cycles) {
       trl_set_error(TRL_ERR_WAIT_TIMEOUT, code_a, code_b, (int)want);
       return false;
     }
@@ -306,4 +307,10 @@ TRL_API int trl_argmax_tp(void* const* ws, int rank, int world, int hmax, const 
   return (int)trl_launch(argmax_tp_kernel, dim3(1), dim3(256), 0, (cudaStream_t)stream,
                          make_peers(ws, rank, world, hmax), (const float*)pv, (const int*)pi, chunks, v_local,
                          (int*)out, M);
+}
+
+// Limit of the bounded waits of the kernels in this file, in milliseconds at 2 GHz.
+TRL_API int trl_comm_set_wait_ms(int ms) {
+  const long long cycles = (long long)ms * 2000000LL;
+  return (int)cudaMemcpyToSymbol(g_comm_wait_cycles, &cycles, sizeof(cycles));
 }

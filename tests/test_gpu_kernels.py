@@ -226,3 +226,49 @@ def test_lora_add_kernel(norm):
         xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * nw
     want = y0.float() + 2.0 * (xf @ a.t()) @ b.t()
     assert float((y.float() - want).abs().max()) < 0.03 * float(want.abs().max())
+
+
+def test_bounded_device_wait_returns_a_status_and_leaves_the_context_usable():
+    """A peer flag that nothing sets: the all-reduce finish kernel gives up after its (shortened)
+    limit, records the error word and returns; the next kernel runs normally."""
+    import ctypes
+
+    from tilerl_b200.factory import make_ops
+    from tilerl_b200.ops import native as N
+    from tilerl_b200.parallel import symm  # registers the comm signatures  # noqa: F401
+    ops = make_ops("cuda")
+    lib = N.lib()
+    N.register("trl_comm_set_wait_ms", [N.I])
+    for fn in ("trl_symm_bytes",):
+        getattr(lib, fn).restype = ctypes.c_size_t
+    hmax = 256
+    nbytes = lib.trl_symm_bytes(hmax, 16)
+    p = ctypes.c_void_p()
+    N.check(lib.trl_symm_alloc(nbytes, ctypes.byref(p)), "alloc")
+    try:
+        N.check(lib.trl_comm_set_wait_ms(200), "set_wait")
+        table = (ctypes.c_void_p * 8)(p.value, p.value, *([None] * 6))   # "world 2", nobody ever pushes
+        res = torch.zeros(1, hmax, dtype=torch.bfloat16, device="cuda")
+        out = torch.zeros_like(res)
+        N.read_error()                                                    # clear
+        t0 = __import__("time").time()
+        N.check(lib.trl_allreduce_finish(table, 0, 2, hmax, res.data_ptr(), res.stride(0), out.data_ptr(),
+                                         out.stride(0), 1, hmax, N.stream()), "finish")
+        torch.cuda.synchronize()
+        assert __import__("time").time() - t0 < 5.0
+        code, a, b, c = N.read_error()
+        assert code != 0 and a == 1, (code, a, b, c)                      # wait site 1 = one-shot flags
+        from tilerl_b200.parallel.health import CommTimeout, raise_on_device_error
+        with pytest.raises(CommTimeout):
+            raise_on_device_error(lambda: (code, a, b, c))
+        # the context is alive: an ordinary kernel still runs and is correct
+        x = torch.randn(4, 512, device="cuda").to(torch.bfloat16)
+        w = torch.ones(512, device="cuda")
+        y = ops._rmsnorm(x, w, 1e-6)
+        torch.cuda.synchronize()
+        ref_y = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6)
+        assert float((y.float() - ref_y).abs().max()) < 0.05
+        assert N.read_error()[0] == 0
+    finally:
+        lib.trl_comm_set_wait_ms(2000)
+        lib.trl_symm_free(p)

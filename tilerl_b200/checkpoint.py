@@ -29,6 +29,7 @@ from __future__ import annotations
 
 import json
 import os
+import zlib
 from typing import Dict, Optional
 
 import torch
@@ -288,12 +289,24 @@ def save_train_state(path: str, rank: int, *, params: Dict[str, torch.Tensor], o
         blob["rng_cuda"] = torch.cuda.get_rng_state()
     fn = os.path.join(path, f"rank{rank:03d}.pt")
     torch.save(blob, fn + ".tmp")
+    with open(fn + ".tmp", "rb") as f:
+        data = f.read()
+    with open(fn + ".crc.tmp", "w") as f:      # integrity sidecar: size and CRC32 of the shard
+        json.dump({"nbytes": len(data), "crc32": zlib.crc32(data)}, f)
     os.replace(fn + ".tmp", fn)
+    os.replace(fn + ".crc.tmp", fn + ".crc")
     return fn
 
 
 def load_train_state(path: str, rank: int, *, params: Dict[str, torch.Tensor], optimizer=None) -> Dict:
     fn = os.path.join(path, f"rank{rank:03d}.pt")
+    if os.path.exists(fn + ".crc"):
+        with open(fn + ".crc") as f:
+            want = json.load(f)
+        with open(fn, "rb") as f:
+            data = f.read()
+        if len(data) != want["nbytes"] or zlib.crc32(data) != want["crc32"]:
+            raise CheckpointError(f"{fn}: size or CRC32 does not match its sidecar (corrupt shard)")
     blob = torch.load(fn, map_location="cpu", weights_only=False)
     for k, v in blob["params"].items():
         if k not in params:
