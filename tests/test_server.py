@@ -229,3 +229,20 @@ def test_stream_pacing():
     t[0] = 1.0
     assert "".join(first + p.pop_ready()) == "bcde"
     assert Pacer(enabled=False).pop_ready() == []
+
+
+def test_web_client_modules_are_served(served):
+    eng, app = served
+
+    async def go():
+        async with _client(app) as client:
+            page = await client.get("/chat")
+            assert page.status_code == 200 and "/static/main.js" in page.text
+            for mod in ("protocol.js", "transport.js", "streamBuffer.js", "render.js", "meter.js", "main.js"):
+                r = await client.get("/static/" + mod)
+                assert r.status_code == 200 and ("export" in r.text or "import" in r.text), mod
+            proto = (await client.get("/static/protocol.js")).text
+            for frame in ("delta", "tool_calls", "done", "error"):
+                assert f'"{frame}"' in proto
+
+    run(go())

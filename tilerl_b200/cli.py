@@ -47,6 +47,7 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--stream-pace", action="store_true")
     s.add_argument("--no-warmup", action="store_true")
     s.add_argument("--dry-run", action="store_true", help="print the memory ledger and exit")
+    s.add_argument("--no-card-guard", action="store_true", help="start even if other processes hold the GPU")
 
     t = sub.add_parser("train", help="SFT / GRPO / on-policy distillation")
     _add_model_flags(t)
@@ -123,6 +124,12 @@ def cmd_serve(args) -> int:
     from .server.app import create_app
     from .tokenizer import load_tokenizer
     dev = _device(args)
+    if dev != "cpu" and not args.no_card_guard:
+        try:
+            from .parallel.health import card_guard
+            card_guard(0)
+        except ImportError:
+            pass                      # no NVML binding in this environment: nothing to check with
     ops = make_ops(dev)
     model = build_model(cfg, dev, seed=args.seed, checkpoint=args.checkpoint, ops=ops if dev != "cpu" else None)
     drafter = None

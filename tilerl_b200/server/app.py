@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import asyncio
 import json
+import os
 import time
 from typing import Any, Dict, List, Optional
 
@@ -143,9 +144,19 @@ def create_app(engine, tokenizer, model_name: str = "tilerl-b200", *, pace: bool
     async def landing():
         return LANDING
 
+    static_dir = os.path.join(os.path.dirname(os.path.abspath(__file__)), "static")
+
     @app.get("/chat", response_class=HTMLResponse)
     async def chat_page():
-        return CHAT_PAGE
+        index = os.path.join(static_dir, "index.html")
+        if os.path.exists(index):           # the modular client (ES modules under /static/)
+            with open(index, encoding="utf-8") as f:
+                return f.read()
+        return CHAT_PAGE                     # single-file fallback
+
+    if os.path.isdir(static_dir):
+        from fastapi.staticfiles import StaticFiles
+        app.mount("/static", StaticFiles(directory=static_dir), name="static")
 
     @app.post("/v1/chat/completions")
     async def chat(request: Request):
