@@ -54,3 +54,11 @@ def test_generate_and_merge(tmp_path, capsys):
 def test_unknown_recipe():
     with pytest.raises(KeyError):
         cli.main(["train", "--recipe", "nope", "--device", "cpu"])
+
+
+def test_train_indexer_warmup(tmp_path, capsys):
+    out = str(tmp_path / "ix")
+    assert cli.main(["train", "--model", "tiny-hybrid", "--indexer-warmup", "--steps", "3", "--ctx", "96",
+                     "--save-model", out, "--runs", str(tmp_path / "r"), "--device", "cpu"]) == 0
+    rec = json.loads([l for l in capsys.readouterr().out.splitlines() if l.startswith("{")][-1])
+    assert rec["steps"] == 3 and os.path.exists(os.path.join(out, "indexer.safetensors"))

@@ -102,3 +102,32 @@ def test_daemon_loop_and_peek():
     eng.stop()
     assert done and len(eng.take(rid).tokens) == 5
     assert eng.liveness()["last_progress_age_s"] == 0.0
+
+
+def test_fp8_kv_pool_serves_close_to_bf16_and_halves_the_pool():
+    """fp8 KV (e4m3 + one fp32 scale per token and head): same greedy tokens on the tiny model's
+    first steps, logits within the fp8 rounding, pool bytes per block ~half of fp32/2."""
+    import torch
+    from tilerl_b200.batch import Batch
+    from tilerl_b200.kv import GdnStatePool, PagedKvPool
+    from tilerl_b200.models.hybrid import HybridModel
+    from tilerl_b200.ops.backend import RefOps
+    cfg = tiny_hybrid()
+    model = HybridModel.build_random(cfg, seed=2)
+    ops = RefOps()
+    outs = []
+    for fp8 in (False, True):
+        kv = PagedKvPool(cfg, 8, dtype=torch.float32, fp8=fp8)
+        st = GdnStatePool(cfg, 4, ring_dtype=torch.float32)
+        seqs = [dict(tokens=list(range(3, 27)), start=0, blocks=[1, 2], slot=1)]
+        lg1 = model.forward(Batch.build(seqs, "cpu"), ops, kv, st).float().clone()
+        lg2 = model.forward(Batch.build([dict(tokens=[5], start=24, blocks=[1, 2], slot=1)], "cpu"), ops, kv, st).float()
+        outs.append((lg1, lg2.clone(), kv.block_bytes()))
+    rel = float((outs[1][1] - outs[0][1]).norm() / outs[0][1].norm())
+    assert 0 < rel < 0.05, rel
+    assert outs[1][0].argmax(-1).tolist() == outs[0][0].argmax(-1).tolist()
+    assert outs[1][2] < 0.4 * outs[0][2]            # fp8 + scales vs the fp32 oracle pool
+    k, v = kv.read_block(1)
+    kv.write_block(3, k, v)
+    k2, _ = kv.read_block(3)
+    assert float((k2 - k).abs().max()) <= 0.07 * float(k.abs().max()) + 1e-6

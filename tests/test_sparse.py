@@ -50,3 +50,46 @@ def test_truly_sparse_run_is_well_formed():
     eng = make_engine(cfg, blocks=200, sparse=mgr)
     out = eng.generate(rand_prompts(cfg, 1, 90, seed=2), SamplingParams(max_tokens=6))[0]
     assert len(out.tokens) == 6 and eng.kv.used_blocks == 0 and not mgr._sel
+
+
+def test_learned_indexer_warmup_lowers_the_kl_to_the_dense_page_mass():
+    import torch
+    from tilerl_b200.config import tiny_hybrid
+    from tilerl_b200.models.hybrid import HybridModel
+    from tilerl_b200.sparse_index import LearnedIndexer, page_mass, topk_recall, warmup
+    cfg = tiny_hybrid()
+    model = HybridModel.build_random(cfg, seed=4)
+    g = torch.Generator().manual_seed(0)
+    seqs = [torch.randint(0, cfg.vocab, (192,), generator=g) for _ in range(3)]
+    ix = LearnedIndexer(cfg, heads=2, dim=16, seed=1)
+    hist = warmup(model, ix, seqs[1:], steps=60, lr=3e-3, queries_per_seq=6)
+    assert sum(hist[-10:]) < 0.85 * sum(hist[:10]), (hist[:3], hist[-3:])
+    # the teacher is a distribution over pages; recall of all pages is the whole mass
+    q, k = torch.randn(4, 64), torch.randn(40, 2, 64)
+    m = page_mass(q, k, 39)
+    assert m.shape == (3,) and abs(float(m.sum()) - 1.0) < 1e-5
+    full = topk_recall(model, ix, seqs[0], top_k=64)
+    assert abs(full - 1.0) < 1e-4
+    sd = ix.state_dict()
+    ix2 = LearnedIndexer(cfg, heads=2, dim=16, seed=9)
+    ix2.load_state_dict(sd)
+    assert abs(topk_recall(model, ix2, seqs[0], top_k=3) - topk_recall(model, ix, seqs[0], top_k=3)) < 1e-6
+
+
+def test_sparse_engine_accepts_a_learned_indexer():
+    import torch
+    from helpers import make_engine, rand_prompts
+    from tilerl_b200.config import tiny_hybrid
+    from tilerl_b200.engine import SamplingParams
+    from tilerl_b200.sparse import SparseConfig, SparseKV
+    from tilerl_b200.sparse_index import LearnedIndexer
+    cfg = tiny_hybrid()
+    ix = LearnedIndexer(cfg, heads=2, dim=16)
+    sp = SparseKV(cfg, SparseConfig(top_k=64, window=2, refresh_ticks=2, min_tokens=32), indexer=ix)
+    dense = make_engine(cfg)
+    eng = make_engine(cfg, sparse=sp)
+    p = rand_prompts(cfg, 1, 80)
+    want = dense.generate(p, SamplingParams(max_tokens=6))[0].tokens
+    # k covers every page: the learned scorer may order them freely, the result equals dense
+    assert eng.generate(p, SamplingParams(max_tokens=6))[0].tokens == want
+    assert sp.stats["sparse_ticks"] > 0

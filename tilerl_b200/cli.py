@@ -7,6 +7,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 from typing import List, Optional
 
@@ -70,6 +71,8 @@ def build_parser() -> argparse.ArgumentParser:
     t.add_argument("--save-model", default=None)
     t.add_argument("--load-adapter", default=None)
     t.add_argument("--served-fp4", action="store_true")
+    t.add_argument("--indexer-warmup", action="store_true", help="train the learned sparse-KV page indexer")
+    t.add_argument("--ctx", type=int, default=None, help="sequence length of the indexer warm-up batches")
     t.add_argument("--runs", default="runs")
 
     b = sub.add_parser("bench", help="prefill / decode throughput, kernel roofline table, calibration")
@@ -170,6 +173,10 @@ def cmd_train(args) -> int:
     from .recipes import expand
     over = {k: getattr(args, k) for k in ("steps", "group", "prompts_per_step", "max_tokens", "micro", "lora_rank",
                                           "lr", "optim", "reward")}
+    if args.indexer_warmup:
+        over["indexer_warmup"] = True
+    if args.ctx:
+        over["ctx"] = args.ctx
     if args.rl:
         over["rl"] = True
     if args.opd:
@@ -180,6 +187,26 @@ def cmd_train(args) -> int:
                                                                   opd=args.opd),
                                                            **{k: v for k, v in over.items() if v is not None}}
     cfg = get_config(flags.get("model", args.model))
+    if flags.get("indexer_warmup"):
+        # the warm-up runs the dense model on the reference backend and trains only the indexer
+        from .factory import build_model as _bm
+        from .sparse_index import LearnedIndexer, warmup
+        model = _bm(cfg, "cpu", seed=args.seed, checkpoint=args.checkpoint)
+        ix = LearnedIndexer(cfg, seed=args.seed)
+        g = torch.Generator().manual_seed(args.seed)
+        seqs = [torch.randint(0, cfg.vocab, (flags.get("ctx") or 256,), generator=g) for _ in range(4)]
+        run = Run({"cmd": "train", **flags}, root=args.runs)
+        hist = warmup(model, ix, seqs, steps=flags["steps"], lr=flags.get("lr") or 3e-3)
+        for i, kl in enumerate(hist):
+            run.log(step=i, kl=kl)
+        print(json.dumps({"kl_first": hist[0], "kl_last": hist[-1], "steps": len(hist)}))
+        if args.save_model:
+            from safetensors.torch import save_file
+            os.makedirs(args.save_model, exist_ok=True)
+            save_file(ix.state_dict(), os.path.join(args.save_model, "indexer.safetensors"))
+            run.artifacts["indexer"] = args.save_model
+        run.finish()
+        return 0
     dev = _device(args)
     ops = make_ops(dev)
     model = build_model(cfg, dev, seed=args.seed, checkpoint=args.checkpoint, ops=ops if dev != "cpu" else None,

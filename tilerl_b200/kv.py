@@ -90,9 +90,19 @@ class PagedKvPool:
 
     # ---- host tier hooks -------------------------------------------------------
     def read_block(self, b: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        if self.fp8:     # tiers move the dequantised page; the scales are re-derived on the way back
+            return (self.k[:, b].float() * self.k_scale[:, b].unsqueeze(-1),
+                    self.v[:, b].float() * self.v_scale[:, b].unsqueeze(-1))
         return self.k[:, b].clone(), self.v[:, b].clone()
 
     def write_block(self, b: int, k: torch.Tensor, v: torch.Tensor) -> None:
+        if self.fp8:
+            from .formats import quantize_kv_fp8
+            k8, ks = quantize_kv_fp8(k.float())
+            v8, vs = quantize_kv_fp8(v.float())
+            self.k[:, b].copy_(k8), self.v[:, b].copy_(v8)
+            self.k_scale[:, b].copy_(ks), self.v_scale[:, b].copy_(vs)
+            return
         self.k[:, b].copy_(k)
         self.v[:, b].copy_(v)
 

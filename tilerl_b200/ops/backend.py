@@ -79,7 +79,12 @@ class RefOps:
             head_dim=cfg.head_dim, rotary_dim=cfg.rotary_dim, theta=cfg.rope_theta,
             eps=cfg.rms_eps, gated=cfg.attn_gated)
         kc, vc = pool.layer(attn_idx)
-        ref.kv_write(kc, vc, k, v, batch.slot_mapping)
+        if getattr(pool, "fp8", False):
+            ref.kv_write_fp8(kc, vc, pool.k_scale[attn_idx], pool.v_scale[attn_idx], k, v, batch.slot_mapping)
+            kc = ref.kv_dequant_fp8(kc, pool.k_scale[attn_idx])
+            vc = ref.kv_dequant_fp8(vc, pool.v_scale[attn_idx])
+        else:
+            ref.kv_write(kc, vc, k, v, batch.slot_mapping)
         scale = 1.0 / math.sqrt(cfg.head_dim)
         table, pos = batch.block_table, batch.positions
         sp = batch.sparse

@@ -201,6 +201,9 @@ class CudaOps:
         return residual
 
     def attention(self, qkv, lp, batch, pool, attn_idx, cfg, n_q, n_kv):
+        if getattr(pool, "fp8", False):
+            raise NotImplementedError("the CUDA attention kernels read a bf16 KV pool; fp8 KV is served by the "
+                                      "reference backend only")
         t = qkv.shape[0]
         d = cfg.head_dim
         q = self.ws.get("q", (t, n_q, d), torch.bfloat16)

@@ -87,6 +87,28 @@ def attn_prep(qkv, q_norm_w, k_norm_w, positions, *, n_q, n_kv, head_dim, rotary
     return q, gate, k, v.clone()
 
 
+def kv_write_fp8(kcache, vcache, kscale, vscale, k, v, slot_mapping):
+    """fp8 KV: e4m3 values with one fp32 scale per (token, head) = amax / 448 (K taken after
+    RoPE).  Pools ``[blocks, hkv, 16, D]`` fp8, scales ``[blocks, hkv, 16]``."""
+    from ..formats import quantize_kv_fp8
+    k8, ks = quantize_kv_fp8(k)
+    v8, vs = quantize_kv_fp8(v)
+    for t in range(k.shape[0]):
+        s = int(slot_mapping[t])
+        if s < 0:
+            continue
+        b, o = divmod(s, KV_BLOCK)
+        kcache[b, :, o] = k8[t]
+        vcache[b, :, o] = v8[t]
+        kscale[b, :, o] = ks[t]
+        vscale[b, :, o] = vs[t]
+
+
+def kv_dequant_fp8(cache, scale):
+    """The fp32 view of an fp8 pool layer (oracle path: the kernels dequantise at the gather)."""
+    return cache.float() * scale.unsqueeze(-1)
+
+
 def kv_write(kcache, vcache, k, v, slot_mapping):
     """Scatter token rows into the paged pools ``[blocks, hkv, 16, D]``;
     ``slot_mapping[t] = block * 16 + offset`` (negative = skip)."""

@@ -100,10 +100,12 @@ class _View:
 
 
 class SparseKV:
-    def __init__(self, cfg, config: Optional[SparseConfig] = None, score_fn: Optional[Callable] = None):
+    def __init__(self, cfg, config: Optional[SparseConfig] = None, score_fn: Optional[Callable] = None,
+                 indexer=None):
         self.cfg = cfg
         self.c = config or SparseConfig()
         self.score_fn = score_fn or quest_scores
+        self.indexer = indexer            # a sparse_index.LearnedIndexer replaces the Quest bound
         self._sel: Dict[Tuple[int, int], torch.Tensor] = {}     # (rid, layer) -> kept early pages
         self._age: Dict[Tuple[int, int], int] = {}
         self._early: Dict[Tuple[int, int], int] = {}
@@ -143,8 +145,10 @@ class SparseKV:
         cached = self._sel.get(key)
         if cached is None or age >= self.c.refresh_ticks:
             if early > 0 and self.c.top_k > 0:
-                bounds = self.page_bounds(kcache, table[:early])
-                scores = self.score_fn(q, bounds)
+                if self.indexer is not None:
+                    scores = self.indexer.scores(layer, q, kcache, table[:early])
+                else:
+                    scores = self.score_fn(q, self.page_bounds(kcache, table[:early]))
                 k = min(self.c.top_k, early)
                 cached = torch.sort(torch.topk(scores, k).indices).values
             else:
