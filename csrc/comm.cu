@@ -7,15 +7,15 @@
 //                          [32] two-shot epoch, [48] argmax epoch
 //   flags  [4 KiB, 8 KiB)  u32: oneshot[2 bufs][8 src] @0, ready[8] @64, done[8] @96, amax[8] @128
 //   amax   [8 KiB, 64 KiB) per source rank: (value, index) pairs for up to 256 rows
-//   slots  [64 KiB, ...)   one-shot partials  fp32 [2 bufs][8 src][8 rows][hmax]
+//   slots  [64 KiB, ...)   one-shot partials  {fp32, epoch} [2 bufs][8 src][8 rows][hmax]
 //   big    [...]           two-shot operand   bf16 [tmax][hmax]
 //
 // * One-shot all-reduce (decode sizes): the row-parallel GEMV pushes its fp32 partial rows
-//   straight into slot [buf][my_rank] of EVERY peer from its epilogue (plain st.global over
-//   NVLink, overlapping the weight stream), the last CTA publishes an epoch flag to every
-//   peer, and `allreduce_finish` on each rank waits for all flags, sums the partials in
-//   rank order (bitwise identical on every rank), adds the residual and writes the
-//   residual stream.  Two buffers alternate by epoch parity; the epoch lives in device
+//   straight into slot [buf][my_rank] of EVERY peer from its epilogue as {value, epoch} pairs,
+//   one 8-byte store each over NVLink (overlapping the weight stream; no fence, counter or
+//   flag stage), and `allreduce_finish` on each rank polls the epoch half of the words it
+//   needs, sums the partials in rank order (bitwise identical on every rank), adds the
+//   residual and writes the residual stream.  Two buffers alternate by epoch parity; the epoch lives in device
 //   memory and is advanced by the finish kernel, so the sequence is CUDA-graph replayable.
 // * Two-shot all-reduce (prefill sizes): every rank reduces its 1/tp slice of the rows by
 //   reading all peers' partials (reduce-scatter), adds the residual and writes the slice
@@ -64,19 +64,14 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t want, int 
   }
 }
 
-__device__ __forceinline__ float* oneshot_slot(unsigned char* ws, int buf, int src, int hmax) {
-  return reinterpret_cast<float*>(ws + OFF_SLOTS) + ((size_t)(buf * MAX_RANKS + src) * ONESHOT_ROWS) * hmax;
+// One-shot slots hold {fp32 value, epoch} pairs (8 bytes, written by one store).
+__device__ __forceinline__ uint2* oneshot_slot(unsigned char* ws, int buf, int src, int hmax) {
+  return reinterpret_cast<uint2*>(ws + OFF_SLOTS) + ((size_t)(buf * MAX_RANKS + src) * ONESHOT_ROWS) * hmax;
 }
 
-// Publish "rank `me` finished pushing epoch e" to every peer.  Called by one thread of the
-// last CTA of the pushing kernel.
-__device__ __forceinline__ void oneshot_publish(const Peers& P, uint32_t epoch) {
-  const int buf = epoch & 1;
-  for (int p = 0; p < P.world; ++p)
-    st_release_sys(reinterpret_cast<uint32_t*>(P.ws[p] + OFF_FLAGS) + buf * MAX_RANKS + P.rank, epoch);
-}
-
-// x[m, n] = residual[m, n] + sum_src partial[src][m][n]; advances the epoch.
+// x[m, n] = residual[m, n] + sum_src partial[src][m][n]; advances the epoch.  Every thread
+// polls the epoch half of exactly the words it sums (bounded), so the sum of an element starts
+// as soon as its last partial has landed.
 __global__ void __launch_bounds__(256)
 allreduce_finish_kernel(const Peers P, const bf16* __restrict__ residual, int ldr, bf16* __restrict__ out,
                         int ldo, int M, int N) {
@@ -86,26 +81,30 @@ allreduce_finish_kernel(const Peers P, const bf16* __restrict__ residual, int ld
   uint32_t* ctrl = reinterpret_cast<uint32_t*>(me);
   const uint32_t epoch = ctrl[0] + 1;
   const int buf = epoch & 1;
-  const uint32_t* flags = reinterpret_cast<const uint32_t*>(me + OFF_FLAGS) + buf * MAX_RANKS;
-  __shared__ int ok_s;
-  if (threadIdx.x == 0) ok_s = 1;
-  __syncthreads();
-  if (threadIdx.x < P.world) {
-    if (!wait_flag(flags + threadIdx.x, epoch, 1, threadIdx.x)) ok_s = 0;
-  }
-  __syncthreads();
-  if (ok_s) {
-    const int total = M * N;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-      const int m = i / N, n = i % N;
-      float v = 0.f;
-      for (int s = 0; s < P.world; ++s) v += __ldcg(oneshot_slot(me, buf, s, P.hmax) + (size_t)m * P.hmax + n);
-      v += __bfloat162float(residual[(size_t)m * ldr + n]);
-      out[(size_t)m * ldo + n] = __float2bfloat16(v);
+  const int total = M * N;
+  bool ok = true;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; ok && i < total; i += gridDim.x * blockDim.x) {
+    const int m = i / N, n = i % N;
+    float v = __bfloat162float(residual[(size_t)m * ldr + n]);
+    for (int s = 0; ok && s < P.world; ++s) {
+      const uint2* w = oneshot_slot(me, buf, s, P.hmax) + (size_t)m * P.hmax + n;
+      uint2 x = ld_relaxed_sys_v2(w);
+      if (x.y != epoch) {
+        const long long t0 = clock64();
+        for (uint32_t it = 0; x.y != epoch; ++it) {
+          x = ld_relaxed_sys_v2(w);
+          if ((it & 15) == 15 && clock64() - t0 > g_comm_wait_cycles) {
+            trl_set_error(TRL_ERR_WAIT_TIMEOUT, 1, s, (int)epoch);
+            ok = false;
+            break;
+          }
+        }
+      }
+      v += __uint_as_float(x.x);
     }
+    if (ok) out[(size_t)m * ldo + n] = __float2bfloat16(v);
   }
-  // the last CTA to finish advances the epoch (all CTAs read ctrl[0] before any can get here
-  // only if they have passed the wait; a separate done counter orders that)
+  // the last CTA to finish advances the epoch
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
@@ -256,13 +255,13 @@ Peers make_peers(void* const* ws, int rank, int world, int hmax) {
 }  // namespace
 
 TRL_API size_t trl_symm_out_offset(int hmax, int tmax) {
-  return OFF_SLOTS + (size_t)2 * MAX_RANKS * ONESHOT_ROWS * hmax * sizeof(float) + (size_t)tmax * hmax * sizeof(bf16);
+  return OFF_SLOTS + (size_t)2 * MAX_RANKS * ONESHOT_ROWS * hmax * sizeof(uint2) + (size_t)tmax * hmax * sizeof(bf16);
 }
 TRL_API size_t trl_symm_bytes(int hmax, int tmax) {
-  return OFF_SLOTS + (size_t)2 * MAX_RANKS * ONESHOT_ROWS * hmax * sizeof(float) + (size_t)2 * tmax * hmax * sizeof(bf16);
+  return OFF_SLOTS + (size_t)2 * MAX_RANKS * ONESHOT_ROWS * hmax * sizeof(uint2) + (size_t)2 * tmax * hmax * sizeof(bf16);
 }
 TRL_API size_t trl_symm_big_offset(int hmax) {
-  return OFF_SLOTS + (size_t)2 * MAX_RANKS * ONESHOT_ROWS * hmax * sizeof(float);
+  return OFF_SLOTS + (size_t)2 * MAX_RANKS * ONESHOT_ROWS * hmax * sizeof(uint2);
 }
 TRL_API int trl_symm_alloc(size_t bytes, void** out) {
   cudaError_t e = cudaMalloc(out, bytes);

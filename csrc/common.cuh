@@ -82,6 +82,18 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x))
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
 
+// 8-byte store visible system-wide as one unit (value + epoch pairs of the one-shot all-reduce)
+// (a single 64-bit scalar access: single-copy atomic by the PTX memory model)
+__device__ __forceinline__ void st_relaxed_sys_v2(void* p, uint2 v) {
+  const unsigned long long w = ((unsigned long long)v.y << 32) | (unsigned long long)v.x;
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ uint2 ld_relaxed_sys_v2(const void* p) {
+  unsigned long long w;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+  return make_uint2((uint32_t)w, (uint32_t)(w >> 32));
+}
+
 // ---- streaming loads -----------------------------------------------------------------------
 __device__ __forceinline__ uint4 ldg_stream_16(const void* p) {
   uint4 v;

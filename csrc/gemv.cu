@@ -216,9 +216,13 @@ gemv_nvfp4_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict
         if (n < N) {
           if (EPI == EPI_PUSH) {
             // fp32 partial row straight into every rank's all-reduce slot (NVLink stores)
+            // {value, epoch} in ONE 8-byte store per peer: the receiver polls the epoch half of
+            // the word it needs, so no fence, counter or separate flag sits between the last
+            // weight byte and the peer's sum
             const uint32_t epoch = *reinterpret_cast<const uint32_t*>(push.ws[push.rank]) + 1;
-            const size_t off = 65536 + ((size_t)(((epoch & 1) * 8 + push.rank) * 8 + push.row0 + m) * push.hmax + n) * 4;
-            for (int p = 0; p < push.world; ++p) *reinterpret_cast<float*>(push.ws[p] + off) = v;
+            const size_t off = 65536 + ((size_t)(((epoch & 1) * 8 + push.rank) * 8 + push.row0 + m) * push.hmax + n) * 8;
+            const uint2 word = make_uint2(__float_as_uint(v), epoch);
+            for (int p = 0; p < push.world; ++p) st_relaxed_sys_v2(push.ws[p] + off, word);
           } else {
             if (EPI == EPI_RESIDUAL) v += __bfloat162float(residual[(size_t)m * ldr + n]);
             if (EPI == EPI_STORE_F32)
@@ -227,22 +231,6 @@ gemv_nvfp4_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict
               reinterpret_cast<bf16*>(yout)[(size_t)m * ldy + n] = __float2bfloat16(v);
           }
         }
-      }
-    }
-  }
-  if (EPI == EPI_PUSH && ldy != 0) {
-    // ldy != 0 marks the last row chunk: when every CTA has pushed, publish the epoch flag
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence_system();
-      uint32_t* ctrl = reinterpret_cast<uint32_t*>(push.ws[push.rank]);
-      const uint32_t epoch = ctrl[0] + 1;
-      const uint32_t prev = atomicAdd(ctrl + 16, 1u);
-      if (prev == gridDim.x - 1) {
-        ctrl[16] = 0;
-        __threadfence_system();
-        for (int p = 0; p < push.world; ++p)
-          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(reinterpret_cast<uint32_t*>(push.ws[p] + 4096) + (epoch & 1) * 8 + push.rank), "r"(epoch) : "memory");
       }
     }
   }
@@ -408,30 +396,15 @@ gemv_nvfp4_sk_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restr
       v *= ts * xs_inv[m];
       if (EPI == EPI_PUSH) {
         const uint32_t epoch = *reinterpret_cast<const uint32_t*>(push.ws[push.rank]) + 1;
-        const size_t off = 65536 + ((size_t)(((epoch & 1) * 8 + push.rank) * 8 + push.row0 + m) * push.hmax + n) * 4;
-        for (int p = 0; p < push.world; ++p) *reinterpret_cast<float*>(push.ws[p] + off) = v;
+        const size_t off = 65536 + ((size_t)(((epoch & 1) * 8 + push.rank) * 8 + push.row0 + m) * push.hmax + n) * 8;
+        const uint2 word = make_uint2(__float_as_uint(v), epoch);
+        for (int p = 0; p < push.world; ++p) st_relaxed_sys_v2(push.ws[p] + off, word);
       } else {
         if (EPI == EPI_RESIDUAL) v += __bfloat162float(residual[(size_t)m * ldr + n]);
         if (EPI == EPI_STORE_F32)
           reinterpret_cast<float*>(yout)[(size_t)m * ldy + n] = v;
         else
           reinterpret_cast<bf16*>(yout)[(size_t)m * ldy + n] = __float2bfloat16(v);
-      }
-    }
-  }
-  if (EPI == EPI_PUSH && ldy != 0) {
-    // ldy != 0 marks the last row chunk: when every CTA has pushed, publish the epoch flag
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence_system();
-      uint32_t* ctrl = reinterpret_cast<uint32_t*>(push.ws[push.rank]);
-      const uint32_t epoch = ctrl[0] + 1;
-      const uint32_t prev = atomicAdd(ctrl + 16, 1u);
-      if (prev == gridDim.x - 1) {
-        ctrl[16] = 0;
-        __threadfence_system();
-        for (int p = 0; p < push.world; ++p)
-          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(reinterpret_cast<uint32_t*>(push.ws[p] + 4096) + (epoch & 1) * 8 + push.rank), "r"(epoch) : "memory");
       }
     }
   }

@@ -5,8 +5,9 @@
 // parallel workspace):
 //
 //   ctrl   [0, 4 KiB)   u32: [0] epoch, [1] CTA-done counter; flags ready[8] @256, done[8] @288
-//   data   [4 KiB, ..)  staging: the rank's bf16 parameter shard (all-gather) or its full flat
-//                       gradient of the current unit (reduce-scatter)
+//   data   [4 KiB, ..)  staging areas (byte offsets are call arguments): the rank's parameter
+//                       shard in the working dtype (all-gather) and its full flat gradient of the
+//                       current unit (reduce-scatter)
 //
 // * all-gather: after a ready handshake every rank copies each peer's shard out of that peer's
 //   staging area into its own full buffer with 16-byte peer loads.
@@ -92,16 +93,23 @@ __device__ __forceinline__ void z_done(const ZPeers& P, uint32_t epoch, int* las
   }
 }
 
+// Four independent 16-byte peer loads per thread and pass: NVLink latency is ~2 us, so the
+// bytes in flight, not the instruction count, set the rate.
 __global__ void __launch_bounds__(512)
-zero_allgather_kernel(const ZPeers P, long shard_vecs, uint4* __restrict__ dst) {
+zero_allgather_kernel(const ZPeers P, size_t off, long shard_vecs, uint4* __restrict__ dst) {
   __shared__ int ok_s, last_s;
   const uint32_t epoch = reinterpret_cast<const uint32_t*>(P.ws[P.rank])[0] + 1;
   if (z_ready(P, epoch, &ok_s)) {
-    const long total = shard_vecs * P.world;
-    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
-      const int p = (int)(i / shard_vecs);
-      const long j = i - (long)p * shard_vecs;
-      dst[i] = reinterpret_cast<const uint4*>(P.ws[p] + Z_OFF_DATA)[j];   // peer load over NVLink
+    const long stride = (long)gridDim.x * blockDim.x;
+    for (int p = 0; p < P.world; ++p) {
+      const uint4* src = reinterpret_cast<const uint4*>(P.ws[p] + off);
+      uint4* d = dst + (long)p * shard_vecs;
+      long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+      for (; i + 3 * stride < shard_vecs; i += 4 * stride) {
+        const uint4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], e = src[i + 3 * stride];
+        d[i] = a, d[i + stride] = b, d[i + 2 * stride] = c, d[i + 3 * stride] = e;
+      }
+      for (; i < shard_vecs; i += stride) d[i] = src[i];
     }
   }
   z_done(P, epoch, &last_s);
@@ -109,7 +117,8 @@ zero_allgather_kernel(const ZPeers P, long shard_vecs, uint4* __restrict__ dst) 
 
 template <bool BF16>
 __global__ void __launch_bounds__(512)
-zero_reduce_scatter_kernel(const ZPeers P, long shard_elems, float scale, float* __restrict__ out, int accumulate) {
+zero_reduce_scatter_kernel(const ZPeers P, size_t off, long shard_elems, float scale, float* __restrict__ out,
+                           int accumulate) {
   __shared__ int ok_s, last_s;
   const uint32_t epoch = reinterpret_cast<const uint32_t*>(P.ws[P.rank])[0] + 1;
   if (z_ready(P, epoch, &ok_s)) {
@@ -120,8 +129,14 @@ zero_reduce_scatter_kernel(const ZPeers P, long shard_elems, float scale, float*
       float acc[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-      for (int s = 0; s < P.world; ++s) {
-        const uint4 v = reinterpret_cast<const uint4*>(P.ws[s] + Z_OFF_DATA + (size_t)P.rank * slice_bytes)[i];
+      uint4 vs[Z_MAX_RANKS];
+#pragma unroll
+      for (int s = 0; s < Z_MAX_RANKS; ++s)   // every peer's load is issued before the first use
+        if (s < P.world) vs[s] = reinterpret_cast<const uint4*>(P.ws[s] + off + (size_t)P.rank * slice_bytes)[i];
+#pragma unroll
+      for (int s = 0; s < Z_MAX_RANKS; ++s) {
+        if (s >= P.world) break;
+        const uint4 v = vs[s];
         if (BF16) {
           const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -152,31 +167,34 @@ ZPeers z_peers(void* const* ws, int rank, int world) {
 int z_grid(long work_items) {
   // a modest grid: these kernels run beside the layer's compute and their CTAs spin while a
   // peer is late; 64 CTAs of 16-byte loads are enough to fill one NVLink direction
-  return (int)max(1L, min(64L, (work_items + 511) / 512));
+  return (int)max(1L, min(128L, (work_items + 511) / 512));
 }
 
 }  // namespace
 
 TRL_API size_t trl_zero_data_offset() { return Z_OFF_DATA; }
 
-// dst (local, 16-byte aligned) receives world * shard_bytes: the staging areas of ranks 0..world-1.
-TRL_API int trl_zero_allgather(void* const* ws, int rank, int world, long shard_bytes, void* dst, void* stream) {
-  if (shard_bytes % 16 != 0 || world > Z_MAX_RANKS || world < 1) return (int)cudaErrorInvalidValue;
+// dst (local, 16-byte aligned) receives world * shard_bytes: the shards found at byte offset
+// `off` (16-byte aligned, >= trl_zero_data_offset()) of the regions of ranks 0..world-1.
+TRL_API int trl_zero_allgather(void* const* ws, int rank, int world, long off, long shard_bytes, void* dst,
+                               void* stream) {
+  if (shard_bytes % 16 != 0 || off % 16 != 0 || world > Z_MAX_RANKS || world < 1) return (int)cudaErrorInvalidValue;
   const long vecs = shard_bytes / 16;
-  zero_allgather_kernel<<<z_grid(vecs * world), 512, 0, (cudaStream_t)stream>>>(z_peers(ws, rank, world), vecs, (uint4*)dst);
+  zero_allgather_kernel<<<z_grid(vecs), 512, 0, (cudaStream_t)stream>>>(z_peers(ws, rank, world), (size_t)off, vecs,
+                                                                        (uint4*)dst);
   return (int)cudaGetLastError();
 }
 
-// Every rank's staging area holds its full flat gradient (world * shard_elems elements, bf16 or
-// fp32); out (fp32, shard_elems) = [out +] scale * sum over ranks of slice `rank`.
-TRL_API int trl_zero_reduce_scatter(void* const* ws, int rank, int world, long shard_elems, int is_bf16, float scale,
-                                    void* out, int accumulate, void* stream) {
-  if (shard_elems % 8 != 0 || world > Z_MAX_RANKS || world < 1) return (int)cudaErrorInvalidValue;
+// At byte offset `off` every rank's region holds its full flat gradient (world * shard_elems
+// elements, bf16 or fp32); out (fp32, shard_elems) = [out +] scale * sum over ranks of slice `rank`.
+TRL_API int trl_zero_reduce_scatter(void* const* ws, int rank, int world, long off, long shard_elems, int is_bf16,
+                                    float scale, void* out, int accumulate, void* stream) {
+  if (shard_elems % 8 != 0 || off % 16 != 0 || world > Z_MAX_RANKS || world < 1) return (int)cudaErrorInvalidValue;
   const ZPeers P = z_peers(ws, rank, world);
   const int grid = z_grid(shard_elems / (is_bf16 ? 8 : 4));
   if (is_bf16)
-    zero_reduce_scatter_kernel<true><<<grid, 512, 0, (cudaStream_t)stream>>>(P, shard_elems, scale, (float*)out, accumulate);
+    zero_reduce_scatter_kernel<true><<<grid, 512, 0, (cudaStream_t)stream>>>(P, (size_t)off, shard_elems, scale, (float*)out, accumulate);
   else
-    zero_reduce_scatter_kernel<false><<<grid, 512, 0, (cudaStream_t)stream>>>(P, shard_elems, scale, (float*)out, accumulate);
+    zero_reduce_scatter_kernel<false><<<grid, 512, 0, (cudaStream_t)stream>>>(P, (size_t)off, shard_elems, scale, (float*)out, accumulate);
   return (int)cudaGetLastError();
 }

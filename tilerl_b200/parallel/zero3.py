@@ -44,7 +44,12 @@ class TorchComm:
         self.rank = dist.get_rank(group) if group is not None else 0
         self.backend = dist.get_backend(group) if group is not None else "none"
 
+    def grad_buffer(self, numel: int, dtype, device) -> torch.Tensor:
+        return torch.zeros(numel, dtype=dtype, device=device)
+
     def all_gather(self, shard: torch.Tensor, full: torch.Tensor, stream=None) -> None:
+        """``shard`` may be the fp32 master shard: it is cast to ``full``'s dtype on the way."""
+        shard = shard.to(full.dtype)
         if self.world == 1:
             full.copy_(shard)
             return
@@ -151,7 +156,7 @@ class Zero3:
     def _gather(self, u: _Unit) -> None:
         if u.full is not None or not u.names:
             return
-        shard = self.master[u.index].to(self.work_dtype)
+        shard = self.master[u.index]                 # fp32; the comm casts it into the working dtype
         full = torch.empty(shard.numel() * self.world, dtype=self.work_dtype, device=self.device)
         self.comm.all_gather(shard, full)
         u.full = full
@@ -202,7 +207,13 @@ class Zero3:
             return
         u = self.units[loc[0]]
         if u.grad is None:
-            u.grad = torch.zeros(self.master[u.index].numel() * self.world, dtype=self.work_dtype, device=self.device)
+            n_flat = self.master[u.index].numel() * self.world
+            if u.index == len(self.units) - 1:
+                # tensors outside the layers get their gradients at both ends of the backward; they
+                # must not sit in the area the layers (one in flight at a time) take turns in
+                u.grad = torch.zeros(n_flat, dtype=self.work_dtype, device=self.device)
+            else:
+                u.grad = self.comm.grad_buffer(n_flat, self.work_dtype, self.device)
             u.pending = len(u.names)
         off = u.offsets[loc[1]]
         u.grad[off:off + grad.numel()] = grad.reshape(-1).to(self.work_dtype)
@@ -298,14 +309,17 @@ class Zero3:
 class P2PComm:
     """ZeRO collectives by the kernels of ``csrc/zero.cu`` over NVLink peer memory.
 
-    One symmetric staging region per rank (``cap_bytes``: the largest unit's flat gradient in
-    the working dtype), exported with CUDA IPC.  Every collective is enqueued on this object's
-    own stream, in program order on every rank, so at most one of them runs per GPU and a
-    prefetch never meets a reduce-scatter half way; the caller's stream is joined before and
-    (unless the call is a prefetch issued from a side stream) after."""
+    One symmetric region per rank, exported with CUDA IPC, with two staging areas: the
+    parameter shard in the working dtype (the fp32 master shard is cast straight into it) and
+    the full flat gradient of the unit being reduced (``grad_buffer`` hands that area out, so
+    the backward writes gradients where the peers will read them -- no staging copy).
+    Every collective is enqueued on this object's own stream, in program order on every rank,
+    so at most one of them runs per GPU and a prefetch never meets a reduce-scatter half way;
+    the caller's stream is joined before and after."""
     align = 8          # elements: shards are moved in 16-byte vectors
 
     def __init__(self, group, device, cap_bytes: int):
+        """``cap_bytes``: the largest unit's flat gradient in the working dtype."""
         import ctypes
 
         from ..ops import native as N
@@ -314,14 +328,17 @@ class P2PComm:
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.backend = "p2p"
         self.lib = N.lib()
-        for name, sig in {"trl_zero_allgather": [N.P, N.I, N.I, ctypes.c_long, N.P, N.P],
-                          "trl_zero_reduce_scatter": [N.P, N.I, N.I, ctypes.c_long, N.I, ctypes.c_float, N.P, N.I, N.P],
+        for name, sig in {"trl_zero_allgather": [N.P, N.I, N.I, ctypes.c_long, ctypes.c_long, N.P, N.P],
+                          "trl_zero_reduce_scatter": [N.P, N.I, N.I, ctypes.c_long, ctypes.c_long, N.I, ctypes.c_float,
+                                                      N.P, N.I, N.P],
                           }.items():
             N.register(name, sig)
         self.lib.trl_zero_data_offset.restype = ctypes.c_size_t
-        self.off = self.lib.trl_zero_data_offset()
-        self.cap = (cap_bytes + 255) // 256 * 256
-        self.nbytes = self.off + self.cap
+        off = self.lib.trl_zero_data_offset()
+        self.cap_grad = (cap_bytes + 255) // 256 * 256
+        self.cap_shard = (cap_bytes // self.world + 4096 + 255) // 256 * 256
+        self.off_shard, self.off_grad = off, off + self.cap_shard
+        self.nbytes = self.off_grad + self.cap_grad
         p = ctypes.c_void_p()
         N.check(self.lib.trl_symm_alloc(self.nbytes, ctypes.byref(p)), "symm_alloc")
         self.local_ptr = p.value
@@ -339,7 +356,8 @@ class P2PComm:
             self.ptrs.append(q.value)
         self.table = (ctypes.c_void_p * 8)(*(self.ptrs + [None] * (8 - self.world)))
         self.mem = torch.as_tensor(_DevMem(self.local_ptr, self.nbytes), device=self.device)
-        self.stage = self.mem[self.off:]
+        self.stage_shard = self.mem[self.off_shard:self.off_shard + self.cap_shard]
+        self.stage_grad = self.mem[self.off_grad:self.off_grad + self.cap_grad]
         self.stream = torch.cuda.Stream(device=self.device)
         self._check = N.check
         dist.barrier(group=group)
@@ -349,31 +367,50 @@ class P2PComm:
         self.stream.wait_stream(cur)
         return cur
 
+    def grad_buffer(self, numel: int, dtype, device) -> torch.Tensor:
+        """The gradient staging area as a zeroed tensor (falls back to ordinary memory if the
+        unit is larger than the area)."""
+        nb = numel * torch.empty(0, dtype=dtype).element_size()
+        if nb > self.cap_grad or getattr(self, "_grad_out", False):
+            return torch.zeros(numel, dtype=dtype, device=device)   # too large, or another unit holds the area
+        self._grad_out = True
+        torch.cuda.current_stream(self.device).wait_stream(self.stream)   # the last reduce-scatter has read it
+        buf = self.stage_grad[:nb].view(dtype)
+        buf.zero_()
+        return buf
+
     def all_gather(self, shard: torch.Tensor, full: torch.Tensor, stream=None) -> None:
-        nb = shard.numel() * shard.element_size()
-        if nb > self.cap or nb % 16:
-            raise ValueError(f"shard of {nb} B does not fit the staging area ({self.cap} B) or is not 16-byte sized")
+        nb = shard.numel() * full.element_size()
+        if nb > self.cap_shard or nb % 16:
+            raise ValueError(f"shard of {nb} B does not fit the staging area ({self.cap_shard} B) or is not 16-byte sized")
         cur = self._enter()
         with torch.cuda.stream(self.stream):
-            self.stage[:nb].copy_(shard.contiguous().view(torch.uint8))
-            self._check(self.lib.trl_zero_allgather(self.table, self.rank, self.world, nb, full.data_ptr(),
-                                                    self.stream.cuda_stream), "zero_allgather")
+            self.stage_shard[:nb].view(full.dtype).copy_(shard)          # cast (fp32 master -> working dtype) and stage
+            self._check(self.lib.trl_zero_allgather(self.table, self.rank, self.world, self.off_shard, nb,
+                                                    full.data_ptr(), self.stream.cuda_stream), "zero_allgather")
         shard.record_stream(self.stream)
         full.record_stream(self.stream)
         cur.wait_stream(self.stream)
 
     def reduce_scatter(self, full: torch.Tensor, shard_out: torch.Tensor, scale: float, accumulate: bool) -> None:
         nb = full.numel() * full.element_size()
-        if nb > self.cap or shard_out.numel() % 8 or full.dtype not in (torch.bfloat16, torch.float32):
+        if nb > self.cap_grad or shard_out.numel() % 8 or full.dtype not in (torch.bfloat16, torch.float32):
             raise ValueError("gradient does not fit the staging area, or shard not a multiple of 8 elements")
         cur = self._enter()
         with torch.cuda.stream(self.stream):
-            self.stage[:nb].copy_(full.contiguous().view(torch.uint8))
-            self._check(self.lib.trl_zero_reduce_scatter(self.table, self.rank, self.world, shard_out.numel(),
-                                                         int(full.dtype == torch.bfloat16), float(scale),
-                                                         shard_out.data_ptr(), int(accumulate),
+            if full.data_ptr() != self.stage_grad.data_ptr():
+                if getattr(self, "_grad_out", False):
+                    # the area is lent to another unit's backward: wait is not an option here, the
+                    # caller owns both; this cannot happen with one layer in flight at a time
+                    raise RuntimeError("gradient staging area is lent out while another unit is reduced")
+                self.stage_grad[:nb].copy_(full.contiguous().view(torch.uint8))
+                full.record_stream(self.stream)
+            else:
+                self._grad_out = False
+            self._check(self.lib.trl_zero_reduce_scatter(self.table, self.rank, self.world, self.off_grad,
+                                                         shard_out.numel(), int(full.dtype == torch.bfloat16),
+                                                         float(scale), shard_out.data_ptr(), int(accumulate),
                                                          self.stream.cuda_stream), "zero_reduce_scatter")
-        full.record_stream(self.stream)
         shard_out.record_stream(self.stream)
         cur.wait_stream(self.stream)
 
