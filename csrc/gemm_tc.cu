@@ -584,7 +584,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
 // J NVFP4 residual terms per token.  column (tok*J + j): xq [cols, K/2], sf tiled (see
 // header), rs[col] fp32.
 //
-// Grid = (tokens, K/4096): every CTA first reduces the whole (L2-resident) row for the
+// Grid = (tokens, slices): every CTA first reduces the whole (L2-resident) row for the
 // norm statistics and the row maximum, then each thread owns one 16-element block and
 // runs all J terms in registers.  The row scale of term j is rs_0 / 4^j -- a bound, not a
 // reduction: one e2m1 term leaves a remainder of at most 1/4 of the block maximum it
@@ -642,11 +642,15 @@ quant_act_kernel(const bf16* __restrict__ x, int ldx, const float* __restrict__ 
   amax = block_max(amax, red);
   const float rs0 = fmaxf(amax, 1e-30f) * (1.f / (6.f * 448.f));
   if (blockIdx.y == 0 && threadIdx.x < J) rs[tok * J + threadIdx.x] = rs0 * exp2f(-2.f * (float)threadIdx.x);
-  // this thread's quarter block
-  const int q4 = blockIdx.y * blockDim.x + threadIdx.x;  // index of the 4-element group
+  // this thread's quarter blocks: one per slice; gridDim.y slices run in parallel, the rest in
+  // a loop (one CTA per row when there are enough rows to fill the GPU: the row is then read
+  // from L2 by one CTA instead of by every slice's CTA)
+  const int n_slices = (kt4 * 16 + (int)blockDim.x - 1) / (int)blockDim.x;
+  for (int sl = blockIdx.y; sl < n_slices; sl += gridDim.y) {
+  const int q4 = sl * blockDim.x + threadIdx.x;          // index of the 4-element group
   const int k = q4 * 4;
   const int b = q4 >> 2;                                  // 16-element block
-  if (b >= kt4 * 4) return;
+  const bool valid = b < kt4 * 4;                         // whole 4-lane groups are valid or not
   float r[4] = {0.f, 0.f, 0.f, 0.f};
   if (k < K) {
     load4(k, r);
@@ -683,9 +687,10 @@ quant_act_kernel(const bf16* __restrict__ x, int ldx, const float* __restrict__ 
     r[3] = fmaf(-d1.y, denom, r[3]);
     if (k < K)
       reinterpret_cast<uint16_t*>(xq + (size_t)col * (K >> 1))[q4] = (uint16_t)((lo & 0xff) | ((hi & 0xff) << 8));
-    if ((threadIdx.x & 3) == 0)  // scale byte (zero for the K padding)
+    if (valid && (threadIdx.x & 3) == 0)  // scale byte (zero for the K padding)
       sf[((size_t)(col >> 7) * kt4 + (b >> 2)) * SF_ATOM + (col & 31) * 16 + ((col & 127) >> 5) * 4 + (b & 3)] =
           (k < K) ? (uint8_t)(s16 & 0xff) : (uint8_t)0;
+  }
   }
 }
 
@@ -743,7 +748,8 @@ TRL_API int trl_quant_act_nvfp4(const void* x, int ldx, const void* norm_w, floa
                                 void* rs, int tokens, int K, int J, int swiglu_in, void* stream) {
   if (K % 16 != 0 || J < 1 || J > 16) return (int)cudaErrorInvalidValue;
   const int nk = (K + KT_ELEMS - 1) / KT_ELEMS;
-  const int slices = (nk * KT_ELEMS / 4 + 255) / 256;  // 4 elements per thread
+  int slices = (nk * KT_ELEMS / 4 + 255) / 256;  // 4 elements per thread
+  if (tokens >= 128) slices = 1;                        // enough rows to fill the GPU: one CTA per row
   return (int)trl_launch(quant_act_kernel, dim3(tokens, slices), dim3(256), 0, (cudaStream_t)stream, (const bf16*)x,
                          ldx, (const float*)norm_w, eps, (uint8_t*)xq, (uint8_t*)sf, (float*)rs, K, J, nk * 4,
                          swiglu_in);
