@@ -144,6 +144,9 @@ class Engine:
         self.think_ids = think_ids
         self.drafter = drafter
         self.spec_width = spec_width if drafter is not None else 0
+        # benchmark seam: count every draft as accepted, to time the verify tick at full acceptance
+        # on models whose greedy choice flips with rounding (random-init weights)
+        self.spec_force_accept = False
         self.graph = graph_runner
         self.sparse = sparse
         self.device = kv_pool.k.device
@@ -529,6 +532,8 @@ class Engine:
         n_ok = 0
         for k in range(len(chain)):
             tok = self._sample(r, logits, base + k, k, amax)
+            if self.spec_force_accept and k < len(drafts):
+                tok = (drafts[k], tok[1])     # timing seam: the draft is taken as the trunk's token
             accepted.append(tok)
             if k < len(drafts) and tok[0] == drafts[k]:
                 n_ok += 1

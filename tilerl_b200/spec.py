@@ -108,7 +108,8 @@ class BlockDrafter:
     def _head(self, x: torch.Tensor) -> torch.Tensor:
         head = self.model.params["embed" if self.model.cfg.tie_embeddings else "lm_head"]
         w = head if isinstance(head, torch.Tensor) else head.dequant()
-        return ref.rmsnorm(x, self.p["out_norm"], 1e-6) @ w.float().t().to(x.device)
+        # in the table's own dtype: a float copy of a [vocab, hidden] table per proposal would cost GBs
+        return (ref.rmsnorm(x, self.p["out_norm"], 1e-6).to(w.dtype) @ w.t().to(x.device)).float()
 
     def context_features(self, taps: Dict[int, torch.Tensor], rows: slice) -> torch.Tensor:
         """Project the concatenated trunk taps of the given token rows: [n, H]."""
@@ -193,11 +194,11 @@ class ChainDrafter:
         n_valid = min(n_run, max(1, getattr(req, "n_last_commit", n_run)))
         h = taps[self.aux_layers[0]][tok_off + n_valid - 1].to(self.fc.dtype)
         head = self.model.params["embed" if self.model.cfg.tie_embeddings else "lm_head"]
-        w = (head if isinstance(head, torch.Tensor) else head.dequant()).float().to(h.device)
+        w = (head if isinstance(head, torch.Tensor) else head.dequant()).to(h.device)
         out, tok = [], req.toks[-1]
         for _ in range(k):
             h = self.step(tok, h)
-            tok = int((h.float() @ w.t()).argmax())
+            tok = int((h.to(w.dtype) @ w.t()).float().argmax())
             out.append(tok)
         return out
 
