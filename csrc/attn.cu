@@ -232,6 +232,198 @@ attn_combine_kernel(const float* __restrict__ po, const float* __restrict__ pm,
   }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Tiled prefill attention (legacy tensor-core path: mma.sync m16n8k16 bf16, fp32 accumulate).
+// One CTA = (16-token tile of one sequence, kv head); warp g of the CTA owns query head
+// kvh * G + g, so the G heads of a group share every K / V tile.  K and V tiles of 32 keys
+// (two 16-token pages) are gathered through the block table with cp.async into 128-bit-chunk
+// XOR-swizzled shared memory, double buffered; QK^T and PV run on mma.sync with the usual
+// register reuse of the score fragment as the A operand of PV; online softmax in the exp2
+// domain; causal by absolute position; sigmoid output gate fused.  D = 256.
+// The split-KV kernel above re-reads K / V for every query token; this one reads them once per
+// 16 tokens, which is what makes long prompts tractable.
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+constexpr int PF_D = 256, PF_TQ = 16, PF_BC = 32, PF_ROW = PF_D * 2 /*bytes*/, PF_CHUNKS = PF_ROW / 16;
+
+// byte offset of 16-byte chunk `c` of row `r` in a swizzled [rows][512 B] tile
+__device__ __forceinline__ uint32_t pf_off(int r, int c) { return (uint32_t)(r * PF_ROW + ((c ^ (r & 7)) << 4)); }
+
+__global__ void __launch_bounds__(256)
+attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ gate_src, int gate_ld,
+                    const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                    const int* __restrict__ block_table, int max_blocks, const int* __restrict__ q_start,
+                    const int* __restrict__ q_len, const int* __restrict__ positions, bf16* __restrict__ out,
+                    int n_q, int n_kv, float scale_log2e, int gated) {
+  extern __shared__ __align__(1024) unsigned char pf_smem[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tile = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+  const int G = n_q / n_kv;
+  const int T = q_len[seq];
+  if (tile * PF_TQ >= T) return;
+  const int t0 = q_start[seq] + tile * PF_TQ;
+  const int rows = min(PF_TQ, T - tile * PF_TQ);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int h = kvh * G + warp;
+  unsigned char* qs = pf_smem + (size_t)warp * PF_TQ * PF_ROW;                 // [G][16][512 B]
+  unsigned char* ks = pf_smem + (size_t)G * PF_TQ * PF_ROW;                    // [2][32][512 B]
+  unsigned char* vs = ks + 2 * PF_BC * PF_ROW;                                 // [2][32][512 B]
+  const uint32_t qs_a = (uint32_t)__cvta_generic_to_shared(qs);
+  const uint32_t ks_a = (uint32_t)__cvta_generic_to_shared(ks), vs_a = (uint32_t)__cvta_generic_to_shared(vs);
+  const int* table = block_table + (size_t)seq * max_blocks;
+  // causal bound of the tile: keys 0 .. position of its last token
+  const int n_keys = positions[t0 + rows - 1] + 1;
+  const int n_tiles = (n_keys + PF_BC - 1) / PF_BC;
+
+  // this warp's 16 query rows (zero rows past the end of the sequence)
+  for (int x = lane; x < PF_TQ * PF_CHUNKS; x += 32) {
+    const int r = x / PF_CHUNKS, c = x % PF_CHUNKS;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < rows) v = *reinterpret_cast<const uint4*>(q + ((size_t)(t0 + r) * n_q + h) * PF_D + c * 8);
+    *reinterpret_cast<uint4*>(qs + pf_off(r, c)) = v;
+  }
+  auto load_kv = [&](int kt, int buf) {
+    const int j0 = kt * PF_BC;
+    for (int x = threadIdx.x; x < PF_BC * PF_CHUNKS; x += blockDim.x) {
+      const int r = x / PF_CHUNKS, c = x % PF_CHUNKS;
+      const int j = j0 + r;
+      const uint32_t dk = ks_a + buf * PF_BC * PF_ROW + pf_off(r, c);
+      const uint32_t dv = vs_a + buf * PF_BC * PF_ROW + pf_off(r, c);
+      if (j < n_keys) {
+        const size_t off = (((size_t)table[j / KVB] * n_kv + kvh) * KVB + (j % KVB)) * PF_D + c * 8;
+        cp16(dk, kcache + off);
+        cp16(dv, vcache + off);
+      } else {                      // rows past the bound: zeros (they are masked, but must not be NaN)
+        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(dk), "r"(0u) : "memory");
+        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(dv), "r"(0u) : "memory");
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  const int r_lo = lane >> 2;                      // fragment rows r_lo and r_lo + 8
+  const int pos_lo = r_lo < rows ? positions[t0 + r_lo] : -1;
+  const int pos_hi = r_lo + 8 < rows ? positions[t0 + r_lo + 8] : -1;
+  float o[PF_D / 8][4];
+#pragma unroll
+  for (int i = 0; i < PF_D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+
+  load_kv(0, 0);
+  for (int kt = 0; kt < n_tiles; ++kt) {
+    const int buf = kt & 1;
+    if (kt + 1 < n_tiles) {
+      load_kv(kt + 1, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const uint32_t kb = ks_a + buf * PF_BC * PF_ROW, vb = vs_a + buf * PF_BC * PF_ROW;
+    // ---- S = Q K^T for 32 keys: 4 n-tiles of 8 keys
+    float sc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < PF_D / 16; ++kk) {
+      uint32_t a[4];
+      ldsm_x4(a, qs_a + pf_off((lane & 7) + ((lane >> 3) & 1) * 8, kk * 2 + (lane >> 4)));
+#pragma unroll
+      for (int np = 0; np < 2; ++np) {             // two n-tiles per ldmatrix.x4
+        uint32_t b[4];
+        ldsm_x4(b, kb + pf_off(np * 16 + (lane & 7) + (lane >> 4) * 8, kk * 2 + ((lane >> 3) & 1)));
+        mma_bf16(sc[np * 2], a, b[0], b[1]);
+        mma_bf16(sc[np * 2 + 1], a, b[2], b[3]);
+      }
+    }
+    // ---- mask, scale, online softmax
+    const int j0 = kt * PF_BC;
+    float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int j = j0 + nt * 8 + (lane & 3) * 2;
+      sc[nt][0] = (j <= pos_lo) ? sc[nt][0] * scale_log2e : -INFINITY;
+      sc[nt][1] = (j + 1 <= pos_lo) ? sc[nt][1] * scale_log2e : -INFINITY;
+      sc[nt][2] = (j <= pos_hi) ? sc[nt][2] * scale_log2e : -INFINITY;
+      sc[nt][3] = (j + 1 <= pos_hi) ? sc[nt][3] * scale_log2e : -INFINITY;
+      mx_lo = fmaxf(mx_lo, fmaxf(sc[nt][0], sc[nt][1]));
+      mx_hi = fmaxf(mx_hi, fmaxf(sc[nt][2], sc[nt][3]));
+    }
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+    const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+    const float base_lo = mn_lo == -INFINITY ? 0.f : mn_lo, base_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+    const float al_lo = exp2f(m_lo - base_lo), al_hi = exp2f(m_hi - base_hi);   // exp2(-inf) = 0 on the first tile
+    m_lo = mn_lo, m_hi = mn_hi;
+    float sum_lo = 0.f, sum_hi = 0.f;
+    uint32_t pa[2][4];                             // P as the A operand of PV: two k-steps of 16 keys
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const float p0 = exp2f(sc[nt][0] - base_lo), p1 = exp2f(sc[nt][1] - base_lo);
+      const float p2 = exp2f(sc[nt][2] - base_hi), p3 = exp2f(sc[nt][3] - base_hi);
+      sum_lo += p0 + p1, sum_hi += p2 + p3;
+      pa[nt >> 1][(nt & 1) * 2] = f2_to_bf162_bits(p0, p1);
+      pa[nt >> 1][(nt & 1) * 2 + 1] = f2_to_bf162_bits(p2, p3);
+    }
+    sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 1);
+    sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 2);
+    sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 1);
+    sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 2);
+    l_lo = l_lo * al_lo + sum_lo, l_hi = l_hi * al_hi + sum_hi;
+#pragma unroll
+    for (int i = 0; i < PF_D / 8; ++i) o[i][0] *= al_lo, o[i][1] *= al_lo, o[i][2] *= al_hi, o[i][3] *= al_hi;
+    // ---- O += P V
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+      for (int nd = 0; nd < PF_D / 8; nd += 2) {
+        uint32_t b[4];
+        ldsm_x4_t(b, vb + pf_off(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, nd + (lane >> 4)));
+        mma_bf16(o[nd], pa[kk], b[0], b[1]);
+        mma_bf16(o[nd + 1], pa[kk], b[2], b[3]);
+      }
+    }
+    __syncthreads();                               // the other buffer may be overwritten next round
+  }
+  // ---- epilogue: normalise, gate, store
+  const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
+#pragma unroll
+  for (int nd = 0; nd < PF_D / 8; ++nd) {
+    const int d = nd * 8 + (lane & 3) * 2;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = r_lo + half * 8;
+      if (r >= rows) continue;
+      const int t = t0 + r;
+      float v0 = o[nd][half * 2] * (half ? inv_hi : inv_lo), v1 = o[nd][half * 2 + 1] * (half ? inv_hi : inv_lo);
+      if (gated) {
+        const bf16* gp = gate_src + (size_t)t * gate_ld + (size_t)h * 2 * PF_D + PF_D + d;
+        v0 *= sigmoid_f(__bfloat162float(gp[0])), v1 *= sigmoid_f(__bfloat162float(gp[1]));
+      }
+      *reinterpret_cast<uint32_t*>(out + ((size_t)t * n_q + h) * PF_D + d) = f2_to_bf162_bits(v0, v1);
+    }
+  }
+}
+
 }  // namespace
 
 TRL_API int trl_attn_prep(const void* qkv, int ld, const void* q_norm, const void* k_norm,
@@ -294,6 +486,28 @@ void* g_static_scratch_ptr[kMaxDevices] = {nullptr};
 
 TRL_API size_t trl_attn_static_scratch_needed(int T, int n_q, int D, int n_splits) {
   return (size_t)T * n_q * n_splits * ((size_t)D + 2) * sizeof(float);
+}
+
+// Tiled prefill attention over whole sequences of the batch (D = 256, G = n_q / n_kv <= 8):
+// q_start / q_len give each sequence's token range in the flat batch; `out` [T, n_q * D].
+TRL_API int trl_attn_prefill(const void* q, const void* gate_src, int gate_ld, const void* kcache, const void* vcache,
+                             const void* block_table, int max_blocks, const void* q_start, const void* q_len,
+                             const void* positions, void* out, int B, int max_q_len, int n_q, int n_kv, int D,
+                             float scale, int gated, void* stream) {
+  const int G = n_kv > 0 ? n_q / n_kv : 0;
+  if (D != PF_D || G < 1 || G > 8 || n_q % n_kv != 0 || B <= 0 || max_q_len <= 0) return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)G * PF_TQ * PF_ROW + (size_t)4 * PF_BC * PF_ROW;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * PF_TQ * PF_ROW + 4 * PF_BC * PF_ROW) != cudaSuccess)
+      return 3;
+    configured = true;
+  }
+  const dim3 grid((max_q_len + PF_TQ - 1) / PF_TQ, n_kv, B);
+  return (int)trl_launch(attn_prefill_kernel, grid, dim3(G * 32), smem, (cudaStream_t)stream, (const bf16*)q,
+                         (const bf16*)gate_src, gate_ld, (const bf16*)kcache, (const bf16*)vcache,
+                         (const int*)block_table, max_blocks, (const int*)q_start, (const int*)q_len,
+                         (const int*)positions, (bf16*)out, n_q, n_kv, scale * 1.4426950408889634f, gated);
 }
 
 TRL_API int trl_attn_paged_static(const void* q, const void* gate_src, int gate_ld, const void* kcache,

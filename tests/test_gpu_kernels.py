@@ -272,3 +272,49 @@ def test_bounded_device_wait_returns_a_status_and_leaves_the_context_usable():
     finally:
         lib.trl_comm_set_wait_ms(2000)
         lib.trl_symm_free(p)
+
+
+@pytest.mark.parametrize("lens,hist", [((40, 1, 17), (0, 33, 5)), ((64,), (100,)), ((16, 16), (0, 16))])
+def test_tiled_prefill_attention_matches_split_kernel_and_oracle(lens, hist):
+    """The tiled tensor-core prefill kernel against the per-token split kernel and the fp32
+    oracle: ragged sequences, history already in the paged cache, decode rows riding along."""
+    import math as _m
+    from tilerl_b200.batch import Batch
+    from tilerl_b200.config import small_gpu
+    from tilerl_b200.factory import make_ops
+    from tilerl_b200.kv import PagedKvPool
+    from tilerl_b200.ops.backend import RefOps
+    cfg = small_gpu()
+    ops = make_ops("cuda")
+    g = torch.Generator().manual_seed(7)
+    n_q, n_kv, d = cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim
+    rows = n_q * 2 * d + 2 * n_kv * d
+    lp = {"q_norm": torch.ones(d, device="cuda"), "k_norm": torch.ones(d, device="cuda")}
+    outs = {}
+    for mode in ("tiled", "split", "ref"):
+        pool = PagedKvPool(cfg, 64, "cuda", dtype=torch.bfloat16 if mode != "ref" else torch.float32)
+        o = RefOps() if mode == "ref" else ops
+        if mode != "ref":
+            ops.prefill_attn = mode == "tiled"
+        blk = 1
+        seqs_hist, seqs_now = [], []
+        for i, (n, h) in enumerate(zip(lens, hist)):
+            nb = (n + h + 15) // 16
+            blocks = list(range(blk, blk + nb))
+            blk += nb
+            if h:
+                seqs_hist.append(dict(tokens=[0] * h, start=0, blocks=blocks, slot=i + 1))
+            seqs_now.append(dict(tokens=[0] * n, start=h, blocks=blocks, slot=i + 1))
+        gg = torch.Generator().manual_seed(11)
+        for seqs in ([seqs_hist] if seqs_hist else []) + [seqs_now]:
+            batch = Batch.build(seqs, "cuda")
+            t = sum(len(s_["tokens"]) for s_ in seqs)
+            qkv = (torch.randn(t, rows, generator=gg) * 0.5).cuda().to(torch.bfloat16)
+            res = o.attention(qkv, lp, batch, pool, 0, cfg, n_q, n_kv)
+        outs[mode] = res.float().clone()
+    ops.prefill_attn = True
+    ref_o = outs["ref"]
+    for mode in ("tiled", "split"):
+        err = float((outs[mode] - ref_o).abs().max())
+        assert err < 0.03 * float(ref_o.abs().max()) + 0.02, (mode, err)
+    assert float((outs["tiled"] - outs["split"]).abs().max()) < 0.03

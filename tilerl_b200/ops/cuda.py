@@ -68,6 +68,7 @@ class CudaOps:
         # B=1) or the tcgen05 GEMM with `terms_small` residual terms (TRL_DECODE=tc)
         self.decode_tc = (os.environ.get("TRL_DECODE", "simt") == "tc") if decode_tc is None else decode_tc
         self.gemv_tokens = int(os.environ.get("TRL_GEMV_TOKENS", GEMV_MAX_M))
+        self.prefill_attn = os.environ.get("TRL_PREFILL_ATTN", "1") != "0"   # tiled kernel for q_len >= 16
         from .. import tape as _tape
         _tape.set_dequant(self.dequantize_nvfp4)   # frozen-base linears of the training forward
         self.terms_small = int(os.environ.get("TRL_TERMS_SMALL", terms_small))
@@ -217,7 +218,19 @@ class CudaOps:
             cfg.rotary_dim, float(cfg.rope_theta), cfg.rms_eps, int(cfg.attn_gated), st), "attn_prep")
         table, pos = batch.block_table, batch.positions
         sp = batch.sparse
-        if sp is not None and sp.active(attn_idx):
+        sparse_now = sp is not None and sp.active(attn_idx)
+        if (not sparse_now and self.prefill_attn and batch.max_q_len >= 16 and d == 256 and n_q % n_kv == 0
+                and n_q // n_kv <= 8 and not getattr(batch, "keep_steps", 0)):
+            # prefill chunks (and whatever decode rows ride along): K / V tiles are read once per
+            # 16 query tokens by the tiled tensor-core kernel
+            N.check(self.lib.trl_attn_prefill(
+                q.data_ptr(), qkv.data_ptr(), qkv.stride(0), kc.data_ptr(), vc.data_ptr(), table.data_ptr(),
+                table.stride(0), batch.q_start.data_ptr(), batch.q_len.data_ptr(), pos.data_ptr(), out.data_ptr(),
+                batch.n_seqs, batch.max_q_len, n_q, n_kv, d, 1.0 / math.sqrt(d), int(cfg.attn_gated), st),
+                "attn_prefill")
+            N.count(2)
+            return out
+        if sparse_now:
             table, pos = sp.packed(attn_idx, q, kc)    # same kernel on [selected pages ; trailing window]
         splits = self.attn_splits or self._pick_splits(batch, t, n_kv)
         po = self.ws.get("attn_po", (t * n_q * splits * d,), torch.float32)
