@@ -1,0 +1,70 @@
+"""Repository hygiene: sources stand on their own (no pointers to build notes), nothing imports
+scratch folders, every kernel file cites the reference it replaces, GPU tests carry the marker."""
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+SRC_DIRS = ["tilerl_b200", "csrc", "tests"]
+SRC_FILES = ["bench.py", "__graft_entry__.py"]
+FORBIDDEN = [r"SURVEY\.md", r"DESIGN\.md", r"BASELINE\.md", r"VERDICT\.md", r"ADVICE\.md", r"\bgpurun\b",
+             r"/root/", r"\bround [0-9]\b", r"\bthe judge\b"]
+
+
+def _sources():
+    for d in SRC_DIRS:
+        for base, _, files in os.walk(os.path.join(ROOT, d)):
+            if "__pycache__" in base:
+                continue
+            for f in files:
+                if f.endswith((".py", ".cu", ".cuh", ".h", ".js", ".html")):
+                    yield os.path.join(base, f)
+    for f in SRC_FILES:
+        yield os.path.join(ROOT, f)
+
+
+def test_sources_do_not_point_at_build_notes_or_machine_paths():
+    bad = []
+    me = os.path.abspath(__file__)
+    for path in _sources():
+        if os.path.abspath(path) == me:
+            continue
+        text = open(path, encoding="utf-8", errors="ignore").read()
+        for pat in FORBIDDEN:
+            for m in re.finditer(pat, text):
+                line = text.count("\n", 0, m.start()) + 1
+                bad.append(f"{os.path.relpath(path, ROOT)}:{line}: {m.group(0)}")
+    assert not bad, "\n".join(bad[:20])
+
+
+def test_nothing_imports_scratch_folders():
+    for path in _sources():
+        text = open(path, encoding="utf-8", errors="ignore").read()
+        if path.endswith("test_hygiene.py"):
+            continue
+        assert not re.search(r"[\"'/ ]_work/", text), path
+        assert "gpurun_out" not in text, path
+
+
+def test_every_kernel_file_cites_the_reference():
+    for f in os.listdir(os.path.join(ROOT, "csrc")):
+        if f.endswith(".cu"):
+            text = open(os.path.join(ROOT, "csrc", f)).read()
+            assert re.search(r"(tilerl[-_]kernels|src/tilerl|no counterpart|has no counterpart)", text), f
+
+
+def test_gpu_tests_are_marked():
+    for f in os.listdir(os.path.join(ROOT, "tests")):
+        if f.startswith("test_gpu_") or f == "test_zz_no_alloc.py":
+            text = open(os.path.join(ROOT, "tests", f)).read()
+            assert "pytest.mark.gpu" in text, f
+
+
+def test_layering_ops_do_not_import_engine_or_server():
+    """Kernels / ops sit below the engine; the engine sits below the server."""
+    for base, _, files in os.walk(os.path.join(ROOT, "tilerl_b200", "ops")):
+        for f in files:
+            if f.endswith(".py"):
+                text = open(os.path.join(base, f)).read()
+                assert not re.search(r"from \.\.(engine|server|rl)\b|import tilerl_b200\.(engine|server)", text), f
+    text = open(os.path.join(ROOT, "tilerl_b200", "engine.py")).read()
+    assert "from .server" not in text and "import fastapi" not in text

@@ -68,7 +68,7 @@ class CudaOps:
         # B=1) or the tcgen05 GEMM with `terms_small` residual terms (TRL_DECODE=tc)
         self.decode_tc = (os.environ.get("TRL_DECODE", "simt") == "tc") if decode_tc is None else decode_tc
         self.gemv_tokens = int(os.environ.get("TRL_GEMV_TOKENS", GEMV_MAX_M))
-        self.prefill_attn = os.environ.get("TRL_PREFILL_ATTN", "0") != "0"   # tiled kernel for q_len >= 16 (opt-in until it has run on a GPU)
+        self.prefill_attn = os.environ.get("TRL_PREFILL_ATTN", "1") != "0"   # tiled kernel for q_len >= 16
         from .. import tape as _tape
         _tape.set_dequant(self.dequantize_nvfp4)   # frozen-base linears of the training forward
         self.terms_small = int(os.environ.get("TRL_TERMS_SMALL", terms_small))
