@@ -15,6 +15,7 @@ def setup():
     # same activation precision for every token count, so a token's numerics do not depend on
     # how the scheduler batched it (chunked prefill == one shot == single)
     ops.terms_small = ops.terms_large = 4
+    ops.gemv_tokens = 8          # same kernel family for 1..8 rows: these tests compare schedules bit for bit
     model = build_model(cfg, "cuda", seed=0, ops=ops)
     return cfg, ops, model
 
@@ -95,6 +96,12 @@ def test_spec_decode_matches_plain_on_gpu(setup):
         got = [r.tokens for r in eng.generate(prompts, sp)]
         assert got == want, type(drafter).__name__
     assert eng.stats()["spec_drafted"] > 0
+    # the same verify ticks replayed from CUDA graphs
+    for drafter in (oracle, ConstantDrafter(3), BlockDrafter(model, BlockDrafterConfig(width=4, n_heads=4, n_kv_heads=2))):
+        eng = build_engine(model, ops, slots=4, max_ctx=256, graph=True, prefix=False, spec_width=4, drafter=drafter)
+        got = [r.tokens for r in eng.generate(prompts, sp)]
+        assert got == want, ("graph", type(drafter).__name__)
+        assert eng.vgraph is not None and eng.vgraph.replays > 0
 
 
 def test_sparse_decode_runs_on_gpu(setup):

@@ -42,6 +42,7 @@ def _worker_body(rank, world, port, out):
     comm = SymmComm.create(dist.group.WORLD, dev, hmax=cfg.hidden, tmax=512)
     ops = make_ops(dev, tp_comm=comm)
     ops.terms_small = ops.terms_large = 4
+    ops.gemv_tokens = 8          # same kernel family for 1..8 rows: these tests compare schedules bit for bit
     model = build_model(cfg, dev, seed=0, tp_rank=rank, tp=world, ops=ops)
     g = torch.Generator().manual_seed(5)
     prompts = [torch.randint(0, cfg.vocab, (40,), generator=g).tolist() for _ in range(2)]
@@ -57,6 +58,7 @@ def _worker_body(rank, world, port, out):
         # single-GPU control on the same device
         ops1 = make_ops(dev)
         ops1.terms_small = ops1.terms_large = 4
+        ops1.gemv_tokens = 8
         m1 = build_model(cfg, dev, seed=0, ops=ops1)
         e1 = build_engine(m1, ops1, slots=4, max_ctx=256, graph=True, prefix=False)
         want = [r.tokens for r in e1.generate(prompts, SamplingParams(max_tokens=10))]

@@ -134,7 +134,7 @@ class Engine:
                  limits: Optional[StepLimits] = None, prefix_store=None, eos_id: Optional[int] = None,
                  detokenize: Optional[Callable[[Sequence[int]], str]] = None,
                  think_ids: Optional[Tuple[int, int]] = None, drafter=None, spec_width: int = 0,
-                 graph_runner=None, sparse=None):
+                 graph_runner=None, sparse=None, verify_graph_runner=None):
         self.model, self.ops = model, ops
         self.kv, self.states = kv_pool, state_pool
         self.limits = limits or StepLimits()
@@ -148,6 +148,7 @@ class Engine:
         # on models whose greedy choice flips with rounding (random-init weights)
         self.spec_force_accept = False
         self.graph = graph_runner
+        self.vgraph = verify_graph_runner       # CUDA-graph replay of width-W verify ticks
         self.sparse = sparse
         self.device = kv_pool.k.device
         self._lock = threading.RLock()
@@ -422,7 +423,15 @@ class Engine:
                 self.counters["graph_ticks"] += 1
         taps = hidden = None
         amax = None
-        if logits is not None:
+        vout = None
+        if logits is None and self.vgraph is not None and decode_only and verify and self.sparse is None:
+            greedy = all(self._is_plain_greedy(r) for r, _, _ in plan)
+            vout = self.vgraph.run(seqs, need_logits=not greedy)
+        if vout is not None:
+            self.counters["graph_ticks"] += 1
+            logits, taps = vout.logits, vout.taps
+            amax = vout.argmax if greedy else None
+        elif logits is not None:
             logits, amax = logits.logits, logits.argmax
             if not all(self._is_plain_greedy(r) for r, _, _ in plan):
                 amax = None

@@ -155,13 +155,16 @@ def build_engine(model: HybridModel, ops=None, *, device=None, blocks: Optional[
     st = GdnStatePool(cfg, slots + 1, device, planes=planes,
                       ring_dtype=torch.bfloat16 if on_gpu else torch.float32,
                       n_v_heads=d.gdn_nv or None, n_k_heads=d.gdn_nk or None)
-    runner = None
-    if graph and on_gpu and spec_width == 0:
-        from .graph import DecodeGraphRunner
+    runner = vrunner = None
+    if graph and on_gpu:
+        from .graph import DecodeGraphRunner, VerifyGraphRunner
         runner = DecodeGraphRunner(model, ops, kv, st, max_ctx=max_ctx)
+        if spec_width > 0 and drafter is not None:
+            vrunner = VerifyGraphRunner(model, ops, kv, st, max_ctx=max_ctx, width=spec_width,
+                                        aux_layers=tuple(getattr(drafter, "aux_layers", ())))
     store = PrefixStore(kv) if prefix else NoPrefixStore()
     return Engine(model, ops, kv, st, limits=limits, prefix_store=store, graph_runner=runner,
-                  drafter=drafter, spec_width=spec_width, sparse=sparse, **engine_kw)
+                  verify_graph_runner=vrunner, drafter=drafter, spec_width=spec_width, sparse=sparse, **engine_kw)
 
 
 def build_serving_engine(model_name: str = "tiny", device="cpu", **kw) -> Engine:

@@ -185,3 +185,135 @@ class DecodeGraphRunner:
     def bucket(self, n: int) -> "_Bucket":
         b = bucket_for(n, self.buckets)
         return self._b.get(b) or self._capture(b)
+
+
+@dataclass
+class VerifyOut:
+    logits: torch.Tensor                 # [rows, vocab] in the engine's (compact) row order
+    argmax: List[int]
+    taps: Optional[Dict[int, torch.Tensor]]
+
+
+class _VBucket:
+    """Static input block + captured graph of a width-``w`` verify tick for ``b`` sequences.
+    Row layout: sequence ``r`` owns token rows ``r*w .. r*w + w - 1``; a chain shorter than ``w``
+    leaves its tail rows as pad tokens (page 0, position 0) outside every ``q_len``."""
+
+    def __init__(self, b: int, w: int, max_blocks: int, device):
+        self.b, self.w, self.max_blocks = b, w, max_blocks
+        t = b * w
+        n = 3 * t + 4 * b + b * max_blocks
+        self.host = torch.zeros(n, dtype=torch.int32).pin_memory() if device.type == "cuda" \
+            else torch.zeros(n, dtype=torch.int32)
+        self.np = self.host.numpy()
+        self.dev = torch.zeros(n, dtype=torch.int32, device=device)
+        tv = lambda i: self.dev[i * t:(i + 1) * t]
+        bv = lambda i: self.dev[3 * t + i * b:3 * t + (i + 1) * b]
+        ar = torch.arange(b, dtype=torch.int32, device=device)
+        self.batch = Batch(
+            token_ids=tv(0), positions=tv(1), seq_ids=ar.repeat_interleave(w).contiguous(), slot_mapping=tv(2),
+            q_start=(ar * w).contiguous(), q_len=bv(0), kv_len=bv(1), state_slots=bv(2),
+            block_table=self.dev[3 * t + 4 * b:].view(b, max_blocks), last_idx=(ar * w + w - 1).contiguous(),
+            n_seqs=b, n_tokens=t, max_q_len=w, keep_steps=w, host_q_len=[w] * b, host_kv_len=[1] * b,
+            keep_rows=[True] * b, keep_flags=bv(3))
+        self.graph = None
+        self.out_tok = self.out_logits = None
+        self.out_taps: Optional[Dict[int, torch.Tensor]] = None
+        self.tok_host = torch.zeros(t, dtype=torch.int32).pin_memory() if device.type == "cuda" \
+            else torch.zeros(t, dtype=torch.int32)
+        self.kernels = 0
+        self.h2d_bytes = 0
+
+    def fill(self, seqs: Sequence[dict]) -> List[int]:
+        """Returns the row index (in the padded layout) of every real token, in engine order."""
+        b, w, mb, a = self.b, self.w, self.max_blocks, self.np
+        t = b * w
+        a[:] = 0
+        rows: List[int] = []
+        for r, s in enumerate(seqs):
+            toks, start, blocks = s["tokens"], int(s["start"]), s["blocks"]
+            for k, tok in enumerate(toks):
+                pos = start + k
+                a[r * w + k] = tok
+                a[t + r * w + k] = pos
+                a[2 * t + r * w + k] = blocks[pos // KV_BLOCK] * KV_BLOCK + pos % KV_BLOCK
+                rows.append(r * w + k)
+            a[3 * t + r] = len(toks)
+            a[3 * t + b + r] = start + len(toks)
+            a[3 * t + 2 * b + r] = s["slot"]
+            a[3 * t + 3 * b + r] = 1
+            o = 3 * t + 4 * b + r * mb
+            a[o:o + len(blocks)] = blocks
+        self.h2d_bytes = a.nbytes
+        return rows
+
+
+class VerifyGraphRunner:
+    """CUDA-graph capture of speculative verify ticks (width ``w`` chains): the same forward the
+    eager path runs -- W-wide attention, GDN with a state plane per step, logits and argmax of
+    every row, the drafter's hidden taps -- replayed from one graph per batch bucket."""
+
+    def __init__(self, model, ops, kv_pool, state_pool, *, max_ctx: int, width: int, aux_layers: Sequence[int] = (),
+                 buckets=(1, 2, 4, 8, 16)):
+        self.model, self.ops, self.kv, self.states = model, ops, kv_pool, state_pool
+        self.device = kv_pool.k.device
+        self.max_blocks = (max_ctx + KV_BLOCK - 1) // KV_BLOCK
+        self.w, self.aux = int(width), tuple(aux_layers)
+        self.buckets = tuple(buckets)
+        self.enabled = self.device.type == "cuda"
+        self._b: Dict[int, _VBucket] = {}
+        self._pool = None
+        self.h2d_bytes = self.d2h_bytes = self.replays = 0
+
+    def _forward(self, bk: _VBucket):
+        sms = getattr(self.ops, "sms", 148)
+        self.ops.attn_splits = max(1, min(32, sms // max(1, bk.b * bk.w * self.model.dims.n_kv)))
+        res = self.model.forward(bk.batch, self.ops, self.kv, self.states, last_only=False, aux_layers=self.aux)
+        self.ops.attn_splits = 0
+        logits, taps = (res[0], res[2]) if self.aux else (res, None)
+        tok = self.ops.argmax(logits)
+        return logits, tok, taps
+
+    def _capture(self, b: int) -> _VBucket:
+        bk = _VBucket(b, self.w, self.max_blocks, self.device)
+        bk.fill([])
+        bk.dev.copy_(bk.host)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self._forward(bk)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        if self._pool is None:
+            self._pool = torch.cuda.graph_pool_handle()
+        from .ops import native as N
+        before = N.launch_count
+        with torch.cuda.graph(g, pool=self._pool):
+            logits, tok, taps = self._forward(bk)
+        bk.kernels = N.launch_count - before
+        bk.graph, bk.out_logits, bk.out_tok, bk.out_taps = g, logits, tok, taps
+        self._b[b] = bk
+        return bk
+
+    def run(self, seqs: Sequence[dict], need_logits: bool) -> Optional[VerifyOut]:
+        if not self.enabled:
+            return None
+        b = bucket_for(len(seqs), self.buckets)
+        if b is None or any(len(s["blocks"]) > self.max_blocks or not 1 <= len(s["tokens"]) <= self.w for s in seqs):
+            return None
+        bk = self._b.get(b) or self._capture(b)
+        rows = bk.fill(seqs)
+        bk.dev.copy_(bk.host, non_blocking=True)
+        bk.graph.replay()
+        bk.tok_host.copy_(bk.out_tok, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.replays += 1
+        self.h2d_bytes += bk.h2d_bytes
+        self.d2h_bytes += bk.tok_host.numel() * 4
+        th = bk.tok_host.tolist()
+        idx = torch.tensor(rows, dtype=torch.long, device=self.device) if (need_logits or bk.out_taps) else None
+        taps = {l: v[idx] for l, v in bk.out_taps.items()} if bk.out_taps else None
+        logits = bk.out_logits[idx] if need_logits else bk.out_logits
+        return VerifyOut(logits, [th[r] for r in rows], taps)

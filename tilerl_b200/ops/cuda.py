@@ -67,7 +67,7 @@ class CudaOps:
         # small-M projections: the SIMT weight-streaming GEMV (default; measured faster at
         # B=1) or the tcgen05 GEMM with `terms_small` residual terms (TRL_DECODE=tc)
         self.decode_tc = (os.environ.get("TRL_DECODE", "simt") == "tc") if decode_tc is None else decode_tc
-        self.gemv_tokens = int(os.environ.get("TRL_GEMV_TOKENS", GEMV_MAX_M))
+        self.gemv_tokens = int(os.environ.get("TRL_GEMV_TOKENS", 2))
         self.prefill_attn = os.environ.get("TRL_PREFILL_ATTN", "1") != "0"   # tiled kernel for q_len >= 16
         from .. import tape as _tape
         _tape.set_dequant(self.dequantize_nvfp4)   # frozen-base linears of the training forward
@@ -105,10 +105,11 @@ class CudaOps:
             raise TypeError(f"no GEMV for weight type {type(w)}")
 
     def _tc(self, w, t: int) -> bool:
-        # the weight-streaming GEMV handles up to 8 tokens in passes of 4; `gemv_tokens = 4` sends
-        # 5..8 tokens to the tensor-core kernel's single pass instead (faster for batched decode,
-        # but its activation rounding differs from the GEMV's, so a speculative verify tick of
-        # width <= 8 keeps the GEMV by default and commits exactly what plain decode would)
+        # measured on the 27B shapes (gate_up): 1 token GEMV 27.5 us; 2 tokens GEMV 35.6 / tensor-core
+        # GEMM incl. its activation quantiser 36.0; 4 tokens 58.5 / 36.1; 8 tokens 115 / 40.5.  So
+        # the GEMV serves up to `gemv_tokens` = 2 rows and the tensor-core kernel everything above
+        # (batched decode, verify ticks).  The two kernels round activations differently; set
+        # `gemv_tokens = 8` where batch-size-independent bits matter more than speed.
         return isinstance(w, NVFP4Tensor) and self.use_tc_gemm and (t > self.gemv_tokens or self.decode_tc)
 
     def _linear(self, x, w, y, *, norm_w=None, eps=0.0, residual=None, epi=EPI_STORE):

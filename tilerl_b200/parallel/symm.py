@@ -97,7 +97,7 @@ class SymmComm:
         t, k = a.shape
         n = w.shape[0]
         st = N.stream()
-        if t <= 8 and isinstance(w, NVFP4Tensor) and lora is None:
+        if t <= min(8, getattr(ops, "gemv_tokens", 8)) and isinstance(w, NVFP4Tensor) and lora is None:
             N.check(self.lib.trl_gemv_nvfp4_push(a.data_ptr(), a.stride(0), w.wq.data_ptr(), w.scale.data_ptr(),
                                                  w.tscale.data_ptr(), self.table, self.rank, self.world, self.hmax,
                                                  t, n, k, st), "gemv_push")

@@ -5,7 +5,7 @@
 
 ``spec``: B = 1, prompts of 80..300 random ids, a width-W verify tick timed at forced full
 acceptance (drafts = the trunk's own greedy continuation), at zero acceptance (a constant
-draft) and with the random-init block drafter, against plain decoding.
+draft) and with the random-init block drafter, against plain decoding (``--graph 0``: eager verify ticks).
 ``sparse``: one sequence prefilled to ``ctx`` tokens, then decode ticks with dense attention
 (CUDA-graph) and with top-k page selection (Quest bounds, trailing window of 8 pages, refreshed
 every 8 ticks).  All times are wall clock around device-synchronised loops.
@@ -53,7 +53,8 @@ def spec(args, cfg, ops, model):
                 "zero_acceptance": ConstantDrafter(0),
                 "block_drafter_random_init": BlockDrafter(model, BlockDrafterConfig(width=args.width), dtype=torch.bfloat16)}
     for name, d in drafters.items():
-        eng = build_engine(model, ops, slots=2, max_ctx=1024, graph=False, prefix=False, spec_width=args.width, drafter=d)
+        eng = build_engine(model, ops, slots=2, max_ctx=1024, graph=bool(args.graph), prefix=False, spec_width=args.width,
+                           drafter=d)
         eng.spec_force_accept = name == "forced_full_acceptance"
         eng.generate(prompts[:1], SamplingParams(max_tokens=8))
         c0 = dict(eng.counters)
@@ -109,6 +110,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=32768)
     ap.add_argument("--top-k", type=int, default=128)
     ap.add_argument("--ticks", type=int, default=32)
+    ap.add_argument("--graph", type=int, default=1, help="spec: replay verify ticks from CUDA graphs")
     args = ap.parse_args()
     from tilerl_b200.config import get_config
     from tilerl_b200.factory import build_model, make_ops
