@@ -386,6 +386,39 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
       };
       // prologue: the first SA weight tiles do not depend on the previous kernel
       int a_issued = 0, b_issued = 0;
+      const bool lockstep = SA == SB;   // equal rings: one barrier pair per stage serves both operands
+      if (lockstep) {
+        // both operands of a stage complete on full_a; the stage is free again on empty_a
+        auto load_ab_b = [&](const Cur& c) {   // activation half of stage c.st, onto full_a
+          const uint32_t st = smem_b0 + (uint32_t)c.st * C::B_STAGE;
+          tma_load_2d(st, &map_x, c.kt * KT_BYTES, c.ct * BN, full_a(c.st));
+#pragma unroll
+          for (int j = 0; j < C::SFB_ATOMS; ++j) {
+            const int atom_row = (c.ct * BN) / 128 + j;
+            bulk_load(st + C::B_ALLOC + j * 4 * SF_ATOM, p.sfx + ((size_t)(atom_row * p.kt4 + c.kt * 4)) * SF_ATOM,
+                      4 * SF_ATOM, full_a(c.st));
+          }
+        };
+        auto load_a_ls = [&](const Cur& c) {   // weight half, expecting the bytes of both halves
+          const uint32_t st = smem_a0 + (uint32_t)c.st * C::A_STAGE;
+          mbar_expect_tx(full_a(c.st), a_tx + b_tx);
+          tma_load_2d(st, &map_w, p.w_tiled ? 0 : c.kt * KT_BYTES,
+                      p.w_tiled ? (c.nt * p.nk + c.kt) * TILE_N : c.nt * TILE_N, full_a(c.st));
+          bulk_load(st + C::A_BYTES, p.sfw + ((size_t)(c.nt * p.kt4 + c.kt * 4)) * SF_ATOM, C::SFA_BYTES, full_a(c.st));
+        };
+        const int pre = min(SA, n_units);
+        for (; a_issued < pre; ++a_issued) load_a_ls(ca), advance(ca, SA);
+        pdl_wait();
+        bool ok = true;
+        for (; ok && b_issued < n_units; ++b_issued) {
+          if (b_issued >= pre) {
+            ok = mbar_wait(empty_a(cb.st), cb.ph ^ 1u, abort_flag);
+            if (!ok) break;
+            load_a_ls(ca), advance(ca, SA), ++a_issued;
+          }
+          load_ab_b(cb), advance(cb, SB);
+        }
+      } else {
       for (; a_issued < min(SA, n_units); ++a_issued) load_a(ca), advance(ca, SA);
       pdl_wait();
       bool ok = true;
@@ -404,6 +437,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         ok = mbar_wait(empty_a(ca.st), ca.ph ^ 1u, abort_flag);
         if (!ok) break;
         load_a(ca), advance(ca, SA), ++a_issued;
+      }
       }
     }
   } else if (warp == 1) {
@@ -429,7 +463,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
           tc_fence_after();
         }
         for (int i = 0; ok && i < len; ++i, ++it) {
-          ok = mbar_wait(full_a(sa_i), sa_ph, abort_flag) && mbar_wait(full_b(sb_i), sb_ph, abort_flag);
+          ok = mbar_wait(full_a(sa_i), sa_ph, abort_flag) && (SA == SB || mbar_wait(full_b(sb_i), sb_ph, abort_flag));
           if (!ok) break;
           tc_fence_after();
           const uint32_t aoff = (uint32_t)sa_i * (uint32_t)(C::A_STAGE >> 4);
@@ -447,7 +481,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             tc_mma_nvfp4_lh(tmem_base, a_lo + aoff + kb * 2, b_lo + boff + kb * 2, op_hi, idesc, sf_cols + kb * 4,
                             sf_cols + 16 + kb * 8, (i | kb) ? 1u : 0u);
           tc_commit(empty_a(sa_i));
-          tc_commit(empty_b(sb_i));
+          if (SA != SB) tc_commit(empty_b(sb_i));
           if (++sa_i == SA) sa_i = 0, sa_ph ^= 1u;
           if (++sb_i == SB) sb_i = 0, sb_ph ^= 1u;
         }
@@ -720,12 +754,11 @@ template <int BN>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, int grid, cudaStream_t st) {
   using C = Cfg<BN>;
   auto kern = gemm_nvfp4_kernel<BN>;
-  // default split of the ring budget: weights first (up to 8 stages, at least 2 activation stages)
-  int sb_min = 2;
-  int sa = (C::RING_BYTES - sb_min * C::B_STAGE) / C::A_STAGE;
+  // default: equal rings (one barrier pair per stage); unequal rings are an experiment knob --
+  // measured on the 27B shapes they did not pay for their second wait / commit per unit
+  int sa = C::RING_BYTES / (C::A_STAGE + C::B_STAGE);
   sa = sa > C::MAX_STAGES ? C::MAX_STAGES : sa;
-  int sb = (C::RING_BYTES - sa * C::A_STAGE) / C::B_STAGE;
-  sb = sb > C::MAX_STAGES ? C::MAX_STAGES : sb;
+  int sb = sa;
   if (const char* e = getenv("TRL_GEMM_SA")) sa = atoi(e);
   if (const char* e = getenv("TRL_GEMM_SB")) sb = atoi(e);
   if (sa < 1 || sb < 1 || sa > C::MAX_STAGES || sb > C::MAX_STAGES || C::smem_bytes(sa, sb) > 227 * 1024)
