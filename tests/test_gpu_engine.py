@@ -136,3 +136,25 @@ def test_seeded_sampling_is_reproducible_on_gpu(setup):
     b = eng.generate(p, sp)
     assert [r.tokens for r in a] == [r.tokens for r in b]
     assert all(len(r.logprobs) == len(r.tokens) and all(l <= 0 for l in r.logprobs) for r in a)
+
+
+def test_graph_captured_before_a_larger_prefill_stays_valid(setup):
+    """A decode graph captured at start-up must survive later growth of the shared workspace
+    (a longer prefill than any seen before the capture)."""
+    from tilerl_b200.engine import SamplingParams
+    from tilerl_b200.factory import build_engine, make_ops
+    cfg, _, model = setup
+    ops = make_ops("cuda")                    # fresh workspace: nothing allocated yet
+    ops.terms_small = ops.terms_large = 4
+    ops.gemv_tokens = 8
+    sp = SamplingParams(max_tokens=10)
+    prompts = _prompts(cfg, 2, 150, 21)
+    eager = build_engine(model, make_ops("cuda"), slots=4, max_ctx=512, graph=False, prefix=False)
+    eager.ops.terms_small = eager.ops.terms_large = 4
+    eager.ops.gemv_tokens = 8
+    want = [r.tokens for r in eager.generate(prompts, sp)]
+    eng = build_engine(model, ops, slots=4, max_ctx=512, graph=True, prefix=False)
+    eng.precapture((1, 2))                    # graphs first, on a workspace sized for 2 rows
+    got = [r.tokens for r in eng.generate(prompts, sp)]   # the 300-token prefill grows every buffer
+    assert eng.counters["graph_ticks"] > 0 and len(ops.ws.retired) > 0
+    assert got == want

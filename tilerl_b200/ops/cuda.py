@@ -31,11 +31,14 @@ GEMV_MAX_M = 8
 
 
 class Workspace:
-    """Named, lazily created, fixed-address device buffers."""
+    """Named, lazily created device buffers.  A buffer that has to grow is replaced, but the old
+    allocation is kept alive: CUDA graphs captured earlier hold its address (a decode graph
+    captured at start-up must survive the first long prefill growing the shared buffers)."""
 
     def __init__(self, device):
         self.device = device
         self.bufs: Dict[str, torch.Tensor] = {}
+        self.retired: list = []
 
     def get(self, name: str, shape, dtype) -> torch.Tensor:
         n = 1
@@ -45,6 +48,8 @@ class Workspace:
         if t is None or t.numel() < n or t.dtype != dtype:
             if t is not None and torch.cuda.is_current_stream_capturing():
                 raise RuntimeError(f"workspace buffer {name!r} would be reallocated during graph capture")
+            if t is not None:
+                self.retired.append(t)
             t = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self.bufs[name] = t
         return t[:n].view(*shape)

@@ -2,10 +2,13 @@
 
     python -m tilerl_b200.utils.config_probe --what spec   [--prompts 8 --gen 128 --width 8]
     python -m tilerl_b200.utils.config_probe --what sparse [--ctx 32768 --top-k 128 --ticks 32]
+    python -m tilerl_b200.utils.config_probe --what batch  [--requests 8 --prompt-len 7400 --gen 256]
 
 ``spec``: B = 1, prompts of 80..300 random ids, a width-W verify tick timed at forced full
 acceptance (drafts = the trunk's own greedy continuation), at zero acceptance (a constant
 draft) and with the random-init block drafter, against plain decoding (``--graph 0``: eager verify ticks).
+``batch``: ``--requests`` concurrent long prompts through continuous batching (chunked prefill,
+then CUDA-graph decode ticks of the whole batch): prefill tok/s and aggregate decode tok/s.
 ``sparse``: one sequence prefilled to ``ctx`` tokens, then decode ticks with dense attention
 (CUDA-graph) and with top-k page selection (Quest bounds, trailing window of 8 pages, refreshed
 every 8 ticks).  All times are wall clock around device-synchronised loops.
@@ -100,9 +103,43 @@ def sparse(args, cfg, ops, model):
     return out
 
 
+def batch(args, cfg, ops, model):
+    """Continuous batching of ``--requests`` long prompts (uniform-random ids), greedy decode."""
+    from tilerl_b200.engine import SamplingParams, StepLimits
+    from tilerl_b200.factory import build_engine
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab, (args.prompt_len,), generator=g).tolist() for _ in range(args.requests)]
+    eng = build_engine(model, ops, slots=args.requests + 1, max_ctx=args.prompt_len + args.gen + 64, graph=True,
+                       prefix=False, limits=StepLimits(max_batch=args.requests, max_batched_tokens=2048))
+    eng.generate([prompts[0][:64]], SamplingParams(max_tokens=4))
+    eng.precapture((args.requests,))
+    sp = SamplingParams(max_tokens=args.gen, ignore_eos=True)
+    rids = [eng.submit(p, sp) for p in prompts]
+
+    def prefill():
+        while any(eng.poll(r)["state"] in ("waiting", "prefill") for r in rids):
+            eng.step()
+    _, t_pre = _sync_time(prefill)
+    n0 = sum(eng.poll(r)["n_out"] for r in rids)
+    ticks0 = eng.counters["decode_ticks"]
+
+    def decode():
+        while any(eng.poll(r)["state"] != "done" for r in rids):
+            eng.step()
+    _, t_dec = _sync_time(decode)
+    n1 = sum(len(eng.take(r).tokens) for r in rids)
+    ticks = eng.counters["decode_ticks"] - ticks0
+    return dict(requests=args.requests, prompt_len=args.prompt_len, gen=args.gen,
+                prefill_s=round(t_pre, 2), prefill_tok_s=round(args.requests * args.prompt_len / t_pre, 1),
+                decode_s=round(t_dec, 2), decode_agg_tok_s=round((n1 - n0) / t_dec, 1),
+                ms_per_decode_tick=round(1000 * t_dec / max(1, ticks), 2), graph_ticks=eng.counters["graph_ticks"])
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", default="spec", choices=["spec", "sparse"])
+    ap.add_argument("--what", default="spec", choices=["spec", "sparse", "batch"])
+    ap.add_argument("--requests", type=int, default=8)
+    ap.add_argument("--prompt-len", type=int, default=7400)
     ap.add_argument("--model", default="qwen38-27b")
     ap.add_argument("--prompts", type=int, default=8)
     ap.add_argument("--gen", type=int, default=128)
@@ -117,7 +154,7 @@ def main():
     cfg = get_config(args.model)
     ops = make_ops("cuda")
     model = build_model(cfg, "cuda", seed=0, ops=ops)
-    res = spec(args, cfg, ops, model) if args.what == "spec" else sparse(args, cfg, ops, model)
+    res = {"spec": spec, "sparse": sparse, "batch": batch}[args.what](args, cfg, ops, model)
     print(json.dumps({"config": args.what, "model": cfg.name, **res}))
 
 
