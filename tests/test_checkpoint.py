@@ -37,6 +37,22 @@ def _hf_tensors(cfg, master, dialect):
             q = F.quantize_fp8_block(w)
             out[name + ".weight"] = q.w8
             out[name + ".weight_scale_inv"] = q.wscale
+        elif dialect == "fp8_channel":
+            s_ = w.abs().amax(-1).clamp_min(1e-12) / 448.0
+            out[name + ".weight"] = (w / s_.unsqueeze(-1)).to(torch.float8_e4m3fn)
+            out[name + ".weight_scale"] = s_
+        elif dialect == "mlx4":
+            from tilerl_b200.checkpoint import quantize_mlx4
+            g = 64 if w.shape[1] % 64 == 0 else 32
+            pk, sc, bi = quantize_mlx4(w, g)
+            out[name + ".weight"], out[name + ".scales"], out[name + ".biases"] = pk, sc, bi
+        elif dialect == "awq":
+            from tilerl_b200.checkpoint import quantize_awq
+            if w.shape[0] % 8 or w.shape[1] % 64 or name == "lm_head":
+                out[name + ".weight"] = w.to(torch.bfloat16)      # AWQ files keep the head and odd shapes dense
+            else:
+                qw, qz, sc = quantize_awq(w, 64)
+                out[name + ".qweight"], out[name + ".qzeros"], out[name + ".scales"] = qw, qz, sc
     out["model.embed_tokens.weight"] = master["embed"]
     out["model.norm.weight"] = master["final_norm"] - 1.0        # zero-centred storage
     put("lm_head", master["lm_head"])
@@ -71,7 +87,20 @@ def _hf_tensors(cfg, master, dialect):
     return {k: v.contiguous() for k, v in out.items()}
 
 
-@pytest.mark.parametrize("dialect,tol", [("bf16", 0.12), ("modelopt", 0.2), ("official", 0.2), ("fp8", 0.2)])
+def test_third_party_4bit_roundtrips():
+    from tilerl_b200.checkpoint import dequantize_awq, dequantize_mlx4, quantize_awq, quantize_mlx4
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(48, 256, generator=g) * 0.05
+    pk, sc, bi = quantize_mlx4(w)
+    assert pk.dtype == torch.int32 and pk.shape == (48, 32)
+    assert float((dequantize_mlx4(pk, sc, bi) - w).abs().max()) <= float(sc.max()) * 0.51
+    qw, qz, s16 = quantize_awq(w, 64)
+    assert qw.shape == (256, 6) and qz.shape == (4, 6) and s16.shape == (4, 48)
+    assert float((dequantize_awq(qw, qz, s16) - w).abs().max()) <= float(s16.float().max()) * 0.6
+
+
+@pytest.mark.parametrize("dialect,tol", [("bf16", 0.12), ("modelopt", 0.2), ("official", 0.2), ("fp8", 0.2),
+                                         ("fp8_channel", 0.2), ("mlx4", 0.25), ("awq", 0.25)])
 def test_load_hf_dialects(tmp_path, dialect, tol):
     cfg = tiny_hybrid()
     master = random_master(cfg, seed=3)

@@ -8,7 +8,10 @@ parameter dict (TP-sharded if asked):
 * NVFP4 "modelopt" files: ``<w>.weight_packed`` (or ``.weight`` uint8) + ``.weight_scale``
   (e4m3 per 16) + ``.weight_global_scale`` (stored as the *reciprocal* tensor scale);
 * official NVFP4 files: ``.weight`` uint8 + ``.weight_scale`` + ``.weight_scale_2``;
-* FP8 128x128-block files: ``.weight`` e4m3 + ``.weight_scale_inv``;
+* FP8 128x128-block files: ``.weight`` e4m3 + ``.weight_scale_inv``; FP8 per-tensor / per-channel:
+  ``.weight`` e4m3 + ``.weight_scale``;
+* MLX 4-bit: ``.weight`` uint32 (8 nibbles, low first) + ``.scales`` + ``.biases`` per group of 64;
+* AWQ: ``.qweight`` int32 ``[K, N/8]`` (AWQ nibble order) + ``.qzeros`` + ``.scales`` per group;
 * this framework's own dialect: ``<name>.wq / .scale / .tscale``.
 
 HF tensor names are mapped onto the fused layouts used here (gate/query interleave for
@@ -66,6 +69,69 @@ def validate_hf_config(cfg: ModelConfig, hf: Dict) -> None:
         raise CheckpointError("sliding-window attention is not supported")
 
 
+# ---- third-party 4-bit dialects ------------------------------------------------------------------
+AWQ_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)          # nibble i of a packed int32 holds output column AWQ_ORDER[i]
+AWQ_REVERSE = (0, 4, 1, 5, 2, 6, 3, 7)        # column c sits in nibble AWQ_REVERSE[c]
+
+
+def _nibbles(p: torch.Tensor) -> torch.Tensor:
+    """``[..., n]`` int32/uint32 -> ``[..., n, 8]`` nibbles, low bits first."""
+    q = p.to(torch.int64) & 0xFFFFFFFF
+    sh = torch.arange(0, 32, 4, dtype=torch.int64)
+    return (q.unsqueeze(-1) >> sh) & 0xF
+
+
+def dequantize_mlx4(w: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, group: int = 64) -> torch.Tensor:
+    """MLX affine 4-bit: ``w [N, K/8]`` packed, ``scales / biases [N, K/group]``; value = q * scale + bias."""
+    n = w.shape[0]
+    q = _nibbles(w).reshape(n, -1).float()
+    k = q.shape[1]
+    return (q.view(n, k // group, group) * scales.float().unsqueeze(-1) + biases.float().unsqueeze(-1)).view(n, k)
+
+
+def quantize_mlx4(w: torch.Tensor, group: int = 64):
+    """Inverse of :func:`dequantize_mlx4` (used by tests and tools): returns (packed, scales, biases)."""
+    n, k = w.shape
+    g = w.float().view(n, k // group, group)
+    lo, hi = g.amin(-1), g.amax(-1)
+    scale = ((hi - lo) / 15.0).clamp_min(1e-12)
+    q = torch.clamp(torch.round((g - lo.unsqueeze(-1)) / scale.unsqueeze(-1)), 0, 15).to(torch.int64).view(n, k // 8, 8)
+    sh = torch.arange(0, 32, 4, dtype=torch.int64)
+    packed = (q << sh).sum(-1)
+    packed = torch.where(packed >= 2 ** 31, packed - 2 ** 32, packed).to(torch.int32)
+    return packed, scale, lo
+
+
+def dequantize_awq(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """AWQ GEMM layout: ``qweight [K, N/8]``, ``qzeros [K/g, N/8]``, ``scales [K/g, N]`` ->
+    dense ``[N, K]`` (this framework keeps weights output-major)."""
+    k = qweight.shape[0]
+    rev = torch.tensor(AWQ_REVERSE)
+    q = _nibbles(qweight)[..., rev].reshape(k, -1).float()                 # [K, N]
+    z = _nibbles(qzeros)[..., rev].reshape(qzeros.shape[0], -1).float()     # [K/g, N]
+    g = k // z.shape[0]
+    w = (q.view(z.shape[0], g, -1) - z.unsqueeze(1)) * scales.float().unsqueeze(1)
+    return w.view(k, -1).t().contiguous()
+
+
+def quantize_awq(w: torch.Tensor, group: int = 128):
+    """Inverse of :func:`dequantize_awq` for tests and tools: dense ``[N, K]`` -> (qweight, qzeros, scales)."""
+    n, k = w.shape
+    wt = w.float().t().contiguous().view(k // group, group, n)               # [K/g, g, N]
+    lo, hi = wt.amin(1), wt.amax(1)
+    scale = ((hi - lo) / 15.0).clamp_min(1e-12)
+    zero = torch.clamp(torch.round(-lo / scale), 0, 15)
+    q = torch.clamp(torch.round(wt / scale.unsqueeze(1)) + zero.unsqueeze(1), 0, 15).to(torch.int64).view(k, n)
+    order = torch.tensor(AWQ_ORDER)
+
+    def pack(x):                                                             # [R, N] -> [R, N/8]
+        x = x.view(x.shape[0], -1, 8)[..., order]
+        sh = torch.arange(0, 32, 4, dtype=torch.int64)
+        p = (x << sh).sum(-1)
+        return torch.where(p >= 2 ** 31, p - 2 ** 32, p).to(torch.int32)
+    return pack(q), pack(zero.to(torch.int64)), scale.to(torch.float16)
+
+
 # ---- tensor-level readers ----------------------------------------------------------------------
 class _Reader:
     """All tensors of a directory, lazily, by name."""
@@ -94,10 +160,14 @@ class _Reader:
         if self.has(base + ".wq"):
             return dequantize_nvfp4(NVFP4Tensor(self.get(base + ".wq"), self.get(base + ".scale").view(torch.float8_e4m3fn),
                                                 self.get(base + ".tscale").float()))
+        if self.has(base + ".qweight"):
+            return dequantize_awq(self.get(base + ".qweight"), self.get(base + ".qzeros"), self.get(base + ".scales"))
         packed = base + ".weight_packed" if self.has(base + ".weight_packed") else base + ".weight"
         if not self.has(packed):
             raise CheckpointError(f"missing tensor for {base}")
         w = self.get(packed)
+        if w.dtype in (torch.uint32, torch.int32) and self.has(base + ".scales") and self.has(base + ".biases"):
+            return dequantize_mlx4(w, self.get(base + ".scales"), self.get(base + ".biases"))
         if w.dtype == torch.uint8 and self.has(base + ".weight_scale"):
             sc = self.get(base + ".weight_scale")
             sc = sc.view(torch.float8_e4m3fn) if sc.dtype == torch.uint8 else sc.to(torch.float8_e4m3fn)
