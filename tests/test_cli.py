@@ -62,3 +62,14 @@ def test_train_indexer_warmup(tmp_path, capsys):
                      "--save-model", out, "--runs", str(tmp_path / "r"), "--device", "cpu"]) == 0
     rec = json.loads([l for l in capsys.readouterr().out.splitlines() if l.startswith("{")][-1])
     assert rec["steps"] == 3 and os.path.exists(os.path.join(out, "indexer.safetensors"))
+
+
+def test_train_adapters_with_evals_and_best_adapter(tmp_path, capsys):
+    out = str(tmp_path / "ad")
+    assert cli.main(["train", "--model", "tiny-hybrid", "--device", "cpu", "--rl", "--lora-rank", "2", "--steps", "3",
+                     "--group", "2", "--prompts-per-step", "1", "--max-tokens", "4", "--eval-every", "1",
+                     "--patience", "5", "--save-model", out, "--runs", str(tmp_path / "r"), "--prompt-len", "6"]) == 0
+    rec = json.loads([l for l in capsys.readouterr().out.splitlines() if l.startswith("{")][-1])
+    assert rec["steps"] == 3 and len(rec["evals"]) == 3 and rec["best_eval"] is not None
+    assert os.path.exists(os.path.join(out, "adapter.safetensors"))
+    assert os.path.exists(os.path.join(out, "adapter-best.safetensors"))

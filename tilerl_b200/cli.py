@@ -73,6 +73,8 @@ def build_parser() -> argparse.ArgumentParser:
     t.add_argument("--served-fp4", action="store_true")
     t.add_argument("--indexer-warmup", action="store_true", help="train the learned sparse-KV page indexer")
     t.add_argument("--ctx", type=int, default=None, help="sequence length of the indexer warm-up batches")
+    t.add_argument("--eval-every", type=int, default=0, help="adapter runs: eval reward on held-out prompts every N steps")
+    t.add_argument("--patience", type=int, default=3, help="adapter runs: stop after this many evals without improvement")
     t.add_argument("--runs", default="runs")
 
     b = sub.add_parser("bench", help="prefill / decode throughput, kernel roofline table, calibration")
@@ -222,6 +224,18 @@ def cmd_train(args) -> int:
     g = torch.Generator().manual_seed(args.seed)
     prompts = [torch.randint(0, cfg.vocab, (args.prompt_len,), generator=g).tolist() for _ in range(64)]
     post = (lambda m: m.requantize_()) if not flags.get("lora_rank") else None
+    if flags.get("lora_rank") and (flags.get("rl") or flags.get("opd")) and (args.eval_every or flags.get("eval_every")):
+        # adapter run with evals, early stop and best-adapter save
+        kw = dict(max_tokens=flags["max_tokens"], prompts_per_step=flags["prompts_per_step"])
+        if not flags.get("opd"):
+            kw.update(group=flags["group"], clip_eps=args.clip_eps, kl_coef=args.kl_coef, micro=flags.get("micro") or 0)
+        out = rl.train_adapters(eng, model, prompts[:48], evals.REWARDS.get(flags["reward"], evals.reward_even), opt,
+                                steps=flags["steps"], eval_prompts=prompts[48:], eval_every=args.eval_every or flags["eval_every"],
+                                patience=flags.get("patience", args.patience), save_dir=args.save_model, run=run,
+                                opd=bool(flags.get("opd")), **kw)
+        print(json.dumps({k: v for k, v in out.items() if k != "history"}, default=str), flush=True)
+        run.finish()
+        return 0
     if flags.get("opd"):
         loop = rl.opd_loop(eng, model, prompts, opt, steps=flags["steps"], max_tokens=flags["max_tokens"],
                            prompts_per_step=flags["prompts_per_step"])

@@ -311,3 +311,59 @@ def pretrain(model, data: Iterator[torch.Tensor], optimizer, *, steps: int, lr: 
     if ckpt_dir:
         save_checkpoint(model, os.path.join(ckpt_dir, "final"))
     return history
+
+
+def eval_reward(engine: Engine, prompts: Sequence[Sequence[int]], reward_fn: Callable, *, max_tokens: int = 16,
+                seed: int = 12345) -> float:
+    """Mean reward of greedy completions on held-out prompts (the eval signal of adapter runs)."""
+    res = engine.generate([list(p) for p in prompts], SamplingParams(max_tokens=max_tokens, seed=seed))
+    return sum(float(reward_fn(p, r.tokens)) for p, r in zip(prompts, res)) / max(1, len(prompts))
+
+
+def train_adapters(engine: Engine, model, prompts: Sequence[Sequence[int]], reward_fn: Callable, optimizer, *,
+                   steps: int, eval_prompts: Optional[Sequence[Sequence[int]]] = None, eval_every: int = 0,
+                   patience: int = 3, save_dir: Optional[str] = None, run=None, opd: bool = False,
+                   **loop_kw) -> Dict[str, object]:
+    """Adapter (LoRA) GRPO / OPD run with periodic evals, early stopping on the eval reward, the
+    best adapter kept on disk and every step logged to the run manifest.
+
+    Parity: reference ``_train_adapters`` (``src/tilerl/train.py:1920-2535``): evals, early stop,
+    ``adapter.safetensors`` + ``adapter-best.safetensors``, run manifest with gates."""
+    from .checkpoint import save_adapter
+    from .ledger import EarlyStop
+    stop = EarlyStop(patience=patience)
+    history: List[Dict[str, object]] = []
+    evals: List[Dict[str, float]] = []
+    if opd:
+        loop = opd_loop(engine, model, prompts, optimizer, steps=steps, **loop_kw)
+    else:
+        loop = grpo_loop(engine, model, prompts, reward_fn, optimizer, steps=steps, **loop_kw)
+    stopped = False
+    for m in loop:
+        history.append(m)
+        if run is not None:
+            run.log(**{k: v for k, v in m.items() if not isinstance(v, dict)})
+        step = int(m["step"])
+        if eval_every and eval_prompts and (step + 1) % eval_every == 0:
+            score = eval_reward(engine, eval_prompts, reward_fn, max_tokens=loop_kw.get("max_tokens", 16))
+            evals.append(dict(step=step, reward=score))
+            if run is not None:
+                run.log(step=step, eval_reward=score)
+            done = stop.update(score, step)
+            if stop.improved and save_dir:
+                os.makedirs(save_dir, exist_ok=True)
+                save_adapter(model, os.path.join(save_dir, "adapter-best.safetensors"))
+            if done:
+                stopped = True
+                break
+    if save_dir:
+        os.makedirs(save_dir, exist_ok=True)
+        save_adapter(model, os.path.join(save_dir, "adapter.safetensors"))
+    out = dict(steps=len(history), evals=evals, best_eval=stop.best, best_step=stop.best_step,
+               early_stopped=stopped, history=history)
+    if run is not None:
+        if stop.best is not None and evals:
+            run.gate("eval_reward_not_worse", stop.best, evals[0]["reward"])
+        if save_dir:
+            run.artifacts["adapter"] = os.path.join(save_dir, "adapter.safetensors")
+    return out
