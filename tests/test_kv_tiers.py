@@ -64,3 +64,29 @@ def test_boot_store_roundtrip_fingerprint_and_crc(tmp_path):
     again = make_engine(cfg, model=eng.model)
     again.prefix = PrefixStore(again.kv)
     assert store.boot(again) == dict(loaded=0, skipped_fingerprint=0, corrupt=1)
+
+
+def test_prefix_store_demotes_to_the_host_tier_and_promotes_on_a_hit():
+    """An entry evicted from the device store comes back from host memory with the same tokens,
+    KV pages and GDN snapshot -- the request that hits it produces what a cold run produces."""
+    from helpers import rand_prompts
+    from tilerl_b200.config import tiny_hybrid
+    from tilerl_b200.engine import Engine, SamplingParams
+    from tilerl_b200.kv import GdnStatePool, PagedKvPool, PrefixStore
+    from tilerl_b200.kv_tiers import DramSnapshots, HostKvPages
+    from tilerl_b200.models.hybrid import HybridModel
+    from tilerl_b200.ops.backend import RefOps
+    cfg = tiny_hybrid()
+    model = HybridModel.build_random(cfg, seed=1)
+    kv = PagedKvPool(cfg, 64, dtype=torch.float32)
+    st = GdnStatePool(cfg, 6, ring_dtype=torch.float32)
+    store = PrefixStore(kv, max_entries=1, host=HostKvPages(1 << 26), dram=DramSnapshots(1 << 26))
+    eng = Engine(model, RefOps(), kv, st, prefix_store=store)
+    a, b = rand_prompts(cfg, 2, 40)
+    sp = SamplingParams(max_tokens=5)
+    cold = eng.generate([a], sp)[0]
+    eng.generate([b], sp)                          # max_entries = 1: publishing b evicts a -> host tier
+    assert store.demotions >= 1 and len(store.cold) >= 1
+    warm = eng.generate([a], sp)[0]
+    assert store.promotions == 1
+    assert warm.tokens == cold.tokens and warm.cached_tokens == 32

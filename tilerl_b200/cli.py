@@ -44,6 +44,9 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--sparse-window-tokens", type=int, default=128)
     s.add_argument("--sparse-refresh-ticks", type=int, default=8)
     s.add_argument("--kv-store", default=None, help="directory of the cold-start KV store")
+    s.add_argument("--kv-cold-bytes", type=int, default=0, help="pinned host bytes for demoted prefix pages (0: off)")
+    s.add_argument("--dram-bytes", type=int, default=1 << 30, help="host bytes for demoted GDN snapshots")
+    s.add_argument("--cold-ssd-path", default=None, help="spill file behind the host tier")
     s.add_argument("--completion-timeout-s", type=float, default=600.0)
     s.add_argument("--stream-pace", action="store_true")
     s.add_argument("--no-warmup", action="store_true")
@@ -152,6 +155,13 @@ def cmd_serve(args) -> int:
                        drafter=drafter, sparse=sparse,
                        limits=StepLimits(args.max_batch, args.max_batched_tokens, max_inflight=args.max_inflight),
                        eos_id=tok.eos_id, detokenize=tok.decode, think_ids=getattr(tok, "think_ids", None))
+    if args.kv_cold_bytes and hasattr(eng.prefix, "host"):
+        from .kv_tiers import ColdSsdFile, DramSnapshots, HostKvPages
+        ssd = None
+        if args.cold_ssd_path:
+            ssd = ColdSsdFile(args.cold_ssd_path, slot_bytes=eng.kv.block_bytes(), slots=4096)
+        eng.prefix.host = HostKvPages(args.kv_cold_bytes, pin=dev != "cpu", cold=ssd)
+        eng.prefix.dram = DramSnapshots(args.dram_bytes)
     if args.kv_store:
         from .kv_tiers import KvBootStore
         print(json.dumps({"kv_boot": KvBootStore(args.kv_store).boot(eng)}))

@@ -209,15 +209,29 @@ class NoPrefixStore:
         return 0
 
 
+@dataclass
+class _Cold:
+    """An evicted entry whose pages live in the host tier (content keys) and whose GDN snapshot
+    lives in the DRAM tier."""
+    tokens: Tuple[int, ...]
+    page_keys: List[str]
+    has_snapshot: bool
+
+
 class PrefixStore:
     def __init__(self, pool: PagedKvPool, max_entries: int = 256,
-                 max_state_bytes: int = 1 << 30):
+                 max_state_bytes: int = 1 << 30, host=None, dram=None, max_cold: int = 1024):
+        """``host`` (``kv_tiers.HostKvPages``) and ``dram`` (``kv_tiers.DramSnapshots``): evicted
+        entries are demoted there instead of being dropped, and promoted back on a later hit."""
         self.pool = pool
         self.max_entries = max_entries
         self.max_state_bytes = max_state_bytes
         self.entries: "OrderedDict[int, _Entry]" = OrderedDict()
         self.state_bytes = 0
         self.hits = self.misses = self.evictions = 0
+        self.host, self.dram, self.max_cold = host, dram, max_cold
+        self.cold: "OrderedDict[int, _Cold]" = OrderedDict()
+        self.promotions = self.demotions = 0
 
     def __len__(self) -> int:
         return len(self.entries)
@@ -264,13 +278,55 @@ class PrefixStore:
                 self.pool.incref(b)
             self.hits += 1
             return PrefixHit(n, list(e.blocks), e.snapshot)
+        for i in range(limit - 1, -1, -1):          # colder: pages in host memory / on SSD
+            hit = self._promote(hashes[i], tokens[:(i + 1) * KV_BLOCK])
+            if hit is not None:
+                self.hits += 1
+                return hit
         self.misses += 1
         return None
+
+    def _promote(self, key: int, tokens: Sequence[int]) -> Optional[PrefixHit]:
+        c = self.cold.get(key)
+        if c is None or c.tokens != tuple(int(t) for t in tokens):
+            return None
+        if self.pool.free_blocks < len(c.page_keys):
+            self.evict_until_free(len(c.page_keys))
+            if self.pool.free_blocks < len(c.page_keys):
+                return None
+        pages = [self.host.promote(k) for k in c.page_keys]
+        snap = self.dram.get(key, self.pool.k.device) if (c.has_snapshot and self.dram is not None) else None
+        if any(p is None for p in pages) or (c.has_snapshot and snap is None):
+            del self.cold[key]                      # a tier dropped part of it: the entry is gone
+            return None
+        blocks = []
+        for k, v in pages:
+            b = self.pool.alloc_block()
+            self.pool.write_block(b, k.to(self.pool.k.device), v.to(self.pool.k.device))
+            blocks.append(b)
+        del self.cold[key]
+        sb = 0 if snap is None else sum(t.numel() * t.element_size() for t in snap)
+        self.entries[key] = _Entry(c.tokens, blocks, snap, sb)     # the store keeps the allocation's reference
+        self.state_bytes += sb
+        self.promotions += 1
+        for b in blocks:
+            self.pool.incref(b)                     # the requester's reference
+        return PrefixHit(len(c.tokens), list(blocks), snap)
 
     def _evict_one(self) -> bool:
         if not self.entries:
             return False
-        _, e = self.entries.popitem(last=False)
+        key, e = self.entries.popitem(last=False)
+        if self.host is not None:
+            keys = [self.host.demote(*self.pool.read_block(b)) for b in e.blocks]
+            if e.snapshot is not None and self.dram is not None:
+                self.dram.put(key, e.snapshot)
+            self.cold[key] = _Cold(e.tokens, keys, e.snapshot is not None and self.dram is not None)
+            self.demotions += 1
+            while len(self.cold) > self.max_cold:
+                _, old = self.cold.popitem(last=False)
+                for k in old.page_keys:
+                    self.host.release(k)
         for b in e.blocks:
             self.pool.release(b)
         self.state_bytes -= e.state_bytes
