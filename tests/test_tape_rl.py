@@ -131,3 +131,43 @@ def test_clipped_ratio_zeroes_gradient():
     st = rl.policy_step(m, ids, [3], [6], torch.tensor([1.0]), None, old_logprobs=old,
                         return_grads=True, max_norm=0.0)
     assert st["clipped"] == 3 and all(float(g.abs().max()) == 0 for g in st["grads"].values())
+
+
+def test_fused_head_cross_entropy_equals_the_unfused_path():
+    """The chunked lm_head + CE op (never forms [T, V]) gives the same loss, log-probabilities and
+    gradients as head -> logits -> cross-entropy, for the SFT mask and for PPO-clip weights, with a
+    frozen and with a trainable head."""
+    import torch
+    from tilerl_b200 import rl
+    from tilerl_b200 import tape as T
+    from tilerl_b200.config import tiny_hybrid
+    from tilerl_b200.models.hybrid import HybridModel
+    from tilerl_b200.ops import ref
+    cfg = tiny_hybrid()
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg.vocab, (3, 11), generator=g)
+    adv = torch.tensor([1.0, -0.5, 0.25])
+    model = HybridModel.build_random(cfg, seed=2, keep_master=True)
+    outs = []
+    for fused in (False, True):
+        st = rl.policy_step(model, ids, [4, 3, 5], [11, 9, 10], adv, None, clip_eps=0.2, micro=2,
+                            return_grads=True, fused_ce=fused)
+        outs.append(st)
+    assert abs(outs[0]["loss"] - outs[1]["loss"]) < 1e-5
+    for k, gref in outs[0]["grads"].items():
+        assert torch.allclose(outs[1]["grads"][k], gref, atol=2e-5, rtol=1e-4), k
+    # the op itself, trainable head, chunk smaller than the token count
+    h = torch.randn(2, 7, cfg.hidden, generator=g)
+    w = torch.randn(cfg.vocab, cfg.hidden, generator=g) * 0.05
+    tg = torch.randint(0, cfg.vocab, (2, 7), generator=g)
+    wt = torch.rand(2, 7, generator=g)
+    tp = T.Tape()
+    tp.watch(h, w)
+    loss, lp = T.linear_cross_entropy(tp, h, w, tg, lambda l: wt, frozen=False, chunk=4)
+    grads = tp.backward(loss)
+    h2, w2 = h.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    lg = h2 @ w2.t()
+    lp_ref = ref.token_logprobs(lg.reshape(-1, cfg.vocab), tg.reshape(-1)).view(2, 7)
+    (-(wt * lp_ref).sum()).backward()
+    assert torch.allclose(lp, lp_ref.detach(), atol=1e-5)
+    assert torch.allclose(grads[id(h)], h2.grad, atol=1e-5) and torch.allclose(grads[id(w)], w2.grad, atol=1e-5)

@@ -282,7 +282,8 @@ class HybridModel:
         return y
 
     def forward_dense(self, tape, ids: torch.Tensor, *, checkpoint_layers: bool = False,
-                      positions: Optional[torch.Tensor] = None, hook=None, cp=None) -> torch.Tensor:
+                      positions: Optional[torch.Tensor] = None, hook=None, cp=None,
+                      return_hidden: bool = False):
         """Full-sequence forward on dense ``ids [B, T]`` with every op recorded on
         ``tape``; no KV cache, zero initial GDN state.  Returns this rank's logits
         ``[B, T, vocab_local]`` (full vocab at TP=1).  ``hook`` (a parameter sharder) is told
@@ -349,4 +350,6 @@ class HybridModel:
         head = "embed" if cfg.tie_embeddings else "lm_head"
         w = P.get("master." + head, P[head])
         frozen = id(w) not in tape.leaves
+        if return_hidden:          # the caller fuses the head with its loss (never forms [T, vocab])
+            return h, w, frozen
         return T.linear(tape, h, w, frozen=frozen)

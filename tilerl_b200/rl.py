@@ -96,11 +96,19 @@ def _scored_mask(ids: torch.Tensor, prompt_lens, seq_lens) -> torch.Tensor:
 
 def forward_backward(model, ids: torch.Tensor, targets: torch.Tensor, weights_fn, *,
                      trainable: Dict[str, torch.Tensor], tp_group=None, tp_world: int = 1,
-                     checkpoint_layers: bool = False, on_grad=None, hook=None):
+                     checkpoint_layers: bool = False, on_grad=None, hook=None, fused_ce: bool = False,
+                     lp_weights_fn=None):
     """One micro-batch: dense forward on a fresh tape, weights from ``weights_fn(logits)``,
-    cross-entropy op, backward.  Returns (loss, named grads, logits)."""
+    cross-entropy op, backward.  Returns (loss, named grads, logits).  With ``fused_ce`` the head
+    and the loss run chunked (``tape.linear_cross_entropy``): ``lp_weights_fn(logprobs [B, T])``
+    gives the weights and the third return value is the target log-probabilities."""
     tp = T.Tape(tp_group, tp_world)
     tp.watch(*trainable.values())
+    if fused_ce and tp_world == 1:
+        h, w, frozen = model.forward_dense(tp, ids, checkpoint_layers=checkpoint_layers, hook=hook, return_hidden=True)
+        loss, lp = T.linear_cross_entropy(tp, h, w, targets, lp_weights_fn, frozen=frozen)
+        grads = tp.backward(loss, on_grad=on_grad)
+        return float(loss), _named_grads(trainable, grads), lp
     logits = model.forward_dense(tp, ids, checkpoint_layers=checkpoint_layers, hook=hook)
     w = weights_fn(logits)
     loss = T.cross_entropy(tp, logits, targets, w)
@@ -122,7 +130,8 @@ def train_step(model, ids: torch.Tensor, optimizer, *, seq_lens=None, max_norm: 
     for s in range(0, b, mb):
         m = mask[s:s + mb].float() / n
         loss, grads, _ = forward_backward(model, ids[s:s + mb], targets[s:s + mb],
-                                          lambda lg, m=m: m.to(lg.device), trainable=trainable, **fb)
+                                          lambda lg, m=m: m.to(lg.device), trainable=trainable,
+                                          lp_weights_fn=lambda lp, m=m: m.to(lp.device), **fb)
         total += loss
         for k, g in grads.items():
             acc[k] = g if k not in acc else acc[k] + g
@@ -150,8 +159,7 @@ def policy_step(model, ids: torch.Tensor, prompt_lens, seq_lens, advantages: tor
         sl = slice(s, s + mb)
         adv = advantages[sl, None].float()
 
-        def weights(lg, sl=sl, adv=adv):
-            lp = ref.token_logprobs(lg.reshape(-1, lg.shape[-1]), targets[sl].reshape(-1)).view(lg.shape[:2])
+        def weights_lp(lp, sl=sl, adv=adv):
             if old_logprobs is None:
                 rho = torch.ones_like(lp)
             else:
@@ -166,7 +174,12 @@ def policy_step(model, ids: torch.Tensor, prompt_lens, seq_lens, advantages: tor
             stats["ratio_mean"] += float((rho * m).sum())
             return w * m / n
 
-        loss, grads, _ = forward_backward(model, ids[sl], targets[sl], weights, trainable=trainable, **fb)
+        def weights(lg, sl=sl):
+            lp = ref.token_logprobs(lg.reshape(-1, lg.shape[-1]), targets[sl].reshape(-1)).view(lg.shape[:2])
+            return weights_lp(lp)
+
+        loss, grads, _ = forward_backward(model, ids[sl], targets[sl], weights, trainable=trainable,
+                                          lp_weights_fn=weights_lp, **fb)
         stats["loss"] += loss
         for k, g in grads.items():
             acc[k] = g if k not in acc else acc[k] + g

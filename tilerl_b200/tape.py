@@ -438,6 +438,50 @@ def cross_entropy(tape: Tape, logits: torch.Tensor, targets: torch.Tensor,
 
 
 @_nograd
+def linear_cross_entropy(tape: Tape, h: torch.Tensor, w: torch.Tensor, targets: torch.Tensor, weights_fn: Callable,
+                         *, frozen: bool = True, chunk: int = 1024):
+    """lm_head + weighted cross-entropy without ever holding ``[T, V]``: the head GEMM runs in
+    token chunks twice -- pass 1 collects the log-probability of every target token, the caller's
+    ``weights_fn(logprobs [T]) -> weights [T]`` (SFT mask / N, or the PPO-clip weight times the
+    advantage) turns them into per-token weights, pass 2 recomputes each chunk's logits and
+    immediately folds ``w_i (softmax - onehot)`` into dH (and dW when the head is trainable).
+    Returns ``(loss, logprobs)``; the gradients are final, backward only scales them.
+
+    Parity: the reference forms the full logits and overwrites them with the gradient
+    (``tilerl_kernels/backend.py:1651-1672``, ``reference.py:1511-1603``)."""
+    t_shape = h.shape[:-1]
+    hf = h.reshape(-1, h.shape[-1])
+    tg = targets.reshape(-1).long()
+    n = hf.shape[0]
+    cd = torch.bfloat16 if h.is_cuda else torch.float32
+    wc = w if w.dtype == cd else w.to(cd)
+    lp = torch.empty(n, dtype=torch.float32, device=h.device)
+    for a in range(0, n, chunk):
+        lg = (hf[a:a + chunk].to(cd) @ wc.t()).float()
+        lp[a:a + chunk] = lg.gather(-1, tg[a:a + chunk, None]).squeeze(-1) - torch.logsumexp(lg, -1)
+    wts = weights_fn(lp.view(t_shape)).reshape(-1).float().to(h.device)
+    loss = -(wts * lp).sum()
+    dh = torch.empty(n, hf.shape[-1], dtype=torch.float32, device=h.device)
+    dw = None if frozen else torch.zeros(w.shape, dtype=torch.float32, device=h.device)
+    for a in range(0, n, chunk):
+        hc = hf[a:a + chunk].to(cd)
+        lg = (hc @ wc.t()).float()
+        g = torch.softmax(lg, -1)
+        g[torch.arange(g.shape[0], device=g.device), tg[a:a + chunk]] -= 1.0
+        g = (g * wts[a:a + chunk, None]).to(cd)
+        dh[a:a + chunk] = (g @ wc).float()
+        if dw is not None:
+            dw += (g.t() @ hc).float()
+    dh = dh.view(h.shape)
+
+    def bwd(g):
+        return (dh * g, dw * g) if dw is not None else (dh * g,)
+
+    tape.record("linear_cross_entropy", (h, w) if dw is not None else (h,), (loss,), bwd)
+    return loss, lp.view(t_shape)
+
+
+@_nograd
 def tp_fork(tape: Tape, x: torch.Tensor) -> torch.Tensor:
     """Identity forward; all-reduce of the gradient in backward (entry of a
     column-parallel region)."""

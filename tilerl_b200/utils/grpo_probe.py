@@ -52,7 +52,7 @@ def main():
     rows = []
     for m in rl.grpo_loop(eng, model, prompts, evals.reward_mod7, opt, steps=args.steps, group=args.group,
                           prompts_per_step=args.prompts, max_tokens=args.gen, clip_eps=0.2, kl_coef=0.0,
-                          micro=args.micro, post_step=post, checkpoint_layers=True):
+                          micro=args.micro, post_step=post, checkpoint_layers=True, fused_ce=True):
         torch.cuda.synchronize()
         rows.append(m)
         print(json.dumps(m, default=float), flush=True)

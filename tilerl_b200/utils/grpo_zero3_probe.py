@@ -91,7 +91,7 @@ def main():
         slens = [len(s) for s in seqs]
         ids = rl.pad_batch(seqs).to(dev)
         stats = rl.policy_step(trainer, ids, plens, slens, adv[mine], z, clip_eps=0.2, kl_coef=0.0, max_norm=0.0,
-                               micro=args.micro, checkpoint_layers=True, on_grad=z.on_grad, hook=z)
+                               micro=args.micro, checkpoint_layers=True, on_grad=z.on_grad, hook=z, fused_ce=True)
         torch.cuda.synchronize()
         t_c = time.perf_counter()
         rs = resync(z, rollout, quantize=ops.quantize_new, refresh=ops.refresh_weight, engine=eng)
