@@ -246,3 +246,19 @@ def test_web_client_modules_are_served(served):
                 assert f'"{frame}"' in proto
 
     run(go())
+
+
+def test_messages_request_capture(served, tmp_path, monkeypatch):
+    eng, app = served
+    rec = tmp_path / "req.jsonl"
+    monkeypatch.setenv("TRL_MESSAGES_RECORD", str(rec))
+
+    async def go():
+        async with _client(app) as client:
+            r = await client.post("/v1/messages", json={"model": "m", "max_tokens": 4,
+                                                        "messages": [{"role": "user", "content": "hi"}]})
+            assert r.status_code == 200
+
+    run(go())
+    lines = rec.read_text().splitlines()
+    assert len(lines) == 1 and json.loads(lines[0])["body"]["max_tokens"] == 4

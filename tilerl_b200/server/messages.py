@@ -14,6 +14,8 @@ from __future__ import annotations
 
 import asyncio
 import json
+import time
+import os
 from typing import Any, Dict, List
 
 from fastapi import Request
@@ -95,6 +97,19 @@ def _blocks(f: core.Final) -> List[Dict[str, Any]]:
     return blocks
 
 
+def _record(body) -> None:
+    """``TRL_MESSAGES_RECORD=<file>``: append every request body as one JSON line (request capture
+    for replaying client traffic; reference ``TILERL_MESSAGES_RECORD``, ``src/tilerl/messages.py``)."""
+    path = os.environ.get("TRL_MESSAGES_RECORD")
+    if not path:
+        return
+    try:
+        with open(path, "a", encoding="utf-8") as f:
+            f.write(json.dumps({"t": time.time(), "body": body}) + "\n")
+    except OSError:
+        pass                      # capture must never fail a request
+
+
 def mount(app, ctx: core.ServeContext) -> None:
     def err(status: int, typ: str, msg: str):
         return JSONResponse({"type": "error", "error": {"type": typ, "message": msg}}, status_code=status)
@@ -103,6 +118,7 @@ def mount(app, ctx: core.ServeContext) -> None:
     async def messages(request: Request):
         try:
             body = await request.json()
+            _record(body)
             n = _normalise(body)
             job = core.submit(ctx, to_chat_messages(body), tools=n["tools"], thinking=n["thinking"],
                               max_tokens=n["max_tokens"], body=body, stop=n["stop"], think_cap=n["cap"])
