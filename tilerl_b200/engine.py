@@ -281,10 +281,18 @@ class Engine:
         self._stop.clear()
 
         def loop():
+            last_probe = time.monotonic()
             while not self._stop.is_set():
                 if not self.has_work():
                     self._wake.wait(0.05)
                     self._wake.clear()
+                    # idle: probe the device now and then, so a dead context is noticed before
+                    # the next request pays for it
+                    if time.monotonic() - last_probe > 5.0 and hasattr(self.ops, "device_alive"):
+                        last_probe = time.monotonic()
+                        if not self.ops.device_alive():  # pragma: no cover - needs a dead device
+                            self._degraded = "device does not answer"
+                            fatal_device_exit(self._degraded)
                     continue
                 if not self._running and batching_window_s > 0:
                     time.sleep(batching_window_s)  # let concurrent submits coalesce

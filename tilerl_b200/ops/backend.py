@@ -67,6 +67,9 @@ class RefOps:
         h = ref.rmsnorm(x, norm_w, eps)
         return ref.swiglu(self._lora(ref.linear(h, w), h, lora)).to(self.act_dtype)
 
+    def device_alive(self) -> bool:
+        return True
+
     def linear_residual(self, a, w, residual, lora=None):
         """Row-parallel linear: partial product, all-reduce over TP, residual add."""
         y = self._lora(ref.linear(a, w), a, lora)

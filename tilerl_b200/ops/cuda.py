@@ -361,6 +361,18 @@ class CudaOps:
         self.quantize_nvfp4_(w.contiguous(), dst)
         return dst
 
+    def device_alive(self) -> bool:
+        """Synchronising probe: False when the context no longer answers (sticky error).  The engine
+        loop polls it and exits the process on False so a supervisor restarts it.
+        Parity: ``Backend.device_alive`` (``tilerl_kernels/backend.py:442-465``)."""
+        try:
+            t = torch.zeros(1, device=self.device)
+            t.add_(1)
+            torch.cuda.synchronize(self.device)
+            return bool(t.item() == 1.0)
+        except RuntimeError:
+            return False
+
     def refresh_weight(self, w: NVFP4Tensor) -> None:
         """Bring the GEMM's tile-contiguous copies of a rewritten weight up to date (in place)."""
         from .gemm_tc import sf_tiled, wq_tiled
