@@ -85,6 +85,21 @@ def _named_grads(trainable: Dict[str, torch.Tensor], grads_by_id) -> Dict[str, t
     return {n: grads_by_id[id(t)] for n, t in trainable.items() if id(t) in grads_by_id}
 
 
+TP_PARTIAL_REPLICATED = ("q_norm", "k_norm", "gdn_norm")
+
+
+def tp_sync_replicated_grads(grads: Dict[str, torch.Tensor], group) -> None:
+    """Per-head norm weights are replicated over the TP ranks but each rank applies them to its own
+    heads only, so its gradient is a partial sum: add the ranks' parts (sorted names: same order
+    everywhere).  Every other replicated tensor sees complete gradients thanks to ``tp_fork``."""
+    import torch.distributed as dist
+    for k in sorted(grads):
+        if k.split(".")[-1] in TP_PARTIAL_REPLICATED:
+            g = grads[k].contiguous()
+            dist.all_reduce(g, group=group)
+            grads[k] = g
+
+
 def _scored_mask(ids: torch.Tensor, prompt_lens, seq_lens) -> torch.Tensor:
     """Positions i whose *next* token is a completion token: plen-1 <= i < slen-1."""
     b, t = ids.shape
@@ -110,6 +125,15 @@ def forward_backward(model, ids: torch.Tensor, targets: torch.Tensor, weights_fn
         grads = tp.backward(loss, on_grad=on_grad)
         return float(loss), _named_grads(trainable, grads), lp
     logits = model.forward_dense(tp, ids, checkpoint_layers=checkpoint_layers, hook=hook)
+    if tp_world > 1:
+        # vocab-parallel logits: the loss and the weights come from the sharded CE
+        if lp_weights_fn is None:
+            raise ValueError("tensor-parallel training needs lp_weights_fn (weights from target log-probabilities)")
+        loss, lp = T.cross_entropy_tp(tp, logits, targets, lp_weights_fn)
+        grads = tp.backward(loss, on_grad=on_grad)
+        named = _named_grads(trainable, grads)
+        tp_sync_replicated_grads(named, tp_group)
+        return float(loss), named, lp
     w = weights_fn(logits)
     loss = T.cross_entropy(tp, logits, targets, w)
     grads = tp.backward(loss, on_grad=on_grad)

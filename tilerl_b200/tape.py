@@ -438,6 +438,40 @@ def cross_entropy(tape: Tape, logits: torch.Tensor, targets: torch.Tensor,
 
 
 @_nograd
+def cross_entropy_tp(tape: Tape, logits: torch.Tensor, targets: torch.Tensor, lp_weights_fn: Callable):
+    """Vocab-parallel weighted cross-entropy: ``logits [.., V / tp]`` is this rank's shard.  Three
+    all-reduces of per-token scalars (max, sum-exp, picked logit) give every rank the target
+    log-probabilities; ``lp_weights_fn(logprobs) -> weights`` and the local gradient shard follow,
+    so the full ``[T, V]`` logits are never gathered.  Returns ``(loss, logprobs)``.
+    Parity: reference ``tilerl_kernels/reference.py:1541-1603`` (sharded CE)."""
+    import torch.distributed as dist
+    lg = logits.reshape(-1, logits.shape[-1]).float()
+    tg = targets.reshape(-1).long()
+    v_local = lg.shape[-1]
+    rank = dist.get_rank(tape.tp_group) if tape.tp_world > 1 else 0
+    m = lg.amax(-1)
+    if tape.tp_world > 1:
+        dist.all_reduce(m, op=dist.ReduceOp.MAX, group=tape.tp_group)
+    se = torch.exp(lg - m[:, None]).sum(-1)
+    loc = tg - rank * v_local
+    ok = (loc >= 0) & (loc < v_local)
+    picked = torch.where(ok, lg.gather(-1, loc.clamp(0, v_local - 1)[:, None]).squeeze(-1), torch.zeros_like(m))
+    if tape.tp_world > 1:
+        dist.all_reduce(se, group=tape.tp_group)
+        dist.all_reduce(picked, group=tape.tp_group)
+    lse = m + torch.log(se)
+    lp = (picked - lse).view(logits.shape[:-1])
+    wts = lp_weights_fn(lp).reshape(-1).float().to(lg.device)
+    loss = -(wts * lp.reshape(-1)).sum()
+    grad = torch.exp(lg - lse[:, None])
+    rows = torch.nonzero(ok).squeeze(-1)
+    grad[rows, loc[rows]] -= 1.0
+    grad = (grad * wts[:, None]).view_as(logits)
+    tape.record("cross_entropy_tp", (logits,), (loss,), lambda g: (grad * g,))
+    return loss, lp
+
+
+@_nograd
 def linear_cross_entropy(tape: Tape, h: torch.Tensor, w: torch.Tensor, targets: torch.Tensor, weights_fn: Callable,
                          *, frozen: bool = True, chunk: int = 1024):
     """lm_head + weighted cross-entropy without ever holding ``[T, V]``: the head GEMM runs in
