@@ -148,6 +148,27 @@ def test_zero3_world1_matches_adamw():
     assert _close(_snapshot(model), _single_step(1))
 
 
+def test_zero3_low_precision_working_copy_keeps_every_leaf_watched():
+    """With a bf16 working copy the vector parameters (norms, GDN vectors) change dtype when they
+    are dropped and re-gathered; every one of them must still be trained: no unit may reach the
+    optimizer step with leaves that never received a gradient, and a norm weight must move."""
+    from tilerl_b200 import rl
+    from tilerl_b200.parallel.zero3 import Zero3
+    cfg, model = _model()
+    ids = _data(cfg, 1)
+    z = Zero3(model, None, lr=1e-2, max_norm=0.0, work_dtype=torch.bfloat16)
+    z.gather_all()
+    before = {k: v.float().clone() for k, v in z.params.items() if k.endswith("norm1") or k.endswith("a_log")}
+    assert before
+    for _ in range(2):
+        rl.train_step(model, ids, z, max_norm=0.0, checkpoint_layers=True, on_grad=z.on_grad, hook=z)
+    assert z.stats.get("flushed", 0) == 0
+    assert z.stats["reduce_scatters"] == 2 * sum(1 for u in z.units if u.names)
+    z.gather_all()
+    for k, v in before.items():
+        assert not torch.equal(z.params[k].float(), v), k
+
+
 def _resync_rank(rank, world):
     """ZeRO-3 over `world` ranks trains; the same ranks serve a TP=`world` NVFP4 model.  After a
     step + resync, every rank's shard must equal what quantising the updated full master and

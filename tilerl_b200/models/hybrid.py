@@ -261,8 +261,10 @@ class HybridModel:
                 continue  # served copy; its master (if kept) is the trainable one
             if k.startswith("master."):
                 out[k] = v
-            elif isinstance(v, torch.Tensor) and v.dtype == torch.float32 and ".lora_" not in k \
+            elif isinstance(v, torch.Tensor) and v.is_floating_point() and ".lora_" not in k \
                     and k not in ("embed", "lm_head"):
+                # by kind, not by dtype: a sharded trainer swaps these tensors' storage for
+                # working-precision views between steps and they must stay in the set
                 out[k] = v
         return out
 

@@ -233,8 +233,11 @@ class Zero3:
 
     def flush(self) -> None:
         """Reduce units whose leaves did not all receive a gradient (unused tensors)."""
-        for u in self.units:
+        staged = getattr(self.comm, "is_staged", lambda t: False)
+        # the unit that borrowed the comm's staging area goes first: the others pass through it
+        for u in sorted(self.units, key=lambda u: not (u.grad is not None and staged(u.grad))):
             if u.grad is not None:
+                self.stats["flushed"] = self.stats.get("flushed", 0) + 1
                 self._reduce(u)
 
     # ---- optimizer --------------------------------------------------------------------------------
@@ -378,6 +381,9 @@ class P2PComm:
         buf = self.stage_grad[:nb].view(dtype)
         buf.zero_()
         return buf
+
+    def is_staged(self, t: torch.Tensor) -> bool:
+        return t.data_ptr() == self.stage_grad.data_ptr()
 
     def all_gather(self, shard: torch.Tensor, full: torch.Tensor, stream=None) -> None:
         nb = shard.numel() * full.element_size()
