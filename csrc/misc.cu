@@ -255,6 +255,7 @@ sample_softmax_kernel(const float* __restrict__ logits, int ld, const int* __res
   __shared__ float s_bcast[2];
   __shared__ int s_pick;
   const int b = blockIdx.x, tid = threadIdx.x;
+  pdl_wait();
   const float* lg = logits + (size_t)rows[b] * ld;
   const float it = inv_temp[b];
   const int C = (V + 1023) / 1024;
@@ -319,6 +320,222 @@ sample_softmax_kernel(const float* __restrict__ logits, int ld, const int* __res
   }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Top-k / top-p (nucleus) sampling on the device, one CTA per row, no sort.
+//
+// Every logit is keyed by its distance below the row maximum in units of 2^-19 nat
+// (q = (max - s) * 2^19, clamped to 24 bits: anything more than 32 nats down has probability
+// < 2e-14 and is never drawn) and weighted by an integer mass m = exp(-(max - s)) * 2^40, so all
+// sums are exact integers and the result does not depend on the order of the atomics.
+//   top-k : the k-th smallest key by a 3-digit radix select over counts; keys equal to it are kept.
+//   top-p : the smallest key whose cumulative mass (in descending probability) reaches top_p * Z,
+//           by the same radix select over masses; the token that crosses the bound is kept.
+//   draw  : inverse CDF at u = hash(seed) over the kept masses in (thread, stride) order.
+// The order of the inverse CDF does not change the distribution, only which token a given u maps to.
+__device__ __forceinline__ unsigned nuc_key(float d) {
+  const float q = d * 524288.f;
+  return (q >= 16777215.f || !(q == q)) ? 0xFFFFFFu : (unsigned)q;
+}
+__device__ __forceinline__ unsigned long long nuc_mass(float d, unsigned q) {
+  return q == 0xFFFFFFu ? 0ull : (unsigned long long)(__expf(-d) * 1099511627776.f);
+}
+
+struct NucShared {
+  unsigned long long hist[256];
+  unsigned long long part[1024];
+  float red[32];
+  float mx;
+  unsigned sel;
+  unsigned long long need;
+  unsigned long long total;
+  int pick;
+};
+
+// Sum of one value per thread over the CTA (all threads get the result).
+__device__ __forceinline__ unsigned long long nuc_block_sum(NucShared& sh, unsigned long long v, int tid) {
+  __syncthreads();
+  sh.part[tid] = v;
+  __syncthreads();
+  if (tid < 32) {
+    unsigned long long a = 0;
+    for (int j = 0; j < 32; ++j) a += sh.part[tid * 32 + j];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+    if (tid == 0) sh.total = a;
+  }
+  __syncthreads();
+  return sh.total;
+}
+
+// Smallest 24-bit key t such that the weight (count or mass) of {q <= t, q <= qcap} reaches `need`
+// (0xFFFFFF when the whole row does not reach it).
+__device__ unsigned nuc_select(NucShared& sh, const float* __restrict__ lg, float it, float mx, int V, bool by_mass,
+                               unsigned long long need, unsigned qcap, int tid) {
+  unsigned prefix = 0;
+  for (int pass = 0; pass < 3; ++pass) {
+    const int shift = 16 - 8 * pass;
+    __syncthreads();
+    if (tid < 256) sh.hist[tid] = 0ull;
+    __syncthreads();
+    for (int i = tid; i < V; i += 1024) {
+      const float d = mx - lg[i] * it;
+      const unsigned q = nuc_key(d);
+      if (q > qcap) continue;
+      if (pass > 0 && (q >> (shift + 8)) != prefix) continue;
+      const unsigned long long w = by_mass ? nuc_mass(d, q) : 1ull;
+      if (w) atomicAdd(&sh.hist[(q >> shift) & 255u], w);
+    }
+    __syncthreads();
+    if (tid < 32) {
+      unsigned long long loc[8], run = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        loc[j] = sh.hist[tid * 8 + j];
+        run += loc[j];
+      }
+      unsigned long long incl = run;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long n = __shfl_up_sync(0xffffffffu, incl, o);
+        if (tid >= o) incl += n;
+      }
+      const unsigned long long excl = incl - run;
+      const bool has = excl < need && incl >= need;
+      const unsigned ball = __ballot_sync(0xffffffffu, has);
+      if (ball == 0u) {
+        if (tid == 0) {
+          sh.sel = (prefix << 8) | 255u;
+          sh.need = need;
+        }
+      } else if (has) {
+        unsigned long long cum = excl;
+        int b = 7;
+        bool found = false;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (!found) {
+            if (j == 7 || cum + loc[j] >= need) b = j, found = true;
+            else cum += loc[j];
+          }
+        }
+        sh.sel = (prefix << 8) | (unsigned)(tid * 8 + b);
+        sh.need = need - cum;
+      }
+    }
+    __syncthreads();
+    prefix = sh.sel;
+    need = sh.need;
+  }
+  return prefix;
+}
+
+__global__ void __launch_bounds__(1024)
+sample_nucleus_kernel(const float* __restrict__ logits, int ld, const int* __restrict__ rows,
+                      const long long* __restrict__ seeds, const float* __restrict__ inv_temp,
+                      const int* __restrict__ top_k, const float* __restrict__ top_p, int* __restrict__ out_tok,
+                      float* __restrict__ out_lp, int V) {
+  __shared__ NucShared sh;
+  const int b = blockIdx.x, tid = threadIdx.x;
+  pdl_wait();
+  const float* lg = logits + (size_t)rows[b] * ld;
+  const float it = inv_temp[b];
+  float mx = -INFINITY;
+  for (int i = tid; i < V; i += 1024) mx = fmaxf(mx, lg[i] * it);
+  mx = warp_max(mx);
+  if ((tid & 31) == 0) sh.red[tid >> 5] = mx;
+  __syncthreads();
+  if (tid < 32) {
+    const float v = warp_max(sh.red[tid]);
+    if (tid == 0) sh.mx = v;
+  }
+  __syncthreads();
+  mx = sh.mx;
+  if (!(mx > -INFINITY)) {   // nothing to draw from (all masked): token 0, logprob 0
+    if (tid == 0) out_tok[b] = 0, out_lp[b] = 0.f;
+    return;
+  }
+  const int k = top_k[b];
+  const float p = top_p[b];
+  unsigned qcut = 0xFFFFFFu;
+  if (k > 0 && k < V) qcut = nuc_select(sh, lg, it, mx, V, false, (unsigned long long)k, 0xFFFFFFu, tid);
+  if (p < 1.f) {
+    unsigned long long z = 0;
+    for (int i = tid; i < V; i += 1024) {
+      const float d = mx - lg[i] * it;
+      const unsigned q = nuc_key(d);
+      if (q <= qcut) z += nuc_mass(d, q);
+    }
+    z = nuc_block_sum(sh, z, tid);
+    unsigned long long want = (unsigned long long)((double)fmaxf(p, 0.f) * (double)z);
+    if (want < 1ull) want = 1ull;
+    const unsigned qp = nuc_select(sh, lg, it, mx, V, true, want, qcut, tid);
+    qcut = min(qcut, qp);
+  }
+  // kept mass per thread over its strided elements, exclusive prefix over threads
+  unsigned long long mine = 0;
+  for (int i = tid; i < V; i += 1024) {
+    const float d = mx - lg[i] * it;
+    const unsigned q = nuc_key(d);
+    if (q <= qcut) mine += nuc_mass(d, q);
+  }
+  __syncthreads();
+  sh.part[tid] = mine;
+  if (tid == 0) sh.pick = -1;
+  __syncthreads();
+  if (tid < 32) {
+    unsigned long long run = 0;
+    for (int j = 0; j < 32; ++j) run += sh.part[tid * 32 + j];
+    unsigned long long incl = run;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned long long n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (tid >= o) incl += n;
+    }
+    unsigned long long acc = incl - run;
+    for (int j = 0; j < 32; ++j) {
+      const unsigned long long v = sh.part[tid * 32 + j];
+      sh.part[tid * 32 + j] = acc;
+      acc += v;
+    }
+    if (tid == 31) sh.total = acc;
+  }
+  __syncthreads();
+  const unsigned long long total = sh.total;
+  if (total == 0ull) {   // cannot happen (the maximum has mass 2^40); keep the output defined
+    if (tid == 0) out_tok[b] = 0, out_lp[b] = 0.f;
+    return;
+  }
+  unsigned long long target = (unsigned long long)((double)sample_u01((unsigned long long)seeds[b]) * (double)total);
+  if (target >= total) target = total - 1ull;
+  const unsigned long long begin = sh.part[tid];
+  if (mine > 0ull && target >= begin && target < begin + mine) sh.pick = tid;   // exactly one thread
+  __syncthreads();
+  if (tid == sh.pick) {
+    unsigned long long acc = begin, m_tok = 0ull;
+    int tok = -1;
+    for (int i0 = tid; i0 < V && tok < 0; i0 += 8 * 1024) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int i = i0 + j * 1024;
+        v[j] = i < V ? lg[i] * it : -INFINITY;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float d = mx - v[j];
+        const unsigned q = nuc_key(d);
+        const unsigned long long m = q <= qcut ? nuc_mass(d, q) : 0ull;
+        if (tok < 0 && m > 0ull) {
+          if (target < acc + m) tok = i0 + j * 1024, m_tok = m;
+          acc += m;
+        }
+      }
+    }
+    out_tok[b] = max(tok, 0);
+    out_lp[b] = logf(fmaxf((float)m_tok, 1.f)) - logf((float)total);
+  }
+}
 
 // ---------------------------------------------------------------------------------------
 // LoRA delta of a served projection, two small kernels instead of a chain of library calls:
@@ -459,6 +676,17 @@ TRL_API int trl_sample_softmax(const void* logits, int ld, const void* rows, con
   if (B <= 0) return 0;
   return (int)trl_launch(sample_softmax_kernel, dim3(B), dim3(1024), 0, (cudaStream_t)stream, (const float*)logits,
                          ld, (const int*)rows, (const long long*)seeds, (const float*)inv_temp, (int*)out_tok,
+                         (float*)out_lp, V);
+}
+
+// As trl_sample_softmax, with a per-entry top_k (0 = off) and top_p (>= 1 = off) restriction.
+TRL_API int trl_sample_nucleus(const void* logits, int ld, const void* rows, const void* seeds,
+                               const void* inv_temp, const void* top_k, const void* top_p, void* out_tok,
+                               void* out_lp, int B, int V, void* stream) {
+  if (B <= 0) return 0;
+  return (int)trl_launch(sample_nucleus_kernel, dim3(B), dim3(1024), 0, (cudaStream_t)stream,
+                         (const float*)logits, ld, (const int*)rows, (const long long*)seeds,
+                         (const float*)inv_temp, (const int*)top_k, (const float*)top_p, (int*)out_tok,
                          (float*)out_lp, V);
 }
 

@@ -208,6 +208,53 @@ def test_sample_softmax_kernel_distribution_and_logprob():
     assert abs(-sum(lps) / n - ent) < 0.15
 
 
+@pytest.mark.parametrize("v,temp,top_k,top_p", [(5003, 0.8, 20, 0.95), (5003, 1.0, 0, 0.8), (248320, 1.0, 20, 0.95),
+                                                 (40000, 0.7, 0, 0.9), (3001, 1.3, 50, 1.0)])
+def test_sample_nucleus_kernel_matches_the_restricted_distribution(v, temp, top_k, top_p):
+    """Top-k / top-p sampler: every drawn token lies in the oracle's kept set, frequencies and
+    log-probabilities follow the renormalised restricted distribution, equal seeds repeat."""
+    from tilerl_b200.factory import make_ops
+    ops = make_ops("cuda")
+    g = torch.Generator().manual_seed(v + top_k)
+    logits = (torch.randn(2, v, generator=g) * 3.0).cuda()
+    n = 4096
+    rows, seeds = [1] * n, list(range(77, 77 + n))
+    toks, lps = ops.sample_rows(logits, rows, seeds, [temp] * n, [top_k] * n, [top_p] * n)
+    toks2, _ = ops.sample_rows(logits, rows, seeds, [temp] * n, [top_k] * n, [top_p] * n)
+    assert toks == toks2
+    lg = logits[1].double().cpu() / temp
+    if top_k:
+        kth = torch.topk(lg, top_k).values[-1]
+        lg = torch.where(lg < kth, torch.full_like(lg, float("-inf")), lg)
+    p = torch.softmax(lg, -1)
+    if top_p < 1.0:
+        sp, si = torch.sort(p, descending=True)
+        cut = (sp.cumsum(0) - sp) >= top_p
+        sp = torch.where(cut, torch.zeros_like(sp), sp)
+        p = torch.zeros_like(p).scatter_(0, si, sp)
+        p = p / p.sum()
+    t = torch.tensor(toks)
+    assert bool((p[t] > 0).all()), "a token outside the kept set was drawn"
+    assert float((torch.tensor(lps).double() - torch.log(p[t])).abs().max()) < 2e-3
+    for i in torch.topk(p, 5).indices.tolist():
+        freq = float((t == i).float().mean())
+        assert abs(freq - float(p[i])) < 4 * (float(p[i]) / n) ** 0.5 + 2e-3, (i, freq, float(p[i]))
+
+
+def test_sample_rows_mixed_restrictions_in_one_launch():
+    """Rows with and without restrictions share one launch; top_k = 1 is the argmax."""
+    from tilerl_b200.factory import make_ops
+    ops = make_ops("cuda")
+    g = torch.Generator().manual_seed(9)
+    logits = (torch.randn(4, 7001, generator=g) * 2.0).cuda()
+    toks, lps = ops.sample_rows(logits, [0, 1, 2, 3], [5, 6, 7, 8], [1.0, 0.5, 1.0, 2.0], [1, 0, 0, 3], [1.0, 1.0, 1e-6, 1.0])
+    am = logits.argmax(-1).tolist()
+    assert toks[0] == am[0] and abs(lps[0]) < 1e-5
+    assert toks[2] == am[2] and abs(lps[2]) < 1e-5      # a vanishing nucleus keeps the top token only
+    assert toks[3] in torch.topk(logits[3], 3).indices.tolist()
+    assert 0 <= toks[1] < 7001 and lps[1] < 0
+
+
 @pytest.mark.parametrize("norm", [False, True])
 def test_lora_add_kernel(norm):
     from tilerl_b200.factory import make_ops

@@ -491,19 +491,19 @@ class Engine:
             and p.max_think_tokens is None
 
     def _presample(self, plan, logits, verify: bool) -> Dict[int, Tuple[int, float]]:
-        """Rows that only need seeded temperature sampling (no top-k / top-p / allowed list) are
-        drawn on the device in one kernel when the backend offers it; everything else goes
-        through the per-row host sampler."""
+        """Rows that need seeded temperature sampling, with or without a top-k / top-p restriction,
+        are drawn on the device in one kernel when the backend offers it; rows with an allowed-id
+        list go through the per-row host sampler."""
         if not hasattr(self.ops, "sample_rows"):
             return {}
-        rows, seeds, temps = [], [], []
+        rows, seeds, temps, ks, ps = [], [], [], [], []
         tok_off = 0
         for i, (r, toks, start) in enumerate(plan):
             n = len(toks)
             p = r.params
             base = tok_off if verify else i
             tok_off += n
-            if p.temperature <= 0.0 or p.top_p < 1.0 or p.top_k or p.allowed_ids is not None:
+            if p.temperature <= 0.0 or p.allowed_ids is not None:
                 continue
             if r.state == PREFILL:
                 if start + n != len(r.prompt):
@@ -515,9 +515,11 @@ class Engine:
                 rows.append(row)
                 seeds.append(ref.sample_seed(p.seed, len(r.out) + k))
                 temps.append(p.temperature)
+                ks.append(int(p.top_k or 0))
+                ps.append(float(p.top_p))
         if not rows:
             return {}
-        toks_, lps = self.ops.sample_rows(logits, rows, seeds, temps)
+        toks_, lps = self.ops.sample_rows(logits, rows, seeds, temps, ks, ps)
         self.io_d2h += 8 * len(rows)
         return {row: (int(t), float(lp)) for row, t, lp in zip(rows, toks_, lps)}
 

@@ -322,21 +322,31 @@ class CudaOps:
         N.count(2)
         return out
 
-    def sample_rows(self, logits: torch.Tensor, rows, seeds, temps):
-        """Seeded temperature sampling of the listed logits rows on the device (one kernel, one
-        device-to-host copy).  Returns ``(tokens, logprobs)`` as Python lists."""
+    def sample_rows(self, logits: torch.Tensor, rows, seeds, temps, top_ks=None, top_ps=None):
+        """Seeded sampling of the listed logits rows on the device (one kernel, one device-to-host
+        copy): plain temperature sampling, or with per-row ``top_ks`` (0 = off) / ``top_ps`` (>= 1 =
+        off) the top-k / nucleus sampler.  Returns ``(tokens, logprobs)`` as Python lists."""
         n = len(rows)
-        meta = torch.tensor([list(rows), [s & 0x7FFFFFFFFFFFFFFF for s in seeds]], dtype=torch.int64)
-        it = torch.tensor([1.0 / t for t in temps], dtype=torch.float32)
+        nucleus = top_ks is not None and any(k or p < 1.0 for k, p in zip(top_ks, top_ps))
+        meta = torch.tensor([list(rows), [s & 0x7FFFFFFFFFFFFFFF for s in seeds],
+                             list(top_ks) if nucleus else [0] * n], dtype=torch.int64)
+        it = torch.tensor([[1.0 / t for t in temps], list(top_ps) if nucleus else [1.0] * n], dtype=torch.float32)
         rows_d = meta[0].to(torch.int32).to(self.device, non_blocking=True)
         seeds_d = meta[1].to(self.device, non_blocking=True)
         it_d = it.to(self.device, non_blocking=True)
         out = torch.empty(2, n, dtype=torch.float32, device=self.device)
         tok = out[0].view(torch.int32)
         lg = logits if logits.dtype == torch.float32 else logits.float()
-        N.check(self.lib.trl_sample_softmax(lg.data_ptr(), lg.stride(0), rows_d.data_ptr(), seeds_d.data_ptr(),
-                                            it_d.data_ptr(), tok.data_ptr(), out[1].data_ptr(), n, lg.shape[1],
-                                            N.stream()), "sample_softmax")
+        if nucleus:
+            k_d = meta[2].to(torch.int32).to(self.device, non_blocking=True)
+            N.check(self.lib.trl_sample_nucleus(lg.data_ptr(), lg.stride(0), rows_d.data_ptr(), seeds_d.data_ptr(),
+                                                it_d[0].data_ptr(), k_d.data_ptr(), it_d[1].data_ptr(),
+                                                tok.data_ptr(), out[1].data_ptr(), n, lg.shape[1], N.stream()),
+                    "sample_nucleus")
+        else:
+            N.check(self.lib.trl_sample_softmax(lg.data_ptr(), lg.stride(0), rows_d.data_ptr(), seeds_d.data_ptr(),
+                                                it_d[0].data_ptr(), tok.data_ptr(), out[1].data_ptr(), n,
+                                                lg.shape[1], N.stream()), "sample_softmax")
         N.count()
         host = out.cpu()
         return host[0].view(torch.int32).tolist(), host[1].tolist()
