@@ -365,3 +365,78 @@ def test_tiled_prefill_attention_matches_split_kernel_and_oracle(lens, hist):
         err = float((outs[mode] - ref_o).abs().max())
         assert err < 0.03 * float(ref_o.abs().max()) + 0.02, (mode, err)
     assert float((outs["tiled"] - outs["split"]).abs().max()) < 0.03
+
+
+@pytest.mark.parametrize("lens,hist", [((5, 1, 33), (0, 40, 7)), ((1, 1), (200, 17))])
+def test_fp8_kv_attention_matches_the_fp8_oracle(lens, hist):
+    """e4m3 KV pool on the device: the quantising prep kernel writes the bytes and scales the
+    oracle writes (up to a rounding flip of the pre-quantisation value), and attention over the
+    fp8 pool matches the oracle over its dequantised pool; both stay close to the bf16 pool."""
+    from tilerl_b200.batch import Batch
+    from tilerl_b200.config import small_gpu
+    from tilerl_b200.factory import make_ops
+    from tilerl_b200.kv import PagedKvPool
+    from tilerl_b200.ops.backend import RefOps
+    cfg = small_gpu()
+    ops = make_ops("cuda")
+    n_q, n_kv, d = cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim
+    rows = n_q * 2 * d + 2 * n_kv * d
+    g = torch.Generator().manual_seed(3)
+    lp = {"q_norm": (1.0 + 0.1 * torch.randn(d, generator=g)).cuda(), "k_norm": (1.0 + 0.1 * torch.randn(d, generator=g)).cuda()}
+    outs, pools = {}, {}
+    for mode in ("cuda_fp8", "ref_fp8", "cuda_bf16"):
+        fp8 = mode != "cuda_bf16"
+        pool = PagedKvPool(cfg, 64, "cuda", dtype=torch.float32 if mode == "ref_fp8" else torch.bfloat16, fp8=fp8)
+        o = RefOps() if mode == "ref_fp8" else ops
+        blk = 1
+        seqs_hist, seqs_now = [], []
+        for i, (n, h) in enumerate(zip(lens, hist)):
+            nb = (n + h + 15) // 16
+            blocks = list(range(blk, blk + nb))
+            blk += nb
+            if h:
+                seqs_hist.append(dict(tokens=[0] * h, start=0, blocks=blocks, slot=i + 1))
+            seqs_now.append(dict(tokens=[0] * n, start=h, blocks=blocks, slot=i + 1))
+        gg = torch.Generator().manual_seed(11)
+        for seqs in ([seqs_hist] if seqs_hist else []) + [seqs_now]:
+            batch = Batch.build(seqs, "cuda")
+            t = sum(len(s_["tokens"]) for s_ in seqs)
+            qkv = (torch.randn(t, rows, generator=gg) * 0.5).cuda().to(torch.bfloat16)
+            res = o.attention(qkv, lp, batch, pool, 0, cfg, n_q, n_kv)
+        outs[mode] = res.float().clone()
+        pools[mode] = pool
+    a, b = pools["cuda_fp8"], pools["ref_fp8"]
+    used = slice(1, blk)
+    for name in ("k", "v"):
+        sa, sb = getattr(a, name + "_scale")[0, used], getattr(b, name + "_scale")[0, used]
+        assert float(((sa - sb).abs() / sb.abs().clamp_min(1e-20)).max()) < 2e-2, name
+        da = getattr(a, name)[0, used].float() * sa.unsqueeze(-1)
+        db = getattr(b, name)[0, used].float() * sb.unsqueeze(-1)
+        assert float((da - db).abs().max()) < 0.08 * float(db.abs().max()), name   # one e4m3 step at most
+        assert float((da - db).abs().mean()) < 0.01 * float(db.abs().max()), name
+    ref_o = outs["ref_fp8"]
+    assert float((outs["cuda_fp8"] - ref_o).abs().max()) < 0.03 * float(ref_o.abs().max()) + 0.02
+    assert float((outs["cuda_fp8"] - outs["cuda_bf16"]).abs().max()) < 0.08 * float(ref_o.abs().max()) + 0.03
+    assert a.k.element_size() == 1
+
+
+def test_fp8_kv_engine_greedy_tokens_close_to_bf16_pool():
+    """The engine serves from an fp8 KV pool on the device: same first greedy tokens as the bf16
+    pool on the small model, with the graph decode path on."""
+    from tilerl_b200.config import small_gpu
+    from tilerl_b200.engine import SamplingParams
+    from tilerl_b200.factory import build_engine, build_model, make_ops
+    cfg = small_gpu()
+    ops = make_ops("cuda")
+    model = build_model(cfg, "cuda", seed=1, ops=ops)
+    prompt = list(range(5, 45))
+    outs = []
+    for fp8 in (False, True):
+        eng = build_engine(model, ops, device="cuda", slots=2, max_ctx=256, prefix=False, graph=True, kv_fp8=fp8)
+        outs.append(eng.generate([prompt], SamplingParams(max_tokens=12, temperature=0.0))[0].tokens)
+    same = 0
+    for x, y in zip(outs[0], outs[1]):
+        if x != y:
+            break
+        same += 1
+    assert same >= 4, (outs, same)

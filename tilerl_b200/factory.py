@@ -111,7 +111,7 @@ def build_model(model: str | ModelConfig, device="cpu", *, seed: int = 0, checkp
 
 
 def fit_blocks(cfg: ModelConfig, free_bytes: int, slots: int, *, planes: int = 1, tp: int = 1,
-               pool_fraction: float = 2.0 / 3.0, max_blocks: int = 1 << 20) -> int:
+               pool_fraction: float = 2.0 / 3.0, max_blocks: int = 1 << 20, kv_fp8: bool = False) -> int:
     """KV pages that fit in ``pool_fraction`` of what is left after the GDN state slots."""
     from .parallel.mesh import tp_dims
     d = tp_dims(cfg, tp)
@@ -119,6 +119,8 @@ def fit_blocks(cfg: ModelConfig, free_bytes: int, slots: int, *, planes: int = 1
     slot_bytes = cfg.n_gdn_layers * (planes * d.gdn_nv * gd * gd * 4 + 16 * d.gdn_conv_dim * 2)
     left = free_bytes - slots * slot_bytes
     per_block = max(1, cfg.n_attn_layers) * d.n_kv * KV_BLOCK * cfg.head_dim * 2 * 2
+    if kv_fp8:   # one byte per value plus one fp32 scale per (token, head), K and V
+        per_block = max(1, cfg.n_attn_layers) * d.n_kv * KV_BLOCK * (cfg.head_dim + 4) * 2
     return int(max(2, min(max_blocks, left * pool_fraction // per_block)))
 
 
@@ -132,7 +134,8 @@ def make_ops(device, tp_comm=None):
 
 def build_engine(model: HybridModel, ops=None, *, device=None, blocks: Optional[int] = None, slots: int = 8,
                  max_ctx: int = 4096, prefix: bool = True, graph: bool = True, spec_width: int = 0,
-                 drafter=None, limits: Optional[StepLimits] = None, sparse=None, **engine_kw) -> Engine:
+                 drafter=None, limits: Optional[StepLimits] = None, sparse=None, kv_fp8: bool = False,
+                 **engine_kw) -> Engine:
     cfg = model.cfg
     if device is None:
         e = model.params["embed"]
@@ -146,12 +149,13 @@ def build_engine(model: HybridModel, ops=None, *, device=None, blocks: Optional[
     if blocks is None:
         if device.type == "cuda":
             free, _ = torch.cuda.mem_get_info(device)
-            blocks = fit_blocks(cfg, free, slots, planes=planes, tp=model.tp,
+            blocks = fit_blocks(cfg, free, slots, planes=planes, tp=model.tp, kv_fp8=kv_fp8,
                                 max_blocks=slots * ((max_ctx + KV_BLOCK - 1) // KV_BLOCK) + 2)
         else:
             blocks = slots * ((max_ctx + KV_BLOCK - 1) // KV_BLOCK) + 2
     on_gpu = device.type == "cuda"
-    kv = PagedKvPool(cfg, blocks, device, dtype=torch.bfloat16 if on_gpu else torch.float32, n_kv_heads=d.n_kv)
+    kv = PagedKvPool(cfg, blocks, device, dtype=torch.bfloat16 if on_gpu else torch.float32, n_kv_heads=d.n_kv,
+                     fp8=kv_fp8)
     st = GdnStatePool(cfg, slots + 1, device, planes=planes,
                       ring_dtype=torch.bfloat16 if on_gpu else torch.float32,
                       n_v_heads=d.gdn_nv or None, n_k_heads=d.gdn_nk or None)

@@ -208,15 +208,14 @@ class CudaOps:
         return residual
 
     def attention(self, qkv, lp, batch, pool, attn_idx, cfg, n_q, n_kv):
-        if getattr(pool, "fp8", False):
-            raise NotImplementedError("the CUDA attention kernels read a bf16 KV pool; fp8 KV is served by the "
-                                      "reference backend only")
         t = qkv.shape[0]
         d = cfg.head_dim
         q = self.ws.get("q", (t, n_q, d), torch.bfloat16)
         out = self.ws.get("act", (t, n_q * d), torch.bfloat16)
         kc, vc = pool.layer(attn_idx)
         st = N.stream()
+        if getattr(pool, "fp8", False):
+            return self._attention_fp8(qkv, lp, batch, pool, attn_idx, cfg, n_q, n_kv, q, out, kc, vc, st)
         N.check(self.lib.trl_attn_prep(
             qkv.data_ptr(), qkv.stride(0), self._f32(lp["q_norm"]).data_ptr(),
             self._f32(lp["k_norm"]).data_ptr(), batch.positions.data_ptr(),
@@ -247,6 +246,34 @@ class CudaOps:
             table.data_ptr(), table.stride(0), batch.seq_ids.data_ptr(),
             pos.data_ptr(), po.data_ptr(), pm.data_ptr(), pl.data_ptr(), out.data_ptr(),
             t, n_q, n_kv, d, splits, 1.0 / math.sqrt(d), int(cfg.attn_gated), st), "attn_paged")
+        N.count(2 + (1 if splits > 1 else 0))
+        return out
+
+    def _attention_fp8(self, qkv, lp, batch, pool, attn_idx, cfg, n_q, n_kv, q, out, kc, vc, st):
+        """e4m3 KV pool with per-(token, head) scales: quantising prep kernel, then the split-KV
+        kernel reading fp8 rows (decode, verify and prefill chunks alike)."""
+        sp = batch.sparse
+        if sp is not None and sp.active(attn_idx):
+            raise NotImplementedError("sparse page selection reads a bf16 KV pool")
+        t = qkv.shape[0]
+        d = cfg.head_dim
+        ks, vs = pool.k_scale[attn_idx], pool.v_scale[attn_idx]
+        N.check(self.lib.trl_attn_prep_fp8(
+            qkv.data_ptr(), qkv.stride(0), self._f32(lp["q_norm"]).data_ptr(),
+            self._f32(lp["k_norm"]).data_ptr(), batch.positions.data_ptr(),
+            batch.slot_mapping.data_ptr(), q.data_ptr(), kc.data_ptr(), vc.data_ptr(), ks.data_ptr(),
+            vs.data_ptr(), t, n_q, n_kv, d, cfg.rotary_dim, float(cfg.rope_theta), cfg.rms_eps,
+            int(cfg.attn_gated), st), "attn_prep_fp8")
+        splits = self.attn_splits or self._pick_splits(batch, t, n_kv)
+        po = self.ws.get("attn_po", (t * n_q * splits * d,), torch.float32)
+        pm = self.ws.get("attn_pm", (t * n_q * splits,), torch.float32)
+        pl = self.ws.get("attn_pl", (t * n_q * splits,), torch.float32)
+        N.check(self.lib.trl_attn_paged_fp8(
+            q.data_ptr(), qkv.data_ptr(), qkv.stride(0), kc.data_ptr(), vc.data_ptr(), ks.data_ptr(),
+            vs.data_ptr(), batch.block_table.data_ptr(), batch.block_table.stride(0),
+            batch.seq_ids.data_ptr(), batch.positions.data_ptr(), po.data_ptr(), pm.data_ptr(),
+            pl.data_ptr(), out.data_ptr(), t, n_q, n_kv, d, splits, 1.0 / math.sqrt(d),
+            int(cfg.attn_gated), st), "attn_paged_fp8")
         N.count(2 + (1 if splits > 1 else 0))
         return out
 

@@ -37,6 +37,8 @@ _SIGS = {
     "trl_argmax_stage1": [P, I, I, I, P, P, P],
     "trl_sample_softmax": [P, I, P, P, P, P, P, I, I, P],
     "trl_sample_nucleus": [P, I, P, P, P, P, P, P, P, I, I, P],
+    "trl_attn_prep_fp8": [P, I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P],
+    "trl_attn_paged_fp8": [P, P, I, P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, F, I, P],
     "trl_attn_prefill": [P, P, I, P, P, P, I, P, P, P, P, I, I, I, I, I, F, I, P],
     "trl_lora_add": [P, I, P, F, P, P, P, P, I, I, I, I, I, F, P],
     "trl_adamw": [P, P, P, P, P, L, F, F, F, F, F, I, F, P],
