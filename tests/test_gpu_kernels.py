@@ -440,3 +440,16 @@ def test_fp8_kv_engine_greedy_tokens_close_to_bf16_pool():
             break
         same += 1
     assert same >= 4, (outs, same)
+
+
+def test_standalone_narrow_decode_binary():
+    """csrc/tests/narrow_decode.cu: every e2m1 byte and every e4m3 byte decodes to the value the
+    format defines (the binary is built by ``python -m tilerl_b200.build --tests``)."""
+    import os
+    import subprocess
+    from tilerl_b200 import build as b
+    exe = os.path.join(b.ROOT, "build", "bin", "narrow_decode")
+    if not os.path.exists(exe):
+        b.build_tests()
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "ok" in r.stdout, (r.returncode, r.stdout, r.stderr)

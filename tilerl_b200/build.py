@@ -88,5 +88,26 @@ def build(force: bool = False, verbose: bool = False, extra_flags=()) -> str:
     return OUT
 
 
+def build_tests(force: bool = False) -> list:
+    """Standalone device checks under ``csrc/tests`` -> ``build/bin/<name>`` (run them on a GPU)."""
+    tdir = os.path.join(CSRC, "tests")
+    bdir = os.path.join(ROOT, "build", "bin")
+    os.makedirs(bdir, exist_ok=True)
+    outs = []
+    for src in sorted(f for f in os.listdir(tdir) if f.endswith(".cu")):
+        out = os.path.join(bdir, src[:-3])
+        sp = os.path.join(tdir, src)
+        if force or not os.path.exists(out) or os.path.getmtime(out) < os.path.getmtime(sp):
+            cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O2", "-std=c++17",
+                   "-o", out, sp]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                raise RuntimeError(f"nvcc failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+        outs.append(out)
+    return outs
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose=True))
+    if "--tests" in sys.argv:
+        print("\n".join(build_tests(force="--force" in sys.argv)))

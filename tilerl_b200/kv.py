@@ -19,6 +19,8 @@ Parity: reference ``src/tilerl/kv_cache.py`` -- ``PagedKvPool:53``,
 """
 from __future__ import annotations
 
+import ctypes
+import os
 from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
@@ -35,6 +37,24 @@ class PoolExhausted(RuntimeError):
     pass
 
 
+def _native_pager(num_blocks: int):
+    """``(lib, handle)`` of a C++ block allocator (``csrc/runtime.cpp``), or None when the library
+    is not built or ``TRL_NATIVE_PAGER=0``."""
+    if os.environ.get("TRL_NATIVE_PAGER", "1") == "0":
+        return None
+    try:
+        from .ops import native
+        if not native.loadable():
+            return None
+        lib = native.lib()
+        if not hasattr(lib, "trl_pager_create"):
+            return None
+        h = lib.trl_pager_create(int(num_blocks))
+        return (lib, ctypes.c_void_p(h)) if h else None
+    except OSError:
+        return None
+
+
 class PagedKvPool:
     def __init__(self, cfg: ModelConfig, num_blocks: int, device="cpu",
                  dtype=torch.bfloat16, fp8: bool = False, n_kv_heads: Optional[int] = None):
@@ -49,34 +69,65 @@ class PagedKvPool:
         if fp8:
             self.k_scale = torch.ones(shape[:-1], dtype=torch.float32, device=device)
             self.v_scale = torch.ones(shape[:-1], dtype=torch.float32, device=device)
-        self.ref = [0] * self.num_blocks
-        self.ref[0] = 1  # pad page, never handed out
-        self._free = list(range(self.num_blocks - 1, 0, -1))
+        self._pager = _native_pager(self.num_blocks)     # C++ free list + refcounts when the library is built
+        if self._pager is None:
+            self._ref = [0] * self.num_blocks
+            self._ref[0] = 1  # pad page, never handed out
+            self._free = list(range(self.num_blocks - 1, 0, -1))
+
+    def __del__(self):
+        pg = getattr(self, "_pager", None)
+        if pg is not None:
+            pg[0].trl_pager_destroy(pg[1])
+            self._pager = None
 
     # ---- allocator -----------------------------------------------------------
     @property
+    def ref(self) -> List[int]:
+        """Reference count of every block (a copy when the native allocator holds them)."""
+        if self._pager is None:
+            return self._ref
+        lib, h = self._pager
+        buf = (ctypes.c_int32 * self.num_blocks)()
+        lib.trl_pager_refs(h, buf, self.num_blocks)
+        return list(buf)
+
+    @property
     def free_blocks(self) -> int:
+        if self._pager is not None:
+            return self._pager[0].trl_pager_free_count(self._pager[1])
         return len(self._free)
 
     @property
     def used_blocks(self) -> int:
-        return self.num_blocks - 1 - len(self._free)
+        return self.num_blocks - 1 - self.free_blocks
 
     def alloc_block(self) -> int:
+        if self._pager is not None:
+            b = self._pager[0].trl_pager_alloc(self._pager[1])
+            if b < 0:
+                raise PoolExhausted("KV pool has no free block")
+            return b
         if not self._free:
             raise PoolExhausted("KV pool has no free block")
         b = self._free.pop()
-        self.ref[b] = 1
+        self._ref[b] = 1
         return b
 
     def incref(self, b: int) -> None:
-        assert self.ref[b] > 0, f"incref of free block {b}"
-        self.ref[b] += 1
+        if self._pager is not None:
+            assert self._pager[0].trl_pager_incref(self._pager[1], int(b)) > 0, f"incref of free block {b}"
+            return
+        assert self._ref[b] > 0, f"incref of free block {b}"
+        self._ref[b] += 1
 
     def release(self, b: int) -> None:
-        assert b != 0 and self.ref[b] > 0, f"release of free block {b}"
-        self.ref[b] -= 1
-        if self.ref[b] == 0:
+        if self._pager is not None:
+            assert self._pager[0].trl_pager_release(self._pager[1], int(b)) >= 0, f"release of free block {b}"
+            return
+        assert b != 0 and self._ref[b] > 0, f"release of free block {b}"
+        self._ref[b] -= 1
+        if self._ref[b] == 0:
             self._free.append(b)
 
     def block_bytes(self) -> int:

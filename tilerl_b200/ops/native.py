@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_float, c_int, c_long, c_void_p
+from ctypes import c_float, c_int, c_long, c_longlong, c_void_p
 from typing import Optional
 
 import torch
@@ -36,6 +36,12 @@ _SIGS = {
     "trl_argmax": [P, I, I, I, P, P, P],
     "trl_argmax_stage1": [P, I, I, I, P, P, P],
     "trl_sample_softmax": [P, I, P, P, P, P, P, I, I, P],
+    # host runtime (csrc/runtime.cpp)
+    "trl_pager_create": [I], "trl_pager_destroy": [P], "trl_pager_alloc": [P], "trl_pager_alloc_many": [P, I, P],
+    "trl_pager_incref": [P, I], "trl_pager_release": [P, I], "trl_pager_free_count": [P],
+    "trl_pager_refcount": [P, I], "trl_pager_refs": [P, P, I],
+    "trl_batch_ints": [c_longlong, I, I],
+    "trl_batch_fill": [I, P, P, P, P, P, P, P, I, I, P, c_longlong],
     "trl_sample_nucleus": [P, I, P, P, P, P, P, P, P, I, I, P],
     "trl_attn_prep_fp8": [P, I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P],
     "trl_attn_paged_fp8": [P, P, I, P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, F, I, P],
@@ -47,6 +53,15 @@ _SIGS = {
     "trl_add": [P, P, P, L, P],
     "trl_decode_advance": [P, P, P, P, P, P, I, I, P, I, P, P],
 }
+
+
+_RESTYPE = {"trl_set_pdl": None, "trl_pager_create": c_void_p, "trl_pager_destroy": None,
+            "trl_batch_ints": c_longlong, "trl_batch_fill": c_longlong}
+
+
+def loadable() -> bool:
+    """The library file exists (the host runtime in it needs no GPU)."""
+    return os.path.exists(_PATH)
 
 
 def lib_path() -> str:
@@ -68,7 +83,7 @@ def lib() -> ctypes.CDLL:
             if fn is None:
                 continue
             fn.argtypes = sig
-            fn.restype = c_int if name != "trl_set_pdl" else None
+            fn.restype = _RESTYPE.get(name, c_int)
     return _LIB
 
 
