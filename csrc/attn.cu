@@ -265,9 +265,31 @@ constexpr int PF_D = 256, PF_TQ = 16, PF_BC = 32, PF_ROW = PF_D * 2 /*bytes*/, P
 // byte offset of 16-byte chunk `c` of row `r` in a swizzled [rows][512 B] tile
 __device__ __forceinline__ uint32_t pf_off(int r, int c) { return (uint32_t)(r * PF_ROW + ((c ^ (r & 7)) << 4)); }
 
+// FP8: the pool holds e4m3 rows with one fp32 scale per (token, kv head).  The raw bytes of the
+// next tile are staged with cp.async (double buffered) while this tile is computed; a conversion
+// pass then expands the staged tile into the (single) swizzled bf16 tile the mma path reads.
+__device__ __forceinline__ void cp4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void e4m3x16_to_bf16(const uint4& raw, float s, uint4& o0, uint4& o1) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  uint32_t r[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 a = h2_to_f2(cvt_e4m3x2_to_h2((uint16_t)(w[i] & 0xFFFFu)));
+    const float2 b = h2_to_f2(cvt_e4m3x2_to_h2((uint16_t)(w[i] >> 16)));
+    r[2 * i] = f2_to_bf162_bits(a.x * s, a.y * s);
+    r[2 * i + 1] = f2_to_bf162_bits(b.x * s, b.y * s);
+  }
+  o0 = make_uint4(r[0], r[1], r[2], r[3]);
+  o1 = make_uint4(r[4], r[5], r[6], r[7]);
+}
+
+template <bool FP8>
 __global__ void __launch_bounds__(256)
 attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ gate_src, int gate_ld,
                     const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                    const float* __restrict__ kscale, const float* __restrict__ vscale,
                     const int* __restrict__ block_table, int max_blocks, const int* __restrict__ q_start,
                     const int* __restrict__ q_len, const int* __restrict__ positions, bf16* __restrict__ out,
                     int n_q, int n_kv, float scale_log2e, int gated) {
@@ -283,8 +305,11 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ gate_sr
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int h = kvh * G + warp;
   unsigned char* qs = pf_smem + (size_t)warp * PF_TQ * PF_ROW;                 // [G][16][512 B]
-  unsigned char* ks = pf_smem + (size_t)G * PF_TQ * PF_ROW;                    // [2][32][512 B]
-  unsigned char* vs = ks + 2 * PF_BC * PF_ROW;                                 // [2][32][512 B]
+  unsigned char* ks = pf_smem + (size_t)G * PF_TQ * PF_ROW;                    // [2][32][512 B] ([1] when FP8)
+  unsigned char* vs = ks + (FP8 ? 1 : 2) * PF_BC * PF_ROW;                     // [2][32][512 B] ([1] when FP8)
+  unsigned char* raw_k = vs + PF_BC * PF_ROW;                                  // FP8: [2][32][256 B] staged e4m3 rows
+  unsigned char* raw_v = raw_k + 2 * PF_BC * PF_D;                             // FP8: [2][32][256 B]
+  float* s_sc = reinterpret_cast<float*>(raw_v + 2 * PF_BC * PF_D);            // FP8: [2][K, V][32] row scales
   const uint32_t qs_a = (uint32_t)__cvta_generic_to_shared(qs);
   const uint32_t ks_a = (uint32_t)__cvta_generic_to_shared(ks), vs_a = (uint32_t)__cvta_generic_to_shared(vs);
   const int* table = block_table + (size_t)seq * max_blocks;
@@ -317,6 +342,44 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ gate_sr
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
+  auto stage_fp8 = [&](int kt, int sb) {
+    const int j0 = kt * PF_BC;
+    const unsigned char* k8 = reinterpret_cast<const unsigned char*>(kcache);
+    const unsigned char* v8 = reinterpret_cast<const unsigned char*>(vcache);
+    const uint32_t rk_a = (uint32_t)__cvta_generic_to_shared(raw_k), rv_a = (uint32_t)__cvta_generic_to_shared(raw_v);
+    const uint32_t sc_a = (uint32_t)__cvta_generic_to_shared(s_sc);
+    for (int x = threadIdx.x; x < PF_BC * 16; x += blockDim.x) {
+      const int r = x >> 4, c = x & 15;
+      const int j = j0 + r;
+      if (j < n_keys) {
+        const size_t ridx = ((size_t)table[j / KVB] * n_kv + kvh) * KVB + (j % KVB);
+        cp16(rk_a + (sb * PF_BC + r) * PF_D + c * 16, k8 + ridx * PF_D + c * 16);
+        cp16(rv_a + (sb * PF_BC + r) * PF_D + c * 16, v8 + ridx * PF_D + c * 16);
+        if (c == 0) {
+          cp4(sc_a + ((sb * 2 + 0) * PF_BC + r) * 4, kscale + ridx);
+          cp4(sc_a + ((sb * 2 + 1) * PF_BC + r) * 4, vscale + ridx);
+        }
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  auto convert_fp8 = [&](int kt, int sb) {
+    const int j0 = kt * PF_BC;
+    for (int x = threadIdx.x; x < PF_BC * 16; x += blockDim.x) {
+      const int r = x >> 4, c = x & 15;
+      uint4 k0 = make_uint4(0u, 0u, 0u, 0u), k1 = k0, v0 = k0, v1 = k0;   // rows past the bound: zeros
+      if (j0 + r < n_keys) {
+        const uint4 rk = *reinterpret_cast<const uint4*>(raw_k + (sb * PF_BC + r) * PF_D + c * 16);
+        const uint4 rv = *reinterpret_cast<const uint4*>(raw_v + (sb * PF_BC + r) * PF_D + c * 16);
+        e4m3x16_to_bf16(rk, s_sc[(sb * 2 + 0) * PF_BC + r], k0, k1);
+        e4m3x16_to_bf16(rv, s_sc[(sb * 2 + 1) * PF_BC + r], v0, v1);
+      }
+      *reinterpret_cast<uint4*>(ks + pf_off(r, 2 * c)) = k0;
+      *reinterpret_cast<uint4*>(ks + pf_off(r, 2 * c + 1)) = k1;
+      *reinterpret_cast<uint4*>(vs + pf_off(r, 2 * c)) = v0;
+      *reinterpret_cast<uint4*>(vs + pf_off(r, 2 * c + 1)) = v1;
+    }
+  };
 
   const int r_lo = lane >> 2;                      // fragment rows r_lo and r_lo + 8
   const int pos_lo = r_lo < rows ? positions[t0 + r_lo] : -1;
@@ -326,16 +389,22 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ gate_sr
   for (int i = 0; i < PF_D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
 
-  load_kv(0, 0);
+  if constexpr (FP8) stage_fp8(0, 0);
+  else load_kv(0, 0);
   for (int kt = 0; kt < n_tiles; ++kt) {
-    const int buf = kt & 1;
+    const int buf = FP8 ? 0 : (kt & 1);
     if (kt + 1 < n_tiles) {
-      load_kv(kt + 1, buf ^ 1);
+      if constexpr (FP8) stage_fp8(kt + 1, (kt + 1) & 1);
+      else load_kv(kt + 1, buf ^ 1);
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
+    if constexpr (FP8) {
+      convert_fp8(kt, kt & 1);
+      __syncthreads();
+    }
     const uint32_t kb = ks_a + buf * PF_BC * PF_ROW, vb = vs_a + buf * PF_BC * PF_ROW;
     // ---- S = Q K^T for 32 keys: 4 n-tiles of 8 keys
     float sc[4][4];
@@ -499,13 +568,40 @@ TRL_API int trl_attn_prefill(const void* q, const void* gate_src, int gate_ld, c
   const size_t smem = (size_t)G * PF_TQ * PF_ROW + (size_t)4 * PF_BC * PF_ROW;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * PF_TQ * PF_ROW + 4 * PF_BC * PF_ROW) != cudaSuccess)
+    if (cudaFuncSetAttribute(attn_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * PF_TQ * PF_ROW + 4 * PF_BC * PF_ROW) != cudaSuccess)
       return 3;
     configured = true;
   }
   const dim3 grid((max_q_len + PF_TQ - 1) / PF_TQ, n_kv, B);
-  return (int)trl_launch(attn_prefill_kernel, grid, dim3(G * 32), smem, (cudaStream_t)stream, (const bf16*)q,
+  return (int)trl_launch(attn_prefill_kernel<false>, grid, dim3(G * 32), smem, (cudaStream_t)stream, (const bf16*)q,
                          (const bf16*)gate_src, gate_ld, (const bf16*)kcache, (const bf16*)vcache,
+                         (const float*)nullptr, (const float*)nullptr,
+                         (const int*)block_table, max_blocks, (const int*)q_start, (const int*)q_len,
+                         (const int*)positions, (bf16*)out, n_q, n_kv, scale * 1.4426950408889634f, gated);
+}
+
+// The same over an e4m3 pool: kcache / vcache are the e4m3 bytes of one layer, kscale / vscale its
+// fp32 row scales [blocks, hkv, 16].
+TRL_API int trl_attn_prefill_fp8(const void* q, const void* gate_src, int gate_ld, const void* kcache,
+                                 const void* vcache, const void* kscale, const void* vscale,
+                                 const void* block_table, int max_blocks, const void* q_start, const void* q_len,
+                                 const void* positions, void* out, int B, int max_q_len, int n_q, int n_kv, int D,
+                                 float scale, int gated, void* stream) {
+  const int G = n_kv > 0 ? n_q / n_kv : 0;
+  if (D != PF_D || G < 1 || G > 8 || n_q % n_kv != 0 || B <= 0 || max_q_len <= 0) return (int)cudaErrorInvalidValue;
+  constexpr size_t kv_bytes = (size_t)2 * PF_BC * PF_ROW + (size_t)4 * PF_BC * PF_D + (size_t)4 * PF_BC * sizeof(float);
+  const size_t smem = (size_t)G * PF_TQ * PF_ROW + kv_bytes;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)(8 * PF_TQ * PF_ROW + kv_bytes)) != cudaSuccess)
+      return 3;
+    configured = true;
+  }
+  const dim3 grid((max_q_len + PF_TQ - 1) / PF_TQ, n_kv, B);
+  return (int)trl_launch(attn_prefill_kernel<true>, grid, dim3(G * 32), smem, (cudaStream_t)stream, (const bf16*)q,
+                         (const bf16*)gate_src, gate_ld, (const bf16*)kcache, (const bf16*)vcache,
+                         (const float*)kscale, (const float*)vscale,
                          (const int*)block_table, max_blocks, (const int*)q_start, (const int*)q_len,
                          (const int*)positions, (bf16*)out, n_q, n_kv, scale * 1.4426950408889634f, gated);
 }

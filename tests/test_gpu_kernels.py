@@ -384,10 +384,11 @@ def test_fp8_kv_attention_matches_the_fp8_oracle(lens, hist):
     g = torch.Generator().manual_seed(3)
     lp = {"q_norm": (1.0 + 0.1 * torch.randn(d, generator=g)).cuda(), "k_norm": (1.0 + 0.1 * torch.randn(d, generator=g)).cuda()}
     outs, pools = {}, {}
-    for mode in ("cuda_fp8", "ref_fp8", "cuda_bf16"):
+    for mode in ("cuda_fp8", "cuda_fp8_split", "ref_fp8", "cuda_bf16"):
         fp8 = mode != "cuda_bf16"
         pool = PagedKvPool(cfg, 64, "cuda", dtype=torch.float32 if mode == "ref_fp8" else torch.bfloat16, fp8=fp8)
         o = RefOps() if mode == "ref_fp8" else ops
+        ops.prefill_attn = mode != "cuda_fp8_split"     # tiled kernel for chunks of >= 16 tokens, or split-KV only
         blk = 1
         seqs_hist, seqs_now = [], []
         for i, (n, h) in enumerate(zip(lens, hist)):
@@ -414,8 +415,11 @@ def test_fp8_kv_attention_matches_the_fp8_oracle(lens, hist):
         db = getattr(b, name)[0, used].float() * sb.unsqueeze(-1)
         assert float((da - db).abs().max()) < 0.08 * float(db.abs().max()), name   # one e4m3 step at most
         assert float((da - db).abs().mean()) < 0.01 * float(db.abs().max()), name
+    ops.prefill_attn = True
     ref_o = outs["ref_fp8"]
     assert float((outs["cuda_fp8"] - ref_o).abs().max()) < 0.03 * float(ref_o.abs().max()) + 0.02
+    assert float((outs["cuda_fp8_split"] - ref_o).abs().max()) < 0.03 * float(ref_o.abs().max()) + 0.02
+    assert float((outs["cuda_fp8"] - outs["cuda_fp8_split"]).abs().max()) < 0.03
     assert float((outs["cuda_fp8"] - outs["cuda_bf16"]).abs().max()) < 0.08 * float(ref_o.abs().max()) + 0.03
     assert a.k.element_size() == 1
 

@@ -264,6 +264,16 @@ class CudaOps:
             batch.slot_mapping.data_ptr(), q.data_ptr(), kc.data_ptr(), vc.data_ptr(), ks.data_ptr(),
             vs.data_ptr(), t, n_q, n_kv, d, cfg.rotary_dim, float(cfg.rope_theta), cfg.rms_eps,
             int(cfg.attn_gated), st), "attn_prep_fp8")
+        if (self.prefill_attn and batch.max_q_len >= 16 and d == 256 and n_q % n_kv == 0 and n_q // n_kv <= 8
+                and not getattr(batch, "keep_steps", 0)):
+            N.check(self.lib.trl_attn_prefill_fp8(
+                q.data_ptr(), qkv.data_ptr(), qkv.stride(0), kc.data_ptr(), vc.data_ptr(), ks.data_ptr(),
+                vs.data_ptr(), batch.block_table.data_ptr(), batch.block_table.stride(0),
+                batch.q_start.data_ptr(), batch.q_len.data_ptr(), batch.positions.data_ptr(), out.data_ptr(),
+                batch.n_seqs, batch.max_q_len, n_q, n_kv, d, 1.0 / math.sqrt(d), int(cfg.attn_gated), st),
+                "attn_prefill_fp8")
+            N.count(2)
+            return out
         splits = self.attn_splits or self._pick_splits(batch, t, n_kv)
         po = self.ws.get("attn_po", (t * n_q * splits * d,), torch.float32)
         pm = self.ws.get("attn_pm", (t * n_q * splits,), torch.float32)
