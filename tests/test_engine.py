@@ -131,3 +131,19 @@ def test_fp8_kv_pool_serves_close_to_bf16_and_halves_the_pool():
     kv.write_block(3, k, v)
     k2, _ = kv.read_block(3)
     assert float((k2 - k).abs().max()) <= 0.07 * float(k.abs().max()) + 1e-6
+
+
+def test_poisoned_pools_give_the_same_tokens():
+    """Reads of unwritten pool memory would show: with every KV page, GDN state and conv ring
+    filled with NaN before the first request, the tokens equal those of zero-filled pools."""
+    from tilerl_b200.engine import SamplingParams
+    cfg = tiny_hybrid()
+    prompts = rand_prompts(cfg, 3, 21)
+    outs = []
+    for poison in (False, True):
+        eng = make_engine(cfg, planes=1)
+        if poison:
+            for t in (eng.kv.k, eng.kv.v, eng.states.states, eng.states.ring):
+                t.fill_(float("nan"))
+        outs.append([r.tokens for r in eng.generate(prompts, SamplingParams(max_tokens=10))])
+    assert outs[0] == outs[1]

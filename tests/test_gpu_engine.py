@@ -158,3 +158,22 @@ def test_graph_captured_before_a_larger_prefill_stays_valid(setup):
     got = [r.tokens for r in eng.generate(prompts, sp)]   # the 300-token prefill grows every buffer
     assert eng.counters["graph_ticks"] > 0 and len(ops.ws.retired) > 0
     assert got == want
+
+
+def test_poisoned_pools_give_the_same_tokens_on_gpu(setup):
+    """With every KV page, GDN state plane and conv ring filled with NaN before the first request
+    (the pad page and pad slot included), graph and eager serving give the tokens of clean pools:
+    no kernel reads pool memory that the request did not write."""
+    from tilerl_b200.engine import SamplingParams
+    from tilerl_b200.factory import build_engine
+    cfg, ops, model = setup
+    prompts = _prompts(cfg, 3, 37, 9)
+    sp = SamplingParams(max_tokens=10)
+    want = [r.tokens for r in build_engine(model, ops, slots=4, max_ctx=256, graph=False, prefix=False).generate(prompts, sp)]
+    for graph in (False, True):
+        eng = build_engine(model, ops, slots=4, max_ctx=256, graph=graph, prefix=False)
+        for t in (eng.kv.k, eng.kv.v, eng.states.states, eng.states.ring):
+            t.fill_(float("nan"))
+        assert [r.tokens for r in eng.generate(prompts, sp)] == want, graph
+    from tilerl_b200.ops import native
+    assert native.read_error()[0] == 0

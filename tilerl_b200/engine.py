@@ -166,6 +166,9 @@ class Engine:
                              spec_drafted=0, spec_accepted=0, cancelled=0, failed=0,
                              finished=0, preempted=0)
         self.timing = os.environ.get("TRL_STEP_TIMING") == "1"
+        # TRL_NVTX=1: every tick and its sampling phase become NVTX ranges, so a profiler can be
+        # limited to them (ncu --nvtx --nvtx-include "tick/", nsys --capture-range=nvtx)
+        self.nvtx = os.environ.get("TRL_NVTX") == "1" and torch.device(self.device).type == "cuda"
         self.last_tick_ms: Dict[str, float] = {}
         self.io_h2d = 0   # bytes copied host->device for tick inputs (eager ticks)
         self.io_d2h = 0   # bytes read back (sampled tokens / logits rows)
@@ -331,7 +334,14 @@ class Engine:
             if not plan:
                 return False
             t1 = time.perf_counter()
-            self._run(plan)
+            if self.nvtx:
+                torch.cuda.nvtx.range_push(f"tick/{len(plan)}seq/{sum(len(t) for _, t, _ in plan)}tok")
+                try:
+                    self._run(plan)
+                finally:
+                    torch.cuda.nvtx.range_pop()
+            else:
+                self._run(plan)
             self.counters["ticks"] += 1
             self._last_progress = time.monotonic()
             if self.timing:

@@ -110,11 +110,13 @@ def batch(args, cfg, ops, model):
     g = torch.Generator().manual_seed(2)
     prompts = [torch.randint(0, cfg.vocab, (args.prompt_len,), generator=g).tolist() for _ in range(args.requests)]
     eng = build_engine(model, ops, slots=args.requests + 1, max_ctx=args.prompt_len + args.gen + 64, graph=True,
-                       prefix=False, limits=StepLimits(max_batch=args.requests, max_batched_tokens=2048))
+                       prefix=False, limits=StepLimits(max_batch=args.requests, max_batched_tokens=2048),
+                       kv_fp8=args.kv_format == "fp8")
     eng.generate([prompts[0][:64]], SamplingParams(max_tokens=4))
     eng.precapture((args.requests,))
-    sp = SamplingParams(max_tokens=args.gen, ignore_eos=True)
-    rids = [eng.submit(p, sp) for p in prompts]
+    rids = [eng.submit(p, SamplingParams(max_tokens=args.gen, ignore_eos=True, temperature=args.temperature,
+                                         top_p=args.top_p, top_k=args.sample_top_k, seed=i))
+            for i, p in enumerate(prompts)]
 
     def prefill():
         while any(eng.poll(r)["state"] in ("waiting", "prefill") for r in rids):
@@ -129,7 +131,9 @@ def batch(args, cfg, ops, model):
     _, t_dec = _sync_time(decode)
     n1 = sum(len(eng.take(r).tokens) for r in rids)
     ticks = eng.counters["decode_ticks"] - ticks0
-    return dict(requests=args.requests, prompt_len=args.prompt_len, gen=args.gen,
+    return dict(requests=args.requests, prompt_len=args.prompt_len, gen=args.gen, kv_format=args.kv_format,
+                sampling=dict(temperature=args.temperature, top_p=args.top_p, top_k=args.sample_top_k),
+                kv_pool_gib=round(2 * eng.kv.k.numel() * eng.kv.k.element_size() / 2 ** 30, 2),
                 prefill_s=round(t_pre, 2), prefill_tok_s=round(args.requests * args.prompt_len / t_pre, 1),
                 decode_s=round(t_dec, 2), decode_agg_tok_s=round((n1 - n0) / t_dec, 1),
                 ms_per_decode_tick=round(1000 * t_dec / max(1, ticks), 2), graph_ticks=eng.counters["graph_ticks"])
@@ -147,6 +151,10 @@ def main():
     ap.add_argument("--ctx", type=int, default=32768)
     ap.add_argument("--top-k", type=int, default=128)
     ap.add_argument("--ticks", type=int, default=32)
+    ap.add_argument("--temperature", type=float, default=0.0, help="batch: sampling temperature (0 = greedy)")
+    ap.add_argument("--top-p", type=float, default=1.0, help="batch: nucleus bound")
+    ap.add_argument("--sample-top-k", type=int, default=0, help="batch: top-k restriction of the sampler")
+    ap.add_argument("--kv-format", default="bf16", choices=["bf16", "fp8"], help="batch: KV pool format")
     ap.add_argument("--graph", type=int, default=1, help="spec: replay verify ticks from CUDA graphs")
     args = ap.parse_args()
     from tilerl_b200.config import get_config
