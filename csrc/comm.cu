@@ -212,7 +212,7 @@ argmax_tp_kernel(const Peers P, const float* __restrict__ pv, const int* __restr
       const int i = pi[row * chunks + c];
       if (v > best || (v == best && i < bi)) best = v, bi = i;
     }
-    const int gi = bi + P.rank * v_local;
+    const int gi = bi == 0x7fffffff ? bi : bi + P.rank * v_local;   // no comparable value (all NaN): keep the sentinel
     for (int p = 0; p < P.world; ++p) {
       float2* slot = reinterpret_cast<float2*>(P.ws[p] + OFF_AMAX) + ((size_t)((epoch & 1) * MAX_RANKS + P.rank) * 256 + row);
       *slot = make_float2(best, __int_as_float(gi));
@@ -239,7 +239,7 @@ argmax_tp_kernel(const Peers P, const float* __restrict__ pv, const int* __restr
       const int i = __float_as_int(v.y);
       if (v.x > best || (v.x == best && i < bi)) best = v.x, bi = i;
     }
-    out[row] = bi;
+    out[row] = bi == 0x7fffffff ? 0 : bi;   // a row without any comparable logit yields token 0, never a wild index
   }
   __syncthreads();
   if (threadIdx.x == 0) ctrl[48] = epoch;

@@ -8,12 +8,18 @@
 namespace {
 
 __global__ void embedding_kernel(const bf16* __restrict__ table, const int* __restrict__ ids,
-                                 bf16* __restrict__ out, int H) {
+                                 bf16* __restrict__ out, int H, int V) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
-  const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)ids[t] * H);
+  const int id = ids[t];
   uint4* dst = reinterpret_cast<uint4*>(out + (size_t)t * H);
+  if (id < 0 || id >= V) {   // never read outside the table: zero row + error word {BOUNDS, 1, token, id}
+    if (threadIdx.x == 0) trl_set_error(TRL_ERR_BOUNDS, 1, t, id);
+    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)id * H);
   for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
 }
 
@@ -105,7 +111,9 @@ argmax_stage2_kernel(const float* __restrict__ pv, const int* __restrict__ pi, i
   __syncthreads();
   if (threadIdx.x == 0) {
     argmax_merge(best, bi, sv[1], si[1]);
-    out[row] = bi;
+    // a row of NaN compares false everywhere and keeps the sentinel: it yields token 0, never a
+    // wild index (the captured decode tick feeds this token to the next tick's embedding gather)
+    out[row] = bi == 0x7fffffff ? 0 : bi;
   }
 }
 
@@ -587,9 +595,9 @@ lora_b_kernel(const float* __restrict__ t, const float* __restrict__ B, bf16* __
 
 }  // namespace
 
-TRL_API int trl_embedding(const void* table, const void* ids, void* out, int T, int H, void* stream) {
+TRL_API int trl_embedding(const void* table, const void* ids, void* out, int T, int H, int V, void* stream) {
   return (int)trl_launch(embedding_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream,
-                         (const bf16*)table, (const int*)ids, (bf16*)out, H);
+                         (const bf16*)table, (const int*)ids, (bf16*)out, H, V);
 }
 TRL_API int trl_gather_rows(const void* x, const void* idx, void* out, int T, int H, void* stream) {
   return (int)trl_launch(gather_rows_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream,

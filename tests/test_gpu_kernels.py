@@ -457,3 +457,26 @@ def test_standalone_narrow_decode_binary():
         b.build_tests()
     r = subprocess.run([exe], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0 and "ok" in r.stdout, (r.returncode, r.stdout, r.stderr)
+
+
+def test_nan_logits_and_wild_token_ids_stay_in_bounds():
+    """A row of NaN logits yields token 0 from the argmax (never the internal sentinel, which
+    the captured decode tick would feed to the next embedding gather), and an embedding gather
+    of an id outside the table writes a zero row and records a bounds error instead of reading."""
+    from tilerl_b200.factory import make_ops
+    from tilerl_b200.ops import native
+    ops = make_ops("cuda")
+    native.read_error()
+    logits = torch.randn(3, 5000, device="cuda")
+    logits[1] = float("nan")
+    got = ops.argmax(logits).tolist()
+    assert got[1] == 0 and got[0] == int(logits[0].argmax()) and got[2] == int(logits[2].argmax())
+    table = torch.randn(100, 256, device="cuda").to(torch.bfloat16)
+    ids = torch.tensor([5, 0x7FFFFFFF, -3, 99], dtype=torch.int32, device="cuda")
+    x = ops.embed(table, ids).clone()
+    torch.cuda.synchronize()
+    assert torch.equal(x[0], table[5]) and torch.equal(x[3], table[99])
+    assert float(x[1].abs().max()) == 0.0 and float(x[2].abs().max()) == 0.0
+    code, a, _, _ = native.read_error()
+    assert code == 2 and a == 1          # bounds error raised by the embedding gather
+    assert native.read_error()[0] == 0   # reading clears it

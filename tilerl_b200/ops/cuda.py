@@ -172,7 +172,8 @@ class CudaOps:
     def embed(self, table, ids):
         t, h = ids.shape[0], table.shape[1]
         x = self.ws.get("x", (t, h), torch.bfloat16)
-        N.check(self.lib.trl_embedding(table.data_ptr(), ids.data_ptr(), x.data_ptr(), t, h, N.stream()), "embedding")
+        N.check(self.lib.trl_embedding(table.data_ptr(), ids.data_ptr(), x.data_ptr(), t, h, table.shape[0],
+                                       N.stream()), "embedding")
         N.count()
         return x
 

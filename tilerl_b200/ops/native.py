@@ -29,7 +29,7 @@ _SIGS = {
     "trl_attn_paged": [P, P, I, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, F, I, P],
     "trl_gdn": [P, I, P, P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, P, P, P, P, P, P, P,
                 I, I, I, I, I, I, I, F, P],
-    "trl_embedding": [P, P, P, I, I, P],
+    "trl_embedding": [P, P, P, I, I, I, P],
     "trl_gather_rows": [P, P, P, I, I, P],
     "trl_rmsnorm": [P, P, P, I, I, F, P],
     "trl_swiglu": [P, P, L, P],
