@@ -293,6 +293,20 @@ struct Cfg {
   }
 };
 
+// Phase timestamps of one launch (TRL_GEMM_DBG bit 4): [CTA][slot] = globaltimer in ns.
+//   0 entry, 1 set-up done, 2 producer past the dependency wait, 3 first operands landed,
+//   4 last MMA issued, 5 first accumulator complete, 6 last TMEM read-out done,
+//   7 split-tile finishing done, 8 teardown.
+constexpr int TRACE_SLOTS = 16, TRACE_CTAS = 256;
+__device__ unsigned long long g_gemm_trace[TRACE_CTAS * TRACE_SLOTS];
+__device__ __forceinline__ void trace_stamp(int dbg, int slot) {
+  if ((dbg & 16) && blockIdx.x < TRACE_CTAS) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    g_gemm_trace[blockIdx.x * TRACE_SLOTS + slot] = t;
+  }
+}
+
 template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -311,6 +325,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   float* rs_s = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(bars) + C::BAR_BYTES);  // [BN] column scales
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) trace_stamp(p.dbg, 0);
   const uint32_t bar0 = smem_u32(bars);
   auto full_a = [&](int s) { return bar0 + 8u * s; };
   auto empty_a = [&](int s) { return bar0 + 8u * (MS + s); };
@@ -338,6 +353,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   pdl_launch_dependents();
+  if (threadIdx.x == 0) trace_stamp(p.dbg, 1);
 
   const long long U = (long long)p.n_tiles * p.c_tiles * p.nk;
   const int G = gridDim.x;
@@ -409,6 +425,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         const int pre = min(SA, n_units);
         for (; a_issued < pre; ++a_issued) load_a_ls(ca), advance(ca, SA);
         pdl_wait();
+        trace_stamp(p.dbg, 2);
         bool ok = true;
         for (; ok && b_issued < n_units; ++b_issued) {
           if (b_issued >= pre) {
@@ -466,6 +483,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
           ok = mbar_wait(full_a(sa_i), sa_ph, abort_flag) && (SA == SB || mbar_wait(full_b(sb_i), sb_ph, abort_flag));
           if (!ok) break;
           tc_fence_after();
+          if (it == 0) trace_stamp(p.dbg, 3);
           const uint32_t aoff = (uint32_t)sa_i * (uint32_t)(C::A_STAGE >> 4);
           const uint32_t boff = (uint32_t)sb_i * (uint32_t)(C::B_STAGE >> 4);
           const uint32_t sf_cols = tmem_base + C::SF_COL0 + (uint32_t)(it & 1) * 64;  // double-buffered by parity
@@ -489,6 +507,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         u += len;
         ++seg;
       }
+      trace_stamp(p.dbg, 4);
     }
   } else {
     // ---------------- epilogue (warps 2..5) ----------------
@@ -535,6 +554,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
       }
       if (!ok) break;
       tc_fence_after();
+      if (seg == 0 && threadIdx.x == 64) trace_stamp(p.dbg, 5);
       // finishing one (token, row) value of a split tile (run-time epilogue kind)
       auto finish = [&](int tok, float v, float res) {
         if (p.epi == EPI_SWIGLU) epi_store<EPI_SWIGLU>(p, tok, n, lane, v, res);
@@ -553,6 +573,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
       }
       tc_fence_before();
       mbar_arrive(accum_empty);
+      if (threadIdx.x == 64) trace_stamp(p.dbg, 6);
       if (!whole) {
         // split tile: the last CTA to arrive finishes it from the per-segment slots
         asm volatile("bar.sync 1, 128;" ::: "memory");   // all slot stores of this CTA issued
@@ -566,33 +587,38 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (*last_flag) {
           __threadfence();
-          constexpr int GB = 4;   // tokens per batch: 4 x 8 slot loads + 4 residual loads in flight
-          for (int g0 = 0; g0 < BN / J; g0 += GB) {
-            float part[GB][8], res[GB];
+          // 16 tokens per batch, segments four at a time: up to 64 slot loads + 16 residual loads
+          // in flight per thread, so a 64-token tile of <= 4 segments costs 4 round trips to L2
+          constexpr int GB = 16, SGB = 4;
+          const int ntok = BN / J;
+          for (int g0 = 0; g0 < ntok; g0 += GB) {
+            float acc[GB], res[GB];
 #pragma unroll
             for (int gi = 0; gi < GB; ++gi) {
-              const int g = g0 + gi;
+              acc[gi] = 0.f;
+              res[gi] = g0 + gi < ntok ? load_res(tok0 + g0 + gi) : 0.f;
+            }
+            for (int sg0 = 0; sg0 < nseg; sg0 += SGB) {
+              float part[GB][SGB];
 #pragma unroll
-              for (int sg = 0; sg < 8; ++sg)
-                part[gi][sg] = (sg < nseg && g < BN / J)
-                                   ? __ldcg(tile_slots + ((size_t)sg * (BN / J) + g) * TILE_N + row) : 0.f;
-              res[gi] = g < BN / J ? load_res(tok0 + g) : 0.f;
+              for (int gi = 0; gi < GB; ++gi)
+#pragma unroll
+                for (int sj = 0; sj < SGB; ++sj)
+                  part[gi][sj] = (sg0 + sj < nseg && g0 + gi < ntok)
+                                     ? __ldcg(tile_slots + ((size_t)(sg0 + sj) * ntok + g0 + gi) * TILE_N + row) : 0.f;
+#pragma unroll
+              for (int gi = 0; gi < GB; ++gi)
+#pragma unroll
+                for (int sj = 0; sj < SGB; ++sj) acc[gi] += part[gi][sj];   // ascending segment order: bitwise reproducible
             }
 #pragma unroll
-            for (int gi = 0; gi < GB; ++gi) {
-              const int g = g0 + gi;
-              if (g >= BN / J) break;
-              float v = 0.f;
-#pragma unroll
-              for (int sg = 0; sg < 8; ++sg) v += part[gi][sg];   // fixed order: bitwise reproducible
-              for (int sg = 8; sg < nseg; ++sg)
-                v += __ldcg(tile_slots + ((size_t)sg * (BN / J) + g) * TILE_N + row);
-              finish(tok0 + g, v, res[gi]);
-            }
+            for (int gi = 0; gi < GB; ++gi)
+              if (g0 + gi < ntok) finish(tok0 + g0 + gi, acc[gi], res[gi]);
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
       }
+      if (threadIdx.x == 64) trace_stamp(p.dbg, 7);
       u += len;
       ++seg;
     }
@@ -611,6 +637,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
   }
+  if (threadIdx.x == 0) trace_stamp(p.dbg, 8);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -652,6 +679,7 @@ quant_act_kernel(const bf16* __restrict__ x, int ldx, const float* __restrict__ 
   float rstd = 1.f;
   if (norm_w != nullptr) {
     float ss = 0.f;
+#pragma unroll 4
     for (int k = threadIdx.x * 4; k < K; k += blockDim.x * 4) {
       float v[4];
       load4(k, v);
@@ -661,6 +689,7 @@ quant_act_kernel(const bf16* __restrict__ x, int ldx, const float* __restrict__ 
     rstd = rsqrtf(ss / (float)K + eps);
   }
   float amax = 0.f;
+#pragma unroll 4
   for (int k = threadIdx.x * 4; k < K; k += blockDim.x * 4) {
     float v[4];
     load4(k, v);
@@ -803,6 +832,12 @@ static int pick_bn(int cols) {
 }
 
 // Bytes of split-K scratch trl_gemm_nvfp4 needs for this problem (0 if no tile is split).
+// Copies the phase timestamps of the last traced launch (TRL_GEMM_DBG=16): n_ctas x 16 values.
+TRL_API int trl_gemm_trace_read(void* out, int n_ctas) {
+  if (n_ctas < 0 || n_ctas > TRACE_CTAS) return (int)cudaErrorInvalidValue;
+  return (int)cudaMemcpyFromSymbol(out, g_gemm_trace, (size_t)n_ctas * TRACE_SLOTS * sizeof(unsigned long long));
+}
+
 TRL_API long trl_gemm_nvfp4_scratch_bytes(int tokens, int J, int N, int K, int max_ctas) {
   const int cols = tokens * J, BN = pick_bn(cols);
   const int n_tiles = (N + TILE_N - 1) / TILE_N, c_tiles = (cols + BN - 1) / BN, nk = (K + KT_ELEMS - 1) / KT_ELEMS;

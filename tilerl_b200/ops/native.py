@@ -42,6 +42,7 @@ _SIGS = {
     "trl_pager_refcount": [P, I], "trl_pager_refs": [P, P, I],
     "trl_batch_ints": [c_longlong, I, I],
     "trl_batch_fill": [I, P, P, P, P, P, P, P, I, I, P, c_longlong],
+    "trl_gemm_trace_read": [P, I],
     "trl_sample_nucleus": [P, I, P, P, P, P, P, P, P, I, I, P],
     "trl_attn_prep_fp8": [P, I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P],
     "trl_attn_paged_fp8": [P, P, I, P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, F, I, P],

@@ -27,6 +27,7 @@ def main():
     ap.add_argument("--max-ctas", type=int, default=0)
     ap.add_argument("--split", type=int, default=1)
     ap.add_argument("--tiled", type=int, default=1)
+    ap.add_argument("--trace", action="store_true", help="gemm: per-phase timestamps of one launch (median, max over CTAs)")
     args = ap.parse_args()
     from tilerl_b200.formats import NVFP4Tensor
     from tilerl_b200.ops.cuda import CudaOps
@@ -95,6 +96,24 @@ def main():
             us = timeit(gemm_only)
             res["gemm_tc_us"] = round(us, 2)
             res["gemm_tc_TBs"] = round(wbytes / us / 1e6, 3)
+            if args.trace:
+                # one traced launch: phase timestamps per CTA, reported in us after the first CTA's entry
+                import os
+                import numpy as np
+                os.environ["TRL_GEMM_DBG"] = "16"
+                gemm_only(ws[0])
+                torch.cuda.synchronize()
+                os.environ.pop("TRL_GEMM_DBG")
+                buf = np.zeros((148, 16), dtype=np.uint64)
+                native.check(ops.lib.trl_gemm_trace_read(buf.ctypes.data, 148), "trace_read")
+                t = buf.astype(np.float64)
+                live = t[:, 0] > 0
+                t0 = t[live, 0].min()
+                names = ["entry", "setup", "dep_wait", "first_operands", "last_mma", "first_accum", "tmem_read",
+                         "finish", "teardown"]
+                res["trace_us"] = {nm: [round(float(np.median(t[live, i] - t0)) / 1e3, 2),
+                                        round(float((t[live, i] - t0).max()) / 1e3, 2)]
+                                   for i, nm in enumerate(names)}
         if args.only in ("", "quant"):
             us = timeit(lambda w: quant_act(ops, x, k, args.terms))
             res["quant_us"] = round(us, 2)
