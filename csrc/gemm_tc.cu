@@ -296,7 +296,8 @@ struct Cfg {
 // Phase timestamps of one launch (TRL_GEMM_DBG bit 4): [CTA][slot] = globaltimer in ns.
 //   0 entry, 1 set-up done, 2 producer past the dependency wait, 3 first operands landed,
 //   4 last MMA issued, 5 first accumulator complete, 6 last TMEM read-out done,
-//   7 split-tile finishing done, 8 teardown.
+//   7 split-tile finishing done, 8 teardown, 9 segment counted, 10 reduction starts,
+//   11 first reduction batch stored.
 constexpr int TRACE_SLOTS = 16, TRACE_CTAS = 256;
 __device__ unsigned long long g_gemm_trace[TRACE_CTAS * TRACE_SLOTS];
 __device__ __forceinline__ void trace_stamp(int dbg, int slot) {
@@ -583,14 +584,79 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
           const int prev = atomicAdd(p.counters + tile, 1);
           *last_flag = (prev == nseg - 1);
           if (prev == nseg - 1) p.counters[tile] = 0;
+          trace_stamp(p.dbg, 9);
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (*last_flag) {
           __threadfence();
-          // 16 tokens per batch, segments four at a time: up to 64 slot loads + 16 residual loads
-          // in flight per thread, so a 64-token tile of <= 4 segments costs 4 round trips to L2
-          constexpr int GB = 16, SGB = 4;
+          if (threadIdx.x == 64) trace_stamp(p.dbg, 10);
           const int ntok = BN / J;
+          const bool vec_ok = (p.N & 3) == 0 && (p.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 &&
+                              (p.epi != EPI_RESIDUAL ||
+                               ((p.ldr & 3) == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 7) == 0));
+          if (vec_ok) {
+            // a thread owns 4 consecutive rows of 4 tokens per pass: 128-bit slot loads, one 64-bit
+            // (bf16) or 128-bit (fp32) store per token, a quarter of the memory instructions of the
+            // row-per-thread mapping; segments are summed in ascending order (bitwise reproducible)
+            constexpr int TQ = 4, SGB = 4;
+            const int e = (int)threadIdx.x - 64;
+            const int rg = e & 31, tsub = e >> 5;
+            const int n4 = nt * TILE_N + rg * 4;
+            for (int g0 = 0; g0 < ntok; g0 += 4 * TQ) {
+              float4 acc[TQ];
+              uint2 res[TQ];
+#pragma unroll
+              for (int q = 0; q < TQ; ++q) {
+                const int g = g0 + q * 4 + tsub, tok = tok0 + g;
+                acc[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+                res[q] = make_uint2(0u, 0u);
+                if (p.epi == EPI_RESIDUAL && g < ntok && tok < p.tokens && n4 < p.N)
+                  res[q] = *reinterpret_cast<const uint2*>(p.residual + (size_t)tok * p.ldr + n4);
+              }
+              for (int sg0 = 0; sg0 < nseg; sg0 += SGB) {
+                float4 part[TQ][SGB];
+#pragma unroll
+                for (int q = 0; q < TQ; ++q)
+#pragma unroll
+                  for (int sj = 0; sj < SGB; ++sj) {
+                    const int g = g0 + q * 4 + tsub;
+                    part[q][sj] = (sg0 + sj < nseg && g < ntok)
+                                      ? __ldcg(reinterpret_cast<const float4*>(
+                                            tile_slots + ((size_t)(sg0 + sj) * ntok + g) * TILE_N + rg * 4))
+                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+                  }
+#pragma unroll
+                for (int q = 0; q < TQ; ++q)
+#pragma unroll
+                  for (int sj = 0; sj < SGB; ++sj) {
+                    acc[q].x += part[q][sj].x, acc[q].y += part[q][sj].y;
+                    acc[q].z += part[q][sj].z, acc[q].w += part[q][sj].w;
+                  }
+              }
+#pragma unroll
+              for (int q = 0; q < TQ; ++q) {
+                const int g = g0 + q * 4 + tsub, tok = tok0 + g;
+                if (g >= ntok || tok >= p.tokens || n4 >= p.N) continue;
+                float4 a = acc[q];
+                if (p.epi == EPI_SWIGLU) {
+                  const float y0 = __fdividef(a.x, 1.f + __expf(-a.x)) * a.y;
+                  const float y1 = __fdividef(a.z, 1.f + __expf(-a.z)) * a.w;
+                  *reinterpret_cast<uint32_t*>(reinterpret_cast<bf16*>(p.out) + (size_t)tok * p.ldo + (n4 >> 1)) =
+                      f2_to_bf162_bits(y0, y1);
+                } else if (p.epi == EPI_STORE_F32) {
+                  *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + (size_t)tok * p.ldo + n4) = a;
+                } else {
+                  const float2 r0 = bf162_bits_to_f2(res[q].x), r1 = bf162_bits_to_f2(res[q].y);
+                  a.x += r0.x, a.y += r0.y, a.z += r1.x, a.w += r1.y;
+                  *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(p.out) + (size_t)tok * p.ldo + n4) =
+                      make_uint2(f2_to_bf162_bits(a.x, a.y), f2_to_bf162_bits(a.z, a.w));
+                }
+              }
+              if (g0 == 0 && threadIdx.x == 64) trace_stamp(p.dbg, 11);
+            }
+          } else {
+          // row-per-thread fallback for outputs that do not allow vector stores
+          constexpr int GB = 16, SGB = 4;
           for (int g0 = 0; g0 < ntok; g0 += GB) {
             float acc[GB], res[GB];
 #pragma unroll
@@ -614,6 +680,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
 #pragma unroll
             for (int gi = 0; gi < GB; ++gi)
               if (g0 + gi < ntok) finish(tok0 + g0 + gi, acc[gi], res[gi]);
+          }
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");

@@ -110,7 +110,7 @@ def main():
                 live = t[:, 0] > 0
                 t0 = t[live, 0].min()
                 names = ["entry", "setup", "dep_wait", "first_operands", "last_mma", "first_accum", "tmem_read",
-                         "finish", "teardown"]
+                         "finish", "teardown", "seg_counted", "reduce_start", "reduce_batch0"]
                 res["trace_us"] = {nm: [round(float(np.median(t[live, i] - t0)) / 1e3, 2),
                                         round(float((t[live, i] - t0).max()) / 1e3, 2)]
                                    for i, nm in enumerate(names)}
