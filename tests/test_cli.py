@@ -13,6 +13,16 @@ def test_serve_dry_run_prints_ledger(capsys):
     assert "weights" in out and "kv pool" in out
 
 
+def test_serve_dry_run_fp8_kv_holds_about_twice_the_tokens(capsys):
+    import re
+    toks = []
+    for fmt in ("bf16", "fp8"):
+        assert cli.main(["serve", "--model", "qwen38-27b", "--dry-run", "--slots", "16", "--kv-format", fmt]) == 0
+        m = re.search(r"kv pool holds ([\d,]+) tokens", capsys.readouterr().out)
+        toks.append(int(m.group(1).replace(",", "")))
+    assert 1.9 < toks[1] / toks[0] < 2.0     # one byte per value plus the per-row scales
+
+
 def test_bench_kernels_table(capsys):
     assert cli.main(["bench", "--model", "qwen38-27b", "--kernels"]) == 0
     out = capsys.readouterr().out

@@ -126,7 +126,7 @@ def cmd_serve(args) -> int:
     cfg = get_config(args.model)
     if args.dry_run:
         p = memory.plan(cfg, slots=args.slots, blocks=args.blocks, max_batched_tokens=args.max_batched_tokens,
-                        planes=args.spec_width if args.draft else 1)
+                        planes=args.spec_width if args.draft else 1, kv_fp8=args.kv_format == "fp8")
         print(memory.memory_table(p))
         return 0
     from .engine import StepLimits
