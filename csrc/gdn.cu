@@ -415,7 +415,318 @@ gdn_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
   }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Chunk-parallel scan for prefill: the same column slicing and thread mapping as the scan
+// above, but the 16 tokens of a chunk are not walked one after the other.  With the chunk's
+// cumulative log-decay G_i, the chunk-start state S0 and, per state column,
+//   p_i = k_i . S0,  r_i = q_i . S0                        (all tokens at once, no chain)
+//   M_ij = beta_i e^{G_i-G_j} (k_i . k_j)  (j < i),   N_ij = e^{G_i-G_j} (q_i . k_j)  (j <= i)
+// the delta rule unrolls to
+//   d_i = beta_i (v_i - e^{G_i} p_i) - sum_{j<i} M_ij d_j     (16 x 16 forward substitution)
+//   o_i = e^{G_i} r_i + sum_{j<=i} N_ij d_j
+//   S   = e^{G_15} S0 + sum_i e^{G_15-G_i} k_i (x) d_i
+// so a token no longer waits for the state update of the one before it: the only serial part
+// is the small triangular solve.  M and N do not depend on the column and are built once per
+// chunk by the CTA.  Tokens past the end of a sequence enter as beta = 0, g = 0, zero rows.
+// Chunks of fewer than WY_MIN tokens run the serial step (identical to gdn_scan_kernel), so a
+// prompt gives the same bits whether it is prefilled in one tick or in 16-aligned pieces.
+// Parity: the chunkwise pipeline of tilerl_kernels/kernels_gdn.py:127-745 (cumsum, kkt,
+// solve_tril, wu, state scan, chunk_o), here in one kernel per layer.
+constexpr int WY_MIN = 4;
+template <int D>
+struct alignas(16) WySmem {
+  static constexpr int Q = 8, R = D / Q, KP = R + 4, RS = Q * KP + 4, TC = SCAN_TC;
+  float q[2][TC][RS];
+  float k[2][TC][RS];
+  float v[2][TC][32];
+  float g[2][TC];
+  float b[2][TC];
+  float o[TC][32];
+  float M[TC][TC];
+  float N[TC][TC];
+  float eG[TC];
+  float w[TC];
+  float Gc[TC];
+  float qk[TC];
+  int last;
+};
+
+template <int D>
+__global__ void __launch_bounds__(256)
+gdn_scan_wy_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
+                   const float* __restrict__ vc, const float* __restrict__ gin,
+                   const float* __restrict__ bin, const bf16* __restrict__ inp, int ld,
+                   float* __restrict__ states, int* __restrict__ cur, bf16* __restrict__ ring,
+                   const int* __restrict__ q_start, const int* __restrict__ q_len,
+                   const int* __restrict__ positions, const int* __restrict__ state_slots,
+                   long state_slot_stride, long plane_stride, long ring_slot_stride,
+                   const float* __restrict__ norm_w, float eps, float* __restrict__ o_scratch,
+                   bf16* __restrict__ out, int nk, int nv) {
+  using SM = WySmem<D>;
+  constexpr int Q = SM::Q, R = SM::R, KP = SM::KP, TC = SM::TC;
+  constexpr int NS = D / 32, NT = 256, NW = NT / 32, CW = 32 / Q;
+  extern __shared__ __align__(16) unsigned char wy_raw[];
+  SM& sm = *reinterpret_cast<SM*>(wy_raw);
+  pdl_launch_dependents();
+  pdl_wait();
+  const int h = blockIdx.x / NS, slice = blockIdx.x % NS, seq = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int r = lane / CW, cl = warp * CW + (lane % CW), col = slice * 32 + cl;
+  const int T = q_len[seq], t0 = q_start[seq];
+  if (T == 0) return;
+  const int slot = state_slots[seq];
+  const int kh = h * nk / nv;
+  const int live = cur[slot];
+  float* sbase = states + (size_t)slot * state_slot_stride + (size_t)h * D * D;
+  float* splane = sbase + (size_t)live * plane_stride;
+  float S[R];
+#pragma unroll
+  for (int j = 0; j < R; ++j) S[j] = splane[(size_t)(r * R + j) * D + col];
+
+  auto stage = [&](int i0, int b) {
+    const int n = min(TC, T - i0);
+    for (int x = tid; x < TC * (D / 4); x += NT) {
+      const int tt = x / (D / 4), pc = x % (D / 4);
+      const int e = pc * 4, dst = (e / R) * KP + (e % R);
+      if (tt < n) {
+        const size_t src = ((size_t)(t0 + i0 + tt) * nk + kh) * D + e;
+        cp_async16(&sm.q[b][tt][dst], qn + src);
+        cp_async16(&sm.k[b][tt][dst], kn + src);
+      } else {   // rows past the end: zeros, so they drop out of every product
+        *reinterpret_cast<float4*>(&sm.q[b][tt][dst]) = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4*>(&sm.k[b][tt][dst]) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    for (int x = tid; x < TC * 8; x += NT) {
+      const int tt = x >> 3, pc = x & 7;
+      if (tt < n) cp_async16(&sm.v[b][tt][pc * 4], vc + ((size_t)(t0 + i0 + tt) * nv + h) * D + slice * 32 + pc * 4);
+      else *reinterpret_cast<float4*>(&sm.v[b][tt][pc * 4]) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (tid < TC) {
+      sm.g[b][tid] = tid < n ? gin[(size_t)(t0 + i0 + tid) * nv + h] : 0.f;
+      sm.b[b][tid] = tid < n ? bin[(size_t)(t0 + i0 + tid) * nv + h] : 0.f;
+    }
+    cp_async_commit();
+  };
+
+  stage(0, 0);
+  int b = 0;
+  for (int i0 = 0; i0 < T; i0 += TC, b ^= 1) {
+    const int n = min(TC, T - i0);
+    const bool wy = n >= WY_MIN;
+    cp_async_wait<0>();
+    __syncthreads();                       // chunk b landed; every thread left the previous chunk
+    if (i0 > 0) {                          // raw outputs of the previous chunk, 128 B rows
+      for (int x = tid; x < TC * 32; x += NT)
+        o_scratch[((size_t)(t0 + i0 - TC + (x >> 5)) * nv + h) * D + slice * 32 + (x & 31)] = sm.o[x >> 5][x & 31];
+    }
+    if (i0 + TC < T) stage(i0 + TC, b ^ 1);
+    if (wy) {
+      if (warp == 0) {                     // cumulative log-decay of the chunk and its exponentials
+        float gc = lane < TC ? sm.g[b][lane] : 0.f;
+#pragma unroll
+        for (int o = 1; o < TC; o <<= 1) {
+          const float nb = __shfl_up_sync(0xffffffffu, gc, o);
+          if (lane >= o) gc += nb;
+        }
+        const float glast = __shfl_sync(0xffffffffu, gc, TC - 1);
+        if (lane < TC) {
+          sm.Gc[lane] = gc;
+          sm.eG[lane] = __expf(gc);
+          sm.w[lane] = __expf(glast - gc);
+        }
+      }
+      __syncthreads();
+      {                                    // M and N: one (i, j) pair per thread, j <= i
+        const int i = tid >> 4, j = tid & 15;
+        float mv = 0.f, nv_ = 0.f;
+        if (j <= i) {
+          float kk = 0.f, qk = 0.f;
+#pragma unroll
+          for (int grp = 0; grp < Q; ++grp) {
+            const float4* ki = reinterpret_cast<const float4*>(&sm.k[b][i][grp * KP]);
+            const float4* kj = reinterpret_cast<const float4*>(&sm.k[b][j][grp * KP]);
+            const float4* qi = reinterpret_cast<const float4*>(&sm.q[b][i][grp * KP]);
+#pragma unroll
+            for (int f = 0; f < R / 4; ++f) {
+              const float4 a = ki[f], c = kj[f], e = qi[f];
+              kk = fmaf(a.x, c.x, kk), kk = fmaf(a.y, c.y, kk), kk = fmaf(a.z, c.z, kk), kk = fmaf(a.w, c.w, kk);
+              qk = fmaf(e.x, c.x, qk), qk = fmaf(e.y, c.y, qk), qk = fmaf(e.z, c.z, qk), qk = fmaf(e.w, c.w, qk);
+            }
+          }
+          const float dec = __expf(sm.Gc[i] - sm.Gc[j]);
+          mv = j < i ? sm.b[b][i] * dec * kk : 0.f;
+          nv_ = dec * qk;
+        }
+        sm.M[i][j] = mv;
+        sm.N[i][j] = nv_;
+      }
+      __syncthreads();                     // M, N visible; s_o flushed
+      float ks[TC], qs[TC];
+#pragma unroll
+      for (int tt = 0; tt < TC; ++tt) {    // p and r of every token against the chunk-start state
+        const float4* k4 = reinterpret_cast<const float4*>(&sm.k[b][tt][r * KP]);
+        const float4* q4 = reinterpret_cast<const float4*>(&sm.q[b][tt][r * KP]);
+        float a0 = 0.f, a1 = 0.f, c0 = 0.f, c1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < R / 4; ++j) {
+          const float4 kk = k4[j], qq = q4[j];
+          a0 = fmaf(kk.x, S[4 * j], a0), a1 = fmaf(kk.y, S[4 * j + 1], a1);
+          a0 = fmaf(kk.z, S[4 * j + 2], a0), a1 = fmaf(kk.w, S[4 * j + 3], a1);
+          c0 = fmaf(qq.x, S[4 * j], c0), c1 = fmaf(qq.y, S[4 * j + 1], c1);
+          c0 = fmaf(qq.z, S[4 * j + 2], c0), c1 = fmaf(qq.w, S[4 * j + 3], c1);
+        }
+        ks[tt] = a0 + a1, qs[tt] = c0 + c1;
+      }
+#pragma unroll
+      for (int m = CW; m < 32; m <<= 1) {
+#pragma unroll
+        for (int tt = 0; tt < TC; ++tt) {
+          ks[tt] += __shfl_xor_sync(0xffffffffu, ks[tt], m);
+          qs[tt] += __shfl_xor_sync(0xffffffffu, qs[tt], m);
+        }
+      }
+      float d[TC];
+#pragma unroll
+      for (int i = 0; i < TC; ++i) {       // forward substitution, the only chain of the chunk
+        float acc = sm.b[b][i] * (sm.v[b][i][cl] - sm.eG[i] * ks[i]);
+#pragma unroll
+        for (int j = 0; j < i; ++j) acc = fmaf(-sm.M[i][j], d[j], acc);
+        d[i] = acc;
+      }
+#pragma unroll
+      for (int i = 0; i < TC; ++i) {       // outputs: row group r writes tokens r and r + 8
+        if ((i & (Q - 1)) == r) {
+          float acc = sm.eG[i] * qs[i];
+#pragma unroll
+          for (int j = 0; j <= i; ++j) acc = fmaf(sm.N[i][j], d[j], acc);
+          sm.o[i][cl] = acc;
+        }
+      }
+      const float glast = sm.eG[TC - 1];
+#pragma unroll
+      for (int j = 0; j < R; ++j) S[j] *= glast;
+#pragma unroll
+      for (int tt = 0; tt < TC; ++tt) {    // state update: all tokens' rank-1 terms at once
+        const float c = sm.w[tt] * d[tt];
+        const float4* k4 = reinterpret_cast<const float4*>(&sm.k[b][tt][r * KP]);
+#pragma unroll
+        for (int j = 0; j < R / 4; ++j) {
+          const float4 kk = k4[j];
+          S[4 * j] = fmaf(kk.x, c, S[4 * j]), S[4 * j + 1] = fmaf(kk.y, c, S[4 * j + 1]);
+          S[4 * j + 2] = fmaf(kk.z, c, S[4 * j + 2]), S[4 * j + 3] = fmaf(kk.w, c, S[4 * j + 3]);
+        }
+      }
+    } else {
+      for (int tt = warp; tt < n; tt += NW) {   // q.k of this chunk's tokens
+        float a = 0.f;
+        for (int e = lane; e < D; e += 32) {
+          const int o = (e / R) * KP + (e % R);
+          a = fmaf(sm.q[b][tt][o], sm.k[b][tt][o], a);
+        }
+        a = warp_sum(a);
+        if (lane == 0) sm.qk[tt] = a;
+      }
+      __syncthreads();                     // q.k visible, s_o flushed
+      for (int tt = 0; tt < n; ++tt) {     // the serial step of gdn_scan_kernel, operation for operation
+        const float eg = __expf(sm.g[b][tt]), beta = sm.b[b][tt], v = sm.v[b][tt][cl], qk = sm.qk[tt];
+        const float4* k4 = reinterpret_cast<const float4*>(&sm.k[b][tt][r * KP]);
+        const float4* q4 = reinterpret_cast<const float4*>(&sm.q[b][tt][r * KP]);
+        float kreg[R];
+        float ks0 = 0.f, ks1 = 0.f, qs0 = 0.f, qs1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < R / 4; ++j) {
+          const float4 kk = k4[j], qq = q4[j];
+          kreg[4 * j] = kk.x, kreg[4 * j + 1] = kk.y, kreg[4 * j + 2] = kk.z, kreg[4 * j + 3] = kk.w;
+          ks0 = fmaf(kk.x, S[4 * j], ks0), ks1 = fmaf(kk.y, S[4 * j + 1], ks1);
+          ks0 = fmaf(kk.z, S[4 * j + 2], ks0), ks1 = fmaf(kk.w, S[4 * j + 3], ks1);
+          qs0 = fmaf(qq.x, S[4 * j], qs0), qs1 = fmaf(qq.y, S[4 * j + 1], qs1);
+          qs0 = fmaf(qq.z, S[4 * j + 2], qs0), qs1 = fmaf(qq.w, S[4 * j + 3], qs1);
+        }
+        float ks = ks0 + ks1, qs = qs0 + qs1;
+#pragma unroll
+        for (int m = CW; m < 32; m <<= 1) {
+          ks += __shfl_xor_sync(0xffffffffu, ks, m);
+          qs += __shfl_xor_sync(0xffffffffu, qs, m);
+        }
+        const float dd = beta * (v - eg * ks);
+#pragma unroll
+        for (int j = 0; j < R; ++j) S[j] = fmaf(kreg[j], dd, eg * S[j]);
+        if (r == 0) sm.o[tt][cl] = fmaf(eg, qs, qk * dd);
+      }
+    }
+  }
+  __syncthreads();
+  {                                        // raw outputs of the last chunk
+    const int i0 = ((T - 1) / TC) * TC, n = T - i0;
+    for (int x = tid; x < n * 32; x += NT)
+      o_scratch[((size_t)(t0 + i0 + (x >> 5)) * nv + h) * D + slice * 32 + (x & 31)] = sm.o[x >> 5][x & 31];
+  }
+#pragma unroll
+  for (int j = 0; j < R; ++j) splane[(size_t)(r * R + j) * D + col] = S[j];
+  const int C = 2 * nk * D + nv * D;
+  if (slice == 0) {
+    // ring refresh: raw q/k rows by the first value head of each key head, v rows by every
+    // head, for the last min(T, RING) tokens of the tick
+    bf16* rg = ring + (size_t)slot * ring_slot_stride;
+    const int first = max(0, T - RING);
+    const int rep = nv / nk;
+    for (int i = first; i < T; ++i) {
+      const int t = t0 + i;
+      const int rrow = positions[t] % RING;
+      const bf16* src = inp + (size_t)t * ld;
+      bf16* dst = rg + (size_t)rrow * C;
+      if (h % rep == 0) {
+        for (int c = tid; c < 2 * D; c += NT) {
+          const int cc = (c < D) ? kh * D + c : nk * D + kh * D + (c - D);
+          dst[cc] = src[cc];
+        }
+      }
+      for (int c = tid; c < D; c += NT) {
+        const int cc = 2 * nk * D + h * D + c;
+        dst[cc] = src[cc];
+      }
+    }
+  }
+  // the last slice of this head to get here normalises the head
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    int* ctr = g_gdn_done + (size_t)seq * nv + h;
+    const int prev = atomicAdd(ctr, 1);
+    sm.last = (prev == NS - 1);
+    if (prev == NS - 1) *ctr = 0;
+  }
+  __syncthreads();
+  if (!sm.last) return;
+  __threadfence();
+  for (int i = warp; i < T; i += NW) {     // gated RMSNorm per token, one warp per token
+    const int t = t0 + i;
+    const float* o = o_scratch + ((size_t)t * nv + h) * D;
+    float ov[D / 32], ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < D / 32; ++j) {
+      ov[j] = __ldcg(o + lane + 32 * j);
+      ss += ov[j] * ov[j];
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)D + eps);
+    const bf16* z = inp + (size_t)t * ld + C + (size_t)h * D;
+#pragma unroll
+    for (int j = 0; j < D / 32; ++j) {
+      const int c = lane + 32 * j;
+      out[((size_t)t * nv + h) * D + c] =
+          __float2bfloat16(ov[j] * rstd * norm_w[c] * silu_f(__bfloat162float(z[c])));
+    }
+  }
+}
+
 }  // namespace
+
+static int g_gdn_wy = -1;   // -1: read TRL_GDN_WY at the first launch
+// Turns the chunk-parallel prefill scan on or off at run time (tests compare the two paths).
+TRL_API void trl_gdn_set_wy(int on) { g_gdn_wy = on ? 1 : 0; }
 
 // Scratch (fp32): qn, kn [T*nk*D]; vc, o_scratch [T*nv*D]; g, beta [T*nv].
 TRL_API int trl_gdn(const void* inp, int ld, const void* conv_w, const void* dt_bias, const void* a_log,
@@ -446,12 +757,34 @@ TRL_API int trl_gdn(const void* inp, int ld, const void* conv_w, const void* dt_
                  (const int*)q_len, (const int*)positions, (const int*)state_slots,                 \
                  (const int*)keep_flags, state_slot_stride, plane_stride, ring_slot_stride,         \
                  (const float*)norm_w, eps, (float*)o_scratch, (bf16*)out, nk, nv, planes)
+#define SCANWY(DD)                                                                                  \
+  {                                                                                                 \
+    auto kern = gdn_scan_wy_kernel<DD>;                                                             \
+    static bool configured = false;                                                                 \
+    if (!configured) {                                                                              \
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                   \
+                               (int)sizeof(WySmem<DD>)) != cudaSuccess) return 3;                   \
+      configured = true;                                                                            \
+    }                                                                                               \
+    e = trl_launch(kern, dim3(nv * (DD / 32), B), dim3(256), sizeof(WySmem<DD>), st,                \
+                   (const float*)qn, (const float*)kn, (const float*)vc, (const float*)g,           \
+                   (const float*)beta, (const bf16*)inp, ld, (float*)states, (int*)cur,             \
+                   (bf16*)ring, (const int*)q_start, (const int*)q_len, (const int*)positions,      \
+                   (const int*)state_slots, state_slot_stride, plane_stride, ring_slot_stride,      \
+                   (const float*)norm_w, eps, (float*)o_scratch, (bf16*)out, nk, nv);               \
+  }
   static const bool legacy = getenv("TRL_GDN_LEGACY") != nullptr;
+  // chunk-parallel scan for ticks that carry prompt tokens (more tokens than sequences) and keep
+  // no per-token states; TRL_GDN_WY=0 turns it off
+  if (g_gdn_wy < 0) g_gdn_wy = !(getenv("TRL_GDN_WY") && atoi(getenv("TRL_GDN_WY")) == 0);
+  const bool wy_on = g_gdn_wy != 0;
   const bool scan = !legacy && (long)B * nv <= GDN_DONE_CAP;
-  if (D == 128) { if (scan) SCAN(128); else RECUR(128); }
-  else if (D == 64) { if (scan) SCAN(64); else RECUR(64); }
+  const bool wy = scan && wy_on && T > B && keep_flags == nullptr;
+  if (D == 128) { if (wy) SCANWY(128) else if (scan) SCAN(128); else RECUR(128); }
+  else if (D == 64) { if (wy) SCANWY(64) else if (scan) SCAN(64); else RECUR(64); }
   else return (int)cudaErrorInvalidValue;
 #undef RECUR
 #undef SCAN
+#undef SCANWY
   return (int)e;
 }

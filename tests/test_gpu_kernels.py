@@ -480,3 +480,46 @@ def test_nan_logits_and_wild_token_ids_stay_in_bounds():
     code, a, _, _ = native.read_error()
     assert code == 2 and a == 1          # bounds error raised by the embedding gather
     assert native.read_error()[0] == 0   # reading clears it
+
+
+@pytest.mark.parametrize("d,nk,nv", [(128, 2, 4), (64, 2, 2)])
+def test_gdn_chunk_parallel_scan_matches_serial_scan_and_oracle(d, nk, nv):
+    """The chunk-parallel prefill scan against the token-by-token scan kernel (same inputs, same
+    start states; fp32 reassociation only) and against the fp32 oracle: ragged prompt lengths, a
+    second prefill tick that continues from non-zero states, full and partial chunks."""
+    from tilerl_b200.batch import Batch
+    from tilerl_b200.config import ModelConfig, GDN
+    from tilerl_b200.factory import make_ops
+    from tilerl_b200.kv import GdnStatePool
+    from tilerl_b200.ops.backend import RefOps
+    ops = make_ops("cuda")
+    cfg = ModelConfig("t", hidden=64, ffn=64, vocab=64, layer_types=(GDN,), n_q_heads=2, n_kv_heads=1,
+                      head_dim=64, rotary_dim=64, rope_theta=1e6, gdn_k_heads=nk, gdn_v_heads=nv,
+                      gdn_head_dim=d)
+    g = torch.Generator().manual_seed(d + nv)
+    lp = dict(conv=(torch.randn(cfg.gdn_conv_dim, 4, generator=g) * 0.3).to(DEV),
+              dt_bias=torch.rand(nv, generator=g).to(DEV), a_log=torch.log(1 + 3 * torch.rand(nv, generator=g)).to(DEV),
+              gdn_norm=(1 + 0.1 * torch.randn(d, generator=g)).to(DEV))
+    lens1, lens2 = (70, 16, 5, 33), (48, 7, 20, 64)
+    pools = {k: GdnStatePool(cfg, 6, DEV, planes=1, ring_dtype=torch.bfloat16) for k in ("wy", "serial", "ref")}
+    try:
+        for tick, lens in enumerate((lens1, lens2)):
+            starts = (0, 0, 0, 0) if tick == 0 else lens1
+            seqs = [dict(tokens=[0] * n, start=s, blocks=list(range(1 + 16 * i, 17 + 16 * i)), slot=i + 1)
+                    for i, (n, s) in enumerate(zip(lens, starts))]
+            batch = Batch.build(seqs, DEV)
+            inp = torch.randn(batch.n_tokens, cfg.gdn_in_rows, generator=g).to(DEV, torch.bfloat16)
+            want = RefOps().gdn(inp, lp, batch, pools["ref"], 0, cfg, nk, nv).float()
+            ops.lib.trl_gdn_set_wy(0)
+            serial = ops.gdn(inp, lp, batch, pools["serial"], 0, cfg, nk, nv).float().clone()
+            ops.lib.trl_gdn_set_wy(1)
+            got = ops.gdn(inp, lp, batch, pools["wy"], 0, cfg, nk, nv).float().clone()
+            assert _rel(got, want) < 2e-2
+            assert _rel(got, serial) < 2e-3                      # bf16 outputs: at most a rounding flip
+            assert _rel(pools["wy"].states, pools["serial"].states) < 1e-5
+            assert _rel(pools["wy"].states, pools["ref"].states) < 1e-3
+            assert torch.equal(pools["wy"].ring, pools["serial"].ring)
+    finally:
+        ops.lib.trl_gdn_set_wy(1)
+    from tilerl_b200.ops import native
+    assert native.read_error()[0] == 0
