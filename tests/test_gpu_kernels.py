@@ -520,6 +520,6 @@ def test_gdn_chunk_parallel_scan_matches_serial_scan_and_oracle(d, nk, nv):
             assert _rel(pools["wy"].states, pools["ref"].states) < 1e-3
             assert torch.equal(pools["wy"].ring, pools["serial"].ring)
     finally:
-        ops.lib.trl_gdn_set_wy(1)
+        ops.lib.trl_gdn_set_wy(0)      # the default path
     from tilerl_b200.ops import native
     assert native.read_error()[0] == 0
