@@ -358,7 +358,12 @@ struct NucShared {
   unsigned long long need;
   unsigned long long total;
   int pick;
+  int ncand;
+  float cd[1024];                 // candidates of the small path: distance below the maximum,
+  int ci[1024];                   // vocabulary index,
+  unsigned long long cm[1024];    // integer mass
 };
+constexpr int NUC_CAP = 1024;
 
 // Sum of one value per thread over the CTA (all threads get the result).
 __device__ __forceinline__ unsigned long long nuc_block_sum(NucShared& sh, unsigned long long v, int tid) {
@@ -378,6 +383,47 @@ __device__ __forceinline__ unsigned long long nuc_block_sum(NucShared& sh, unsig
 
 // Smallest 24-bit key t such that the weight (count or mass) of {q <= t, q <= qcap} reaches `need`
 // (0xFFFFFF when the whole row does not reach it).
+// Warp 0 scans the 256-bin histogram for the bin where the running weight reaches `need` and
+// leaves the extended prefix in sh.sel and the weight still wanted inside that bin in sh.need.
+__device__ __forceinline__ void nuc_pick(NucShared& sh, unsigned prefix, unsigned long long need, int tid) {
+  if (tid < 32) {
+    unsigned long long loc[8], run = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      loc[j] = sh.hist[tid * 8 + j];
+      run += loc[j];
+    }
+    unsigned long long incl = run;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned long long n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (tid >= o) incl += n;
+    }
+    const unsigned long long excl = incl - run;
+    const bool has = excl < need && incl >= need;
+    const unsigned ball = __ballot_sync(0xffffffffu, has);
+    if (ball == 0u) {
+      if (tid == 0) {
+        sh.sel = (prefix << 8) | 255u;
+        sh.need = need;
+      }
+    } else if (has) {
+      unsigned long long cum = excl;
+      int b = 7;
+      bool found = false;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (!found) {
+          if (j == 7 || cum + loc[j] >= need) b = j, found = true;
+          else cum += loc[j];
+        }
+      }
+      sh.sel = (prefix << 8) | (unsigned)(tid * 8 + b);
+      sh.need = need - cum;
+    }
+  }
+}
+
 __device__ unsigned nuc_select(NucShared& sh, const float* __restrict__ lg, float it, float mx, int V, bool by_mass,
                                unsigned long long need, unsigned qcap, int tid) {
   unsigned prefix = 0;
@@ -395,42 +441,7 @@ __device__ unsigned nuc_select(NucShared& sh, const float* __restrict__ lg, floa
       if (w) atomicAdd(&sh.hist[(q >> shift) & 255u], w);
     }
     __syncthreads();
-    if (tid < 32) {
-      unsigned long long loc[8], run = 0;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        loc[j] = sh.hist[tid * 8 + j];
-        run += loc[j];
-      }
-      unsigned long long incl = run;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const unsigned long long n = __shfl_up_sync(0xffffffffu, incl, o);
-        if (tid >= o) incl += n;
-      }
-      const unsigned long long excl = incl - run;
-      const bool has = excl < need && incl >= need;
-      const unsigned ball = __ballot_sync(0xffffffffu, has);
-      if (ball == 0u) {
-        if (tid == 0) {
-          sh.sel = (prefix << 8) | 255u;
-          sh.need = need;
-        }
-      } else if (has) {
-        unsigned long long cum = excl;
-        int b = 7;
-        bool found = false;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          if (!found) {
-            if (j == 7 || cum + loc[j] >= need) b = j, found = true;
-            else cum += loc[j];
-          }
-        }
-        sh.sel = (prefix << 8) | (unsigned)(tid * 8 + b);
-        sh.need = need - cum;
-      }
-    }
+    nuc_pick(sh, prefix, need, tid);
     __syncthreads();
     prefix = sh.sel;
     need = sh.need;
@@ -467,6 +478,73 @@ sample_nucleus_kernel(const float* __restrict__ logits, int ld, const int* __res
   const float p = top_p[b];
   unsigned qcut = 0xFFFFFFu;
   if (k > 0 && k < V) qcut = nuc_select(sh, lg, it, mx, V, false, (unsigned long long)k, 0xFFFFFFu, tid);
+  if (k > 0 && k < V && k <= NUC_CAP / 2) {
+    // Small path (the served default, top_k of a few tens): the tokens that survive top-k are
+    // compacted into shared memory in one pass and everything after that (normaliser, nucleus
+    // bound, draw) runs over those few entries instead of over the vocabulary again.  The
+    // compaction order is not deterministic, so nothing below depends on it: sums are integer,
+    // and the inverse CDF runs in vocabulary-index order.
+    if (tid == 0) sh.ncand = 0;
+    __syncthreads();
+    for (int i = tid; i < V; i += 1024) {
+      const float d = mx - lg[i] * it;
+      if (nuc_key(d) <= qcut) {
+        const int pos = atomicAdd(&sh.ncand, 1);
+        if (pos < NUC_CAP) sh.cd[pos] = d, sh.ci[pos] = i;
+      }
+    }
+    __syncthreads();
+    const int n = sh.ncand;
+    if (n <= NUC_CAP) {
+      const bool valid = tid < n;
+      const float my_d = valid ? sh.cd[tid] : 0.f;
+      const unsigned my_q = valid ? nuc_key(my_d) : 0xFFFFFFu;
+      const unsigned long long my_m = valid ? nuc_mass(my_d, my_q) : 0ull;
+      const int my_i = valid ? sh.ci[tid] : 0x7fffffff;
+      unsigned qp = 0xFFFFFFu;
+      if (p < 1.f) {
+        const unsigned long long z = nuc_block_sum(sh, my_m, tid);
+        unsigned long long want = (unsigned long long)((double)fmaxf(p, 0.f) * (double)z);
+        if (want < 1ull) want = 1ull;
+        unsigned prefix = 0;
+        for (int pass = 0; pass < 3; ++pass) {   // the same radix select, over the candidates
+          const int shift = 16 - 8 * pass;
+          __syncthreads();
+          if (tid < 256) sh.hist[tid] = 0ull;
+          __syncthreads();
+          if (my_m && (pass == 0 || (my_q >> (shift + 8)) == prefix)) atomicAdd(&sh.hist[(my_q >> shift) & 255u], my_m);
+          __syncthreads();
+          nuc_pick(sh, prefix, want, tid);
+          __syncthreads();
+          prefix = sh.sel;
+          want = sh.need;
+        }
+        qp = prefix;
+      }
+      const bool kept = valid && my_m > 0ull && my_q <= qp;
+      const unsigned long long total = nuc_block_sum(sh, kept ? my_m : 0ull, tid);
+      __syncthreads();
+      sh.cm[tid] = kept ? my_m : 0ull;
+      if (!valid) sh.ci[tid] = 0x7fffffff;
+      if (tid == 0) sh.pick = -1;
+      __syncthreads();
+      if (total == 0ull) {
+        if (tid == 0) out_tok[b] = 0, out_lp[b] = 0.f;
+        return;
+      }
+      unsigned long long target = (unsigned long long)((double)sample_u01((unsigned long long)seeds[b]) * (double)total);
+      if (target >= total) target = total - 1ull;
+      if (kept) {
+        unsigned long long before = 0ull;      // mass of the kept candidates with a smaller index
+        for (int c = 0; c < n; ++c) before += sh.ci[c] < my_i ? sh.cm[c] : 0ull;
+        if (target >= before && target < before + my_m) {   // exactly one candidate
+          out_tok[b] = my_i;
+          out_lp[b] = logf((float)my_m) - logf((float)total);
+        }
+      }
+      return;
+    }
+  }
   if (p < 1.f) {
     unsigned long long z = 0;
     for (int i = tid; i < V; i += 1024) {
