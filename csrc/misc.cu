@@ -364,6 +364,7 @@ struct NucShared {
   unsigned long long cm[1024];    // integer mass
 };
 constexpr int NUC_CAP = 1024;
+constexpr int NUC_U = 8;   // vocabulary loads in flight per thread in every pass (the passes are latency-bound otherwise)
 
 // Sum of one value per thread over the CTA (all threads get the result).
 __device__ __forceinline__ unsigned long long nuc_block_sum(NucShared& sh, unsigned long long v, int tid) {
@@ -432,13 +433,20 @@ __device__ unsigned nuc_select(NucShared& sh, const float* __restrict__ lg, floa
     __syncthreads();
     if (tid < 256) sh.hist[tid] = 0ull;
     __syncthreads();
-    for (int i = tid; i < V; i += 1024) {
-      const float d = mx - lg[i] * it;
-      const unsigned q = nuc_key(d);
-      if (q > qcap) continue;
-      if (pass > 0 && (q >> (shift + 8)) != prefix) continue;
-      const unsigned long long w = by_mass ? nuc_mass(d, q) : 1ull;
-      if (w) atomicAdd(&sh.hist[(q >> shift) & 255u], w);
+    for (int i0 = tid; i0 < V; i0 += NUC_U * 1024) {   // NUC_U loads in flight per thread
+      float x[NUC_U];
+#pragma unroll
+      for (int u = 0; u < NUC_U; ++u) x[u] = i0 + u * 1024 < V ? lg[i0 + u * 1024] : 0.f;
+#pragma unroll
+      for (int u = 0; u < NUC_U; ++u) {
+        if (i0 + u * 1024 >= V) continue;
+        const float d = mx - x[u] * it;
+        const unsigned q = nuc_key(d);
+        if (q > qcap) continue;
+        if (pass > 0 && (q >> (shift + 8)) != prefix) continue;
+        const unsigned long long w = by_mass ? nuc_mass(d, q) : 1ull;
+        if (w) atomicAdd(&sh.hist[(q >> shift) & 255u], w);
+      }
     }
     __syncthreads();
     nuc_pick(sh, prefix, need, tid);
@@ -460,7 +468,13 @@ sample_nucleus_kernel(const float* __restrict__ logits, int ld, const int* __res
   const float* lg = logits + (size_t)rows[b] * ld;
   const float it = inv_temp[b];
   float mx = -INFINITY;
-  for (int i = tid; i < V; i += 1024) mx = fmaxf(mx, lg[i] * it);
+  for (int i0 = tid; i0 < V; i0 += NUC_U * 1024) {
+    float x[NUC_U];
+#pragma unroll
+    for (int u = 0; u < NUC_U; ++u) x[u] = i0 + u * 1024 < V ? lg[i0 + u * 1024] * it : -INFINITY;
+#pragma unroll
+    for (int u = 0; u < NUC_U; ++u) mx = fmaxf(mx, x[u]);
+  }
   mx = warp_max(mx);
   if ((tid & 31) == 0) sh.red[tid >> 5] = mx;
   __syncthreads();
@@ -486,11 +500,17 @@ sample_nucleus_kernel(const float* __restrict__ logits, int ld, const int* __res
     // and the inverse CDF runs in vocabulary-index order.
     if (tid == 0) sh.ncand = 0;
     __syncthreads();
-    for (int i = tid; i < V; i += 1024) {
-      const float d = mx - lg[i] * it;
-      if (nuc_key(d) <= qcut) {
-        const int pos = atomicAdd(&sh.ncand, 1);
-        if (pos < NUC_CAP) sh.cd[pos] = d, sh.ci[pos] = i;
+    for (int i0 = tid; i0 < V; i0 += NUC_U * 1024) {
+      float x[NUC_U];
+#pragma unroll
+      for (int u = 0; u < NUC_U; ++u) x[u] = i0 + u * 1024 < V ? lg[i0 + u * 1024] : 0.f;
+#pragma unroll
+      for (int u = 0; u < NUC_U; ++u) {
+        const float d = mx - x[u] * it;
+        if (i0 + u * 1024 < V && nuc_key(d) <= qcut) {
+          const int pos = atomicAdd(&sh.ncand, 1);
+          if (pos < NUC_CAP) sh.cd[pos] = d, sh.ci[pos] = i0 + u * 1024;
+        }
       }
     }
     __syncthreads();
@@ -547,10 +567,16 @@ sample_nucleus_kernel(const float* __restrict__ logits, int ld, const int* __res
   }
   if (p < 1.f) {
     unsigned long long z = 0;
-    for (int i = tid; i < V; i += 1024) {
-      const float d = mx - lg[i] * it;
-      const unsigned q = nuc_key(d);
-      if (q <= qcut) z += nuc_mass(d, q);
+    for (int i0 = tid; i0 < V; i0 += NUC_U * 1024) {
+      float x[NUC_U];
+#pragma unroll
+      for (int u = 0; u < NUC_U; ++u) x[u] = i0 + u * 1024 < V ? lg[i0 + u * 1024] : 0.f;
+#pragma unroll
+      for (int u = 0; u < NUC_U; ++u) {
+        const float d = mx - x[u] * it;
+        const unsigned q = nuc_key(d);
+        if (i0 + u * 1024 < V && q <= qcut) z += nuc_mass(d, q);
+      }
     }
     z = nuc_block_sum(sh, z, tid);
     unsigned long long want = (unsigned long long)((double)fmaxf(p, 0.f) * (double)z);
@@ -560,10 +586,16 @@ sample_nucleus_kernel(const float* __restrict__ logits, int ld, const int* __res
   }
   // kept mass per thread over its strided elements, exclusive prefix over threads
   unsigned long long mine = 0;
-  for (int i = tid; i < V; i += 1024) {
-    const float d = mx - lg[i] * it;
-    const unsigned q = nuc_key(d);
-    if (q <= qcut) mine += nuc_mass(d, q);
+  for (int i0 = tid; i0 < V; i0 += NUC_U * 1024) {
+    float x[NUC_U];
+#pragma unroll
+    for (int u = 0; u < NUC_U; ++u) x[u] = i0 + u * 1024 < V ? lg[i0 + u * 1024] : 0.f;
+#pragma unroll
+    for (int u = 0; u < NUC_U; ++u) {
+      const float d = mx - x[u] * it;
+      const unsigned q = nuc_key(d);
+      if (i0 + u * 1024 < V && q <= qcut) mine += nuc_mass(d, q);
+    }
   }
   __syncthreads();
   sh.part[tid] = mine;
