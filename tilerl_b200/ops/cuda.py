@@ -361,33 +361,39 @@ class CudaOps:
         return out
 
     def sample_rows(self, logits: torch.Tensor, rows, seeds, temps, top_ks=None, top_ps=None):
-        """Seeded sampling of the listed logits rows on the device (one kernel, one device-to-host
-        copy): plain temperature sampling, or with per-row ``top_ks`` (0 = off) / ``top_ps`` (>= 1 =
-        off) the top-k / nucleus sampler.  Returns ``(tokens, logprobs)`` as Python lists."""
+        """Seeded sampling of the listed logits rows on the device: plain temperature sampling, or
+        with per-row ``top_ks`` (0 = off) / ``top_ps`` (>= 1 = off) the top-k / nucleus sampler.
+        One pinned staging block and one host-to-device copy carry all per-row arguments, one
+        kernel draws every row, one device-to-host copy brings tokens and log-probabilities back.
+        Returns ``(tokens, logprobs)`` as Python lists."""
+        import numpy as np
         n = len(rows)
         nucleus = top_ks is not None and any(k or p < 1.0 for k, p in zip(top_ks, top_ps))
-        meta = torch.tensor([list(rows), [s & 0x7FFFFFFFFFFFFFFF for s in seeds],
-                             list(top_ks) if nucleus else [0] * n], dtype=torch.int64)
-        it = torch.tensor([[1.0 / t for t in temps], list(top_ps) if nucleus else [1.0] * n], dtype=torch.float32)
-        rows_d = meta[0].to(torch.int32).to(self.device, non_blocking=True)
-        seeds_d = meta[1].to(self.device, non_blocking=True)
-        it_d = it.to(self.device, non_blocking=True)
-        out = torch.empty(2, n, dtype=torch.float32, device=self.device)
-        tok = out[0].view(torch.int32)
+        pin = getattr(self, "_samp_pin", None)
+        if pin is None or pin.numel() < 8 * n:
+            pin = self._samp_pin = torch.empty(max(8 * n, 1024), dtype=torch.int32).pin_memory()
+        a = pin.numpy()          # int32 words: [seeds 2n][rows n][1/T n][top_k n][top_p n] | [tokens n][logprobs n]
+        a[:2 * n].view(np.int64)[:] = np.fromiter((s & 0x7FFFFFFFFFFFFFFF for s in seeds), dtype=np.int64, count=n)
+        a[2 * n:3 * n] = np.asarray(rows, dtype=np.int32)
+        a[3 * n:4 * n].view(np.float32)[:] = (1.0 / np.asarray(temps, dtype=np.float64)).astype(np.float32)
+        a[4 * n:5 * n] = np.asarray(top_ks, dtype=np.int32) if nucleus else 0
+        a[5 * n:6 * n].view(np.float32)[:] = np.asarray(top_ps, dtype=np.float32) if nucleus else 1.0
+        dev = torch.empty(8 * n, dtype=torch.int32, device=self.device)
+        dev[:6 * n].copy_(pin[:6 * n], non_blocking=True)
+        base = dev.data_ptr()
+        seeds_p, rows_p, it_p, k_p, p_p = base, base + 8 * n, base + 12 * n, base + 16 * n, base + 20 * n
+        tok_p, lp_p = base + 24 * n, base + 28 * n
         lg = logits if logits.dtype == torch.float32 else logits.float()
         if nucleus:
-            k_d = meta[2].to(torch.int32).to(self.device, non_blocking=True)
-            N.check(self.lib.trl_sample_nucleus(lg.data_ptr(), lg.stride(0), rows_d.data_ptr(), seeds_d.data_ptr(),
-                                                it_d[0].data_ptr(), k_d.data_ptr(), it_d[1].data_ptr(),
-                                                tok.data_ptr(), out[1].data_ptr(), n, lg.shape[1], N.stream()),
-                    "sample_nucleus")
+            N.check(self.lib.trl_sample_nucleus(lg.data_ptr(), lg.stride(0), rows_p, seeds_p, it_p, k_p, p_p,
+                                                tok_p, lp_p, n, lg.shape[1], N.stream()), "sample_nucleus")
         else:
-            N.check(self.lib.trl_sample_softmax(lg.data_ptr(), lg.stride(0), rows_d.data_ptr(), seeds_d.data_ptr(),
-                                                it_d[0].data_ptr(), tok.data_ptr(), out[1].data_ptr(), n,
+            N.check(self.lib.trl_sample_softmax(lg.data_ptr(), lg.stride(0), rows_p, seeds_p, it_p, tok_p, lp_p, n,
                                                 lg.shape[1], N.stream()), "sample_softmax")
         N.count()
-        host = out.cpu()
-        return host[0].view(torch.int32).tolist(), host[1].tolist()
+        pin[6 * n:8 * n].copy_(dev[6 * n:], non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return a[6 * n:7 * n].tolist(), a[7 * n:8 * n].view(np.float32).tolist()
 
     # ---- training / maintenance kernels ------------------------------------------------------
     def quantize_nvfp4_(self, w: torch.Tensor, dst: NVFP4Tensor, keep_tscale: bool = False) -> None:
