@@ -154,6 +154,8 @@ def build_engine(model: HybridModel, ops=None, *, device=None, blocks: Optional[
         else:
             blocks = slots * ((max_ctx + KV_BLOCK - 1) // KV_BLOCK) + 2
     on_gpu = device.type == "cuda"
+    if kv_fp8 and sparse is not None and on_gpu:
+        raise ValueError("sparse page selection reads a bf16 KV pool on the device: use --kv-format bf16 with --sparse-k")
     kv = PagedKvPool(cfg, blocks, device, dtype=torch.bfloat16 if on_gpu else torch.float32, n_kv_heads=d.n_kv,
                      fp8=kv_fp8)
     st = GdnStatePool(cfg, slots + 1, device, planes=planes,
