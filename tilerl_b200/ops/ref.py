@@ -501,3 +501,53 @@ def sample(logits_row, temperature: float, top_p: float, top_k: int, seed: int,
     gen.manual_seed(seed)
     tok = int(torch.multinomial(probs.cpu(), 1, generator=gen))
     return tok, float(torch.log(probs[tok]))
+
+
+def sample_nucleus_model(logits_row, temperature: float, top_k: int, top_p: float, u: float):
+    """Executable model of the device top-k / top-p sampler (``csrc/misc.cu``:
+    ``sample_nucleus_kernel``), which never sorts: every logit is keyed by its distance below the
+    row maximum in 2^-19 nat steps (24 bits, clamped) and weighted by an integer mass
+    ``exp(-distance) * 2^40``; the k-th key and the nucleus bound are the smallest keys whose
+    cumulative count / mass reaches ``k`` / ``top_p * Z``; the draw is the inverse CDF at ``u`` over
+    the kept masses in vocabulary order.  Returns ``(kept mask, token, logprob)``.  The kept set
+    equals :func:`sample`'s (up to keys closer than 2^-19 nat, which are kept together)."""
+    import numpy as np
+    s = (np.asarray(logits_row, dtype=np.float32) * np.float32(1.0 / temperature)).astype(np.float32)
+    d = (s.max() - s).astype(np.float32)
+    qf = d * np.float32(524288.0)
+    q = np.where((qf >= 16777215.0) | np.isnan(qf), 0xFFFFFF, qf.astype(np.int64))
+    m = np.where(q == 0xFFFFFF, 0, (np.exp(-d.astype(np.float64)).astype(np.float32) * np.float32(2.0 ** 40)).astype(np.int64))
+
+    def select(weight, need, qcap):
+        """Smallest key t with weight{q <= t, q <= qcap} >= need, by three 8-bit digits."""
+        prefix = 0
+        for ps in range(3):
+            shift = 16 - 8 * ps
+            ok = q <= qcap
+            if ps:
+                ok &= (q >> (shift + 8)) == prefix
+            hist = np.zeros(256, dtype=np.int64)
+            np.add.at(hist, (q[ok] >> shift) & 255, weight[ok])
+            cum, b = 0, 255
+            for j in range(256):
+                if cum + hist[j] >= need:
+                    b, need = j, need - cum
+                    break
+                cum += hist[j]
+            prefix = (prefix << 8) | b
+        return prefix
+
+    v = s.shape[0]
+    qcut = 0xFFFFFF
+    if 0 < top_k < v:
+        qcut = select(np.ones(v, dtype=np.int64), top_k, 0xFFFFFF)
+    if top_p < 1.0:
+        z = int(m[q <= qcut].sum())
+        qcut = min(qcut, select(m, max(1, int(top_p * float(z))), qcut))
+    kept = (q <= qcut) & (m > 0)
+    mm = np.where(kept, m, 0)
+    cs = np.cumsum(mm)
+    total = int(cs[-1])
+    target = min(total - 1, int(u * float(total)))
+    tok = int(np.searchsorted(cs, target, side="right"))
+    return torch.from_numpy(kept), tok, float(np.log(mm[tok] / total))
