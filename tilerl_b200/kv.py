@@ -78,8 +78,11 @@ class PagedKvPool:
     def __del__(self):
         pg = getattr(self, "_pager", None)
         if pg is not None:
-            pg[0].trl_pager_destroy(pg[1])
             self._pager = None
+            try:
+                pg[0].trl_pager_destroy(pg[1])
+            except Exception:  # noqa: BLE001 - interpreter shutdown: the library may be gone already
+                pass
 
     # ---- allocator -----------------------------------------------------------
     @property
