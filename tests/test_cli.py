@@ -29,6 +29,12 @@ def test_bench_kernels_table(capsys):
     assert "gate_up" in out and "bound" in out.lower()
 
 
+def test_bench_registry_lists_the_support_matrix(capsys):
+    assert cli.main(["bench", "--registry"]) == 0
+    out = capsys.readouterr().out
+    assert "gemm_nvfp4_kernel" in out and "sm100" in out and "ref.py" in out
+
+
 def test_bench_runs_tiny(capsys):
     assert cli.main(["bench", "--model", "tiny", "--device", "cpu", "--prompt-len", "16", "--gen", "4"]) == 0
     rec = json.loads(capsys.readouterr().out.strip().splitlines()[-1])

@@ -88,6 +88,7 @@ def build_parser() -> argparse.ArgumentParser:
     b.add_argument("--gen", type=int, default=64)
     b.add_argument("--batches", default="1")
     b.add_argument("--kernels", action="store_true", help="print the declared cost table and bounds")
+    b.add_argument("--registry", action="store_true", help="print the kernel support matrix (op, precision, target, kernel)")
     b.add_argument("--calibrate", action="store_true", help="measure HBM / GEMM / H2D floors")
     b.add_argument("--tp", type=int, default=1)
     b.add_argument("--record", action="store_true", help="append results to the bench store")
@@ -280,6 +281,13 @@ def cmd_bench(args) -> int:
     if args.calibrate:
         import dataclasses
         print(json.dumps(dataclasses.asdict(calibrate(_device(args)))))
+        return 0
+    if args.registry:
+        from .ops import registry as R
+        print(f"{'op':28s} {'precision':9s} {'target':6s} {'kernel':60s} source")
+        for (precision, arch), table in sorted(R._CELLS.items()):
+            for op, k in sorted(table.items()):
+                print(f"{op:28s} {precision:9s} {arch:6s} {k.name[:60]:60s} {k.source}")
         return 0
     pk = load_peaks()
     if args.kernels:
