@@ -11,7 +11,7 @@ LEVEL = {
     "config": 0, "formats": 0, "tokenizer": 0, "ledger": 0, "recipes": 0, "benchrec": 0, "build": 0,
     "ops": 1, "tape": 1, "parallel": 1, "models": 1, "optim": 1,
     "batch": 2, "kv": 2, "kv_tiers": 2, "sparse": 2, "spec": 2, "graph": 2, "memory": 2, "kernel_cost": 2,
-    "calibration": 2, "checkpoint": 2, "merge": 2,
+    "calibration": 2, "checkpoint": 2, "merge": 2, "mega": 2,
     "sparse_index": 3, "engine": 3,
     "factory": 4, "evals": 4, "server": 4,
     "generate": 5, "rl": 5,
