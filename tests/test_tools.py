@@ -105,3 +105,17 @@ def test_offline_generate_and_eval(tmp_path):
     eng = make_engine(tiny())
     res = evals.evaluate(eng, ByteTokenizer(), [{"question": "1+1?", "answer": "2"}], max_tokens=4)
     assert res["n"] == 1 and 0.0 <= res["accuracy"] <= 1.0
+
+
+def test_committed_measurements_pass_the_schema_and_their_floors():
+    """bench/measurements.jsonl (the numbers quoted in BASELINE.md as records): every line
+    validates, none beats its physical floor, and the headline shapes are present."""
+    import os
+    from tilerl_b200 import benchrec as B
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench", "measurements.jsonl")
+    recs = B.load(path)
+    assert len(recs) >= 20
+    for r in recs:
+        assert B.validate(r)["status"] == "ok", r
+    dec = [r for r in recs if r["metric"] == "decode_tok_s" and r["shape"]["tp"] == 1]
+    assert dec and dec[0]["floor"] > dec[0]["value"] > 92.4      # above the reference's published figure
