@@ -108,7 +108,7 @@ def test_offline_generate_and_eval(tmp_path):
 
 
 def test_committed_measurements_pass_the_schema_and_their_floors():
-    """bench/measurements.jsonl (the numbers quoted in BASELINE.md as records): every line
+    """bench/measurements.jsonl (the measured figures of this build as records): every line
     validates, none beats its physical floor, and the headline shapes are present."""
     import os
     from tilerl_b200 import benchrec as B
