@@ -54,3 +54,33 @@ def test_spec_with_chunked_prefill_and_prefix_cache():
     assert [r.tokens for r in eng.generate(prompts, sp)] == want
     assert [r.tokens for r in eng.generate(prompts, sp)] == want     # second pass: prefix hits
     assert eng.prefix.hits == 2
+
+
+def test_drafter_checkpoint_round_trip(tmp_path):
+    """A saved drafter loads back with identical tensors and proposes the same drafts, so serving
+    with it gives the same counters; a drafter for another trunk width is refused."""
+    import pytest
+    from tilerl_b200.config import tiny
+    from tilerl_b200.models.hybrid import HybridModel
+    from tilerl_b200.spec import BlockDrafterConfig, load_drafter, save_drafter
+    cfg = tiny_hybrid()
+    prompts = rand_prompts(cfg, 2, 20, seed=4)
+    sp = SamplingParams(max_tokens=12)
+    want, base = _run(cfg, prompts, sp)
+    model = base.model
+    for name, d in (("block", BlockDrafter(model, BlockDrafterConfig(width=4, n_layers=1), seed=5)),
+                    ("chain", ChainDrafter(model, seed=5))):
+        path = str(tmp_path / name)
+        save_drafter(d, path)
+        d2 = load_drafter(model, path)
+        assert type(d2) is type(d) and d2.aux_layers == d.aux_layers
+        if name == "block":
+            assert all(torch.equal(d.p[k], d2.p[k]) for k in d.p)
+        got1, e1 = _run(cfg, prompts, sp, drafter=d, width=4, model=model)
+        got2, e2 = _run(cfg, prompts, sp, drafter=d2, width=4, model=model)
+        assert got1 == got2 == want
+        assert e1.counters["spec_accepted"] == e2.counters["spec_accepted"]
+    other = HybridModel.build_random(tiny(), seed=0)
+    if other.cfg.hidden != cfg.hidden:
+        with pytest.raises(ValueError):
+            load_drafter(other, str(tmp_path / "block"))

@@ -38,6 +38,7 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--no-decode-graph", dest="graph", action="store_false")
     s.add_argument("--no-prefix", action="store_true")
     s.add_argument("--draft", default=None, choices=[None, "block", "chain"])
+    s.add_argument("--draft-checkpoint", default=None, help="directory written by spec.save_drafter (kind is read from it)")
     s.add_argument("--spec-width", type=int, default=8)
     s.add_argument("--sparse-k", type=int, default=0)
     s.add_argument("--sparse-min-tokens", type=int, default=4096)
@@ -127,7 +128,7 @@ def cmd_serve(args) -> int:
     cfg = get_config(args.model)
     if args.dry_run:
         p = memory.plan(cfg, slots=args.slots, blocks=args.blocks, max_batched_tokens=args.max_batched_tokens,
-                        planes=args.spec_width if args.draft else 1, kv_fp8=args.kv_format == "fp8")
+                        planes=args.spec_width if (args.draft or args.draft_checkpoint) else 1, kv_fp8=args.kv_format == "fp8")
         print(memory.memory_table(p))
         return 0
     from .engine import StepLimits
@@ -144,7 +145,10 @@ def cmd_serve(args) -> int:
     ops = make_ops(dev)
     model = build_model(cfg, dev, seed=args.seed, checkpoint=args.checkpoint, ops=ops if dev != "cpu" else None)
     drafter = None
-    if args.draft:
+    if args.draft_checkpoint:
+        from .spec import load_drafter
+        drafter = load_drafter(model, args.draft_checkpoint)
+    elif args.draft:
         from .spec import BlockDrafter, ChainDrafter
         drafter = BlockDrafter(model) if args.draft == "block" else ChainDrafter(model)
     sparse = None

@@ -234,3 +234,60 @@ class ConstantDrafter:
 
     def release(self, rid: int) -> None:
         pass
+
+
+# ---- drafter checkpoints -------------------------------------------------------------------------
+def save_drafter(drafter, path: str) -> None:
+    """Writes a block or chain drafter as ``<path>/drafter.safetensors`` plus ``drafter.json``
+    (kind, shape-defining config, tap layers)."""
+    import dataclasses
+    import json
+    import os
+    from safetensors.torch import save_file
+    os.makedirs(path, exist_ok=True)
+    if isinstance(drafter, BlockDrafter):
+        tensors = {k: v.detach().cpu().contiguous() for k, v in drafter.p.items()}
+        meta = {"kind": "block", "config": dataclasses.asdict(drafter.cfg), "aux_layers": list(drafter.aux_layers)}
+    elif isinstance(drafter, ChainDrafter):
+        tensors = {k: getattr(drafter, k).detach().cpu().contiguous() for k in ("fc", "mix", "n1", "n2")}
+        meta = {"kind": "chain", "aux_layers": list(drafter.aux_layers)}
+    else:
+        raise TypeError(f"{type(drafter).__name__} has no parameters to save")
+    meta["hidden"] = int(drafter.model.cfg.hidden)
+    save_file(tensors, os.path.join(path, "drafter.safetensors"))
+    with open(os.path.join(path, "drafter.json"), "w") as f:
+        json.dump(meta, f)
+
+
+def load_drafter(model, path: str, dtype=torch.float32):
+    """The drafter saved by :func:`save_drafter`, bound to ``model`` (its embedding and lm_head) on
+    the model's device.  Refuses a drafter trained for another trunk width or tensor shapes that do
+    not match the recorded config.
+    Parity: reference ``src/tilerl/spec.py:863`` (``load_draft``) and ``:1148`` (``load_dflash2``)."""
+    import json
+    import os
+    from safetensors.torch import load_file
+    with open(os.path.join(path, "drafter.json")) as f:
+        meta = json.load(f)
+    if meta.get("hidden") != int(model.cfg.hidden):
+        raise ValueError(f"drafter was built for hidden size {meta.get('hidden')}, the model has {model.cfg.hidden}")
+    tensors = load_file(os.path.join(path, "drafter.safetensors"))
+    dev = model.params["embed"].device
+    if meta["kind"] == "block":
+        d = BlockDrafter(model, BlockDrafterConfig(**meta["config"]), dtype=dtype)
+        if set(tensors) != set(d.p):
+            raise ValueError("drafter checkpoint does not hold the tensors of its recorded config")
+        for k, v in tensors.items():
+            if tuple(v.shape) != tuple(d.p[k].shape):
+                raise ValueError(f"drafter tensor {k} has shape {tuple(v.shape)}, expected {tuple(d.p[k].shape)}")
+            d.p[k] = v.to(dev, dtype)
+    elif meta["kind"] == "chain":
+        d = ChainDrafter(model, dtype=dtype)
+        for k in ("fc", "mix", "n1", "n2"):
+            if tuple(tensors[k].shape) != tuple(getattr(d, k).shape):
+                raise ValueError(f"drafter tensor {k} has the wrong shape")
+            setattr(d, k, tensors[k].to(dev, dtype))
+    else:
+        raise ValueError(f"unknown drafter kind {meta['kind']!r}")
+    d.aux_layers = tuple(meta["aux_layers"])
+    return d
