@@ -89,3 +89,14 @@ def test_train_adapters_with_evals_and_best_adapter(tmp_path, capsys):
     assert rec["steps"] == 3 and len(rec["evals"]) == 3 and rec["best_eval"] is not None
     assert os.path.exists(os.path.join(out, "adapter.safetensors"))
     assert os.path.exists(os.path.join(out, "adapter-best.safetensors"))
+
+
+def test_train_deterministic_flag_repeats_the_run(capsys, tmp_path, monkeypatch):
+    """Two runs of the tiny GRPO recipe with --deterministic log the same losses."""
+    monkeypatch.setenv("TRL_RUNS", str(tmp_path))
+    outs = []
+    for _ in range(2):
+        assert cli.main(["train", "--recipe", "grpo-tiny-smoke", "--device", "cpu", "--deterministic", "--steps", "2"]) == 0
+        lines = [json.loads(ln) for ln in capsys.readouterr().out.splitlines() if ln.startswith("{")]
+        outs.append([(ln.get("loss"), ln.get("reward_mean")) for ln in lines if "loss" in ln])
+    assert outs[0] and outs[0] == outs[1]

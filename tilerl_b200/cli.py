@@ -77,6 +77,8 @@ def build_parser() -> argparse.ArgumentParser:
     t.add_argument("--save-model", default=None)
     t.add_argument("--load-adapter", default=None)
     t.add_argument("--served-fp4", action="store_true")
+    t.add_argument("--deterministic", action="store_true",
+                   help="deterministic torch algorithms and fixed seeds (repeatable runs, slower)")
     t.add_argument("--indexer-warmup", action="store_true", help="train the learned sparse-KV page indexer")
     t.add_argument("--ctx", type=int, default=None, help="sequence length of the indexer warm-up batches")
     t.add_argument("--eval-every", type=int, default=0, help="adapter runs: eval reward on held-out prompts every N steps")
@@ -190,6 +192,10 @@ def cmd_train(args) -> int:
     from .ledger import Run
     from .optim import make_optimizer
     from .recipes import expand
+    if getattr(args, "deterministic", False):
+        os.environ.setdefault("CUBLAS_WORKSPACE_CONFIG", ":4096:8")
+        torch.use_deterministic_algorithms(True, warn_only=True)
+        torch.manual_seed(int(getattr(args, "seed", 0) or 0))
     over = {k: getattr(args, k) for k in ("steps", "group", "prompts_per_step", "max_tokens", "micro", "lora_rank",
                                           "lr", "optim", "reward")}
     if args.indexer_warmup:
