@@ -46,6 +46,9 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--sparse-refresh-ticks", type=int, default=8)
     s.add_argument("--kv-format", default="bf16", choices=["bf16", "fp8"],
                    help="KV pool format: bf16, or e4m3 with one fp32 scale per token and head")
+    s.add_argument("--kv-fp8", dest="kv_format", action="store_const", const="fp8", help="same as --kv-format fp8")
+    s.add_argument("--device-reserve-mib", type=int, default=0,
+                   help="device memory left out of the KV pool sizing (other tenants of the GPU, fragmentation)")
     s.add_argument("--kv-store", default=None, help="directory of the cold-start KV store")
     s.add_argument("--kv-cold-bytes", type=int, default=0, help="pinned host bytes for demoted prefix pages (0: off)")
     s.add_argument("--dram-bytes", type=int, default=1 << 30, help="host bytes for demoted GDN snapshots")
@@ -162,6 +165,7 @@ def cmd_serve(args) -> int:
     eng = build_engine(model, ops, device=dev, blocks=args.blocks, slots=args.slots, max_ctx=args.max_ctx,
                        prefix=not args.no_prefix, graph=args.graph, spec_width=args.spec_width if drafter else 0,
                        drafter=drafter, sparse=sparse, kv_fp8=args.kv_format == "fp8",
+                       reserve_bytes=args.device_reserve_mib << 20,
                        limits=StepLimits(args.max_batch, args.max_batched_tokens, max_inflight=args.max_inflight),
                        eos_id=tok.eos_id, detokenize=tok.decode, think_ids=getattr(tok, "think_ids", None))
     if args.kv_cold_bytes and hasattr(eng.prefix, "host"):

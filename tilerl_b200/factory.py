@@ -135,7 +135,7 @@ def make_ops(device, tp_comm=None):
 def build_engine(model: HybridModel, ops=None, *, device=None, blocks: Optional[int] = None, slots: int = 8,
                  max_ctx: int = 4096, prefix: bool = True, graph: bool = True, spec_width: int = 0,
                  drafter=None, limits: Optional[StepLimits] = None, sparse=None, kv_fp8: bool = False,
-                 **engine_kw) -> Engine:
+                 reserve_bytes: int = 0, **engine_kw) -> Engine:
     cfg = model.cfg
     if device is None:
         e = model.params["embed"]
@@ -149,6 +149,7 @@ def build_engine(model: HybridModel, ops=None, *, device=None, blocks: Optional[
     if blocks is None:
         if device.type == "cuda":
             free, _ = torch.cuda.mem_get_info(device)
+            free = max(0, free - int(reserve_bytes))
             blocks = fit_blocks(cfg, free, slots, planes=planes, tp=model.tp, kv_fp8=kv_fp8,
                                 max_blocks=slots * ((max_ctx + KV_BLOCK - 1) // KV_BLOCK) + 2)
         else:
