@@ -100,3 +100,10 @@ def test_train_deterministic_flag_repeats_the_run(capsys, tmp_path, monkeypatch)
         lines = [json.loads(ln) for ln in capsys.readouterr().out.splitlines() if ln.startswith("{")]
         outs.append([(ln.get("loss"), ln.get("reward_mean")) for ln in lines if "loss" in ln])
     assert outs[0] and outs[0] == outs[1]
+
+
+def test_serve_learned_scorer_needs_an_indexer_checkpoint():
+    import pytest
+    with pytest.raises(SystemExit) as e:
+        cli.main(["serve", "--model", "tiny", "--device", "cpu", "--sparse-k", "4", "--scorer", "learned"])
+    assert "--indexer" in str(e.value)

@@ -41,6 +41,9 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--draft-checkpoint", default=None, help="directory written by spec.save_drafter (kind is read from it)")
     s.add_argument("--spec-width", type=int, default=8)
     s.add_argument("--sparse-k", type=int, default=0)
+    s.add_argument("--scorer", default="quest", choices=["quest", "learned"],
+                   help="sparse page scores: Quest min/max bounds, or the learned indexer")
+    s.add_argument("--indexer", default=None, help="directory holding indexer.safetensors (for --scorer learned)")
     s.add_argument("--sparse-min-tokens", type=int, default=4096)
     s.add_argument("--sparse-window-tokens", type=int, default=128)
     s.add_argument("--sparse-refresh-ticks", type=int, default=8)
@@ -159,8 +162,17 @@ def cmd_serve(args) -> int:
     sparse = None
     if args.sparse_k:
         from .sparse import SparseConfig, SparseKV
+        indexer = None
+        if args.scorer == "learned":
+            # the page indexer trained by `train --indexer-warmup --save-model DIR` replaces the Quest bound
+            if not args.indexer:
+                raise SystemExit("--scorer learned needs --indexer DIR (written by train --indexer-warmup --save-model)")
+            from safetensors.torch import load_file
+            from .sparse_index import LearnedIndexer
+            indexer = LearnedIndexer(cfg, device=dev, n_q=model.dims.n_q)
+            indexer.load_state_dict(load_file(os.path.join(args.indexer, "indexer.safetensors")))
         sparse = SparseKV(cfg, SparseConfig(args.sparse_k, max(1, args.sparse_window_tokens // 16),
-                                            args.sparse_refresh_ticks, args.sparse_min_tokens))
+                                            args.sparse_refresh_ticks, args.sparse_min_tokens), indexer=indexer)
     tok = load_tokenizer(args.tokenizer, cfg.vocab)
     eng = build_engine(model, ops, device=dev, blocks=args.blocks, slots=args.slots, max_ctx=args.max_ctx,
                        prefix=not args.no_prefix, graph=args.graph, spec_width=args.spec_width if drafter else 0,
