@@ -147,3 +147,36 @@ def test_poisoned_pools_give_the_same_tokens():
                 t.fill_(float("nan"))
         outs.append([r.tokens for r in eng.generate(prompts, SamplingParams(max_tokens=10))])
     assert outs[0] == outs[1]
+
+
+def test_batched_sampler_seam_gets_every_sampling_row_of_a_tick():
+    """A backend that offers ``sample_rows`` receives, in one call per tick, every row that samples
+    (plain temperature, top-k, top-p) with its seed stream and restrictions; greedy rows and rows
+    with an allowed-id list stay on their own paths; tokens equal the per-row host sampler's."""
+    from tilerl_b200.engine import SamplingParams
+    from tilerl_b200.ops import ref
+    from tilerl_b200.ops.backend import RefOps
+
+    calls = []
+
+    class Ops(RefOps):
+        def sample_rows(self, logits, rows, seeds, temps, top_ks=None, top_ps=None):
+            calls.append((list(rows), list(top_ks), list(top_ps)))
+            out = [ref.sample(logits[r].detach().float().cpu(), t, p, k, s)
+                   for r, s, t, k, p in zip(rows, seeds, temps, top_ks, top_ps)]
+            return [o[0] for o in out], [o[1] for o in out]
+
+    cfg = tiny_hybrid()
+    prompts = rand_prompts(cfg, 4, 9)
+    params = [SamplingParams(max_tokens=6, temperature=1.0, seed=1),
+              SamplingParams(max_tokens=6, temperature=0.8, top_k=5, top_p=0.9, seed=2),
+              SamplingParams(max_tokens=6),
+              SamplingParams(max_tokens=6, temperature=1.0, allowed_ids=(1, 2, 3, 4), seed=3)]
+    want = [r.tokens for r in make_engine(cfg).generate(prompts, params)]
+    eng = make_engine(cfg)
+    eng.ops = Ops()
+    got = [r.tokens for r in eng.generate(prompts, params)]
+    assert got == want
+    assert calls and all(len(c[0]) == 2 for c in calls)          # the two sampling rows, never the other two
+    assert all(c[1] == [0, 5] and c[2] == [1.0, 0.9] for c in calls)
+    assert all(t in (1, 2, 3, 4) for t in got[3])
