@@ -1,0 +1,445 @@
+// Streamed NVFP4 GEMV for the decode tick (M <= 2 rows): the weights arrive through a
+// shared-memory ring filled by bulk asynchronous copies, so that
+//
+//   * the first ring fill is issued BEFORE griddepcontrol.wait -- weights do not depend on
+//     the previous kernel -- and DRAM keeps streaming while the predecessor drains and
+//     while this kernel stages its activation row;
+//   * the bytes in flight per SM (CTAs x 8 warps x NS stages of 2304 B) do not cost
+//     registers: the kernel runs at <= 80 registers and 256 threads, three CTAs fit on an
+//     SM, and a grid of two CTAs per SM leaves the third slot to the NEXT kernel of the
+//     stream, whose CTAs start under programmatic dependent launch, fill their rings and
+//     wait.  The fixed cost between two projections of a tick (launch, prologue, first-byte
+//     latency, tail) then overlaps with the neighbours instead of adding to them.
+//
+// The kernel reads a *stream layout* copy of the weight (built once per weight by
+// trl_gemv_stream_pack): rows are taken in pairs and K in steps of 32 chunks of 32
+// weights; one unit = (row pair, step) holds
+//     [n x 16 B row 0][n x 16 B row 1][n x 2 B scales row 0][n x 2 B scales row 1]
+// (n = 32 chunks, fewer in the last step of a row), units of a pair and pairs follow each
+// other without gaps.  A CTA owns a contiguous block of row pairs and its warps split the
+// block's units evenly (the balanced split of gemv_nvfp4_sk_kernel), so every warp streams
+// ONE contiguous byte range, two units (2304 B) per bulk copy: measured on a B200, copies of
+// 1152 B reach 4-5 TB/s of HBM reads, 2304 B and more reach 6 TB/s.
+//
+// Arithmetic is that of gemv.cu: e2m1 -> f16x2 by the native cvt, f16x2 FMA inside a
+// 16-element scale block, fp32 across blocks, per-row power-of-two activation scale.
+//
+// Reference parity: `linear_fp4_gemv` of
+// packages/tilerl-kernels/src/tilerl_kernels/kernels_linear.py:924-978 (register-streamed,
+// twiddled layout); the ring, the layout and the overlap with the neighbouring kernels have
+// no counterpart there.
+#include <stdlib.h>
+
+#include "common.cuh"
+
+enum { EPI2_STORE = 0, EPI2_RESIDUAL = 1, EPI2_SWIGLU = 2, EPI2_STORE_F32 = 3, EPI2_PUSH = 4 };
+
+namespace {
+
+constexpr int G2_THREADS = 256;
+constexpr int G2_WARPS = G2_THREADS / 32;
+constexpr int G2_MAX_NS = 8;
+constexpr int UNIT_BYTES = 1152;              // full unit: 32 chunks x (16 + 16 + 2 + 2) bytes
+constexpr int STAGE_UNITS = 2;                // units per bulk copy / ring stage
+constexpr int STAGE_BYTES = STAGE_UNITS * UNIT_BYTES;
+constexpr long long G2_WAIT_CYCLES = 4000000000LL;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void g2_mbar_init(uint32_t bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void g2_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t g2_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{ .reg .pred p;\n"
+      "  mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "  selp.u32 %0, 1, 0, p; }\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ void g2_bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+// x (bf16 [M, K], optional RMSNorm) -> shared memory as f16 scaled by a per-row power of two
+// (16 products of |w| <= 6 then stay below the f16 maximum).  Piece p (8 halves) of 32-element
+// chunk c sits at ((p * nchunks + c) * 8) halves: the four 16-byte reads of a chunk are
+// conflict-free across lanes.  xs_inv[m] = 1 / applied scale.
+template <int M>
+__device__ __forceinline__ void g2_stage_x(const bf16* __restrict__ x, int ldx, int K,
+                                           const float* __restrict__ norm_w, float eps, __half* xs,
+                                           float* xs_inv, float* red) {
+  const int nchunks = K >> 5;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+#pragma unroll
+  for (int m = 0; m < M; ++m) {
+    const bf16* xr = x + (size_t)m * ldx;
+    float ss = 0.f, amax = 0.f;
+    for (int k = threadIdx.x * 2; k < K; k += G2_THREADS * 2) {
+      float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(xr + k));
+      ss += v.x * v.x + v.y * v.y;
+      if (norm_w != nullptr) {
+        const float2 nw = *reinterpret_cast<const float2*>(norm_w + k);
+        v.x *= nw.x, v.y *= nw.y;
+      }
+      amax = fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y)));
+    }
+    ss = warp_sum(ss);
+    amax = warp_max(amax);
+    __syncthreads();
+    if (lane == 0) red[w] = ss, red[32 + w] = amax;
+    __syncthreads();
+    ss = warp_sum(lane < G2_WARPS ? red[lane] : 0.f);
+    amax = warp_max(lane < G2_WARPS ? red[32 + lane] : 0.f);
+    float rstd = 1.f;
+    if (norm_w != nullptr) {
+      rstd = rsqrtf(ss / (float)K + eps);
+      amax *= rstd * 1.01f;   // bf16 rounding of the normalised values can add < 0.4 %
+    }
+    int e = 0;
+    if (amax > 0.f) frexpf(amax, &e);   // amax = f * 2^e, f in [0.5, 1)
+    const float s = exp2f((float)(8 - e));
+    if (threadIdx.x == 0) xs_inv[m] = exp2f((float)(e - 8));
+    __half* dst = xs + (size_t)m * K;
+    for (int k = threadIdx.x * 2; k < K; k += G2_THREADS * 2) {
+      float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(xr + k));
+      if (norm_w != nullptr) {
+        const float2 nw = *reinterpret_cast<const float2*>(norm_w + k);
+        v.x = __bfloat162float(__float2bfloat16(v.x * rstd * nw.x));
+        v.y = __bfloat162float(__float2bfloat16(v.y * rstd * nw.y));
+      }
+      const int c = k >> 5, p = (k >> 3) & 3, o = k & 7;
+      *reinterpret_cast<__half2*>(dst + ((size_t)(p * nchunks + c) << 3) + o) = __floats2half2_rn(v.x * s, v.y * s);
+    }
+  }
+  __syncthreads();
+}
+
+__device__ __forceinline__ int g2_owner(int unit, int U, int W) {
+  int w = (int)(((long long)unit * W) / U);
+  while (w + 1 < W && (int)(((long long)(w + 1) * U) / W) <= unit) ++w;
+  while (w > 0 && (int)(((long long)w * U) / W) > unit) --w;
+  return w;
+}
+
+template <int M, int EPI>
+__global__ void __launch_bounds__(G2_THREADS, 3)
+gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ wst,
+             const float* __restrict__ tscale, const float* __restrict__ norm_w, float eps,
+             const bf16* __restrict__ residual, int ldr, void* __restrict__ yout, int ldy, int N, int K,
+             int nslot, int NS, const TrlPushArgs push) {
+  constexpr int W = G2_WARPS;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  // ring [W][NS][STAGE_BYTES] | bars [W][NS] | xs [M][K] f16 | xs_inv[8] | red[64] | slots
+  unsigned char* ring = smem_raw;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)W * NS * STAGE_BYTES);
+  __half* xs = reinterpret_cast<__half*>(reinterpret_cast<unsigned char*>(bars) + W * G2_MAX_NS * 8);
+  float* xs_inv = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(xs) + (size_t)M * K * sizeof(__half));
+  float* red = xs_inv + 8;
+  float* slots = red + 64;   // [pairs_local][2 rows][nslot][M]
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int npairs = N >> 1;
+  const int p_lo = (int)(((long long)blockIdx.x * npairs) / gridDim.x);
+  const int p_hi = (int)(((long long)(blockIdx.x + 1) * npairs) / gridDim.x);
+  const int pl = p_hi - p_lo;
+  const int nchunks = K >> 5;
+  const int nsteps = (nchunks + 31) >> 5;
+  const int nlast = nchunks - 32 * (nsteps - 1);
+  const uint32_t pair_bytes = (uint32_t)nchunks * 36u;
+  const int U = pl * nsteps;
+  const int u0 = (int)(((long long)warp * U) / W), u1 = (int)(((long long)(warp + 1) * U) / W);
+
+  const uint32_t ring_w = smem_addr(ring + (size_t)warp * NS * STAGE_BYTES);
+  const uint32_t bar_w = smem_addr(bars + warp * G2_MAX_NS);
+  // producer cursor (lane 0): byte offset of the next unit and its step index
+  const uint8_t* src = wst + (size_t)p_lo * pair_bytes;
+  uint32_t p_off = (uint32_t)(u0 / nsteps) * pair_bytes + (uint32_t)(u0 % nsteps) * (uint32_t)UNIT_BYTES;
+  int p_step = u0 % nsteps, p_unit = u0, p_slot = 0;
+  auto issue = [&]() {   // one stage: the next STAGE_UNITS units of this warp's range (fewer at its end)
+    uint32_t bytes = 0;
+#pragma unroll
+    for (int g = 0; g < STAGE_UNITS; ++g) {
+      if (p_unit < u1) {
+        bytes += (p_step == nsteps - 1) ? (uint32_t)nlast * 36u : (uint32_t)UNIT_BYTES;
+        if (++p_step == nsteps) p_step = 0;
+        ++p_unit;
+      }
+    }
+    const uint32_t bar = bar_w + 8u * p_slot;
+    g2_expect_tx(bar, bytes);
+    g2_bulk_load(ring_w + (uint32_t)p_slot * STAGE_BYTES, src + p_off, bytes, bar);
+    p_off += bytes;
+    if (++p_slot == NS) p_slot = 0;
+  };
+  if (lane == 0) {
+    for (int s = 0; s < NS; ++s) g2_mbar_init(bar_w + 8u * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // first ring fill: independent of the previous kernel
+    for (int s = 0; s < NS && p_unit < u1; ++s) issue();
+  }
+  for (int i = threadIdx.x; i < pl * 2 * nslot * M; i += G2_THREADS) slots[i] = 0.f;
+  pdl_launch_dependents();
+  pdl_wait();
+  g2_stage_x<M>(x, ldx, K, norm_w, eps, xs, xs_inv, red);   // ends with a block barrier
+
+  bool ok = true;
+  if (u0 < u1) {
+    int cp = u0 / nsteps, cs = u0 % nsteps, slot = 0;
+    uint32_t parity = 0;
+    float acc[2][M];
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+      for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
+    auto flush = [&](int pair_local) {
+      // two-slot mode: slot 0 belongs to the warp that holds the pair's first unit
+      const int sl = nslot == 2 ? (pair_local * nsteps >= u0 ? 0 : 1) : warp - g2_owner(pair_local * nsteps, U, W);
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          const float v = warp_sum(acc[r][m]);
+          if (lane == 0) slots[((size_t)(pair_local * 2 + r) * nslot + sl) * M + m] = v;
+          acc[r][m] = 0.f;
+        }
+    };
+    for (int u = u0; u < u1;) {
+      const uint32_t bar = bar_w + 8u * slot;
+      if (!g2_try_wait(bar, parity)) {
+        const long long t0 = clock64();
+        uint32_t it = 0;
+        while (!g2_try_wait(bar, parity)) {
+          if ((++it & 63) == 0 && clock64() - t0 > G2_WAIT_CYCLES) {
+            trl_set_error(TRL_ERR_MBAR_TIMEOUT, (int)blockIdx.x, 200 + warp, u);
+            ok = false;
+            break;
+          }
+        }
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const unsigned char* ub = ring + ((size_t)warp * NS + slot) * STAGE_BYTES;
+#pragma unroll
+      for (int g = 0; g < STAGE_UNITS; ++g) {
+        if (u >= u1) break;
+        const int n = (cs == nsteps - 1) ? nlast : 32;
+        if (lane < n) {
+          const int c = cs * 32 + lane;
+          uint4 wv[2];
+          uint16_t sv[2];
+          wv[0] = *reinterpret_cast<const uint4*>(ub + lane * 16);
+          wv[1] = *reinterpret_cast<const uint4*>(ub + n * 16 + lane * 16);
+          sv[0] = *reinterpret_cast<const uint16_t*>(ub + n * 32 + lane * 2);
+          sv[1] = *reinterpret_cast<const uint16_t*>(ub + n * 34 + lane * 2);
+#pragma unroll
+          for (int m = 0; m < M; ++m) {
+            uint32_t xh[16];
+            const __half* xm = xs + (size_t)m * K;
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+              const uint4 t = *reinterpret_cast<const uint4*>(xm + ((size_t)(p * nchunks + c) << 3));
+              xh[p * 4 + 0] = t.x, xh[p * 4 + 1] = t.y, xh[p * 4 + 2] = t.z, xh[p * 4 + 3] = t.w;
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+              const float2 sc = h2_to_f2(cvt_e4m3x2_to_h2(sv[r]));
+              const uint32_t w4[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
+#pragma unroll
+              for (int blk = 0; blk < 2; ++blk) {
+                uint32_t a = 0u;  // f16x2 zero
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                  uint32_t h[4];
+                  cvt_e2m1x8_to_h2x4(w4[blk * 2 + q], h);
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) a = hfma2_u(h[i], xh[(blk * 2 + q) * 4 + i], a);
+                }
+                const float2 af = h2_to_f2(a);
+                acc[r][m] = fmaf(blk == 0 ? sc.x : sc.y, af.x + af.y, acc[r][m]);
+              }
+            }
+          }
+        }
+        ub += n * 36;
+        ++u;
+        if (++cs == nsteps) {
+          flush(cp);
+          cs = 0, ++cp;
+        }
+      }
+      __syncwarp();
+      if (lane == 0 && p_unit < u1) issue();   // refill the stage just consumed
+      if (++slot == NS) slot = 0, parity ^= 1u;
+    }
+    if (ok && cs != 0) flush(cp);   // range ended inside a pair
+    if (!ok) {
+      // copies may still be in flight towards this CTA's shared memory: let them land
+      const long long t0 = clock64();
+      while (clock64() - t0 < 2000000LL) {
+      }
+    }
+  }
+  __syncthreads();
+
+  // block-wide epilogue over this CTA's rows
+  const float ts = *tscale;
+  if (EPI == EPI2_SWIGLU) {
+    for (int i = threadIdx.x; i < pl * M; i += G2_THREADS) {
+      const int pr = i / M, m = i % M;
+      float g = 0.f, u = 0.f;
+      for (int sl = 0; sl < nslot; ++sl) {
+        g += slots[((size_t)(pr * 2) * nslot + sl) * M + m];
+        u += slots[((size_t)(pr * 2 + 1) * nslot + sl) * M + m];
+      }
+      const float sc = ts * xs_inv[m];
+      const int n = (p_lo + pr) * 2;
+      reinterpret_cast<bf16*>(yout)[(size_t)m * ldy + (n >> 1)] = __float2bfloat16(silu_f(g * sc) * (u * sc));
+    }
+  } else {
+    for (int i = threadIdx.x; i < pl * 2 * M; i += G2_THREADS) {
+      const int rl = i / M, m = i % M;
+      const int n = p_lo * 2 + rl;
+      float v = 0.f;
+      for (int sl = 0; sl < nslot; ++sl) v += slots[((size_t)rl * nslot + sl) * M + m];
+      v *= ts * xs_inv[m];
+      if (EPI == EPI2_PUSH) {
+        const uint32_t epoch = *reinterpret_cast<const uint32_t*>(push.ws[push.rank]) + 1;
+        const size_t off = 65536 + ((size_t)(((epoch & 1) * 8 + push.rank) * 8 + push.row0 + m) * push.hmax + n) * 8;
+        const uint2 word = make_uint2(__float_as_uint(v), epoch);
+        for (int p = 0; p < push.world; ++p) st_relaxed_sys_v2(push.ws[p] + off, word);
+      } else {
+        if (EPI == EPI2_RESIDUAL) v += __bfloat162float(residual[(size_t)m * ldr + n]);
+        if (EPI == EPI2_STORE_F32)
+          reinterpret_cast<float*>(yout)[(size_t)m * ldy + n] = v;
+        else
+          reinterpret_cast<bf16*>(yout)[(size_t)m * ldy + n] = __float2bfloat16(v);
+      }
+    }
+  }
+}
+
+// (wq [N, K/2], scale [N, K/16]) -> stream layout.  One thread per (row, chunk).
+__global__ void __launch_bounds__(256)
+gemv_stream_pack_kernel(const uint8_t* __restrict__ wq, const uint8_t* __restrict__ scale,
+                        uint8_t* __restrict__ out, int N, int K) {
+  const int nchunks = K >> 5;
+  const long long total = (long long)N * nchunks;
+  const int nsteps = (nchunks + 31) >> 5;
+  const int nlast = nchunks - 32 * (nsteps - 1);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int row = (int)(i / nchunks), c = (int)(i % nchunks);
+    const int p = row >> 1, r = row & 1, s = c >> 5, j = c & 31;
+    const int n = (s == nsteps - 1) ? nlast : 32;
+    uint8_t* ub = out + (size_t)p * nchunks * 36 + (size_t)s * UNIT_BYTES;
+    *reinterpret_cast<uint4*>(ub + (size_t)(r * n + j) * 16) =
+        *reinterpret_cast<const uint4*>(wq + (size_t)row * (K >> 1) + (size_t)c * 16);
+    *reinterpret_cast<uint16_t*>(ub + (size_t)n * 32 + (size_t)(r * n + j) * 2) =
+        *reinterpret_cast<const uint16_t*>(scale + (size_t)row * (K >> 4) + (size_t)c * 2);
+  }
+}
+
+int g2_num_sms() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return sms;
+}
+
+template <int M, int EPI>
+cudaError_t launch_gemv2(const bf16* x, int ldx, const uint8_t* wst, const float* ts, const float* norm_w,
+                         float eps, const bf16* res, int ldr, void* y, int ldy, int N, int K, cudaStream_t st,
+                         const TrlPushArgs& push) {
+  constexpr int W = G2_WARPS;
+  const int npairs = N / 2;
+  static const int ctas_per_sm = getenv("TRL_GEMV2_CTAS") ? atoi(getenv("TRL_GEMV2_CTAS")) : 3;
+  const int grid = min(g2_num_sms() * ctas_per_sm, npairs);
+  const int pl_max = (npairs + grid - 1) / grid;
+  const int nslot = (npairs / grid) >= W ? 2 : W;
+  const size_t fixed = (size_t)W * G2_MAX_NS * 8 + (size_t)M * K * sizeof(__half) + 8 * sizeof(float) +
+                       64 * sizeof(float) + (size_t)pl_max * 2 * nslot * M * sizeof(float);
+  // three CTAs per SM when the activation row leaves room for a useful ring, else two
+  static const int ns_env = getenv("TRL_GEMV2_NS") ? atoi(getenv("TRL_GEMV2_NS")) : 0;
+  int ns = (int)((74 * 1024 - (long)fixed) / (W * STAGE_BYTES));
+  if (ns < 2) ns = (int)((112 * 1024 - (long)fixed) / (W * STAGE_BYTES));
+  if (ns_env > 0) ns = ns_env;
+  ns = min(ns, G2_MAX_NS);
+  if (ns < 2) return cudaErrorInvalidValue;
+  const size_t smem = (size_t)W * ns * STAGE_BYTES + fixed;
+  auto kern = gemv2_kernel<M, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    configured = true;
+  }
+  return trl_launch(kern, dim3(grid), dim3(G2_THREADS), smem, st, x, ldx, wst, ts, norm_w, eps, res, ldr, y, ldy,
+                    N, K, nslot, ns, push);
+}
+
+template <int EPI>
+cudaError_t dispatch2(int M, const bf16* x, int ldx, const uint8_t* wst, const float* ts, const float* norm_w,
+                      float eps, const bf16* res, int ldr, void* y, int ldy, int N, int K, cudaStream_t st,
+                      const TrlPushArgs& push = TrlPushArgs()) {
+  if (M == 1) return launch_gemv2<1, EPI>(x, ldx, wst, ts, norm_w, eps, res, ldr, y, ldy, N, K, st, push);
+  if (M == 2) return launch_gemv2<2, EPI>(x, ldx, wst, ts, norm_w, eps, res, ldr, y, ldy, N, K, st, push);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+// Bytes of the stream layout of an [N, K] NVFP4 weight (N even, K % 128 == 0).
+TRL_API long trl_gemv_stream_bytes(int N, int K) {
+  if (N <= 0 || (N & 1) || K <= 0 || (K % 128) != 0) return -1;
+  return (long)(N / 2) * (K / 32) * 36;
+}
+
+TRL_API int trl_gemv_stream_pack(const void* wq, const void* scale, void* out, int N, int K, void* stream) {
+  if (trl_gemv_stream_bytes(N, K) < 0) return (int)cudaErrorInvalidValue;
+  const long long total = (long long)N * (K / 32);
+  const int grid = (int)min((long long)4096, (total + 255) / 256);
+  gemv_stream_pack_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)wq, (const uint8_t*)scale,
+                                                                 (uint8_t*)out, N, K);
+  return (int)cudaGetLastError();
+}
+
+// y = epi(tscale * norm(x) @ W^T) for M <= 2 rows from the stream layout of W.
+TRL_API int trl_gemv2_nvfp4(const void* x, int ldx, const void* wst, const void* tscale, const void* norm_w, float eps,
+                            const void* residual, int ldr, void* y, int ldy, int M, int N, int K, int epi,
+                            void* stream) {
+  if (trl_gemv_stream_bytes(N, K) < 0 || M < 1 || M > 2) return (int)cudaErrorInvalidValue;
+  cudaStream_t st = (cudaStream_t)stream;
+  const bf16* xp = (const bf16*)x;
+  const bf16* rp = (const bf16*)residual;
+  const uint8_t* wp = (const uint8_t*)wst;
+  const float* tp = (const float*)tscale;
+  const float* np_ = (const float*)norm_w;
+  switch (epi) {
+    case EPI2_STORE: return (int)dispatch2<EPI2_STORE>(M, xp, ldx, wp, tp, np_, eps, rp, ldr, y, ldy, N, K, st);
+    case EPI2_RESIDUAL: return (int)dispatch2<EPI2_RESIDUAL>(M, xp, ldx, wp, tp, np_, eps, rp, ldr, y, ldy, N, K, st);
+    case EPI2_SWIGLU: return (int)dispatch2<EPI2_SWIGLU>(M, xp, ldx, wp, tp, np_, eps, rp, ldr, y, ldy, N, K, st);
+    case EPI2_STORE_F32: return (int)dispatch2<EPI2_STORE_F32>(M, xp, ldx, wp, tp, np_, eps, rp, ldr, y, ldy, N, K, st);
+  }
+  return (int)cudaErrorInvalidValue;
+}
+
+// Row-parallel variant: fp32 partial rows go into every rank's one-shot all-reduce slot.
+TRL_API int trl_gemv2_nvfp4_push(const void* x, int ldx, const void* wst, const void* tscale, void* const* ws,
+                                 int rank, int world, int hmax, int M, int N, int K, void* stream) {
+  if (trl_gemv_stream_bytes(N, K) < 0 || M < 1 || M > 2 || N > hmax) return (int)cudaErrorInvalidValue;
+  TrlPushArgs push;
+  for (int i = 0; i < 8; ++i) push.ws[i] = i < world ? (unsigned char*)ws[i] : nullptr;
+  push.rank = rank, push.world = world, push.hmax = hmax, push.row0 = 0;
+  return (int)dispatch2<EPI2_PUSH>(M, (const bf16*)x, ldx, (const uint8_t*)wst, (const float*)tscale, nullptr, 0.f,
+                                   nullptr, 0, nullptr, 0, N, K, (cudaStream_t)stream, push);
+}

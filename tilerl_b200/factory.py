@@ -86,15 +86,18 @@ def build_random_streaming(cfg: ModelConfig, device, seed: int = 0, tp_rank: int
 
 def materialize(model: HybridModel, ops) -> None:
     """Create the device-side operand layouts up front (tile-contiguous weight nibbles and
-    128x4-tiled scales for the tcgen05 GEMM) so the first request does not pay for them.
+    128x4-tiled scales for the tcgen05 GEMM, the stream layout of the decode GEMV) so the first
+    request does not pay for them.
     Reference: ``Backend.materialize`` (``backend.py:975-1021``)."""
     if getattr(ops, "name", "") != "cuda" or not getattr(ops, "use_tc_gemm", False):
         return
-    from .ops.gemm_tc import sf_tiled, wq_tiled
+    from .ops.gemm_tc import sf_tiled, stream_ok, w_stream, wq_tiled
     for v in model.params.values():
         if isinstance(v, NVFP4Tensor):
             sf_tiled(v)
             wq_tiled(v)
+            if getattr(ops, "gemv_stream", False) and stream_ok(v):
+                w_stream(v)
 
 
 def build_model(model: str | ModelConfig, device="cpu", *, seed: int = 0, checkpoint: Optional[str] = None,

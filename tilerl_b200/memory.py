@@ -40,7 +40,7 @@ def weight_bytes(cfg: ModelConfig, tp: int = 1, tiled_copy: bool = True) -> int:
         if tp > 1 and is_sharded(name):
             b //= tp
         if fmt == "nvfp4" and tiled_copy:
-            b *= 2      # tile-contiguous operand copy kept next to the checkpoint layout
+            b *= 3      # tile-contiguous GEMM operand copy and the GEMV stream-layout copy next to the checkpoint layout
         total += b
     return total
 

@@ -73,6 +73,9 @@ class CudaOps:
         # B=1) or the tcgen05 GEMM with `terms_small` residual terms (TRL_DECODE=tc)
         self.decode_tc = (os.environ.get("TRL_DECODE", "simt") == "tc") if decode_tc is None else decode_tc
         self.gemv_tokens = int(os.environ.get("TRL_GEMV_TOKENS", 2))
+        # rows <= 2: the ring-streamed GEMV on the weight's stream-layout copy (TRL_GEMV_STREAM=0: the
+        # register-streamed kernels on the checkpoint layout)
+        self.gemv_stream = os.environ.get("TRL_GEMV_STREAM", "1") != "0"
         self.prefill_attn = os.environ.get("TRL_PREFILL_ATTN", "1") != "0"   # tiled kernel for q_len >= 16
         from .. import tape as _tape
         _tape.set_dequant(self.dequantize_nvfp4)   # frozen-base linears of the training forward
@@ -91,7 +94,16 @@ class CudaOps:
 
     def _gemv(self, x, w, y, *, norm_w=None, eps=0.0, residual=None, epi=EPI_STORE):
         m, k = x.shape
-        if isinstance(w, NVFP4Tensor):
+        if isinstance(w, NVFP4Tensor) and m <= 2 and self.gemv_stream and self._stream_ok(w) \
+                and (m * k * 2 <= 88 * 1024):
+            from .gemm_tc import w_stream
+            n = w.wq.shape[0]
+            N.check(self.lib.trl_gemv2_nvfp4(
+                x.data_ptr(), x.stride(0), w_stream(w).data_ptr(), w.tscale.data_ptr(),
+                N.ptr(norm_w), eps, N.ptr(residual), residual.stride(0) if residual is not None else 0,
+                y.data_ptr(), y.stride(0), m, n, k, epi, N.stream()), "gemv2_nvfp4")
+            N.count()
+        elif isinstance(w, NVFP4Tensor):
             n = w.wq.shape[0]
             N.check(self.lib.trl_gemv_nvfp4(
                 x.data_ptr(), x.stride(0), w.wq.data_ptr(), w.scale.data_ptr(), w.tscale.data_ptr(),
@@ -108,6 +120,11 @@ class CudaOps:
             N.count((m + 3) // 4)
         else:
             raise TypeError(f"no GEMV for weight type {type(w)}")
+
+    @staticmethod
+    def _stream_ok(w) -> bool:
+        n, k = w.shape
+        return n % 2 == 0 and k % 128 == 0
 
     def _tc(self, w, t: int) -> bool:
         # measured on the 27B shapes (gate_up): 1 token GEMV 27.5 us; 2 tokens GEMV 35.6 / tensor-core
@@ -429,11 +446,13 @@ class CudaOps:
 
     def refresh_weight(self, w: NVFP4Tensor) -> None:
         """Bring the GEMM's tile-contiguous copies of a rewritten weight up to date (in place)."""
-        from .gemm_tc import sf_tiled, wq_tiled
+        from .gemm_tc import sf_tiled, w_stream, wq_tiled
         if getattr(w, "wq_tiled", None) is not None:
             wq_tiled(w)
         if getattr(w, "sf_tiled", None) is not None:
             sf_tiled(w)
+        if getattr(w, "w_stream", None) is not None:
+            w_stream(w)
 
     def dequantize_nvfp4(self, w: NVFP4Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         n, k = w.shape

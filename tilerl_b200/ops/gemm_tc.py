@@ -21,6 +21,10 @@ N.register("trl_quant_act_nvfp4", [N.P, N.I, N.P, N.F, N.P, N.P, N.P, N.I, N.I, 
 N.register("trl_gemm_nvfp4", [N.P, N.P, N.P, N.P, N.P, N.P, N.P, N.I, N.P, N.I, N.P, N.P, N.L,
                               N.I, N.I, N.I, N.I, N.I, N.I, N.I, N.I, N.P])
 N.register("trl_gemm_nvfp4_scratch_bytes", [N.I, N.I, N.I, N.I, N.I])
+N.register("trl_gemv_stream_bytes", [N.I, N.I])
+N.register("trl_gemv_stream_pack", [N.P, N.P, N.P, N.I, N.I, N.P])
+N.register("trl_gemv2_nvfp4", [N.P, N.I, N.P, N.P, N.P, N.F, N.P, N.I, N.P, N.I, N.I, N.I, N.I, N.I, N.P])
+N.register("trl_gemv2_nvfp4_push", [N.P, N.I, N.P, N.P, N.P, N.I, N.I, N.I, N.I, N.I, N.I, N.P])
 
 KT = 256  # K elements per k-tile
 
@@ -76,6 +80,45 @@ def sf_tiled(w: NVFP4Tensor) -> torch.Tensor:
     elif getattr(w, "sf_version", None) != w.scale._version:
         t.copy_(tile_scales(w.scale, w.shape[1]))
         w.sf_version = w.scale._version
+    return t
+
+
+def stream_layout(wq: torch.Tensor, scale: torch.Tensor, K: int) -> torch.Tensor:
+    """Torch statement of the GEMV stream layout (``csrc/gemv2.cu``): rows in pairs, K in steps of
+    32 chunks of 32 weights; unit (pair, step) = ``[n x 16 B row 0][n x 16 B row 1][n x 2 B scales
+    row 0][n x 2 B scales row 1]`` with n = 32 (fewer in a row's last step), units back to back."""
+    n_rows, kb = wq.shape
+    nchunks = K // 32
+    w = wq.view(n_rows // 2, 2, nchunks, 16)
+    s = scale.view(torch.uint8).view(n_rows // 2, 2, nchunks, 2)
+    parts = []
+    for c0 in range(0, nchunks, 32):
+        c1 = min(nchunks, c0 + 32)
+        parts.append(w[:, :, c0:c1].reshape(n_rows // 2, -1))
+        parts.append(s[:, :, c0:c1].reshape(n_rows // 2, -1))
+    return torch.cat(parts, dim=1).contiguous().view(-1)
+
+
+def stream_ok(w: NVFP4Tensor) -> bool:
+    n, k = w.shape
+    return n % 2 == 0 and k % 128 == 0
+
+
+def w_stream(w: NVFP4Tensor) -> torch.Tensor:
+    """The weight's stream-layout copy for the decode GEMV (built on the device, refreshed in place
+    when the weight was rewritten so captured graphs keep their address)."""
+    t = getattr(w, "w_stream", None)
+    fresh = t is None
+    ver = (w.wq._version, w.scale._version)
+    if fresh:
+        n, k = w.shape
+        t = torch.empty((n // 2) * (k // 32) * 36, dtype=torch.uint8, device=w.wq.device)
+        w.w_stream = t
+    if fresh or getattr(w, "stream_version", None) != ver:
+        n, k = w.shape
+        N.check(N.lib().trl_gemv_stream_pack(w.wq.data_ptr(), w.scale.data_ptr(), t.data_ptr(), n, k, N.stream()),
+                "gemv_stream_pack")
+        w.stream_version = ver
     return t
 
 

@@ -31,7 +31,7 @@ def main():
     args = ap.parse_args()
     from tilerl_b200.formats import NVFP4Tensor
     from tilerl_b200.ops.cuda import CudaOps
-    from tilerl_b200.ops.gemm_tc import gemm_nvfp4, quant_act, sf_tiled, wq_tiled
+    from tilerl_b200.ops.gemm_tc import gemm_nvfp4, quant_act, sf_tiled, w_stream, wq_tiled
     from tilerl_b200.ops import native
     dev = torch.device("cuda", 0)
     ops = CudaOps(dev)
@@ -49,6 +49,7 @@ def main():
                             torch.ones(1, device=dev))
             sf_tiled(w)
             wq_tiled(w)
+            w_stream(w)
             ws.append(w)
         x = torch.randn(args.m, k, device=dev).to(torch.bfloat16)
         y = torch.zeros(args.m, n, dtype=torch.bfloat16, device=dev)
