@@ -68,28 +68,60 @@ __device__ __forceinline__ void g2_bulk_load(uint32_t dst, const void* src, uint
                : "memory");
 }
 
+__device__ __forceinline__ uint4 g2_lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint16_t g2_lds16(uint32_t a) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+  return v;
+}
+
 // x (bf16 [M, K], optional RMSNorm) -> shared memory as f16 scaled by a per-row power of two
 // (16 products of |w| <= 6 then stay below the f16 maximum).  Piece p (8 halves) of 32-element
 // chunk c sits at ((p * nchunks + c) * 8) halves: the four 16-byte reads of a chunk are
 // conflict-free across lanes.  xs_inv[m] = 1 / applied scale.
+// One pass: a thread keeps its (up to XV) 8-element vectors of the row in registers between the
+// statistics and the scaled write.
+constexpr int G2_XV = 9;   // K <= 9 * 256 * 8 = 18432
 template <int M>
 __device__ __forceinline__ void g2_stage_x(const bf16* __restrict__ x, int ldx, int K,
                                            const float* __restrict__ norm_w, float eps, __half* xs,
                                            float* xs_inv, float* red) {
-  const int nchunks = K >> 5;
+  const int nchunks = K >> 5, nvec = K >> 3;
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
 #pragma unroll
   for (int m = 0; m < M; ++m) {
     const bf16* xr = x + (size_t)m * ldx;
+    uint4 xv[G2_XV];
     float ss = 0.f, amax = 0.f;
-    for (int k = threadIdx.x * 2; k < K; k += G2_THREADS * 2) {
-      float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(xr + k));
-      ss += v.x * v.x + v.y * v.y;
-      if (norm_w != nullptr) {
-        const float2 nw = *reinterpret_cast<const float2*>(norm_w + k);
-        v.x *= nw.x, v.y *= nw.y;
+#pragma unroll
+    for (int i = 0; i < G2_XV; ++i) {
+      const int v = threadIdx.x + i * G2_THREADS;
+      xv[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (v < nvec) xv[i] = *reinterpret_cast<const uint4*>(xr + (size_t)v * 8);
+    }
+#pragma unroll
+    for (int i = 0; i < G2_XV; ++i) {
+      const int v = threadIdx.x + i * G2_THREADS;
+      if (v < nvec) {
+        const uint32_t u4[4] = {xv[i].x, xv[i].y, xv[i].z, xv[i].w};
+        float nw[8];
+        if (norm_w != nullptr) {
+          const float4 a = *reinterpret_cast<const float4*>(norm_w + (size_t)v * 8);
+          const float4 b = *reinterpret_cast<const float4*>(norm_w + (size_t)v * 8 + 4);
+          nw[0] = a.x, nw[1] = a.y, nw[2] = a.z, nw[3] = a.w, nw[4] = b.x, nw[5] = b.y, nw[6] = b.z, nw[7] = b.w;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = bf162_bits_to_f2(u4[j]);
+          ss += f.x * f.x + f.y * f.y;
+          if (norm_w != nullptr) f.x *= nw[2 * j], f.y *= nw[2 * j + 1];
+          amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
       }
-      amax = fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y)));
     }
     ss = warp_sum(ss);
     amax = warp_max(amax);
@@ -105,31 +137,45 @@ __device__ __forceinline__ void g2_stage_x(const bf16* __restrict__ x, int ldx, 
     }
     int e = 0;
     if (amax > 0.f) frexpf(amax, &e);   // amax = f * 2^e, f in [0.5, 1)
-    const float s = exp2f((float)(8 - e));
+    const float sc = exp2f((float)(8 - e));
     if (threadIdx.x == 0) xs_inv[m] = exp2f((float)(e - 8));
     __half* dst = xs + (size_t)m * K;
-    for (int k = threadIdx.x * 2; k < K; k += G2_THREADS * 2) {
-      float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(xr + k));
-      if (norm_w != nullptr) {
-        const float2 nw = *reinterpret_cast<const float2*>(norm_w + k);
-        v.x = __bfloat162float(__float2bfloat16(v.x * rstd * nw.x));
-        v.y = __bfloat162float(__float2bfloat16(v.y * rstd * nw.y));
+#pragma unroll
+    for (int i = 0; i < G2_XV; ++i) {
+      const int v = threadIdx.x + i * G2_THREADS;
+      if (v < nvec) {
+        const uint32_t u4[4] = {xv[i].x, xv[i].y, xv[i].z, xv[i].w};
+        uint32_t o[4];
+        float nw[8];
+        if (norm_w != nullptr) {
+          const float4 a = *reinterpret_cast<const float4*>(norm_w + (size_t)v * 8);
+          const float4 b = *reinterpret_cast<const float4*>(norm_w + (size_t)v * 8 + 4);
+          nw[0] = a.x, nw[1] = a.y, nw[2] = a.z, nw[3] = a.w, nw[4] = b.x, nw[5] = b.y, nw[6] = b.z, nw[7] = b.w;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = bf162_bits_to_f2(u4[j]);
+          if (norm_w != nullptr) {
+            f.x = __bfloat162float(__float2bfloat16(f.x * rstd * nw[2 * j]));
+            f.y = __bfloat162float(__float2bfloat16(f.y * rstd * nw[2 * j + 1]));
+          }
+          const __half2 h = __floats2half2_rn(f.x * sc, f.y * sc);
+          o[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        // vector v = piece (v & 3) of chunk (v >> 2)
+        *reinterpret_cast<uint4*>(dst + ((size_t)((v & 3) * nchunks + (v >> 2)) << 3)) = make_uint4(o[0], o[1], o[2], o[3]);
       }
-      const int c = k >> 5, p = (k >> 3) & 3, o = k & 7;
-      *reinterpret_cast<__half2*>(dst + ((size_t)(p * nchunks + c) << 3) + o) = __floats2half2_rn(v.x * s, v.y * s);
     }
   }
   __syncthreads();
 }
 
+// Warp w of W owns units [w * U / W, (w + 1) * U / W): the owner of `unit` (U * W < 2^31).
 __device__ __forceinline__ int g2_owner(int unit, int U, int W) {
-  int w = (int)(((long long)unit * W) / U);
-  while (w + 1 < W && (int)(((long long)(w + 1) * U) / W) <= unit) ++w;
-  while (w > 0 && (int)(((long long)w * U) / W) > unit) --w;
-  return w;
+  return ((unit + 1) * W - 1) / U;
 }
 
-template <int M, int EPI>
+template <int M, int EPI, bool FULL>
 __global__ void __launch_bounds__(G2_THREADS, 3)
 gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ wst,
              const float* __restrict__ tscale, const float* __restrict__ norm_w, float eps,
@@ -191,6 +237,8 @@ gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ ws
   g2_stage_x<M>(x, ldx, K, norm_w, eps, xs, xs_inv, red);   // ends with a block barrier
 
   bool ok = true;
+  const uint32_t xs_a = smem_addr(xs) + (uint32_t)lane * 16u;
+  const uint32_t pstride = (uint32_t)nchunks * 16u, xrow_bytes = (uint32_t)K * 2u;
   if (u0 < u1) {
     int cp = u0 / nsteps, cs = u0 % nsteps, slot = 0;
     uint32_t parity = 0;
@@ -226,39 +274,35 @@ gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ ws
       }
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      const unsigned char* ub = ring + ((size_t)warp * NS + slot) * STAGE_BYTES;
+      uint32_t ua = ring_w + (uint32_t)slot * STAGE_BYTES;   // shared address of the current unit
 #pragma unroll
       for (int g = 0; g < STAGE_UNITS; ++g) {
         if (u >= u1) break;
-        const int n = (cs == nsteps - 1) ? nlast : 32;
-        if (lane < n) {
-          const int c = cs * 32 + lane;
-          uint4 wv[2];
-          uint16_t sv[2];
-          wv[0] = *reinterpret_cast<const uint4*>(ub + lane * 16);
-          wv[1] = *reinterpret_cast<const uint4*>(ub + n * 16 + lane * 16);
-          sv[0] = *reinterpret_cast<const uint16_t*>(ub + n * 32 + lane * 2);
-          sv[1] = *reinterpret_cast<const uint16_t*>(ub + n * 34 + lane * 2);
+        const int n = FULL ? 32 : ((cs == nsteps - 1) ? nlast : 32);
+        if (FULL || lane < n) {
+          const uint4 wv0 = g2_lds128(ua + lane * 16);
+          const uint4 wv1 = g2_lds128(ua + n * 16 + lane * 16);
+          const uint16_t sv[2] = {g2_lds16(ua + n * 32 + lane * 2), g2_lds16(ua + n * 34 + lane * 2)};
+          const uint32_t w4[2][4] = {{wv0.x, wv0.y, wv0.z, wv0.w}, {wv1.x, wv1.y, wv1.z, wv1.w}};
+          const uint32_t xa = xs_a + (uint32_t)cs * 512u;    // chunk cs * 32 + lane, piece 0
 #pragma unroll
           for (int m = 0; m < M; ++m) {
             uint32_t xh[16];
-            const __half* xm = xs + (size_t)m * K;
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
-              const uint4 t = *reinterpret_cast<const uint4*>(xm + ((size_t)(p * nchunks + c) << 3));
+              const uint4 t = g2_lds128(xa + (uint32_t)m * xrow_bytes + (uint32_t)p * pstride);
               xh[p * 4 + 0] = t.x, xh[p * 4 + 1] = t.y, xh[p * 4 + 2] = t.z, xh[p * 4 + 3] = t.w;
             }
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
               const float2 sc = h2_to_f2(cvt_e4m3x2_to_h2(sv[r]));
-              const uint32_t w4[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
 #pragma unroll
               for (int blk = 0; blk < 2; ++blk) {
                 uint32_t a = 0u;  // f16x2 zero
 #pragma unroll
                 for (int q = 0; q < 2; ++q) {
                   uint32_t h[4];
-                  cvt_e2m1x8_to_h2x4(w4[blk * 2 + q], h);
+                  cvt_e2m1x8_to_h2x4(w4[r][blk * 2 + q], h);
 #pragma unroll
                   for (int i = 0; i < 4; ++i) a = hfma2_u(h[i], xh[(blk * 2 + q) * 4 + i], a);
                 }
@@ -268,7 +312,7 @@ gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ ws
             }
           }
         }
-        ub += n * 36;
+        ua += (uint32_t)n * 36u;
         ++u;
         if (++cs == nsteps) {
           flush(cp);
@@ -376,15 +420,19 @@ cudaError_t launch_gemv2(const bf16* x, int ldx, const uint8_t* wst, const float
   ns = min(ns, G2_MAX_NS);
   if (ns < 2) return cudaErrorInvalidValue;
   const size_t smem = (size_t)W * ns * STAGE_BYTES + fixed;
-  auto kern = gemv2_kernel<M, EPI>;
   static bool configured = false;
   if (!configured) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    cudaFuncSetAttribute(gemv2_kernel<M, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(gemv2_kernel<M, EPI, true>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    cudaFuncSetAttribute(gemv2_kernel<M, EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(gemv2_kernel<M, EPI, false>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     configured = true;
   }
-  return trl_launch(kern, dim3(grid), dim3(G2_THREADS), smem, st, x, ldx, wst, ts, norm_w, eps, res, ldr, y, ldy,
-                    N, K, nslot, ns, push);
+  if ((K % 1024) == 0)   // every step of a row is full: 32 chunks
+    return trl_launch(gemv2_kernel<M, EPI, true>, dim3(grid), dim3(G2_THREADS), smem, st, x, ldx, wst, ts, norm_w,
+                      eps, res, ldr, y, ldy, N, K, nslot, ns, push);
+  return trl_launch(gemv2_kernel<M, EPI, false>, dim3(grid), dim3(G2_THREADS), smem, st, x, ldx, wst, ts, norm_w,
+                    eps, res, ldr, y, ldy, N, K, nslot, ns, push);
 }
 
 template <int EPI>
@@ -417,7 +465,7 @@ TRL_API int trl_gemv_stream_pack(const void* wq, const void* scale, void* out, i
 TRL_API int trl_gemv2_nvfp4(const void* x, int ldx, const void* wst, const void* tscale, const void* norm_w, float eps,
                             const void* residual, int ldr, void* y, int ldy, int M, int N, int K, int epi,
                             void* stream) {
-  if (trl_gemv_stream_bytes(N, K) < 0 || M < 1 || M > 2) return (int)cudaErrorInvalidValue;
+  if (trl_gemv_stream_bytes(N, K) < 0 || M < 1 || M > 2 || K > G2_XV * G2_THREADS * 8) return (int)cudaErrorInvalidValue;
   cudaStream_t st = (cudaStream_t)stream;
   const bf16* xp = (const bf16*)x;
   const bf16* rp = (const bf16*)residual;
@@ -436,7 +484,8 @@ TRL_API int trl_gemv2_nvfp4(const void* x, int ldx, const void* wst, const void*
 // Row-parallel variant: fp32 partial rows go into every rank's one-shot all-reduce slot.
 TRL_API int trl_gemv2_nvfp4_push(const void* x, int ldx, const void* wst, const void* tscale, void* const* ws,
                                  int rank, int world, int hmax, int M, int N, int K, void* stream) {
-  if (trl_gemv_stream_bytes(N, K) < 0 || M < 1 || M > 2 || N > hmax) return (int)cudaErrorInvalidValue;
+  if (trl_gemv_stream_bytes(N, K) < 0 || M < 1 || M > 2 || N > hmax || K > G2_XV * G2_THREADS * 8)
+    return (int)cudaErrorInvalidValue;
   TrlPushArgs push;
   for (int i = 0; i < 8; ++i) push.ws[i] = i < world ? (unsigned char*)ws[i] : nullptr;
   push.rank = rank, push.world = world, push.hmax = hmax, push.row0 = 0;

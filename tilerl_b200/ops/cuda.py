@@ -95,7 +95,7 @@ class CudaOps:
     def _gemv(self, x, w, y, *, norm_w=None, eps=0.0, residual=None, epi=EPI_STORE):
         m, k = x.shape
         if isinstance(w, NVFP4Tensor) and m <= 2 and self.gemv_stream and self._stream_ok(w) \
-                and (m * k * 2 <= 88 * 1024):
+                and (m * k * 2 <= 88 * 1024) and k <= 18432:
             from .gemm_tc import w_stream
             n = w.wq.shape[0]
             N.check(self.lib.trl_gemv2_nvfp4(

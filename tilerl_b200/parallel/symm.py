@@ -98,7 +98,7 @@ class SymmComm:
         n = w.shape[0]
         st = N.stream()
         if t <= min(8, getattr(ops, "gemv_tokens", 8)) and isinstance(w, NVFP4Tensor) and lora is None:
-            if t <= 2 and getattr(ops, "gemv_stream", False) and ops._stream_ok(w) and t * k * 2 <= 88 * 1024:
+            if t <= 2 and getattr(ops, "gemv_stream", False) and ops._stream_ok(w) and t * k * 2 <= 88 * 1024 and k <= 18432:
                 from ..ops.gemm_tc import w_stream
                 N.check(self.lib.trl_gemv2_nvfp4_push(a.data_ptr(), a.stride(0), w_stream(w).data_ptr(),
                                                       w.tscale.data_ptr(), self.table, self.rank, self.world,
