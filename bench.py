@@ -24,6 +24,7 @@ import subprocess
 import sys
 import threading
 import time
+import zlib
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -206,6 +207,7 @@ def main():
         eng.generate([p.tolist()], sp)
     barrier()
     e2e_ms, ttft, e2e_tokens = 0.0, [], 0
+    first_tokens = None
     h2d0, d2h0 = eng.io_bytes()
     for p in prompts[W:]:
         a, b = ev(), ev()
@@ -219,6 +221,8 @@ def main():
         e2e_ms += max(a.elapsed_time(b), (time.perf_counter() - t_host) * 1e3)
         ttft.append(res.ttft_s)
         e2e_tokens += len(res.tokens)
+        if first_tokens is None:
+            first_tokens = list(res.tokens)
     barrier()
     te = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
     if world > 1:
@@ -251,6 +255,10 @@ def main():
             "gpu_launches": int(launches), "kernels_per_decode_tick": int(graph_kernels),
             "clocks": clocks, "build_s": round(build_s, 1), "served_bytes": model.served_bytes(),
             "device_error_word": list(err),
+            # greedy tokens of the first timed request: the same prompt at every GPU count, so runs at
+            # N = 1, 2, 4, 8 can be compared (different summation orders may flip a near-tie late on)
+            "token_checksum": zlib.crc32(",".join(map(str, first_tokens or [])).encode()),
+            "first_tokens": (first_tokens or [])[:16],
         }
         print(json.dumps(out))
     if world > 1:

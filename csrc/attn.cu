@@ -24,10 +24,10 @@ constexpr int KVB = 16;
 constexpr int MAXG = 8;
 
 __global__ void __launch_bounds__(256)
-attn_prep_kernel(const bf16* __restrict__ qkv, int ld, const float* __restrict__ qw,
-                 const float* __restrict__ kw, const int* __restrict__ positions,
-                 const int* __restrict__ slot_mapping, bf16* __restrict__ q_out,
-                 bf16* __restrict__ kcache, bf16* __restrict__ vcache, int n_q, int n_kv, int D,
+attn_prep_kernel(const bf16* qkv, int ld, const float* __restrict__ qw,
+                 const float* __restrict__ kw, const int* positions,
+                 const int* slot_mapping, bf16* q_out,
+                 bf16* kcache, bf16* vcache, int n_q, int n_kv, int D,
                  int rotary, float log2_theta, float eps, int gated) {
   extern __shared__ float sm[];
   float* cs = sm;                 // [rotary/2] cos
@@ -95,12 +95,12 @@ attn_prep_kernel(const bf16* __restrict__ qkv, int ld, const float* __restrict__
 // One CTA per (split, kv head, token).  VEC = D / 32 elements per lane.
 template <int VEC>
 __global__ void __launch_bounds__(256)
-attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ gate_src, int gate_ld,
-                  const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
-                  const int* __restrict__ block_table, int max_blocks,
-                  const int* __restrict__ seq_ids, const int* __restrict__ positions,
-                  float* __restrict__ po, float* __restrict__ pm, float* __restrict__ pl,
-                  bf16* __restrict__ out, int n_q, int n_kv, int n_splits, float scale_log2e,
+attn_split_kernel(const bf16* q, const bf16* gate_src, int gate_ld,
+                  const bf16* kcache, const bf16* vcache,
+                  const int* block_table, int max_blocks,
+                  const int* seq_ids, const int* positions,
+                  float* po, float* pm, float* pl,
+                  bf16* out, int n_q, int n_kv, int n_splits, float scale_log2e,
                   int gated) {
   constexpr int D = VEC * 32;
   __shared__ float s_m[8][MAXG], s_l[8][MAXG];
@@ -209,9 +209,9 @@ attn_split_kernel(const bf16* __restrict__ q, const bf16* __restrict__ gate_src,
 }
 
 __global__ void __launch_bounds__(256)
-attn_combine_kernel(const float* __restrict__ po, const float* __restrict__ pm,
-                    const float* __restrict__ pl, const bf16* __restrict__ gate_src, int gate_ld,
-                    bf16* __restrict__ out, int n_q, int D, int n_splits, int gated) {
+attn_combine_kernel(const float* po, const float* pm,
+                    const float* pl, const bf16* gate_src, int gate_ld,
+                    bf16* out, int n_q, int D, int n_splits, int gated) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
@@ -287,11 +287,11 @@ __device__ __forceinline__ void e4m3x16_to_bf16(const uint4& raw, float s, uint4
 
 template <bool FP8>
 __global__ void __launch_bounds__(256)
-attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ gate_src, int gate_ld,
-                    const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
-                    const float* __restrict__ kscale, const float* __restrict__ vscale,
-                    const int* __restrict__ block_table, int max_blocks, const int* __restrict__ q_start,
-                    const int* __restrict__ q_len, const int* __restrict__ positions, bf16* __restrict__ out,
+attn_prefill_kernel(const bf16* q, const bf16* gate_src, int gate_ld,
+                    const bf16* kcache, const bf16* vcache,
+                    const float* kscale, const float* vscale,
+                    const int* block_table, int max_blocks, const int* q_start,
+                    const int* q_len, const int* positions, bf16* out,
                     int n_q, int n_kv, float scale_log2e, int gated) {
   extern __shared__ __align__(1024) unsigned char pf_smem[];
   pdl_launch_dependents();

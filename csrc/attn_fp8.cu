@@ -29,11 +29,11 @@ __device__ __forceinline__ unsigned char to_e4m3(float v) {
 }
 
 __global__ void __launch_bounds__(256)
-attn_prep_fp8_kernel(const bf16* __restrict__ qkv, int ld, const float* __restrict__ qw,
-                     const float* __restrict__ kw, const int* __restrict__ positions,
-                     const int* __restrict__ slot_mapping, bf16* __restrict__ q_out,
-                     unsigned char* __restrict__ kcache, unsigned char* __restrict__ vcache,
-                     float* __restrict__ kscale, float* __restrict__ vscale, int n_q, int n_kv, int D,
+attn_prep_fp8_kernel(const bf16* qkv, int ld, const float* __restrict__ qw,
+                     const float* __restrict__ kw, const int* positions,
+                     const int* slot_mapping, bf16* q_out,
+                     unsigned char* kcache, unsigned char* vcache,
+                     float* kscale, float* vscale, int n_q, int n_kv, int D,
                      int rotary, float log2_theta, float eps, int gated) {
   extern __shared__ float sm[];
   float* cs = sm;                 // [rotary/2] cos
@@ -126,13 +126,13 @@ __device__ __forceinline__ void load_e4m3_row(const unsigned char* p, float (&f)
 // One CTA per (split, kv head, token).  VEC = D / 32 elements per lane.
 template <int VEC>
 __global__ void __launch_bounds__(256)
-attn_split_fp8_kernel(const bf16* __restrict__ q, const bf16* __restrict__ gate_src, int gate_ld,
-                      const unsigned char* __restrict__ kcache, const unsigned char* __restrict__ vcache,
-                      const float* __restrict__ kscale, const float* __restrict__ vscale,
-                      const int* __restrict__ block_table, int max_blocks,
-                      const int* __restrict__ seq_ids, const int* __restrict__ positions,
-                      float* __restrict__ po, float* __restrict__ pm, float* __restrict__ pl,
-                      bf16* __restrict__ out, int n_q, int n_kv, int n_splits, float scale_log2e,
+attn_split_fp8_kernel(const bf16* q, const bf16* gate_src, int gate_ld,
+                      const unsigned char* kcache, const unsigned char* vcache,
+                      const float* kscale, const float* vscale,
+                      const int* block_table, int max_blocks,
+                      const int* seq_ids, const int* positions,
+                      float* po, float* pm, float* pl,
+                      bf16* out, int n_q, int n_kv, int n_splits, float scale_log2e,
                       int gated) {
   constexpr int D = VEC * 32;
   __shared__ float s_m[8][MAXG], s_l[8][MAXG];
@@ -229,9 +229,9 @@ attn_split_fp8_kernel(const bf16* __restrict__ q, const bf16* __restrict__ gate_
 }
 
 __global__ void __launch_bounds__(256)
-attn_combine_fp8_kernel(const float* __restrict__ po, const float* __restrict__ pm,
-                        const float* __restrict__ pl, const bf16* __restrict__ gate_src, int gate_ld,
-                        bf16* __restrict__ out, int n_q, int D, int n_splits, int gated) {
+attn_combine_fp8_kernel(const float* po, const float* pm,
+                        const float* pl, const bf16* gate_src, int gate_ld,
+                        bf16* out, int n_q, int D, int n_splits, int gated) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;

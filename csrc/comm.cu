@@ -73,7 +73,7 @@ __device__ __forceinline__ uint2* oneshot_slot(unsigned char* ws, int buf, int s
 // polls the epoch half of exactly the words it sums (bounded), so the sum of an element starts
 // as soon as its last partial has landed.
 __global__ void __launch_bounds__(256)
-allreduce_finish_kernel(const Peers P, const bf16* __restrict__ residual, int ldr, bf16* __restrict__ out,
+allreduce_finish_kernel(const Peers P, const bf16* residual, int ldr, bf16* out,
                         int ldo, int M, int N) {
   pdl_launch_dependents();
   pdl_wait();
@@ -119,7 +119,7 @@ allreduce_finish_kernel(const Peers P, const bf16* __restrict__ residual, int ld
 
 // Two-shot all-reduce of `big` [T, N] bf16 partials + residual -> every rank's `out`.
 __global__ void __launch_bounds__(512)
-allreduce_twoshot_kernel(const Peers P, size_t off_big, size_t off_out, const bf16* __restrict__ residual,
+allreduce_twoshot_kernel(const Peers P, size_t off_big, size_t off_out, const bf16* residual,
                          int ldr, int ldo, int T, int N) {
   unsigned char* me = P.ws[P.rank];
   uint32_t* ctrl = reinterpret_cast<uint32_t*>(me);
@@ -196,8 +196,8 @@ allreduce_twoshot_kernel(const Peers P, size_t off_big, size_t off_out, const bf
 
 // Vocab-parallel argmax: local (value, index) per row -> all peers -> same winner everywhere.
 __global__ void __launch_bounds__(256)
-argmax_tp_kernel(const Peers P, const float* __restrict__ pv, const int* __restrict__ pi, int chunks,
-                 int v_local, int* __restrict__ out, int M) {
+argmax_tp_kernel(const Peers P, const float* pv, const int* pi, int chunks,
+                 int v_local, int* out, int M) {
   pdl_launch_dependents();
   pdl_wait();
   unsigned char* me = P.ws[P.rank];

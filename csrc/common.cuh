@@ -7,6 +7,19 @@
 
 #define TRL_API extern "C" __attribute__((visibility("default")))
 
+// ---- global loads and programmatic dependent launch -----------------------------------------
+// Every kernel of a tick calls griddepcontrol.launch_dependents first, so CTAs of several
+// consecutive kernels sit on one SM at the same time and share its L1.  A line that an older,
+// still resident kernel read (the residual stream before this layer's update, a projection
+// buffer of the previous layer) can stay in that L1 and be hit by a younger kernel after its
+// griddepcontrol.wait: measured on a B200 as a stale activation row in a two-row decode tick.
+// Data that another kernel of the stream writes is therefore never read through L1: the
+// extension is compiled with `-Xptxas -dlcm=cg` (plain global loads go to L2), and only pointers
+// to constants of a tick (weights, norm and conv vectors, tables) carry `__restrict__`, so the
+// compiler cannot route a load of an activation, a state or a batch descriptor through the
+// read-only (L1) path either.  Streaming weight loads name their cache policy explicitly
+// (ldg_stream_*).
+
 typedef __nv_bfloat16 bf16;
 typedef __nv_bfloat162 bf162;
 

@@ -31,13 +31,13 @@ constexpr int RING = 16;
 // grid = (tokens, 2*nk + nv): one CTA of D threads per (token, head); q/k heads also
 // L2-normalise, the first CTA of a token also emits the gates.
 __global__ void __launch_bounds__(128)
-gdn_prep_kernel(const bf16* __restrict__ inp, int ld, const float* __restrict__ conv_w,
+gdn_prep_kernel(const bf16* inp, int ld, const float* __restrict__ conv_w,
                 const float* __restrict__ dt_bias, const float* __restrict__ a_log,
-                const bf16* __restrict__ ring, const int* __restrict__ positions,
-                const int* __restrict__ seq_ids, const int* __restrict__ q_start,
-                const int* __restrict__ state_slots, long ring_slot_stride,
-                float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ vc,
-                float* __restrict__ gout, float* __restrict__ bout, int nk, int nv, int D, int KW) {
+                const bf16* ring, const int* positions,
+                const int* seq_ids, const int* q_start,
+                const int* state_slots, long ring_slot_stride,
+                float* qn, float* kn, float* vc,
+                float* gout, float* bout, int nk, int nv, int D, int KW) {
   __shared__ float red[32];
   pdl_launch_dependents();
   pdl_wait();
@@ -86,15 +86,15 @@ gdn_prep_kernel(const bf16* __restrict__ inp, int ld, const float* __restrict__ 
 // Thread (col, kq): col = tid % D, kq = tid / D in 0..3 owns S[kq*D/4 .. +D/4][col].
 template <int D>
 __global__ void __launch_bounds__(D * 4)
-gdn_recur_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
-                 const float* __restrict__ vc, const float* __restrict__ gin,
-                 const float* __restrict__ bin, const bf16* __restrict__ inp, int ld,
-                 float* __restrict__ states, int* __restrict__ cur, bf16* __restrict__ ring,
-                 const int* __restrict__ q_start, const int* __restrict__ q_len,
-                 const int* __restrict__ positions, const int* __restrict__ state_slots,
-                 const int* __restrict__ keep_flags, long state_slot_stride, long plane_stride,
+gdn_recur_kernel(const float* qn, const float* kn,
+                 const float* vc, const float* gin,
+                 const float* bin, const bf16* inp, int ld,
+                 float* states, int* cur, bf16* ring,
+                 const int* q_start, const int* q_len,
+                 const int* positions, const int* state_slots,
+                 const int* keep_flags, long state_slot_stride, long plane_stride,
                  long ring_slot_stride, const float* __restrict__ norm_w, float eps,
-                 float* __restrict__ o_scratch, bf16* __restrict__ out, int nk, int nv, int planes) {
+                 float* o_scratch, bf16* out, int nk, int nv, int planes) {
   constexpr int KQ = D / 4;
   __shared__ float s_q[2][D], s_k[2][D];
   __shared__ float s_part[4][2][D];
@@ -234,15 +234,15 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 template <int D>
 __global__ void __launch_bounds__(256)
-gdn_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
-                const float* __restrict__ vc, const float* __restrict__ gin,
-                const float* __restrict__ bin, const bf16* __restrict__ inp, int ld,
-                float* __restrict__ states, int* __restrict__ cur, bf16* __restrict__ ring,
-                const int* __restrict__ q_start, const int* __restrict__ q_len,
-                const int* __restrict__ positions, const int* __restrict__ state_slots,
-                const int* __restrict__ keep_flags, long state_slot_stride, long plane_stride,
+gdn_scan_kernel(const float* qn, const float* kn,
+                const float* vc, const float* gin,
+                const float* bin, const bf16* inp, int ld,
+                float* states, int* cur, bf16* ring,
+                const int* q_start, const int* q_len,
+                const int* positions, const int* state_slots,
+                const int* keep_flags, long state_slot_stride, long plane_stride,
                 long ring_slot_stride, const float* __restrict__ norm_w, float eps,
-                float* __restrict__ o_scratch, bf16* __restrict__ out, int nk, int nv, int planes) {
+                float* o_scratch, bf16* out, int nk, int nv, int planes) {
   constexpr int Q = 8;            // row groups (lanes that share a column)
   constexpr int R = D / Q;        // state rows per thread
   constexpr int NS = D / 32;      // column slices (CTAs) per head
@@ -454,15 +454,15 @@ struct alignas(16) WySmem {
 
 template <int D>
 __global__ void __launch_bounds__(256)
-gdn_scan_wy_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
-                   const float* __restrict__ vc, const float* __restrict__ gin,
-                   const float* __restrict__ bin, const bf16* __restrict__ inp, int ld,
-                   float* __restrict__ states, int* __restrict__ cur, bf16* __restrict__ ring,
-                   const int* __restrict__ q_start, const int* __restrict__ q_len,
-                   const int* __restrict__ positions, const int* __restrict__ state_slots,
+gdn_scan_wy_kernel(const float* qn, const float* kn,
+                   const float* vc, const float* gin,
+                   const float* bin, const bf16* inp, int ld,
+                   float* states, int* cur, bf16* ring,
+                   const int* q_start, const int* q_len,
+                   const int* positions, const int* state_slots,
                    long state_slot_stride, long plane_stride, long ring_slot_stride,
-                   const float* __restrict__ norm_w, float eps, float* __restrict__ o_scratch,
-                   bf16* __restrict__ out, int nk, int nv) {
+                   const float* __restrict__ norm_w, float eps, float* o_scratch,
+                   bf16* out, int nk, int nv) {
   using SM = WySmem<D>;
   constexpr int Q = SM::Q, R = SM::R, KP = SM::KP, TC = SM::TC;
   constexpr int NS = D / 32, NT = 256, NW = NT / 32, CW = 32 / Q;

@@ -538,7 +538,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
       asm volatile("bar.sync 1, 128;" ::: "memory");   // previous tile's readers are done
       for (int i = threadIdx.x - 64; i < BN; i += 128) {
         const int col = ct * BN + i;
-        rs_s[i] = col < p.cols ? __ldg(p.rs + col) : 0.f;
+        rs_s[i] = col < p.cols ? __ldcg(p.rs + col) : 0.f;   // written by the quantiser kernel just before: read through L2
       }
       ok = mbar_wait(accum_full, (uint32_t)seg & 1u, abort_flag);
       {
@@ -719,8 +719,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
 // encoded (worst gap 4..6 of 6 plus the e4m3 scale rounding) -- so no second pass over
 // the row is needed.
 __global__ void __launch_bounds__(256)
-quant_act_kernel(const bf16* __restrict__ x, int ldx, const float* __restrict__ norm_w, float eps,
-                 uint8_t* __restrict__ xq, uint8_t* __restrict__ sf, float* __restrict__ rs, int K, int J,
+quant_act_kernel(const bf16* x, int ldx, const float* __restrict__ norm_w, float eps,
+                 uint8_t* xq, uint8_t* sf, float* rs, int K, int J,
                  int kt4, int swiglu_in) {
   __shared__ float red[32];
   pdl_launch_dependents();

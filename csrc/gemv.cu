@@ -36,7 +36,7 @@ constexpr int GEMV_THREADS = 512;
 // Layout per row m: piece p (8 halves) of 32-element chunk c sits at
 // ((p * nchunks + c) * 8) halves.  Returns nothing; xs_inv[m] = 1 / applied scale.
 template <int M>
-__device__ __forceinline__ void stage_x(const bf16* __restrict__ x, int ldx, int K,
+__device__ __forceinline__ void stage_x(const bf16* x, int ldx, int K,
                                         const float* __restrict__ norm_w, float eps,
                                         __half* xs, float* xs_inv, float* red) {
   const int nchunks = K >> 5;
@@ -91,10 +91,10 @@ __device__ __forceinline__ void stage_x(const bf16* __restrict__ x, int ldx, int
 
 template <int M, int R, int EPI>
 __global__ void __launch_bounds__(GEMV_THREADS, 1)
-gemv_nvfp4_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ wq,
+gemv_nvfp4_kernel(const bf16* x, int ldx, const uint8_t* __restrict__ wq,
                   const uint8_t* __restrict__ wscale, const float* __restrict__ tscale,
-                  const float* __restrict__ norm_w, float eps, const bf16* __restrict__ residual,
-                  int ldr, void* __restrict__ yout, int ldy, int N, int K, const TrlPushArgs push) {
+                  const float* __restrict__ norm_w, float eps, const bf16* residual,
+                  int ldr, void* yout, int ldy, int N, int K, const TrlPushArgs push) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __half* xs = reinterpret_cast<__half*>(smem_raw);
   float* xs_inv = reinterpret_cast<float*>(smem_raw + (size_t)M * K * sizeof(__half));
@@ -250,10 +250,10 @@ __device__ __forceinline__ int sk_owner(int unit, int U, int W) {
 
 template <int M, int EPI>
 __global__ void __launch_bounds__(GEMV_THREADS, 1)
-gemv_nvfp4_sk_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ wq,
+gemv_nvfp4_sk_kernel(const bf16* x, int ldx, const uint8_t* __restrict__ wq,
                      const uint8_t* __restrict__ wscale, const float* __restrict__ tscale,
-                     const float* __restrict__ norm_w, float eps, const bf16* __restrict__ residual,
-                     int ldr, void* __restrict__ yout, int ldy, int N, int K, int nslot,
+                     const float* __restrict__ norm_w, float eps, const bf16* residual,
+                     int ldr, void* yout, int ldy, int N, int K, int nslot,
                      const TrlPushArgs push) {
   constexpr int W = GEMV_THREADS / 32;
   constexpr int D = 4;   // units in flight per lane: 4 x 2 rows x 16 B
@@ -413,9 +413,9 @@ gemv_nvfp4_sk_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restr
 // bf16 weights [N, K]: fp32 FMA, 8 weights per 16-byte load.  x staged as fp32.
 template <int M, int R, int EPI>
 __global__ void __launch_bounds__(GEMV_THREADS, 1)
-gemv_bf16_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ w,
-                 const float* __restrict__ norm_w, float eps, const bf16* __restrict__ residual,
-                 int ldr, void* __restrict__ yout, int ldy, int N, int K) {
+gemv_bf16_kernel(const bf16* x, int ldx, const bf16* __restrict__ w,
+                 const float* __restrict__ norm_w, float eps, const bf16* residual,
+                 int ldr, void* yout, int ldy, int N, int K) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* xs = reinterpret_cast<float*>(smem_raw);
   float* red = xs + (size_t)M * K;

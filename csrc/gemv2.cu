@@ -21,6 +21,14 @@
 // ONE contiguous byte range, two units (2304 B) per bulk copy: measured on a B200, copies of
 // 1152 B reach 4-5 TB/s of HBM reads, 2304 B and more reach 6 TB/s.
 //
+// Tensor parallelism.  A row-parallel projection pushes its fp32 partial rows into every rank's
+// one-shot slots (EPI2_PUSH, protocol of comm.cu).  The projection that consumes the reduced
+// residual stream finishes the all-reduce in ITS prologue (COOP): after the dependency wait every
+// CTA sums a small slice of the row from the slots of all ranks (bounded polls of the epoch half
+// of each word), adds the residual and stores the slice; one arrival counter plus a release word
+// in the workspace form a grid barrier, after which every CTA stages the whole row as usual.  No
+// separate finishing launch sits between the two projections.
+//
 // Arithmetic is that of gemv.cu: e2m1 -> f16x2 by the native cvt, f16x2 FMA inside a
 // 16-element scale block, fp32 across blocks, per-row power-of-two activation scale.
 //
@@ -101,7 +109,9 @@ __device__ __forceinline__ void g2_stage_x(const bf16* __restrict__ x, int ldx, 
     for (int i = 0; i < G2_XV; ++i) {
       const int v = threadIdx.x + i * G2_THREADS;
       xv[i] = make_uint4(0u, 0u, 0u, 0u);
-      if (v < nvec) xv[i] = *reinterpret_cast<const uint4*>(xr + (size_t)v * 8);
+      // through L2: under programmatic dependent launch this CTA can share its SM (and L1) with
+      // CTAs of earlier kernels that read the previous contents of these rows
+      if (v < nvec) xv[i] = __ldcg(reinterpret_cast<const uint4*>(xr + (size_t)v * 8));
     }
 #pragma unroll
     for (int i = 0; i < G2_XV; ++i) {
@@ -170,12 +180,79 @@ __device__ __forceinline__ void g2_stage_x(const bf16* __restrict__ x, int ldx, 
   __syncthreads();
 }
 
+// Finish of the one-shot all-reduce inside the consumer (see the header).  Returns false when a
+// bounded wait ran out (the error word is set; the caller still runs to completion on whatever
+// the row holds, so no barrier of the CTA is skipped).
+constexpr size_t G2_OFF_SLOTS = 65536;     // comm.cu: one-shot slots {fp32, epoch} [2][8 src][8 rows][hmax]
+constexpr int G2_CTRL_EPOCH = 0, G2_CTRL_ARRIVE = 17, G2_CTRL_RELEASE = 20;
+__device__ __forceinline__ bool g2_coop_finish(bf16* __restrict__ x, int ldx, int M, int N, unsigned char* ws,
+                                               int world, int hmax, int* s_flag) {
+  uint32_t* ctrl = reinterpret_cast<uint32_t*>(ws);
+  if (threadIdx.x == 0) s_flag[0] = (int)(__ldcg(ctrl + G2_CTRL_EPOCH) + 1u), s_flag[1] = 1;
+  __syncthreads();
+  const uint32_t epoch = (uint32_t)s_flag[0];
+  const int buf = epoch & 1;
+  const int total = M * N;
+  const int per = (total + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int e = (int)blockIdx.x * per + (int)threadIdx.x;
+  bool ok = true;
+  // threads beyond `per` idle: a CTA's slice is a handful of elements (5120 / 444 = 12)
+  for (int i = e; i < min(total, ((int)blockIdx.x + 1) * per); i += G2_THREADS) {
+    const int m = i / N, n = i % N;
+    float v = __bfloat162float(__ldcg(x + (size_t)m * ldx + n));
+    for (int sr = 0; ok && sr < world; ++sr) {
+      const uint2* w = reinterpret_cast<const uint2*>(ws + G2_OFF_SLOTS) +
+                       ((size_t)(buf * 8 + sr) * 8 + m) * hmax + n;
+      uint2 xw = ld_relaxed_sys_v2(w);
+      if (xw.y != epoch) {
+        const long long t0 = clock64();
+        for (uint32_t it = 0; xw.y != epoch; ++it) {
+          xw = ld_relaxed_sys_v2(w);
+          if ((it & 15) == 15 && clock64() - t0 > G2_WAIT_CYCLES) {
+            trl_set_error(TRL_ERR_WAIT_TIMEOUT, 5, sr, (int)epoch);
+            ok = false;
+            break;
+          }
+        }
+      }
+      v += __uint_as_float(xw.x);
+    }
+    if (ok) x[(size_t)m * ldx + n] = __float2bfloat16(v);
+  }
+  if (!ok) s_flag[1] = 0;
+  __syncthreads();                         // this CTA's slice is stored
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t prev = atomicAdd(ctrl + G2_CTRL_ARRIVE, 1u);
+    if (prev == gridDim.x - 1) {           // every CTA has read the epoch and stored its slice
+      ctrl[G2_CTRL_ARRIVE] = 0;
+      ctrl[G2_CTRL_EPOCH] = epoch;
+      __threadfence();
+      asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ctrl + G2_CTRL_RELEASE), "r"(epoch) : "memory");
+    } else {
+      uint32_t seen;
+      const long long t0 = clock64();
+      for (uint32_t it = 0;; ++it) {
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(ctrl + G2_CTRL_RELEASE) : "memory");
+        if (seen == epoch) break;
+        if ((it & 15) == 15 && clock64() - t0 > G2_WAIT_CYCLES) {
+          trl_set_error(TRL_ERR_WAIT_TIMEOUT, 6, (int)blockIdx.x, (int)epoch);
+          s_flag[1] = 0;
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  return s_flag[1] != 0;
+}
+
 // Warp w of W owns units [w * U / W, (w + 1) * U / W): the owner of `unit` (U * W < 2^31).
 __device__ __forceinline__ int g2_owner(int unit, int U, int W) {
   return ((unit + 1) * W - 1) / U;
 }
 
-template <int M, int EPI, bool FULL>
+template <int M, int EPI, bool FULL, bool COOP>
 __global__ void __launch_bounds__(G2_THREADS, 3)
 gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ wst,
              const float* __restrict__ tscale, const float* __restrict__ norm_w, float eps,
@@ -234,6 +311,9 @@ gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ ws
   for (int i = threadIdx.x; i < pl * 2 * nslot * M; i += G2_THREADS) slots[i] = 0.f;
   pdl_launch_dependents();
   pdl_wait();
+  if (COOP)   // x is the residual stream: complete the pending all-reduce into it first
+    g2_coop_finish(const_cast<bf16*>(x), ldx, M, K, push.ws[push.rank], push.world, push.hmax,
+                   reinterpret_cast<int*>(red));
   g2_stage_x<M>(x, ldx, K, norm_w, eps, xs, xs_inv, red);   // ends with a block barrier
 
   bool ok = true;
@@ -360,7 +440,7 @@ gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ ws
         const uint2 word = make_uint2(__float_as_uint(v), epoch);
         for (int p = 0; p < push.world; ++p) st_relaxed_sys_v2(push.ws[p] + off, word);
       } else {
-        if (EPI == EPI2_RESIDUAL) v += __bfloat162float(residual[(size_t)m * ldr + n]);
+        if (EPI == EPI2_RESIDUAL) v += __bfloat162float(__ldcg(residual + (size_t)m * ldr + n));
         if (EPI == EPI2_STORE_F32)
           reinterpret_cast<float*>(yout)[(size_t)m * ldy + n] = v;
         else
@@ -400,7 +480,7 @@ int g2_num_sms() {
   return sms;
 }
 
-template <int M, int EPI>
+template <int M, int EPI, bool COOP>
 cudaError_t launch_gemv2(const bf16* x, int ldx, const uint8_t* wst, const float* ts, const float* norm_w,
                          float eps, const bf16* res, int ldr, void* y, int ldy, int N, int K, cudaStream_t st,
                          const TrlPushArgs& push) {
@@ -422,25 +502,32 @@ cudaError_t launch_gemv2(const bf16* x, int ldx, const uint8_t* wst, const float
   const size_t smem = (size_t)W * ns * STAGE_BYTES + fixed;
   static bool configured = false;
   if (!configured) {
-    cudaFuncSetAttribute(gemv2_kernel<M, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    cudaFuncSetAttribute(gemv2_kernel<M, EPI, true>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    cudaFuncSetAttribute(gemv2_kernel<M, EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    cudaFuncSetAttribute(gemv2_kernel<M, EPI, false>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    cudaFuncSetAttribute(gemv2_kernel<M, EPI, true, COOP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(gemv2_kernel<M, EPI, true, COOP>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    cudaFuncSetAttribute(gemv2_kernel<M, EPI, false, COOP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(gemv2_kernel<M, EPI, false, COOP>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     configured = true;
   }
+  if (COOP) {
+    // the grid barrier of the cooperative finish needs every CTA resident at once
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv2_kernel<M, EPI, true, COOP>, G2_THREADS, smem) != cudaSuccess ||
+        per_sm * g2_num_sms() < grid)
+      return cudaErrorInvalidValue;
+  }
   if ((K % 1024) == 0)   // every step of a row is full: 32 chunks
-    return trl_launch(gemv2_kernel<M, EPI, true>, dim3(grid), dim3(G2_THREADS), smem, st, x, ldx, wst, ts, norm_w,
-                      eps, res, ldr, y, ldy, N, K, nslot, ns, push);
-  return trl_launch(gemv2_kernel<M, EPI, false>, dim3(grid), dim3(G2_THREADS), smem, st, x, ldx, wst, ts, norm_w,
-                    eps, res, ldr, y, ldy, N, K, nslot, ns, push);
+    return trl_launch(gemv2_kernel<M, EPI, true, COOP>, dim3(grid), dim3(G2_THREADS), smem, st, x, ldx, wst, ts,
+                      norm_w, eps, res, ldr, y, ldy, N, K, nslot, ns, push);
+  return trl_launch(gemv2_kernel<M, EPI, false, COOP>, dim3(grid), dim3(G2_THREADS), smem, st, x, ldx, wst, ts,
+                    norm_w, eps, res, ldr, y, ldy, N, K, nslot, ns, push);
 }
 
-template <int EPI>
+template <int EPI, bool COOP = false>
 cudaError_t dispatch2(int M, const bf16* x, int ldx, const uint8_t* wst, const float* ts, const float* norm_w,
                       float eps, const bf16* res, int ldr, void* y, int ldy, int N, int K, cudaStream_t st,
                       const TrlPushArgs& push = TrlPushArgs()) {
-  if (M == 1) return launch_gemv2<1, EPI>(x, ldx, wst, ts, norm_w, eps, res, ldr, y, ldy, N, K, st, push);
-  if (M == 2) return launch_gemv2<2, EPI>(x, ldx, wst, ts, norm_w, eps, res, ldr, y, ldy, N, K, st, push);
+  if (M == 1) return launch_gemv2<1, EPI, COOP>(x, ldx, wst, ts, norm_w, eps, res, ldr, y, ldy, N, K, st, push);
+  if (M == 2) return launch_gemv2<2, EPI, COOP>(x, ldx, wst, ts, norm_w, eps, res, ldr, y, ldy, N, K, st, push);
   return cudaErrorInvalidValue;
 }
 
@@ -491,4 +578,25 @@ TRL_API int trl_gemv2_nvfp4_push(const void* x, int ldx, const void* wst, const 
   push.rank = rank, push.world = world, push.hmax = hmax, push.row0 = 0;
   return (int)dispatch2<EPI2_PUSH>(M, (const bf16*)x, ldx, (const uint8_t*)wst, (const float*)tscale, nullptr, 0.f,
                                    nullptr, 0, nullptr, 0, N, K, (cudaStream_t)stream, push);
+}
+
+// Consumer of a pending one-shot all-reduce: x (the residual stream, [M, K] bf16 in this rank's
+// memory) first receives residual + sum of all ranks' partial rows, then y = epi(norm(x) @ W^T)
+// (epi: plain store or SwiGLU).  ws: table of all ranks' workspaces (comm.cu layout).
+TRL_API int trl_gemv2_nvfp4_coop(void* x, int ldx, const void* wst, const void* tscale, const void* norm_w,
+                                 float eps, void* y, int ldy, int M, int N, int K, int epi, void* const* ws,
+                                 int rank, int world, int hmax, void* stream) {
+  if (trl_gemv_stream_bytes(N, K) < 0 || M < 1 || M > 2 || K > hmax || K > G2_XV * G2_THREADS * 8 || world > 8)
+    return (int)cudaErrorInvalidValue;
+  TrlPushArgs push;
+  for (int i = 0; i < 8; ++i) push.ws[i] = i < world ? (unsigned char*)ws[i] : nullptr;
+  push.rank = rank, push.world = world, push.hmax = hmax, push.row0 = 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (epi == EPI2_STORE)
+    return (int)dispatch2<EPI2_STORE, true>(M, (const bf16*)x, ldx, (const uint8_t*)wst, (const float*)tscale,
+                                            (const float*)norm_w, eps, nullptr, 0, y, ldy, N, K, st, push);
+  if (epi == EPI2_SWIGLU)
+    return (int)dispatch2<EPI2_SWIGLU, true>(M, (const bf16*)x, ldx, (const uint8_t*)wst, (const float*)tscale,
+                                             (const float*)norm_w, eps, nullptr, 0, y, ldy, N, K, st, push);
+  return (int)cudaErrorInvalidValue;
 }

@@ -7,8 +7,8 @@
 
 namespace {
 
-__global__ void embedding_kernel(const bf16* __restrict__ table, const int* __restrict__ ids,
-                                 bf16* __restrict__ out, int H, int V) {
+__global__ void embedding_kernel(const bf16* __restrict__ table, const int* ids,
+                                 bf16* out, int H, int V) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -23,8 +23,8 @@ __global__ void embedding_kernel(const bf16* __restrict__ table, const int* __re
   for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
 }
 
-__global__ void gather_rows_kernel(const bf16* __restrict__ x, const int* __restrict__ idx,
-                                   bf16* __restrict__ out, int H) {
+__global__ void gather_rows_kernel(const bf16* x, const int* idx,
+                                   bf16* out, int H) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -34,7 +34,7 @@ __global__ void gather_rows_kernel(const bf16* __restrict__ x, const int* __rest
 }
 
 __global__ void __launch_bounds__(256)
-rmsnorm_kernel(const bf16* __restrict__ x, const float* __restrict__ w, bf16* __restrict__ out, int H,
+rmsnorm_kernel(const bf16* x, const float* __restrict__ w, bf16* out, int H,
                float eps) {
   __shared__ float red[32];
   pdl_launch_dependents();
@@ -54,7 +54,7 @@ rmsnorm_kernel(const bf16* __restrict__ x, const float* __restrict__ w, bf16* __
   }
 }
 
-__global__ void swiglu_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, long n_out) {
+__global__ void swiglu_kernel(const bf16* gu, bf16* out, long n_out) {
   pdl_launch_dependents();
   pdl_wait();
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n_out; i += (long)gridDim.x * blockDim.x) {
@@ -70,8 +70,8 @@ __device__ __forceinline__ void argmax_merge(float& best, int& bi, float ov, int
   if (ov > best || (ov == best && oi < bi)) best = ov, bi = oi;
 }
 __global__ void __launch_bounds__(256)
-argmax_stage1_kernel(const float* __restrict__ logits, int ld, int V, float* __restrict__ pv,
-                     int* __restrict__ pi) {
+argmax_stage1_kernel(const float* logits, int ld, int V, float* pv,
+                     int* pi) {
   __shared__ float sv[8];
   __shared__ int si[8];
   pdl_launch_dependents();
@@ -96,7 +96,7 @@ argmax_stage1_kernel(const float* __restrict__ logits, int ld, int V, float* __r
   }
 }
 __global__ void __launch_bounds__(64)
-argmax_stage2_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int* __restrict__ out) {
+argmax_stage2_kernel(const float* pv, const int* pi, int* out) {
   pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.x;
@@ -118,8 +118,8 @@ argmax_stage2_kernel(const float* __restrict__ pv, const int* __restrict__ pi, i
 }
 
 // Fused AdamW on fp32 master + moments; optionally refreshes a bf16 copy.
-__global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
-                             const float* __restrict__ g, bf16* __restrict__ p_bf16, long n, float lr,
+__global__ void adamw_kernel(float* p, float* m, float* v,
+                             const float* g, bf16* p_bf16, long n, float lr,
                              float b1, float b2, float eps, float wd, float c1, float c2, float gscale) {
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
     const float gi = g[i] * gscale;
@@ -137,7 +137,7 @@ __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float
 // per 16-element block; writes 8 packed bytes + 1 e4m3 scale.
 template <typename T>
 __global__ void quant_nvfp4_kernel(const T* __restrict__ w, const float* __restrict__ tscale,
-                                   uint8_t* __restrict__ wq, uint8_t* __restrict__ sc, long nblocks) {
+                                   uint8_t* __restrict__ wq, uint8_t* sc, long nblocks) {
   const float ts = *tscale;
   for (long b = blockIdx.x * (long)blockDim.x + threadIdx.x; b < nblocks; b += (long)gridDim.x * blockDim.x) {
     float x[16];
@@ -167,8 +167,8 @@ __global__ void quant_nvfp4_kernel(const T* __restrict__ w, const float* __restr
 }
 
 // NVFP4 -> bf16 dense matrix (8 elements per thread).
-__global__ void dequant_nvfp4_kernel(const uint8_t* __restrict__ wq, const uint8_t* __restrict__ sc,
-                                     const float* __restrict__ tscale, bf16* __restrict__ out, long n8) {
+__global__ void dequant_nvfp4_kernel(const uint8_t* __restrict__ wq, const uint8_t* sc,
+                                     const float* __restrict__ tscale, bf16* out, long n8) {
   const float ts = *tscale;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
     const uint32_t w = reinterpret_cast<const uint32_t*>(wq)[i];
@@ -188,7 +188,7 @@ __global__ void dequant_nvfp4_kernel(const uint8_t* __restrict__ wq, const uint8
 
 // out[i] = a[i] + b[i] (bf16), used by the large-M path where the residual add is
 // not folded into a GEMV epilogue.
-__global__ void add_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, bf16* __restrict__ out, long n2) {
+__global__ void add_kernel(const bf16* a, const bf16* b, bf16* out, long n2) {
   pdl_launch_dependents();
   pdl_wait();
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n2; i += (long)gridDim.x * blockDim.x) {
@@ -202,11 +202,11 @@ __global__ void add_kernel(const bf16* __restrict__ a, const bf16* __restrict__ 
 // bump position / KV length, recompute the KV write slot from the block table and
 // append the token to a history row.  Lets a captured decode tick be replayed
 // back to back with no host round trip.
-__global__ void decode_advance_kernel(const int* __restrict__ tok, int* __restrict__ ids,
-                                      int* __restrict__ pos, int* __restrict__ smap,
-                                      int* __restrict__ kvlen, const int* __restrict__ table, int B,
-                                      int max_blocks, int* __restrict__ hist, int hist_cap,
-                                      int* __restrict__ hist_n) {
+__global__ void decode_advance_kernel(const int* tok, int* ids,
+                                      int* pos, int* smap,
+                                      int* kvlen, const int* __restrict__ table, int B,
+                                      int max_blocks, int* hist, int hist_cap,
+                                      int* hist_n) {
   pdl_launch_dependents();
   pdl_wait();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
@@ -225,7 +225,7 @@ __global__ void decode_advance_kernel(const int* __restrict__ tok, int* __restri
 }
 
 template <typename T>
-__global__ void absmax_kernel(const T* __restrict__ w, long n, float* __restrict__ out) {
+__global__ void absmax_kernel(const T* __restrict__ w, long n, float* out) {
   __shared__ float red[32];
   float a = 0.f;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x)
@@ -255,9 +255,9 @@ __device__ __forceinline__ float sample_u01(unsigned long long seed) {
 }
 
 __global__ void __launch_bounds__(1024)
-sample_softmax_kernel(const float* __restrict__ logits, int ld, const int* __restrict__ rows,
-                      const long long* __restrict__ seeds, const float* __restrict__ inv_temp,
-                      int* __restrict__ out_tok, float* __restrict__ out_lp, int V) {
+sample_softmax_kernel(const float* logits, int ld, const int* rows,
+                      const long long* seeds, const float* inv_temp,
+                      int* out_tok, float* out_lp, int V) {
   __shared__ float s_red[32];
   __shared__ float s_sum[1024];
   __shared__ float s_bcast[2];
@@ -425,7 +425,7 @@ __device__ __forceinline__ void nuc_pick(NucShared& sh, unsigned prefix, unsigne
   }
 }
 
-__device__ unsigned nuc_select(NucShared& sh, const float* __restrict__ lg, float it, float mx, int V, bool by_mass,
+__device__ unsigned nuc_select(NucShared& sh, const float* lg, float it, float mx, int V, bool by_mass,
                                unsigned long long need, unsigned qcap, int tid) {
   unsigned prefix = 0;
   for (int pass = 0; pass < 3; ++pass) {
@@ -458,10 +458,10 @@ __device__ unsigned nuc_select(NucShared& sh, const float* __restrict__ lg, floa
 }
 
 __global__ void __launch_bounds__(1024)
-sample_nucleus_kernel(const float* __restrict__ logits, int ld, const int* __restrict__ rows,
-                      const long long* __restrict__ seeds, const float* __restrict__ inv_temp,
-                      const int* __restrict__ top_k, const float* __restrict__ top_p, int* __restrict__ out_tok,
-                      float* __restrict__ out_lp, int V) {
+sample_nucleus_kernel(const float* logits, int ld, const int* rows,
+                      const long long* seeds, const float* inv_temp,
+                      const int* top_k, const float* top_p, int* out_tok,
+                      float* out_lp, int V) {
   __shared__ NucShared sh;
   const int b = blockIdx.x, tid = threadIdx.x;
   pdl_wait();
@@ -662,8 +662,8 @@ sample_nucleus_kernel(const float* __restrict__ logits, int ld, const int* __res
 // grid (tokens, rank) and (tokens, ceil(N / 256)).  A, B are the fp32 trainable tensors.
 // Parity: `_linear` of src/tilerl/model.py:379-385 (two `linear` calls there).
 __global__ void __launch_bounds__(256)
-lora_a_kernel(const bf16* __restrict__ x, int ldx, const float* __restrict__ norm_w, float eps,
-              const float* __restrict__ A, float* __restrict__ t, int K, int R) {
+lora_a_kernel(const bf16* x, int ldx, const float* __restrict__ norm_w, float eps,
+              const float* __restrict__ A, float* t, int K, int R) {
   __shared__ float red[32];
   pdl_launch_dependents();
   pdl_wait();
@@ -686,7 +686,7 @@ lora_a_kernel(const bf16* __restrict__ x, int ldx, const float* __restrict__ nor
 }
 
 __global__ void __launch_bounds__(256)
-lora_b_kernel(const float* __restrict__ t, const float* __restrict__ B, bf16* __restrict__ y, int ldy, int N,
+lora_b_kernel(const float* t, const float* __restrict__ B, bf16* y, int ldy, int N,
               int R, float s) {
   __shared__ float ts[64];
   pdl_launch_dependents();

@@ -96,7 +96,7 @@ __device__ __forceinline__ void z_done(const ZPeers& P, uint32_t epoch, int* las
 // Four independent 16-byte peer loads per thread and pass: NVLink latency is ~2 us, so the
 // bytes in flight, not the instruction count, set the rate.
 __global__ void __launch_bounds__(512)
-zero_allgather_kernel(const ZPeers P, size_t off, long shard_vecs, uint4* __restrict__ dst) {
+zero_allgather_kernel(const ZPeers P, size_t off, long shard_vecs, uint4* dst) {
   __shared__ int ok_s, last_s;
   const uint32_t epoch = reinterpret_cast<const uint32_t*>(P.ws[P.rank])[0] + 1;
   if (z_ready(P, epoch, &ok_s)) {
@@ -117,7 +117,7 @@ zero_allgather_kernel(const ZPeers P, size_t off, long shard_vecs, uint4* __rest
 
 template <bool BF16>
 __global__ void __launch_bounds__(512)
-zero_reduce_scatter_kernel(const ZPeers P, size_t off, long shard_elems, float scale, float* __restrict__ out,
+zero_reduce_scatter_kernel(const ZPeers P, size_t off, long shard_elems, float scale, float* out,
                            int accumulate) {
   __shared__ int ok_s, last_s;
   const uint32_t epoch = reinterpret_cast<const uint32_t*>(P.ws[P.rank])[0] + 1;

@@ -33,7 +33,7 @@ def _worker_body(rank, world, port, out):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     from tilerl_b200.batch import Batch
-    from tilerl_b200.config import small_gpu
+    from tilerl_b200.config import small_gpu_tp as small_gpu
     from tilerl_b200.engine import SamplingParams
     from tilerl_b200.factory import build_engine, build_model, make_ops
     from tilerl_b200.ops import native
@@ -47,8 +47,43 @@ def _worker_body(rank, world, port, out):
     g = torch.Generator().manual_seed(5)
     prompts = [torch.randint(0, cfg.vocab, (40,), generator=g).tolist() for _ in range(2)]
     eng = build_engine(model, ops, slots=4, max_ctx=256, graph=True, prefix=False)
+
+    def prompt_logits(m, o, e, forced=None, forced_next=(1, 2)):
+        """Full-vocabulary logits (a) of every position of prompt 0 followed by `forced` tokens in
+        one prefill (tensor-core GEMM + two-shot all-reduce path) and (b) of one decode step of BOTH
+        prompts in one batch after their prefill (2-row GEMV path with the fused one-shot
+        all-reduce), on fresh blocks."""
+        seqs = []
+        for pr in prompts:
+            blocks = [e.kv.alloc_block() for _ in range(6)]
+            slot = e.states.alloc_slot()
+            e.states.states[slot].zero_(), e.states.ring[slot].zero_()
+            e.states.cur[slot] = 0
+            seqs.append((pr, blocks, slot))
+        full = prompts[0] + list(forced or [])
+        b = Batch.build([dict(tokens=full, start=0, blocks=seqs[0][1], slot=seqs[0][2])], dev)
+        lg_all = o.full_logits(m.forward(b, o, e.kv, e.states, last_only=False)).float()[:, :cfg.vocab].cpu()
+        e.states.states[seqs[0][2]].zero_(), e.states.ring[seqs[0][2]].zero_()
+        e.states.cur[seqs[0][2]] = 0
+        b = Batch.build([dict(tokens=pr, start=0, blocks=bl, slot=sl) for pr, bl, sl in seqs], dev)
+        m.forward(b, o, e.kv, e.states)
+        nxt = forced_next      # both engines decode the same tokens, whatever their own argmax
+        b = Batch.build([dict(tokens=[nx], start=len(pr), blocks=bl, slot=sl)
+                         for nx, (pr, bl, sl) in zip(nxt, seqs)], dev)
+        lg1 = o.full_logits(m.forward(b, o, e.kv, e.states)).float()[:, :cfg.vocab].cpu()
+        for _, blocks, slot in seqs:
+            for blk in blocks:
+                e.kv.release(blk)
+            e.states.release(slot)
+        return lg_all, lg1
+
     res = eng.generate(prompts, SamplingParams(max_tokens=10))
     toks = [r.tokens for r in res]
+    # the same requests with the all-reduce finished by its own kernel: same sums in the same order
+    comm.fuse_finish = False
+    eng_u = build_engine(model, ops, slots=4, max_ctx=256, graph=True, prefix=False)
+    toks_unfused = [r.tokens for r in eng_u.generate(prompts, SamplingParams(max_tokens=10))]
+    comm.fuse_finish = True
     # sampled request exercises the full-logits gather
     samp = eng.generate([prompts[0]], SamplingParams(max_tokens=4, temperature=1.0, seed=3))[0].tokens
     samp2 = eng.generate([prompts[0]], SamplingParams(max_tokens=4, temperature=1.0, seed=3))[0].tokens
@@ -63,8 +98,27 @@ def _worker_body(rank, world, port, out):
         e1 = build_engine(m1, ops1, slots=4, max_ctx=256, graph=True, prefix=False)
         want = [r.tokens for r in e1.generate(prompts, SamplingParams(max_tokens=10))]
         want_s = e1.generate([prompts[0]], SamplingParams(max_tokens=4, temperature=1.0, seed=3))[0].tokens
-        out.put(dict(toks=toks, want=want, samp=samp, samp2=samp2, want_s=want_s, err=err,
-                     graph=eng.counters["graph_ticks"], vocab=cfg.vocab))
+        out.put(dict(toks=toks, toks_unfused=toks_unfused, want=want, samp=samp, samp2=samp2, want_s=want_s,
+                     err=err, graph=eng.counters["graph_ticks"], vocab=cfg.vocab))
+    # teacher-forced comparison: every rank runs the TP forward over prompt 0 + the single-GPU
+    # engine's tokens; rank 0 runs the same on one GPU
+    forced = [None, None]
+    if rank == 0:
+        forced = [want[0], [w[0] for w in want]]
+    dist.broadcast_object_list(forced, src=0)
+    lg = prompt_logits(model, ops, eng, forced[0], forced[1])
+    if rank == 0:
+        ref_all, ref_dec = prompt_logits(m1, ops1, e1, forced[0], forced[1])
+        tp_all, tp_dec = lg
+        rel = [float((tp_all - ref_all).norm() / ref_all.norm())] + \
+              [float((tp_dec[i] - ref_dec[i]).norm() / ref_dec[i].norm()) for i in range(tp_dec.shape[0])]
+        # positions where the two engines pick different tokens must be near-ties of the reference
+        pick_tp, pick_ref = tp_all.argmax(-1), ref_all.argmax(-1)
+        err_abs = (tp_all - ref_all).abs().max(-1).values
+        gap = ref_all.gather(1, pick_ref[:, None])[:, 0] - ref_all.gather(1, pick_tp[:, None])[:, 0]
+        bad = int(((pick_tp != pick_ref) & (gap > 2 * err_abs)).sum())
+        out.put(dict(rel=rel, bad=bad, flips=int((pick_tp != pick_ref).sum()), positions=int(pick_ref.numel()),
+                     dec_same=int((tp_dec.argmax(-1) == ref_dec.argmax(-1)).sum())))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -73,12 +127,9 @@ def _worker_body(rank, world, port, out):
 def test_tp_engine_matches_single_gpu(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    from tilerl_b200.config import small_gpu
+    from tilerl_b200.config import small_gpu_tp
     from tilerl_b200.parallel.mesh import check_alignment
-    try:
-        check_alignment(small_gpu(), world)
-    except ValueError as e:
-        pytest.skip(f"the small test model does not divide {world} ways: {e}")
+    check_alignment(small_gpu_tp(), world)    # the gate model divides 2, 4 and 8 ways: nothing is skipped
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
@@ -87,6 +138,9 @@ def test_tp_engine_matches_single_gpu(world):
     for p in procs:
         p.start()
     res = out.get(timeout=600)
+    if "error" not in res:
+        res2 = out.get(timeout=600)
+        res = {**res, **res2} if "error" not in res2 else res2
     if "error" in res:
         for p in procs:
             p.kill()
@@ -96,12 +150,112 @@ def test_tp_engine_matches_single_gpu(world):
         assert p.exitcode == 0
     assert res["err"][0] == 0, res["err"]
     assert res["graph"] >= 8
-    # greedy tokens: identical up to rare near-ties from the different summation order
-    agree = sum(a == b for t, w in zip(res["toks"], res["want"]) for a, b in zip(t, w))
-    assert agree >= 18, (res["toks"], res["want"])
-    assert res["toks"][0][:3] == res["want"][0][:3]
+    # logits of the prefill path and of a decode step: the TP engine sums the same products in another
+    # order and rounds each rank's partial rows (bf16 on the prefill path) before the sum, so it agrees
+    # with one GPU to bf16 rounding carried through the layers (measured 1-2 % of the logit norm)
+    assert max(res["rel"]) < 3e-2, res["rel"]
+    # teacher-forced over prompt 0 + 10 tokens: wherever TP and one GPU pick different tokens, the
+    # reference's own margin between the two is within twice the largest logit difference there
+    assert res["bad"] == 0, res
+    assert res["flips"] <= res["positions"] // 8, res
+    # fused (finish inside the consuming GEMV) and stand-alone finishing kernels sum the same
+    # values in the same order: identical tokens, not merely close ones
+    assert res["toks"] == res["toks_unfused"], (res["toks"], res["toks_unfused"])
+    assert [t[0] for t in res["toks"]] == [w[0] for w in res["want"]]
     # sampling: the random-init model's distribution is almost flat, so the token drawn at a
     # fixed seed moves with rounding-level logit differences between TP degrees; what must hold
     # is that a TP engine repeats itself and draws valid ids through the gathered vocab shards
     assert res["samp"] == res["samp2"] and len(res["samp"]) == 4
     assert all(0 <= t < res["vocab"] for t in res["samp"])
+
+
+def _ops_worker(rank, world, port, out):
+    try:
+        import torch.distributed as dist
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        from tilerl_b200 import formats as F
+        from tilerl_b200.factory import make_ops
+        from tilerl_b200.ops import native, ref
+        from tilerl_b200.parallel.symm import SymmComm
+        h, kfull, n2 = 1024, 2048, 1536
+        comm = SymmComm.create(dist.group.WORLD, dev, hmax=h, tmax=64)
+        ops = make_ops(dev, tp_comm=comm)
+        g = torch.Generator().manual_seed(11)
+        w_row = torch.randn(h, kfull, generator=g) * 0.02            # row-parallel: K sharded
+        w_col = torch.randn(n2, h, generator=g) * 0.02               # its consumer (replicated here)
+        nw = (1 + 0.1 * torch.randn(h, generator=g)).to(dev)
+        ks = kfull // world
+        wq_row = F.quantize_nvfp4(w_row[:, rank * ks:(rank + 1) * ks].contiguous()).to(dev)
+        wq_col = F.quantize_nvfp4(w_col).to(dev)
+        results = {}
+        for t in (1, 2):
+            a_full = (torch.randn(t, kfull, generator=g) * 3).to(torch.bfloat16)
+            x0 = torch.randn(t, h, generator=g).to(torch.bfloat16)
+            a = a_full[:, rank * ks:(rank + 1) * ks].contiguous().to(dev)
+            # fp32 statement: every rank's partial of ITS quantised shard, summed in rank order
+            parts = [None] * world
+            part = ref.linear(a, wq_row).float()
+            dist.all_gather_object(parts, part.cpu())
+            want_x = x0.float()
+            for p_ in parts:
+                want_x = want_x + p_
+            want_x = want_x.to(torch.bfloat16)
+            for fused in (True, False):
+                comm.fuse_finish = fused
+                x = ops.ws.get("x", (t, h), torch.bfloat16)
+                x.copy_(x0.to(dev))
+                for rep in range(3):       # consecutive all-reduces alternate the slot buffers
+                    if rep:
+                        x.copy_(x0.to(dev))
+                    ops.linear_residual(a, wq_row, x)
+                    y = ops.norm_linear(x, nw, wq_col, 1e-6).clone()
+                    ops.settle()
+                    torch.cuda.synchronize()
+                    dist.barrier()
+                want_y = ref.linear(ref.rmsnorm(want_x.to(dev), nw, 1e-6).to(torch.bfloat16), wq_col)
+                results[(t, fused)] = (float((x.float().cpu() - want_x.float()).abs().max()),
+                                       float((y.float() - want_y.float()).norm() / want_y.float().norm()),
+                                       x.clone().cpu(), y.cpu())
+        err = native.read_error()
+        if rank == 0:
+            out.put(dict(err=err, res={k: v[:2] for k, v in results.items()},
+                         same={t: bool(torch.equal(results[(t, True)][2], results[(t, False)][2]) and
+                                       torch.equal(results[(t, True)][3], results[(t, False)][3])) for t in (1, 2)}))
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:  # noqa: BLE001
+        import traceback
+        out.put(dict(error=f"rank {rank}:\n{traceback.format_exc()}"))
+        raise
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tp_row_parallel_gemv_with_allreduce_finished_by_its_consumer(world):
+    """One row-parallel projection (push epilogue) followed by the projection that consumes the
+    residual stream, for 1 and 2 rows: the all-reduce finished inside the consumer's prologue gives
+    the bits of the stand-alone finishing kernel and both match the fp32 statement."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ops_worker, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = out.get(timeout=300)
+    if "error" in res:
+        for p in procs:
+            p.kill()
+        pytest.fail(res["error"])
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert res["err"][0] == 0, res["err"]
+    for (t, fused), (dx, ry) in res["res"].items():
+        assert dx <= 0.0625, (t, fused, dx)        # one bf16 step of the residual stream's magnitude
+        assert ry < 8e-3, (t, fused, ry)
+    assert all(res["same"].values()), res["same"]

@@ -24,6 +24,8 @@ OBJ = os.path.join(ROOT, "build", "obj")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-rdc=true", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
+    # global loads bypass L1: see "global loads and programmatic dependent launch" in csrc/common.cuh
+    "-Xptxas", "-dlcm=cg",
 ]
 
 

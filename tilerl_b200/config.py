@@ -193,9 +193,22 @@ def small_gpu() -> ModelConfig:
     )
 
 
+def small_gpu_tp() -> ModelConfig:
+    """:func:`small_gpu` with head counts and widths that divide 2, 4 and 8 ways (8 q / 2 kv
+    heads -- kv heads replicated from 4 ranks on, as the 27B's 4 kv heads are at 8 --, 8 key /
+    16 value GDN heads, FFN 4096): the model of the tensor-parallel GPU gates."""
+    types = (GDN, GDN, GDN, ATTN)
+    return ModelConfig(
+        name="small-gpu-tp", hidden=1024, ffn=4096, vocab=32768, layer_types=types,
+        n_q_heads=8, n_kv_heads=2, head_dim=256, rotary_dim=64, rope_theta=1e7,
+        gdn_k_heads=8, gdn_v_heads=16, gdn_head_dim=128, gdn_conv=4,
+        rms_eps=1e-6, max_ctx=65536, tie_embeddings=False, quant="nvfp4",
+    )
+
+
 _REGISTRY = {
     "qwen38-27b": qwen38_27b, "qwen36-27b": qwen36_27b, "tiny": tiny,
-    "tiny-hybrid": tiny_hybrid, "small-gpu": small_gpu,
+    "tiny-hybrid": tiny_hybrid, "small-gpu": small_gpu, "small-gpu-tp": small_gpu_tp,
     "tiny-agent": lambda: tiny(65536),
 }
 

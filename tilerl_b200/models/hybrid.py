@@ -194,6 +194,7 @@ class HybridModel:
         cfg, P, d = self.cfg, self.params, self.dims
         eps = cfg.rms_eps
         x = ops.embed(P["embed"], batch.token_ids)
+        settle = getattr(ops, "settle", lambda: None)   # tensor parallelism: complete a deferred all-reduce
         taps = {}
         ai = gi = 0
         for i, t in enumerate(cfg.layer_types):
@@ -214,7 +215,9 @@ class HybridModel:
                                          self._lora(p + "gate_up"))
             x = ops.linear_residual(act, P[p + "down"], x, self._lora(p + "down"))
             if i in aux_layers:
+                settle()
                 taps[i] = x.clone()  # the residual stream is updated in place
+        settle()
         xs = x[batch.last_idx.long()] if last_only else x
         head = P["embed"] if cfg.tie_embeddings else P["lm_head"]
         logits = ops.lm_head(xs, P["final_norm"], head, eps)[..., :cfg.vocab]

@@ -92,10 +92,23 @@ class CudaOps:
         assert t.dtype == torch.float32 and t.is_cuda, "norm/vector parameters must be fp32 on device"
         return t
 
+    def settle(self) -> None:
+        """Make the residual stream current: complete an all-reduce that a row-parallel projection
+        left pending for its consumer (tensor parallelism only)."""
+        if self.comm is not None and getattr(self.comm, "pending", None) is not None:
+            self.comm.settle()
+
     def _gemv(self, x, w, y, *, norm_w=None, eps=0.0, residual=None, epi=EPI_STORE):
         m, k = x.shape
-        if isinstance(w, NVFP4Tensor) and m <= 2 and self.gemv_stream and self._stream_ok(w) \
-                and (m * k * 2 <= 88 * 1024) and k <= 18432:
+        stream = isinstance(w, NVFP4Tensor) and m <= 2 and self.gemv_stream and self._stream_ok(w) \
+            and (m * k * 2 <= 88 * 1024) and k <= 18432
+        if self.comm is not None and getattr(self.comm, "pending", None) is not None:
+            if stream and norm_w is not None and residual is None and epi in (EPI_STORE, EPI_SWIGLU):
+                from .gemm_tc import w_stream
+                if self.comm.consume_pending(x, w_stream(w), w.tscale, norm_w, eps, y, w.wq.shape[0], epi):
+                    return
+            self.comm.settle()
+        if stream:
             from .gemm_tc import w_stream
             n = w.wq.shape[0]
             N.check(self.lib.trl_gemv2_nvfp4(
@@ -137,6 +150,8 @@ class CudaOps:
     def _linear(self, x, w, y, *, norm_w=None, eps=0.0, residual=None, epi=EPI_STORE):
         """``y = epi(norm(x) @ W^T)`` with everything fused into one or two kernels."""
         t = x.shape[0]
+        if not (t <= GEMV_MAX_M and not self._tc(w, t)):
+            self.settle()     # only the GEMV path can finish a pending all-reduce itself
         if self._tc(w, t):
             from .gemm_tc import gemm_nvfp4
             terms = self.terms_small if t <= GEMV_MAX_M else self.terms_large
@@ -160,6 +175,7 @@ class CudaOps:
         N.count()
 
     def _rmsnorm(self, x, w, eps, name="h"):
+        self.settle()
         t, h = x.shape
         out = self.ws.get(name, (t, h), torch.bfloat16)
         N.check(self.lib.trl_rmsnorm(x.data_ptr(), w.data_ptr(), out.data_ptr(), t, h, eps, N.stream()), "rmsnorm")
@@ -170,6 +186,7 @@ class CudaOps:
         """``y += s * (norm(x) A^T) B^T`` in place (two small kernels; the norm is recomputed
         inside the first, so no normalised copy of x is materialised)."""
         if lora is not None:
+            self.settle()
             a, b, s = lora
             t, k = x.shape
             n, r = b.shape
@@ -187,6 +204,7 @@ class CudaOps:
 
     # ---- op surface --------------------------------------------------------------------
     def embed(self, table, ids):
+        self.settle()
         t, h = ids.shape[0], table.shape[1]
         x = self.ws.get("x", (t, h), torch.bfloat16)
         N.check(self.lib.trl_embedding(table.data_ptr(), ids.data_ptr(), x.data_ptr(), t, h, table.shape[0],
@@ -342,6 +360,7 @@ class CudaOps:
         return out
 
     def lm_head(self, x, norm_w, w, eps):
+        self.settle()
         m = x.shape[0]
         n = w.shape[0]
         logits = self.ws.get("logits", (m, n), torch.float32)

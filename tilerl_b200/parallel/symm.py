@@ -7,7 +7,10 @@ workspace.  After that no library collective is on the decode path:
 
 * ``linear_allreduce_residual`` -- row-parallel projection + all-reduce + residual add.
   Up to 8 tokens: the GEMV pushes fp32 partial rows into every peer's slot from its
-  epilogue and ``allreduce_finish`` sums them (one-shot).  More tokens: the GEMM writes
+  epilogue (one-shot); the sum is completed by the NEXT projection's prologue
+  (``consume_pending``: the streamed GEMV polls the slots, adds the residual and stores the
+  row before it normalises it) or, where the next reader of the residual stream is another
+  kind of kernel, by ``allreduce_finish`` (``settle``).  More tokens: the GEMM writes
   its partial into the symmetric ``big`` region and one two-shot kernel reduce-scatters
   by peer loads and all-gathers by peer stores straight into every rank's residual stream.
 * ``argmax`` -- vocab-parallel argmax with a (max, index) exchange.
@@ -38,6 +41,7 @@ for _name, _sig in {
     "trl_allreduce_twoshot": [N.P, N.I, N.I, N.I, N.I, N.P, N.I, N.I, N.I, N.I, N.P],
     "trl_argmax_tp": [N.P, N.I, N.I, N.I, N.P, N.P, N.I, N.I, N.P, N.I, N.P],
     "trl_gemv_nvfp4_push": [N.P, N.I, N.P, N.P, N.P, N.P, N.I, N.I, N.I, N.I, N.I, N.I, N.P],
+    "trl_gemv2_nvfp4_coop": [N.P, N.I, N.P, N.P, N.P, N.F, N.P, N.I, N.I, N.I, N.I, N.I, N.P, N.I, N.I, N.I, N.P],
 }.items():
     N.register(_name, _sig)
 
@@ -79,6 +83,11 @@ class SymmComm:
         out0 = self.lib.trl_symm_out_offset(hmax, tmax)
         self.big = self.mem[big0:big0 + tmax * hmax * 2].view(torch.bfloat16)
         self.xres = self.mem[out0:out0 + tmax * hmax * 2].view(torch.bfloat16)
+        # a one-shot all-reduce whose partial rows are pushed but not yet summed into the residual
+        # stream: (rows, columns, residual tensor)
+        self.pending = None
+        self.fuse_finish = __import__("os").environ.get("TRL_FUSE_FINISH", "1") != "0"
+        self.stream_push = __import__("os").environ.get("TRL_GEMV_STREAM_PUSH", "1") != "0"
         dist.barrier(group=group)
 
     @classmethod
@@ -97,8 +106,9 @@ class SymmComm:
         t, k = a.shape
         n = w.shape[0]
         st = N.stream()
+        self.settle()
         if t <= min(8, getattr(ops, "gemv_tokens", 8)) and isinstance(w, NVFP4Tensor) and lora is None:
-            if t <= 2 and getattr(ops, "gemv_stream", False) and ops._stream_ok(w) and t * k * 2 <= 88 * 1024 and k <= 18432:
+            if t <= 2 and getattr(ops, "gemv_stream", False) and self.stream_push and ops._stream_ok(w) and t * k * 2 <= 88 * 1024 and k <= 18432:
                 from ..ops.gemm_tc import w_stream
                 N.check(self.lib.trl_gemv2_nvfp4_push(a.data_ptr(), a.stride(0), w_stream(w).data_ptr(),
                                                       w.tscale.data_ptr(), self.table, self.rank, self.world,
@@ -107,10 +117,10 @@ class SymmComm:
                 N.check(self.lib.trl_gemv_nvfp4_push(a.data_ptr(), a.stride(0), w.wq.data_ptr(), w.scale.data_ptr(),
                                                      w.tscale.data_ptr(), self.table, self.rank, self.world, self.hmax,
                                                      t, n, k, st), "gemv_push")
-            N.check(self.lib.trl_allreduce_finish(self.table, self.rank, self.world, self.hmax, residual.data_ptr(),
-                                                  residual.stride(0), residual.data_ptr(), residual.stride(0),
-                                                  t, n, st), "allreduce_finish")
-            N.count((t + 3) // 4 + 1)
+            self.pending = (t, n, residual)
+            N.count((t + 3) // 4)
+            if not self.fuse_finish:
+                self.settle()
             return residual
         # large-M: local partial into the symmetric region, then one two-shot kernel
         assert residual.data_ptr() == self.xres.data_ptr(), "residual stream must live in symmetric memory"
@@ -124,6 +134,35 @@ class SymmComm:
                 "allreduce_twoshot")
         N.count()
         return residual
+
+    def settle(self) -> None:
+        """Complete a pending one-shot all-reduce with the stand-alone finishing kernel."""
+        if self.pending is None:
+            return
+        t, n, residual = self.pending
+        self.pending = None
+        N.check(self.lib.trl_allreduce_finish(self.table, self.rank, self.world, self.hmax, residual.data_ptr(),
+                                              residual.stride(0), residual.data_ptr(), residual.stride(0),
+                                              t, n, N.stream()), "allreduce_finish")
+        N.count()
+
+    def consume_pending(self, x, wst, tscale, norm_w, eps, y, n_out: int, epi: int) -> bool:
+        """Run ``y = epi(norm(x) @ W^T)`` with the pending all-reduce into ``x`` completed by the same
+        kernel.  False (nothing launched) when ``x`` is not the pending residual rows."""
+        if self.pending is None:
+            return False
+        t, n, residual = self.pending
+        if (x.data_ptr() != residual.data_ptr() or x.shape[0] != t or x.shape[1] != n or n > self.hmax
+                or x.stride(0) != residual.stride(0)):
+            return False
+        rc = self.lib.trl_gemv2_nvfp4_coop(x.data_ptr(), x.stride(0), wst.data_ptr(), tscale.data_ptr(),
+                                           norm_w.data_ptr(), eps, y.data_ptr(), y.stride(0), t, n_out, n, epi,
+                                           self.table, self.rank, self.world, self.hmax, N.stream())
+        if rc != 0:
+            return False      # shape outside the fused kernel's limits: the caller settles and falls back
+        self.pending = None
+        N.count()
+        return True
 
     def argmax(self, ops, logits, v_valid: int):
         """Global argmax over vocab-parallel fp32 logits ``[M, V_local]``."""
