@@ -33,7 +33,7 @@ attn_prep_kernel(const bf16* qkv, int ld, const float* __restrict__ qw,
   float* cs = sm;                 // [rotary/2] cos
   float* sn = sm + rotary / 2;    // [rotary/2] sin
   float* buf = sn + rotary / 2;   // [warps][D]
-  pdl_launch_dependents();
+  pdl_launch_dependents(3);
   pdl_wait();
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -105,7 +105,7 @@ attn_split_kernel(const bf16* q, const bf16* gate_src, int gate_ld,
   constexpr int D = VEC * 32;
   __shared__ float s_m[8][MAXG], s_l[8][MAXG];
   extern __shared__ float s_acc[];  // [8 warps][MAXG][D]
-  pdl_launch_dependents();
+  pdl_launch_dependents(4);
   pdl_wait();
   const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(256)
 attn_combine_kernel(const float* po, const float* pm,
                     const float* pl, const bf16* gate_src, int gate_ld,
                     bf16* out, int n_q, int D, int n_splits, int gated) {
-  pdl_launch_dependents();
+  pdl_launch_dependents(5);
   pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
   const size_t base = ((size_t)t * n_q + h) * n_splits;

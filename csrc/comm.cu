@@ -75,7 +75,7 @@ __device__ __forceinline__ uint2* oneshot_slot(unsigned char* ws, int buf, int s
 __global__ void __launch_bounds__(256)
 allreduce_finish_kernel(const Peers P, const bf16* residual, int ldr, bf16* out,
                         int ldo, int M, int N) {
-  pdl_launch_dependents();
+  pdl_launch_dependents(10);
   pdl_wait();
   unsigned char* me = P.ws[P.rank];
   uint32_t* ctrl = reinterpret_cast<uint32_t*>(me);

@@ -50,12 +50,60 @@ struct TrlPushArgs {
   int rank, world, hmax, row0;
 };
 
+// ---- tick timeline (builds with -DTRL_TRACE only) ----------------------------------------------
+// Per launch: {kind, entry of CTA 0, end of its dependency wait, its exit} in nanoseconds of
+// %globaltimer, recorded from pdl_launch_dependents(kind) / pdl_wait() / trl_trace_end();
+// trl_trace_read copies the records out.  Without the flag nothing is compiled in.
+#ifdef TRL_TRACE
+constexpr int TRL_TRACE_CAP = 8192;
+struct TrlTraceRec { unsigned long long kind, t_entry, t_dep, t_exit; };
+extern __device__ TrlTraceRec g_trl_trace[TRL_TRACE_CAP];
+extern __device__ unsigned int g_trl_trace_n;
+__device__ __forceinline__ unsigned long long trl_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ unsigned int& trl_trace_slot() {
+  __shared__ unsigned int s;
+  return s;
+}
+__device__ __forceinline__ bool trl_trace_lead() {
+  return threadIdx.x == 0 && threadIdx.y == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+}
+__device__ __forceinline__ void trl_trace_begin(int kind) {
+  if (trl_trace_lead()) {
+    const unsigned int i = atomicAdd(&g_trl_trace_n, 1u);
+    trl_trace_slot() = i;
+    if (i < TRL_TRACE_CAP) {
+      g_trl_trace[i].kind = (unsigned long long)kind, g_trl_trace[i].t_entry = trl_now();
+      g_trl_trace[i].t_dep = 0, g_trl_trace[i].t_exit = 0;
+    }
+  }
+}
+__device__ __forceinline__ void trl_trace_dep() {
+  if (trl_trace_lead() && trl_trace_slot() < TRL_TRACE_CAP) g_trl_trace[trl_trace_slot()].t_dep = trl_now();
+}
+__device__ __forceinline__ void trl_trace_end() {
+  if (trl_trace_lead() && trl_trace_slot() < TRL_TRACE_CAP) g_trl_trace[trl_trace_slot()].t_exit = trl_now();
+}
+#else
+__device__ __forceinline__ void trl_trace_begin(int) {}
+__device__ __forceinline__ void trl_trace_dep() {}
+__device__ __forceinline__ void trl_trace_end() {}
+#endif
+
 // ---- programmatic dependent launch ----------------------------------------------------
 // Every kernel calls pdl_launch_dependents() first (the next kernel in the stream
 // may begin its own prologue) and pdl_wait() before touching anything a
-// predecessor wrote.  Without the launch attribute both are no-ops.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() {
+// predecessor wrote.  Without the launch attribute both are no-ops.  `kind` names the kernel in
+// the timeline of a -DTRL_TRACE build.
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  trl_trace_dep();
+}
+__device__ __forceinline__ void pdl_launch_dependents(int kind = 0) {
+  trl_trace_begin(kind);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 

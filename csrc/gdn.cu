@@ -39,7 +39,7 @@ gdn_prep_kernel(const bf16* inp, int ld, const float* __restrict__ conv_w,
                 float* qn, float* kn, float* vc,
                 float* gout, float* bout, int nk, int nv, int D, int KW) {
   __shared__ float red[32];
-  pdl_launch_dependents();
+  pdl_launch_dependents(12);
   pdl_wait();
   const int t = blockIdx.x, head = blockIdx.y;
   const int C = 2 * nk * D + nv * D;
@@ -255,7 +255,7 @@ gdn_scan_kernel(const float* qn, const float* kn,
   __shared__ float s_g[2][TC], s_b[2][TC], s_qk[2][TC];
   __shared__ __align__(16) float s_o[TC][32];
   __shared__ int s_last;
-  pdl_launch_dependents();
+  pdl_launch_dependents(2);
   pdl_wait();
   const int h = blockIdx.x / NS, slice = blockIdx.x % NS, seq = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -392,6 +392,7 @@ gdn_scan_kernel(const float* qn, const float* kn,
     if (prev == NS - 1) *ctr = 0;
   }
   __syncthreads();
+  trl_trace_end();
   if (!s_last) return;
   __threadfence();
   for (int i = warp; i < T; i += NW) {     // gated RMSNorm per token, one warp per token
@@ -725,6 +726,124 @@ gdn_scan_wy_kernel(const float* qn, const float* kn,
 }  // namespace
 
 static int g_gdn_wy = -1;   // -1: read TRL_GDN_WY at the first launch
+
+// ---------------------------------------------------------------------------------------
+// Decode tick (exactly one token per sequence, no kept planes) of a layer in ONE launch.
+// One CTA of 4 * D threads owns a whole (sequence, value head): thread (col, kq) holds the D / 4
+// state rows [kq * D / 4, ...) of column col, so every state load and store of a warp is one
+// contiguous 128-byte row segment.
+//   * before the dependency wait: the state (written by the previous tick) is loaded into
+//     registers -- the slot and the live plane of a sequence are written by the host before a
+//     tick and never by a kernel of a decode tick -- so the 2 x D x D x 4 bytes of the head are
+//     already on their way while the in-projection GEMV still runs;
+//   * after it: the prep of the token (conv + SiLU of the q / k / v channels of this head, L2
+//     norms, gates) in three thread groups, the delta-rule step with one shared-memory reduction
+//     over the four row groups, the gated RMSNorm of the head's output row and the ring refresh.
+// No scratch buffer, no cross-CTA counter.
+template <int D>
+__global__ void __launch_bounds__(D * 4)
+gdn_decode_kernel(const bf16* inp, int ld, const float* __restrict__ conv_w,
+                  const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                  const float* __restrict__ norm_w, float* states, const int* cur, bf16* ring,
+                  const int* positions, const int* q_start, const int* state_slots, long state_slot_stride,
+                  long plane_stride, long ring_slot_stride, float eps, bf16* out, int nk, int nv, int KW) {
+  constexpr int KQ = D / 4, WG = D / 32;      // state rows per thread, warps per thread group
+  __shared__ float s_q[D], s_k[D], s_v[D];
+  __shared__ float s_part[4][2][D];
+  __shared__ float s_ss[3][WG], s_qk[4], s_gb[2];
+  const int h = blockIdx.x, seq = blockIdx.y;
+  const int tid = threadIdx.x, col = tid % D, kq = tid / D, lane = tid & 31;
+  const int kh = h * nk / nv;
+  const int slot = state_slots[seq];
+  float* sp = states + (size_t)slot * state_slot_stride + (size_t)cur[slot] * plane_stride + (size_t)h * D * D;
+  float S[KQ];
+#pragma unroll
+  for (int i = 0; i < KQ; ++i) S[i] = sp[(size_t)(kq * KQ + i) * D + col];
+  pdl_launch_dependents(2);
+  pdl_wait();
+  const int t = q_start[seq], pos = positions[t];
+  const int C = 2 * nk * D + nv * D;
+  const bf16* row = inp + (size_t)t * ld;
+  bf16* rg = ring + (size_t)slot * ring_slot_stride;
+  // prep: thread group kq = 0 / 1 / 2 -> the q / k / v channel `col` of this head
+  float val = 0.f;
+  int ch = 0;
+  if (kq < 3) {
+    ch = (kq == 0 ? kh * D : kq == 1 ? nk * D + kh * D : 2 * nk * D + h * D) + col;
+    float acc = 0.f;
+    for (int j = 0; j < KW; ++j) {  // tap KW-1 multiplies the newest row
+      const int back = KW - 1 - j, pj = pos - back;
+      float v = 0.f;
+      if (pj >= 0) v = __bfloat162float(back == 0 ? row[ch] : rg[(size_t)(pj % RING) * C + ch]);
+      acc = fmaf(v, conv_w[(size_t)ch * KW + j], acc);
+    }
+    val = silu_f(acc);
+    if (kq < 2) {
+      const float w_ = warp_sum(val * val);
+      if (lane == 0) s_ss[kq][col >> 5] = w_;
+    }
+  } else if (col == 0) {
+    const bf16* ab = row + C + nv * D;
+    s_gb[0] = -__expf(a_log[h]) * softplus_f(__bfloat162float(ab[h]) + dt_bias[h]);
+    s_gb[1] = sigmoid_f(__bfloat162float(ab[nv + h]));
+  }
+  __syncthreads();
+  if (kq < 2) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < WG; ++i) ss += s_ss[kq][i];
+    const float nrm = rsqrtf(ss + 1e-12f) * (kq == 0 ? rsqrtf((float)D) : 1.f);
+    (kq == 0 ? s_q : s_k)[col] = val * nrm;
+  } else if (kq == 2) {
+    s_v[col] = val;
+  }
+  __syncthreads();
+  // the step: S <- e^g S;  d = beta (v - S^T k);  S <- S + k d^T;  o = S^T q
+  const float eg = __expf(s_gb[0]), beta = s_gb[1], v = s_v[col];
+  float kreg[KQ];
+  float ks = 0.f, qs = 0.f, qk = 0.f;
+#pragma unroll
+  for (int j = 0; j < KQ; ++j) {
+    const float kk = s_k[kq * KQ + j], qq = s_q[kq * KQ + j];
+    kreg[j] = kk;
+    ks = fmaf(kk, S[j], ks);
+    qs = fmaf(qq, S[j], qs);
+    qk = fmaf(qq, kk, qk);
+  }
+  s_part[kq][0][col] = ks;
+  s_part[kq][1][col] = qs;
+  if (col == 0) s_qk[kq] = qk;
+  __syncthreads();
+  const float ksum = (s_part[0][0][col] + s_part[1][0][col]) + (s_part[2][0][col] + s_part[3][0][col]);
+  const float qsum = (s_part[0][1][col] + s_part[1][1][col]) + (s_part[2][1][col] + s_part[3][1][col]);
+  const float qkd = (s_qk[0] + s_qk[1]) + (s_qk[2] + s_qk[3]);
+  const float d = beta * (v - eg * ksum);
+#pragma unroll
+  for (int j = 0; j < KQ; ++j) sp[(size_t)(kq * KQ + j) * D + col] = fmaf(kreg[j], d, eg * S[j]);
+  float o = 0.f;
+  if (kq == 0) {
+    o = fmaf(eg, qsum, qkd * d);
+    const float w_ = warp_sum(o * o);
+    if (lane == 0) s_ss[2][col >> 5] = w_;
+  }
+  // ring refresh: the raw q / k rows by the first value head of each key head, the v row by every head
+  {
+    bf16* dst = rg + (size_t)(pos % RING) * C;
+    if (kq < 2 && h % (nv / nk) == 0) dst[ch] = row[ch];
+    if (kq == 2) dst[ch] = row[ch];
+  }
+  __syncthreads();
+  if (kq == 0) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < WG; ++i) ss += s_ss[2][i];
+    const float rstd = rsqrtf(ss / (float)D + eps);
+    const float z = __bfloat162float(row[C + (size_t)h * D + col]);
+    out[((size_t)t * nv + h) * D + col] = __float2bfloat16(o * rstd * norm_w[col] * silu_f(z));
+  }
+  trl_trace_end();
+}
+
 // Turns the chunk-parallel prefill scan on or off at run time (tests compare the two paths).
 TRL_API void trl_gdn_set_wy(int on) { g_gdn_wy = on ? 1 : 0; }
 
@@ -789,4 +908,24 @@ TRL_API int trl_gdn(const void* inp, int ld, const void* conv_w, const void* dt_
 #undef SCAN
 #undef SCANWY
   return (int)e;
+}
+
+// Decode tick of a Gated-DeltaNet layer in ONE launch: every sequence carries exactly one token
+// (its row in `inp` is q_start[seq]), no per-token planes are kept.
+TRL_API int trl_gdn_decode(const void* inp, int ld, const void* conv_w, const void* dt_bias, const void* a_log,
+                           const void* norm_w, void* states, const void* cur, void* ring, const void* positions,
+                           const void* q_start, const void* state_slots, long state_slot_stride,
+                           long plane_stride, long ring_slot_stride, void* out, int B, int nk, int nv, int D,
+                           int KW, float eps, void* stream) {
+  if ((D != 128 && D != 64) || nk <= 0 || nv % nk != 0 || B <= 0 || B > 65535) return (int)cudaErrorInvalidValue;
+  cudaStream_t st = (cudaStream_t)stream;
+#define DECODE(DD)                                                                                          \
+  return (int)trl_launch(gdn_decode_kernel<DD>, dim3(nv, B), dim3(DD * 4), 0, st, (const bf16*)inp, ld,     \
+                         (const float*)conv_w, (const float*)dt_bias, (const float*)a_log,                  \
+                         (const float*)norm_w, (float*)states, (const int*)cur, (bf16*)ring,                \
+                         (const int*)positions, (const int*)q_start, (const int*)state_slots,               \
+                         state_slot_stride, plane_stride, ring_slot_stride, eps, (bf16*)out, nk, nv, KW)
+  if (D == 128) DECODE(128);
+  DECODE(64);
+#undef DECODE
 }

@@ -25,6 +25,11 @@
 
 __device__ TrlError g_trl_error = {0, 0, 0, 0};
 int g_trl_use_pdl = 1;
+#ifdef TRL_TRACE
+__device__ TrlTraceRec g_trl_trace[TRL_TRACE_CAP];
+__device__ unsigned int g_trl_trace_n = 0;
+__device__ unsigned int g_trl_trace_cur = 0;
+#endif
 
 enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_STORE_F32 = 3, EPI_PUSH = 4 };
 
@@ -419,7 +424,7 @@ gemv_bf16_kernel(const bf16* x, int ldx, const bf16* __restrict__ w,
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* xs = reinterpret_cast<float*>(smem_raw);
   float* red = xs + (size_t)M * K;
-  pdl_launch_dependents();
+  pdl_launch_dependents(6);
   pdl_wait();
 #pragma unroll
   for (int m = 0; m < M; ++m) {
@@ -677,4 +682,24 @@ TRL_API int trl_gemv_nvfp4_push(const void* x, int ldx, const void* wq, const vo
     if (e != cudaSuccess) return (int)e;
   }
   return 0;
+}
+
+// Timeline records of the launches since the last reset (builds with -DTRL_TRACE; otherwise
+// returns 0 records).  out: n x 4 uint64 {kind, entry, dependency wait done, exit} in ns.
+TRL_API int trl_trace_read(void* out, int cap, int reset) {
+#ifdef TRL_TRACE
+  unsigned int n = 0;
+  if (cudaMemcpyFromSymbol(&n, g_trl_trace_n, sizeof(n)) != cudaSuccess) return -1;
+  if ((int)n > cap) n = cap;
+  if (n > TRL_TRACE_CAP) n = TRL_TRACE_CAP;
+  if (n && cudaMemcpyFromSymbol(out, g_trl_trace, (size_t)n * sizeof(TrlTraceRec)) != cudaSuccess) return -1;
+  if (reset) {
+    const unsigned int z = 0;
+    cudaMemcpyToSymbol(g_trl_trace_n, &z, sizeof(z));
+  }
+  return (int)n;
+#else
+  (void)out, (void)cap, (void)reset;
+  return 0;
+#endif
 }

@@ -309,7 +309,7 @@ gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ ws
     for (int s = 0; s < NS && p_unit < u1; ++s) issue();
   }
   for (int i = threadIdx.x; i < pl * 2 * nslot * M; i += G2_THREADS) slots[i] = 0.f;
-  pdl_launch_dependents();
+  pdl_launch_dependents(100 + EPI * 2 + (COOP ? 1 : 0));
   pdl_wait();
   if (COOP)   // x is the residual stream: complete the pending all-reduce into it first
     g2_coop_finish(const_cast<bf16*>(x), ldx, M, K, push.ws[push.rank], push.world, push.hmax,
@@ -448,6 +448,7 @@ gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ ws
       }
     }
   }
+  trl_trace_end();
 }
 
 // (wq [N, K/2], scale [N, K/16]) -> stream layout.  One thread per (row, chunk).

@@ -9,7 +9,7 @@ namespace {
 
 __global__ void embedding_kernel(const bf16* __restrict__ table, const int* ids,
                                  bf16* out, int H, int V) {
-  pdl_launch_dependents();
+  pdl_launch_dependents(7);
   pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];

@@ -209,7 +209,7 @@ def test_gdn_kernel(ops, d, nk, nv):
     lp = dict(conv=(torch.randn(cfg.gdn_conv_dim, 4, generator=g) * 0.3).to(DEV),
               dt_bias=torch.rand(nv, generator=g).to(DEV), a_log=torch.log(1 + 3 * torch.rand(nv, generator=g)).to(DEV),
               gdn_norm=(1 + 0.1 * torch.randn(d, generator=g)).to(DEV))
-    pools = [GdnStatePool(cfg, 4, DEV, planes=4, ring_dtype=torch.bfloat16) for _ in range(2)]
+    pools = [GdnStatePool(cfg, 4, DEV, planes=4, ring_dtype=torch.bfloat16) for _ in range(3)]
     # tick 1: prefill 19 tokens on slot 1, 3 tokens on slot 2; tick 2: decode; tick 3: verify (keep)
     ticks = [
         ([dict(tokens=list(range(19)), start=0, blocks=[1, 2], slot=1), dict(tokens=[1, 2, 3], start=0, blocks=[3], slot=2)], 0),
@@ -220,10 +220,20 @@ def test_gdn_kernel(ops, d, nk, nv):
         batch = Batch.build(seqs, DEV, keep_steps=keep)
         inp = (torch.randn(batch.n_tokens, cfg.gdn_in_rows, generator=g)).to(DEV, torch.bfloat16)
         want = RefOps().gdn(inp, lp, batch, pools[0], 0, cfg, nk, nv)
-        got = ops.gdn(inp, lp, batch, pools[1], 0, cfg, nk, nv)
+        got = ops.gdn(inp, lp, batch, pools[1], 0, cfg, nk, nv).clone()
         assert _rel(got, want) < 2e-2
         assert _rel(pools[1].states, pools[0].states) < 1e-3
         assert torch.equal(pools[1].ring, pools[0].ring)
+        # the decode tick ran as one launch (state prefetch, prep, step and gated norm in one kernel);
+        # the two-launch path (prep kernel, then scan) must give the same numbers from the same pools
+        ops.gdn_fused_decode = False
+        try:
+            got2 = ops.gdn(inp, lp, batch, pools[2], 0, cfg, nk, nv)
+        finally:
+            ops.gdn_fused_decode = True
+        assert _rel(got, got2) < 3e-3                    # another summation order: a bf16 step here and there
+        assert torch.allclose(pools[1].states, pools[2].states, rtol=1e-4, atol=1e-6)
+        assert torch.equal(pools[1].ring, pools[2].ring)
         if keep:
             for p in pools:
                 p.select_step(1, 1)

@@ -52,14 +52,20 @@ def _stamp(path: str) -> str:
     return h.hexdigest()
 
 
-def build(force: bool = False, verbose: bool = False, extra_flags=()) -> str:
-    os.makedirs(OBJ, exist_ok=True)
+def build(force: bool = False, verbose: bool = False, extra_flags=(), trace: bool = False) -> str:
+    """``trace=True`` builds ``tilerl_b200/_C_trace.so`` with ``-DTRL_TRACE`` (per-launch timestamps of a
+    tick, read by ``tilerl_b200.utils.tick_trace``) next to the normal library."""
+    obj_dir = OBJ + ("_trace" if trace else "")
+    out_path = OUT.replace("_C.so", "_C_trace.so") if trace else OUT
+    if trace:
+        extra_flags = tuple(extra_flags) + ("-DTRL_TRACE",)
+    os.makedirs(obj_dir, exist_ok=True)
     nvcc = _nvcc()
     jobs = []
     objs = []
     for src in _sources():
         sp = os.path.join(CSRC, src)
-        op = os.path.join(OBJ, src + ".o")
+        op = os.path.join(obj_dir, src + ".o")
         st = op + ".stamp"
         objs.append(op)
         stamp = _stamp(sp)
@@ -81,13 +87,13 @@ def build(force: bool = False, verbose: bool = False, extra_flags=()) -> str:
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(run, jobs))
-    if jobs or not os.path.exists(OUT):
+    if jobs or not os.path.exists(out_path):
         cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-rdc=true",
-               "-Xcompiler", "-fPIC", *objs, "-o", OUT]
+               "-Xcompiler", "-fPIC", *objs, "-o", out_path]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
-    return OUT
+    return out_path
 
 
 def build_tests(force: bool = False) -> list:
@@ -110,6 +116,6 @@ def build_tests(force: bool = False) -> list:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose=True))
+    print(build(force="--force" in sys.argv, verbose=True, trace="--trace" in sys.argv))
     if "--tests" in sys.argv:
         print("\n".join(build_tests(force="--force" in sys.argv)))

@@ -77,6 +77,7 @@ class CudaOps:
         # register-streamed kernels on the checkpoint layout)
         self.gemv_stream = os.environ.get("TRL_GEMV_STREAM", "1") != "0"
         self.prefill_attn = os.environ.get("TRL_PREFILL_ATTN", "1") != "0"   # tiled kernel for q_len >= 16
+        self.gdn_fused_decode = os.environ.get("TRL_GDN_FUSED", "1") != "0"    # decode ticks: prep inside the scan kernel
         from .. import tape as _tape
         _tape.set_dequant(self.dequantize_nvfp4)   # frozen-base linears of the training forward
         self.terms_small = int(os.environ.get("TRL_TERMS_SMALL", terms_small))
@@ -346,6 +347,19 @@ class CudaOps:
         s_l = states[:, gdn_idx]
         r_l = ring[:, gdn_idx]
         keep = batch.keep_flags if batch.keep_steps else None
+        if self.gdn_fused_decode and keep is None and t == batch.n_seqs and batch.max_q_len == 1 \
+                and nv % nk == 0 and d in (64, 128):
+            # decode tick: one launch per layer (state prefetched before the dependency wait, prep,
+            # step and gated norm in one kernel)
+            N.check(self.lib.trl_gdn_decode(
+                inp.data_ptr(), inp.stride(0), self._f32(lp["conv"]).data_ptr(),
+                self._f32(lp["dt_bias"]).data_ptr(), self._f32(lp["a_log"]).data_ptr(),
+                self._f32(lp["gdn_norm"]).data_ptr(), s_l.data_ptr(), spool.cur.data_ptr(), r_l.data_ptr(),
+                batch.positions.data_ptr(), batch.q_start.data_ptr(), batch.state_slots.data_ptr(),
+                states.stride(0), states.stride(2), ring.stride(0), out.data_ptr(), batch.n_seqs, nk, nv, d,
+                cfg.gdn_conv, cfg.rms_eps, N.stream()), "gdn_decode")
+            N.count()
+            return out
         N.check(self.lib.trl_gdn(
             inp.data_ptr(), inp.stride(0), self._f32(lp["conv"]).data_ptr(),
             self._f32(lp["dt_bias"]).data_ptr(), self._f32(lp["a_log"]).data_ptr(),

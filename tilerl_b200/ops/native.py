@@ -16,7 +16,9 @@ from typing import Optional
 import torch
 
 _LIB: Optional[ctypes.CDLL] = None
-_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "_C.so")
+# TRL_TRACE_LIB=1 loads the timeline build (``python -m tilerl_b200.build --trace``) instead
+_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                     "_C_trace.so" if os.environ.get("TRL_TRACE_LIB") == "1" else "_C.so")
 
 P, I, L, F = c_void_p, c_int, c_long, c_float
 
@@ -24,11 +26,13 @@ _SIGS = {
     "trl_gemv_nvfp4": [P, I, P, P, P, P, F, P, I, P, I, I, I, I, I, P],
     "trl_gemv_bf16": [P, I, P, P, F, P, I, P, I, I, I, I, I, P],
     "trl_set_pdl": [I],
+    "trl_trace_read": [P, I, I],
     "trl_error_read": [P, I],
     "trl_attn_prep": [P, I, P, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P],
     "trl_attn_paged": [P, P, I, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, F, I, P],
     "trl_gdn": [P, I, P, P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, P, P, P, P, P, P, P,
                 I, I, I, I, I, I, I, F, P],
+    "trl_gdn_decode": [P, I, P, P, P, P, P, P, P, P, P, P, L, L, L, P, I, I, I, I, I, F, P],
     "trl_embedding": [P, P, P, I, I, I, P],
     "trl_gather_rows": [P, P, P, I, I, P],
     "trl_rmsnorm": [P, P, P, I, I, F, P],

@@ -1,0 +1,79 @@
+"""Timeline of one decode tick: where the time between two dependent kernels goes.
+
+    python -m tilerl_b200.build --trace
+    TRL_TRACE_LIB=1 python -m tilerl_b200.utils.tick_trace [--model qwen38-27b] [--ctx 512]
+
+The ``-DTRL_TRACE`` build records, per launch, when CTA 0 entered the kernel and when its
+dependency wait ended.  The wait of launch ``i + 1`` ends when launch ``i`` has completed, so
+``dep[i + 1] - dep[i]`` is launch ``i``'s share of the tick's critical path; ``dep[i] -
+entry[i]`` says how early the launch was resident (overlap won by programmatic dependent launch).
+The tool replays the captured B = 1 decode graph, reads the records and prints the per-kernel sums.
+"""
+from __future__ import annotations
+
+import argparse
+import collections
+import json
+
+import numpy as np
+import torch
+
+KINDS = {2: "gdn_scan", 3: "attn_prep", 4: "attn_split", 5: "attn_combine", 6: "gemv_bf16(lm_head)", 7: "embedding",
+         10: "allreduce_finish", 12: "gdn_prep", 100: "gemv2 store", 101: "gemv2 store+coop", 102: "gemv2 residual",
+         104: "gemv2 swiglu", 105: "gemv2 swiglu+coop", 106: "gemv2 store_f32", 108: "gemv2 push", 0: "other"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="qwen38-27b")
+    ap.add_argument("--ctx", type=int, default=512)
+    ap.add_argument("--ticks", type=int, default=4)
+    args = ap.parse_args()
+    from tilerl_b200.config import get_config
+    from tilerl_b200.factory import build_engine, build_model, make_ops
+    from tilerl_b200.engine import SamplingParams
+    from tilerl_b200.ops import native
+    dev = torch.device("cuda", 0)
+    cfg = get_config(args.model)
+    ops = make_ops(dev)
+    model = build_model(cfg, dev, seed=0, ops=ops)
+    eng = build_engine(model, ops, slots=2, max_ctx=args.ctx + 64, graph=True, prefix=False)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, cfg.vocab, (args.ctx,), generator=g).tolist()
+    eng.generate([prompt], SamplingParams(max_tokens=4, ignore_eos=True))      # captures the graph
+    torch.cuda.synchronize()
+    buf = np.zeros((8192, 4), dtype=np.uint64)
+    native.lib().trl_trace_read(buf.ctypes.data, 8192, 1)                       # reset
+    eng.generate([prompt], SamplingParams(max_tokens=args.ticks + 1, ignore_eos=True))
+    torch.cuda.synchronize()
+    n = native.lib().trl_trace_read(buf.ctypes.data, 8192, 1)
+    if n <= 0:
+        raise SystemExit("no records: load the -DTRL_TRACE build with TRL_TRACE_LIB=1")
+    rec = buf[:n].astype(np.int64)
+    # the last tick: from the last embedding launch on
+    emb = [i for i in range(n) if rec[i, 0] == 7]
+    if len(emb) < 2:
+        raise SystemExit("fewer than two ticks recorded")
+    a, b = emb[-2], emb[-1]
+    tick = rec[a:b + 1]
+    dep = tick[:, 2]
+    share = collections.OrderedDict()
+    early = collections.OrderedDict()
+    for i in range(len(tick) - 1):
+        name = KINDS.get(int(tick[i, 0]), f"kind {int(tick[i, 0])}")
+        d = share.setdefault(name, [0, 0.0])
+        d[0] += 1
+        d[1] += (dep[i + 1] - dep[i]) / 1e3
+        e = early.setdefault(name, 0.0)
+        early[name] = e + (dep[i] - tick[i, 1]) / 1e3
+    total = (dep[-1] - dep[0]) / 1e3
+    out = {"tick_us": round(total, 1), "launches": len(tick) - 1,
+           "critical_path_us": {k: {"n": v[0], "sum": round(v[1], 1), "avg": round(v[1] / v[0], 2),
+                                    "resident_before_dep_avg": round(early[k] / v[0], 2)}
+                                for k, v in sorted(share.items(), key=lambda kv: -kv[1][1])}}
+    print(json.dumps(out, indent=1))
+    print("tick_trace done")
+
+
+if __name__ == "__main__":
+    main()
