@@ -22,6 +22,7 @@ namespace {
 
 constexpr int KVB = 16;
 constexpr int MAXG = 8;
+constexpr int COMBINE_SPLITS = 64;     // splits whose (max, denominator) the combine kernel stages in shared memory
 
 __global__ void __launch_bounds__(256)
 attn_prep_kernel(const bf16* qkv, int ld, const float* __restrict__ qw,
@@ -50,8 +51,9 @@ attn_prep_kernel(const bf16* qkv, int ld, const float* __restrict__ qw,
   const int per_q = gated ? 2 * D : D;
   const int slot = slot_mapping[t];
   float* hb = buf + (size_t)warp * D;
-  // heads 0..n_q-1 = q, n_q..n_q+n_kv-1 = k, then v
-  for (int h = warp; h < n_q + 2 * n_kv; h += nw) {
+  // heads 0..n_q-1 = q, n_q..n_q+n_kv-1 = k, then v; CTA blockIdx.y takes heads [y * nw, (y + 1) * nw):
+  // a decode tick's single token is spread over several CTAs instead of one walking 32 heads
+  for (int h = blockIdx.y * nw + warp; h < min(n_q + 2 * n_kv, ((int)blockIdx.y + 1) * nw); h += nw) {
     const bool is_q = h < n_q, is_k = !is_q && h < n_q + n_kv;
     const bf16* src = is_q ? row + (size_t)h * per_q
                            : row + (size_t)n_q * per_q + (size_t)(h - n_q) * D;
@@ -137,13 +139,27 @@ attn_split_kernel(const bf16* q, const bf16* gate_src, int gate_ld,
 #pragma unroll
     for (int v = 0; v < VEC; ++v) acc[g][v] = 0.f;
   }
-  for (int j = lo + warp; j < hi; j += 8) {
+  // K / V rows of this warp's next key are requested while the current key is processed
+  auto row_off = [&](int j) {
     const int blk = table[j / KVB];
-    const size_t off = (((size_t)blk * n_kv + kvh) * KVB + (j % KVB)) * D + lane * VEC;
+    return (((size_t)blk * n_kv + kvh) * KVB + (j % KVB)) * D + lane * VEC;
+  };
+  uint4 kk_n = make_uint4(0u, 0u, 0u, 0u), vv_n = kk_n;
+  if (VEC == 8 && lo + warp < hi) {
+    const size_t o0 = row_off(lo + warp);
+    kk_n = *reinterpret_cast<const uint4*>(kcache + o0);
+    vv_n = *reinterpret_cast<const uint4*>(vcache + o0);
+  }
+  for (int j = lo + warp; j < hi; j += 8) {
+    const size_t off = row_off(j);
     float kf[VEC], vf[VEC];
     if (VEC == 8) {
-      const uint4 kk = *reinterpret_cast<const uint4*>(kcache + off);
-      const uint4 vv = *reinterpret_cast<const uint4*>(vcache + off);
+      const uint4 kk = kk_n, vv = vv_n;
+      if (j + 8 < hi) {
+        const size_t o1 = row_off(j + 8);
+        kk_n = *reinterpret_cast<const uint4*>(kcache + o1);
+        vv_n = *reinterpret_cast<const uint4*>(vcache + o1);
+      }
       const uint32_t ku[4] = {kk.x, kk.y, kk.z, kk.w}, vu[4] = {vv.x, vv.y, vv.z, vv.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -208,23 +224,42 @@ attn_split_kernel(const bf16* q, const bf16* gate_src, int gate_ld,
   }
 }
 
+
 __global__ void __launch_bounds__(256)
 attn_combine_kernel(const float* po, const float* pm,
                     const float* pl, const bf16* gate_src, int gate_ld,
                     bf16* out, int n_q, int D, int n_splits, int gated) {
+  __shared__ float s_pm[COMBINE_SPLITS], s_pl[COMBINE_SPLITS];
   pdl_launch_dependents(5);
   pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
   const size_t base = ((size_t)t * n_q + h) * n_splits;
+  // (max, denominator) of every split once per CTA; the partial rows then come eight loads at a
+  // time, and splits that saw no key (max = -inf) are not read at all
+  const bool staged = n_splits <= COMBINE_SPLITS;
+  if (staged) {
+    for (int s = threadIdx.x; s < n_splits; s += blockDim.x) s_pm[s] = pm[base + s], s_pl[s] = pl[base + s];
+    __syncthreads();
+  }
   float mm = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, pm[base + s]);
+  for (int s = 0; s < n_splits; ++s) mm = fmaxf(mm, staged ? s_pm[s] : pm[base + s]);
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float ll = 0.f, a = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float ms = pm[base + s];
-      const float c = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
-      ll += pl[base + s] * c;
-      a += po[(base + s) * D + d] * c;
+    for (int s0 = 0; s0 < n_splits; s0 += 8) {
+      float pv[8], ms[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        ms[k] = (s0 + k < n_splits) ? (staged ? s_pm[s0 + k] : pm[base + s0 + k]) : -INFINITY;
+        pv[k] = (ms[k] != -INFINITY) ? po[(base + s0 + k) * D + d] : 0.f;
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        if (ms[k] != -INFINITY) {      // ascending split order, as before
+          const float c = exp2f(ms[k] - mm);
+          ll += (staged ? s_pl[s0 + k] : pl[base + s0 + k]) * c;
+          a += pv[k] * c;
+        }
+      }
     }
     float o = ll > 0.f ? a / ll : 0.f;
     if (gated) o *= sigmoid_f(__bfloat162float(gate_src[(size_t)t * gate_ld + (size_t)h * 2 * D + D + d]));
@@ -501,7 +536,8 @@ TRL_API int trl_attn_prep(const void* qkv, int ld, const void* q_norm, const voi
                           float eps, int gated, void* stream) {
   const int threads = 256;
   const size_t smem = (size_t)(rotary + (threads / 32) * D) * sizeof(float);
-  return (int)trl_launch(attn_prep_kernel, dim3(T), dim3(threads), smem, (cudaStream_t)stream,
+  const int chunks = (n_q + 2 * n_kv + threads / 32 - 1) / (threads / 32);   // one warp per head
+  return (int)trl_launch(attn_prep_kernel, dim3(T, chunks), dim3(threads), smem, (cudaStream_t)stream,
                          (const bf16*)qkv, ld, (const float*)q_norm, (const float*)k_norm,
                          (const int*)positions, (const int*)slot_mapping, (bf16*)q_out, (bf16*)kcache,
                          (bf16*)vcache, n_q, n_kv, D, rotary, log2f(theta), eps, gated);
@@ -513,7 +549,7 @@ TRL_API int trl_attn_paged(const void* q, const void* gate_src, int gate_ld, con
                            const void* seq_ids, const void* positions, void* po, void* pm, void* pl,
                            void* out, int T, int n_q, int n_kv, int D, int n_splits, float scale,
                            int gated, void* stream) {
-  if (n_q % n_kv != 0 || n_q / n_kv > MAXG) return (int)cudaErrorInvalidValue;
+  if (n_kv <= 0 || n_q <= 0 || n_q % n_kv != 0 || n_q / n_kv > MAXG) return (int)cudaErrorInvalidValue;
   cudaStream_t st = (cudaStream_t)stream;
   const float sl2 = scale * 1.4426950408889634f;
   const dim3 grid(n_splits, n_kv, T);
@@ -610,7 +646,7 @@ TRL_API int trl_attn_paged_static(const void* q, const void* gate_src, int gate_
                                   const void* vcache, const void* block_table, int max_blocks,
                                   const void* seq_ids, const void* positions, void* out, int T, int n_q,
                                   int n_kv, int D, int n_splits, float scale, int gated, void* stream) {
-  if (T <= 0 || n_q <= 0 || n_splits <= 0 || D <= 0) return (int)cudaErrorInvalidValue;
+  if (T <= 0 || n_q <= 0 || n_kv <= 0 || n_splits <= 0 || D <= 0) return (int)cudaErrorInvalidValue;
   const size_t need = trl_attn_static_scratch_needed(T, n_q, D, n_splits);
   if (need > (size_t)TRL_ATTN_STATIC_SCRATCH_BYTES) return (int)cudaErrorInvalidValue;
   int dev = 0;

@@ -339,27 +339,93 @@ gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ ws
           acc[r][m] = 0.f;
         }
     };
-    for (int u = u0; u < u1;) {
-      const uint32_t bar = bar_w + 8u * slot;
-      if (!g2_try_wait(bar, parity)) {
-        const long long t0 = clock64();
-        uint32_t it = 0;
-        while (!g2_try_wait(bar, parity)) {
-          if ((++it & 63) == 0 && clock64() - t0 > G2_WAIT_CYCLES) {
-            trl_set_error(TRL_ERR_MBAR_TIMEOUT, (int)blockIdx.x, 200 + warp, u);
-            ok = false;
-            break;
+    // one 32-chunk unit at shared address `ua` (already offset by lane * 16), step `st` of its row pair
+    auto unit_full = [&](uint32_t ua, int st) {
+      const uint4 wv0 = g2_lds128(ua), wv1 = g2_lds128(ua + 512u);
+      const uint16_t sv[2] = {g2_lds16(ua + 1024u - (uint32_t)lane * 14u), g2_lds16(ua + 1088u - (uint32_t)lane * 14u)};
+      const uint32_t w4[2][4] = {{wv0.x, wv0.y, wv0.z, wv0.w}, {wv1.x, wv1.y, wv1.z, wv1.w}};
+      const uint32_t xa = xs_a + (uint32_t)st * 512u;
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        uint32_t xh[16];
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          const uint4 t = g2_lds128(xa + (uint32_t)m * xrow_bytes + (uint32_t)p * pstride);
+          xh[p * 4 + 0] = t.x, xh[p * 4 + 1] = t.y, xh[p * 4 + 2] = t.z, xh[p * 4 + 3] = t.w;
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const float2 sc = h2_to_f2(cvt_e4m3x2_to_h2(sv[r]));
+#pragma unroll
+          for (int blk = 0; blk < 2; ++blk) {
+            uint32_t a = 0u;  // f16x2 zero
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              uint32_t h[4];
+              cvt_e2m1x8_to_h2x4(w4[r][blk * 2 + q], h);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) a = hfma2_u(h[i], xh[(blk * 2 + q) * 4 + i], a);
+            }
+            const float2 af = h2_to_f2(a);
+            acc[r][m] = fmaf(blk == 0 ? sc.x : sc.y, af.x + af.y, acc[r][m]);
           }
         }
       }
-      ok = __all_sync(0xffffffffu, ok);
+    };
+    auto wait_stage = [&](uint32_t bar, uint32_t par, int u) {
+      if (g2_try_wait(bar, par)) return true;
+      const long long t0 = clock64();
+      bool fine = true;
+      for (uint32_t it = 1; !g2_try_wait(bar, par); ++it) {
+        if ((it & 63) == 0 && clock64() - t0 > G2_WAIT_CYCLES) {
+          trl_set_error(TRL_ERR_MBAR_TIMEOUT, (int)blockIdx.x, 200 + warp, u);
+          fine = false;
+          break;
+        }
+      }
+      return (bool)__all_sync(0xffffffffu, fine);
+    };
+    if (FULL) {
+      // every unit holds 32 chunks: constant offsets, two units per stage, no per-lane predicate
+      const int n_units = u1 - u0;
+      int p_left = u1 - p_unit;                    // units the producer has not requested yet
+      for (int base = 0; base < n_units; base += STAGE_UNITS) {
+        ok = wait_stage(bar_w + 8u * slot, parity, u0 + base);
+        if (!ok) break;
+        const uint32_t ua = ring_w + (uint32_t)slot * STAGE_BYTES + (uint32_t)lane * 16u;
+        unit_full(ua, cs);
+        if (++cs == nsteps) {
+          flush(cp);
+          cs = 0, ++cp;
+        }
+        if (base + 1 < n_units) {
+          unit_full(ua + UNIT_BYTES, cs);
+          if (++cs == nsteps) {
+            flush(cp);
+            cs = 0, ++cp;
+          }
+        }
+        __syncwarp();
+        if (lane == 0 && p_left > 0) {             // refill the stage just consumed
+          const uint32_t bytes = (uint32_t)min(p_left, STAGE_UNITS) * UNIT_BYTES;
+          const uint32_t bar = bar_w + 8u * slot;
+          g2_expect_tx(bar, bytes);
+          g2_bulk_load(ring_w + (uint32_t)slot * STAGE_BYTES, src + p_off, bytes, bar);
+          p_off += bytes;
+          p_left -= STAGE_UNITS;
+        }
+        if (++slot == NS) slot = 0, parity ^= 1u;
+      }
+    } else {
+    for (int u = u0; u < u1;) {
+      ok = wait_stage(bar_w + 8u * slot, parity, u);
       if (!ok) break;
       uint32_t ua = ring_w + (uint32_t)slot * STAGE_BYTES;   // shared address of the current unit
 #pragma unroll
       for (int g = 0; g < STAGE_UNITS; ++g) {
         if (u >= u1) break;
-        const int n = FULL ? 32 : ((cs == nsteps - 1) ? nlast : 32);
-        if (FULL || lane < n) {
+        const int n = (cs == nsteps - 1) ? nlast : 32;
+        if (lane < n) {
           const uint4 wv0 = g2_lds128(ua + lane * 16);
           const uint4 wv1 = g2_lds128(ua + n * 16 + lane * 16);
           const uint16_t sv[2] = {g2_lds16(ua + n * 32 + lane * 2), g2_lds16(ua + n * 34 + lane * 2)};
@@ -402,6 +468,7 @@ gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ ws
       __syncwarp();
       if (lane == 0 && p_unit < u1) issue();   // refill the stage just consumed
       if (++slot == NS) slot = 0, parity ^= 1u;
+    }
     }
     if (ok && cs != 0) flush(cp);   // range ended inside a pair
     if (!ok) {

@@ -90,3 +90,60 @@ def test_prefix_store_demotes_to_the_host_tier_and_promotes_on_a_hit():
     warm = eng.generate([a], sp)[0]
     assert store.promotions == 1
     assert warm.tokens == cold.tokens and warm.cached_tokens == 32
+
+
+def test_clear_drops_cold_tiers_too_so_a_weight_change_cannot_serve_stale_kv():
+    """``Engine.invalidate_weights`` clears the prefix store: an entry that had been demoted to host
+    memory must not be promoted afterwards (it was computed with the old weights), and clearing
+    must not copy anything to the host on the way."""
+    from helpers import rand_prompts
+    from tilerl_b200.config import tiny_hybrid
+    from tilerl_b200.engine import Engine, SamplingParams
+    from tilerl_b200.kv import GdnStatePool, PagedKvPool, PrefixStore
+    from tilerl_b200.kv_tiers import DramSnapshots, HostKvPages
+    from tilerl_b200.models.hybrid import HybridModel
+    from tilerl_b200.ops.backend import RefOps
+    cfg = tiny_hybrid()
+    model = HybridModel.build_random(cfg, seed=1)
+    kv = PagedKvPool(cfg, 64, dtype=torch.float32)
+    st = GdnStatePool(cfg, 6, ring_dtype=torch.float32)
+    host, dram = HostKvPages(1 << 26), DramSnapshots(1 << 26)
+    store = PrefixStore(kv, max_entries=1, host=host, dram=dram)
+    eng = Engine(model, RefOps(), kv, st, prefix_store=store)
+    a, b = rand_prompts(cfg, 2, 40)
+    sp = SamplingParams(max_tokens=3)
+    eng.generate([a], sp)
+    eng.generate([b], sp)                          # a is now cold (host pages + DRAM snapshot), b is warm
+    assert len(store.cold) == 1 and len(store.entries) == 1
+    demotions, free_before = store.demotions, None
+    eng.invalidate_weights()
+    assert len(store.entries) == 0 and len(store.cold) == 0
+    assert store.demotions == demotions            # nothing was copied out while clearing
+    assert len(host.pages) == 0 and len(dram.items) == 0 and dram.bytes == 0
+    assert kv.used_blocks == 0
+    misses = store.misses
+    again = eng.generate([a], sp)[0]
+    assert again.cached_tokens == 0 and store.misses == misses + 1 and store.promotions == 0
+
+
+def test_refcount_calls_survive_python_optimised_mode(tmp_path):
+    """The native incref / release calls are statements of their own (never the operand of an
+    ``assert``): under ``python -O`` a shared prefix block keeps its references."""
+    import subprocess
+    import sys
+    code = (
+        "import torch\n"
+        "from tilerl_b200.config import tiny_hybrid\n"
+        "from tilerl_b200.kv import PagedKvPool\n"
+        "kv = PagedKvPool(tiny_hybrid(), 8, dtype=torch.float32)\n"
+        "b = kv.alloc_block(); free = kv.free_blocks\n"
+        "kv.incref(b); kv.release(b)\n"
+        "assert_free = kv.free_blocks\n"
+        "kv.release(b)\n"
+        "print(free, assert_free, kv.free_blocks)\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-O", "-c", code], capture_output=True, text=True, cwd=root,
+                         env={**os.environ, "PYTHONPATH": root})
+    assert out.returncode == 0, out.stderr
+    free, mid, end = map(int, out.stdout.split())
+    assert mid == free and end == free + 1

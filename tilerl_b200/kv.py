@@ -119,14 +119,18 @@ class PagedKvPool:
 
     def incref(self, b: int) -> None:
         if self._pager is not None:
-            assert self._pager[0].trl_pager_incref(self._pager[1], int(b)) > 0, f"incref of free block {b}"
+            rc = self._pager[0].trl_pager_incref(self._pager[1], int(b))   # the call itself, never inside an assert
+            if rc <= 0:
+                raise AssertionError(f"incref of free block {b}")
             return
         assert self._ref[b] > 0, f"incref of free block {b}"
         self._ref[b] += 1
 
     def release(self, b: int) -> None:
         if self._pager is not None:
-            assert self._pager[0].trl_pager_release(self._pager[1], int(b)) >= 0, f"release of free block {b}"
+            rc = self._pager[0].trl_pager_release(self._pager[1], int(b))
+            if rc < 0:
+                raise AssertionError(f"release of free block {b}")
             return
         assert b != 0 and self._ref[b] > 0, f"release of free block {b}"
         self._ref[b] -= 1
@@ -394,5 +398,19 @@ class PrefixStore:
         return n
 
     def clear(self) -> None:
-        while self._evict_one():
-            pass
+        """Drop every entry, warm and cold, WITHOUT demoting: the store is cleared when the weights
+        changed, and KV pages or GDN snapshots computed with the old weights must not come back from
+        a host / DRAM tier on a later lookup."""
+        while self.entries:
+            _, e = self.entries.popitem(last=False)
+            for b in e.blocks:
+                self.pool.release(b)
+            self.state_bytes -= e.state_bytes
+            self.evictions += 1
+        while self.cold:
+            key, c = self.cold.popitem(last=False)
+            if self.host is not None:
+                for k in c.page_keys:
+                    self.host.release(k)
+            if c.has_snapshot and self.dram is not None:
+                self.dram.drop(key)

@@ -180,6 +180,11 @@ class DramSnapshots:
         self.items.move_to_end(key)
         return tuple(t.to(device) for t in s)
 
+    def drop(self, key: int) -> None:
+        s = self.items.pop(key, None)
+        if s is not None:
+            self.bytes -= self._nbytes(s)
+
 
 def weights_fingerprint(model) -> str:
     """Cheap identity of the served weights: shapes plus a sample of bytes of every tensor."""

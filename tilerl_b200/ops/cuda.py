@@ -330,7 +330,9 @@ class CudaOps:
             return 1
         longest = max(batch.host_kv_len) if batch.host_kv_len else 1
         want = max(1, self.sms // max(1, t * n_kv))
-        return max(1, min(want, 32, (longest + 127) // 128))
+        # a warp walks its keys one after the other: 32 keys (two pages) per split keep that walk at
+        # four keys per warp
+        return max(1, min(want, 32, (longest + 31) // 32))
 
     def gdn(self, inp, lp, batch, spool, gdn_idx, cfg, nk, nv):
         t = inp.shape[0]
