@@ -171,3 +171,49 @@ def test_fused_head_cross_entropy_equals_the_unfused_path():
     (-(wt * lp_ref).sum()).backward()
     assert torch.allclose(lp, lp_ref.detach(), atol=1e-5)
     assert torch.allclose(grads[id(h)], h2.grad, atol=1e-5) and torch.allclose(grads[id(w)], w2.grad, atol=1e-5)
+
+
+def test_group_advantages_signal_and_group_count():
+    """A group whose task reward is constant gets zeros even when a length term separates its rows
+    (a length-only gradient), and a reward count that is not a whole number of groups, or not the
+    number of groups the caller means, is refused."""
+    import pytest
+    task = [1.0, 1.0, 1.0, 1.0, 0.0, 1.0, 0.0, 1.0]
+    lens = [3, 9, 5, 7, 4, 4, 8, 8]
+    shaped = [t - 0.01 * n for t, n in zip(task, lens)]
+    adv = rl.group_advantages(shaped, 4, signal=task, groups=2)
+    assert torch.all(adv[:4] == 0)                       # constant signal: silent group
+    assert adv[4] < 0 < adv[5] and adv[6] < 0 < adv[7]   # the other group keeps its ordering
+    plain = rl.group_advantages(shaped, 4)               # without the signal the length term fills the advantage
+    assert plain[:4].abs().max() > 0.5
+    with pytest.raises(ValueError):
+        rl.group_advantages(shaped[:7], 4)
+    with pytest.raises(ValueError):
+        rl.group_advantages(shaped, 4, groups=1)
+    # dead rows do not make a constant-signal group look ordered
+    adv = rl.group_advantages([1.0, 1.0, 0.0, 1.0], 4, live=[True, True, False, True], signal=[1.0, 1.0, 0.0, 1.0])
+    assert torch.all(adv == 0)
+
+
+def test_opd_loop_teacher_generates_student_trains_and_weights_are_restored():
+    """On-policy distillation on the tiny model: every step yields a finite loss, the student's
+    adapters move, the EMA teacher follows them more slowly, the live tensors hold the STUDENT after
+    each step (the teacher was only swapped in for the rollout), and the engine's prefix store holds
+    nothing computed under the other set of weights."""
+    cfg = tiny_hybrid()
+    eng = make_engine(cfg, seed=3)
+    model = eng.model
+    keys = model.add_lora(rank=4, alpha=8.0)
+    for k in keys:
+        if k.endswith("lora_b"):
+            model.params[k].normal_(0, 0.02)
+    before = {k: v.detach().clone() for k, v in model.trainable().items()}
+    opt = AdamW(model.trainable(), lr=1e-2)
+    prompts = rand_prompts(cfg, 4, 12)
+    out = list(rl.opd_loop(eng, model, prompts, opt, steps=3, max_tokens=6, ema=0.5, prompts_per_step=2))
+    assert len(out) == 3 and all(torch.isfinite(torch.tensor(m["loss"])) for m in out)
+    assert all(m["tokens"] > 0 for m in out)
+    after = model.trainable()
+    moved = sum(float((after[k] - before[k]).abs().sum()) for k in before)
+    assert moved > 0
+    assert len(eng.prefix) == 0          # nothing cached under either set of weights survives a step

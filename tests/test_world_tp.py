@@ -44,3 +44,74 @@ def test_tp_serving_equals_single_rank(world):
 def test_tp_serving_negative_control_no_collective():
     got = run_world(2, _tp_serve, True)
     assert got[0] != _single()
+
+
+# ---- training: one clipped optimizer step under TP equals the single-rank step -------------------
+def _train_setup():
+    from tilerl_b200.config import tiny_hybrid
+    cfg = tiny_hybrid()
+    g = torch.Generator().manual_seed(8)
+    return cfg, torch.randint(0, cfg.vocab, (2, 10), generator=g)
+
+
+def _train_single(max_norm):
+    from tilerl_b200 import rl
+    from tilerl_b200.models.hybrid import HybridModel
+    from tilerl_b200.optim import AdamW
+    cfg, ids = _train_setup()
+    model = HybridModel.build_random(cfg, seed=6, keep_master=True)
+    tr = model.trainable("full")
+    m = rl.train_step(model, ids, AdamW(tr, lr=1e-2), max_norm=max_norm)
+    return m["grad_norm"], {k: v.detach().clone() for k, v in tr.items()}
+
+
+def _train_rank(rank, world, max_norm, local_clip):
+    import torch.distributed as dist
+    from tilerl_b200 import rl
+    from tilerl_b200.models.hybrid import HybridModel
+    from tilerl_b200.optim import AdamW
+    cfg, ids = _train_setup()
+    model = HybridModel.build_random(cfg, seed=6, tp_rank=rank, tp=world, keep_master=True)
+    tr = model.trainable("full")
+    kw = dict(tp_group=dist.group.WORLD, tp_world=world)
+    if local_clip:     # mutation: each rank clips by the norm of what it holds
+        orig = rl._clip
+        rl._clip = lambda grads, mn, fb: orig(grads, mn, {})
+    m = rl.train_step(model, ids, AdamW(tr, lr=1e-2), max_norm=max_norm, **kw)
+    return m["grad_norm"], {k: v.detach().numpy().copy() for k, v in tr.items()}
+
+
+def _compare(got, want, cfg, world):
+    from tilerl_b200.parallel.mesh import grad_is_sharded, shard_param
+    worst_rep, worst = 0.0, 0.0
+    for rank, (_, params) in enumerate(got):
+        for k, v in params.items():
+            base = k[len("master."):] if k.startswith("master.") else k
+            v = torch.from_numpy(v)
+            ref = shard_param(cfg, base, want[k], rank, world)
+            err = float((v.double() - ref.double()).norm() / (ref.double().norm() + 1e-12))
+            worst = max(worst, err)
+            if not grad_is_sharded(k):
+                worst_rep = max(worst_rep, float((v.double() - torch.from_numpy(got[0][1][k]).double()).abs().max()))
+    return worst, worst_rep
+
+
+def test_tp_train_step_clips_with_one_global_norm_and_matches_single_rank():
+    """The gradient norm here is ~10x the clip threshold, so the coefficient matters: every TP rank
+    must use the norm of the WHOLE gradient (sharded squares summed over ranks, replicated ones
+    counted once), take the same step as one rank would, and keep replicated parameters identical."""
+    cfg, _ = _train_setup()
+    norm1, want = _train_single(0.05)
+    got = run_world(2, _train_rank, 0.05, False)
+    assert norm1 > 0.2                                     # the clip is active
+    for n, _ in got:
+        assert abs(n - norm1) < 2e-3 * norm1
+    worst, worst_rep = _compare(got, want, cfg, 2)
+    assert worst < 2e-3 and worst_rep < 1e-6
+
+
+def test_tp_train_step_negative_control_local_norm():
+    cfg, _ = _train_setup()
+    norm1, want = _train_single(0.05)
+    got = run_world(2, _train_rank, 0.05, True)
+    assert any(abs(n - norm1) > 1e-2 * norm1 for n, _ in got)

@@ -32,17 +32,21 @@ def clip_grad_norm(grads: Dict[str, torch.Tensor], max_norm: float, *, sharded: 
     """Global-norm clip in place.  Under TP the squared norms of sharded tensors are
     summed across ranks while replicated tensors are counted once: one all-reduce
     of two numbers in fp64."""
-    sh = torch.zeros((), dtype=torch.float64)
-    rep = torch.zeros((), dtype=torch.float64)
+    dev = next(iter(grads.values())).device if grads else torch.device("cpu")
+    sh = torch.zeros((), dtype=torch.float64, device=dev)
+    rep = torch.zeros((), dtype=torch.float64, device=dev)
     for k, g in grads.items():
-        s = g.double().pow(2).sum().cpu()
+        s = g.double().pow(2).sum()
         if sharded is not None and sharded(k):
             sh += s
         else:
             rep += s
     if tp_world > 1:
         import torch.distributed as dist
-        buf = torch.stack([sh, rep * tp_world])
+        # every rank contributes its shard's squares and its (identical) copy of the replicated ones:
+        # after the sum the replicated part is tp_world times too large, the sharded part is whole.
+        # The buffer lives on the gradients' device (NCCL reduces device tensors only).
+        buf = torch.stack([sh, rep])
         dist.all_reduce(buf, group=tp_group)
         total = float(buf[0] + buf[1] / tp_world)
     else:

@@ -164,6 +164,20 @@ def is_sharded(name: str) -> bool:
     return shard_dim(name) is not None
 
 
+def grad_is_sharded(name: str) -> bool:
+    """Whether the gradient stored under ``name`` (a parameter name, its ``master.`` copy or a LoRA
+    factor) is this rank's shard of a larger tensor -- its squared norm then adds over the TP ranks --
+    or a replicated tensor every rank holds whole (counted once).  A LoRA factor follows the split
+    of its projection: B with a column-parallel base, A with a row-parallel one."""
+    if name.startswith("master."):
+        name = name[len("master."):]
+    if name.endswith(".lora_a") or name.endswith(".lora_b"):
+        base, which = name[:-7], name[-1]
+        d = shard_dim(base)
+        return (d == 0 and which == "b") or (d == 1 and which == "a")
+    return is_sharded(name)
+
+
 def shard_spec(cfg: ModelConfig, name: str, rank: int, tp: int):
     """How rank ``rank`` cuts parameter ``name``: ``("full",)``, ``("rows", [(a, b), ...], pad_to)``
     (row ranges concatenated, optionally zero-padded to ``pad_to`` source rows first) or

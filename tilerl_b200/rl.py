@@ -40,12 +40,26 @@ from .ops import ref
 
 
 def group_advantages(rewards: Sequence[float], group: int, live: Optional[Sequence[bool]] = None,
-                     eps: float = 1e-6) -> torch.Tensor:
+                     eps: float = 1e-6, signal: Optional[Sequence[float]] = None,
+                     groups: Optional[int] = None) -> torch.Tensor:
     """``(r - mean_g) / std_g`` within each group of ``group`` consecutive samples.
     A group whose live samples all tie gets zeros (no signal); dead samples (empty
-    completions) get zero and do not enter the statistics."""
+    completions) get zero and do not enter the statistics.
+
+    ``signal``: the reward without shaping terms (the length penalty).  A group whose signal is
+    constant over its live rows has no ordering left except the shaping term, and normalisation
+    would blow that up to a full-size advantage (a length-only gradient); such a group gets zeros.
+    ``groups``: how many groups the caller means to pass; checked, because the count is otherwise
+    inferred from the length.  The number of rewards must be a whole number of groups.
+    Parity: reference ``group_advantages`` (``src/tilerl/train.py:740-801``)."""
     r = torch.tensor(list(rewards), dtype=torch.float32)
+    if group < 1 or len(r) % group:
+        raise ValueError(f"group_advantages: {len(r)} rewards are not a whole number of groups of {group}")
+    if groups is not None and len(r) // group != groups:
+        raise ValueError(f"group_advantages: {len(r)} rewards make {len(r) // group} groups of {group}, "
+                         f"the caller expected {groups}")
     lv = torch.ones_like(r, dtype=torch.bool) if live is None else torch.tensor(list(live), dtype=torch.bool)
+    sg = r if signal is None else torch.tensor(list(signal), dtype=torch.float32)
     adv = torch.zeros_like(r)
     for g0 in range(0, len(r), group):
         sl = slice(g0, g0 + group)
@@ -56,6 +70,9 @@ def group_advantages(rewards: Sequence[float], group: int, live: Optional[Sequen
         sd = x.std(unbiased=False)
         if float(sd) < eps:
             continue
+        sx = sg[sl][m]
+        if float(sx.max()) == float(sx.min()):
+            continue                       # constant signal: what differs is shaping only
         a = torch.zeros(m.shape[0])
         a[m] = (x - x.mean()) / (sd + eps)
         adv[sl] = a
@@ -98,6 +115,17 @@ def tp_sync_replicated_grads(grads: Dict[str, torch.Tensor], group) -> None:
             g = grads[k].contiguous()
             dist.all_reduce(g, group=group)
             grads[k] = g
+
+
+def _clip(grads: Dict[str, torch.Tensor], max_norm: float, fb: Dict[str, object]) -> float:
+    """Global-norm clip with the SAME coefficient on every TP rank: sharded gradients add their
+    squares over the ranks, replicated ones count once; without this each rank would clip by its
+    own shard's norm and the replicated parameters (norms, embeddings) would drift apart."""
+    world = int(fb.get("tp_world", 1) or 1)
+    if world > 1:
+        from .parallel.mesh import grad_is_sharded
+        return clip_grad_norm(grads, max_norm, sharded=grad_is_sharded, tp_group=fb.get("tp_group"), tp_world=world)
+    return clip_grad_norm(grads, max_norm)
 
 
 def _scored_mask(ids: torch.Tensor, prompt_lens, seq_lens) -> torch.Tensor:
@@ -159,7 +187,7 @@ def train_step(model, ids: torch.Tensor, optimizer, *, seq_lens=None, max_norm: 
         total += loss
         for k, g in grads.items():
             acc[k] = g if k not in acc else acc[k] + g
-    norm = clip_grad_norm(acc, max_norm)
+    norm = _clip(acc, max_norm, fb)
     optimizer.step(acc, lr)
     return dict(loss=total, grad_norm=norm, tokens=n)
 
@@ -208,7 +236,7 @@ def policy_step(model, ids: torch.Tensor, prompt_lens, seq_lens, advantages: tor
         for k, g in grads.items():
             acc[k] = g if k not in acc else acc[k] + g
     stats["ratio_mean"] /= n
-    stats["grad_norm"] = clip_grad_norm(acc, max_norm)
+    stats["grad_norm"] = _clip(acc, max_norm, fb)
     stats["tokens"] = n
     if optimizer is not None:
         optimizer.step(acc, lr)
@@ -253,9 +281,10 @@ def grpo_loop(engine: Engine, model, prompts: Sequence[Sequence[int]], reward_fn
         t1 = time.perf_counter()
         comps = [r.tokens if r is not None else [] for r in results]
         live = [len(c) > 0 for c in comps]
-        rewards = [float(reward_fn(batch_prompts[i // group], c)) - length_penalty * len(c)
-                   for i, c in enumerate(comps)]
-        adv = group_advantages(rewards, group, live)
+        task = [float(reward_fn(batch_prompts[i // group], c)) for i, c in enumerate(comps)]
+        rewards = [t - length_penalty * len(c) for t, c in zip(task, comps)]
+        # the task reward is the signal: a group that only differs in length gets no gradient
+        adv = group_advantages(rewards, group, live, signal=task, groups=prompts_per_step)
         seqs = [list(batch_prompts[i // group]) + c for i, c in enumerate(comps)]
         plens = [len(batch_prompts[i // group]) for i in range(len(seqs))]
         slens = [len(s) for s in seqs]
@@ -288,46 +317,48 @@ def grpo_loop(engine: Engine, model, prompts: Sequence[Sequence[int]], reward_fn
 
 def opd_loop(engine: Engine, model, prompts, optimizer, *, steps: int, max_tokens: int = 16,
              ema: float = 0.99, prompts_per_step: int = 2, lr=None, seed: int = 0, **fb):
-    """On-policy self-distillation: the student samples, an EMA copy of the
-    trainable tensors (the teacher) scores the same tokens, and the student
-    minimises the token-level reverse-KL estimate ``logp_s - logp_t`` on its own
-    samples (weights = stop-gradient of that gap)."""
+    """On-policy distillation with an EMA teacher: the engine generates each completion under an
+    exponential moving average of the trainable tensors (the teacher: the same model, only
+    adapter-sized memory is duplicated), then the student weights are swapped back in and take one
+    supervised :func:`train_step` on prompt + completion.  The swaps copy INTO the live tensors and
+    never rebind them -- the engine and captured graphs read those objects -- and the engine's
+    cached state is invalidated around every swap, because a prefix entry or a captured graph made
+    under one set of weights must not be replayed under the other.
+
+    Parity: reference ``opd_loop`` (``src/tilerl/train.py:1138-1200``): teacher generates under the
+    EMA adapters, student runs ``train_step``; here ``prompts_per_step`` prompts form one batch."""
     trainable = model.trainable()
     teacher = {k: v.detach().clone() for k, v in trainable.items()}
+    student = {k: v.detach().clone() for k, v in trainable.items()}
+
+    def swap_in(src):
+        with torch.no_grad():
+            for k, v in trainable.items():
+                v.copy_(src[k])
+        model.requantize_()
+        engine.invalidate_weights()
+
+    engine.invalidate_weights()
     cursor = 0
     for step in range(steps):
         ps = [prompts[(cursor + i) % len(prompts)] for i in range(prompts_per_step)]
         cursor += prompts_per_step
+        swap_in(teacher)                                   # the teacher generates
         rids = [engine.submit(p, SamplingParams(max_tokens=max_tokens, temperature=1.0, seed=seed + step * 131 + i))
                 for i, p in enumerate(ps)]
         results = drain(engine, rids)
         seqs = [list(p) + (r.tokens if r else []) for p, r in zip(ps, results)]
+        swap_in(student)                                   # the student learns from it
         ids = pad_batch(seqs).to(engine.device)
-        plens, slens = [len(p) for p in ps], [len(s) for s in seqs]
-        mask = _scored_mask(ids, plens, slens)
-        n = max(1.0, float(mask.sum()))
-        targets = torch.roll(ids, -1, 1)
-        # teacher scores with EMA weights swapped in
-        saved = {k: v.detach().clone() for k, v in trainable.items()}
-        for k, v in trainable.items():
-            v.copy_(teacher[k])
-        tl = model.forward_dense(T.Tape(), ids)
-        lp_t = ref.token_logprobs(tl.reshape(-1, tl.shape[-1]), targets.reshape(-1)).view(ids.shape)
-        for k, v in trainable.items():
-            v.copy_(saved[k])
-
-        def weights(lg):
-            lp_s = ref.token_logprobs(lg.reshape(-1, lg.shape[-1]), targets.reshape(-1)).view(ids.shape)
-            return -(lp_s - lp_t) * mask / n   # descend on E[(logp_s - logp_t) * grad logp_s]
-
-        loss, grads, _ = forward_backward(model, ids, targets, weights, trainable=trainable, **fb)
-        clip_grad_norm(grads, 1.0)
-        optimizer.step(grads, lr)
-        for k, v in trainable.items():
-            teacher[k].mul_(ema).add_(v.detach(), alpha=1 - ema)
+        m = train_step(model, ids, optimizer, seq_lens=[len(s) for s in seqs], lr=lr, **fb)
+        with torch.no_grad():
+            for k, v in trainable.items():
+                student[k].copy_(v)
+                teacher[k].mul_(ema).add_(v.detach(), alpha=1 - ema)
         model.requantize_()
         engine.invalidate_weights()
-        yield dict(step=step, loss=loss, tokens=n)
+        yield dict(step=step, loss=m["loss"], tokens=m["tokens"], grad_norm=m["grad_norm"],
+                   completion_tokens=sum(len(r.tokens) if r else 0 for r in results))
 
 
 def pretrain(model, data: Iterator[torch.Tensor], optimizer, *, steps: int, lr: float, warmup: int = 0,
