@@ -168,3 +168,20 @@ def test_adapter_and_train_state_resume(tmp_path):
     g = {k: torch.full_like(v, 0.5) for k, v in tr.items()}
     opt.step(g), opt2.step(g)
     assert all(torch.equal(tr[k], tr2[k]) for k in tr)
+
+
+def test_norm_fold_is_decided_by_name_not_by_value(tmp_path):
+    """A trained zero-centred norm far from zero (mean |w| above 0.5) still gets its +1, and the GDN
+    output norm, which is stored as is, never does -- whatever its values look like."""
+    cfg = tiny_hybrid()
+    master = random_master(cfg, seed=3)
+    master["L0.norm1"] = torch.full_like(master["L0.norm1"], 1.8)          # stored as 0.8: not "small"
+    master["L1.q_norm"] = torch.linspace(0.2, 2.5, master["L1.q_norm"].numel())
+    master["final_norm"] = torch.full_like(master["final_norm"], 2.0)
+    master["L0.gdn_norm"] = torch.full_like(master["L0.gdn_norm"], 0.05)   # plain norm with small weights
+    d = str(tmp_path / "n")
+    os.makedirs(d)
+    save_file(_hf_tensors(cfg, master, "bf16"), os.path.join(d, "model.safetensors"))
+    m = load_checkpoint(cfg, d)
+    for k in ("L0.norm1", "L1.q_norm", "final_norm", "L0.gdn_norm", "L1.norm2", "L1.k_norm"):
+        assert torch.allclose(m.params[k].float(), master[k].float(), atol=1e-2), k

@@ -195,3 +195,35 @@ def test_card_guard_with_a_fake_nvml():
     card_guard(0, nvml=Fake([P(1, 100 << 20)]))                      # a small foreign context is tolerated
     with pytest.raises(RuntimeError, match="in use by other processes"):
         card_guard(0, nvml=Fake([P(1, 40 << 30)]))
+
+
+def test_engine_reads_the_device_error_word_every_tick_and_fails_the_tick():
+    """A bounded device wait that ran out (here: a fake error word on the third tick, as a TP peer
+    that never pushed its partial rows would leave) must not turn into tokens: ``step`` raises
+    ``CommTimeout``, the running request ends with that error and the engine serves the next one."""
+    from helpers import make_engine, rand_prompts
+    from tilerl_b200.config import tiny_hybrid
+    from tilerl_b200.engine import SamplingParams
+    from tilerl_b200.parallel.health import CommTimeout
+    cfg = tiny_hybrid()
+    eng = make_engine(cfg)
+    reads = {"n": 0}
+
+    def fake_read():
+        reads["n"] += 1
+        return (1, 5, 3, 17) if reads["n"] == 3 else (0, 0, 0, 0)
+
+    eng.ops.read_device_error = fake_read
+    try:
+        rid = eng.submit(rand_prompts(cfg, 1, 12)[0], SamplingParams(max_tokens=8))
+        with pytest.raises(CommTimeout, match="code=1 a=5 b=3 c=17"):
+            for _ in range(10):
+                eng.step()
+        assert reads["n"] == 3                                   # one read per tick
+        res = eng.take(rid)
+        assert res is not None and res.error and "device wait gave up" in res.error
+        assert eng.stats()["device_errors"] == 1 and eng.liveness()["degraded"]
+        out = eng.generate([rand_prompts(cfg, 1, 12)[0]], SamplingParams(max_tokens=4))[0]
+        assert len(out.tokens) == 4 and not out.error
+    finally:
+        del eng.ops.read_device_error

@@ -214,8 +214,11 @@ def assemble_master(cfg: ModelConfig, reader: _Reader) -> Dict[str, torch.Tensor
     out: Dict[str, torch.Tensor] = {}
 
     def norm(name: str) -> torch.Tensor:
-        w = reader.get(name).float()
-        return w + 1.0 if float(w.abs().mean()) < 0.5 else w   # zero-centred storage -> +1 fold
+        # HF checkpoints of this family store these norms zero-centred (y = x_normed * (1 + w)): the
+        # +1 is folded in by NAME -- input / post-attention / q / k / final norm always, the GDN output
+        # norm never -- as the reference does (src/tilerl/model.py:810-811, :1162), not by looking at
+        # the values: a trained weight far from zero must load like any other
+        return reader.get(name).float() + 1.0
 
     if own:
         return {}

@@ -342,11 +342,29 @@ class Engine:
                     torch.cuda.nvtx.range_pop()
             else:
                 self._run(plan)
+            self._check_device_error()
             self.counters["ticks"] += 1
             self._last_progress = time.monotonic()
             if self.timing:
                 self.last_tick_ms = dict(prep=(t1 - t0) * 1e3, run=(time.perf_counter() - t1) * 1e3)
             return True
+
+    def _check_device_error(self) -> None:
+        """A kernel's bounded wait that ran out (a TP peer that never pushed its partial rows, a
+        copy that never landed) leaves a record in the device error word and returns: the tick then
+        completed on incomplete sums.  Read the word once per tick; on a record, fail the requests
+        of this tick instead of emitting their tokens, and tell the caller."""
+        read = getattr(self.ops, "read_device_error", None)
+        if read is None:
+            return
+        code, a, b, c = read()
+        if code:
+            from .parallel.health import CommTimeout
+            msg = f"device wait gave up: code={code} a={a} b={b} c={c}"
+            self.counters["device_errors"] = self.counters.get("device_errors", 0) + 1
+            self._degraded = msg
+            self._fail_running(msg)
+            raise CommTimeout(msg)
 
     def _blocks_needed(self, n_tokens: int) -> int:
         return (n_tokens + KV_BLOCK - 1) // KV_BLOCK

@@ -467,6 +467,12 @@ class CudaOps:
         self.quantize_nvfp4_(w.contiguous(), dst)
         return dst
 
+    def read_device_error(self, clear: bool = True):
+        """``(code, a, b, c)`` of the device error word: non-zero code when a bounded wait of a kernel
+        (a peer's partial rows, an mbarrier) ran out since the last read.  Synchronises the stream."""
+        torch.cuda.current_stream(self.device).synchronize()
+        return N.read_error(clear)
+
     def device_alive(self) -> bool:
         """Synchronising probe: False when the context no longer answers (sticky error).  The engine
         loop polls it and exits the process on False so a supervisor restarts it.

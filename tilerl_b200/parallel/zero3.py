@@ -239,6 +239,9 @@ class Zero3:
             if u.grad is not None:
                 self.stats["flushed"] = self.stats.get("flushed", 0) + 1
                 self._reduce(u)
+        wait = getattr(self.comm, "wait", None)
+        if wait is not None:
+            wait()                 # the reduced shards are read next (norm, optimizer)
 
     # ---- optimizer --------------------------------------------------------------------------------
     def grad_norm(self) -> float:
@@ -260,11 +263,25 @@ class Zero3:
         self.t += 1
         lr = self.lr if lr is None else lr
         b1, b2 = self.betas
+        fused = None
+        if self.device.type == "cuda":
+            from ..ops import native as N
+            if N.available():
+                fused = N
         for i, g in enumerate(self.gshard):
             if g is None:
                 continue
-            g = g * clip
             m, v, w = self.m[i], self.v[i], self.master[i]
+            if fused is not None and g.dtype == torch.float32 and g.is_contiguous():
+                # one kernel per unit: the clip coefficient rides along as the gradient scale, no
+                # temporaries of the shard's size
+                fused.check(fused.lib().trl_adamw(w.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), None,
+                                                  w.numel(), lr, b1, b2, self.eps, self.wd, self.t, clip,
+                                                  fused.stream()), "adamw")
+                fused.count()
+                self.gshard[i] = None
+                continue
+            g = g * clip
             m.mul_(b1).add_(g, alpha=1 - b1)
             v.mul_(b2).addcmul_(g, g, value=1 - b2)
             mhat = m / (1 - b1 ** self.t)
@@ -274,7 +291,17 @@ class Zero3:
             w.sub_(lr * mhat / (vhat.sqrt() + self.eps))
             self.gshard[i] = None
         self._drop(self.units[-1])
+        self.check_device()
         return norm
+
+    def check_device(self) -> None:
+        """Raise ``CommTimeout`` when a bounded wait of a peer-memory collective ran out during the
+        step (the kernels record it in the device error word and return)."""
+        if self.device.type == "cuda" and getattr(self.comm, "device_waits", False):
+            from ..ops import native as N
+            from .health import raise_on_device_error
+            torch.cuda.synchronize(self.device)
+            raise_on_device_error(lambda: N.read_error(True))
 
     # ---- whole-model views --------------------------------------------------------------------------
     def gather_all(self) -> None:
@@ -312,14 +339,19 @@ class Zero3:
 class P2PComm:
     """ZeRO collectives by the kernels of ``csrc/zero.cu`` over NVLink peer memory.
 
-    One symmetric region per rank, exported with CUDA IPC, with two staging areas: the
-    parameter shard in the working dtype (the fp32 master shard is cast straight into it) and
-    the full flat gradient of the unit being reduced (``grad_buffer`` hands that area out, so
-    the backward writes gradients where the peers will read them -- no staging copy).
-    Every collective is enqueued on this object's own stream, in program order on every rank,
-    so at most one of them runs per GPU and a prefetch never meets a reduce-scatter half way;
-    the caller's stream is joined before and after."""
+    One symmetric region per rank, exported with CUDA IPC, with the staging areas: the
+    parameter shard in the working dtype (the fp32 master shard is cast straight into it) and TWO
+    areas for the full flat gradient of a unit (``grad_buffer`` hands them out in turn, so the
+    backward writes gradients where the peers will read them -- no staging copy -- and the
+    backward of the next layer fills one area while the reduce-scatter of the previous layer still
+    reads the other).  Every collective is enqueued on this object's own stream, in program order
+    on every rank, so at most one of them runs per GPU and a prefetch never meets a
+    reduce-scatter half way.  The caller's stream is joined before every collective; after an
+    all-gather it is joined again (the parameters are about to be used), after a reduce-scatter it
+    is NOT: the reduced shard is awaited by ``wait()`` (``Zero3.flush``) or by the event of its
+    area, so the reduction overlaps the backward that follows."""
     align = 8          # elements: shards are moved in 16-byte vectors
+    device_waits = True      # its kernels wait on peers with a bound and record a give-up on the device
 
     def __init__(self, group, device, cap_bytes: int):
         """``cap_bytes``: the largest unit's flat gradient in the working dtype."""
@@ -341,7 +373,8 @@ class P2PComm:
         self.cap_grad = (cap_bytes + 255) // 256 * 256
         self.cap_shard = (cap_bytes // self.world + 4096 + 255) // 256 * 256
         self.off_shard, self.off_grad = off, off + self.cap_shard
-        self.nbytes = self.off_grad + self.cap_grad
+        self.off_grads = [self.off_grad, self.off_grad + self.cap_grad]
+        self.nbytes = self.off_grad + 2 * self.cap_grad
         p = ctypes.c_void_p()
         N.check(self.lib.trl_symm_alloc(self.nbytes, ctypes.byref(p)), "symm_alloc")
         self.local_ptr = p.value
@@ -360,7 +393,11 @@ class P2PComm:
         self.table = (ctypes.c_void_p * 8)(*(self.ptrs + [None] * (8 - self.world)))
         self.mem = torch.as_tensor(_DevMem(self.local_ptr, self.nbytes), device=self.device)
         self.stage_shard = self.mem[self.off_shard:self.off_shard + self.cap_shard]
-        self.stage_grad = self.mem[self.off_grad:self.off_grad + self.cap_grad]
+        self.stage_grads = [self.mem[o:o + self.cap_grad] for o in self.off_grads]
+        self.stage_grad = self.stage_grads[0]
+        self._lent = [False, False]            # area handed to a unit's backward, not yet reduced
+        self._read_done = [None, None]         # event: the last reduce-scatter has read the area
+        self._next_area = 0
         self.stream = torch.cuda.Stream(device=self.device)
         self._check = N.check
         dist.barrier(group=group)
@@ -371,19 +408,34 @@ class P2PComm:
         return cur
 
     def grad_buffer(self, numel: int, dtype, device) -> torch.Tensor:
-        """The gradient staging area as a zeroed tensor (falls back to ordinary memory if the
-        unit is larger than the area)."""
+        """A gradient staging area as a zeroed tensor (ordinary memory if the unit is larger than an
+        area or both areas are lent out)."""
         nb = numel * torch.empty(0, dtype=dtype).element_size()
-        if nb > self.cap_grad or getattr(self, "_grad_out", False):
-            return torch.zeros(numel, dtype=dtype, device=device)   # too large, or another unit holds the area
-        self._grad_out = True
-        torch.cuda.current_stream(self.device).wait_stream(self.stream)   # the last reduce-scatter has read it
-        buf = self.stage_grad[:nb].view(dtype)
+        k = self._next_area
+        if self._lent[k]:
+            k ^= 1
+        if nb > self.cap_grad or self._lent[k]:
+            return torch.zeros(numel, dtype=dtype, device=device)
+        self._lent[k] = True
+        self._next_area = k ^ 1
+        if self._read_done[k] is not None:           # the reduce-scatter that last used this area has read it
+            torch.cuda.current_stream(self.device).wait_event(self._read_done[k])
+        buf = self.stage_grads[k][:nb].view(dtype)
         buf.zero_()
         return buf
 
+    def _area_of(self, t: torch.Tensor) -> int:
+        for k, a in enumerate(self.stage_grads):
+            if t.data_ptr() == a.data_ptr():
+                return k
+        return -1
+
     def is_staged(self, t: torch.Tensor) -> bool:
-        return t.data_ptr() == self.stage_grad.data_ptr()
+        return self._area_of(t) >= 0
+
+    def wait(self) -> None:
+        """Join the caller's stream with everything enqueued here (the reduced shards are read next)."""
+        torch.cuda.current_stream(self.device).wait_stream(self.stream)
 
     def all_gather(self, shard: torch.Tensor, full: torch.Tensor, stream=None) -> None:
         nb = shard.numel() * full.element_size()
@@ -402,23 +454,27 @@ class P2PComm:
         nb = full.numel() * full.element_size()
         if nb > self.cap_grad or shard_out.numel() % 8 or full.dtype not in (torch.bfloat16, torch.float32):
             raise ValueError("gradient does not fit the staging area, or shard not a multiple of 8 elements")
-        cur = self._enter()
+        self._enter()
+        k = self._area_of(full)
         with torch.cuda.stream(self.stream):
-            if full.data_ptr() != self.stage_grad.data_ptr():
-                if getattr(self, "_grad_out", False):
-                    # the area is lent to another unit's backward: wait is not an option here, the
-                    # caller owns both; this cannot happen with one layer in flight at a time
-                    raise RuntimeError("gradient staging area is lent out while another unit is reduced")
-                self.stage_grad[:nb].copy_(full.contiguous().view(torch.uint8))
+            if k < 0:
+                k = 0 if not self._lent[0] else 1
+                if self._lent[k]:
+                    # both areas are lent to units whose backward is still running: cannot happen with
+                    # at most two layers in flight
+                    raise RuntimeError("both gradient staging areas are lent out while another unit is reduced")
+                self.stage_grads[k][:nb].copy_(full.contiguous().view(torch.uint8))   # ordered on this stream
                 full.record_stream(self.stream)
             else:
-                self._grad_out = False
-            self._check(self.lib.trl_zero_reduce_scatter(self.table, self.rank, self.world, self.off_grad,
+                self._lent[k] = False
+            self._check(self.lib.trl_zero_reduce_scatter(self.table, self.rank, self.world, self.off_grads[k],
                                                          shard_out.numel(), int(full.dtype == torch.bfloat16),
                                                          float(scale), shard_out.data_ptr(), int(accumulate),
                                                          self.stream.cuda_stream), "zero_reduce_scatter")
+            ev = torch.cuda.Event()
+            ev.record(self.stream)
+            self._read_done[k] = ev
         shard_out.record_stream(self.stream)
-        cur.wait_stream(self.stream)
 
     def all_reduce_scalar(self, t: torch.Tensor) -> torch.Tensor:
         if self.world > 1:
