@@ -89,7 +89,7 @@ def build_parser() -> argparse.ArgumentParser:
     t.add_argument("--ctx", type=int, default=None, help="sequence length of the indexer warm-up batches")
     t.add_argument("--eval-every", type=int, default=0, help="adapter runs: eval reward on held-out prompts every N steps")
     t.add_argument("--patience", type=int, default=3, help="adapter runs: stop after this many evals without improvement")
-    t.add_argument("--runs", default="runs")
+    t.add_argument("--runs", default=None, help="run manifest directory (default: $TRL_RUNS or ./runs)")
 
     b = sub.add_parser("bench", help="prefill / decode throughput, kernel roofline table, calibration")
     _add_model_flags(b)
@@ -117,7 +117,7 @@ def build_parser() -> argparse.ArgumentParser:
     m.add_argument("--method", default="average", choices=["average", "ties", "dare", "iso"])
 
     lg = sub.add_parser("ledger", help="list runs, show lineage, list devices")
-    lg.add_argument("--runs", default="runs")
+    lg.add_argument("--runs", default=None, help="run manifest directory (default: $TRL_RUNS or ./runs)")
     lg.add_argument("--show", default=None)
     lg.add_argument("--devices", action="store_true")
     return ap
@@ -205,7 +205,7 @@ def cmd_train(args) -> int:
     from .checkpoint import load_adapter, save_adapter, save_checkpoint
     from .config import get_config
     from .factory import build_engine, build_model, make_ops
-    from .ledger import Run
+    from .ledger import Run, runs_dir
     from .optim import make_optimizer
     from .recipes import expand
     if getattr(args, "deterministic", False):
@@ -236,7 +236,7 @@ def cmd_train(args) -> int:
         ix = LearnedIndexer(cfg, seed=args.seed)
         g = torch.Generator().manual_seed(args.seed)
         seqs = [torch.randint(0, cfg.vocab, (flags.get("ctx") or 256,), generator=g) for _ in range(4)]
-        run = Run({"cmd": "train", **flags}, root=args.runs)
+        run = Run({"cmd": "train", **flags}, root=args.runs or runs_dir())
         hist = warmup(model, ix, seqs, steps=flags["steps"], lr=flags.get("lr") or 3e-3)
         for i, kl in enumerate(hist):
             run.log(step=i, kl=kl)
@@ -257,7 +257,7 @@ def cmd_train(args) -> int:
         if args.load_adapter:
             load_adapter(model, args.load_adapter)
     opt = make_optimizer(flags.get("optim", "adamw"), model.trainable(), flags["lr"])
-    run = Run({"cmd": "train", **flags}, root=args.runs)
+    run = Run({"cmd": "train", **flags}, root=args.runs or runs_dir())
     eng = build_engine(model, ops, device=dev, slots=flags["group"] * flags["prompts_per_step"] + 1,
                        max_ctx=args.prompt_len + flags["max_tokens"] + 32, prefix=False, graph=False)
     g = torch.Generator().manual_seed(args.seed)

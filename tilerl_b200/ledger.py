@@ -13,7 +13,11 @@ import time
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional
 
-RUNS_DIR = os.environ.get("TRL_RUNS", "runs")
+def runs_dir() -> str:
+    """Where run manifests live: ``$TRL_RUNS`` (read at call time, so a test or a job can point it
+    elsewhere) or ``./runs``."""
+    return os.environ.get("TRL_RUNS", "runs")
+
 
 
 def run_id(inputs: Dict[str, Any]) -> str:
@@ -36,7 +40,7 @@ class Gate:
 @dataclass
 class Run:
     inputs: Dict[str, Any]
-    root: str = RUNS_DIR
+    root: str = field(default_factory=runs_dir)
     parent: Optional[str] = None
     id: str = ""
     metrics: List[Dict[str, Any]] = field(default_factory=list)
@@ -77,12 +81,12 @@ class Run:
         os.replace(tmp, os.path.join(self.dir, "manifest.json"))
 
 
-def load_run(rid: str, root: str = RUNS_DIR) -> Dict[str, Any]:
-    with open(os.path.join(root, rid, "manifest.json")) as f:
+def load_run(rid: str, root: Optional[str] = None) -> Dict[str, Any]:
+    with open(os.path.join(root or runs_dir(), rid, "manifest.json")) as f:
         return json.load(f)
 
 
-def lineage(rid: str, root: str = RUNS_DIR) -> List[str]:
+def lineage(rid: str, root: Optional[str] = None) -> List[str]:
     chain = []
     cur: Optional[str] = rid
     while cur and cur not in chain:
@@ -94,8 +98,9 @@ def lineage(rid: str, root: str = RUNS_DIR) -> List[str]:
     return chain
 
 
-def list_runs(root: str = RUNS_DIR) -> List[Dict[str, Any]]:
+def list_runs(root: Optional[str] = None) -> List[Dict[str, Any]]:
     out = []
+    root = root or runs_dir()
     if os.path.isdir(root):
         for d in sorted(os.listdir(root)):
             try:

@@ -188,3 +188,55 @@ class SymmComm:
             if r != self.rank and p:
                 self.lib.trl_ipc_close(p)
         self.lib.trl_symm_free(self.local_ptr)
+
+
+class NcclComm:
+    """The unfused control: the same tensor-parallel op surface as :class:`SymmComm`, but every
+    collective is a library call -- ``dist.all_reduce`` after each row-parallel projection, an
+    all-gather of the vocabulary shards for the argmax -- on top of this repository's own
+    single-GPU kernels.  It is what the fused peer-memory kernels are measured against on the same
+    box (``bench.py --impl unfused``); NCCL calls are not captured by the decode graph here, so
+    its ticks run eagerly, as the reference's TP ticks do
+    (``src/tilerl/tensor_parallel.py:20-24``; collectives ``tilerl_kernels/backend.py:260-281``)."""
+    graph_capturable = False
+
+    def __init__(self, group, device):
+        self.group, self.device = group, torch.device(device)
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.pending = None
+
+    def attach(self, ops) -> None:
+        pass
+
+    def settle(self) -> None:
+        pass
+
+    def consume_pending(self, *a, **k) -> bool:
+        return False
+
+    def linear_allreduce_residual(self, ops, a, w, residual, lora=None):
+        t, n = a.shape[0], w.shape[0]
+        part = ops.ws.get("nccl_part", (t, n), torch.bfloat16)
+        ops._linear(a, w, part)
+        if lora is not None:
+            ops._lora_add(part, a, lora)
+        dist.all_reduce(part, group=self.group)
+        residual.add_(part)
+        N.count(2)
+        return residual
+
+    def all_gather_logits(self, logits: torch.Tensor) -> torch.Tensor:
+        parts = [torch.empty_like(logits) for _ in range(self.world)]
+        dist.all_gather(parts, logits.contiguous(), group=self.group)
+        return torch.cat(parts, dim=-1)
+
+    def argmax(self, ops, logits, v_valid: int):
+        full = self.all_gather_logits(logits)
+        if ops.vocab:
+            full = full[..., :ops.vocab]
+        out = ops.ws.get("argmax", (logits.shape[0],), torch.int32)
+        out.copy_(full.argmax(-1).to(torch.int32))
+        return out
+
+    def close(self) -> None:
+        pass
