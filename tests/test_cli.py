@@ -107,3 +107,40 @@ def test_serve_learned_scorer_needs_an_indexer_checkpoint():
     with pytest.raises(SystemExit) as e:
         cli.main(["serve", "--model", "tiny", "--device", "cpu", "--sparse-k", "4", "--scorer", "learned"])
     assert "--indexer" in str(e.value)
+
+
+def test_bench_suites_are_product_entry_points(capsys):
+    """``bench --suite list`` names the measurement suites; each one is an importable module with a
+    ``main(argv)`` whose ``--help`` parses (the suites themselves need a GPU)."""
+    import importlib
+    import pytest
+    from tilerl_b200 import suites
+    assert cli.main(["bench", "--suite", "list"]) == 0
+    names = capsys.readouterr().out.split()
+    assert set(names) == set(suites.SUITES) and {"spec", "batch", "sparse", "tick", "grpo", "grpo-zero3"} <= set(names)
+    for mod, _ in suites.SUITES.values():
+        m = importlib.import_module(f"tilerl_b200.suites.{mod}")
+        with pytest.raises(SystemExit) as e:
+            m.main(["--help"])
+        assert e.value.code == 0
+    capsys.readouterr()
+    with pytest.raises(SystemExit):
+        cli.main(["bench", "--suite", "nope"])
+    with pytest.raises(SystemExit):
+        cli.main(["bench", "--no-such-flag"])          # unknown flags stay errors outside --suite
+
+
+def test_bench_record_line_appends_validated_records(tmp_path, monkeypatch, capsys):
+    from tilerl_b200 import benchrec
+    store = tmp_path / "m.jsonl"
+    monkeypatch.setenv("TRL_BENCH_STORE", str(store))
+    line = {"metric": "decode_tok_s_b1_27b_nvfp4_prompt512_gen64", "value": 200.0, "n_gpus": 2, "warmup": 3,
+            "config": {"model": "qwen38-27b", "prompt_len": 512, "gen_len": 64}, "prefill_tok_s": 9000.0,
+            "decode_ms_per_tick": 5.0, "served_bytes": 10_000_000_000,
+            "e2e": {"request_tok_s": 150.0, "ttft_ms": 40.0}}
+    f = tmp_path / "line.json"
+    f.write_text("noise\n" + json.dumps(line) + "\n")
+    assert cli.main(["bench", "--record-line", str(f)]) == 0
+    recs = benchrec.load(str(store))
+    assert {r["metric"] for r in recs} == {"decode_tok_s", "decode_ms_per_tick", "prefill_tok_s", "e2e_request_tok_s", "ttft_ms"}
+    assert all(r["status"] == "ok" and r["shape"]["tp"] == 2 for r in recs)

@@ -15,7 +15,7 @@ LEVEL = {
     "sparse_index": 3, "engine": 3,
     "factory": 4, "evals": 4, "server": 4,
     "generate": 5, "rl": 5,
-    "cli": 6, "utils": 6,
+    "cli": 6, "utils": 6, "suites": 6,
 }
 
 

@@ -18,6 +18,10 @@ import time
 from typing import Any, Dict, List, Optional
 
 STORE = os.environ.get("TRL_BENCH_STORE", os.path.join("bench", "measurements.jsonl"))
+
+
+def store_path() -> str:
+    return os.environ.get("TRL_BENCH_STORE", STORE)
 GATE_RATIO = 0.97
 
 # metric -> (unit, higher_is_better, required shape keys)
@@ -90,8 +94,9 @@ def validate(rec: Dict[str, Any]) -> Dict[str, Any]:
     return rec
 
 
-def append(rec: Dict[str, Any], path: str = STORE) -> Dict[str, Any]:
+def append(rec: Dict[str, Any], path: Optional[str] = None) -> Dict[str, Any]:
     rec = validate(rec)
+    path = path or store_path()
     os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
     with open(path, "a") as f:
         f.write(json.dumps(rec, sort_keys=True) + "\n")
@@ -125,3 +130,31 @@ def gate(rec: Dict[str, Any], records: List[Dict[str, Any]], ratio: float = GATE
     hib = METRICS[rec["metric"]][1]
     r = rec["value"] / base["value"] if hib else base["value"] / rec["value"]
     return {"passed": r >= ratio, "ratio": round(r, 4), "baseline": base["value"], "baseline_commit": base["commit"]}
+
+
+def records_from_bench_line(line: Dict[str, Any], *, hbm_gbs: Optional[float] = None) -> List[Dict[str, Any]]:
+    """The records held by one JSON line of the repository's ``bench.py`` (decode and prefill
+    throughput, tick time, end-to-end request rate, time to first token), with the decode floor
+    from the served bytes a tick streams at ``hbm_gbs`` (no floor without it)."""
+    cfg = line.get("config", {})
+    tp = int(line.get("n_gpus", 1))
+    model, plen, gen = cfg.get("model", "?"), int(cfg.get("prompt_len", 0)), int(cfg.get("gen_len", 0))
+    warm = int(line.get("warmup", 3))
+    floor_tok_s = None
+    if hbm_gbs and line.get("served_bytes"):
+        floor_tok_s = hbm_gbs * 1e9 / float(line["served_bytes"])     # a tick cannot stream faster than HBM
+    dshape = {"model": model, "batch": 1, "ctx": plen, "tp": tp}
+    out = [make_record("decode_tok_s", line["value"], dshape, warm=warm, floor=floor_tok_s)]
+    if line.get("decode_ms_per_tick"):
+        out.append(make_record("decode_ms_per_tick", line["decode_ms_per_tick"], dshape, warm=warm,
+                               floor=(1e3 / floor_tok_s if floor_tok_s else None)))
+    if line.get("prefill_tok_s"):
+        out.append(make_record("prefill_tok_s", line["prefill_tok_s"], {"model": model, "prompt_len": plen, "tp": tp},
+                               warm=warm))
+    e2e = line.get("e2e") or {}
+    if e2e.get("request_tok_s"):
+        out.append(make_record("e2e_request_tok_s", e2e["request_tok_s"],
+                               {"model": model, "prompt_len": plen, "gen": gen, "tp": tp}, warm=warm))
+    if e2e.get("ttft_ms"):
+        out.append(make_record("ttft_ms", e2e["ttft_ms"], {"model": model, "prompt_len": plen, "tp": tp}, warm=warm))
+    return out

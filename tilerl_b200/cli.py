@@ -101,6 +101,11 @@ def build_parser() -> argparse.ArgumentParser:
     b.add_argument("--calibrate", action="store_true", help="measure HBM / GEMM / H2D floors")
     b.add_argument("--tp", type=int, default=1)
     b.add_argument("--record", action="store_true", help="append results to the bench store")
+    b.add_argument("--suite", default=None,
+                   help="run a measurement suite (spec, batch, sparse, tick, grpo, grpo-zero3; 'list' prints them); "
+                        "flags the bench parser does not know go to the suite")
+    b.add_argument("--record-line", default=None, metavar="FILE",
+                   help="append the records of a bench.py JSON line (a file holding that line) to the bench store")
 
     g = sub.add_parser("generate", help="offline generation, one process per GPU")
     _add_model_flags(g)
@@ -303,6 +308,23 @@ def cmd_bench(args) -> int:
     from . import kernel_cost as kc
     from .calibration import calibrate, load_peaks
     from .config import get_config
+    if args.suite:
+        from . import suites
+        if args.suite == "list":
+            print("\n".join(sorted(suites.SUITES)))
+            return 0
+        return suites.run(args.suite, getattr(args, "suite_args", []))
+    if args.record_line:
+        from . import benchrec
+        with open(args.record_line) as f:
+            lines = [ln for ln in f.read().splitlines() if ln.startswith("{")]
+        n = 0
+        from .calibration import load_peaks
+        for rec in benchrec.records_from_bench_line(json.loads(lines[-1]), hbm_gbs=load_peaks().hbm_gbs):
+            benchrec.append(rec)
+            n += 1
+        print(f"appended {n} records to {benchrec.store_path()}")
+        return 0
     cfg = get_config(args.model)
     if args.calibrate:
         import dataclasses
@@ -381,7 +403,10 @@ def cmd_ledger(args) -> int:
 
 
 def main(argv: Optional[List[str]] = None) -> int:
-    args = build_parser().parse_args(argv)
+    args, rest = build_parser().parse_known_args(argv)
+    if rest and not (args.cmd == "bench" and args.suite):
+        build_parser().parse_args(argv)          # unknown flags are an error everywhere else
+    args.suite_args = rest
     return {"serve": cmd_serve, "train": cmd_train, "bench": cmd_bench, "generate": cmd_generate,
             "merge": cmd_merge, "ledger": cmd_ledger}[args.cmd](args)
 

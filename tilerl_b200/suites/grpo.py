@@ -1,6 +1,6 @@
 """Time GRPO steps on one GPU: rollout through the engine, policy update on the tape.
 
-    python -m tilerl_b200.utils.grpo_probe --model qwen38-27b --group 8 --prompts 1 \
+    python -m tilerl_b200.suites.grpo --model qwen38-27b --group 8 --prompts 1 \
         --prompt-len 256 --gen 1024 --lora 16 --micro 1 --steps 2
 
 Prints one JSON line per step with the phase timings (rollout / score / train / invalidate) and
@@ -16,8 +16,8 @@ import time
 import torch
 
 
-def main():
-    ap = argparse.ArgumentParser()
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="tilerl_b200.suites.grpo")
     ap.add_argument("--model", default="qwen38-27b")
     ap.add_argument("--group", type=int, default=8)
     ap.add_argument("--prompts", type=int, default=1)
@@ -28,7 +28,7 @@ def main():
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--lr", type=float, default=1e-6)
     ap.add_argument("--graph", type=int, default=1)
-    args = ap.parse_args()
+    args = ap.parse_args(argv)
     from tilerl_b200 import evals, rl
     from tilerl_b200.config import get_config
     from tilerl_b200.factory import build_engine, build_model, make_ops

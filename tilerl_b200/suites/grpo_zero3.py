@@ -2,7 +2,7 @@
 ranks (one process per GPU, launched by torchrun):
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
-        -m tilerl_b200.utils.grpo_zero3_probe --model qwen38-27b --prompts 8 --group 8 \
+        -m tilerl_b200.suites.grpo_zero3 --model qwen38-27b --prompts 8 --group 8 \
         --prompt-len 256 --gen 512 --steps 2
 
 Every rank holds (a) its TP shard of the NVFP4 rollout weights and (b) its ZeRO-3 shard of the
@@ -23,8 +23,8 @@ import torch
 import torch.distributed as dist
 
 
-def main():
-    ap = argparse.ArgumentParser()
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="tilerl_b200.suites.grpo_zero3")
     ap.add_argument("--model", default="qwen38-27b")
     ap.add_argument("--prompts", type=int, default=8)
     ap.add_argument("--group", type=int, default=8)
@@ -34,7 +34,7 @@ def main():
     ap.add_argument("--lr", type=float, default=1e-6)
     ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"])
     ap.add_argument("--micro", type=int, default=0, help="sequences per micro-batch on a rank (0: all)")
-    args = ap.parse_args()
+    args = ap.parse_args(argv)
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)

@@ -1,8 +1,8 @@
 """Timings of the speculative-decode and long-context sparse-KV configurations on one GPU.
 
-    python -m tilerl_b200.utils.config_probe --what spec   [--prompts 8 --gen 128 --width 8]
-    python -m tilerl_b200.utils.config_probe --what sparse [--ctx 32768 --top-k 128 --ticks 32]
-    python -m tilerl_b200.utils.config_probe --what batch  [--requests 8 --prompt-len 7400 --gen 256]
+    python -m tilerl_b200.suites.serve --what spec   [--prompts 8 --gen 128 --width 8]
+    python -m tilerl_b200.suites.serve --what sparse [--ctx 32768 --top-k 128 --ticks 32]
+    python -m tilerl_b200.suites.serve --what batch  [--requests 8 --prompt-len 7400 --gen 256]
 
 ``spec``: B = 1, prompts of 80..300 random ids, a width-W verify tick timed at forced full
 acceptance (drafts = the trunk's own greedy continuation), at zero acceptance (a constant
@@ -139,8 +139,8 @@ def batch(args, cfg, ops, model):
                 ms_per_decode_tick=round(1000 * t_dec / max(1, ticks), 2), graph_ticks=eng.counters["graph_ticks"])
 
 
-def main():
-    ap = argparse.ArgumentParser()
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="tilerl_b200.suites.serve")
     ap.add_argument("--what", default="spec", choices=["spec", "sparse", "batch"])
     ap.add_argument("--requests", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=7400)
@@ -156,7 +156,7 @@ def main():
     ap.add_argument("--sample-top-k", type=int, default=0, help="batch: top-k restriction of the sampler")
     ap.add_argument("--kv-format", default="bf16", choices=["bf16", "fp8"], help="batch: KV pool format")
     ap.add_argument("--graph", type=int, default=1, help="spec: replay verify ticks from CUDA graphs")
-    args = ap.parse_args()
+    args = ap.parse_args(argv)
     from tilerl_b200.config import get_config
     from tilerl_b200.factory import build_model, make_ops
     cfg = get_config(args.model)

@@ -1,7 +1,7 @@
 """Run a few eager decode ticks (and optionally one prefill) of a model so a profiler
 can list every kernel of a tick with its device time.
 
-    python -m tilerl_b200.utils.tick_probe --model qwen38-27b --ticks 3 --ctx 512
+    python -m tilerl_b200.suites.tick --model qwen38-27b --ticks 3 --ctx 512
 
 Under ``ncu --metrics gpu__time_duration.sum`` the last tick's launches give the
 per-kernel time shares of the decode tick.  With ``--events`` the script prints its
@@ -16,15 +16,15 @@ import json
 import torch
 
 
-def main():
-    ap = argparse.ArgumentParser()
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="tilerl_b200.suites.tick")
     ap.add_argument("--model", default="qwen38-27b")
     ap.add_argument("--ticks", type=int, default=3)
     ap.add_argument("--ctx", type=int, default=512)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--prefill", type=int, default=0, help="also run one prefill of this many tokens")
     ap.add_argument("--events", action="store_true")
-    args = ap.parse_args()
+    args = ap.parse_args(argv)
     from tilerl_b200.batch import Batch
     from tilerl_b200.config import get_config
     from tilerl_b200.factory import build_model, make_ops
@@ -61,7 +61,7 @@ def main():
     if args.events:
         print(json.dumps({"tick_ms": {k: round(v, 4) for k, v in sorted(times.items(), key=lambda kv: -kv[1])},
                           "total_ms": round(sum(times.values()), 3)}))
-    print("tick_probe done")
+    print("tick suite done")
 
 
 def _wrap(ops, times):
