@@ -16,10 +16,11 @@
 // HBM speed with bf16-accurate activations.
 //
 // Schedule: stream-K.  The (tile, k-tile) units are split evenly over one CTA per
-// SM; a CTA whose range covers a whole tile finishes it from TMEM, otherwise partial
-// tiles are reduced with fp32 red.global.add into a scratch buffer and the last
-// arriving CTA of the tile (atomic counter) runs the epilogue and re-zeroes the
-// scratch.  Small-N / large-K projections (down_proj, o_proj) therefore use every SM.
+// SM; a CTA whose range covers a whole tile finishes it from TMEM, otherwise it stores its
+// partial tile into its own fp32 slot of a scratch buffer, and the last CTA of the tile to
+// arrive (atomic counter, reset by that CTA) sums the slots in segment order -- bitwise
+// reproducible, nothing to zero -- and runs the epilogue.  Small-N / large-K projections
+// (down_proj, o_proj) therefore use every SM.
 //
 // Warp roles (192 threads): warp 0 = TMA producer (weight tiles are prefetched
 // *before* griddepcontrol.wait, since they do not depend on the previous kernel),
@@ -191,7 +192,6 @@ struct GemmParams {
   int n_tiles, c_tiles, nk, kt4;
   int max_seg;
   int w_tiled; // weights stored tile-contiguous [n_tiles, nk, 128 rows, 128 B]
-  int dbg;     // timing experiments only: bit0 skip SF copies, bit1 skip MMAs, bit2 skip activation loads, bit3 skip the epilogue body
   int split;   // 1: stream-K over (tile, k-tile) units; 0: whole tiles per CTA
   int sa, sb;  // stages of the weight ring and of the activation ring
   int epi;
@@ -293,19 +293,23 @@ struct Cfg {
   }
 };
 
-// Phase timestamps of one launch (TRL_GEMM_DBG bit 4): [CTA][slot] = globaltimer in ns.
+// Phase timestamps of one launch (builds with -DTRL_TRACE only): [CTA][slot] = globaltimer in ns.
 //   0 entry, 1 set-up done, 2 producer past the dependency wait, 3 first operands landed,
 //   4 last MMA issued, 5 first accumulator complete, 6 last TMEM read-out done,
 //   7 split-tile finishing done, 8 teardown, 9 segment counted, 10 reduction starts,
 //   11 first reduction batch stored.
 constexpr int TRACE_SLOTS = 16, TRACE_CTAS = 256;
 __device__ unsigned long long g_gemm_trace[TRACE_CTAS * TRACE_SLOTS];
-__device__ __forceinline__ void trace_stamp(int dbg, int slot) {
-  if ((dbg & 16) && blockIdx.x < TRACE_CTAS) {
+__device__ __forceinline__ void trace_stamp(int slot) {
+#ifdef TRL_TRACE
+  if (blockIdx.x < TRACE_CTAS) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     g_gemm_trace[blockIdx.x * TRACE_SLOTS + slot] = t;
   }
+#else
+  (void)slot;
+#endif
 }
 
 template <int BN>
@@ -326,7 +330,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   float* rs_s = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(bars) + C::BAR_BYTES);  // [BN] column scales
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) trace_stamp(p.dbg, 0);
+  if (threadIdx.x == 0) trace_stamp(0);
   const uint32_t bar0 = smem_u32(bars);
   auto full_a = [&](int s) { return bar0 + 8u * s; };
   auto empty_a = [&](int s) { return bar0 + 8u * (MS + s); };
@@ -354,7 +358,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   pdl_launch_dependents();
-  if (threadIdx.x == 0) trace_stamp(p.dbg, 1);
+  if (threadIdx.x == 0) trace_stamp(1);
 
   const long long U = (long long)p.n_tiles * p.c_tiles * p.nk;
   const int G = gridDim.x;
@@ -426,7 +430,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         const int pre = min(SA, n_units);
         for (; a_issued < pre; ++a_issued) load_a_ls(ca), advance(ca, SA);
         pdl_wait();
-        trace_stamp(p.dbg, 2);
+        trace_stamp(2);
         bool ok = true;
         for (; ok && b_issued < n_units; ++b_issued) {
           if (b_issued >= pre) {
@@ -484,19 +488,19 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
           ok = mbar_wait(full_a(sa_i), sa_ph, abort_flag) && (SA == SB || mbar_wait(full_b(sb_i), sb_ph, abort_flag));
           if (!ok) break;
           tc_fence_after();
-          if (it == 0) trace_stamp(p.dbg, 3);
+          if (it == 0) trace_stamp(3);
           const uint32_t aoff = (uint32_t)sa_i * (uint32_t)(C::A_STAGE >> 4);
           const uint32_t boff = (uint32_t)sb_i * (uint32_t)(C::B_STAGE >> 4);
           const uint32_t sf_cols = tmem_base + C::SF_COL0 + (uint32_t)(it & 1) * 64;  // double-buffered by parity
 #pragma unroll
-          for (int kb = 0; kb < 4 && !(p.dbg & 1); ++kb) {
+          for (int kb = 0; kb < 4; ++kb) {
             tc_cp_sf_lh(sf_cols + kb * 4, sfa_lo + aoff + kb * (SF_ATOM >> 4), sf_hi);
 #pragma unroll
             for (int j = 0; j < C::SFB_ATOMS; ++j)
               tc_cp_sf_lh(sf_cols + 16 + kb * 8 + j * 4, sfb_lo + boff + (j * 4 + kb) * (SF_ATOM >> 4), sf_hi);
           }
 #pragma unroll
-          for (int kb = 0; kb < 4 && !(p.dbg & 2); ++kb)
+          for (int kb = 0; kb < 4; ++kb)
             tc_mma_nvfp4_lh(tmem_base, a_lo + aoff + kb * 2, b_lo + boff + kb * 2, op_hi, idesc, sf_cols + kb * 4,
                             sf_cols + 16 + kb * 8, (i | kb) ? 1u : 0u);
           tc_commit(empty_a(sa_i));
@@ -508,7 +512,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         u += len;
         ++seg;
       }
-      trace_stamp(p.dbg, 4);
+      trace_stamp(4);
     }
   } else {
     // ---------------- epilogue (warps 2..5) ----------------
@@ -555,7 +559,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
       }
       if (!ok) break;
       tc_fence_after();
-      if (seg == 0 && threadIdx.x == 64) trace_stamp(p.dbg, 5);
+      if (seg == 0 && threadIdx.x == 64) trace_stamp(5);
       // finishing one (token, row) value of a split tile (run-time epilogue kind)
       auto finish = [&](int tok, float v, float res) {
         if (p.epi == EPI_SWIGLU) epi_store<EPI_SWIGLU>(p, tok, n, lane, v, res);
@@ -566,7 +570,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         return (p.epi == EPI_RESIDUAL && tok < p.tokens && n < p.N)
                    ? __bfloat162float(p.residual[(size_t)tok * p.ldr + n]) : 0.f;
       };
-      if (!(p.dbg & 8)) {
+      {
         const uint32_t taddr0 = tmem_base + ((uint32_t)(quad * 32) << 16);
         if (J == 4) epilogue_dispatch<BN, 4>(p, whole, taddr0, rs_s, ts, tok0, n, lane, slot + row);
         else if (J == 2) epilogue_dispatch<BN, 2>(p, whole, taddr0, rs_s, ts, tok0, n, lane, slot + row);
@@ -574,7 +578,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
       }
       tc_fence_before();
       mbar_arrive(accum_empty);
-      if (threadIdx.x == 64) trace_stamp(p.dbg, 6);
+      if (threadIdx.x == 64) trace_stamp(6);
       if (!whole) {
         // split tile: the last CTA to arrive finishes it from the per-segment slots
         asm volatile("bar.sync 1, 128;" ::: "memory");   // all slot stores of this CTA issued
@@ -584,12 +588,12 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
           const int prev = atomicAdd(p.counters + tile, 1);
           *last_flag = (prev == nseg - 1);
           if (prev == nseg - 1) p.counters[tile] = 0;
-          trace_stamp(p.dbg, 9);
+          trace_stamp(9);
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (*last_flag) {
           __threadfence();
-          if (threadIdx.x == 64) trace_stamp(p.dbg, 10);
+          if (threadIdx.x == 64) trace_stamp(10);
           const int ntok = BN / J;
           const bool vec_ok = (p.N & 3) == 0 && (p.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 &&
                               (p.epi != EPI_RESIDUAL ||
@@ -652,7 +656,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                       make_uint2(f2_to_bf162_bits(a.x, a.y), f2_to_bf162_bits(a.z, a.w));
                 }
               }
-              if (g0 == 0 && threadIdx.x == 64) trace_stamp(p.dbg, 11);
+              if (g0 == 0 && threadIdx.x == 64) trace_stamp(11);
             }
           } else {
           // row-per-thread fallback for outputs that do not allow vector stores
@@ -685,7 +689,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
       }
-      if (threadIdx.x == 64) trace_stamp(p.dbg, 7);
+      if (threadIdx.x == 64) trace_stamp(7);
       u += len;
       ++seg;
     }
@@ -704,7 +708,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
   }
-  if (threadIdx.x == 0) trace_stamp(p.dbg, 8);
+  if (threadIdx.x == 0) trace_stamp(8);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -899,7 +903,7 @@ static int pick_bn(int cols) {
 }
 
 // Bytes of split-K scratch trl_gemm_nvfp4 needs for this problem (0 if no tile is split).
-// Copies the phase timestamps of the last traced launch (TRL_GEMM_DBG=16): n_ctas x 16 values.
+// Copies the phase timestamps of the last launch of a -DTRL_TRACE build: n_ctas x 16 values (zeros otherwise).
 TRL_API int trl_gemm_trace_read(void* out, int n_ctas) {
   if (n_ctas < 0 || n_ctas > TRACE_CTAS) return (int)cudaErrorInvalidValue;
   return (int)cudaMemcpyFromSymbol(out, g_gemm_trace, (size_t)n_ctas * TRACE_SLOTS * sizeof(unsigned long long));
@@ -950,10 +954,6 @@ TRL_API int trl_gemm_nvfp4(const void* wq, const void* sfw, const void* tscale, 
   if (max_ctas > 0) sms = min(sms, max_ctas);
   const long long U = (long long)p.n_tiles * p.c_tiles * p.nk;
   p.split = split;
-  {
-    const char* e = getenv("TRL_GEMM_DBG");
-    p.dbg = e ? atoi(e) : 0;
-  }
   p.w_tiled = w_tiled;
   const int grid = split ? (int)min((long long)sms, U) : min(sms, p.n_tiles * p.c_tiles);
   p.max_seg = split ? max_segments(U, grid, p.nk) : 1;

@@ -99,12 +99,10 @@ def main():
             res["gemm_tc_TBs"] = round(wbytes / us / 1e6, 3)
             if args.trace:
                 # one traced launch: phase timestamps per CTA, reported in us after the first CTA's entry
-                import os
+                # needs the timeline build: python -m tilerl_b200.build --trace; TRL_TRACE_LIB=1
                 import numpy as np
-                os.environ["TRL_GEMM_DBG"] = "16"
                 gemm_only(ws[0])
                 torch.cuda.synchronize()
-                os.environ.pop("TRL_GEMM_DBG")
                 buf = np.zeros((148, 16), dtype=np.uint64)
                 native.check(ops.lib.trl_gemm_trace_read(buf.ctypes.data, 148), "trace_read")
                 t = buf.astype(np.float64)
