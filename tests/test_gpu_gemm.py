@@ -133,3 +133,32 @@ def test_gemm_nvfp4_epilogues_and_fused_norm(ops):
     from tilerl_b200.ops import native
     torch.cuda.synchronize()
     assert native.read_error()[0] == 0
+
+
+@pytest.mark.parametrize("outliers", [False, True])
+def test_two_residual_terms_are_at_least_as_accurate_as_e4m3_1x128_activations(ops, outliers):
+    """The M > 1 path quantises an activation row into two NVFP4 residual terms.  Its error against
+    the exact product (bf16 activations x dequantised weights) must not exceed what the same GEMM
+    gives with the activations quantised to e4m3 with one scale per 1 x 128 block -- the FP8
+    activation format this path stands in for -- on plain and on outlier-heavy rows."""
+    from tilerl_b200.ops.gemm_tc import gemm_nvfp4
+    t, n, k = 96, 1024, 5120
+    g = torch.Generator().manual_seed(21)
+    w = _w(n, k, 17)
+    x = torch.randn(t, k, generator=g)
+    if outliers:                                  # a few channels 30x larger, as residual streams have
+        idx = torch.randint(0, k, (24,), generator=g)
+        x[:, idx] *= 30.0
+    x = x.to(DEV, torch.bfloat16)
+    wd = w.dequant().float()
+    exact = x.float() @ wd.t()
+    # e4m3 with a scale per 1 x 128 block (amax / 448), in torch
+    xb = x.float().view(t, k // 128, 128)
+    s = xb.abs().amax(-1, keepdim=True).clamp_min(1e-12) / 448.0
+    x8 = ((xb / s).to(torch.float8_e4m3fn).float() * s).view(t, k)
+    err_fp8 = _rel(x8 @ wd.t(), exact)
+    y = torch.zeros(t, n, dtype=torch.float32, device=DEV)
+    gemm_nvfp4(ops, x, w, y, terms=2, epi=3)
+    torch.cuda.synchronize()
+    err_j2 = _rel(y, exact)
+    assert err_j2 <= err_fp8 * 1.05 + 1e-4, (err_j2, err_fp8)

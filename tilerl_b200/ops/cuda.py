@@ -132,6 +132,9 @@ class CudaOps:
                 residual.stride(0) if residual is not None else 0, y.data_ptr(), y.stride(0),
                 m, n, k, epi, N.stream()), "gemv_bf16")
             N.count((m + 3) // 4)
+        elif isinstance(w, FP8BlockTensor):
+            from . import gemm_fp8
+            gemm_fp8.gemv(self, x, w, y, norm_w=norm_w, eps=eps, residual=residual, epi=epi)
         else:
             raise TypeError(f"no GEMV for weight type {type(w)}")
 
@@ -153,6 +156,10 @@ class CudaOps:
         t = x.shape[0]
         if not (t <= GEMV_MAX_M and not self._tc(w, t)):
             self.settle()     # only the GEMV path can finish a pending all-reduce itself
+        if isinstance(w, FP8BlockTensor) and w.shape[1] % 128 == 0:
+            from . import gemm_fp8
+            gemm_fp8.linear(self, x, w, y, norm_w=norm_w, eps=eps, residual=residual, epi=epi)
+            return
         if self._tc(w, t):
             from .gemm_tc import gemm_nvfp4
             terms = self.terms_small if t <= GEMV_MAX_M else self.terms_large
@@ -384,7 +391,7 @@ class CudaOps:
             self._gemv(x.contiguous(), w, logits, norm_w=self._f32(norm_w), eps=eps, epi=EPI_STORE_F32)
         else:
             xc = x.contiguous()
-            if isinstance(w, NVFP4Tensor) and self.use_tc_gemm:
+            if (isinstance(w, NVFP4Tensor) and self.use_tc_gemm) or isinstance(w, FP8BlockTensor):
                 self._linear(xc, w, logits, norm_w=self._f32(norm_w), eps=eps, epi=EPI_STORE_F32)
             else:
                 h = self._rmsnorm(xc, norm_w, eps, name="h_head")

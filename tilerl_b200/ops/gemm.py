@@ -6,6 +6,8 @@
   activation is quantised on the fly to NVFP4 (e2m1, e4m3 scale per 16, fp32 scale
   per token), both operands are streamed by TMA and multiplied by
   ``tcgen05.mma.kind::mxf4nvf4.block_scale`` with the accumulator in TMEM.
+* FP8 block weights: ``ops/gemm_fp8.py`` (``tcgen05.mma.kind::f8f6f4`` with per-128-k
+  promotion; ``csrc/gemm_fp8.cu``).
 * bf16 weights: the tcgen05 ``kind::f16`` GEMM (``csrc/gemm_bf16.cu``).
 
 ``TRL_GEMM=dequant`` selects a debugging path (dequantise to bf16 into scratch,
@@ -38,6 +40,9 @@ def linear(ops, x: torch.Tensor, w, y: torch.Tensor) -> None:
         torch.matmul(x, wd.t(), out=y)
         return
     if isinstance(w, FP8BlockTensor):
+        if hasattr(ops.lib, "trl_gemm_fp8") and _MODE == "tc" and w.shape[1] % 128 == 0:
+            from . import gemm_fp8
+            return gemm_fp8.linear(ops, x, w, y)
         wd = w.dequant().to(torch.bfloat16)
         torch.matmul(x, wd.t(), out=y)
         return

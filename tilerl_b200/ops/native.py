@@ -32,6 +32,9 @@ _SIGS = {
     "trl_attn_paged": [P, P, I, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, F, I, P],
     "trl_gdn": [P, I, P, P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, P, P, P, P, P, P, P,
                 I, I, I, I, I, I, I, F, P],
+    "trl_quant_act_fp8": [P, I, P, F, P, P, I, I, I, P],
+    "trl_gemm_fp8": [P, P, P, P, P, I, P, I, I, I, I, I, P],
+    "trl_gemv_fp8": [P, I, P, P, P, F, P, I, P, I, I, I, I, I, P],
     "trl_gdn_decode": [P, I, P, P, P, P, P, P, P, P, P, P, L, L, L, P, I, I, I, I, I, F, P],
     "trl_embedding": [P, P, P, I, I, I, P],
     "trl_gather_rows": [P, P, P, I, I, P],

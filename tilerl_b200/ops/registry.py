@@ -101,6 +101,11 @@ register("bf16", "sm100", {
     "linear_bf16_gemm": Kernel("torch.matmul (cuBLAS)", "tilerl_b200/ops/gemm.py", note="plain library GEMM"),
 })
 register("fp8", "sm100", {
+    "linear_fp8": Kernel("gemm_fp8_kernel", "csrc/gemm_fp8.cu", "trl_gemm_fp8",
+                         note="tcgen05 kind::f8f6f4, 128x128 weight blocks, per-128-k promotion from TMEM"),
+    "linear_fp8_gemv": Kernel("gemv_fp8_kernel", "csrc/gemm_fp8.cu", "trl_gemv_fp8"),
+    "quant_fp8": Kernel("quant_act_fp8_kernel", "csrc/gemm_fp8.cu", "trl_quant_act_fp8",
+                        note="RMSNorm / SwiGLU + e4m3 with one scale per token and 128 k"),
     "attn_prep": Kernel("attn_prep_fp8_kernel", "csrc/attn_fp8.cu", "trl_attn_prep_fp8", note="e4m3 KV pool"),
     "paged_attention_decode": Kernel("attn_split_fp8_kernel", "csrc/attn_fp8.cu", "trl_attn_paged_fp8"),
     "paged_attention_prefill": Kernel("attn_prefill_kernel<true>", "csrc/attn.cu", "trl_attn_prefill_fp8"),

@@ -1,6 +1,6 @@
 """Time individual kernels at the 27B's projection shapes with CUDA events.
 
-    python -m tilerl_b200.utils.kernel_bench [--m 1] [--only gemm|gemv|quant] [--reps 20]
+    python -m tilerl_b200.utils.kernel_bench [--m 1] [--only gemm|gemv|quant|fp8] [--reps 20]
 
 Each measurement rotates over enough distinct weight copies to exceed the 126 MB L2,
 so every launch streams its weights from HBM; the figure printed is achieved weight
@@ -113,6 +113,32 @@ def main():
                 res["trace_us"] = {nm: [round(float(np.median(t[live, i] - t0)) / 1e3, 2),
                                         round(float((t[live, i] - t0).max()) / 1e3, 2)]
                                    for i, nm in enumerate(names)}
+        if args.only == "fp8":
+            # block-scaled FP8 weights of the same shape: quantiser + tcgen05 GEMM, or the GEMV up to 8 rows
+            from tilerl_b200.formats import FP8BlockTensor
+            from tilerl_b200.ops import gemm_fp8
+            del ws
+            torch.cuda.empty_cache()
+            fbytes = n * k + (n // 128 + 1) * (k // 128) * 4
+            ws = [FP8BlockTensor(torch.randint(0, 120, (n, k), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn),
+                                 torch.rand((n + 127) // 128, k // 128, device=dev) + 0.5)
+                  for _ in range(max(2, int(400e6 // fbytes) + 1))]
+            copies = len(ws)
+            if args.m <= gemm_fp8.GEMV_ROWS:
+                us = timeit(lambda w: gemm_fp8.gemv(ops, x, w, y))
+                res["gemv_fp8_us"] = round(us, 2)
+                res["gemv_fp8_TBs"] = round(fbytes / us / 1e6, 3)
+            us = timeit(lambda w: gemm_fp8.gemm(ops, x, w, y))
+            res["quant+gemm_fp8_us"] = round(us, 2)
+            res["quant+gemm_fp8_TFLOPs"] = round(2.0 * args.m * n * k / us / 1e6, 1)
+            x8, sc = gemm_fp8.quant_act(ops, x)
+
+            def fp8_only(w):
+                native.check(ops.lib.trl_gemm_fp8(w.w8.data_ptr(), w.wscale.data_ptr(), x8.data_ptr(), sc.data_ptr(),
+                                                  None, 0, y.data_ptr(), y.stride(0), args.m, n, k, 0, native.stream()))
+            us = timeit(fp8_only)
+            res["gemm_fp8_us"] = round(us, 2)
+            res["gemm_fp8_TFLOPs"] = round(2.0 * args.m * n * k / us / 1e6, 1)
         if args.only in ("", "quant"):
             us = timeit(lambda w: quant_act(ops, x, k, args.terms))
             res["quant_us"] = round(us, 2)

@@ -2,6 +2,8 @@
 
     python -m tilerl_b200.build --trace
     TRL_TRACE_LIB=1 python -m tilerl_b200.utils.tick_trace [--model qwen38-27b] [--ctx 512]
+    TRL_TRACE_LIB=1 python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 \
+        -m tilerl_b200.utils.tick_trace          # tensor-parallel tick, rank 0's timeline
 
 The ``-DTRL_TRACE`` build records, per launch, when CTA 0 entered the kernel and when its
 dependency wait ended.  The wait of launch ``i + 1`` ends when launch ``i`` has completed, so
@@ -20,7 +22,7 @@ import torch
 
 KINDS = {2: "gdn_scan", 3: "attn_prep", 4: "attn_split", 5: "attn_combine", 6: "gemv_bf16(lm_head)", 7: "embedding",
          10: "allreduce_finish", 12: "gdn_prep", 100: "gemv2 store", 101: "gemv2 store+coop", 102: "gemv2 residual",
-         104: "gemv2 swiglu", 105: "gemv2 swiglu+coop", 106: "gemv2 store_f32", 108: "gemv2 push", 0: "other"}
+         104: "gemv2 swiglu", 105: "gemv2 swiglu+coop", 106: "gemv2 store_f32", 108: "gemv2 push", 109: "gemv2 push+coop", 0: "other"}
 
 
 def main():
@@ -33,10 +35,19 @@ def main():
     from tilerl_b200.factory import build_engine, build_model, make_ops
     from tilerl_b200.engine import SamplingParams
     from tilerl_b200.ops import native
-    dev = torch.device("cuda", 0)
+    import os
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    torch.cuda.set_device(dev)
     cfg = get_config(args.model)
-    ops = make_ops(dev)
-    model = build_model(cfg, dev, seed=0, ops=ops)
+    comm = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+        from tilerl_b200.parallel.symm import SymmComm
+        comm = SymmComm.create(dist.group.WORLD, dev)
+    ops = make_ops(dev, tp_comm=comm)
+    model = build_model(cfg, dev, seed=0, tp_rank=rank, tp=world, ops=ops)
     eng = build_engine(model, ops, slots=2, max_ctx=args.ctx + 64, graph=True, prefix=False)
     g = torch.Generator().manual_seed(1)
     prompt = torch.randint(0, cfg.vocab, (args.ctx,), generator=g).tolist()
@@ -71,8 +82,13 @@ def main():
            "critical_path_us": {k: {"n": v[0], "sum": round(v[1], 1), "avg": round(v[1] / v[0], 2),
                                     "resident_before_dep_avg": round(early[k] / v[0], 2)}
                                 for k, v in sorted(share.items(), key=lambda kv: -kv[1][1])}}
-    print(json.dumps(out, indent=1))
-    print("tick_trace done")
+    if rank == 0:
+        print(json.dumps(out, indent=1))
+        print("tick_trace done")
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
