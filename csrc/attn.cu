@@ -528,6 +528,195 @@ attn_prefill_kernel(const bf16* q, const bf16* gate_src, int gate_ld,
   }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Split-KV decode / verify attention on the tensor cores (mma.sync m16n8k16 bf16, fp32
+// accumulate; D = 256).  One CTA = (key split, kv head, group of `tpg` consecutive tokens of one
+// sequence): the G query heads of the kv head times the group's tokens are the (up to 16) rows
+// of ONE M tile, so a K / V row is read once for all of them -- the scalar kernel above reads
+// it once per token and spends 2 G D fp32 FMAs per key on it.  The CTA walks its key range in
+// tiles of 64 keys gathered through the block table with cp.async (double buffered, 128-bit
+// chunk XOR swizzle); warp w owns keys [16 w, 16 w + 16) of every tile with its own online
+// softmax state, and the four warps are merged through shared memory at the end.  Output:
+// the same split partials (unnormalised row, running max in the exp2 domain, denominator) the
+// combine kernel reads, or the finished gated row when there is one split.
+constexpr int DM_KEYS = 64, DM_WARPS = 4, DM_ROWS = 16;
+constexpr int DM_SMEM = DM_ROWS * PF_ROW + 4 * DM_KEYS * PF_ROW;     // Q tile + K, V double buffered
+
+__global__ void __launch_bounds__(DM_WARPS * 32)
+attn_decode_mma_kernel(const bf16* q, const bf16* gate_src, int gate_ld, const bf16* kcache, const bf16* vcache,
+                       const int* block_table, int max_blocks, const int* seq_ids, const int* positions,
+                       float* po, float* pm, float* pl, bf16* out, int T, int n_q, int n_kv, int n_splits,
+                       int tpg, float scale_log2e, int gated) {
+  extern __shared__ __align__(1024) unsigned char dm_smem[];
+  __shared__ float s_m[DM_WARPS][DM_ROWS], s_l[DM_WARPS][DM_ROWS];
+  pdl_launch_dependents(4);
+  pdl_wait();
+  const int split = blockIdx.x, kvh = blockIdx.y, t0 = blockIdx.z * tpg;
+  const int G = n_q / n_kv;
+  const int nt = min(tpg, T - t0);
+  const int rows = nt * G;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int kv_len = positions[t0 + nt - 1] + 1;            // the group's last token sees the most keys
+  const int* table = block_table + (size_t)seq_ids[t0] * max_blocks;
+  const int pages = (kv_len + KVB - 1) / KVB;
+  const int pps = (pages + n_splits - 1) / n_splits;
+  const int lo = split * pps * KVB, hi = min(kv_len, (split + 1) * pps * KVB);
+  const int n_tiles = hi > lo ? (hi - lo + DM_KEYS - 1) / DM_KEYS : 0;
+
+  unsigned char* qs = dm_smem;                               // [16][512 B]
+  unsigned char* ks = dm_smem + DM_ROWS * PF_ROW;            // [2][64][512 B]
+  unsigned char* vs = ks + 2 * DM_KEYS * PF_ROW;             // [2][64][512 B]
+  const uint32_t qs_a = (uint32_t)__cvta_generic_to_shared(qs);
+  const uint32_t ks_a = (uint32_t)__cvta_generic_to_shared(ks), vs_a = (uint32_t)__cvta_generic_to_shared(vs);
+
+  // row r of the tile = (token r / G of the group, head r % G of the kv head); unused rows are zero
+  for (int x = threadIdx.x; x < DM_ROWS * PF_CHUNKS; x += blockDim.x) {
+    const int r = x / PF_CHUNKS, c = x % PF_CHUNKS;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < rows) v = *reinterpret_cast<const uint4*>(q + ((size_t)(t0 + r / G) * n_q + kvh * G + r % G) * PF_D + c * 8);
+    *reinterpret_cast<uint4*>(qs + pf_off(r, c)) = v;
+  }
+  auto load_kv = [&](int kt, int buf) {
+    const int j0 = lo + kt * DM_KEYS;
+    for (int x = threadIdx.x; x < DM_KEYS * PF_CHUNKS; x += blockDim.x) {
+      const int r = x / PF_CHUNKS, c = x % PF_CHUNKS;      // a warp covers one 512-byte row
+      const int j = j0 + r;
+      const uint32_t dk = ks_a + buf * DM_KEYS * PF_ROW + pf_off(r, c);
+      const uint32_t dv = vs_a + buf * DM_KEYS * PF_ROW + pf_off(r, c);
+      if (j < hi) {
+        const size_t off = (((size_t)table[j / KVB] * n_kv + kvh) * KVB + (j % KVB)) * PF_D + c * 8;
+        cp16(dk, kcache + off);
+        cp16(dv, vcache + off);
+      } else {                      // past the range: zeros (masked below, but must not be NaN)
+        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(dk), "r"(0u) : "memory");
+        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(dv), "r"(0u) : "memory");
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  const int r_lo = lane >> 2;                      // fragment rows r_lo and r_lo + 8
+  const int pos_lo = r_lo < rows ? positions[t0 + r_lo / G] : -1;
+  const int pos_hi = r_lo + 8 < rows ? positions[t0 + (r_lo + 8) / G] : -1;
+  float o[PF_D / 8][4];
+#pragma unroll
+  for (int i = 0; i < PF_D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+
+  if (n_tiles > 0) load_kv(0, 0);
+  for (int kt = 0; kt < n_tiles; ++kt) {
+    const int buf = kt & 1;
+    if (kt + 1 < n_tiles) {
+      load_kv(kt + 1, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const int jw = lo + kt * DM_KEYS + warp * 16;     // this warp's first key of the tile
+    if (jw < hi) {
+      const uint32_t kb = ks_a + buf * DM_KEYS * PF_ROW, vb = vs_a + buf * DM_KEYS * PF_ROW;
+      // ---- S = Q K^T for this warp's 16 keys: two n-tiles of 8
+      float sc[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < PF_D / 16; ++kk) {
+        uint32_t a[4], b[4];
+        ldsm_x4(a, qs_a + pf_off((lane & 7) + ((lane >> 3) & 1) * 8, kk * 2 + (lane >> 4)));
+        ldsm_x4(b, kb + pf_off(warp * 16 + (lane & 7) + (lane >> 4) * 8, kk * 2 + ((lane >> 3) & 1)));
+        mma_bf16(sc[0], a, b[0], b[1]);
+        mma_bf16(sc[1], a, b[2], b[3]);
+      }
+      // ---- mask (causal per row, and the end of the split's range), scale, online softmax
+      float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+      for (int n8 = 0; n8 < 2; ++n8) {
+        const int j = jw + n8 * 8 + (lane & 3) * 2;
+        const bool in0 = j < hi, in1 = j + 1 < hi;
+        sc[n8][0] = (in0 && j <= pos_lo) ? sc[n8][0] * scale_log2e : -INFINITY;
+        sc[n8][1] = (in1 && j + 1 <= pos_lo) ? sc[n8][1] * scale_log2e : -INFINITY;
+        sc[n8][2] = (in0 && j <= pos_hi) ? sc[n8][2] * scale_log2e : -INFINITY;
+        sc[n8][3] = (in1 && j + 1 <= pos_hi) ? sc[n8][3] * scale_log2e : -INFINITY;
+        mx_lo = fmaxf(mx_lo, fmaxf(sc[n8][0], sc[n8][1]));
+        mx_hi = fmaxf(mx_hi, fmaxf(sc[n8][2], sc[n8][3]));
+      }
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+      const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+      const float base_lo = mn_lo == -INFINITY ? 0.f : mn_lo, base_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+      const float al_lo = exp2f(m_lo - base_lo), al_hi = exp2f(m_hi - base_hi);
+      m_lo = mn_lo, m_hi = mn_hi;
+      float sum_lo = 0.f, sum_hi = 0.f;
+      uint32_t pa[4];                                // P as the A operand of PV: one k-step of 16 keys
+#pragma unroll
+      for (int n8 = 0; n8 < 2; ++n8) {
+        const float p0 = exp2f(sc[n8][0] - base_lo), p1 = exp2f(sc[n8][1] - base_lo);
+        const float p2 = exp2f(sc[n8][2] - base_hi), p3 = exp2f(sc[n8][3] - base_hi);
+        sum_lo += p0 + p1, sum_hi += p2 + p3;
+        pa[n8 * 2] = f2_to_bf162_bits(p0, p1);
+        pa[n8 * 2 + 1] = f2_to_bf162_bits(p2, p3);
+      }
+      sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 1);
+      sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 2);
+      sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 1);
+      sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 2);
+      l_lo = l_lo * al_lo + sum_lo, l_hi = l_hi * al_hi + sum_hi;
+#pragma unroll
+      for (int i = 0; i < PF_D / 8; ++i) o[i][0] *= al_lo, o[i][1] *= al_lo, o[i][2] *= al_hi, o[i][3] *= al_hi;
+      // ---- O += P V
+#pragma unroll
+      for (int nd = 0; nd < PF_D / 8; nd += 2) {
+        uint32_t b[4];
+        ldsm_x4_t(b, vb + pf_off(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, nd + (lane >> 4)));
+        mma_bf16(o[nd], pa, b[0], b[1]);
+        mma_bf16(o[nd + 1], pa, b[2], b[3]);
+      }
+    }
+    __syncthreads();                               // the other buffer may be overwritten next round
+  }
+
+  // ---- merge the four warps (each saw different keys) through shared memory
+  float* so = reinterpret_cast<float*>(ks);        // [4 warps][16 rows][256] fp32 = the K buffers
+  if ((lane & 3) == 0) {
+    s_m[warp][r_lo] = m_lo, s_m[warp][r_lo + 8] = m_hi;
+    s_l[warp][r_lo] = l_lo, s_l[warp][r_lo + 8] = l_hi;
+  }
+#pragma unroll
+  for (int nd = 0; nd < PF_D / 8; ++nd) {
+    const int d = nd * 8 + (lane & 3) * 2;
+    *reinterpret_cast<float2*>(so + ((size_t)warp * DM_ROWS + r_lo) * PF_D + d) = make_float2(o[nd][0], o[nd][1]);
+    *reinterpret_cast<float2*>(so + ((size_t)warp * DM_ROWS + r_lo + 8) * PF_D + d) = make_float2(o[nd][2], o[nd][3]);
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < rows * PF_D; idx += blockDim.x) {
+    const int r = idx / PF_D, d = idx % PF_D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DM_WARPS; ++w) mm = fmaxf(mm, s_m[w][r]);
+    float ll = 0.f, a = 0.f;
+#pragma unroll
+    for (int w = 0; w < DM_WARPS; ++w) {
+      const float c = (s_m[w][r] == -INFINITY) ? 0.f : exp2f(s_m[w][r] - mm);
+      ll += s_l[w][r] * c;
+      a += so[((size_t)w * DM_ROWS + r) * PF_D + d] * c;
+    }
+    const int t = t0 + r / G, h = kvh * G + r % G;
+    if (n_splits == 1) {
+      float ov = ll > 0.f ? a / ll : 0.f;
+      if (gated) ov *= sigmoid_f(__bfloat162float(gate_src[(size_t)t * gate_ld + (size_t)h * 2 * PF_D + PF_D + d]));
+      out[((size_t)t * n_q + h) * PF_D + d] = __float2bfloat16(ov);
+    } else {
+      const size_t base = ((size_t)t * n_q + h) * n_splits + split;
+      po[base * PF_D + d] = a;
+      if (d == 0) pm[base] = mm, pl[base] = ll;
+    }
+  }
+}
+
 }  // namespace
 
 TRL_API int trl_attn_prep(const void* qkv, int ld, const void* q_norm, const void* k_norm,
@@ -569,6 +758,38 @@ TRL_API int trl_attn_paged(const void* q, const void* gate_src, int gate_ld, con
   else if (D == 64) SPLIT_CASE(2)
   else return (int)cudaErrorInvalidValue;
 #undef SPLIT_CASE
+  if (e != cudaSuccess) return (int)e;
+  if (n_splits > 1)
+    e = trl_launch(attn_combine_kernel, dim3(T, n_q), dim3(min(D, 256)), 0, st, (const float*)po,
+                   (const float*)pm, (const float*)pl, (const bf16*)gate_src, gate_ld, (bf16*)out, n_q,
+                   D, n_splits, gated);
+  return (int)e;
+}
+
+// Tensor-core variant of trl_attn_paged for the bf16 pool (D = 256): `tpg` consecutive tokens of the
+// batch that belong to one sequence (1 for decode; a divisor of the verify width) share a CTA, with
+// tpg * (n_q / n_kv) <= 16 rows.  Same scratch and combine as trl_attn_paged.
+TRL_API int trl_attn_decode_mma(const void* q, const void* gate_src, int gate_ld, const void* kcache,
+                                const void* vcache, const void* block_table, int max_blocks,
+                                const void* seq_ids, const void* positions, void* po, void* pm, void* pl,
+                                void* out, int T, int n_q, int n_kv, int D, int n_splits, int tpg, float scale,
+                                int gated, void* stream) {
+  if (D != PF_D || n_kv <= 0 || n_q <= 0 || n_q % n_kv != 0 || tpg < 1 || tpg * (n_q / n_kv) > DM_ROWS || T <= 0 ||
+      n_splits < 1)
+    return (int)cudaErrorInvalidValue;
+  cudaStream_t st = (cudaStream_t)stream;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DM_SMEM) != cudaSuccess)
+      return 3;
+    configured = true;
+  }
+  const dim3 grid(n_splits, n_kv, (T + tpg - 1) / tpg);
+  cudaError_t e = trl_launch(attn_decode_mma_kernel, grid, dim3(DM_WARPS * 32), (size_t)DM_SMEM, st, (const bf16*)q,
+                             (const bf16*)gate_src, gate_ld, (const bf16*)kcache, (const bf16*)vcache,
+                             (const int*)block_table, max_blocks, (const int*)seq_ids, (const int*)positions,
+                             (float*)po, (float*)pm, (float*)pl, (bf16*)out, T, n_q, n_kv, n_splits, tpg,
+                             scale * 1.4426950408889634f, gated);
   if (e != cudaSuccess) return (int)e;
   if (n_splits > 1)
     e = trl_launch(attn_combine_kernel, dim3(T, n_q), dim3(min(D, 256)), 0, st, (const float*)po,

@@ -29,6 +29,7 @@ int g_trl_use_pdl = 1;
 __device__ TrlTraceRec g_trl_trace[TRL_TRACE_CAP];
 __device__ unsigned int g_trl_trace_n = 0;
 __device__ unsigned int g_trl_trace_cur = 0;
+__device__ unsigned long long g_trl_last_exit = 0;
 #endif
 
 enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_STORE_F32 = 3, EPI_PUSH = 4 };
@@ -685,7 +686,8 @@ TRL_API int trl_gemv_nvfp4_push(const void* x, int ldx, const void* wq, const vo
 }
 
 // Timeline records of the launches since the last reset (builds with -DTRL_TRACE; otherwise
-// returns 0 records).  out: n x 4 uint64 {kind, entry, dependency wait done, exit} in ns.
+// returns 0 records).  out: n x 8 uint64 {kind, entry, dependency wait done, exit, mark 0, mark 1,
+// latest exit of any CTA of the launches before, unused} in ns.
 TRL_API int trl_trace_read(void* out, int cap, int reset) {
 #ifdef TRL_TRACE
   unsigned int n = 0;

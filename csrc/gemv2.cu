@@ -87,24 +87,23 @@ __device__ __forceinline__ uint16_t g2_lds16(uint32_t a) {
   return v;
 }
 
-// x (bf16 [M, K], optional RMSNorm) -> shared memory as f16 scaled by a per-row power of two
-// (16 products of |w| <= 6 then stay below the f16 maximum).  Piece p (8 halves) of 32-element
-// chunk c sits at ((p * nchunks + c) * 8) halves: the four 16-byte reads of a chunk are
-// conflict-free across lanes.  xs_inv[m] = 1 / applied scale.
-// One pass: a thread keeps its (up to XV) 8-element vectors of the row in registers between the
-// statistics and the scaled write.
+// x (bf16 [M, K], optional RMSNorm weight) -> shared memory as f16.  Piece p (8 halves) of
+// 32-element chunk c sits at ((p * nchunks + c) * 8) halves: the four 16-byte reads of a chunk are
+// conflict-free across lanes.  One pass: a thread holds up to XV 8-element vectors of the row.
 constexpr int G2_XV = 9;   // K <= 9 * 256 * 8 = 18432
+// The activation row is staged as f16 (x * norm weight * 2^-4, clamped to the f16 range): no
+// reduction sits between the dependency and the first product.  The row's 1 / rms is a scalar and
+// multiplies the finished dot product instead (g2_row_scale); its sum of squares is collected here.
+constexpr float G2_X_PRESCALE = 0.0625f;
 template <int M>
 __device__ __forceinline__ void g2_stage_x(const bf16* __restrict__ x, int ldx, int K,
-                                           const float* __restrict__ norm_w, float eps, __half* xs,
-                                           float* xs_inv, float* red) {
+                                           const float* __restrict__ norm_w, __half* xs, float* red) {
   const int nchunks = K >> 5, nvec = K >> 3;
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
 #pragma unroll
   for (int m = 0; m < M; ++m) {
     const bf16* xr = x + (size_t)m * ldx;
     uint4 xv[G2_XV];
-    float ss = 0.f, amax = 0.f;
 #pragma unroll
     for (int i = 0; i < G2_XV; ++i) {
       const int v = threadIdx.x + i * G2_THREADS;
@@ -113,42 +112,7 @@ __device__ __forceinline__ void g2_stage_x(const bf16* __restrict__ x, int ldx, 
       // CTAs of earlier kernels that read the previous contents of these rows
       if (v < nvec) xv[i] = __ldcg(reinterpret_cast<const uint4*>(xr + (size_t)v * 8));
     }
-#pragma unroll
-    for (int i = 0; i < G2_XV; ++i) {
-      const int v = threadIdx.x + i * G2_THREADS;
-      if (v < nvec) {
-        const uint32_t u4[4] = {xv[i].x, xv[i].y, xv[i].z, xv[i].w};
-        float nw[8];
-        if (norm_w != nullptr) {
-          const float4 a = *reinterpret_cast<const float4*>(norm_w + (size_t)v * 8);
-          const float4 b = *reinterpret_cast<const float4*>(norm_w + (size_t)v * 8 + 4);
-          nw[0] = a.x, nw[1] = a.y, nw[2] = a.z, nw[3] = a.w, nw[4] = b.x, nw[5] = b.y, nw[6] = b.z, nw[7] = b.w;
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float2 f = bf162_bits_to_f2(u4[j]);
-          ss += f.x * f.x + f.y * f.y;
-          if (norm_w != nullptr) f.x *= nw[2 * j], f.y *= nw[2 * j + 1];
-          amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
-        }
-      }
-    }
-    ss = warp_sum(ss);
-    amax = warp_max(amax);
-    __syncthreads();
-    if (lane == 0) red[w] = ss, red[32 + w] = amax;
-    __syncthreads();
-    ss = warp_sum(lane < G2_WARPS ? red[lane] : 0.f);
-    amax = warp_max(lane < G2_WARPS ? red[32 + lane] : 0.f);
-    float rstd = 1.f;
-    if (norm_w != nullptr) {
-      rstd = rsqrtf(ss / (float)K + eps);
-      amax *= rstd * 1.01f;   // bf16 rounding of the normalised values can add < 0.4 %
-    }
-    int e = 0;
-    if (amax > 0.f) frexpf(amax, &e);   // amax = f * 2^e, f in [0.5, 1)
-    const float sc = exp2f((float)(8 - e));
-    if (threadIdx.x == 0) xs_inv[m] = exp2f((float)(e - 8));
+    float ss = 0.f;
     __half* dst = xs + (size_t)m * K;
 #pragma unroll
     for (int i = 0; i < G2_XV; ++i) {
@@ -165,19 +129,29 @@ __device__ __forceinline__ void g2_stage_x(const bf16* __restrict__ x, int ldx, 
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           float2 f = bf162_bits_to_f2(u4[j]);
-          if (norm_w != nullptr) {
-            f.x = __bfloat162float(__float2bfloat16(f.x * rstd * nw[2 * j]));
-            f.y = __bfloat162float(__float2bfloat16(f.y * rstd * nw[2 * j + 1]));
-          }
-          const __half2 h = __floats2half2_rn(f.x * sc, f.y * sc);
+          ss += f.x * f.x + f.y * f.y;
+          if (norm_w != nullptr) f.x *= nw[2 * j], f.y *= nw[2 * j + 1];
+          f.x = fminf(fmaxf(f.x * G2_X_PRESCALE, -65504.f), 65504.f);
+          f.y = fminf(fmaxf(f.y * G2_X_PRESCALE, -65504.f), 65504.f);
+          const __half2 h = __floats2half2_rn(f.x, f.y);
           o[j] = *reinterpret_cast<const uint32_t*>(&h);
         }
         // vector v = piece (v & 3) of chunk (v >> 2)
         *reinterpret_cast<uint4*>(dst + ((size_t)((v & 3) * nchunks + (v >> 2)) << 3)) = make_uint4(o[0], o[1], o[2], o[3]);
       }
     }
+    ss = warp_sum(ss);
+    if (lane == 0) red[m * G2_WARPS + w] = ss;     // summed by g2_row_scale after the main loop
   }
   __syncthreads();
+}
+
+// 1 / rms of activation row m (1 without a norm) times the inverse of the staging prescale.
+__device__ __forceinline__ float g2_row_scale(const float* red, int m, int K, bool norm, float eps) {
+  float ss = 0.f;
+#pragma unroll
+  for (int w = 0; w < G2_WARPS; ++w) ss += red[m * G2_WARPS + w];
+  return (norm ? rsqrtf(ss / (float)K + eps) : 1.f) * (1.f / G2_X_PRESCALE);
 }
 
 // Finish of the one-shot all-reduce inside the consumer (see the header).  Returns false when a
@@ -260,7 +234,7 @@ gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ ws
              int nslot, int NS, const TrlPushArgs push) {
   constexpr int W = G2_WARPS;
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  // ring [W][NS][STAGE_BYTES] | bars [W][NS] | xs [M][K] f16 | xs_inv[8] | red[64] | slots
+  // ring [W][NS][STAGE_BYTES] | bars [W][NS] | xs [M][K] f16 | 8 spare floats | red[64] | slots
   unsigned char* ring = smem_raw;
   uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)W * NS * STAGE_BYTES);
   __half* xs = reinterpret_cast<__half*>(reinterpret_cast<unsigned char*>(bars) + W * G2_MAX_NS * 8);
@@ -311,10 +285,17 @@ gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ ws
   for (int i = threadIdx.x; i < pl * 2 * nslot * M; i += G2_THREADS) slots[i] = 0.f;
   pdl_launch_dependents(100 + EPI * 2 + (COOP ? 1 : 0));
   pdl_wait();
+  // epilogue operands that do not depend on this kernel's own work: requested now, used at the end
+  float res0 = 0.f;
+  uint32_t push_epoch = 0;
+  if (EPI == EPI2_RESIDUAL && (int)threadIdx.x < pl * 2 * M)
+    res0 = __bfloat162float(__ldcg(residual + (size_t)(threadIdx.x % M) * ldr + p_lo * 2 + threadIdx.x / M));
+  if (EPI == EPI2_PUSH) push_epoch = __ldcg(reinterpret_cast<const uint32_t*>(push.ws[push.rank])) + 1;
   if (COOP)   // x is the residual stream: complete the pending all-reduce into it first
     g2_coop_finish(const_cast<bf16*>(x), ldx, M, K, push.ws[push.rank], push.world, push.hmax,
                    reinterpret_cast<int*>(red));
-  g2_stage_x<M>(x, ldx, K, norm_w, eps, xs, xs_inv, red);   // ends with a block barrier
+  g2_stage_x<M>(x, ldx, K, norm_w, xs, red);   // ends with a block barrier
+  trl_trace_mark(0);
 
   bool ok = true;
   const uint32_t xs_a = smem_addr(xs) + (uint32_t)lane * 16u;
@@ -478,10 +459,14 @@ gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ ws
       }
     }
   }
+  trl_trace_mark(1);
   __syncthreads();
 
   // block-wide epilogue over this CTA's rows
   const float ts = *tscale;
+  float rsc[M];
+#pragma unroll
+  for (int m = 0; m < M; ++m) rsc[m] = ts * g2_row_scale(red, m, K, norm_w != nullptr, eps);
   if (EPI == EPI2_SWIGLU) {
     for (int i = threadIdx.x; i < pl * M; i += G2_THREADS) {
       const int pr = i / M, m = i % M;
@@ -490,7 +475,7 @@ gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ ws
         g += slots[((size_t)(pr * 2) * nslot + sl) * M + m];
         u += slots[((size_t)(pr * 2 + 1) * nslot + sl) * M + m];
       }
-      const float sc = ts * xs_inv[m];
+      const float sc = rsc[m];
       const int n = (p_lo + pr) * 2;
       reinterpret_cast<bf16*>(yout)[(size_t)m * ldy + (n >> 1)] = __float2bfloat16(silu_f(g * sc) * (u * sc));
     }
@@ -500,14 +485,14 @@ gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ ws
       const int n = p_lo * 2 + rl;
       float v = 0.f;
       for (int sl = 0; sl < nslot; ++sl) v += slots[((size_t)rl * nslot + sl) * M + m];
-      v *= ts * xs_inv[m];
+      v *= rsc[m];
       if (EPI == EPI2_PUSH) {
-        const uint32_t epoch = *reinterpret_cast<const uint32_t*>(push.ws[push.rank]) + 1;
+        const uint32_t epoch = push_epoch;
         const size_t off = 65536 + ((size_t)(((epoch & 1) * 8 + push.rank) * 8 + push.row0 + m) * push.hmax + n) * 8;
         const uint2 word = make_uint2(__float_as_uint(v), epoch);
         for (int p = 0; p < push.world; ++p) st_relaxed_sys_v2(push.ws[p] + off, word);
       } else {
-        if (EPI == EPI2_RESIDUAL) v += __bfloat162float(__ldcg(residual + (size_t)m * ldr + n));
+        if (EPI == EPI2_RESIDUAL) v += i < G2_THREADS ? res0 : __bfloat162float(__ldcg(residual + (size_t)m * ldr + n));
         if (EPI == EPI2_STORE_F32)
           reinterpret_cast<float*>(yout)[(size_t)m * ldy + n] = v;
         else

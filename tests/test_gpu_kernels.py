@@ -582,3 +582,53 @@ def test_gdn_chunk_parallel_scan_matches_serial_scan_and_oracle(d, nk, nv):
         ops.lib.trl_gdn_set_wy(0)      # the default path
     from tilerl_b200.ops import native
     assert native.read_error()[0] == 0
+
+
+@pytest.mark.parametrize("w,hist", [(1, (0, 15, 16, 63, 64, 65, 1000)), (8, (0, 9, 250)), (2, (5, 77)), (3, (31, 100))])
+@pytest.mark.parametrize("n_q,n_kv", [(24, 4), (8, 2)])
+def test_tensor_core_decode_attention_matches_scalar_kernel_and_oracle(w, hist, n_q, n_kv):
+    """The mma split-KV kernel (kv-group x window rows as one tile) on decode rows and verify
+    windows: contexts that end inside a page, inside a 64-key tile and across many tiles, every
+    split count, against the scalar split kernel and the fp32 oracle; run twice for determinism."""
+    import dataclasses
+    from tilerl_b200.batch import Batch
+    from tilerl_b200.config import small_gpu
+    from tilerl_b200.factory import make_ops
+    from tilerl_b200.kv import PagedKvPool
+    from tilerl_b200.ops.backend import RefOps
+    cfg = dataclasses.replace(small_gpu(), n_q_heads=n_q, n_kv_heads=n_kv)
+    ops = make_ops("cuda")
+    assert ops.attn_mma
+    d = cfg.head_dim
+    rows = n_q * 2 * d + 2 * n_kv * d
+    lp = {"q_norm": torch.ones(d, device="cuda"), "k_norm": torch.ones(d, device="cuda")}
+    outs = {}
+    for mode in ("mma1", "mma4", "mma7", "mma_auto", "mma_auto2", "scalar", "ref"):
+        pool = PagedKvPool(cfg, 96, "cuda", dtype=torch.bfloat16 if mode != "ref" else torch.float32)
+        o = RefOps() if mode == "ref" else ops
+        ops.attn_mma = mode.startswith("mma")
+        ops.attn_splits = {"mma1": 1, "mma4": 4, "mma7": 7}.get(mode, 0)
+        blk = 1
+        seqs_hist, seqs_now = [], []
+        for i, h in enumerate(hist):
+            nb = (w + h + 15) // 16
+            blocks = list(range(blk, blk + nb))
+            blk += nb
+            if h:
+                seqs_hist.append(dict(tokens=[0] * h, start=0, blocks=blocks, slot=i + 1))
+            seqs_now.append(dict(tokens=[0] * w, start=h, blocks=blocks, slot=i + 1))
+        gg = torch.Generator().manual_seed(13)
+        for seqs in ([seqs_hist] if seqs_hist else []) + [seqs_now]:
+            batch = Batch.build(seqs, "cuda")
+            t = sum(len(s_["tokens"]) for s_ in seqs)
+            qkv = (torch.randn(t, rows, generator=gg) * 0.5).cuda().to(torch.bfloat16)
+            res = o.attention(qkv, lp, batch, pool, 0, cfg, n_q, n_kv)
+        outs[mode] = res.float().clone()
+    ops.attn_mma, ops.attn_splits = True, 0
+    ref_o = outs["ref"]
+    for mode in ("mma1", "mma4", "mma7", "scalar"):
+        err = float((outs[mode] - ref_o).abs().max())
+        assert err < 0.03 * float(ref_o.abs().max()) + 0.02, (mode, err)
+    assert torch.equal(outs["mma_auto"], outs["mma_auto2"])
+    for mode in ("mma1", "mma4", "mma7", "mma_auto"):
+        assert float((outs[mode] - outs["scalar"]).abs().max()) < 0.03, mode

@@ -83,6 +83,7 @@ class CudaOps:
         self.terms_small = int(os.environ.get("TRL_TERMS_SMALL", terms_small))
         self.terms_large = int(os.environ.get("TRL_TERMS_LARGE", terms_large))
         self.act_dtype = torch.bfloat16
+        self.attn_mma = os.environ.get("TRL_ATTN_MMA", "1") != "0" and hasattr(self.lib, "trl_attn_decode_mma")
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.vocab = None   # set by the engine builder: real vocabulary size (TP pads it)
         if comm is not None:
@@ -281,15 +282,26 @@ class CudaOps:
             return out
         if sparse_now:
             table, pos = sp.packed(attn_idx, q, kc)    # same kernel on [selected pages ; trailing window]
-        splits = self.attn_splits or self._pick_splits(batch, t, n_kv)
+        mma = self.attn_mma and d == 256 and n_q % n_kv == 0 and n_q // n_kv <= 16
+        tpg = self._tokens_per_group(batch, t, n_q // n_kv) if mma else 1
+        splits = self.attn_splits or self._pick_splits(batch, t // tpg if mma else t, n_kv, 64 if mma else 32)
         po = self.ws.get("attn_po", (t * n_q * splits * d,), torch.float32)
         pm = self.ws.get("attn_pm", (t * n_q * splits,), torch.float32)
         pl = self.ws.get("attn_pl", (t * n_q * splits,), torch.float32)
-        N.check(self.lib.trl_attn_paged(
-            q.data_ptr(), qkv.data_ptr(), qkv.stride(0), kc.data_ptr(), vc.data_ptr(),
-            table.data_ptr(), table.stride(0), batch.seq_ids.data_ptr(),
-            pos.data_ptr(), po.data_ptr(), pm.data_ptr(), pl.data_ptr(), out.data_ptr(),
-            t, n_q, n_kv, d, splits, 1.0 / math.sqrt(d), int(cfg.attn_gated), st), "attn_paged")
+        if mma:
+            # decode / verify rows: the heads of a kv group (times the rows of a verify window) are one
+            # tensor-core tile, K / V rows are read once per group
+            N.check(self.lib.trl_attn_decode_mma(
+                q.data_ptr(), qkv.data_ptr(), qkv.stride(0), kc.data_ptr(), vc.data_ptr(),
+                table.data_ptr(), table.stride(0), batch.seq_ids.data_ptr(),
+                pos.data_ptr(), po.data_ptr(), pm.data_ptr(), pl.data_ptr(), out.data_ptr(),
+                t, n_q, n_kv, d, splits, tpg, 1.0 / math.sqrt(d), int(cfg.attn_gated), st), "attn_decode_mma")
+        else:
+            N.check(self.lib.trl_attn_paged(
+                q.data_ptr(), qkv.data_ptr(), qkv.stride(0), kc.data_ptr(), vc.data_ptr(),
+                table.data_ptr(), table.stride(0), batch.seq_ids.data_ptr(),
+                pos.data_ptr(), po.data_ptr(), pm.data_ptr(), pl.data_ptr(), out.data_ptr(),
+                t, n_q, n_kv, d, splits, 1.0 / math.sqrt(d), int(cfg.attn_gated), st), "attn_paged")
         N.count(2 + (1 if splits > 1 else 0))
         return out
 
@@ -331,15 +343,28 @@ class CudaOps:
         N.count(2 + (1 if splits > 1 else 0))
         return out
 
-    def _pick_splits(self, batch, t: int, n_kv: int) -> int:
-        """Enough CTAs to fill the GPU when few tokens attend to long contexts."""
+    def _pick_splits(self, batch, t: int, n_kv: int, keys: int = 32) -> int:
+        """Enough CTAs to fill the GPU when few tokens attend to long contexts; a split covers at
+        least ``keys`` keys (scalar kernel: 32 = four keys per warp; tensor-core kernel: one 64-key
+        tile)."""
         if t * n_kv >= self.sms:
             return 1
         longest = max(batch.host_kv_len) if batch.host_kv_len else 1
         want = max(1, self.sms // max(1, t * n_kv))
-        # a warp walks its keys one after the other: 32 keys (two pages) per split keep that walk at
-        # four keys per warp
-        return max(1, min(want, 32, (longest + 31) // 32))
+        return max(1, min(want, 32, (longest + keys - 1) // keys))
+
+    @staticmethod
+    def _tokens_per_group(batch, t: int, g: int) -> int:
+        """Rows of one sequence that may share a tile of the tensor-core decode kernel: a divisor of the
+        (uniform) rows per sequence with ``rows * g <= 16``; 1 when the batch is ragged."""
+        w = batch.max_q_len
+        if w <= 1 or t != batch.n_seqs * w:
+            return 1
+        best = 1
+        for c in range(1, w + 1):
+            if w % c == 0 and c * g <= 16:
+                best = c
+        return best
 
     def gdn(self, inp, lp, batch, spool, gdn_idx, cfg, nk, nv):
         t = inp.shape[0]

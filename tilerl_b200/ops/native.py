@@ -52,6 +52,7 @@ _SIGS = {
     "trl_gemm_trace_read": [P, I],
     "trl_gdn_set_wy": [I],
     "trl_sample_nucleus": [P, I, P, P, P, P, P, P, P, I, I, P],
+    "trl_attn_decode_mma": [P, P, I, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P],
     "trl_attn_prep_fp8": [P, I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P],
     "trl_attn_paged_fp8": [P, P, I, P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, F, I, P],
     "trl_attn_prefill_fp8": [P, P, I, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, F, I, P],

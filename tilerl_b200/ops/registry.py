@@ -117,8 +117,10 @@ register("any", "sm100", {
     "swiglu": Kernel("swiglu_kernel", "csrc/misc.cu", "trl_swiglu"),
     "add": Kernel("add_kernel", "csrc/misc.cu", "trl_add"),
     "attn_prep": Kernel("attn_prep_kernel", "csrc/attn.cu", "trl_attn_prep"),
-    "paged_attention_decode": Kernel("attn_split_kernel + attn_combine_kernel", "csrc/attn.cu", "trl_attn_paged",
-                                     note="decode, verify width W, short chunks"),
+    "paged_attention_decode": Kernel("attn_decode_mma_kernel + attn_combine_kernel", "csrc/attn.cu", "trl_attn_decode_mma",
+                                     note="decode, verify width W, short chunks: kv-group x window rows as one mma tile"),
+    "paged_attention_decode_scalar": Kernel("attn_split_kernel + attn_combine_kernel", "csrc/attn.cu", "trl_attn_paged",
+                                            note="head dims other than 256; TRL_ATTN_MMA=0"),
     "paged_attention_prefill": Kernel("attn_prefill_kernel<false>", "csrc/attn.cu", "trl_attn_prefill"),
     "gdn": Kernel("gdn_prep_kernel + gdn_scan_kernel / gdn_scan_wy_kernel / gdn_recur_kernel", "csrc/gdn.cu", "trl_gdn"),
     "argmax": Kernel("argmax_stage1_kernel + argmax_stage2_kernel", "csrc/misc.cu", "trl_argmax"),

@@ -1,6 +1,10 @@
 """Collective micro-benchmarks across the GPUs of one box (torchrun, one rank per GPU):
 
-* the row-parallel projection + all-reduce of a decode tick: NCCL (GEMV kernel then
+* the decode tick's pair "row-parallel down projection pushes its partial rows, the gate_up
+  projection that follows sums them inside its own launch", against the same two kernels with no
+  communication and against NCCL, with the fraction of the roofline (weight stream at the measured
+  HBM read rate, or the pushed words at the measured peer-copy rate, whichever is slower);
+* the row-parallel projection + all-reduce alone: NCCL (GEMV kernel then
   ``dist.all_reduce`` then residual add) against the fused path (GEMV whose epilogue pushes fp32
   partials into every peer's slot + ``allreduce_finish``), for the down projection of the 27B
   sharded ``world`` ways;
@@ -107,6 +111,42 @@ def main():
         out["decode_down_proj"]["fused_us"] - out["decode_down_proj"]["gemv_only_us"], 2)
     out["decode_down_proj"]["allreduce_cost_nccl_us"] = round(
         out["decode_down_proj"]["nccl_us"] - out["decode_down_proj"]["gemv_only_us"], 2)
+
+    # ---- decode: the tick's pattern = row-parallel projection pushes, the next (column-parallel)
+    # projection completes the all-reduce inside its own launch, norm folded in -------------------
+    from tilerl_b200.ops.cuda import EPI_SWIGLU
+    n_up = 2 * 17408 // world
+    w_up = NVFP4Tensor(torch.randint(0, 255, (n_up, h // 2), dtype=torch.uint8, device=dev),
+                       (torch.rand(n_up, h // 16, device=dev) + 0.5).to(torch.float8_e4m3fn), torch.ones(1, device=dev))
+    nw = torch.ones(h, device=dev)
+    act = torch.zeros(1, n_up // 2, dtype=torch.bfloat16, device=dev)
+
+    def pair_fused():
+        comm.linear_allreduce_residual(ops, a, w, res)
+        ops._linear(res, w_up, act, norm_w=nw, eps=1e-6, epi=EPI_SWIGLU)
+
+    def pair_local():      # same two projections without any communication (the floor of the pair)
+        ops._gemv(a, w, y, residual=res, epi=1)
+        ops._linear(y, w_up, act, norm_w=nw, eps=1e-6, epi=EPI_SWIGLU)
+
+    def pair_nccl():
+        ops._gemv(a, w, y)
+        dist.all_reduce(y)
+        res.add_(y)
+        ops._linear(res, w_up, act, norm_w=nw, eps=1e-6, epi=EPI_SWIGLU)
+
+    from tilerl_b200.ops.gemm_tc import w_stream
+    w_stream(w), w_stream(w_up)
+    wbytes = (h * k + n_up * h) * 9 // 16            # e2m1 + e4m3 scale per 16
+    link_bytes = h * 8 * (world - 1)                  # {fp32, epoch} words this rank sends, per direction
+    hbm_us = wbytes / 6.85e6                          # weight stream at the measured read rate (6.85 TB/s)
+    link_us = link_bytes / (NVLINK_PEER_GBS * 1e3)
+    fused_us = _time(pair_fused, 50, True)
+    comm.settle()
+    out["decode_pair_down_then_gate_up"] = dict(
+        fused_us=round(fused_us, 2), local_no_comm_us=round(_time(pair_local, 50, True), 2),
+        nccl_us=round(_time(pair_nccl, 50, False), 2), weight_bytes=wbytes, link_bytes_per_direction=link_bytes,
+        roofline_us=round(max(hbm_us, link_us), 2), roofline_fraction=round(max(hbm_us, link_us) / fused_us, 3))
 
     # ---- prefill-sized all-reduce ----------------------------------------------------------------
     rows = []

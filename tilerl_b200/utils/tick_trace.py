@@ -53,7 +53,7 @@ def main():
     prompt = torch.randint(0, cfg.vocab, (args.ctx,), generator=g).tolist()
     eng.generate([prompt], SamplingParams(max_tokens=4, ignore_eos=True))      # captures the graph
     torch.cuda.synchronize()
-    buf = np.zeros((8192, 4), dtype=np.uint64)
+    buf = np.zeros((8192, 8), dtype=np.uint64)
     native.lib().trl_trace_read(buf.ctypes.data, 8192, 1)                       # reset
     eng.generate([prompt], SamplingParams(max_tokens=args.ticks + 1, ignore_eos=True))
     torch.cuda.synchronize()
@@ -70,6 +70,7 @@ def main():
     dep = tick[:, 2]
     share = collections.OrderedDict()
     early = collections.OrderedDict()
+    phases = collections.OrderedDict()
     for i in range(len(tick) - 1):
         name = KINDS.get(int(tick[i, 0]), f"kind {int(tick[i, 0])}")
         d = share.setdefault(name, [0, 0.0])
@@ -77,13 +78,25 @@ def main():
         d[1] += (dep[i + 1] - dep[i]) / 1e3
         e = early.setdefault(name, 0.0)
         early[name] = e + (dep[i] - tick[i, 1]) / 1e3
+        # phases of CTA 0 after its wait (kernels that mark them), and what follows its exit
+        if tick[i, 4] and tick[i, 5] and tick[i, 3]:
+            ph = phases.setdefault(name, [0, 0.0, 0.0, 0.0, 0.0, 0.0])
+            ph[0] += 1
+            ph[1] += (tick[i, 4] - dep[i]) / 1e3          # dependency resolved -> activation staged
+            ph[2] += (tick[i, 5] - tick[i, 4]) / 1e3      # main loop of CTA 0's first warp
+            ph[3] += (tick[i, 3] - tick[i, 5]) / 1e3      # epilogue of CTA 0
+            if tick[i + 1, 6]:
+                ph[4] += (int(tick[i + 1, 6]) - int(tick[i, 3])) / 1e3    # last CTA's exit after CTA 0's
+                ph[5] += (int(dep[i + 1]) - int(tick[i + 1, 6])) / 1e3    # last exit -> next launch released
     total = (dep[-1] - dep[0]) / 1e3
     out = {"tick_us": round(total, 1), "launches": len(tick) - 1,
            "critical_path_us": {k: {"n": v[0], "sum": round(v[1], 1), "avg": round(v[1] / v[0], 2),
                                     "resident_before_dep_avg": round(early[k] / v[0], 2)}
                                 for k, v in sorted(share.items(), key=lambda kv: -kv[1][1])}}
+    out["phases_us_avg"] = {k: dict(zip(("staged", "main_loop", "epilogue", "last_cta_after_cta0", "release_after_last_exit"),
+                                        [round(x / v[0], 2) for x in v[1:]])) for k, v in phases.items()}
     if rank == 0:
-        print(json.dumps(out, indent=1))
+        print(json.dumps(out))
         print("tick_trace done")
     if world > 1:
         import torch.distributed as dist
