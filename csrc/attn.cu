@@ -557,7 +557,8 @@ attn_decode_mma_kernel(const bf16* q, const bf16* gate_src, int gate_ld, const b
   const int nt = min(tpg, T - t0);
   const int rows = nt * G;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int kv_len = positions[t0 + nt - 1] + 1;            // the group's last token sees the most keys
+  int kv_len = 0;                                           // keys the group's furthest row sees (rows of a
+  for (int i = 0; i < nt; ++i) kv_len = max(kv_len, positions[t0 + i] + 1);   // padded window need not ascend)
   const int* table = block_table + (size_t)seq_ids[t0] * max_blocks;
   const int pages = (kv_len + KVB - 1) / KVB;
   const int pps = (pages + n_splits - 1) / n_splits;

@@ -52,12 +52,12 @@ struct TrlPushArgs {
 
 // ---- tick timeline (builds with -DTRL_TRACE only) ----------------------------------------------
 // Per launch: {kind, entry of CTA 0, end of its dependency wait, its exit, two phase marks of CTA 0
-// (trl_trace_mark), the latest exit of any CTA of the launches before it, unused} in
+// (trl_trace_mark), the latest exit of any CTA of the launches before it, unused, eight more marks} in
 // nanoseconds of %globaltimer, recorded from pdl_launch_dependents(kind) / pdl_wait() /
 // trl_trace_end(); trl_trace_read copies the records out.  Without the flag nothing is compiled in.
 #ifdef TRL_TRACE
 constexpr int TRL_TRACE_CAP = 8192;
-struct TrlTraceRec { unsigned long long kind, t_entry, t_dep, t_exit, t_mark[2], t_prev_last_exit, pad; };
+struct TrlTraceRec { unsigned long long kind, t_entry, t_dep, t_exit, t_mark[2], t_prev_last_exit, pad, t_more[8]; };
 extern __device__ unsigned long long g_trl_last_exit;
 extern __device__ TrlTraceRec g_trl_trace[TRL_TRACE_CAP];
 extern __device__ unsigned int g_trl_trace_n;
@@ -81,6 +81,7 @@ __device__ __forceinline__ void trl_trace_begin(int kind) {
       g_trl_trace[i].kind = (unsigned long long)kind, g_trl_trace[i].t_entry = trl_now();
       g_trl_trace[i].t_dep = 0, g_trl_trace[i].t_exit = 0;
       g_trl_trace[i].t_mark[0] = 0, g_trl_trace[i].t_mark[1] = 0, g_trl_trace[i].t_prev_last_exit = 0;
+      for (int k = 0; k < 8; ++k) g_trl_trace[i].t_more[k] = 0;
     }
   }
 }
@@ -92,7 +93,10 @@ __device__ __forceinline__ void trl_trace_dep() {
   }
 }
 __device__ __forceinline__ void trl_trace_mark(int which) {
-  if (trl_trace_lead() && trl_trace_slot() < TRL_TRACE_CAP) g_trl_trace[trl_trace_slot()].t_mark[which] = trl_now();
+  if (trl_trace_lead() && trl_trace_slot() < TRL_TRACE_CAP) {
+    if (which < 2) g_trl_trace[trl_trace_slot()].t_mark[which] = trl_now();
+    else if (which < 10) g_trl_trace[trl_trace_slot()].t_more[which - 2] = trl_now();
+  }
 }
 __device__ __forceinline__ void trl_trace_end() {
   if (threadIdx.x == 0 && threadIdx.y == 0) atomicMax(&g_trl_last_exit, trl_now());

@@ -686,8 +686,8 @@ TRL_API int trl_gemv_nvfp4_push(const void* x, int ldx, const void* wq, const vo
 }
 
 // Timeline records of the launches since the last reset (builds with -DTRL_TRACE; otherwise
-// returns 0 records).  out: n x 8 uint64 {kind, entry, dependency wait done, exit, mark 0, mark 1,
-// latest exit of any CTA of the launches before, unused} in ns.
+// returns 0 records).  out: n x 16 uint64 {kind, entry, dependency wait done, exit, mark 0, mark 1,
+// latest exit of any CTA of the launches before, unused, marks 2..9} in ns.
 TRL_API int trl_trace_read(void* out, int cap, int reset) {
 #ifdef TRL_TRACE
   unsigned int n = 0;

@@ -42,6 +42,18 @@
 
 enum { EPI2_STORE = 0, EPI2_RESIDUAL = 1, EPI2_SWIGLU = 2, EPI2_STORE_F32 = 3, EPI2_PUSH = 4 };
 
+// One projection of a chained launch (trl_gemv2_chain), as the host passes it.
+struct TrlChainOp {
+  const void* x;          // [M, K] bf16 activation rows (for coop = 1: the residual stream, updated in place)
+  const void* wst;        // stream layout of the [N, K] NVFP4 weight
+  const void* tscale;
+  const void* norm_w;     // fp32 [K] or null
+  const void* residual;   // EPI2_RESIDUAL: [M, N] bf16
+  void* out;
+  int ldx, ldr, ldy, N, K, epi, coop;
+  float eps;
+};
+
 namespace {
 
 constexpr int G2_THREADS = 256;
@@ -129,12 +141,12 @@ __device__ __forceinline__ void g2_stage_x(const bf16* __restrict__ x, int ldx, 
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           float2 f = bf162_bits_to_f2(u4[j]);
-          ss += f.x * f.x + f.y * f.y;
-          if (norm_w != nullptr) f.x *= nw[2 * j], f.y *= nw[2 * j + 1];
-          f.x = fminf(fmaxf(f.x * G2_X_PRESCALE, -65504.f), 65504.f);
-          f.y = fminf(fmaxf(f.y * G2_X_PRESCALE, -65504.f), 65504.f);
-          const __half2 h = __floats2half2_rn(f.x, f.y);
-          o[j] = *reinterpret_cast<const uint32_t*>(&h);
+          if (norm_w != nullptr) {
+            ss += f.x * f.x + f.y * f.y;
+            f.x *= nw[2 * j], f.y *= nw[2 * j + 1];
+          }
+          // saturating conversion: values beyond the f16 range become +-65504, never inf
+          asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(o[j]) : "f"(f.y * G2_X_PRESCALE), "f"(f.x * G2_X_PRESCALE));
         }
         // vector v = piece (v & 3) of chunk (v >> 2)
         *reinterpret_cast<uint4*>(dst + ((size_t)((v & 3) * nchunks + (v >> 2)) << 3)) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -158,7 +170,7 @@ __device__ __forceinline__ float g2_row_scale(const float* red, int m, int K, bo
 // bounded wait ran out (the error word is set; the caller still runs to completion on whatever
 // the row holds, so no barrier of the CTA is skipped).
 constexpr size_t G2_OFF_SLOTS = 65536;     // comm.cu: one-shot slots {fp32, epoch} [2][8 src][8 rows][hmax]
-constexpr int G2_CTRL_EPOCH = 0, G2_CTRL_ARRIVE = 17, G2_CTRL_RELEASE = 20;
+constexpr int G2_CTRL_EPOCH = 0, G2_CTRL_ARRIVE = 17, G2_CTRL_RELEASE = 64;   // the polled word has a 128-byte line of its own
 __device__ __forceinline__ bool g2_coop_finish(bf16* __restrict__ x, int ldx, int M, int N, unsigned char* ws,
                                                int world, int hmax, int* s_flag) {
   uint32_t* ctrl = reinterpret_cast<uint32_t*>(ws);
@@ -209,6 +221,7 @@ __device__ __forceinline__ bool g2_coop_finish(bf16* __restrict__ x, int ldx, in
       for (uint32_t it = 0;; ++it) {
         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(ctrl + G2_CTRL_RELEASE) : "memory");
         if (seen == epoch) break;
+        __nanosleep(32);
         if ((it & 15) == 15 && clock64() - t0 > G2_WAIT_CYCLES) {
           trl_set_error(TRL_ERR_WAIT_TIMEOUT, 6, (int)blockIdx.x, (int)epoch);
           s_flag[1] = 0;
@@ -283,6 +296,14 @@ gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ ws
     for (int s = 0; s < NS && p_unit < u1; ++s) issue();
   }
   for (int i = threadIdx.x; i < pl * 2 * nslot * M; i += G2_THREADS) slots[i] = 0.f;
+  // the norm weights are a constant parameter: bring this thread's lines into L1 while waiting
+  if (norm_w != nullptr) {
+#pragma unroll
+    for (int i = 0; i < G2_XV; ++i) {
+      const int v = threadIdx.x + i * G2_THREADS;
+      if (v < (K >> 3)) asm volatile("prefetch.global.L1 [%0];" ::"l"(norm_w + (size_t)v * 8));
+    }
+  }
   pdl_launch_dependents(100 + EPI * 2 + (COOP ? 1 : 0));
   pdl_wait();
   // epilogue operands that do not depend on this kernel's own work: requested now, used at the end
@@ -523,6 +544,366 @@ gemv_stream_pack_kernel(const uint8_t* __restrict__ wq, const uint8_t* __restric
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// Chain of up to four projections in ONE launch.  Consecutive decode projections depend on each
+// other through a full activation row, so between two of them every CTA must have stored its
+// rows: here that is a grid barrier (arrival counter + release generation, bounded waits)
+// instead of a kernel boundary.  What the chain buys is the weight stream: a warp's producer
+// simply continues with its share of the NEXT projection when the current one is exhausted, so
+// the rings refill across the barrier and the activation staging, where separate launches can
+// only prefetch once their CTAs have found room on an SM.  Ops: plain / residual / SwiGLU / fp32
+// store, tensor-parallel push, and the cooperative all-reduce finish in front of an op.
+struct G2Op {
+  const bf16* x;
+  const uint8_t* wst;
+  const float* tscale;
+  const float* norm_w;
+  const bf16* residual;
+  void* out;
+  int ldx, ldr, ldy, N, K, nslot, epi, coop;
+  float eps;
+};
+constexpr int G2_CHAIN_MAX = 4;
+struct G2Chain {
+  G2Op op[G2_CHAIN_MAX];
+  int n_ops;
+  int xs_bytes;          // bytes reserved for the staged activation rows (max over the ops)
+  uint32_t* bar;         // [0] arrival counter, [32] release generation (separate 128-byte lines)
+};
+constexpr int G2_BAR_RELEASE = 32;
+
+struct G2Range {
+  int p_lo, pl, nchunks, nsteps, nlast, U, u0, u1;
+  uint32_t pair_bytes;
+};
+__device__ __forceinline__ G2Range g2_range(const G2Op& o, int warp) {
+  G2Range r;
+  const int npairs = o.N >> 1;
+  r.p_lo = (int)(((long long)blockIdx.x * npairs) / gridDim.x);
+  r.pl = (int)(((long long)(blockIdx.x + 1) * npairs) / gridDim.x) - r.p_lo;
+  r.nchunks = o.K >> 5;
+  r.nsteps = (r.nchunks + 31) >> 5;
+  r.nlast = r.nchunks - 32 * (r.nsteps - 1);
+  r.pair_bytes = (uint32_t)r.nchunks * 36u;
+  r.U = r.pl * r.nsteps;
+  r.u0 = (int)(((long long)warp * r.U) / G2_WARPS);
+  r.u1 = (int)(((long long)(warp + 1) * r.U) / G2_WARPS);
+  return r;
+}
+
+// Grid barrier of the chain: generation `target` is released by the last CTA to arrive.
+__device__ __forceinline__ bool g2_grid_barrier(uint32_t* bar, uint32_t target, int* s_flag) {
+  __syncthreads();                       // this CTA's stores of the finished op are issued
+  if (threadIdx.x == 0) {
+    s_flag[2] = 1;
+    __threadfence();
+    const uint32_t prev = atomicAdd(bar, 1u);
+    if (prev == gridDim.x - 1) {
+      bar[0] = 0;
+      __threadfence();
+      asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(bar + G2_BAR_RELEASE), "r"(target) : "memory");
+    } else {
+      uint32_t seen;
+      const long long t0 = clock64();
+      for (uint32_t it = 0;; ++it) {
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(bar + G2_BAR_RELEASE) : "memory");
+        if (seen == target) break;
+        __nanosleep(32);                  // hundreds of CTAs poll one word: leave the L2 slice room for the arrivals
+        if ((it & 15) == 15 && clock64() - t0 > G2_WAIT_CYCLES) {
+          trl_set_error(TRL_ERR_WAIT_TIMEOUT, 7, (int)blockIdx.x, (int)target);
+          s_flag[2] = 0;
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  return s_flag[2] != 0;
+}
+
+template <int M>
+__global__ void __launch_bounds__(G2_THREADS, 3)
+gemv2_chain_kernel(const __grid_constant__ G2Chain ch, int NS, const TrlPushArgs push) {
+  constexpr int W = G2_WARPS;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  // ring [W][NS][STAGE_BYTES] | bars [W][MAX_NS] | xs (xs_bytes) | 8 spare floats | red[64] | slots
+  unsigned char* ring = smem_raw;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)W * NS * STAGE_BYTES);
+  __half* xs = reinterpret_cast<__half*>(reinterpret_cast<unsigned char*>(bars) + W * G2_MAX_NS * 8);
+  float* red = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(xs) + ch.xs_bytes) + 8;
+  float* slots = red + 64;
+  int* s_flag = reinterpret_cast<int*>(red + 48);      // [0..1] cooperative finish, [2] chain barrier, [3] generation
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t ring_w = smem_addr(ring + (size_t)warp * NS * STAGE_BYTES);
+  const uint32_t bar_w = smem_addr(bars + warp * G2_MAX_NS);
+
+  // ---- producer (lane 0 of each warp): walks this warp's unit ranges of op 0, 1, ... in order
+  int pj = 0, p_unit = 0, p_step = 0, p_slot = 0;
+  uint32_t p_off = 0;
+  G2Range pr = g2_range(ch.op[0], warp);
+  const uint8_t* p_src = ch.op[0].wst + (size_t)pr.p_lo * pr.pair_bytes;
+  auto p_enter = [&]() {                 // position the cursor at the start of op pj's range
+    p_unit = pr.u0, p_step = pr.u0 % pr.nsteps;
+    p_off = (uint32_t)(pr.u0 / pr.nsteps) * pr.pair_bytes + (uint32_t)(pr.u0 % pr.nsteps) * (uint32_t)UNIT_BYTES;
+  };
+  p_enter();
+  auto issue = [&]() {   // one stage: the next STAGE_UNITS units of the producer's current op
+    while (pj < ch.n_ops && p_unit >= pr.u1) {
+      if (++pj < ch.n_ops) {
+        pr = g2_range(ch.op[pj], warp);
+        p_src = ch.op[pj].wst + (size_t)pr.p_lo * pr.pair_bytes;
+        p_enter();
+      }
+    }
+    if (pj >= ch.n_ops) return;
+    uint32_t bytes = 0;
+#pragma unroll
+    for (int g = 0; g < STAGE_UNITS; ++g) {
+      if (p_unit < pr.u1) {
+        bytes += (p_step == pr.nsteps - 1) ? (uint32_t)pr.nlast * 36u : (uint32_t)UNIT_BYTES;
+        if (++p_step == pr.nsteps) p_step = 0;
+        ++p_unit;
+      }
+    }
+    const uint32_t bar = bar_w + 8u * p_slot;
+    g2_expect_tx(bar, bytes);
+    g2_bulk_load(ring_w + (uint32_t)p_slot * STAGE_BYTES, p_src + p_off, bytes, bar);
+    p_off += bytes;
+    if (++p_slot == NS) p_slot = 0;
+  };
+  if (lane == 0) {
+    for (int s = 0; s < NS; ++s) g2_mbar_init(bar_w + 8u * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (int s = 0; s < NS; ++s) issue();     // weights never depend on the previous kernel
+  }
+  pdl_launch_dependents(120);
+  pdl_wait();
+  if (threadIdx.x == 0) s_flag[3] = (int)__ldcg(ch.bar + G2_BAR_RELEASE);
+  __syncthreads();
+  const uint32_t gen0 = (uint32_t)s_flag[3];
+  uint32_t n_bar = 0;
+
+  int slot = 0;
+  uint32_t parity = 0;
+  bool ok = true;
+  for (int j = 0; j < ch.n_ops; ++j) {
+    const G2Op& o = ch.op[j];
+    const G2Range cr = g2_range(o, warp);
+    const int K = o.K, nslot = o.nslot, nsteps = cr.nsteps, pl = cr.pl, p_lo = cr.p_lo;
+    const bool full = (K & 1023) == 0;
+    // the cooperative finish has a grid barrier of its own after which every CTA is past op j - 1
+    if (j > 0 && !o.coop) ok = g2_grid_barrier(ch.bar, gen0 + (++n_bar), s_flag) && ok;
+    else __syncthreads();                 // slots and red of the previous op are free
+    trl_trace_mark(3 * j);                // past the barrier in front of op j
+    for (int i = threadIdx.x; i < pl * 2 * nslot * M; i += G2_THREADS) slots[i] = 0.f;
+    float res0 = 0.f;
+    uint32_t push_epoch = 0;
+    if (o.epi == EPI2_RESIDUAL && (int)threadIdx.x < pl * 2 * M)
+      res0 = __bfloat162float(__ldcg(o.residual + (size_t)(threadIdx.x % M) * o.ldr + p_lo * 2 + threadIdx.x / M));
+    if (o.epi == EPI2_PUSH) push_epoch = __ldcg(reinterpret_cast<const uint32_t*>(push.ws[push.rank])) + 1;
+    if (o.coop)
+      ok = g2_coop_finish(const_cast<bf16*>(o.x), o.ldx, M, K, push.ws[push.rank], push.world, push.hmax, s_flag) && ok;
+    g2_stage_x<M>(o.x, o.ldx, K, o.norm_w, xs, red);   // ends with a block barrier
+    trl_trace_mark(3 * j + 1);
+
+    const uint32_t xs_a = smem_addr(xs) + (uint32_t)lane * 16u;
+    const uint32_t pstride = (uint32_t)cr.nchunks * 16u, xrow_bytes = (uint32_t)K * 2u;
+    if (cr.u0 < cr.u1 && ok) {
+      int cp = cr.u0 / nsteps, cs = cr.u0 % nsteps;
+      float acc[2][M];
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
+      auto flush = [&](int pair_local) {
+        const int sl = nslot == 2 ? (pair_local * nsteps >= cr.u0 ? 0 : 1) : warp - g2_owner(pair_local * nsteps, cr.U, W);
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+          for (int m = 0; m < M; ++m) {
+            const float v = warp_sum(acc[r][m]);
+            if (lane == 0) slots[((size_t)(pair_local * 2 + r) * nslot + sl) * M + m] = v;
+            acc[r][m] = 0.f;
+          }
+      };
+      // one unit of n chunks at shared address `ua`, step `st` of its row pair (n = 32: every lane works)
+      auto unit = [&](uint32_t ua, int st, int n) {
+        if (lane < n) {
+          const uint4 wv0 = g2_lds128(ua + lane * 16);
+          const uint4 wv1 = g2_lds128(ua + n * 16 + lane * 16);
+          const uint16_t sv[2] = {g2_lds16(ua + n * 32 + lane * 2), g2_lds16(ua + n * 34 + lane * 2)};
+          const uint32_t w4[2][4] = {{wv0.x, wv0.y, wv0.z, wv0.w}, {wv1.x, wv1.y, wv1.z, wv1.w}};
+          const uint32_t xa = xs_a + (uint32_t)st * 512u;
+#pragma unroll
+          for (int m = 0; m < M; ++m) {
+            uint32_t xh[16];
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+              const uint4 t = g2_lds128(xa + (uint32_t)m * xrow_bytes + (uint32_t)p * pstride);
+              xh[p * 4 + 0] = t.x, xh[p * 4 + 1] = t.y, xh[p * 4 + 2] = t.z, xh[p * 4 + 3] = t.w;
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+              const float2 sc = h2_to_f2(cvt_e4m3x2_to_h2(sv[r]));
+#pragma unroll
+              for (int blk = 0; blk < 2; ++blk) {
+                uint32_t a = 0u;  // f16x2 zero
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                  uint32_t h[4];
+                  cvt_e2m1x8_to_h2x4(w4[r][blk * 2 + q], h);
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) a = hfma2_u(h[i], xh[(blk * 2 + q) * 4 + i], a);
+                }
+                const float2 af = h2_to_f2(a);
+                acc[r][m] = fmaf(blk == 0 ? sc.x : sc.y, af.x + af.y, acc[r][m]);
+              }
+            }
+          }
+        }
+      };
+      // the same with 32 chunks (K % 1024 == 0): constant offsets, no per-lane predicate
+      auto unit_full = [&](uint32_t ua, int st) {
+        const uint4 wv0 = g2_lds128(ua), wv1 = g2_lds128(ua + 512u);
+        const uint16_t sv[2] = {g2_lds16(ua + 1024u - (uint32_t)lane * 14u), g2_lds16(ua + 1088u - (uint32_t)lane * 14u)};
+        const uint32_t w4[2][4] = {{wv0.x, wv0.y, wv0.z, wv0.w}, {wv1.x, wv1.y, wv1.z, wv1.w}};
+        const uint32_t xa = xs_a + (uint32_t)st * 512u;
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          uint32_t xh[16];
+#pragma unroll
+          for (int p = 0; p < 4; ++p) {
+            const uint4 t = g2_lds128(xa + (uint32_t)m * xrow_bytes + (uint32_t)p * pstride);
+            xh[p * 4 + 0] = t.x, xh[p * 4 + 1] = t.y, xh[p * 4 + 2] = t.z, xh[p * 4 + 3] = t.w;
+          }
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const float2 sc = h2_to_f2(cvt_e4m3x2_to_h2(sv[r]));
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk) {
+              uint32_t a = 0u;  // f16x2 zero
+#pragma unroll
+              for (int q = 0; q < 2; ++q) {
+                uint32_t h[4];
+                cvt_e2m1x8_to_h2x4(w4[r][blk * 2 + q], h);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) a = hfma2_u(h[i], xh[(blk * 2 + q) * 4 + i], a);
+              }
+              const float2 af = h2_to_f2(a);
+              acc[r][m] = fmaf(blk == 0 ? sc.x : sc.y, af.x + af.y, acc[r][m]);
+            }
+          }
+        }
+      };
+      auto wait_stage = [&](uint32_t bar, uint32_t par, int u) {
+        if (g2_try_wait(bar, par)) return true;
+        const long long t0 = clock64();
+        bool fine = true;
+        for (uint32_t it = 1; !g2_try_wait(bar, par); ++it) {
+          if ((it & 63) == 0 && clock64() - t0 > G2_WAIT_CYCLES) {
+            trl_set_error(TRL_ERR_MBAR_TIMEOUT, (int)blockIdx.x, 300 + warp, u);
+            fine = false;
+            break;
+          }
+        }
+        return (bool)__all_sync(0xffffffffu, fine);
+      };
+      if (full) {
+        for (int u = cr.u0; u < cr.u1; u += STAGE_UNITS) {
+          ok = wait_stage(bar_w + 8u * slot, parity, u);
+          if (!ok) break;
+          const uint32_t ua = ring_w + (uint32_t)slot * STAGE_BYTES + (uint32_t)lane * 16u;
+          unit_full(ua, cs);
+          if (++cs == nsteps) {
+            flush(cp);
+            cs = 0, ++cp;
+          }
+          if (u + 1 < cr.u1) {
+            unit_full(ua + UNIT_BYTES, cs);
+            if (++cs == nsteps) {
+              flush(cp);
+              cs = 0, ++cp;
+            }
+          }
+          __syncwarp();
+          if (lane == 0) issue();          // refill the stage just consumed (this op's or a later op's bytes)
+          if (++slot == NS) slot = 0, parity ^= 1u;
+        }
+      } else {
+        for (int u = cr.u0; u < cr.u1;) {
+          ok = wait_stage(bar_w + 8u * slot, parity, u);
+          if (!ok) break;
+          uint32_t ua = ring_w + (uint32_t)slot * STAGE_BYTES;
+#pragma unroll
+          for (int g = 0; g < STAGE_UNITS; ++g) {
+            if (u >= cr.u1) break;
+            const int n = (cs != nsteps - 1) ? 32 : cr.nlast;
+            unit(ua, cs, n);
+            ua += (uint32_t)n * 36u;
+            ++u;
+            if (++cs == nsteps) {
+              flush(cp);
+              cs = 0, ++cp;
+            }
+          }
+          __syncwarp();
+          if (lane == 0) issue();
+          if (++slot == NS) slot = 0, parity ^= 1u;
+        }
+      }
+      if (ok && cs != 0) flush(cp);        // range ended inside a pair
+    }
+    trl_trace_mark(3 * j + 2);
+    __syncthreads();
+
+    // block-wide epilogue over this CTA's rows of op j
+    const float ts = *o.tscale;
+    float rsc[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) rsc[m] = ts * g2_row_scale(red, m, K, o.norm_w != nullptr, o.eps);
+    if (o.epi == EPI2_SWIGLU) {
+      for (int i = threadIdx.x; i < pl * M; i += G2_THREADS) {
+        const int pr_ = i / M, m = i % M;
+        float g = 0.f, u = 0.f;
+        for (int sl = 0; sl < nslot; ++sl) {
+          g += slots[((size_t)(pr_ * 2) * nslot + sl) * M + m];
+          u += slots[((size_t)(pr_ * 2 + 1) * nslot + sl) * M + m];
+        }
+        const float sc = rsc[m];
+        const int n = (p_lo + pr_) * 2;
+        reinterpret_cast<bf16*>(o.out)[(size_t)m * o.ldy + (n >> 1)] = __float2bfloat16(silu_f(g * sc) * (u * sc));
+      }
+    } else {
+      for (int i = threadIdx.x; i < pl * 2 * M; i += G2_THREADS) {
+        const int rl = i / M, m = i % M;
+        const int n = p_lo * 2 + rl;
+        float v = 0.f;
+        for (int sl = 0; sl < nslot; ++sl) v += slots[((size_t)rl * nslot + sl) * M + m];
+        v *= rsc[m];
+        if (o.epi == EPI2_PUSH) {
+          const size_t off = 65536 + ((size_t)(((push_epoch & 1) * 8 + push.rank) * 8 + push.row0 + m) * push.hmax + n) * 8;
+          const uint2 word = make_uint2(__float_as_uint(v), push_epoch);
+          for (int p = 0; p < push.world; ++p) st_relaxed_sys_v2(push.ws[p] + off, word);
+        } else {
+          if (o.epi == EPI2_RESIDUAL) v += i < G2_THREADS ? res0 : __bfloat162float(__ldcg(o.residual + (size_t)m * o.ldr + n));
+          if (o.epi == EPI2_STORE_F32)
+            reinterpret_cast<float*>(o.out)[(size_t)m * o.ldy + n] = v;
+          else
+            reinterpret_cast<bf16*>(o.out)[(size_t)m * o.ldy + n] = __float2bfloat16(v);
+        }
+      }
+    }
+  }
+  if (!ok) {
+    // copies may still be in flight towards this CTA's shared memory: let them land
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) {
+    }
+  }
+  trl_trace_end();
+}
+
 int g2_num_sms() {
   static int sms = 0;
   if (sms == 0) {
@@ -582,6 +963,49 @@ cudaError_t dispatch2(int M, const bf16* x, int ldx, const uint8_t* wst, const f
   if (M == 1) return launch_gemv2<1, EPI, COOP>(x, ldx, wst, ts, norm_w, eps, res, ldr, y, ldy, N, K, st, push);
   if (M == 2) return launch_gemv2<2, EPI, COOP>(x, ldx, wst, ts, norm_w, eps, res, ldr, y, ldy, N, K, st, push);
   return cudaErrorInvalidValue;
+}
+
+
+template <int M>
+cudaError_t launch_chain(const TrlChainOp* ops, int n_ops, uint32_t* bar, const TrlPushArgs& push, cudaStream_t st) {
+  constexpr int W = G2_WARPS;
+  static const int ctas_per_sm = getenv("TRL_GEMV2_CTAS") ? atoi(getenv("TRL_GEMV2_CTAS")) : 3;
+  int grid = g2_num_sms() * ctas_per_sm;
+  int kmax = 0;
+  for (int j = 0; j < n_ops; ++j) grid = min(grid, ops[j].N / 2), kmax = max(kmax, ops[j].K);
+  G2Chain ch;
+  ch.n_ops = n_ops, ch.bar = bar, ch.xs_bytes = M * kmax * (int)sizeof(__half);
+  size_t slot_bytes = 0;
+  for (int j = 0; j < n_ops; ++j) {
+    const TrlChainOp& a = ops[j];
+    G2Op& o = ch.op[j];
+    const int npairs = a.N / 2;
+    o.x = (const bf16*)a.x, o.wst = (const uint8_t*)a.wst, o.tscale = (const float*)a.tscale;
+    o.norm_w = (const float*)a.norm_w, o.residual = (const bf16*)a.residual, o.out = a.out;
+    o.ldx = a.ldx, o.ldr = a.ldr, o.ldy = a.ldy, o.N = a.N, o.K = a.K, o.epi = a.epi, o.coop = a.coop, o.eps = a.eps;
+    o.nslot = (npairs / grid) >= W ? 2 : W;
+    const int pl_max = (npairs + grid - 1) / grid;
+    slot_bytes = max(slot_bytes, (size_t)pl_max * 2 * o.nslot * M * sizeof(float));
+  }
+  for (int j = n_ops; j < G2_CHAIN_MAX; ++j) ch.op[j] = ch.op[0];
+  const size_t fixed = (size_t)W * G2_MAX_NS * 8 + (size_t)ch.xs_bytes + 8 * sizeof(float) + 64 * sizeof(float) + slot_bytes;
+  int ns = (int)((74 * 1024 - (long)fixed) / (W * STAGE_BYTES));
+  if (ns < 2) ns = (int)((112 * 1024 - (long)fixed) / (W * STAGE_BYTES));
+  ns = min(ns, G2_MAX_NS);
+  if (ns < 2) return cudaErrorInvalidValue;
+  const size_t smem = (size_t)W * ns * STAGE_BYTES + fixed;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(gemv2_chain_kernel<M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(gemv2_chain_kernel<M>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    configured = true;
+  }
+  // the grid barriers need every CTA resident at once
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv2_chain_kernel<M>, G2_THREADS, smem) != cudaSuccess ||
+      per_sm * g2_num_sms() < grid)
+    return cudaErrorInvalidValue;
+  return trl_launch(gemv2_chain_kernel<M>, dim3(grid), dim3(G2_THREADS), smem, st, ch, ns, push);
 }
 
 }  // namespace
@@ -652,4 +1076,25 @@ TRL_API int trl_gemv2_nvfp4_coop(void* x, int ldx, const void* wst, const void* 
     return (int)dispatch2<EPI2_SWIGLU, true>(M, (const bf16*)x, ldx, (const uint8_t*)wst, (const float*)tscale,
                                              (const float*)norm_w, eps, nullptr, 0, y, ldy, N, K, st, push);
   return (int)cudaErrorInvalidValue;
+}
+
+// Up to four dependent projections (M <= 2 rows) in one launch: op j + 1 may read what op j stored.
+// `bar`: 64 zero-initialised uint32 words in device memory that belong to this stream of launches.
+// ws / rank / world / hmax: the tensor-parallel workspace table for EPI2_PUSH and coop ops (null / 0 without).
+TRL_API int trl_gemv2_chain(const void* ops, int n_ops, int M, void* bar, void* const* ws, int rank, int world,
+                            int hmax, void* stream) {
+  const TrlChainOp* a = (const TrlChainOp*)ops;
+  if (n_ops < 1 || n_ops > G2_CHAIN_MAX || M < 1 || M > 2 || bar == nullptr) return (int)cudaErrorInvalidValue;
+  for (int j = 0; j < n_ops; ++j) {
+    if (trl_gemv_stream_bytes(a[j].N, a[j].K) < 0 || a[j].K > G2_XV * G2_THREADS * 8) return (int)cudaErrorInvalidValue;
+    if (a[j].epi < EPI2_STORE || a[j].epi > EPI2_PUSH) return (int)cudaErrorInvalidValue;
+    if ((a[j].epi == EPI2_PUSH || a[j].coop) && (ws == nullptr || world < 1 || world > 8)) return (int)cudaErrorInvalidValue;
+    if (a[j].epi == EPI2_PUSH && a[j].N > hmax) return (int)cudaErrorInvalidValue;
+    if (a[j].coop && (a[j].K > hmax || (a[j].epi != EPI2_STORE && a[j].epi != EPI2_SWIGLU))) return (int)cudaErrorInvalidValue;
+  }
+  TrlPushArgs push;
+  for (int i = 0; i < 8; ++i) push.ws[i] = (ws != nullptr && i < world) ? (unsigned char*)ws[i] : nullptr;
+  push.rank = rank, push.world = world, push.hmax = hmax, push.row0 = 0;
+  if (M == 1) return (int)launch_chain<1>(a, n_ops, (uint32_t*)bar, push, (cudaStream_t)stream);
+  return (int)launch_chain<2>(a, n_ops, (uint32_t*)bar, push, (cudaStream_t)stream);
 }

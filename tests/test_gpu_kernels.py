@@ -36,7 +36,7 @@ def test_gemv_nvfp4_plain(ops, m, n, k):
     w = _q(n, k, seed=n + k)
     x = (torch.randn(m, k, generator=torch.Generator().manual_seed(m)) * 2).to(DEV, torch.bfloat16)
     y = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
-    ops._gemv(x, w, y)
+    ops.gemv_now(x, w, y)
     want = ref.linear(x, w)
     assert _rel(y, want) < 6e-3
     from tilerl_b200.ops import native
@@ -50,18 +50,18 @@ def test_gemv_nvfp4_fused_norm_residual_swiglu_f32(ops):
     x = (torch.randn(m, k, generator=g) * 30).to(DEV, torch.bfloat16)   # large activations: range scaling
     nw = (1 + 0.1 * torch.randn(k, generator=g)).to(DEV)
     y = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
-    ops._gemv(x, w, y, norm_w=nw, eps=1e-6)
+    ops.gemv_now(x, w, y, norm_w=nw, eps=1e-6)
     h = ref.rmsnorm(x, nw, 1e-6).to(torch.bfloat16)
     assert _rel(y, ref.linear(h, w)) < 6e-3
     res = torch.randn(m, n, generator=g).to(DEV, torch.bfloat16)
     out = res.clone()
-    ops._gemv(x, w, out, residual=out, epi=1)
+    ops.gemv_now(x, w, out, residual=out, epi=1)
     assert _rel(out, ref.linear(x, w, res)) < 6e-3
     act = torch.empty(m, n // 2, dtype=torch.bfloat16, device=DEV)
-    ops._gemv(x, w, act, norm_w=nw, eps=1e-6, epi=2)
+    ops.gemv_now(x, w, act, norm_w=nw, eps=1e-6, epi=2)
     assert _rel(act, ref.swiglu(ref.linear(h, w))) < 1e-2
     yf = torch.empty(m, n, dtype=torch.float32, device=DEV)
-    ops._gemv(x, w, yf, epi=3)
+    ops.gemv_now(x, w, yf, epi=3)
     assert _rel(yf, ref.linear(x, w)) < 3e-3
 
 
@@ -85,16 +85,16 @@ def test_streamed_gemv_matches_oracle_and_register_kernel(ops, m, n, k):
         ops.gemv_stream = stream
         outs = []
         y = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
-        ops._gemv(x, w, y, norm_w=nw, eps=1e-6)
+        ops.gemv_now(x, w, y, norm_w=nw, eps=1e-6)
         outs.append(y)
         out = res.clone()
-        ops._gemv(x, w, out, residual=out, epi=1)
+        ops.gemv_now(x, w, out, residual=out, epi=1)
         outs.append(out)
         act = torch.empty(m, n // 2, dtype=torch.bfloat16, device=DEV)
-        ops._gemv(x, w, act, norm_w=nw, eps=1e-6, epi=2)
+        ops.gemv_now(x, w, act, norm_w=nw, eps=1e-6, epi=2)
         outs.append(act)
         yf = torch.empty(m, n, dtype=torch.float32, device=DEV)
-        ops._gemv(x, w, yf, epi=3)
+        ops.gemv_now(x, w, yf, epi=3)
         outs.append(yf)
         torch.cuda.synchronize()
         return outs
@@ -121,7 +121,7 @@ def test_gemv_bf16_lm_head_shape(ops):
     x = torch.randn(2, k, generator=g).to(DEV, torch.bfloat16)
     nw = torch.ones(k, device=DEV)
     y = torch.empty(2, n, dtype=torch.float32, device=DEV)
-    ops._gemv(x, w, y, norm_w=nw, eps=1e-6, epi=3)
+    ops.gemv_now(x, w, y, norm_w=nw, eps=1e-6, epi=3)
     want = ref.linear(ref.rmsnorm(x, nw, 1e-6).to(torch.bfloat16), w)
     assert _rel(y, want) < 2e-3
     tok = ops.argmax(y)
@@ -632,3 +632,51 @@ def test_tensor_core_decode_attention_matches_scalar_kernel_and_oracle(w, hist, 
     assert torch.equal(outs["mma_auto"], outs["mma_auto2"])
     for mode in ("mma1", "mma4", "mma7", "mma_auto"):
         assert float((outs[mode] - outs["scalar"]).abs().max()) < 0.03, mode
+
+
+@pytest.mark.parametrize("m", [1, 2])
+@pytest.mark.parametrize("h,ffn,inner", [(1024, 3072, 2048), (5120, 2176, 1152)])
+def test_chained_projections_equal_separate_launches(ops, m, h, ffn, inner):
+    """A layer's worth of dependent decode projections (norm + in-projection, output projection +
+    residual, norm + gate_up + SwiGLU, down projection + residual) queued into one chained launch
+    gives the bits of the four separate launches, twice in a row, and matches the fp32 oracle.
+    Shapes with K % 1024 != 0 take the ragged-step path inside the chain."""
+    from tilerl_b200.ops import native
+    g = torch.Generator().manual_seed(h + ffn + m)
+    w_in, w_out = _q(2 * inner, h, seed=1), _q(h, inner, seed=2)
+    w_gu, w_down = _q(2 * ffn, h, seed=3), _q(h, ffn, seed=4)
+    x0 = torch.randn(m, h, generator=g).to(DEV, torch.bfloat16)
+    nw1 = (1 + 0.1 * torch.randn(h, generator=g)).to(DEV)
+    nw2 = (1 + 0.1 * torch.randn(h, generator=g)).to(DEV)
+
+    def layer(chain: bool):
+        ops.chain = chain
+        x = x0.clone()
+        y = torch.empty(m, 2 * inner, dtype=torch.bfloat16, device=DEV)
+        act = torch.empty(m, ffn, dtype=torch.bfloat16, device=DEV)
+        launches = native.launch_count
+        ops._gemv(x, w_in, y, norm_w=nw1, eps=1e-6)
+        a = y[:, :inner]                               # a strided view feeds the next projection
+        ops._gemv(a, w_out, x, residual=x, epi=1)
+        ops._gemv(x, w_gu, act, norm_w=nw2, eps=1e-6, epi=2)
+        ops._gemv(act, w_down, x, residual=x, epi=1)
+        ops.flush()
+        torch.cuda.synchronize()
+        return x, y, act, native.launch_count - launches
+
+    keep = ops.chain
+    try:
+        c1, c2, s1 = layer(True), layer(True), layer(False)
+    finally:
+        ops.chain = keep
+    assert c1[3] == 1 and s1[3] == 4
+    for a, b, c in zip(c1[:3], c2[:3], s1[:3]):
+        assert torch.equal(a, b) and torch.equal(a, c)
+    h1 = ref.rmsnorm(x0, nw1, 1e-6).to(torch.bfloat16)
+    y = ref.linear(h1, w_in).to(torch.bfloat16)
+    x1 = ref.linear(y[:, :inner], w_out, x0).to(torch.bfloat16)
+    gu = ref.linear(ref.rmsnorm(x1, nw2, 1e-6).to(torch.bfloat16), w_gu).float()
+    act = (torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]).to(torch.bfloat16)
+    x2 = ref.linear(act, w_down, x1)
+    assert _rel(c1[0], x2) < 1e-2
+    assert native.read_error()[0] == 0

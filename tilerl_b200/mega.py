@@ -123,6 +123,7 @@ def interpret(program: Program, model, batch, ops, kv_pool, state_pool) -> torch
         elif op == NORM_SWIGLU:
             buf[dst] = ops.norm_linear_swiglu(buf[src], prm[p0], prm[p1], eps, None)
         elif op == GATHER_LAST:
+            getattr(ops, "settle", lambda: None)()     # queued projections write the row before it is gathered
             buf[dst] = buf[src][batch.last_idx.long()]
         elif op == LM_HEAD:
             buf[dst] = ops.lm_head(buf[src], prm[p0], prm[p1], eps)[..., :cfg.vocab]

@@ -18,6 +18,7 @@ launch M ``:733-905``).
 from __future__ import annotations
 
 import math
+import ctypes
 import os
 from typing import Dict, Optional
 
@@ -27,6 +28,16 @@ from ..formats import FP8BlockTensor, NVFP4Tensor
 from . import native as N
 
 EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU, EPI_STORE_F32 = 0, 1, 2, 3
+EPI_PUSH = 4            # tensor-parallel row-parallel projection: partial rows pushed to every rank
+CHAIN_MAX = 4
+
+
+class ChainOp(ctypes.Structure):
+    """One projection of a chained launch (``TrlChainOp`` of ``csrc/gemv2.cu``)."""
+    _fields_ = [("x", ctypes.c_void_p), ("wst", ctypes.c_void_p), ("tscale", ctypes.c_void_p),
+                ("norm_w", ctypes.c_void_p), ("residual", ctypes.c_void_p), ("out", ctypes.c_void_p),
+                ("ldx", ctypes.c_int), ("ldr", ctypes.c_int), ("ldy", ctypes.c_int), ("N", ctypes.c_int),
+                ("K", ctypes.c_int), ("epi", ctypes.c_int), ("coop", ctypes.c_int), ("eps", ctypes.c_float)]
 GEMV_MAX_M = 8
 
 
@@ -84,6 +95,16 @@ class CudaOps:
         self.terms_large = int(os.environ.get("TRL_TERMS_LARGE", terms_large))
         self.act_dtype = torch.bfloat16
         self.attn_mma = os.environ.get("TRL_ATTN_MMA", "1") != "0" and hasattr(self.lib, "trl_attn_decode_mma")
+        # TRL_GEMV_CHAIN=1: consecutive 1-2 row projections are queued and go out as one chained launch
+        # (grid barriers between them, weight rings refilled across the barriers); anything else
+        # flushes the queue.  Off by default: measured on the 27B tick a grid barrier costs more than the
+        # kernel boundary it replaces (the CTAs of one projection finish 6-9 us apart and the barrier
+        # waits for the last, where separate launches let the next kernel's CTAs move in as slots free up):
+        # 5.54 ms per tick chained, 4.37 ms as separate launches.
+        self.chain = os.environ.get("TRL_GEMV_CHAIN", "0") == "1" and hasattr(self.lib, "trl_gemv2_chain")
+        self._queue = []          # [(ChainOp fields, rows, tensors kept alive)]
+        self._chain_bar = torch.zeros(64, dtype=torch.int32, device=self.device)
+        self.chain_kmax = int(os.environ.get("TRL_GEMV_CHAIN_KMAX", "65536"))   # longer rows are launched alone
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.vocab = None   # set by the engine builder: real vocabulary size (TP pads it)
         if comm is not None:
@@ -95,10 +116,70 @@ class CudaOps:
         return t
 
     def settle(self) -> None:
-        """Make the residual stream current: complete an all-reduce that a row-parallel projection
-        left pending for its consumer (tensor parallelism only)."""
+        """Make every buffer current: launch the queued projections and complete an all-reduce
+        that a row-parallel projection left pending for its consumer (tensor parallelism only)."""
+        self.flush()
         if self.comm is not None and getattr(self.comm, "pending", None) is not None:
             self.comm.settle()
+
+    # ---- chained projections ------------------------------------------------------------
+    def _enqueue(self, m, x, wst, tscale, norm_w, eps, residual, out, n, k, epi, coop=0) -> None:
+        if self._queue and (self._queue[0][1] != m or k > self.chain_kmax or self._queue[-1][0]["K"] > self.chain_kmax):
+            self.flush()
+        f = dict(x=x.data_ptr(), wst=wst.data_ptr(), tscale=tscale.data_ptr(), norm_w=N.ptr(norm_w),
+                 residual=N.ptr(residual), out=N.ptr(out), ldx=x.stride(0),
+                 ldr=residual.stride(0) if residual is not None else 0, ldy=out.stride(0) if out is not None else 0,
+                 N=n, K=k, epi=epi, coop=coop, eps=float(eps))
+        self._queue.append((f, m, (x, wst, tscale, norm_w, residual, out)))
+        if len(self._queue) == CHAIN_MAX:
+            self.flush()
+
+    def gemv_now(self, x, w, y, **kw) -> None:
+        """``_gemv`` launched at once (tests, probes): the queued form leaves ``y`` unwritten until
+        ``flush`` / ``settle`` or the next op that is not a 1-2 row projection."""
+        self._gemv(x, w, y, **kw)
+        self.flush()
+
+    def flush(self) -> None:
+        """Launch what ``_enqueue`` collected: one chained launch, or the single-projection kernels
+        when the chain is one op long or the chained launch is refused (grid not co-resident)."""
+        q = self._queue
+        if not q:
+            return
+        self._queue = []
+        comm = self.comm if (self.comm is not None and hasattr(self.comm, "table")) else None
+        if len(q) > 1:
+            arr = (ChainOp * len(q))(*[ChainOp(**f) for f, _, _ in q])
+            rc = self.lib.trl_gemv2_chain(arr, len(q), q[0][1], self._chain_bar.data_ptr(),
+                                          comm.table if comm else None, comm.rank if comm else 0,
+                                          comm.world if comm else 0, comm.hmax if comm else 0, N.stream())
+            if rc == 0:
+                N.count()
+                return
+        for f, m, _ in q:
+            self._launch_single(f, m, comm)
+
+    def _launch_single(self, f, m, comm) -> None:
+        st = N.stream()
+        if f["epi"] == EPI_PUSH:
+            N.check(self.lib.trl_gemv2_nvfp4_push(f["x"], f["ldx"], f["wst"], f["tscale"], comm.table, comm.rank,
+                                                  comm.world, comm.hmax, m, f["N"], f["K"], st), "gemv2_push")
+        elif f["coop"]:
+            rc = self.lib.trl_gemv2_nvfp4_coop(f["x"], f["ldx"], f["wst"], f["tscale"], f["norm_w"], f["eps"],
+                                               f["out"], f["ldy"], m, f["N"], f["K"], f["epi"], comm.table,
+                                               comm.rank, comm.world, comm.hmax, st)
+            if rc != 0:     # outside the cooperative kernel's limits: finishing kernel, then the plain projection
+                N.check(self.lib.trl_allreduce_finish(comm.table, comm.rank, comm.world, comm.hmax, f["x"], f["ldx"],
+                                                      f["x"], f["ldx"], m, f["K"], st), "allreduce_finish")
+                N.check(self.lib.trl_gemv2_nvfp4(f["x"], f["ldx"], f["wst"], f["tscale"], f["norm_w"], f["eps"],
+                                                 None, 0, f["out"], f["ldy"], m, f["N"], f["K"], f["epi"], st),
+                        "gemv2_nvfp4")
+                N.count()
+        else:
+            N.check(self.lib.trl_gemv2_nvfp4(f["x"], f["ldx"], f["wst"], f["tscale"], f["norm_w"], f["eps"],
+                                             f["residual"], f["ldr"], f["out"], f["ldy"], m, f["N"], f["K"],
+                                             f["epi"], st), "gemv2_nvfp4")
+        N.count()
 
     def _gemv(self, x, w, y, *, norm_w=None, eps=0.0, residual=None, epi=EPI_STORE):
         m, k = x.shape
@@ -107,18 +188,28 @@ class CudaOps:
         if self.comm is not None and getattr(self.comm, "pending", None) is not None:
             if stream and norm_w is not None and residual is None and epi in (EPI_STORE, EPI_SWIGLU):
                 from .gemm_tc import w_stream
-                if self.comm.consume_pending(x, w_stream(w), w.tscale, norm_w, eps, y, w.wq.shape[0], epi):
+                if self.chain and self.comm.pending_is(x):
+                    # the consumer completes the all-reduce itself, inside the chained launch
+                    self.comm.pending = None
+                    self._enqueue(m, x, w_stream(w), w.tscale, norm_w, eps, None, y, w.wq.shape[0], k, epi, coop=1)
                     return
-            self.comm.settle()
+                if not self.chain and self.comm.consume_pending(x, w_stream(w), w.tscale, norm_w, eps, y, w.wq.shape[0], epi):
+                    return
+            self.settle()
         if stream:
             from .gemm_tc import w_stream
             n = w.wq.shape[0]
+            if self.chain:
+                self._enqueue(m, x, w_stream(w), w.tscale, norm_w, eps, residual, y, n, k, epi)
+                return
             N.check(self.lib.trl_gemv2_nvfp4(
                 x.data_ptr(), x.stride(0), w_stream(w).data_ptr(), w.tscale.data_ptr(),
                 N.ptr(norm_w), eps, N.ptr(residual), residual.stride(0) if residual is not None else 0,
                 y.data_ptr(), y.stride(0), m, n, k, epi, N.stream()), "gemv2_nvfp4")
             N.count()
-        elif isinstance(w, NVFP4Tensor):
+            return
+        self.flush()
+        if isinstance(w, NVFP4Tensor):
             n = w.wq.shape[0]
             N.check(self.lib.trl_gemv_nvfp4(
                 x.data_ptr(), x.stride(0), w.wq.data_ptr(), w.scale.data_ptr(), w.tscale.data_ptr(),
@@ -159,6 +250,7 @@ class CudaOps:
             self.settle()     # only the GEMV path can finish a pending all-reduce itself
         if isinstance(w, FP8BlockTensor) and w.shape[1] % 128 == 0:
             from . import gemm_fp8
+            self.settle()
             gemm_fp8.linear(self, x, w, y, norm_w=norm_w, eps=eps, residual=residual, epi=epi)
             return
         if self._tc(w, t):
@@ -253,6 +345,7 @@ class CudaOps:
         return residual
 
     def attention(self, qkv, lp, batch, pool, attn_idx, cfg, n_q, n_kv):
+        self.flush()
         t = qkv.shape[0]
         d = cfg.head_dim
         q = self.ws.get("q", (t, n_q, d), torch.bfloat16)
@@ -367,6 +460,7 @@ class CudaOps:
         return best
 
     def gdn(self, inp, lp, batch, spool, gdn_idx, cfg, nk, nv):
+        self.flush()
         t = inp.shape[0]
         d = cfg.gdn_head_dim
         f32 = torch.float32
@@ -427,12 +521,14 @@ class CudaOps:
 
     def full_logits(self, logits):
         """Full-vocabulary logits (gathers the vocab shards under TP)."""
+        self.flush()
         if self.comm is not None and self.comm.world > 1:
             full = self.comm.all_gather_logits(logits)
             return full[..., :self.vocab] if self.vocab else full
         return logits
 
     def argmax(self, logits):
+        self.flush()
         m, v = logits.shape
         if self.comm is not None and self.comm.world > 1:
             v_valid = (self.vocab or v * self.comm.world) - self.comm.rank * v
@@ -450,6 +546,7 @@ class CudaOps:
         One pinned staging block and one host-to-device copy carry all per-row arguments, one
         kernel draws every row, one device-to-host copy brings tokens and log-probabilities back.
         Returns ``(tokens, logprobs)`` as Python lists."""
+        self.flush()
         import numpy as np
         n = len(rows)
         nucleus = top_ks is not None and any(k or p < 1.0 for k, p in zip(top_ks, top_ps))

@@ -97,6 +97,7 @@ class SymmComm:
     # ---- workspace views handed to CudaOps ----------------------------------------------------
     def attach(self, ops) -> None:
         """Place the residual stream and the row-parallel GEMM output in symmetric memory."""
+        self.ops = ops
         ops.ws.bufs["x"] = self.xres
         ops.ws.bufs["rowout"] = self.big
 
@@ -110,6 +111,13 @@ class SymmComm:
         if t <= min(8, getattr(ops, "gemv_tokens", 8)) and isinstance(w, NVFP4Tensor) and lora is None:
             if t <= 2 and getattr(ops, "gemv_stream", False) and self.stream_push and ops._stream_ok(w) and t * k * 2 <= 88 * 1024 and k <= 18432:
                 from ..ops.gemm_tc import w_stream
+                if getattr(ops, "chain", False) and n <= self.hmax:
+                    from ..ops.cuda import EPI_PUSH
+                    ops._enqueue(t, a, w_stream(w), w.tscale, None, 0.0, None, None, n, k, EPI_PUSH)
+                    self.pending = (t, n, residual)
+                    if not self.fuse_finish:
+                        self.settle()
+                    return residual
                 N.check(self.lib.trl_gemv2_nvfp4_push(a.data_ptr(), a.stride(0), w_stream(w).data_ptr(),
                                                       w.tscale.data_ptr(), self.table, self.rank, self.world,
                                                       self.hmax, t, n, k, st), "gemv2_push")
@@ -135,10 +143,20 @@ class SymmComm:
         N.count()
         return residual
 
+    def pending_is(self, x) -> bool:
+        """True when ``x`` is exactly the residual rows whose all-reduce is pending."""
+        if self.pending is None:
+            return False
+        t, n, residual = self.pending
+        return (x.data_ptr() == residual.data_ptr() and x.shape[0] == t and x.shape[1] == n and n <= self.hmax
+                and x.stride(0) == residual.stride(0))
+
     def settle(self) -> None:
         """Complete a pending one-shot all-reduce with the stand-alone finishing kernel."""
         if self.pending is None:
             return
+        if getattr(self, "ops", None) is not None:
+            self.ops.flush()          # the pushing projection may still sit in the launch queue
         t, n, residual = self.pending
         self.pending = None
         N.check(self.lib.trl_allreduce_finish(self.table, self.rank, self.world, self.hmax, residual.data_ptr(),
@@ -214,12 +232,16 @@ class NcclComm:
     def consume_pending(self, *a, **k) -> bool:
         return False
 
+    def pending_is(self, x) -> bool:
+        return False
+
     def linear_allreduce_residual(self, ops, a, w, residual, lora=None):
         t, n = a.shape[0], w.shape[0]
         part = ops.ws.get("nccl_part", (t, n), torch.bfloat16)
         ops._linear(a, w, part)
         if lora is not None:
             ops._lora_add(part, a, lora)
+        ops.flush()
         dist.all_reduce(part, group=self.group)
         residual.add_(part)
         N.count(2)

@@ -93,7 +93,7 @@ def main():
     y = torch.zeros(1, h, dtype=torch.bfloat16, device=dev)
 
     def nccl_path():
-        ops._gemv(a, w, y)
+        ops.gemv_now(a, w, y)
         dist.all_reduce(y)
         res.add_(y)
 
@@ -101,7 +101,7 @@ def main():
         comm.linear_allreduce_residual(ops, a, w, res)
 
     def gemv_only():
-        ops._gemv(a, w, y)
+        ops.gemv_now(a, w, y)
 
     out["decode_down_proj"] = dict(
         gemv_only_us=round(_time(gemv_only, 50, True), 2),
@@ -124,16 +124,19 @@ def main():
     def pair_fused():
         comm.linear_allreduce_residual(ops, a, w, res)
         ops._linear(res, w_up, act, norm_w=nw, eps=1e-6, epi=EPI_SWIGLU)
+        ops.flush()
 
     def pair_local():      # same two projections without any communication (the floor of the pair)
         ops._gemv(a, w, y, residual=res, epi=1)
         ops._linear(y, w_up, act, norm_w=nw, eps=1e-6, epi=EPI_SWIGLU)
+        ops.flush()
 
     def pair_nccl():
-        ops._gemv(a, w, y)
+        ops.gemv_now(a, w, y)
         dist.all_reduce(y)
         res.add_(y)
         ops._linear(res, w_up, act, norm_w=nw, eps=1e-6, epi=EPI_SWIGLU)
+        ops.flush()
 
     from tilerl_b200.ops.gemm_tc import w_stream
     w_stream(w), w_stream(w_up)

@@ -75,7 +75,7 @@ def main():
             return e0.elapsed_time(e1) / args.reps * 1e3  # us
 
         if args.only in ("", "gemv") and args.m <= 8:
-            us = timeit(lambda w: ops._gemv(x, w, y))
+            us = timeit(lambda w: ops.gemv_now(x, w, y))
             res["gemv_simt_us"] = round(us, 2)
             res["gemv_simt_TBs"] = round(wbytes / us / 1e6, 3)
         if args.only in ("", "gemm"):

@@ -22,7 +22,7 @@ import torch
 
 KINDS = {2: "gdn_scan", 3: "attn_prep", 4: "attn_split", 5: "attn_combine", 6: "gemv_bf16(lm_head)", 7: "embedding",
          10: "allreduce_finish", 12: "gdn_prep", 100: "gemv2 store", 101: "gemv2 store+coop", 102: "gemv2 residual",
-         104: "gemv2 swiglu", 105: "gemv2 swiglu+coop", 106: "gemv2 store_f32", 108: "gemv2 push", 109: "gemv2 push+coop", 0: "other"}
+         104: "gemv2 swiglu", 105: "gemv2 swiglu+coop", 106: "gemv2 store_f32", 108: "gemv2 push", 109: "gemv2 push+coop", 120: "gemv2 chain", 0: "other"}
 
 
 def main():
@@ -53,7 +53,7 @@ def main():
     prompt = torch.randint(0, cfg.vocab, (args.ctx,), generator=g).tolist()
     eng.generate([prompt], SamplingParams(max_tokens=4, ignore_eos=True))      # captures the graph
     torch.cuda.synchronize()
-    buf = np.zeros((8192, 8), dtype=np.uint64)
+    buf = np.zeros((8192, 16), dtype=np.uint64)
     native.lib().trl_trace_read(buf.ctypes.data, 8192, 1)                       # reset
     eng.generate([prompt], SamplingParams(max_tokens=args.ticks + 1, ignore_eos=True))
     torch.cuda.synchronize()
@@ -88,6 +88,18 @@ def main():
             if tick[i + 1, 6]:
                 ph[4] += (int(tick[i + 1, 6]) - int(tick[i, 3])) / 1e3    # last CTA's exit after CTA 0's
                 ph[5] += (int(dep[i + 1]) - int(tick[i + 1, 6])) / 1e3    # last exit -> next launch released
+    # chained launches (kind 120): marks 0..9 = per op (past its barrier, row staged, main loop done)
+    chain = [tick[i] for i in range(len(tick) - 1) if int(tick[i, 0]) == 120 and tick[i, 4]]
+    if chain:
+        c = np.array(chain, dtype=np.float64)
+        marks = np.concatenate([c[:, 4:6], c[:, 8:16]], axis=1)            # marks 0..9
+        rel = (marks - c[:, 2:3]) / 1e3
+        rel[marks == 0] = np.nan
+        names = [f"op{j}:{w}" for j in range(4) for w in ("past_barrier", "staged", "main_done")][:10]
+        out_chain = {nm: round(float(np.nanmean(rel[:, k])), 2) for k, nm in enumerate(names) if not np.all(np.isnan(rel[:, k]))}
+        out_chain["exit"] = round(float(np.mean((c[:, 3] - c[:, 2]) / 1e3)), 2)
+    else:
+        out_chain = None
     total = (dep[-1] - dep[0]) / 1e3
     out = {"tick_us": round(total, 1), "launches": len(tick) - 1,
            "critical_path_us": {k: {"n": v[0], "sum": round(v[1], 1), "avg": round(v[1] / v[0], 2),
@@ -95,6 +107,8 @@ def main():
                                 for k, v in sorted(share.items(), key=lambda kv: -kv[1][1])}}
     out["phases_us_avg"] = {k: dict(zip(("staged", "main_loop", "epilogue", "last_cta_after_cta0", "release_after_last_exit"),
                                         [round(x / v[0], 2) for x in v[1:]])) for k, v in phases.items()}
+    if out_chain:
+        out["chain_marks_us_after_dependency_avg"] = out_chain
     if rank == 0:
         print(json.dumps(out))
         print("tick_trace done")
