@@ -28,8 +28,10 @@ namespace {
 
 constexpr int RING = 16;
 
-// grid = (tokens, 2*nk + nv): one CTA of D threads per (token, head); q/k heads also
-// L2-normalise, the first CTA of a token also emits the gates.
+// grid = (ceil(tokens / TPC), 2*nk + nv), 128 threads: a thread owns 8 adjacent channels of one token
+// (D / 8 threads per token, TPC = 1024 / D tokens per CTA): four 16-byte row loads (the conv window), depthwise
+// causal conv + SiLU; q/k heads L2-normalise with shuffles inside the token's thread group; the head-0
+// CTA of a tile also emits the gates.  No shared memory, no block barrier.
 __global__ void __launch_bounds__(128)
 gdn_prep_kernel(const bf16* inp, int ld, const float* __restrict__ conv_w,
                 const float* __restrict__ dt_bias, const float* __restrict__ a_log,
@@ -37,48 +39,85 @@ gdn_prep_kernel(const bf16* inp, int ld, const float* __restrict__ conv_w,
                 const int* seq_ids, const int* q_start,
                 const int* state_slots, long ring_slot_stride,
                 float* qn, float* kn, float* vc,
-                float* gout, float* bout, int nk, int nv, int D, int KW) {
-  __shared__ float red[32];
+                float* gout, float* bout, int nk, int nv, int D, int KW, int T) {
   pdl_launch_dependents(12);
   pdl_wait();
-  const int t = blockIdx.x, head = blockIdx.y;
+  const int tpt = D >> 3;                       // threads per token
+  const int tpc = 128 / tpt;                    // tokens per CTA
+  const int t = blockIdx.x * tpc + threadIdx.x / tpt, head = blockIdx.y;
+  const int d = (threadIdx.x % tpt) * 8;
   const int C = 2 * nk * D + nv * D;
-  const int pos = positions[t];
-  const int seq = seq_ids[t];
-  const int t0 = q_start[seq];
-  const bf16* rg = ring + (size_t)state_slots[seq] * ring_slot_stride;
-  const int d = threadIdx.x;
   const int c = head * D + d;
-  float acc = 0.f;
-  for (int j = 0; j < KW; ++j) {  // tap KW-1 multiplies the newest row
-    const int back = KW - 1 - j;
-    const int pj = pos - back;
-    float v = 0.f;
-    if (pj >= 0) {
-      if (t - back >= t0)
-        v = __bfloat162float(inp[(size_t)(t - back) * ld + c]);
-      else
-        v = __bfloat162float(rg[(size_t)(pj % RING) * C + c]);
+  float val[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) val[e] = 0.f;
+  if (t < T) {
+    const int pos = positions[t];
+    const int seq = seq_ids[t];
+    const int t0 = q_start[seq];
+    const bf16* rg = ring + (size_t)state_slots[seq] * ring_slot_stride;
+    uint4 rows[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {               // tap KW-1 multiplies the newest row
+      rows[j] = make_uint4(0u, 0u, 0u, 0u);
+      if (j < KW) {
+        const int back = KW - 1 - j;
+        const int pj = pos - back;
+        if (pj >= 0) {
+          const bf16* src = t - back >= t0 ? inp + (size_t)(t - back) * ld + c : rg + (size_t)(pj % RING) * C + c;
+          if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+            rows[j] = *reinterpret_cast<const uint4*>(src);
+          } else {                              // row width not a multiple of 8 (odd head counts of a TP shard): 4-byte pieces
+            const uint32_t* s32 = reinterpret_cast<const uint32_t*>(src);
+            rows[j] = make_uint4(s32[0], s32[1], s32[2], s32[3]);
+          }
+        }
+      }
     }
-    acc = fmaf(v, conv_w[(size_t)c * KW + j], acc);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float wt[4] = {0.f, 0.f, 0.f, 0.f};
+      if (KW == 4) {
+        const float4 w4 = *reinterpret_cast<const float4*>(conv_w + (size_t)(c + e) * 4);
+        wt[0] = w4.x, wt[1] = w4.y, wt[2] = w4.z, wt[3] = w4.w;
+      } else {
+        for (int j = 0; j < KW; ++j) wt[j] = conv_w[(size_t)(c + e) * KW + j];
+      }
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t wd = e < 2 ? rows[j].x : e < 4 ? rows[j].y : e < 6 ? rows[j].z : rows[j].w;
+        const float2 f = bf162_bits_to_f2(wd);
+        acc = fmaf((e & 1) ? f.y : f.x, wt[j], acc);
+      }
+      val[e] = silu_f(acc);
+    }
   }
-  const float val = silu_f(acc);
   if (head < 2 * nk) {
-    const float ss = block_sum(val * val, red);
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += val[e] * val[e];
+    for (int m = 1; m < tpt; m <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);   // the token's threads are lane-aligned
     const float nrm = rsqrtf(ss + 1e-12f) * (head < nk ? rsqrtf((float)D) : 1.f);
-    if (head < nk)
-      qn[((size_t)t * nk + head) * D + d] = val * nrm;
-    else
-      kn[((size_t)t * nk + (head - nk)) * D + d] = val * nrm;
-  } else {
-    vc[((size_t)t * nv + (head - 2 * nk)) * D + d] = val;
+    if (t < T) {
+      float* dst = (head < nk ? qn + ((size_t)t * nk + head) * D : kn + ((size_t)t * nk + (head - nk)) * D) + d;
+      *reinterpret_cast<float4*>(dst) = make_float4(val[0] * nrm, val[1] * nrm, val[2] * nrm, val[3] * nrm);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(val[4] * nrm, val[5] * nrm, val[6] * nrm, val[7] * nrm);
+    }
+  } else if (t < T) {
+    float* dst = vc + ((size_t)t * nv + (head - 2 * nk)) * D + d;
+    *reinterpret_cast<float4*>(dst) = make_float4(val[0], val[1], val[2], val[3]);
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(val[4], val[5], val[6], val[7]);
   }
   if (head == 0) {
-    const bf16* ab = inp + (size_t)t * ld + C + nv * D;
-    for (int h = threadIdx.x; h < nv; h += blockDim.x) {
+    const int tb = blockIdx.x * tpc;
+    for (int x = threadIdx.x; x < tpc * nv; x += blockDim.x) {
+      const int tt = tb + x / nv, h = x % nv;
+      if (tt >= T) break;
+      const bf16* ab = inp + (size_t)tt * ld + C + nv * D;
       const float a = __bfloat162float(ab[h]), b = __bfloat162float(ab[nv + h]);
-      gout[(size_t)t * nv + h] = -__expf(a_log[h]) * softplus_f(a + dt_bias[h]);
-      bout[(size_t)t * nv + h] = sigmoid_f(b);
+      gout[(size_t)tt * nv + h] = -__expf(a_log[h]) * softplus_f(a + dt_bias[h]);
+      bout[(size_t)tt * nv + h] = sigmoid_f(b);
     }
   }
 }
@@ -723,9 +762,373 @@ gdn_scan_wy_kernel(const float* qn, const float* kn,
   }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Chunk-parallel prefill scan on the tensor cores (mma.sync m16n8k16 bf16, fp32 accumulate;
+// dk = dv = 128).  One CTA of 8 warps per (sequence, value head) walks the sequence in chunks of
+// 16 tokens; the fp32 state lives in accumulator fragments (warp w owns state rows 16 w .. 16 w + 15)
+// with a bf16 copy in shared memory as the B operand of the products that read it.  Per chunk
+// (G_i = running sum of the log-decays, all decays applied in fp32):
+//   KK = K K^T, QK = Q K^T                       (16 x 16 x 128, warps 0 and 1)
+//   A = beta_i KK_ij e^{G_i - G_j} (j < i),  T = (I + A)^-1   (forward substitution, one warp; bf16 hi + lo)
+//   W = T (K beta e^G),  U = T (V beta)          (16 x 128 x 16 each)
+//   V' = U - W S                                 (16 x 128 x 128)
+//   O = (Q e^G) S + (QK e^{G_i - G_j}, j <= i) V'
+//   S <- e^{G_last} S + (K e^{G_last - G})^T V'  (128 x 128 x 16)
+// followed by the gated RMSNorm of the 16 output rows.  Operands are bf16 (the state's bf16 copy
+// included), accumulation and the state itself fp32: the precision of chunked delta-rule kernels
+// on tensor cores in general.  Reference parity: the six-stage chunk pipeline of
+// packages/tilerl-kernels/src/tilerl_kernels/kernels_gdn.py:128-537 (cumsum, kkt, solve_tril, wu,
+// state scan, chunk output), here one kernel.
+constexpr int GC_C = 16, GC_D = 128, GC_ROW = GC_D * 2;     // chunk, head dim, bytes of a bf16 row over dk
+constexpr int GC_NS = 2, GC_DV = GC_D / GC_NS, GC_VROW = GC_DV * 2;   // value columns per CTA, bytes of such a row
+struct GcSmem {
+  float sq[2][GC_C][GC_D], sk[2][GC_C][GC_D];    // fp32 q, k of the current and the next chunk
+  float sv[2][GC_C][GC_DV];                      // fp32 v, this CTA's columns
+  float sg[2][GC_C], sb[2][GC_C];
+  __align__(128) unsigned char qraw[GC_C * GC_ROW], kraw[GC_C * GC_ROW], qe[GC_C * GC_ROW], kb[GC_C * GC_ROW],
+      ws[GC_C * GC_ROW];                                                 // bf16 [16][128 dk], 16-byte chunks XOR-swizzled
+  __align__(128) unsigned char vb[GC_C * GC_VROW], vn[GC_C * GC_VROW];   // bf16 [16][64 dv]
+  __align__(128) unsigned char sbf[GC_D * GC_VROW];                      // bf16 copy of the state [dk][64 dv], swizzled
+  __align__(16) unsigned char kdt[GC_D * 32];                            // (K e^{G_last - G})^T  bf16 [128][16]
+  __align__(16) unsigned char t_hi[GC_C * 32], t_lo[GC_C * 32], qkm[GC_C * 32];   // bf16 [16][16]
+  float a[GC_C][GC_C + 1];                       // fp32 A
+};
+__device__ __forceinline__ void gc_cp4(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ uint32_t gc_off(int r, int c) { return (uint32_t)(r * GC_ROW + ((c ^ (r & 7)) << 4)); }
+__device__ __forceinline__ uint32_t gc_offv(int r, int c) { return (uint32_t)(r * GC_VROW + ((c ^ (r & 7)) << 4)); }
+__device__ __forceinline__ void gc_ldsm(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void gc_ldsm_t(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void gc_ldsm2_t(uint32_t (&r)[2], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__device__ __forceinline__ void gc_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// grid (2 nv, B): CTA = (value head, half of its value columns, sequence).  The delta rule never mixes
+// value columns, so the two halves of a head are independent scans; what depends only on q, k and
+// the gates (KK, QK, T, W) is computed by both.  Raw outputs go to o_scratch (fp32); the gated
+// RMSNorm, which needs whole rows, is the small kernel below.
+__global__ void __launch_bounds__(256, 2)
+gdn_chunk_mma_kernel(const float* qn, const float* kn, const float* vc, const float* gin, const float* bin,
+                     float* states, int* cur, bf16* ring, const bf16* inp, int ld, const int* q_start,
+                     const int* q_len, const int* positions, const int* state_slots, long state_slot_stride,
+                     long plane_stride, long ring_slot_stride, float* o_scratch, int nk, int nv) {
+  constexpr int D = GC_D, C = GC_C, DV = GC_DV;
+  extern __shared__ __align__(128) unsigned char gc_raw[];
+  GcSmem& sm = *reinterpret_cast<GcSmem*>(gc_raw);
+  pdl_launch_dependents(2);
+  pdl_wait();
+  const int h = blockIdx.x / GC_NS, c0 = (blockIdx.x % GC_NS) * DV, seq = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int T = q_len[seq], t0 = q_start[seq];
+  if (T == 0) return;
+  const int slot = state_slots[seq];
+  const int kh = h * nk / nv;
+  const int live = cur[slot];
+  float* sp = states + (size_t)slot * state_slot_stride + (size_t)h * D * D + (size_t)live * plane_stride + c0;
+  const int g8 = lane >> 2, t4 = lane & 3;
+  const int lrow = (lane & 7) + ((lane >> 3) & 1) * 8;      // ldmatrix row of this lane (both x4 layouts used here)
+
+  auto u32 = [](const void* p) { return (uint32_t)__cvta_generic_to_shared(p); };
+  const uint32_t a_qraw = u32(sm.qraw), a_kraw = u32(sm.kraw), a_qe = u32(sm.qe), a_kb = u32(sm.kb), a_vb = u32(sm.vb),
+                 a_ws = u32(sm.ws), a_vn = u32(sm.vn), a_sbf = u32(sm.sbf), a_kdt = u32(sm.kdt), a_thi = u32(sm.t_hi),
+                 a_tlo = u32(sm.t_lo), a_qkm = u32(sm.qkm);
+
+  // state rows 16 warp .. 16 warp + 15, this CTA's 64 columns, as accumulator fragments
+  float S[DV / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < DV / 8; ++nt) {
+    const float2 lo = *reinterpret_cast<const float2*>(sp + (size_t)(16 * warp + g8) * D + nt * 8 + t4 * 2);
+    const float2 hi = *reinterpret_cast<const float2*>(sp + (size_t)(16 * warp + g8 + 8) * D + nt * 8 + t4 * 2);
+    S[nt][0] = lo.x, S[nt][1] = lo.y, S[nt][2] = hi.x, S[nt][3] = hi.y;
+  }
+  auto store_sbf = [&]() {
+#pragma unroll
+    for (int nt = 0; nt < DV / 8; ++nt) {
+      *reinterpret_cast<uint32_t*>(sm.sbf + gc_offv(16 * warp + g8, nt) + t4 * 4) = f2_to_bf162_bits(S[nt][0], S[nt][1]);
+      *reinterpret_cast<uint32_t*>(sm.sbf + gc_offv(16 * warp + g8 + 8, nt) + t4 * 4) = f2_to_bf162_bits(S[nt][2], S[nt][3]);
+    }
+  };
+  store_sbf();
+
+  auto stage = [&](int i0, int b) {      // fp32 q, k, v rows and the gates of chunk i0 .. i0 + 15 (rows past T: zeros)
+    for (int x = tid; x < C * (D / 4); x += 256) {
+      const int tt = x / (D / 4), e = (x % (D / 4)) * 4;
+      if (i0 + tt < T) {
+        const size_t src = ((size_t)(t0 + i0 + tt) * nk + kh) * D + e;
+        cp_async16(&sm.sq[b][tt][e], qn + src);
+        cp_async16(&sm.sk[b][tt][e], kn + src);
+      } else {
+        *reinterpret_cast<float4*>(&sm.sq[b][tt][e]) = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4*>(&sm.sk[b][tt][e]) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    {
+      const int tt = tid >> 4, e = (tid & 15) * 4;
+      if (i0 + tt < T) cp_async16(&sm.sv[b][tt][e], vc + ((size_t)(t0 + i0 + tt) * nv + h) * D + c0 + e);
+      else *reinterpret_cast<float4*>(&sm.sv[b][tt][e]) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (tid < C) {                       // gates: asynchronous too, nothing of the next chunk is waited for here
+      if (i0 + tid < T) {
+        gc_cp4(&sm.sg[b][tid], gin + (size_t)(t0 + i0 + tid) * nv + h);
+        gc_cp4(&sm.sb[b][tid], bin + (size_t)(t0 + i0 + tid) * nv + h);
+      } else {
+        sm.sg[b][tid] = 0.f, sm.sb[b][tid] = 0.f;                           // padding rows: no decay, no update
+      }
+    }
+    cp_async_commit();
+  };
+
+  stage(0, 0);
+  int b = 0;
+  for (int i0 = 0; i0 < T; i0 += C, b ^= 1) {
+    cp_async_wait<0>();
+    __syncthreads();                       // chunk b landed; the previous chunk's tiles are free
+    if (i0 + C < T) stage(i0 + C, b ^ 1);
+    // running sums of the log-decays, recomputed where they are needed (16 broadcast reads)
+    float g_last = 0.f;
+#pragma unroll
+    for (int j = 0; j < C; ++j) g_last += sm.sg[b][j];
+    // ---- operand tiles (bf16) from the staged fp32 rows: thread = (token, 8 columns)
+    {
+      const int tt = tid >> 4, ch = tid & 15, e = ch * 8;
+      float gi = 0.f;
+      for (int j = 0; j <= tt; ++j) gi += sm.sg[b][j];
+      const float eg = __expf(gi), beta = sm.sb[b][tt], kbs = beta * eg;
+      const float4 q0 = *reinterpret_cast<const float4*>(&sm.sq[b][tt][e]), q1 = *reinterpret_cast<const float4*>(&sm.sq[b][tt][e + 4]);
+      const float4 k0 = *reinterpret_cast<const float4*>(&sm.sk[b][tt][e]), k1 = *reinterpret_cast<const float4*>(&sm.sk[b][tt][e + 4]);
+      const float qv[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+      const float kv[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
+      uint32_t oq[4], ok_[4], oqe[4], okb[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        oq[j] = f2_to_bf162_bits(qv[2 * j], qv[2 * j + 1]);
+        ok_[j] = f2_to_bf162_bits(kv[2 * j], kv[2 * j + 1]);
+        oqe[j] = f2_to_bf162_bits(qv[2 * j] * eg, qv[2 * j + 1] * eg);
+        okb[j] = f2_to_bf162_bits(kv[2 * j] * kbs, kv[2 * j + 1] * kbs);
+      }
+      const uint32_t off = gc_off(tt, ch);
+      *reinterpret_cast<uint4*>(sm.qraw + off) = make_uint4(oq[0], oq[1], oq[2], oq[3]);
+      *reinterpret_cast<uint4*>(sm.kraw + off) = make_uint4(ok_[0], ok_[1], ok_[2], ok_[3]);
+      *reinterpret_cast<uint4*>(sm.qe + off) = make_uint4(oqe[0], oqe[1], oqe[2], oqe[3]);
+      *reinterpret_cast<uint4*>(sm.kb + off) = make_uint4(okb[0], okb[1], okb[2], okb[3]);
+      if (ch < DV / 8) {
+        const float4 v0 = *reinterpret_cast<const float4*>(&sm.sv[b][tt][e]), v1 = *reinterpret_cast<const float4*>(&sm.sv[b][tt][e + 4]);
+        *reinterpret_cast<uint4*>(sm.vb + gc_offv(tt, ch)) =
+            make_uint4(f2_to_bf162_bits(v0.x * beta, v0.y * beta), f2_to_bf162_bits(v0.z * beta, v0.w * beta),
+                       f2_to_bf162_bits(v1.x * beta, v1.y * beta), f2_to_bf162_bits(v1.z * beta, v1.w * beta));
+      }
+    }
+    {
+      // transposed decayed keys [dk][token]: thread = (dk row, 8 tokens), one 16-byte store
+      const int r = tid & 127, half = tid >> 7;
+      float gi = 0.f;
+      for (int j = 0; j < half * 8; ++j) gi += sm.sg[b][j];
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        gi += sm.sg[b][half * 8 + 2 * j];
+        const float x0 = sm.sk[b][half * 8 + 2 * j][r] * __expf(g_last - gi);
+        gi += sm.sg[b][half * 8 + 2 * j + 1];
+        const float x1 = sm.sk[b][half * 8 + 2 * j + 1][r] * __expf(g_last - gi);
+        o[j] = f2_to_bf162_bits(x0, x1);
+      }
+      *reinterpret_cast<uint4*>(sm.kdt + (size_t)r * 32 + half * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    __syncthreads();
+    // ---- warp 0: KK -> A -> T = (I + A)^-1;  warp 1: QK';  warps 2..7 meanwhile start O = (Q e^G) S
+    float O[4] = {0.f, 0.f, 0.f, 0.f};     // this warp's 8 value columns
+    auto qs_product = [&]() {
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t af[4], bs[2];
+        gc_ldsm(af, a_qe + gc_off(lrow, kk * 2 + (lane >> 4)));
+        gc_ldsm2_t(bs, a_sbf + gc_offv(kk * 16 + lrow, warp));
+        gc_mma(O, af, bs[0], bs[1]);
+      }
+    };
+    if (warp < 2) {
+      float gc[C];                         // inclusive running sums
+      {
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < C; ++j) acc += sm.sg[b][j], gc[j] = acc;
+      }
+      float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      const uint32_t a_base = warp == 0 ? a_kraw : a_qraw;
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t af[4], bfr[4];
+        gc_ldsm(af, a_base + gc_off(lrow, kk * 2 + (lane >> 4)));
+        gc_ldsm(bfr, a_kraw + gc_off((lane & 7) + (lane >> 4) * 8, kk * 2 + ((lane >> 3) & 1)));
+        gc_mma(acc[0], af, bfr[0], bfr[1]);
+        gc_mma(acc[1], af, bfr[2], bfr[3]);
+      }
+#pragma unroll
+      for (int n8 = 0; n8 < 2; ++n8)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = g8 + (e >> 1) * 8, j = n8 * 8 + t4 * 2 + (e & 1);
+          float gi_ = 0.f, gj_ = 0.f;
+#pragma unroll
+          for (int q = 0; q < C; ++q) gi_ = q == i ? gc[q] : gi_, gj_ = q == j ? gc[q] : gj_;
+          const float dec = j <= i ? __expf(gi_ - gj_) : 0.f;
+          if (warp == 0) sm.a[i][j] = j < i ? sm.sb[b][i] * acc[n8][e] * dec : 0.f;
+          else *reinterpret_cast<bf16*>(sm.qkm + i * 32 + j * 2) = __float2bfloat16(acc[n8][e] * dec);
+        }
+      if (warp == 0) {
+        __syncwarp();
+        if (lane < C) {                    // lane j solves column j of T by forward substitution
+          float tcol[C];
+#pragma unroll
+          for (int i = 0; i < C; ++i) {
+            float v = i == lane ? 1.f : 0.f;
+#pragma unroll
+            for (int m = 0; m < i; ++m) v -= sm.a[i][m] * tcol[m];
+            tcol[i] = i < lane ? 0.f : v;
+          }
+#pragma unroll
+          for (int i = 0; i < C; ++i) {
+            const bf16 hi = __float2bfloat16(tcol[i]);
+            *reinterpret_cast<bf16*>(sm.t_hi + i * 32 + lane * 2) = hi;
+            *reinterpret_cast<bf16*>(sm.t_lo + i * 32 + lane * 2) = __float2bfloat16(tcol[i] - __bfloat162float(hi));
+          }
+        }
+      }
+    } else {
+      qs_product();
+    }
+    __syncthreads();
+    // ---- W = T (K beta e^G) over all of dk (16 columns per warp); U = T (V beta), this warp's 8 value columns
+    if (warp < 2) qs_product();
+    float U[4] = {0.f, 0.f, 0.f, 0.f};
+    {
+      float Wf[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      uint32_t thi[4], tlo[4], bk[4], bv[2];
+      const uint32_t trow = (uint32_t)(lrow * 32 + (lane >> 4) * 16);
+      gc_ldsm(thi, a_thi + trow);
+      gc_ldsm(tlo, a_tlo + trow);
+      gc_ldsm_t(bk, a_kb + gc_off(lrow, 2 * warp + (lane >> 4)));
+      gc_ldsm2_t(bv, a_vb + gc_offv(lrow, warp));
+      gc_mma(Wf[0], thi, bk[0], bk[1]), gc_mma(Wf[1], thi, bk[2], bk[3]);
+      gc_mma(Wf[0], tlo, bk[0], bk[1]), gc_mma(Wf[1], tlo, bk[2], bk[3]);
+      gc_mma(U, thi, bv[0], bv[1]);
+      gc_mma(U, tlo, bv[0], bv[1]);
+#pragma unroll
+      for (int n8 = 0; n8 < 2; ++n8) {
+        *reinterpret_cast<uint32_t*>(sm.ws + gc_off(g8, 2 * warp + n8) + t4 * 4) = f2_to_bf162_bits(Wf[n8][0], Wf[n8][1]);
+        *reinterpret_cast<uint32_t*>(sm.ws + gc_off(g8 + 8, 2 * warp + n8) + t4 * 4) = f2_to_bf162_bits(Wf[n8][2], Wf[n8][3]);
+      }
+    }
+    __syncthreads();
+    // ---- V' = U - W S (this warp's 8 columns), kept as the bf16 B operand of the next two products
+    {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t af[4], bs[2];
+        gc_ldsm(af, a_ws + gc_off(lrow, kk * 2 + (lane >> 4)));
+        gc_ldsm2_t(bs, a_sbf + gc_offv(kk * 16 + lrow, warp));
+        gc_mma(acc, af, bs[0], bs[1]);
+      }
+      *reinterpret_cast<uint32_t*>(sm.vn + gc_offv(g8, warp) + t4 * 4) = f2_to_bf162_bits(U[0] - acc[0], U[1] - acc[1]);
+      *reinterpret_cast<uint32_t*>(sm.vn + gc_offv(g8 + 8, warp) + t4 * 4) = f2_to_bf162_bits(U[2] - acc[2], U[3] - acc[3]);
+    }
+    __syncthreads();
+    // ---- O += QK' V' (this warp's 8 columns) -> raw rows; state rows of this warp: S <- e^{G_last} S + Kd^T V'
+    {
+      uint32_t aq[4], bvn[2];
+      gc_ldsm(aq, a_qkm + (uint32_t)(lrow * 32 + (lane >> 4) * 16));
+      gc_ldsm2_t(bvn, a_vn + gc_offv(lrow, warp));
+      gc_mma(O, aq, bvn[0], bvn[1]);
+      float* orow = o_scratch + ((size_t)(t0 + i0) * nv + h) * D + c0 + 8 * warp + t4 * 2;
+      if (i0 + g8 < T) *reinterpret_cast<float2*>(orow + (size_t)g8 * nv * D) = make_float2(O[0], O[1]);
+      if (i0 + g8 + 8 < T) *reinterpret_cast<float2*>(orow + (size_t)(g8 + 8) * nv * D) = make_float2(O[2], O[3]);
+      const float el = __expf(g_last);
+      uint32_t ak[4];
+      gc_ldsm(ak, a_kdt + (uint32_t)((16 * warp + lrow) * 32 + (lane >> 4) * 16));
+#pragma unroll
+      for (int nt = 0; nt < DV / 8; nt += 2) {
+        uint32_t bvv[4];
+        gc_ldsm_t(bvv, a_vn + gc_offv(lrow, nt + (lane >> 4)));
+#pragma unroll
+        for (int e = 0; e < 4; ++e) S[nt][e] *= el, S[nt + 1][e] *= el;
+        gc_mma(S[nt], ak, bvv[0], bvv[1]);
+        gc_mma(S[nt + 1], ak, bvv[2], bvv[3]);
+      }
+    }
+    __syncthreads();                       // every warp has read the old state copy
+    store_sbf();
+  }
+  // ---- state back to its plane; conv ring refresh for the last tokens (as the token-serial scan does)
+#pragma unroll
+  for (int nt = 0; nt < DV / 8; ++nt) {
+    *reinterpret_cast<float2*>(sp + (size_t)(16 * warp + g8) * D + nt * 8 + t4 * 2) = make_float2(S[nt][0], S[nt][1]);
+    *reinterpret_cast<float2*>(sp + (size_t)(16 * warp + g8 + 8) * D + nt * 8 + t4 * 2) = make_float2(S[nt][2], S[nt][3]);
+  }
+  if (c0 == 0) {
+    const int cw = 2 * nk * D + nv * D;
+    bf16* rg = ring + (size_t)slot * ring_slot_stride;
+    const int first = max(0, T - RING);
+    const int rep = nv / nk;
+    for (int i = first; i < T; ++i) {
+      const int t = t0 + i;
+      const int rrow = positions[t] % RING;
+      const bf16* src = inp + (size_t)t * ld;
+      bf16* dst = rg + (size_t)rrow * cw;
+      if (h % rep == 0) {
+        for (int c = tid; c < 2 * D; c += 256) {
+          const int cc = (c < D) ? kh * D + c : nk * D + kh * D + (c - D);
+          dst[cc] = src[cc];
+        }
+      }
+      for (int c = tid; c < D; c += 256) {
+        const int cc = 2 * nk * D + h * D + c;
+        dst[cc] = src[cc];
+      }
+    }
+  }
+  trl_trace_end();
+}
+
+// Gated RMSNorm of raw GDN output rows: out[t, h, :] = o * rsqrt(mean(o^2) + eps) * w * silu(z); one warp per row.
+__global__ void __launch_bounds__(256)
+gdn_gated_norm_kernel(const float* o_scratch, const bf16* inp, int ld, const float* __restrict__ norm_w, float eps,
+                      bf16* out, int rows, int nk, int nv) {
+  constexpr int D = GC_D;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int t = row / nv, h = row % nv;
+  const float4 ov = __ldcg(reinterpret_cast<const float4*>(o_scratch + (size_t)row * D) + lane);
+  const uint2 zr = *reinterpret_cast<const uint2*>(inp + (size_t)t * ld + (2 * nk * D + nv * D) + (size_t)h * D + lane * 4);
+  const float4 w = *reinterpret_cast<const float4*>(norm_w + lane * 4);
+  const float ss = warp_sum(ov.x * ov.x + ov.y * ov.y + ov.z * ov.z + ov.w * ov.w);
+  const float rstd = rsqrtf(ss / (float)D + eps);
+  const float2 z0 = bf162_bits_to_f2(zr.x), z1 = bf162_bits_to_f2(zr.y);
+  uint2 o;
+  o.x = f2_to_bf162_bits(ov.x * rstd * w.x * silu_f(z0.x), ov.y * rstd * w.y * silu_f(z0.y));
+  o.y = f2_to_bf162_bits(ov.z * rstd * w.z * silu_f(z1.x), ov.w * rstd * w.w * silu_f(z1.y));
+  *reinterpret_cast<uint2*>(out + (size_t)row * D + lane * 4) = o;
+}
+
 }  // namespace
 
 static int g_gdn_wy = -1;   // -1: read TRL_GDN_WY at the first launch
+static int g_gdn_mma = -1;  // -1: on unless TRL_GDN_MMA=0 (read at the first launch)
 
 // ---------------------------------------------------------------------------------------
 // Decode tick (exactly one token per sequence, no kept planes) of a layer in ONE launch.
@@ -846,6 +1249,8 @@ gdn_decode_kernel(const bf16* inp, int ld, const float* __restrict__ conv_w,
 
 // Turns the chunk-parallel prefill scan on or off at run time (tests compare the two paths).
 TRL_API void trl_gdn_set_wy(int on) { g_gdn_wy = on ? 1 : 0; }
+// Prefill scan on the tensor cores (gdn_chunk_mma_kernel): 1 on, 0 off (token-serial scan), -1 = the environment's choice.
+TRL_API void trl_gdn_set_mma(int on) { g_gdn_mma = on; }
 
 // Scratch (fp32): qn, kn [T*nk*D]; vc, o_scratch [T*nv*D]; g, beta [T*nv].
 TRL_API int trl_gdn(const void* inp, int ld, const void* conv_w, const void* dt_bias, const void* a_log,
@@ -856,11 +1261,14 @@ TRL_API int trl_gdn(const void* inp, int ld, const void* conv_w, const void* dt_
                     void* beta, void* o_scratch, void* out, int T, int B, int nk, int nv, int D, int KW,
                     int planes, float eps, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
-  cudaError_t e = trl_launch(gdn_prep_kernel, dim3(T, 2 * nk + nv), dim3(D), 0, st, (const bf16*)inp, ld,
-                             (const float*)conv_w, (const float*)dt_bias, (const float*)a_log,
+  if (KW > 4) return (int)cudaErrorInvalidValue;
+  if ((D != 64 && D != 128) || (ld % 2) != 0) return (int)cudaErrorInvalidValue;
+  const int prep_tpc = 1024 / D;
+  cudaError_t e = trl_launch(gdn_prep_kernel, dim3((T + prep_tpc - 1) / prep_tpc, 2 * nk + nv), dim3(128), 0, st,
+                             (const bf16*)inp, ld, (const float*)conv_w, (const float*)dt_bias, (const float*)a_log,
                              (const bf16*)ring, (const int*)positions, (const int*)seq_ids,
                              (const int*)q_start, (const int*)state_slots, ring_slot_stride,
-                             (float*)qn, (float*)kn, (float*)vc, (float*)g, (float*)beta, nk, nv, D, KW);
+                             (float*)qn, (float*)kn, (float*)vc, (float*)g, (float*)beta, nk, nv, D, KW, T);
   if (e != cudaSuccess) return (int)e;
 #define RECUR(DD)                                                                                   \
   e = trl_launch(gdn_recur_kernel<DD>, dim3(nv, B), dim3(DD * 4), 0, st, (const float*)qn,          \
@@ -891,6 +1299,24 @@ TRL_API int trl_gdn(const void* inp, int ld, const void* conv_w, const void* dt_
                    (bf16*)ring, (const int*)q_start, (const int*)q_len, (const int*)positions,      \
                    (const int*)state_slots, state_slot_stride, plane_stride, ring_slot_stride,      \
                    (const float*)norm_w, eps, (float*)o_scratch, (bf16*)out, nk, nv);               \
+  }
+  // prefill ticks (more tokens than sequences, no per-token state planes) with dk = dv = 128 take the
+  // tensor-core chunk kernel; TRL_GDN_MMA=0 (or trl_gdn_set_mma(0)) falls back to the token-serial scan
+  if (g_gdn_mma < 0) g_gdn_mma = (getenv("TRL_GDN_MMA") && atoi(getenv("TRL_GDN_MMA")) == 0) ? 0 : 1;
+  if (g_gdn_mma != 0 && D == 128 && T > B && keep_flags == nullptr) {
+    static bool configured = false;
+    if (!configured) {
+      if (cudaFuncSetAttribute(gdn_chunk_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(GcSmem)) != cudaSuccess)
+        return 3;
+      configured = true;
+    }
+    e = trl_launch(gdn_chunk_mma_kernel, dim3(nv * GC_NS, B), dim3(256), sizeof(GcSmem), st, (const float*)qn,
+                   (const float*)kn, (const float*)vc, (const float*)g, (const float*)beta, (float*)states, (int*)cur,
+                   (bf16*)ring, (const bf16*)inp, ld, (const int*)q_start, (const int*)q_len, (const int*)positions,
+                   (const int*)state_slots, state_slot_stride, plane_stride, ring_slot_stride, (float*)o_scratch, nk, nv);
+    if (e != cudaSuccess) return (int)e;
+    return (int)trl_launch(gdn_gated_norm_kernel, dim3((T * nv + 7) / 8), dim3(256), 0, st, (const float*)o_scratch,
+                           (const bf16*)inp, ld, (const float*)norm_w, eps, (bf16*)out, T * nv, nk, nv);
   }
   static const bool legacy = getenv("TRL_GDN_LEGACY") != nullptr;
   // chunk-parallel scan for ticks that carry prompt tokens (more tokens than sequences) and keep

@@ -216,6 +216,7 @@ def test_gdn_kernel(ops, d, nk, nv):
         ([dict(tokens=[5], start=19, blocks=[1, 2], slot=1), dict(tokens=[6], start=3, blocks=[3], slot=2)], 0),
         ([dict(tokens=[5, 6, 7], start=20, blocks=[1, 2], slot=1, keep=True)], 3),
     ]
+    ops.lib.trl_gdn_set_mma(0)       # this test holds the fp32 token-serial kernels to tight state tolerances
     for seqs, keep in ticks:
         batch = Batch.build(seqs, DEV, keep_steps=keep)
         inp = (torch.randn(batch.n_tokens, cfg.gdn_in_rows, generator=g)).to(DEV, torch.bfloat16)
@@ -237,6 +238,7 @@ def test_gdn_kernel(ops, d, nk, nv):
         if keep:
             for p in pools:
                 p.select_step(1, 1)
+    ops.lib.trl_gdn_set_mma(-1)
 
 
 def test_sample_softmax_kernel_distribution_and_logprob():
@@ -561,6 +563,7 @@ def test_gdn_chunk_parallel_scan_matches_serial_scan_and_oracle(d, nk, nv):
               gdn_norm=(1 + 0.1 * torch.randn(d, generator=g)).to(DEV))
     lens1, lens2 = (70, 16, 5, 33), (48, 7, 20, 64)
     pools = {k: GdnStatePool(cfg, 6, DEV, planes=1, ring_dtype=torch.bfloat16) for k in ("wy", "serial", "ref")}
+    ops.lib.trl_gdn_set_mma(0)
     try:
         for tick, lens in enumerate((lens1, lens2)):
             starts = (0, 0, 0, 0) if tick == 0 else lens1
@@ -580,7 +583,53 @@ def test_gdn_chunk_parallel_scan_matches_serial_scan_and_oracle(d, nk, nv):
             assert torch.equal(pools["wy"].ring, pools["serial"].ring)
     finally:
         ops.lib.trl_gdn_set_wy(0)      # the default path
+        ops.lib.trl_gdn_set_mma(-1)
     from tilerl_b200.ops import native
+    assert native.read_error()[0] == 0
+
+
+@pytest.mark.parametrize("nk,nv", [(2, 4), (16, 48)])
+def test_gdn_tensor_core_chunk_kernel_matches_serial_scan_and_oracle(nk, nv):
+    """The mma chunk kernel (16-token chunks, bf16 operands, fp32 state) against the fp32
+    token-serial scan and the fp32 oracle: lengths around the chunk size, a long prompt, decode
+    rows riding along, a second tick that continues from the states of the first; run twice."""
+    from tilerl_b200.batch import Batch
+    from tilerl_b200.config import ModelConfig, GDN
+    from tilerl_b200.factory import make_ops
+    from tilerl_b200.kv import GdnStatePool
+    from tilerl_b200.ops import native
+    from tilerl_b200.ops.backend import RefOps
+    ops = make_ops("cuda")
+    d = 128
+    cfg = ModelConfig("t", hidden=64, ffn=64, vocab=64, layer_types=(GDN,), n_q_heads=2, n_kv_heads=1,
+                      head_dim=64, rotary_dim=64, rope_theta=1e6, gdn_k_heads=nk, gdn_v_heads=nv,
+                      gdn_head_dim=d)
+    g = torch.Generator().manual_seed(nk + nv)
+    lp = dict(conv=(torch.randn(cfg.gdn_conv_dim, 4, generator=g) * 0.3).to(DEV),
+              dt_bias=torch.rand(nv, generator=g).to(DEV), a_log=torch.log(1 + 3 * torch.rand(nv, generator=g)).to(DEV),
+              gdn_norm=(1 + 0.1 * torch.randn(d, generator=g)).to(DEV))
+    lens1, lens2 = (1, 15, 16, 17, 300), (31, 1, 48, 2, 212)
+    pools = {k: GdnStatePool(cfg, 8, DEV, planes=1, ring_dtype=torch.bfloat16) for k in ("mma", "mma2", "serial", "ref")}
+    try:
+        for tick, lens in enumerate((lens1, lens2)):
+            starts = (0,) * len(lens) if tick == 0 else lens1
+            seqs = [dict(tokens=[0] * n, start=s, blocks=list(range(1 + 32 * i, 33 + 32 * i)), slot=i + 1)
+                    for i, (n, s) in enumerate(zip(lens, starts))]
+            batch = Batch.build(seqs, DEV)
+            inp = torch.randn(batch.n_tokens, cfg.gdn_in_rows, generator=g).to(DEV, torch.bfloat16)
+            want = RefOps().gdn(inp, lp, batch, pools["ref"], 0, cfg, nk, nv).float()
+            ops.lib.trl_gdn_set_mma(0)
+            serial = ops.gdn(inp, lp, batch, pools["serial"], 0, cfg, nk, nv).float().clone()
+            ops.lib.trl_gdn_set_mma(1)
+            got = ops.gdn(inp, lp, batch, pools["mma"], 0, cfg, nk, nv).float().clone()
+            got2 = ops.gdn(inp, lp, batch, pools["mma2"], 0, cfg, nk, nv).float().clone()
+            assert torch.equal(got, got2) and torch.equal(pools["mma"].states, pools["mma2"].states)
+            assert _rel(got, want) < 2e-2, _rel(got, want)
+            assert _rel(got, serial) < 1.5e-2, _rel(got, serial)
+            assert _rel(pools["mma"].states, pools["ref"].states) < 1e-2, _rel(pools["mma"].states, pools["ref"].states)
+            assert torch.equal(pools["mma"].ring, pools["serial"].ring)
+    finally:
+        ops.lib.trl_gdn_set_mma(-1)
     assert native.read_error()[0] == 0
 
 

@@ -51,6 +51,7 @@ _SIGS = {
     "trl_batch_fill": [I, P, P, P, P, P, P, P, I, I, P, c_longlong],
     "trl_gemm_trace_read": [P, I],
     "trl_gdn_set_wy": [I],
+    "trl_gdn_set_mma": [I],
     "trl_sample_nucleus": [P, I, P, P, P, P, P, P, P, I, I, P],
     "trl_attn_decode_mma": [P, P, I, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P],
     "trl_gemv2_chain": [P, I, I, P, P, I, I, I, P],
@@ -67,7 +68,7 @@ _SIGS = {
 }
 
 
-_RESTYPE = {"trl_set_pdl": None, "trl_gdn_set_wy": None, "trl_pager_create": c_void_p, "trl_pager_destroy": None,
+_RESTYPE = {"trl_set_pdl": None, "trl_gdn_set_wy": None, "trl_gdn_set_mma": None, "trl_pager_create": c_void_p, "trl_pager_destroy": None,
             "trl_batch_ints": c_longlong, "trl_batch_fill": c_longlong}
 
 
