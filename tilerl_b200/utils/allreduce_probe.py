@@ -190,7 +190,10 @@ def main():
         us_ag_n = _time(lambda: dist.all_gather_into_tensor(full, shard), 10, False)
         us_ag_p = _time(lambda: zc.all_gather(shard, full), 10, False)
         us_rs_n = _time(lambda: dist.reduce_scatter_tensor(tmp, grad), 10, False)
-        us_rs_p = _time(lambda: zc.reduce_scatter(grad, gout, 1.0 / world, True), 10, False)
+        def rs_p2p():          # the kernel runs on the communicator's stream: wait for it, as the optimizer step does
+            zc.reduce_scatter(grad, gout, 1.0 / world, True)
+            zc.wait()
+        us_rs_p = _time(rs_p2p, 10, False)
         recv = n_full * 2 * (world - 1) / world
         zrows.append(dict(unit_mib=mb, allgather_nccl_us=round(us_ag_n, 1), allgather_p2p_us=round(us_ag_p, 1),
                           allgather_p2p_gbs=round(recv / us_ag_p / 1e3, 1),
