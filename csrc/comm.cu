@@ -75,7 +75,9 @@ __device__ __forceinline__ uint2* oneshot_slot(unsigned char* ws, int buf, int s
 __global__ void __launch_bounds__(256)
 allreduce_finish_kernel(const Peers P, const bf16* residual, int ldr, bf16* out,
                         int ldo, int M, int N) {
-  pdl_launch_dependents(10);
+  // a kernel that spins on peers' stores lets the next kernel in only after its last poll: an early
+  // dependent's CTAs would sit on SM slots while this grid (or a peer's) still waits for CTAs to run
+  pdl_enter(10);
   pdl_wait();
   unsigned char* me = P.ws[P.rank];
   uint32_t* ctrl = reinterpret_cast<uint32_t*>(me);
@@ -106,6 +108,7 @@ allreduce_finish_kernel(const Peers P, const bf16* residual, int ldr, bf16* out,
   }
   // the last CTA to finish advances the epoch
   __syncthreads();
+  pdl_trigger();
   if (threadIdx.x == 0) {
     __threadfence();
     const uint32_t prev = atomicAdd(ctrl + 17, 1u);
@@ -198,7 +201,7 @@ allreduce_twoshot_kernel(const Peers P, size_t off_big, size_t off_out, const bf
 __global__ void __launch_bounds__(256)
 argmax_tp_kernel(const Peers P, const float* pv, const int* pi, int chunks,
                  int v_local, int* out, int M) {
-  pdl_launch_dependents();
+  pdl_enter();
   pdl_wait();
   unsigned char* me = P.ws[P.rank];
   uint32_t* ctrl = reinterpret_cast<uint32_t*>(me);
@@ -242,6 +245,7 @@ argmax_tp_kernel(const Peers P, const float* pv, const int* pi, int chunks,
     out[row] = bi == 0x7fffffff ? 0 : bi;   // a row without any comparable logit yields token 0, never a wild index
   }
   __syncthreads();
+  pdl_trigger();
   if (threadIdx.x == 0) ctrl[48] = epoch;
 }
 

@@ -122,6 +122,9 @@ __device__ __forceinline__ void pdl_launch_dependents(int kind = 0) {
   trl_trace_begin(kind);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
+// The same in two steps, for kernels that let their dependents in later than at entry.
+__device__ __forceinline__ void pdl_enter(int kind = 0) { trl_trace_begin(kind); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---- small math --------------------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {

@@ -105,7 +105,9 @@ gemv_nvfp4_kernel(const bf16* x, int ldx, const uint8_t* __restrict__ wq,
   __half* xs = reinterpret_cast<__half*>(smem_raw);
   float* xs_inv = reinterpret_cast<float*>(smem_raw + (size_t)M * K * sizeof(__half));
   float* red = xs_inv + 8;
-  pdl_launch_dependents();
+  // a pushing kernel lets the next kernel in only after its pushes (see allreduce_finish_kernel)
+  pdl_enter();
+  if (EPI != EPI_PUSH) pdl_trigger();
   pdl_wait();
   stage_x<M>(x, ldx, K, norm_w, eps, xs, xs_inv, red);
 
@@ -240,6 +242,7 @@ gemv_nvfp4_kernel(const bf16* x, int ldx, const uint8_t* __restrict__ wq,
       }
     }
   }
+  if (EPI == EPI_PUSH) pdl_trigger();
 }
 
 // Balanced variant.  A CTA owns a contiguous block of row PAIRS and its 16 warps split that
@@ -268,7 +271,8 @@ gemv_nvfp4_sk_kernel(const bf16* x, int ldx, const uint8_t* __restrict__ wq,
   float* xs_inv = reinterpret_cast<float*>(smem_raw + (size_t)M * K * sizeof(__half));
   float* red = xs_inv + 8;
   float* slots = red + 64;   // [pairs_local][2 rows][nslot][M]
-  pdl_launch_dependents();
+  pdl_enter();
+  if (EPI != EPI_PUSH) pdl_trigger();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int npairs = N >> 1;
   const int p_lo = (int)(((long long)blockIdx.x * npairs) / gridDim.x);
@@ -414,6 +418,7 @@ gemv_nvfp4_sk_kernel(const bf16* x, int ldx, const uint8_t* __restrict__ wq,
       }
     }
   }
+  if (EPI == EPI_PUSH) pdl_trigger();
 }
 
 // bf16 weights [N, K]: fp32 FMA, 8 weights per 16-byte load.  x staged as fp32.

@@ -195,7 +195,8 @@ __device__ __forceinline__ bool g2_coop_finish(bf16* __restrict__ x, int ldx, in
         for (uint32_t it = 0; xw.y != epoch; ++it) {
           xw = ld_relaxed_sys_v2(w);
           if ((it & 15) == 15 && clock64() - t0 > G2_WAIT_CYCLES) {
-            trl_set_error(TRL_ERR_WAIT_TIMEOUT, 5, sr, (int)epoch);
+            // a = 5, b = source rank | epoch found in the slot << 8, c = epoch waited for
+            trl_set_error(TRL_ERR_WAIT_TIMEOUT, 5, sr | (int)(xw.y << 8), (int)epoch);
             ok = false;
             break;
           }
@@ -223,7 +224,8 @@ __device__ __forceinline__ bool g2_coop_finish(bf16* __restrict__ x, int ldx, in
         if (seen == epoch) break;
         __nanosleep(32);
         if ((it & 15) == 15 && clock64() - t0 > G2_WAIT_CYCLES) {
-          trl_set_error(TRL_ERR_WAIT_TIMEOUT, 6, (int)blockIdx.x, (int)epoch);
+          // a = 6, b = arrivals counted so far | CTA << 16, c = epoch waited for
+          trl_set_error(TRL_ERR_WAIT_TIMEOUT, 6, (int)(__ldcg(ctrl + G2_CTRL_ARRIVE) | (blockIdx.x << 16)), (int)epoch);
           s_flag[1] = 0;
           break;
         }
@@ -244,7 +246,7 @@ __global__ void __launch_bounds__(G2_THREADS, 3)
 gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ wst,
              const float* __restrict__ tscale, const float* __restrict__ norm_w, float eps,
              const bf16* __restrict__ residual, int ldr, void* __restrict__ yout, int ldy, int N, int K,
-             int nslot, int NS, const TrlPushArgs push) {
+             int nslot, int NS, const TrlPushArgs push, int trig) {
   constexpr int W = G2_WARPS;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   // ring [W][NS][STAGE_BYTES] | bars [W][NS] | xs [M][K] f16 | 8 spare floats | red[64] | slots
@@ -304,7 +306,12 @@ gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ ws
       if (v < (K >> 3)) asm volatile("prefetch.global.L1 [%0];" ::"l"(norm_w + (size_t)v * 8));
     }
   }
-  pdl_launch_dependents(100 + EPI * 2 + (COOP ? 1 : 0));
+  // When the next kernel may come in (trig): 0 = at entry for every kernel; 1 = a kernel with the grid
+  // barrier of the cooperative finish lets it in only behind that barrier; 2 = in addition a pushing
+  // kernel lets it in only after its pushes.
+  const bool late = (COOP && trig >= 1) || (EPI == EPI2_PUSH && trig >= 2);
+  pdl_enter(100 + EPI * 2 + (COOP ? 1 : 0));
+  if (!late) pdl_trigger();
   pdl_wait();
   // epilogue operands that do not depend on this kernel's own work: requested now, used at the end
   float res0 = 0.f;
@@ -315,6 +322,7 @@ gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ ws
   if (COOP)   // x is the residual stream: complete the pending all-reduce into it first
     g2_coop_finish(const_cast<bf16*>(x), ldx, M, K, push.ws[push.rank], push.world, push.hmax,
                    reinterpret_cast<int*>(red));
+  if (COOP && late) pdl_trigger();
   g2_stage_x<M>(x, ldx, K, norm_w, xs, red);   // ends with a block barrier
   trl_trace_mark(0);
 
@@ -521,6 +529,7 @@ gemv2_kernel(const bf16* __restrict__ x, int ldx, const uint8_t* __restrict__ ws
       }
     }
   }
+  if (EPI == EPI2_PUSH && late) pdl_trigger();
   trl_trace_end();
 }
 
@@ -677,7 +686,8 @@ gemv2_chain_kernel(const __grid_constant__ G2Chain ch, int NS, const TrlPushArgs
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     for (int s = 0; s < NS; ++s) issue();     // weights never depend on the previous kernel
   }
-  pdl_launch_dependents(120);
+  pdl_enter(120);                        // the next kernel is let in behind this launch's last grid barrier
+  if (ch.n_ops == 1 && !ch.op[0].coop) pdl_trigger();
   pdl_wait();
   if (threadIdx.x == 0) s_flag[3] = (int)__ldcg(ch.bar + G2_BAR_RELEASE);
   __syncthreads();
@@ -704,6 +714,7 @@ gemv2_chain_kernel(const __grid_constant__ G2Chain ch, int NS, const TrlPushArgs
     if (o.epi == EPI2_PUSH) push_epoch = __ldcg(reinterpret_cast<const uint32_t*>(push.ws[push.rank])) + 1;
     if (o.coop)
       ok = g2_coop_finish(const_cast<bf16*>(o.x), o.ldx, M, K, push.ws[push.rank], push.world, push.hmax, s_flag) && ok;
+    if (j == ch.n_ops - 1 && (ch.n_ops > 1 || o.coop)) pdl_trigger();
     g2_stage_x<M>(o.x, o.ldx, K, o.norm_w, xs, red);   // ends with a block barrier
     trl_trace_mark(3 * j + 1);
 
@@ -904,6 +915,12 @@ gemv2_chain_kernel(const __grid_constant__ G2Chain ch, int NS, const TrlPushArgs
   trl_trace_end();
 }
 
+int g_g2_trigger = -1;
+int g2_trigger_mode() {
+  if (g_g2_trigger < 0) g_g2_trigger = getenv("TRL_TP_TRIGGER") ? atoi(getenv("TRL_TP_TRIGGER")) : 2;
+  return g_g2_trigger;
+}
+
 int g2_num_sms() {
   static int sms = 0;
   if (sms == 0) {
@@ -951,9 +968,9 @@ cudaError_t launch_gemv2(const bf16* x, int ldx, const uint8_t* wst, const float
   }
   if ((K % 1024) == 0)   // every step of a row is full: 32 chunks
     return trl_launch(gemv2_kernel<M, EPI, true, COOP>, dim3(grid), dim3(G2_THREADS), smem, st, x, ldx, wst, ts,
-                      norm_w, eps, res, ldr, y, ldy, N, K, nslot, ns, push);
+                      norm_w, eps, res, ldr, y, ldy, N, K, nslot, ns, push, g2_trigger_mode());
   return trl_launch(gemv2_kernel<M, EPI, false, COOP>, dim3(grid), dim3(G2_THREADS), smem, st, x, ldx, wst, ts,
-                    norm_w, eps, res, ldr, y, ldy, N, K, nslot, ns, push);
+                    norm_w, eps, res, ldr, y, ldy, N, K, nslot, ns, push, g2_trigger_mode());
 }
 
 template <int EPI, bool COOP = false>
@@ -1098,3 +1115,6 @@ TRL_API int trl_gemv2_chain(const void* ops, int n_ops, int M, void* bar, void* 
   if (M == 1) return (int)launch_chain<1>(a, n_ops, (uint32_t*)bar, push, (cudaStream_t)stream);
   return (int)launch_chain<2>(a, n_ops, (uint32_t*)bar, push, (cudaStream_t)stream);
 }
+
+// When tensor-parallel projections let the next kernel in (see gemv2_kernel): 0, 1 or 2; -1 = the environment's choice.
+TRL_API void trl_gemv2_set_trigger(int mode) { g_g2_trigger = mode; }

@@ -219,9 +219,36 @@ def _ops_worker(rank, world, port, out):
                 results[(t, fused)] = (float((x.float().cpu() - want_x.float()).abs().max()),
                                        float((y.float() - want_y.float()).norm() / want_y.float().norm()),
                                        x.clone().cpu(), y.cpu())
+        # the same pair back to back inside one CUDA graph, no host synchronisation in between: the
+        # launches overlap as far as the kernels admit their successors, and every rank must still get
+        # every CTA of every launch onto an SM (a pushing kernel lets the next one in only after its
+        # pushes, the consumer only behind its grid barrier).  A stall shows as a wait that runs out.
+        comm.fuse_finish = True
+        x = ops.ws.get("x", (1, h), torch.bfloat16)
+        x.zero_()
+        a1 = (torch.randn(1, ks, generator=g) * 0.01).to(torch.bfloat16).to(dev)
+        torch.cuda.synchronize()
+        dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(16):
+                    ops.linear_residual(a1, wq_row, x)
+                    ops.norm_linear(x, nw, wq_col, 1e-6)
+                    ops.settle()
+        import time
+        torch.cuda.synchronize()
+        dist.barrier()
+        t_begin = time.time()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        replay_s = time.time() - t_begin
         err = native.read_error()
         if rank == 0:
-            out.put(dict(err=err, res={k: v[:2] for k, v in results.items()},
+            out.put(dict(err=err, replay_s=replay_s, res={k: v[:2] for k, v in results.items()},
                          same={t: bool(torch.equal(results[(t, True)][2], results[(t, False)][2]) and
                                        torch.equal(results[(t, True)][3], results[(t, False)][3])) for t in (1, 2)}))
         dist.barrier()
@@ -255,6 +282,7 @@ def test_tp_row_parallel_gemv_with_allreduce_finished_by_its_consumer(world):
         p.join(timeout=120)
         assert p.exitcode == 0
     assert res["err"][0] == 0, res["err"]
+    assert res["replay_s"] < 0.5, res["replay_s"]      # 48 pairs of ~30 us; a bounded wait that runs out takes 2 s
     for (t, fused), (dx, ry) in res["res"].items():
         assert dx <= 0.0625, (t, fused, dx)        # one bf16 step of the residual stream's magnitude
         assert ry < 8e-3, (t, fused, ry)

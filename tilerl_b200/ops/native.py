@@ -50,6 +50,7 @@ _SIGS = {
     "trl_batch_ints": [c_longlong, I, I],
     "trl_batch_fill": [I, P, P, P, P, P, P, P, I, I, P, c_longlong],
     "trl_gemm_trace_read": [P, I],
+    "trl_gemv2_set_trigger": [I],
     "trl_gdn_set_wy": [I],
     "trl_gdn_set_mma": [I],
     "trl_sample_nucleus": [P, I, P, P, P, P, P, P, P, I, I, P],
@@ -68,7 +69,7 @@ _SIGS = {
 }
 
 
-_RESTYPE = {"trl_set_pdl": None, "trl_gdn_set_wy": None, "trl_gdn_set_mma": None, "trl_pager_create": c_void_p, "trl_pager_destroy": None,
+_RESTYPE = {"trl_set_pdl": None, "trl_gdn_set_wy": None, "trl_gemv2_set_trigger": None, "trl_gdn_set_mma": None, "trl_pager_create": c_void_p, "trl_pager_destroy": None,
             "trl_batch_ints": c_longlong, "trl_batch_fill": c_longlong}
 
 
