@@ -597,7 +597,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
 // encoded (worst gap 4..6 of 6 plus the e4m3 scale rounding) -- so no second pass over
 // the row is needed.
 __global__ void __launch_bounds__(256)
-quant_act_3pass_kernel(const bf16* x, int ldx, const float* __restrict__ norm_w, float eps,
+quant_act_kernel(const bf16* x, int ldx, const float* __restrict__ norm_w, float eps,
                  uint8_t* xq, uint8_t* sf, float* rs, int K, int J,
                  int kt4, int swiglu_in) {
   __shared__ float red[32];
@@ -702,108 +702,6 @@ quant_act_3pass_kernel(const bf16* x, int ldx, const float* __restrict__ norm_w,
   }
 }
 
-// The same quantiser with the row held in registers: one pass of loads, then the norm statistics,
-// the row maximum and the encoding all work on the thread's own groups (K <= 18432: up to 18 groups
-// of four elements per thread).  The three-pass form above serves longer rows.
-constexpr int QA_GROUPS = 18;
-__global__ void __launch_bounds__(256)
-quant_act_kernel(const bf16* x, int ldx, const float* __restrict__ norm_w, float eps,
-                 uint8_t* xq, uint8_t* sf, float* rs, int K, int J,
-                 int kt4, int swiglu_in) {
-  __shared__ float red[32];
-  pdl_launch_dependents();
-  pdl_wait();
-  const int tok = blockIdx.x;
-  const bf16* xr = x + (size_t)tok * ldx;
-  float v[QA_GROUPS][4];
-#pragma unroll
-  for (int i = 0; i < QA_GROUPS; ++i) {
-    const int k = (i * 256 + (int)threadIdx.x) * 4;
-    v[i][0] = v[i][1] = v[i][2] = v[i][3] = 0.f;
-    if (k < K) {
-      if (swiglu_in) {  // interleaved (gate, up) pairs: K outputs from 2K inputs
-        const uint4 u = *reinterpret_cast<const uint4*>(xr + 2 * k);
-        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 gu = bf162_bits_to_f2(w[e]);
-          v[i][e] = __bfloat162float(__float2bfloat16(silu_f(gu.x) * gu.y));
-        }
-      } else {
-        const uint2 u = *reinterpret_cast<const uint2*>(xr + k);
-        const float2 a = bf162_bits_to_f2(u.x), b = bf162_bits_to_f2(u.y);
-        v[i][0] = a.x, v[i][1] = a.y, v[i][2] = b.x, v[i][3] = b.y;
-      }
-    }
-  }
-  if (norm_w != nullptr) {
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < QA_GROUPS; ++i) ss += v[i][0] * v[i][0] + v[i][1] * v[i][1] + v[i][2] * v[i][2] + v[i][3] * v[i][3];
-    ss = block_sum(ss, red);
-    const float rstd = rsqrtf(ss / (float)K + eps);
-#pragma unroll
-    for (int i = 0; i < QA_GROUPS; ++i) {
-      const int k = (i * 256 + (int)threadIdx.x) * 4;
-      if (k < K) {
-        const float4 w = *reinterpret_cast<const float4*>(norm_w + k);
-        v[i][0] = __bfloat162float(__float2bfloat16(v[i][0] * rstd * w.x));
-        v[i][1] = __bfloat162float(__float2bfloat16(v[i][1] * rstd * w.y));
-        v[i][2] = __bfloat162float(__float2bfloat16(v[i][2] * rstd * w.z));
-        v[i][3] = __bfloat162float(__float2bfloat16(v[i][3] * rstd * w.w));
-      }
-    }
-  }
-  float amax = 0.f;
-#pragma unroll
-  for (int i = 0; i < QA_GROUPS; ++i)
-    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i][0]), fabsf(v[i][1])), fmaxf(fabsf(v[i][2]), fabsf(v[i][3]))));
-  amax = block_max(amax, red);
-  const float rs0 = fmaxf(amax, 1e-30f) * (1.f / (6.f * 448.f));
-  if (blockIdx.y == 0 && threadIdx.x < J) rs[tok * J + threadIdx.x] = rs0 * exp2f(-2.f * (float)threadIdx.x);
-  const int n_slices = (kt4 * 16 + 255) / 256;       // groups of 256 four-element groups, K padding included
-  int mine = (int)blockIdx.y;                         // slices blockIdx.y, blockIdx.y + gridDim.y, ...
-#pragma unroll
-  for (int sl = 0; sl < QA_GROUPS; ++sl) {
-    if (sl != mine || sl >= n_slices) continue;
-    mine += (int)gridDim.y;
-    const int q4 = sl * 256 + (int)threadIdx.x;        // index of the 4-element group
-    const int k = q4 * 4;
-    const int b = q4 >> 2;                             // 16-element block
-    const bool valid = b < kt4 * 4;                    // whole 4-lane groups are valid or not
-    float r[4] = {v[sl][0], v[sl][1], v[sl][2], v[sl][3]};
-    float rscale = rs0;
-    for (int j = 0; j < J; ++j, rscale *= 0.25f) {
-      const int col = tok * J + j;
-      float bm = fmaxf(fmaxf(fabsf(r[0]), fabsf(r[1])), fmaxf(fabsf(r[2]), fabsf(r[3])));
-      bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
-      bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
-      const float s = fminf(__fdividef(bm, 6.f * rscale), 448.f);
-      uint16_t s16;
-      asm("{ .reg .b16 t; cvt.rn.satfinite.e4m3x2.f32 t, %1, %2; mov.b16 %0, t; }" : "=h"(s16) : "f"(0.f), "f"(s));
-      const float sfv = h2_to_f2(cvt_e4m3x2_to_h2(s16)).x;
-      const float denom = sfv * rscale;
-      const float inv = denom > 0.f ? __frcp_rn(denom) : 0.f;
-      uint16_t lo, hi;
-      asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u16.u8 %0, t; }" : "=h"(lo) : "f"(r[1] * inv), "f"(r[0] * inv));
-      asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u16.u8 %0, t; }" : "=h"(hi) : "f"(r[3] * inv), "f"(r[2] * inv));
-      uint32_t h0, h1;
-      asm("{ .reg .b8 t; cvt.u8.u16 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(h0) : "h"(lo));
-      asm("{ .reg .b8 t; cvt.u8.u16 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(h1) : "h"(hi));
-      const float2 d0 = h2_to_f2(h0), d1 = h2_to_f2(h1);
-      r[0] = fmaf(-d0.x, denom, r[0]);   // the next term encodes the remainder
-      r[1] = fmaf(-d0.y, denom, r[1]);
-      r[2] = fmaf(-d1.x, denom, r[2]);
-      r[3] = fmaf(-d1.y, denom, r[3]);
-      if (k < K)
-        reinterpret_cast<uint16_t*>(xq + (size_t)col * (K >> 1))[q4] = (uint16_t)((lo & 0xff) | ((hi & 0xff) << 8));
-      if (valid && (threadIdx.x & 3) == 0)  // scale byte (zero for the K padding)
-        sf[((size_t)(col >> 7) * kt4 + (b >> 2)) * SF_ATOM + (col & 31) * 16 + ((col & 127) >> 5) * 4 + (b & 3)] =
-            (k < K) ? (uint8_t)(s16 & 0xff) : (uint8_t)0;
-    }
-  }
-}
-
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -859,10 +757,6 @@ TRL_API int trl_quant_act_nvfp4(const void* x, int ldx, const void* norm_w, floa
   const int nk = (K + KT_ELEMS - 1) / KT_ELEMS;
   int slices = (nk * KT_ELEMS / 4 + 255) / 256;  // 4 elements per thread
   if (tokens >= 128) slices = 1;                        // enough rows to fill the GPU: one CTA per row
-  if (nk * 4 * 16 > QA_GROUPS * 256)   // rows longer than the register-resident form holds
-    return (int)trl_launch(quant_act_3pass_kernel, dim3(tokens, slices), dim3(256), 0, (cudaStream_t)stream, (const bf16*)x,
-                         ldx, (const float*)norm_w, eps, (uint8_t*)xq, (uint8_t*)sf, (float*)rs, K, J, nk * 4,
-                         swiglu_in);
   return (int)trl_launch(quant_act_kernel, dim3(tokens, slices), dim3(256), 0, (cudaStream_t)stream, (const bf16*)x,
                          ldx, (const float*)norm_w, eps, (uint8_t*)xq, (uint8_t*)sf, (float*)rs, K, J, nk * 4,
                          swiglu_in);
