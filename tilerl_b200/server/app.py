@@ -30,7 +30,7 @@ from . import prompt as P
 from .pacing import Pacer
 
 CHAT_FIELDS = {
-    "model", "messages", "max_tokens", "max_completion_tokens", "temperature", "top_p", "seed", "stop",
+    "model", "messages", "max_tokens", "max_completion_tokens", "temperature", "top_p", "top_k", "seed", "stop",
     "stream", "stream_options", "logprobs", "top_logprobs", "tools", "tool_choice", "reasoning_effort",
     "chat_template_kwargs", "enable_thinking", "n", "user", "metadata", "presence_penalty",
     "frequency_penalty", "response_format", "parallel_tool_calls", "store",

@@ -128,11 +128,19 @@ def render_chat(messages: List[Dict[str, Any]], *, tools=None, enable_thinking: 
 
 
 def sampling(body: Dict[str, Any], thinking: bool) -> Dict[str, Any]:
-    """Request fields over model-card defaults; top_k only from the defaults."""
+    """Request fields over model-card defaults (``top_k`` is an extension the web client sends;
+    0 switches the restriction off)."""
     d = dict(SAMPLING[bool(thinking)])
     for k in ("temperature", "top_p"):
         if body.get(k) is not None:
             d[k] = float(body[k])
+    if body.get("top_k") is not None:
+        try:
+            d["top_k"] = int(body["top_k"])
+        except (TypeError, ValueError):
+            raise BadRequest("top_k must be an integer", "top_k") from None
+        if d["top_k"] < 0:
+            raise BadRequest("top_k must be >= 0", "top_k")
     if not 0.0 <= d["temperature"] <= 2.0:
         raise BadRequest("temperature must be in [0, 2]", "temperature")
     if not 0.0 < d["top_p"] <= 1.0:

@@ -1,5 +1,6 @@
-// Smooths bursty deltas into a steady reveal: text is queued and released at a rate that adapts
-// to the backlog (never more than `maxLagMs` behind), on animation frames.
+// Smooths bursty deltas into a steady reveal: text is queued and released on animation frames at a
+// rate that adapts to the backlog (per frame at least backlog * dt / maxLagMs characters, so a burst
+// shrinks by a factor e every `maxLagMs`; never slower than `baseCps`).
 export class StreamBuffer {
   constructor(onText, {baseCps = 400, maxLagMs = 250, now = () => performance.now(),
                        raf = (cb) => requestAnimationFrame(cb)} = {}) {
