@@ -16,6 +16,11 @@
 // Pool layout: [blocks, hkv, 16, D] bf16 per layer; block_table [B, max_blocks].
 // Reference parity: kernels_mma.py:168-366 (attn_prep), kernels_attn.py:151-334
 // (split decode + combine) of packages/tilerl-kernels/src/tilerl_kernels.
+#include <cuda.h>
+
+#include <mutex>
+#include <vector>
+
 #include "common.cuh"
 
 namespace {
@@ -540,23 +545,76 @@ attn_prefill_kernel(const bf16* q, const bf16* gate_src, int gate_ld,
 // softmax state, and the four warps are merged through shared memory at the end.  Output:
 // the same split partials (unnormalised row, running max in the exp2 domain, denominator) the
 // combine kernel reads, or the finished gated row when there is one split.
-constexpr int DM_KEYS = 64, DM_WARPS = 4, DM_ROWS = 16;
-constexpr int DM_SMEM = DM_ROWS * PF_ROW + 4 * DM_KEYS * PF_ROW;     // Q tile + K, V double buffered
+constexpr int DM_KEYS = 64, DM_WARPS = 4, DM_ROWS = 16, DM_STAGES = 3, DM_TAB = 512;
+constexpr int DM_RS = PF_ROW + 16;                 // Q row stride in shared memory: 512 B of data + 16 B, so that the
+                                                   // eight rows of an ldmatrix fall into different banks without a swizzle
+constexpr int DM_QBYTES = 9216;                    // 16 Q rows (8448 B) rounded up to the 1024-byte alignment of the stages
+constexpr int DM_PAGE = KVB * PF_ROW;              // one page of one kv head: 16 keys x 512 B, contiguous in the pool
+constexpr int DM_SLAB = KVB * 128;                 // 128-byte column slab of a page: the unit of the 128-byte swizzle
+constexpr int DM_TILE = (DM_KEYS / KVB) * DM_PAGE;
+constexpr int DM_SMEM = 1024 + DM_QBYTES + 2 * DM_STAGES * DM_TILE + 64;    // alignment slack, Q tile, K and V rings, barriers
+constexpr long long DM_WAIT_CYCLES = 4000000000LL;
+static_assert(DM_WARPS * 16 == DM_KEYS && KVB == 16, "a consumer warp owns one page of every tile");
 
-__global__ void __launch_bounds__(DM_WARPS * 32)
-attn_decode_mma_kernel(const bf16* q, const bf16* gate_src, int gate_ld, const bf16* kcache, const bf16* vcache,
+__device__ __forceinline__ uint32_t dm_off(int r, int c) { return (uint32_t)(r * DM_RS + c * 16); }
+// 16-byte chunk c (0..31) of key `key` (0..63) of a stage.  A page arrives as four slabs [16 keys][128 B] under the
+// tensor map's 128-byte swizzle: within a slab the chunk index is XORed with the key's low three bits.
+__device__ __forceinline__ uint32_t dm_kv_off(int key, int c) {
+  const int r = key & 15;
+  return (uint32_t)((key >> 4) * DM_PAGE + (c >> 3) * DM_SLAB + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+}
+__device__ __forceinline__ uint32_t dm_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{ .reg .pred p;\n"
+      "  mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "  selp.u32 %0, 1, 0, p; }\n"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok;
+}
+
+// Warps 0-3 compute, warp 4 produces.  The pool is described to the copy engine as a tensor
+// {64 elements, rows of 512 B, 4 column slabs of 128 B}: ONE tiled copy brings a whole page of a kv head
+// (16 keys, 8 KB) as four swizzled slabs, so a 64-key tile is eight copies (K and V of four pages)
+// into a three-stage ring.  A stage's "full" mbarrier counts the bytes, its "empty" mbarrier the four
+// consumer warps.  The block-table entries of the CTA's key range are read into shared memory once,
+// so no global load sits in the loop.  map3d == 0: the same layout from 2-D copies, one per slab.
+__global__ void __launch_bounds__((DM_WARPS + 1) * 32)
+attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, int map3d,
+                       const bf16* q, const bf16* gate_src, int gate_ld,
                        const int* block_table, int max_blocks, const int* seq_ids, const int* positions,
                        float* po, float* pm, float* pl, bf16* out, int T, int n_q, int n_kv, int n_splits,
                        int tpg, float scale_log2e, int gated) {
-  extern __shared__ __align__(1024) unsigned char dm_smem[];
+  extern __shared__ unsigned char dm_smem_raw[];
   __shared__ float s_m[DM_WARPS][DM_ROWS], s_l[DM_WARPS][DM_ROWS];
+  __shared__ int s_tab[DM_TAB];
+  __shared__ volatile int s_ok;
+  const int split = blockIdx.x, kvh = blockIdx.y, t0 = blockIdx.z * tpg;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t raw_a = (uint32_t)__cvta_generic_to_shared(dm_smem_raw);
+  unsigned char* dm_smem = dm_smem_raw + (((raw_a + 1023u) & ~1023u) - raw_a);
+  unsigned char* qs = dm_smem;                               // [16][528 B]
+  unsigned char* ks = dm_smem + DM_QBYTES;                   // [stages][4 pages][4 slabs][16 keys][128 B]
+  unsigned char* vs = ks + DM_STAGES * DM_TILE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(vs + DM_STAGES * DM_TILE);   // full[stages], empty[stages]
+  const uint32_t qs_a = (uint32_t)__cvta_generic_to_shared(qs);
+  const uint32_t ks_a = (uint32_t)__cvta_generic_to_shared(ks), vs_a = (uint32_t)__cvta_generic_to_shared(vs);
+  const uint32_t bar_a = (uint32_t)__cvta_generic_to_shared(bars);
+  auto full = [&](int st) { return bar_a + 8u * st; };
+  auto empty = [&](int st) { return bar_a + 8u * (DM_STAGES + st); };
+  if (threadIdx.x == 0) {
+    for (int st = 0; st < DM_STAGES; ++st) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(full(st)));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty(st)), "r"(DM_WARPS));
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    s_ok = 1;
+  }
   pdl_launch_dependents(4);
   pdl_wait();
-  const int split = blockIdx.x, kvh = blockIdx.y, t0 = blockIdx.z * tpg;
   const int G = n_q / n_kv;
   const int nt = min(tpg, T - t0);
   const int rows = nt * G;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   int kv_len = 0;                                           // keys the group's furthest row sees (rows of a
   for (int i = 0; i < nt; ++i) kv_len = max(kv_len, positions[t0 + i] + 1);   // padded window need not ascend)
   const int* table = block_table + (size_t)seq_ids[t0] * max_blocks;
@@ -564,38 +622,62 @@ attn_decode_mma_kernel(const bf16* q, const bf16* gate_src, int gate_ld, const b
   const int pps = (pages + n_splits - 1) / n_splits;
   const int lo = split * pps * KVB, hi = min(kv_len, (split + 1) * pps * KVB);
   const int n_tiles = hi > lo ? (hi - lo + DM_KEYS - 1) / DM_KEYS : 0;
-
-  unsigned char* qs = dm_smem;                               // [16][512 B]
-  unsigned char* ks = dm_smem + DM_ROWS * PF_ROW;            // [2][64][512 B]
-  unsigned char* vs = ks + 2 * DM_KEYS * PF_ROW;             // [2][64][512 B]
-  const uint32_t qs_a = (uint32_t)__cvta_generic_to_shared(qs);
-  const uint32_t ks_a = (uint32_t)__cvta_generic_to_shared(ks), vs_a = (uint32_t)__cvta_generic_to_shared(vs);
+  const int page0 = lo / KVB, n_pages = hi > lo ? (hi - lo + KVB - 1) / KVB : 0;
+  const bool tab_cached = n_pages <= DM_TAB;
+  if (tab_cached)
+    for (int i = threadIdx.x; i < n_pages; i += blockDim.x) s_tab[i] = table[page0 + i];
 
   // row r of the tile = (token r / G of the group, head r % G of the kv head); unused rows are zero
   for (int x = threadIdx.x; x < DM_ROWS * PF_CHUNKS; x += blockDim.x) {
     const int r = x / PF_CHUNKS, c = x % PF_CHUNKS;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (r < rows) v = *reinterpret_cast<const uint4*>(q + ((size_t)(t0 + r / G) * n_q + kvh * G + r % G) * PF_D + c * 8);
-    *reinterpret_cast<uint4*>(qs + pf_off(r, c)) = v;
+    *reinterpret_cast<uint4*>(qs + dm_off(r, c)) = v;
   }
-  auto load_kv = [&](int kt, int buf) {
-    const int j0 = lo + kt * DM_KEYS;
-    for (int x = threadIdx.x; x < DM_KEYS * PF_CHUNKS; x += blockDim.x) {
-      const int r = x / PF_CHUNKS, c = x % PF_CHUNKS;      // a warp covers one 512-byte row
-      const int j = j0 + r;
-      const uint32_t dk = ks_a + buf * DM_KEYS * PF_ROW + pf_off(r, c);
-      const uint32_t dv = vs_a + buf * DM_KEYS * PF_ROW + pf_off(r, c);
-      if (j < hi) {
-        const size_t off = (((size_t)table[j / KVB] * n_kv + kvh) * KVB + (j % KVB)) * PF_D + c * 8;
-        cp16(dk, kcache + off);
-        cp16(dv, vcache + off);
-      } else {                      // past the range: zeros (masked below, but must not be NaN)
-        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(dk), "r"(0u) : "memory");
-        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(dv), "r"(0u) : "memory");
+  __syncthreads();                                 // barriers initialised, table and Q rows in place
+  auto bounded_wait = [&](uint32_t bar, uint32_t parity, int what) {
+    if (dm_try_wait(bar, parity)) return true;
+    const long long t_begin = clock64();
+    for (uint32_t it = 1; !dm_try_wait(bar, parity); ++it) {
+      if ((it & 63) == 0) {
+        if (!s_ok) return false;
+        if (clock64() - t_begin > DM_WAIT_CYCLES) {
+          trl_set_error(TRL_ERR_MBAR_TIMEOUT, (int)blockIdx.x, what, (int)parity);
+          s_ok = 0;
+          return false;
+        }
       }
     }
-    asm volatile("cp.async.commit_group;" ::: "memory");
+    return true;
   };
+
+  if (warp == DM_WARPS) {
+    // ---------------- producer ----------------
+    for (int kt = 0; kt < n_tiles; ++kt) {
+      const int st = kt % DM_STAGES;
+      if (kt >= DM_STAGES && !bounded_wait(empty(st), (uint32_t)(kt / DM_STAGES - 1) & 1u, 410 + st)) break;
+      const int j0 = lo + kt * DM_KEYS;
+      const int n_pg = min(DM_KEYS / KVB, (hi - j0 + KVB - 1) / KVB);     // whole pages: keys past `hi` are masked
+      if (lane == 0)
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full(st)), "r"((uint32_t)(n_pg * 2 * DM_PAGE)) : "memory");
+      __syncwarp();
+      // lane -> (K or V, page of the tile, slab); with the 3-D map the lanes of slab 0 copy the whole page
+      const int is_v = lane >> 4, pg = (lane >> 2) & 3, sl = lane & 3;
+      if (pg < n_pg && (!map3d || sl == 0)) {
+        const int pi = j0 / KVB + pg;
+        const int blk = tab_cached ? s_tab[pi - page0] : table[pi];
+        const int y = (blk * n_kv + kvh) * KVB;
+        const uint32_t dst = (is_v ? vs_a : ks_a) + st * DM_TILE + pg * DM_PAGE + sl * DM_SLAB;
+        const CUtensorMap* mp = is_v ? &map_v : &map_k;
+        if (map3d)
+          asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                       ::"r"(dst), "l"(mp), "r"(0), "r"(y), "r"(0), "r"(full(st)) : "memory");
+        else
+          asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                       ::"r"(dst), "l"(mp), "r"(sl * 64), "r"(y), "r"(full(st)) : "memory");
+      }
+    }
+  }
 
   const int r_lo = lane >> 2;                      // fragment rows r_lo and r_lo + 8
   const int pos_lo = r_lo < rows ? positions[t0 + r_lo / G] : -1;
@@ -605,19 +687,21 @@ attn_decode_mma_kernel(const bf16* q, const bf16* gate_src, int gate_ld, const b
   for (int i = 0; i < PF_D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
 
-  if (n_tiles > 0) load_kv(0, 0);
-  for (int kt = 0; kt < n_tiles; ++kt) {
-    const int buf = kt & 1;
-    if (kt + 1 < n_tiles) {
-      load_kv(kt + 1, buf ^ 1);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
-    __syncthreads();
+  for (int kt = 0; kt < n_tiles && warp < DM_WARPS; ++kt) {
+    const int buf = kt % DM_STAGES;
+    if (!bounded_wait(full(buf), (uint32_t)(kt / DM_STAGES) & 1u, 400 + buf)) break;
     const int jw = lo + kt * DM_KEYS + warp * 16;     // this warp's first key of the tile
-    if (jw < hi) {
-      const uint32_t kb = ks_a + buf * DM_KEYS * PF_ROW, vb = vs_a + buf * DM_KEYS * PF_ROW;
+    if (jw < hi && s_ok) {
+      const uint32_t kb = ks_a + buf * DM_TILE, vb = vs_a + buf * DM_TILE;
+      if (jw + 16 > hi) {
+        // the page's keys past the range hold whatever the pool holds: their scores are masked by a
+        // select, but 0 x V must be 0, so their V rows are cleared (only this warp reads them)
+        for (int x = lane; x < (jw + 16 - hi) * PF_CHUNKS; x += 32) {
+          const int key = warp * 16 + (hi - jw) + x / PF_CHUNKS;
+          asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(vb + dm_kv_off(key, x % PF_CHUNKS)), "r"(0u) : "memory");
+        }
+        __syncwarp();
+      }
       // ---- S = Q K^T for this warp's 16 keys: two n-tiles of 8
       float sc[2][4];
 #pragma unroll
@@ -625,8 +709,8 @@ attn_decode_mma_kernel(const bf16* q, const bf16* gate_src, int gate_ld, const b
 #pragma unroll
       for (int kk = 0; kk < PF_D / 16; ++kk) {
         uint32_t a[4], b[4];
-        ldsm_x4(a, qs_a + pf_off((lane & 7) + ((lane >> 3) & 1) * 8, kk * 2 + (lane >> 4)));
-        ldsm_x4(b, kb + pf_off(warp * 16 + (lane & 7) + (lane >> 4) * 8, kk * 2 + ((lane >> 3) & 1)));
+        ldsm_x4(a, qs_a + dm_off((lane & 7) + ((lane >> 3) & 1) * 8, kk * 2 + (lane >> 4)));
+        ldsm_x4(b, kb + dm_kv_off(warp * 16 + (lane & 7) + (lane >> 4) * 8, kk * 2 + ((lane >> 3) & 1)));
         mma_bf16(sc[0], a, b[0], b[1]);
         mma_bf16(sc[1], a, b[2], b[3]);
       }
@@ -672,25 +756,34 @@ attn_decode_mma_kernel(const bf16* q, const bf16* gate_src, int gate_ld, const b
 #pragma unroll
       for (int nd = 0; nd < PF_D / 8; nd += 2) {
         uint32_t b[4];
-        ldsm_x4_t(b, vb + pf_off(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, nd + (lane >> 4)));
+        ldsm_x4_t(b, vb + dm_kv_off(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, nd + (lane >> 4)));
         mma_bf16(o[nd], pa, b[0], b[1]);
         mma_bf16(o[nd + 1], pa, b[2], b[3]);
       }
     }
-    __syncthreads();                               // the other buffer may be overwritten next round
+    __syncwarp();
+    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty(buf)) : "memory");   // this warp is done with the stage
+  }
+  __syncthreads();                                 // every warp is out of its loop: the K ring becomes the merge buffer
+  if (!s_ok) {                                     // copies may still be in flight towards this CTA's shared memory
+    const long long t_begin = clock64();
+    while (clock64() - t_begin < 2000000LL) {
+    }
   }
 
   // ---- merge the four warps (each saw different keys) through shared memory
-  float* so = reinterpret_cast<float*>(ks);        // [4 warps][16 rows][256] fp32 = the K buffers
-  if ((lane & 3) == 0) {
-    s_m[warp][r_lo] = m_lo, s_m[warp][r_lo + 8] = m_hi;
-    s_l[warp][r_lo] = l_lo, s_l[warp][r_lo + 8] = l_hi;
-  }
+  float* so = reinterpret_cast<float*>(ks);        // [4 warps][16 rows][256] fp32, inside the K buffers
+  if (warp < DM_WARPS) {
+    if ((lane & 3) == 0) {
+      s_m[warp][r_lo] = m_lo, s_m[warp][r_lo + 8] = m_hi;
+      s_l[warp][r_lo] = l_lo, s_l[warp][r_lo + 8] = l_hi;
+    }
 #pragma unroll
-  for (int nd = 0; nd < PF_D / 8; ++nd) {
-    const int d = nd * 8 + (lane & 3) * 2;
-    *reinterpret_cast<float2*>(so + ((size_t)warp * DM_ROWS + r_lo) * PF_D + d) = make_float2(o[nd][0], o[nd][1]);
-    *reinterpret_cast<float2*>(so + ((size_t)warp * DM_ROWS + r_lo + 8) * PF_D + d) = make_float2(o[nd][2], o[nd][3]);
+    for (int nd = 0; nd < PF_D / 8; ++nd) {
+      const int d = nd * 8 + (lane & 3) * 2;
+      *reinterpret_cast<float2*>(so + ((size_t)warp * DM_ROWS + r_lo) * PF_D + d) = make_float2(o[nd][0], o[nd][1]);
+      *reinterpret_cast<float2*>(so + ((size_t)warp * DM_ROWS + r_lo + 8) * PF_D + d) = make_float2(o[nd][2], o[nd][3]);
+    }
   }
   __syncthreads();
   for (int idx = threadIdx.x; idx < rows * PF_D; idx += blockDim.x) {
@@ -767,16 +860,85 @@ TRL_API int trl_attn_paged(const void* q, const void* gate_src, int gate_ld, con
   return (int)e;
 }
 
+namespace {
+
+// Tensor maps of a layer's K and V pools for attn_decode_mma_kernel, cached by (pointers, blocks, heads).
+// Preferred form: {64 elements, rows (512 B apart), 4 column slabs (128 B apart)} with a box of a whole
+// page {64, 16, 4} under the 128-byte swizzle; if the driver refuses that encoding, a 2-D map
+// {256 elements, rows} with a box of one slab {64, 16}.
+struct DmMaps {
+  const void *k, *v;
+  int n_blocks, n_kv, mode3d;
+  CUtensorMap mk, mv;
+};
+typedef CUresult (*DmEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+std::mutex g_dm_mu;
+std::vector<DmMaps> g_dm_maps;
+DmEncodeFn g_dm_encode = nullptr;
+
+int dm_encode(CUtensorMap* m, const void* base, uint64_t rows, int mode3d) {
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r;
+  if (mode3d) {
+    const cuuint64_t dims[3] = {64, rows, 4};
+    const cuuint64_t strides[2] = {(cuuint64_t)PF_ROW, 128};
+    const cuuint32_t box[3] = {64, (cuuint32_t)KVB, 4};
+    r = g_dm_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    const cuuint64_t dims[2] = {(cuuint64_t)PF_D, rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)PF_ROW};
+    const cuuint32_t box[2] = {64, (cuuint32_t)KVB};
+    r = g_dm_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
+  return r == CUDA_SUCCESS ? 0 : 1;
+}
+
+// 0 on success; fills `out`.  force2d: environment TRL_ATTN_MAP2D=1 selects the per-slab form.
+int dm_get_maps(const void* k, const void* v, int n_blocks, int n_kv, DmMaps* out) {
+  std::lock_guard<std::mutex> lock(g_dm_mu);
+  for (const DmMaps& e : g_dm_maps)
+    if (e.k == k && e.v == v && e.n_blocks == n_blocks && e.n_kv == n_kv) {
+      *out = e;
+      return 0;
+    }
+  if (!g_dm_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) return 1;
+    g_dm_encode = (DmEncodeFn)fn;
+  }
+  static const bool force2d = [] { const char* e = getenv("TRL_ATTN_MAP2D"); return e && e[0] == '1'; }();
+  DmMaps m;
+  m.k = k, m.v = v, m.n_blocks = n_blocks, m.n_kv = n_kv;
+  const uint64_t rows = (uint64_t)n_blocks * n_kv * KVB;
+  m.mode3d = force2d ? 0 : 1;
+  if (m.mode3d && (dm_encode(&m.mk, k, rows, 1) || dm_encode(&m.mv, v, rows, 1))) m.mode3d = 0;
+  if (!m.mode3d && (dm_encode(&m.mk, k, rows, 0) || dm_encode(&m.mv, v, rows, 0))) return 2;
+  if (g_dm_maps.size() >= 1024) g_dm_maps.erase(g_dm_maps.begin(), g_dm_maps.begin() + 512);
+  g_dm_maps.push_back(m);
+  *out = m;
+  return 0;
+}
+
+}  // namespace
+
 // Tensor-core variant of trl_attn_paged for the bf16 pool (D = 256): `tpg` consecutive tokens of the
 // batch that belong to one sequence (1 for decode; a divisor of the verify width) share a CTA, with
-// tpg * (n_q / n_kv) <= 16 rows.  Same scratch and combine as trl_attn_paged.
+// tpg * (n_q / n_kv) <= 16 rows.  Same scratch and combine as trl_attn_paged.  The pools are
+// [n_blocks, n_kv, 16, D] bf16 at 16-byte aligned addresses.
 TRL_API int trl_attn_decode_mma(const void* q, const void* gate_src, int gate_ld, const void* kcache,
-                                const void* vcache, const void* block_table, int max_blocks,
+                                const void* vcache, const void* block_table, int max_blocks, int n_blocks,
                                 const void* seq_ids, const void* positions, void* po, void* pm, void* pl,
                                 void* out, int T, int n_q, int n_kv, int D, int n_splits, int tpg, float scale,
                                 int gated, void* stream) {
   if (D != PF_D || n_kv <= 0 || n_q <= 0 || n_q % n_kv != 0 || tpg < 1 || tpg * (n_q / n_kv) > DM_ROWS || T <= 0 ||
-      n_splits < 1)
+      n_splits < 1 || n_blocks <= 0 || ((uintptr_t)kcache & 15) || ((uintptr_t)vcache & 15))
     return (int)cudaErrorInvalidValue;
   cudaStream_t st = (cudaStream_t)stream;
   static bool configured = false;
@@ -785,9 +947,11 @@ TRL_API int trl_attn_decode_mma(const void* q, const void* gate_src, int gate_ld
       return 3;
     configured = true;
   }
+  DmMaps maps;
+  if (dm_get_maps(kcache, vcache, n_blocks, n_kv, &maps)) return (int)cudaErrorInvalidValue;
   const dim3 grid(n_splits, n_kv, (T + tpg - 1) / tpg);
-  cudaError_t e = trl_launch(attn_decode_mma_kernel, grid, dim3(DM_WARPS * 32), (size_t)DM_SMEM, st, (const bf16*)q,
-                             (const bf16*)gate_src, gate_ld, (const bf16*)kcache, (const bf16*)vcache,
+  cudaError_t e = trl_launch(attn_decode_mma_kernel, grid, dim3((DM_WARPS + 1) * 32), (size_t)DM_SMEM, st, maps.mk, maps.mv,
+                             maps.mode3d, (const bf16*)q, (const bf16*)gate_src, gate_ld,
                              (const int*)block_table, max_blocks, (const int*)seq_ids, (const int*)positions,
                              (float*)po, (float*)pm, (float*)pl, (bf16*)out, T, n_q, n_kv, n_splits, tpg,
                              scale * 1.4426950408889634f, gated);

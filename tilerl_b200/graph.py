@@ -99,7 +99,7 @@ class DecodeGraphRunner:
 
     def _splits_for(self, b: int) -> int:
         sms = getattr(self.ops, "sms", 148)
-        return max(1, min(32, sms // max(1, b * self.model.dims.n_kv)))
+        return max(1, min(64, sms // max(1, b * self.model.dims.n_kv)))
 
     def _forward(self, bk: _Bucket):
         self.ops.attn_splits = self._splits_for(bk.b)

@@ -386,7 +386,7 @@ class CudaOps:
             # tensor-core tile, K / V rows are read once per group
             N.check(self.lib.trl_attn_decode_mma(
                 q.data_ptr(), qkv.data_ptr(), qkv.stride(0), kc.data_ptr(), vc.data_ptr(),
-                table.data_ptr(), table.stride(0), batch.seq_ids.data_ptr(),
+                table.data_ptr(), table.stride(0), kc.shape[0], batch.seq_ids.data_ptr(),
                 pos.data_ptr(), po.data_ptr(), pm.data_ptr(), pl.data_ptr(), out.data_ptr(),
                 t, n_q, n_kv, d, splits, tpg, 1.0 / math.sqrt(d), int(cfg.attn_gated), st), "attn_decode_mma")
         else:
@@ -440,9 +440,15 @@ class CudaOps:
         """Enough CTAs to fill the GPU when few tokens attend to long contexts; a split covers at
         least ``keys`` keys (scalar kernel: 32 = four keys per warp; tensor-core kernel: one 64-key
         tile)."""
+        longest = max(batch.host_kv_len) if batch.host_kv_len else 1
+        if keys >= 64:
+            # tensor-core kernel: one CTA is resident per SM (its K / V ring takes the shared memory), so
+            # one wave of CTAs: more splits than that only queue behind the first wave
+            if t * n_kv >= self.sms:
+                return 1
+            return max(1, min(self.sms // max(1, t * n_kv), 64, (longest + keys - 1) // keys))
         if t * n_kv >= self.sms:
             return 1
-        longest = max(batch.host_kv_len) if batch.host_kv_len else 1
         want = max(1, self.sms // max(1, t * n_kv))
         return max(1, min(want, 32, (longest + keys - 1) // keys))
 
