@@ -374,7 +374,8 @@ def main():
             "data": "synthetic (uniform-random token ids, random-init N(0,0.02) weights quantised to NVFP4)",
             "config": {"model": cfg.name, "global_batch": 1, "seq_len": args.prompt_len + args.gen,
                        "prompt_len": args.prompt_len, "gen_len": args.gen, "parallelism": f"tp{world}",
-                       "l2": "inputs larger than L2 (each tick streams >10 GB of weights per GPU)",
+                       "l2": ("inputs larger than L2 (every rank holds %.1f GB of weights and streams them each tick)"
+                              % (model.served_bytes() / 1e9)),
                        "decode": ("eager ticks, NCCL all-reduce after each row-parallel projection" if unfused
                                   else "CUDA-graph ticks, device-side advance")},
             "prefill_tok_s": round(prefill_tok_s, 1),

@@ -1,6 +1,7 @@
 """Time individual kernels at the 27B's projection shapes with CUDA events.
 
     python -m tilerl_b200.utils.kernel_bench [--m 1] [--only gemm|gemv|quant|fp8] [--reps 20]
+    python -m tilerl_b200.utils.kernel_bench --only attn --ctx 32768 --batch 1 [--splits 37] [--eager 5]
 
 Each measurement rotates over enough distinct weight copies to exceed the 126 MB L2,
 so every launch streams its weights from HBM; the figure printed is achieved weight
@@ -17,6 +18,59 @@ SHAPES = {"gate_up": (34816, 5120), "down": (5120, 17408), "gdn_in": (16480, 512
           "qkv": (14336, 5120), "o": (5120, 6144)}
 
 
+def attention_bench(args):
+    """One attention layer of the 27B at decode (prep + split-KV kernel + combine) over a paged pool
+    holding ``--batch`` sequences of ``--ctx`` tokens: device time per layer and K / V bytes per second.
+    ``--eager N`` runs N plain launches instead (the form to put under a profiler)."""
+    from tilerl_b200.batch import Batch
+    from tilerl_b200.config import get_config
+    from tilerl_b200.factory import make_ops
+    from tilerl_b200.kv import PagedKvPool
+    dev = "cuda"
+    cfg = get_config("qwen38-27b")
+    ops = make_ops(dev)
+    n_q, n_kv, d = cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim
+    rows = n_q * 2 * d + 2 * n_kv * d
+    lp = {"q_norm": torch.ones(d, device=dev), "k_norm": torch.ones(d, device=dev)}
+    ctx, b = args.ctx, args.batch
+    nb = (ctx + 16) // 16 + 1
+    pool = PagedKvPool(cfg, b * nb + 2, dev, dtype=torch.bfloat16)
+    kc, vc = pool.layer(0)
+    kc.normal_()
+    vc.normal_()
+    seqs = [dict(tokens=[1], start=ctx, blocks=list(range(1 + i * nb, 1 + (i + 1) * nb)), slot=i + 1) for i in range(b)]
+    batch = Batch.build(seqs, dev)
+    qkv = (torch.randn(b, rows, device=dev) * 0.5).to(torch.bfloat16)
+    out = []
+    for splits in ([args.splits] if args.splits >= 0 else (0, 4, 9, 18, 37, 64)):
+        ops.attn_splits = splits
+        if args.eager:
+            for _ in range(args.eager):
+                ops.attention(qkv, lp, batch, pool, 0, cfg, n_q, n_kv)
+            torch.cuda.synchronize()
+            continue
+        for _ in range(3):
+            ops.attention(qkv, lp, batch, pool, 0, cfg, n_q, n_kv)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(args.reps):
+                ops.attention(qkv, lp, batch, pool, 0, cfg, n_q, n_kv)
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) / args.reps * 1e3
+        kv_bytes = 2 * b * ctx * n_kv * d * 2
+        out.append({"ctx": ctx, "batch": b, "splits": splits or "auto", "us_per_layer": round(us, 1),
+                    "kv_MB": round(kv_bytes / 1e6), "TBps": round(kv_bytes / us / 1e6, 2)})
+    print(json.dumps(out, indent=1))
+    print("kernel_bench done")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--m", type=int, default=1)
@@ -28,7 +82,13 @@ def main():
     ap.add_argument("--split", type=int, default=1)
     ap.add_argument("--tiled", type=int, default=1)
     ap.add_argument("--trace", action="store_true", help="gemm: per-phase timestamps of one launch (median, max over CTAs)")
+    ap.add_argument("--ctx", type=int, default=32768, help="attn: context length")
+    ap.add_argument("--batch", type=int, default=1, help="attn: sequences")
+    ap.add_argument("--splits", type=int, default=-1, help="attn: KV splits (0 = the backend's choice, -1 = sweep)")
+    ap.add_argument("--eager", type=int, default=0, help="attn: this many plain launches, no timing")
     args = ap.parse_args()
+    if args.only == "attn":
+        return attention_bench(args)
     from tilerl_b200.formats import NVFP4Tensor
     from tilerl_b200.ops.cuda import CudaOps
     from tilerl_b200.ops.gemm_tc import gemm_nvfp4, quant_act, sf_tiled, w_stream, wq_tiled
