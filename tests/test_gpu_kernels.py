@@ -128,6 +128,42 @@ def test_gemv_bf16_lm_head_shape(ops):
     assert tok.tolist() == want.argmax(-1).tolist()
 
 
+@pytest.mark.parametrize("m", [3, 5, 8, 11, 16])
+def test_gemv_bf16_tensor_core_rows_match_oracle_and_the_fma_kernel(ops, m):
+    """3..16 rows against bf16 weights take one tensor-core pass (k summed under a fixed permutation):
+    compared with the fp32 oracle, with the FMA kernel two rows at a time, for every epilogue, on an
+    N that is no multiple of the 16-row warp tile; run twice for the same bits."""
+    from tilerl_b200.ops import native
+    g = torch.Generator().manual_seed(10 + m)
+    n, k = 4099, 5120
+    w = (torch.randn(n, k, generator=g) * 0.02).to(DEV, torch.bfloat16)
+    x = torch.randn(m, k, generator=g).to(DEV, torch.bfloat16)
+    nw = (1.0 + 0.1 * torch.randn(k, generator=g)).to(DEV)
+    res = torch.randn(m, n, generator=g).to(DEV, torch.bfloat16)
+    h = ref.rmsnorm(x, nw, 1e-6).to(torch.bfloat16)
+    # fp32 logits with the norm fused
+    y = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemv_now(x, w, y, norm_w=nw, eps=1e-6, epi=3)
+    y2 = torch.empty_like(y)
+    ops.gemv_now(x, w, y2, norm_w=nw, eps=1e-6, epi=3)
+    assert torch.equal(y, y2)
+    want = ref.linear(h, w)
+    assert _rel(y, want) < 2e-3
+    four = torch.empty_like(y)
+    for r0 in range(0, m, 2):
+        ops.gemv_now(x[r0:r0 + 2], w, four[r0:r0 + 2], norm_w=nw, eps=1e-6, epi=3)
+    assert _rel(y, four) < 1e-4
+    assert ops.argmax(y).tolist() == want.argmax(-1).tolist()
+    # bf16 store without norm, and the residual epilogue
+    yb = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops.gemv_now(x, w, yb)
+    assert _rel(yb, ref.linear(x, w)) < 6e-3
+    yr = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops.gemv_now(x, w, yr, residual=res, epi=1)
+    assert _rel(yr, ref.linear(x, w, res)) < 6e-3
+    assert native.read_error()[0] == 0
+
+
 def test_quant_kernel_bit_exact_and_dequant(ops):
     g = torch.Generator().manual_seed(3)
     for dtype in (torch.float32, torch.bfloat16):

@@ -223,7 +223,9 @@ class CudaOps:
                 x.data_ptr(), x.stride(0), w.data_ptr(), N.ptr(norm_w), eps, N.ptr(residual),
                 residual.stride(0) if residual is not None else 0, y.data_ptr(), y.stride(0),
                 m, n, k, epi, N.stream()), "gemv_bf16")
-            N.count((m + 3) // 4)
+            # 3..16 rows whose activations fit shared memory: one tensor-core pass over the weights
+            one_pass = 2 < m <= 16 and k % 32 == 0 and (8 if m <= 8 else 16) * (k + 32) * 2 <= 200 * 1024
+            N.count(1 if one_pass else (m + 3) // 4)
         elif isinstance(w, FP8BlockTensor):
             from . import gemm_fp8
             gemm_fp8.gemv(self, x, w, y, norm_w=norm_w, eps=eps, residual=residual, epi=epi)
@@ -512,7 +514,8 @@ class CudaOps:
         m = x.shape[0]
         n = w.shape[0]
         logits = self.ws.get("logits", (m, n), torch.float32)
-        if m <= GEMV_MAX_M:
+        if m <= GEMV_MAX_M or (m <= 16 and isinstance(w, torch.Tensor) and w.dtype == torch.bfloat16):
+            # bf16 head: up to 16 rows share one pass over the vocabulary matrix (tensor-core GEMV)
             self._gemv(x.contiguous(), w, logits, norm_w=self._f32(norm_w), eps=eps, epi=EPI_STORE_F32)
         else:
             xc = x.contiguous()

@@ -98,6 +98,8 @@ register("nvfp4", "sm100", {
 })
 register("bf16", "sm100", {
     "linear_bf16_gemv": Kernel("gemv_bf16_kernel", "csrc/gemv.cu", "trl_gemv_bf16"),
+    "linear_bf16_gemv_rows16": Kernel("gemv_bf16_mma_kernel", "csrc/gemv.cu", "trl_gemv_bf16",
+                                      note="3..16 rows (batched / verify lm_head): one mma.sync pass over the weights"),
     "linear_bf16_gemm": Kernel("torch.matmul (cuBLAS)", "tilerl_b200/ops/gemm.py", note="plain library GEMM"),
 })
 register("fp8", "sm100", {
