@@ -65,6 +65,49 @@ def test_gemv_nvfp4_fused_norm_residual_swiglu_f32(ops):
     assert _rel(yf, ref.linear(x, w)) < 3e-3
 
 
+@pytest.mark.parametrize("m", [3, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(4104, 5120), (520, 17408), (24, 512), (1030, 6144), (34816, 5120)])
+def test_nvfp4_tensor_core_rows_kernel_matches_oracle(ops, m, n, k):
+    """3..16 rows against NVFP4 weights on mma.sync (weights streamed once, f16 activations): every
+    epilogue against the fp32 oracle, on row counts that end in a half tile or in fewer than 8 rows,
+    with activations staged in one phase (k = 5120), in 2 and in 17 phases (k = 17408 at 8 / 16 rows),
+    fewer half tiles than CTAs (n = 24), the largest projection of the 27B; run twice for the same
+    bits; the backend's dispatch for these row counts lands on the same kernel."""
+    from tilerl_b200.ops import native
+    w = _q(n, k, seed=n + k + m)
+    g = torch.Generator().manual_seed(m * 7 + n)
+    x = (torch.randn(m, k, generator=g) * 20).to(DEV, torch.bfloat16)
+    nw = (1 + 0.1 * torch.randn(k, generator=g)).to(DEV)
+    res = torch.randn(m, n, generator=g).to(DEV, torch.bfloat16)
+
+    def mma(y, *, norm_w=None, residual=None, epi=0):
+        rc = ops.lib.trl_gemv_nvfp4_mma(
+            x.data_ptr(), x.stride(0), w.wq.data_ptr(), w.scale.data_ptr(), w.tscale.data_ptr(),
+            native.ptr(norm_w), 1e-6, native.ptr(residual), residual.stride(0) if residual is not None else 0,
+            y.data_ptr(), y.stride(0), m, n, k, epi, native.stream())
+        assert rc == 0, rc
+        return y
+
+    h = ref.rmsnorm(x, nw, 1e-6).to(torch.bfloat16)
+    y = mma(torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV), norm_w=nw)
+    y2 = mma(torch.empty(m, n, dtype=torch.bfloat16, device=DEV), norm_w=nw)
+    assert torch.equal(y, y2)
+    assert _rel(y, ref.linear(h, w)) < 6e-3
+    out = mma(res.clone(), residual=res, epi=1)
+    assert _rel(out, ref.linear(x, w, res)) < 6e-3
+    act = mma(torch.full((m, n // 2), float("nan"), dtype=torch.bfloat16, device=DEV), norm_w=nw, epi=2)
+    assert _rel(act, ref.swiglu(ref.linear(h, w))) < 1e-2
+    yf = mma(torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV), epi=3)
+    assert _rel(yf, ref.linear(x, w)) < 3e-3
+    # the backend sends these row counts here
+    if m <= ops.mma_tokens and k <= ops.mma_kmax:
+        yd = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+        ops._linear(x, w, yd, norm_w=nw, eps=1e-6)
+        torch.cuda.synchronize()
+        assert torch.equal(yd, y)
+    assert native.read_error()[0] == 0
+
+
 @pytest.mark.parametrize("m", [1, 2])
 @pytest.mark.parametrize("n,k", [(96, 256), (130, 1152), (5120, 6144), (1030, 17408), (5120, 2176), (640, 5120)])
 def test_streamed_gemv_matches_oracle_and_register_kernel(ops, m, n, k):

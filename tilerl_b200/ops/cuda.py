@@ -39,6 +39,7 @@ class ChainOp(ctypes.Structure):
                 ("ldx", ctypes.c_int), ("ldr", ctypes.c_int), ("ldy", ctypes.c_int), ("N", ctypes.c_int),
                 ("K", ctypes.c_int), ("epi", ctypes.c_int), ("coop", ctypes.c_int), ("eps", ctypes.c_float)]
 GEMV_MAX_M = 8
+MMA_MAX_M = 16     # rows served by the mma.sync NVFP4 kernel (csrc/gemv_mma.cu)
 
 
 class Workspace:
@@ -95,6 +96,9 @@ class CudaOps:
         self.terms_large = int(os.environ.get("TRL_TERMS_LARGE", terms_large))
         self.act_dtype = torch.bfloat16
         self.attn_mma = os.environ.get("TRL_ATTN_MMA", "1") != "0" and hasattr(self.lib, "trl_attn_decode_mma")
+        self.gemv_mma = os.environ.get("TRL_GEMV_MMA", "1") != "0" and hasattr(self.lib, "trl_gemv_nvfp4_mma")
+        self.mma_tokens = int(os.environ.get("TRL_GEMV_MMA_TOKENS", "8"))      # rows it serves (the kernel takes up to 16)
+        self.mma_kmax = int(os.environ.get("TRL_GEMV_MMA_KMAX", "8192"))      # longer rows go to the tcgen05 GEMM
         # TRL_GEMV_CHAIN=1: consecutive 1-2 row projections are queued and go out as one chained launch
         # (grid barriers between them, weight rings refilled across the barriers); anything else
         # flushes the queue.  Off by default: measured on the 27B tick a grid barrier costs more than the
@@ -255,6 +259,20 @@ class CudaOps:
             self.settle()
             gemm_fp8.linear(self, x, w, y, norm_w=norm_w, eps=eps, residual=residual, epi=epi)
             return
+        if (self._tc(w, t) and self.gemv_mma and t <= self.mma_tokens and x.shape[1] <= self.mma_kmax
+                and not self.decode_tc and x.stride(0) % 8 == 0):
+            # 3..16 rows (batched decode, verify windows): f16 activations against the NVFP4 weights on
+            # mma.sync, weights streamed once, no activation quantiser; shapes it does not take
+            # (cudaErrorNotSupported) go on to the quantiser + tcgen05 GEMM below
+            rc = self.lib.trl_gemv_nvfp4_mma(
+                x.data_ptr(), x.stride(0), w.wq.data_ptr(), w.scale.data_ptr(), w.tscale.data_ptr(),
+                N.ptr(norm_w), eps, N.ptr(residual), residual.stride(0) if residual is not None else 0,
+                y.data_ptr(), y.stride(0), t, w.wq.shape[0], x.shape[1], epi, N.stream())
+            if rc == 0:
+                N.count()
+                return
+            if rc != 801:
+                N.check(rc, "gemv_nvfp4_mma")
         if self._tc(w, t):
             from .gemm_tc import gemm_nvfp4
             terms = self.terms_small if t <= GEMV_MAX_M else self.terms_large

@@ -65,11 +65,14 @@ def arch_for(device) -> str:
 
 
 # Projection kernel by launch M (token rows): the weight-streaming GEMV up to `gemv_tokens`
-# rows, the tcgen05 block-scaled GEMM above (measured crossover on the 27B shapes: 2 rows tie).
+# rows, the mma.sync kernel with f16 activations up to 16 rows (batched decode, verify windows),
+# the tcgen05 block-scaled GEMM above.
 def linear_kernel_for(m: int, gemv_tokens: int = 2, precision: str = "nvfp4") -> str:
     if precision == "bf16":
         return "linear_bf16_gemv" if m <= 8 else "linear_bf16_gemm"
-    return "linear_nvfp4_gemv" if m <= gemv_tokens else "linear_nvfp4_gemm"
+    if m <= gemv_tokens:
+        return "linear_nvfp4_gemv"
+    return "linear_nvfp4_rows16" if m <= 16 else "linear_nvfp4_gemm"
 
 
 _REF = "tilerl_b200/ops/ref.py"
@@ -89,6 +92,8 @@ register("any", "cpu", {
 register("nvfp4", "sm100", {
     "linear_nvfp4_gemv": Kernel("gemv_nvfp4_kernel / gemv_nvfp4_sk_kernel", "csrc/gemv.cu", "trl_gemv_nvfp4",
                                 note="M <= 8; RMSNorm prologue; residual / SwiGLU / fp32 / TP-push epilogues"),
+    "linear_nvfp4_rows16": Kernel("gemv_nvfp4_mma_kernel", "csrc/gemv_mma.cu", "trl_gemv_nvfp4_mma",
+                                  note="3..16 rows: weights as the mma.sync A operand, f16 activations, every epilogue"),
     "linear_nvfp4_gemm": Kernel("gemm_nvfp4_kernel", "csrc/gemm_tc.cu", "trl_gemm_nvfp4", "tilerl_b200.ops.gemm_tc",
                                 note="tcgen05.mma kind::mxf4nvf4.block_scale, TMA, TMEM accumulator, stream-K"),
     "quant_act_nvfp4": Kernel("quant_act_kernel", "csrc/gemm_tc.cu", "trl_quant_act_nvfp4", "tilerl_b200.ops.gemm_tc",
