@@ -72,7 +72,7 @@ def test_nvfp4_tensor_core_rows_kernel_matches_oracle(ops, m, n, k):
     epilogue against the fp32 oracle, on row counts that end in a half tile or in fewer than 8 rows,
     with activations staged in one phase (k = 5120), in 2 and in 17 phases (k = 17408 at 8 / 16 rows),
     fewer half tiles than CTAs (n = 24), the largest projection of the 27B; run twice for the same
-    bits; the backend's dispatch for these row counts lands on the same kernel."""
+    bits; with the backend's switch on, its dispatch for these row counts lands on the same kernel."""
     from tilerl_b200.ops import native
     w = _q(n, k, seed=n + k + m)
     g = torch.Generator().manual_seed(m * 7 + n)
@@ -101,9 +101,14 @@ def test_nvfp4_tensor_core_rows_kernel_matches_oracle(ops, m, n, k):
     assert _rel(yf, ref.linear(x, w)) < 3e-3
     # the backend sends these row counts here
     if m <= ops.mma_tokens and k <= ops.mma_kmax:
-        yd = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
-        ops._linear(x, w, yd, norm_w=nw, eps=1e-6)
-        torch.cuda.synchronize()
+        was = ops.gemv_mma
+        ops.gemv_mma = True
+        try:
+            yd = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+            ops._linear(x, w, yd, norm_w=nw, eps=1e-6)
+            torch.cuda.synchronize()
+        finally:
+            ops.gemv_mma = was
         assert torch.equal(yd, y)
     assert native.read_error()[0] == 0
 

@@ -53,8 +53,11 @@ def test_resolution_falls_through_and_refuses_unknown_cells():
 
 
 def test_linear_bands_follow_the_dispatch_of_the_cuda_backend():
-    assert [R.linear_kernel_for(m) for m in (1, 2, 3, 8, 16, 17, 64, 512)] == \
-        ["linear_nvfp4_gemv"] * 2 + ["linear_nvfp4_rows16"] * 3 + ["linear_nvfp4_gemm"] * 3
+    assert [R.linear_kernel_for(m) for m in (1, 2, 3, 8, 64, 512)] == \
+        ["linear_nvfp4_gemv"] * 2 + ["linear_nvfp4_gemm"] * 4
+    assert [R.linear_kernel_for(m, mma_rows=True) for m in (2, 3, 16, 17)] == \
+        ["linear_nvfp4_gemv", "linear_nvfp4_rows16", "linear_nvfp4_rows16", "linear_nvfp4_gemm"]
+    R.resolve("linear_nvfp4_rows16", "nvfp4", "sm100")
     assert R.linear_kernel_for(8, gemv_tokens=8) == "linear_nvfp4_gemv"
     assert R.arch_for("cpu") == "cpu"
     for m in (1, 8, 512):

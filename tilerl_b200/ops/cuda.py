@@ -96,7 +96,13 @@ class CudaOps:
         self.terms_large = int(os.environ.get("TRL_TERMS_LARGE", terms_large))
         self.act_dtype = torch.bfloat16
         self.attn_mma = os.environ.get("TRL_ATTN_MMA", "1") != "0" and hasattr(self.lib, "trl_attn_decode_mma")
-        self.gemv_mma = os.environ.get("TRL_GEMV_MMA", "1") != "0" and hasattr(self.lib, "trl_gemv_nvfp4_mma")
+        # TRL_GEMV_MMA=1: 3..16 rows against NVFP4 weights go to the mma.sync kernel with f16 activations
+        # (csrc/gemv_mma.cu) instead of the activation quantiser + tcgen05 GEMM.  Off by default: launch for
+        # launch it ties with that pair on the 27B shapes (gate_up at 8 rows 34.1 us against 34.6), but inside
+        # a B = 8 decode tick it loses, 14.5 ms against 10.65: decoding e2m1 on the CUDA cores costs 26
+        # instructions per MMA (issue slots 46 % busy, no pipe saturated), and its staging of the activation rows
+        # sits behind the dependency of every launch where the GEMM's prologue does not.
+        self.gemv_mma = os.environ.get("TRL_GEMV_MMA", "0") == "1" and hasattr(self.lib, "trl_gemv_nvfp4_mma")
         self.mma_tokens = int(os.environ.get("TRL_GEMV_MMA_TOKENS", "8"))      # rows it serves (the kernel takes up to 16)
         self.mma_kmax = int(os.environ.get("TRL_GEMV_MMA_KMAX", "8192"))      # longer rows go to the tcgen05 GEMM
         # TRL_GEMV_CHAIN=1: consecutive 1-2 row projections are queued and go out as one chained launch

@@ -65,14 +65,14 @@ def arch_for(device) -> str:
 
 
 # Projection kernel by launch M (token rows): the weight-streaming GEMV up to `gemv_tokens`
-# rows, the mma.sync kernel with f16 activations up to 16 rows (batched decode, verify windows),
-# the tcgen05 block-scaled GEMM above.
-def linear_kernel_for(m: int, gemv_tokens: int = 2, precision: str = "nvfp4") -> str:
+# rows, the tcgen05 block-scaled GEMM above; with `mma_rows` (the backend's TRL_GEMV_MMA switch, off by
+# default) 3..16 rows go to the mma.sync kernel with f16 activations.
+def linear_kernel_for(m: int, gemv_tokens: int = 2, precision: str = "nvfp4", mma_rows: bool = False) -> str:
     if precision == "bf16":
         return "linear_bf16_gemv" if m <= 8 else "linear_bf16_gemm"
     if m <= gemv_tokens:
         return "linear_nvfp4_gemv"
-    return "linear_nvfp4_rows16" if m <= 16 else "linear_nvfp4_gemm"
+    return "linear_nvfp4_rows16" if (mma_rows and m <= 16) else "linear_nvfp4_gemm"
 
 
 _REF = "tilerl_b200/ops/ref.py"
