@@ -703,6 +703,28 @@ lora_b_kernel(const float* t, const float* __restrict__ B, bf16* y, int ldy, int
   *yp = __float2bfloat16(__bfloat162float(*yp) + s * acc);
 }
 
+// Speculative verify tick, greedy acceptance on the device.  Sequence b owns rows b*W .. b*W + q_len[b] - 1
+// of the tick: row k carried the chain token c_k (c_0 the last committed token, c_1.. the drafts) and
+// `tok[b*W + k]` is the trunk's argmax after it.  accept[b] = number of leading drafts the trunk
+// reproduced (c_{k+1} == tok[k]); the GDN state plane stored after chain token accept[b] becomes the
+// sequence's current one (cur[state_slots[b]], the index write of GdnStatePool.select_step).
+// pack: [B*W argmax tokens ; B accept counts], one buffer for the host to fetch.
+// Reference parity: the accept walk of spec.py:1071-1146 (src/tilerl), which the reference runs on the host.
+__global__ void spec_accept_kernel(const int* tok, const int* chain, const int* q_len, const int* state_slots,
+                                   int* cur, int* pack, int B, int W) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = B * W;
+  for (int i = threadIdx.x; i < t; i += blockDim.x) pack[i] = tok[i];
+  for (int b = threadIdx.x; b < B; b += blockDim.x) {
+    const int n = q_len[b];
+    int ok = 0;
+    while (ok + 1 < n && tok[b * W + ok] == chain[b * W + ok + 1]) ++ok;
+    pack[t + b] = ok;
+    if (n > 0) cur[state_slots[b]] = ok;
+  }
+}
+
 }  // namespace
 
 TRL_API int trl_embedding(const void* table, const void* ids, void* out, int T, int H, int V, void* stream) {
@@ -723,6 +745,13 @@ TRL_API int trl_swiglu(const void* gu, void* out, long n_out, void* stream) {
                          (bf16*)out, n_out);
 }
 // scratch: M * 64 floats followed by M * 64 ints.
+TRL_API int trl_spec_accept(const void* tok, const void* chain, const void* q_len, const void* state_slots, void* cur,
+                            void* pack, int B, int W, void* stream) {
+  if (B <= 0 || W <= 0) return (int)cudaErrorInvalidValue;
+  return (int)trl_launch(spec_accept_kernel, dim3(1), dim3(128), 0, (cudaStream_t)stream, (const int*)tok,
+                         (const int*)chain, (const int*)q_len, (const int*)state_slots, (int*)cur, (int*)pack, B, W);
+}
+
 TRL_API int trl_argmax(const void* logits, int ld, int M, int V, void* out, void* scratch, void* stream) {
   float* pv = (float*)scratch;
   int* pi = (int*)(pv + (size_t)M * ARGMAX_CHUNKS);

@@ -123,6 +123,18 @@ def test_spec_decode_matches_plain_on_gpu(setup):
         got = [r.tokens for r in eng.generate(prompts, sp)]
         _assert_same_or_near_tie(cfg, ops, model, prompts, want, got, ("graph", type(drafter).__name__))
         assert eng.vgraph is not None and eng.vgraph.replays > 0
+        # greedy requests: the graph counted the accepted drafts and selected the state plane itself;
+        # the host walk over the same ticks accepts exactly as many and commits the same tokens
+        c = eng.stats()
+        assert c["spec_device_accepts"] > 0
+        if not isinstance(drafter, BlockDrafter):           # (the block drafter keeps state of its own between runs)
+            host = build_engine(model, ops, slots=4, max_ctx=256, graph=True, prefix=False, spec_width=4, drafter=drafter)
+            host.spec_device_accept = False
+            got_host = [r.tokens for r in host.generate(prompts, sp)]
+            ch = host.stats()
+            assert ch["spec_device_accepts"] == 0
+            assert got_host == got
+            assert (ch["spec_drafted"], ch["spec_accepted"]) == (c["spec_drafted"], c["spec_accepted"])
 
 
 def test_sparse_decode_runs_on_gpu(setup):

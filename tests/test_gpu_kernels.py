@@ -212,6 +212,35 @@ def test_gemv_bf16_tensor_core_rows_match_oracle_and_the_fma_kernel(ops, m):
     assert native.read_error()[0] == 0
 
 
+def test_spec_accept_kernel_counts_reproduced_drafts_and_selects_the_state_plane(ops):
+    """Greedy acceptance of a verify tick on the device against the host walk: full, partial and zero
+    acceptance, a chain of one token, a padded sequence (q_len 0: its state slot stays untouched)."""
+    from types import SimpleNamespace
+    from tilerl_b200.ops import native
+    b, w = 5, 4
+    chain = torch.tensor([[7, 11, 12, 13], [7, 11, 12, 13], [7, 11, 12, 13], [9, 0, 0, 0], [0, 0, 0, 0]], dtype=torch.int32)
+    tok = torch.tensor([[11, 12, 13, 99], [11, 50, 13, 99], [40, 12, 13, 99], [21, 0, 0, 0], [0, 0, 0, 0]], dtype=torch.int32)
+    q_len = torch.tensor([4, 4, 4, 1, 0], dtype=torch.int32)
+    slots = torch.tensor([3, 1, 4, 2, 0], dtype=torch.int32)
+    want = []
+    for r in range(b):
+        ok = 0
+        while ok + 1 < int(q_len[r]) and int(tok[r, ok]) == int(chain[r, ok + 1]):
+            ok += 1
+        want.append(ok)
+    assert want == [3, 1, 0, 0, 0]
+    cur = torch.full((6,), 9, dtype=torch.int32, device=DEV)
+    pack = torch.full((b * w + b,), -1, dtype=torch.int32, device=DEV)
+    batch = SimpleNamespace(n_seqs=b, n_tokens=b * w, token_ids=chain.flatten().to(DEV), q_len=q_len.to(DEV),
+                            state_slots=slots.to(DEV))
+    ops.spec_accept(tok.flatten().to(DEV), batch, cur, pack)
+    torch.cuda.synchronize()
+    assert pack[:b * w].cpu().tolist() == tok.flatten().tolist()
+    assert pack[b * w:].cpu().tolist() == want
+    assert cur.cpu().tolist() == [9, 1, 0, 3, 0, 9]          # slot 0 (the padded row's) and slot 5 untouched
+    assert native.read_error()[0] == 0
+
+
 def test_quant_kernel_bit_exact_and_dequant(ops):
     g = torch.Generator().manual_seed(3)
     for dtype in (torch.float32, torch.bfloat16):

@@ -147,6 +147,8 @@ class Engine:
         # benchmark seam: count every draft as accepted, to time the verify tick at full acceptance
         # on models whose greedy choice flips with rounding (random-init weights)
         self.spec_force_accept = False
+        # False: walk the chain on the host even when the verify graph counted the accepted drafts (test seam)
+        self.spec_device_accept = True
         self.graph = graph_runner
         self.vgraph = verify_graph_runner       # CUDA-graph replay of width-W verify ticks
         self.sparse = sparse
@@ -163,7 +165,7 @@ class Engine:
         self._degraded: Optional[str] = None
         self.counters = dict(ticks=0, prefill_ticks=0, decode_ticks=0, mixed_ticks=0,
                              graph_ticks=0, tokens_generated=0, prompt_tokens=0,
-                             spec_drafted=0, spec_accepted=0, cancelled=0, failed=0,
+                             spec_drafted=0, spec_accepted=0, spec_device_accepts=0, cancelled=0, failed=0,
                              finished=0, preempted=0)
         self.timing = os.environ.get("TRL_STEP_TIMING") == "1"
         # TRL_NVTX=1: every tick and its sampling phase become NVTX ranges, so a profiler can be
@@ -460,6 +462,7 @@ class Engine:
         taps = hidden = None
         amax = None
         vout = None
+        dev_accept = None       # per sequence: drafts accepted, counted (and the state plane selected) on the device
         if logits is None and self.vgraph is not None and decode_only and verify and self.sparse is None:
             greedy = all(self._is_plain_greedy(r) for r, _, _ in plan)
             vout = self.vgraph.run(seqs, need_logits=not greedy)
@@ -467,6 +470,7 @@ class Engine:
             self.counters["graph_ticks"] += 1
             logits, taps = vout.logits, vout.taps
             amax = vout.argmax if greedy else None
+            dev_accept = vout.accept if greedy else None
         elif logits is not None:
             logits, amax = logits.logits, logits.argmax
             if not all(self._is_plain_greedy(r) for r, _, _ in plan):
@@ -507,7 +511,8 @@ class Engine:
                     self._commit(r, [self._sample(r, logits, last, 0, amax)])
                     self._offer_draft(r, taps, tok_off, n)
             else:
-                self._verify_commit(r, toks, logits, base, verify, amax)
+                self._verify_commit(r, toks, logits, base, verify, amax,
+                                    dev_accept[i] if dev_accept is not None else None)
                 self._offer_draft(r, taps, tok_off, n)
             tok_off += n
 
@@ -568,13 +573,25 @@ class Engine:
         return ref.sample(logits[row].detach().float().cpu(), p.temperature, p.top_p, p.top_k,
                           ref.sample_seed(p.seed, idx), allowed)
 
-    def _verify_commit(self, r: _Req, chain: List[int], logits, base: int, verify: bool, amax=None) -> None:
+    def _verify_commit(self, r: _Req, chain: List[int], logits, base: int, verify: bool, amax=None,
+                       dev_accept: Optional[int] = None) -> None:
+        """``dev_accept``: the verify graph already walked this sequence's chain under greedy acceptance
+        and selected the GDN state plane (``spec_accept_kernel``); the host then only commits."""
+        on_device = dev_accept is not None and amax is not None and not self.spec_force_accept \
+            and self.spec_device_accept and self._is_plain_greedy(r)
         if not verify or len(chain) == 1:
             self._commit(r, [self._sample(r, logits, base, 0, amax)])
-            if verify:
+            if verify and not on_device:
                 self.states.select_step(r.slot, 0)
             return
         drafts = chain[1:]
+        if on_device:
+            n_ok = int(dev_accept)
+            self.counters["spec_drafted"] += len(drafts)
+            self.counters["spec_accepted"] += n_ok
+            self.counters["spec_device_accepts"] += 1
+            self._commit(r, [(amax[base + k], 0.0) for k in range(n_ok + 1)])
+            return
         accepted: List[Tuple[int, float]] = []
         n_ok = 0
         for k in range(len(chain)):

@@ -192,6 +192,9 @@ class VerifyOut:
     logits: torch.Tensor                 # [rows, vocab] in the engine's (compact) row order
     argmax: List[int]
     taps: Optional[Dict[int, torch.Tensor]]
+    # drafts each sequence's trunk reproduced under greedy acceptance, counted on the device, which has
+    # also selected the matching GDN state plane; None when the backend has no such kernel
+    accept: Optional[List[int]] = None
 
 
 class _VBucket:
@@ -217,10 +220,10 @@ class _VBucket:
             n_seqs=b, n_tokens=t, max_q_len=w, keep_steps=w, host_q_len=[w] * b, host_kv_len=[1] * b,
             keep_rows=[True] * b, keep_flags=bv(3))
         self.graph = None
-        self.out_tok = self.out_logits = None
+        self.out_tok = self.out_logits = self.out_pack = None
         self.out_taps: Optional[Dict[int, torch.Tensor]] = None
-        self.tok_host = torch.zeros(t, dtype=torch.int32).pin_memory() if device.type == "cuda" \
-            else torch.zeros(t, dtype=torch.int32)
+        self.tok_host = torch.zeros(t + b, dtype=torch.int32).pin_memory() if device.type == "cuda" \
+            else torch.zeros(t + b, dtype=torch.int32)      # [argmax of every row ; accept count of every sequence]
         self.kernels = 0
         self.h2d_bytes = 0
 
@@ -272,7 +275,12 @@ class VerifyGraphRunner:
         self.ops.attn_splits = 0
         logits, taps = (res[0], res[2]) if self.aux else (res, None)
         tok = self.ops.argmax(logits)
-        return logits, tok, taps
+        pack = None
+        if hasattr(self.ops, "spec_accept") and getattr(self.states, "cur", None) is not None:
+            # accept length per sequence and the state-plane selection, inside the graph
+            pack = self.ops.ws.get(f"spec_pack_{bk.b}", (bk.b * bk.w + bk.b,), torch.int32)
+            self.ops.spec_accept(tok, bk.batch, self.states.cur, pack)
+        return logits, tok, taps, pack
 
     def _capture(self, b: int) -> _VBucket:
         bk = _VBucket(b, self.w, self.max_blocks, self.device)
@@ -291,9 +299,9 @@ class VerifyGraphRunner:
         from .ops import native as N
         before = N.launch_count
         with torch.cuda.graph(g, pool=self._pool):
-            logits, tok, taps = self._forward(bk)
+            logits, tok, taps, pack = self._forward(bk)
         bk.kernels = N.launch_count - before
-        bk.graph, bk.out_logits, bk.out_tok, bk.out_taps = g, logits, tok, taps
+        bk.graph, bk.out_logits, bk.out_tok, bk.out_taps, bk.out_pack = g, logits, tok, taps, pack
         self._b[b] = bk
         return bk
 
@@ -307,13 +315,18 @@ class VerifyGraphRunner:
         rows = bk.fill(seqs)
         bk.dev.copy_(bk.host, non_blocking=True)
         bk.graph.replay()
-        bk.tok_host.copy_(bk.out_tok, non_blocking=True)
+        t = bk.b * bk.w
+        if bk.out_pack is not None:
+            bk.tok_host.copy_(bk.out_pack, non_blocking=True)
+        else:
+            bk.tok_host[:t].copy_(bk.out_tok, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         self.replays += 1
         self.h2d_bytes += bk.h2d_bytes
-        self.d2h_bytes += bk.tok_host.numel() * 4
+        self.d2h_bytes += (bk.tok_host.numel() if bk.out_pack is not None else t) * 4
         th = bk.tok_host.tolist()
+        accept = th[t:t + len(seqs)] if bk.out_pack is not None else None
         idx = torch.tensor(rows, dtype=torch.long, device=self.device) if (need_logits or bk.out_taps) else None
         taps = {l: v[idx] for l, v in bk.out_taps.items()} if bk.out_taps else None
         logits = bk.out_logits[idx] if need_logits else bk.out_logits
-        return VerifyOut(logits, [th[r] for r in rows], taps)
+        return VerifyOut(logits, [th[r] for r in rows], taps, accept)

@@ -560,6 +560,18 @@ class CudaOps:
             return full[..., :self.vocab] if self.vocab else full
         return logits
 
+    def spec_accept(self, tok, batch, cur, pack) -> None:
+        """Greedy acceptance of a verify tick on the device: ``pack[:B*W]`` gets the argmax tokens,
+        ``pack[B*W:]`` the number of drafts each sequence's trunk reproduced, and ``cur`` (the GDN pool's
+        current-plane index) is set to it for every sequence of the tick."""
+        self.flush()
+        b = batch.n_seqs
+        w = batch.n_tokens // b
+        N.check(self.lib.trl_spec_accept(tok.data_ptr(), batch.token_ids.data_ptr(), batch.q_len.data_ptr(),
+                                         batch.state_slots.data_ptr(), cur.data_ptr(), pack.data_ptr(), b, w,
+                                         N.stream()), "spec_accept")
+        N.count()
+
     def argmax(self, logits):
         self.flush()
         m, v = logits.shape

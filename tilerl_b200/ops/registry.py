@@ -133,6 +133,8 @@ register("any", "sm100", {
     "argmax": Kernel("argmax_stage1_kernel + argmax_stage2_kernel", "csrc/misc.cu", "trl_argmax"),
     "sample": Kernel("sample_softmax_kernel", "csrc/misc.cu", "trl_sample_softmax"),
     "sample_nucleus": Kernel("sample_nucleus_kernel", "csrc/misc.cu", "trl_sample_nucleus"),
+    "spec_accept": Kernel("spec_accept_kernel", "csrc/misc.cu", "trl_spec_accept",
+                          note="greedy accept length + GDN state-plane selection of a verify tick, inside its graph"),
     "lora": Kernel("lora_a_kernel + lora_b_kernel", "csrc/misc.cu", "trl_lora_add"),
     "adamw": Kernel("adamw_kernel", "csrc/misc.cu", "trl_adamw"),
     "decode_advance": Kernel("decode_advance_kernel", "csrc/misc.cu", "trl_decode_advance"),
