@@ -579,16 +579,69 @@ __device__ __forceinline__ uint32_t dm_try_wait(uint32_t bar, uint32_t parity) {
 // into a three-stage ring.  A stage's "full" mbarrier counts the bytes, its "empty" mbarrier the four
 // consumer warps.  The block-table entries of the CTA's key range are read into shared memory once,
 // so no global load sits in the loop.  map3d == 0: the same layout from 2-D copies, one per slab.
+//
+// FUSED (decode ticks: one new token per sequence, rotary width 64): the kernel is the whole attention
+// layer.  `q` is then the raw fused projection row [hq x (query ; gate)] ++ [hkv x D] ++ [hkv x D] (leading
+// dimension gate_ld): every CTA normalises and rotates the six query rows of its kv head itself, the CTA
+// whose key range holds the new position does the same for the new K row, copies the V row, writes both
+// to the pool and patches them into its shared-memory tile (the tile copy may have fetched the page before
+// the write landed); the last CTA of a (token, kv head) to finish merges the split partials and writes the
+// gated output rows, so neither the prep nor the combine kernel is launched.
+struct DmFused {
+  const float *q_norm, *k_norm;
+  const int* slot_mapping;
+  bf16 *kcache, *vcache;
+  int* counters;                                   // [T * n_kv], zero between launches
+  float log2_theta, eps;
+  int rotary;
+};
+constexpr int DM_ROT_HALF = 32;                    // the fused form takes rotary == 64
+
+// One head row of the fused projection: RMSNorm (fp32), rotation of the first 64 dims by the position's
+// angles, bf16.  Lane l owns dims 8l .. 8l + 7; lanes 0-3 pair with lanes 4-7 for the rotation.
+__device__ __forceinline__ uint4 dm_prep_row(const bf16* src, const float* __restrict__ w, float eps, const float* cs,
+                                             const float* sn, int lane) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(src + lane * 8);
+  const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+  float v[8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = bf162_bits_to_f2(rw[i]);
+    v[2 * i] = f.x, v[2 * i + 1] = f.y;
+    ss += f.x * f.x + f.y * f.y;
+  }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / (float)PF_D + eps);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = v[i] * rstd * w[lane * 8 + i];
+  float o[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float other = __shfl_xor_sync(0xffffffffu, v[i], 4);
+    const int d = lane * 8 + i;
+    if (lane < 4) o[i] = v[i] * cs[d] - other * sn[d];
+    else if (lane < 8) o[i] = v[i] * cs[d - DM_ROT_HALF] + other * sn[d - DM_ROT_HALF];
+    else o[i] = v[i];
+  }
+  return make_uint4(f2_to_bf162_bits(o[0], o[1]), f2_to_bf162_bits(o[2], o[3]), f2_to_bf162_bits(o[4], o[5]),
+                    f2_to_bf162_bits(o[6], o[7]));
+}
+
+template <bool FUSED>
 __global__ void __launch_bounds__((DM_WARPS + 1) * 32)
 attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, int map3d,
                        const bf16* q, const bf16* gate_src, int gate_ld,
                        const int* block_table, int max_blocks, const int* seq_ids, const int* positions,
                        float* po, float* pm, float* pl, bf16* out, int T, int n_q, int n_kv, int n_splits,
-                       int tpg, float scale_log2e, int gated) {
+                       int tpg, float scale_log2e, int gated, const DmFused fz) {
   extern __shared__ unsigned char dm_smem_raw[];
   __shared__ float s_m[DM_WARPS][DM_ROWS], s_l[DM_WARPS][DM_ROWS];
   __shared__ int s_tab[DM_TAB];
   __shared__ volatile int s_ok;
+  __shared__ float s_cs[DM_ROT_HALF], s_sn[DM_ROT_HALF];
+  __shared__ __align__(16) uint4 s_knew[32], s_vnew[32];      // the new token's K and V rows (bf16 x 256)
+  __shared__ int s_last;
   const int split = blockIdx.x, kvh = blockIdx.y, t0 = blockIdx.z * tpg;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t raw_a = (uint32_t)__cvta_generic_to_shared(dm_smem_raw);
@@ -619,7 +672,10 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   for (int i = 0; i < nt; ++i) kv_len = max(kv_len, positions[t0 + i] + 1);   // padded window need not ascend)
   const int* table = block_table + (size_t)seq_ids[t0] * max_blocks;
   const int pages = (kv_len + KVB - 1) / KVB;
-  const int pps = (pages + n_splits - 1) / n_splits;
+  // the grid's split count is fixed when a graph is captured, the context is not: a short context is cut
+  // into splits of at least 128 keys, the CTAs past them find an empty range and write a neutral partial
+  const int n_eff = max(1, min(n_splits, (kv_len + 127) / 128));
+  const int pps = (pages + n_eff - 1) / n_eff;
   const int lo = split * pps * KVB, hi = min(kv_len, (split + 1) * pps * KVB);
   const int n_tiles = hi > lo ? (hi - lo + DM_KEYS - 1) / DM_KEYS : 0;
   const int page0 = lo / KVB, n_pages = hi > lo ? (hi - lo + KVB - 1) / KVB : 0;
@@ -628,11 +684,45 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     for (int i = threadIdx.x; i < n_pages; i += blockDim.x) s_tab[i] = table[page0 + i];
 
   // row r of the tile = (token r / G of the group, head r % G of the kv head); unused rows are zero
-  for (int x = threadIdx.x; x < DM_ROWS * PF_CHUNKS; x += blockDim.x) {
-    const int r = x / PF_CHUNKS, c = x % PF_CHUNKS;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (r < rows) v = *reinterpret_cast<const uint4*>(q + ((size_t)(t0 + r / G) * n_q + kvh * G + r % G) * PF_D + c * 8);
-    *reinterpret_cast<uint4*>(qs + dm_off(r, c)) = v;
+  const int new_pos = kv_len - 1;                  // FUSED: the position of the tick's token
+  if (FUSED) {
+    if (threadIdx.x < DM_ROT_HALF) {               // the position's rotation angles, in double like the prep kernel
+      const double inv = exp2(-(double)(2 * threadIdx.x) / (double)fz.rotary * (double)fz.log2_theta);
+      double sd, cd;
+      sincos((double)new_pos * inv, &sd, &cd);
+      s_cs[threadIdx.x] = (float)cd, s_sn[threadIdx.x] = (float)sd;
+    }
+    for (int x = threadIdx.x; x < (DM_ROWS - rows) * PF_CHUNKS; x += blockDim.x)
+      *reinterpret_cast<uint4*>(qs + dm_off(rows + x / PF_CHUNKS, x % PF_CHUNKS)) = make_uint4(0u, 0u, 0u, 0u);
+    __syncthreads();
+    const bf16* row = q + (size_t)t0 * gate_ld;
+    const int per_q = gated ? 2 * PF_D : PF_D;
+    // the G query rows, then the new K row and the new V row, dealt round the five warps
+    for (int job = warp; job < rows + 2; job += DM_WARPS + 1) {
+      if (job < rows) {
+        const uint4 v = dm_prep_row(row + (size_t)(kvh * G + job) * per_q, fz.q_norm, fz.eps, s_cs, s_sn, lane);
+        *reinterpret_cast<uint4*>(qs + dm_off(job, lane)) = v;
+      } else if (new_pos >= lo && new_pos < hi) {
+        const int slot = fz.slot_mapping[t0];
+        const size_t dst = (((size_t)(slot / KVB) * n_kv + kvh) * KVB + (slot % KVB)) * PF_D + lane * 8;
+        if (job == rows) {
+          const uint4 v = dm_prep_row(row + (size_t)n_q * per_q + (size_t)kvh * PF_D, fz.k_norm, fz.eps, s_cs, s_sn, lane);
+          s_knew[lane] = v;
+          if (slot >= 0) *reinterpret_cast<uint4*>(fz.kcache + dst) = v;
+        } else {
+          const uint4 v = *reinterpret_cast<const uint4*>(row + (size_t)n_q * per_q + (size_t)(n_kv + kvh) * PF_D + lane * 8);
+          s_vnew[lane] = v;
+          if (slot >= 0) *reinterpret_cast<uint4*>(fz.vcache + dst) = v;
+        }
+      }
+    }
+  } else {
+    for (int x = threadIdx.x; x < DM_ROWS * PF_CHUNKS; x += blockDim.x) {
+      const int r = x / PF_CHUNKS, c = x % PF_CHUNKS;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (r < rows) v = *reinterpret_cast<const uint4*>(q + ((size_t)(t0 + r / G) * n_q + kvh * G + r % G) * PF_D + c * 8);
+      *reinterpret_cast<uint4*>(qs + dm_off(r, c)) = v;
+    }
   }
   __syncthreads();                                 // barriers initialised, table and Q rows in place
   auto bounded_wait = [&](uint32_t bar, uint32_t parity, int what) {
@@ -693,6 +783,14 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int jw = lo + kt * DM_KEYS + warp * 16;     // this warp's first key of the tile
     if (jw < hi && s_ok) {
       const uint32_t kb = ks_a + buf * DM_TILE, vb = vs_a + buf * DM_TILE;
+      if (FUSED && new_pos >= jw && new_pos < jw + 16) {
+        // this tick's token: its rows come from this CTA's registers, not from the page copy
+        const int key = warp * 16 + (new_pos - jw);
+        const uint4 kn = s_knew[lane], vn = s_vnew[lane];
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(kb + dm_kv_off(key, lane)), "r"(kn.x), "r"(kn.y), "r"(kn.z), "r"(kn.w) : "memory");
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(vb + dm_kv_off(key, lane)), "r"(vn.x), "r"(vn.y), "r"(vn.z), "r"(vn.w) : "memory");
+        __syncwarp();
+      }
       if (jw + 16 > hi) {
         // the page's keys past the range hold whatever the pool holds: their scores are masked by a
         // select, but 0 x V must be 0, so their V rows are cleared (only this warp reads them)
@@ -803,10 +901,53 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       float ov = ll > 0.f ? a / ll : 0.f;
       if (gated) ov *= sigmoid_f(__bfloat162float(gate_src[(size_t)t * gate_ld + (size_t)h * 2 * PF_D + PF_D + d]));
       out[((size_t)t * n_q + h) * PF_D + d] = __float2bfloat16(ov);
-    } else {
+    } else if (!FUSED || split < n_eff) {          // FUSED: the merge below reads the first n_eff splits only
       const size_t base = ((size_t)t * n_q + h) * n_splits + split;
       po[base * PF_D + d] = a;
       if (d == 0) pm[base] = mm, pl[base] = ll;
+    }
+  }
+  if (FUSED && n_splits > 1) {
+    // the last CTA of this (token, kv head) to get here merges the splits: what the combine kernel does
+    // for a head, here for the G heads of the group
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int old = atomicAdd(fz.counters + (size_t)t0 * n_kv + kvh, 1);
+      s_last = old == n_splits - 1;
+      if (s_last) fz.counters[(size_t)t0 * n_kv + kvh] = 0;     // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    float* wgt = so;                               // [G][n_eff] weights exp2(m_s - m) / l, in the (idle) K ring
+    for (int x = threadIdx.x; x < rows * n_eff; x += blockDim.x) {
+      const int r = x / n_eff;
+      const size_t base = ((size_t)t0 * n_q + kvh * G + r) * n_splits;
+      float mm = -INFINITY, ll = 0.f;
+      for (int s2 = 0; s2 < n_eff; ++s2) mm = fmaxf(mm, __ldcg(pm + base + s2));
+      for (int s2 = 0; s2 < n_eff; ++s2) {
+        const float ms = __ldcg(pm + base + s2);
+        if (ms != -INFINITY) ll += __ldcg(pl + base + s2) * exp2f(ms - mm);
+      }
+      const float ms = __ldcg(pm + base + x % n_eff);
+      wgt[x] = (ms != -INFINITY && ll > 0.f) ? exp2f(ms - mm) / ll : 0.f;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < rows * PF_D; idx += blockDim.x) {
+      const int r = idx / PF_D, d = idx % PF_D, h = kvh * G + r;
+      const size_t base = ((size_t)t0 * n_q + h) * n_splits;
+      float a = 0.f;
+      for (int s0 = 0; s0 < n_eff; s0 += 8) {
+        float pv[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) pv[k] = (s0 + k < n_eff) ? __ldcg(po + (base + s0 + k) * PF_D + d) : 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          if (s0 + k < n_eff) a += pv[k] * wgt[r * n_eff + s0 + k];
+      }
+      if (gated) a *= sigmoid_f(__bfloat162float(gate_src[(size_t)t0 * gate_ld + (size_t)h * 2 * PF_D + PF_D + d]));
+      out[((size_t)t0 * n_q + h) * PF_D + d] = __float2bfloat16(a);
     }
   }
 }
@@ -943,24 +1084,57 @@ TRL_API int trl_attn_decode_mma(const void* q, const void* gate_src, int gate_ld
   cudaStream_t st = (cudaStream_t)stream;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(attn_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DM_SMEM) != cudaSuccess)
+    if (cudaFuncSetAttribute(attn_decode_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DM_SMEM) != cudaSuccess)
       return 3;
     configured = true;
   }
   DmMaps maps;
   if (dm_get_maps(kcache, vcache, n_blocks, n_kv, &maps)) return (int)cudaErrorInvalidValue;
   const dim3 grid(n_splits, n_kv, (T + tpg - 1) / tpg);
-  cudaError_t e = trl_launch(attn_decode_mma_kernel, grid, dim3((DM_WARPS + 1) * 32), (size_t)DM_SMEM, st, maps.mk, maps.mv,
+  DmFused none = {};
+  cudaError_t e = trl_launch(attn_decode_mma_kernel<false>, grid, dim3((DM_WARPS + 1) * 32), (size_t)DM_SMEM, st, maps.mk, maps.mv,
                              maps.mode3d, (const bf16*)q, (const bf16*)gate_src, gate_ld,
                              (const int*)block_table, max_blocks, (const int*)seq_ids, (const int*)positions,
                              (float*)po, (float*)pm, (float*)pl, (bf16*)out, T, n_q, n_kv, n_splits, tpg,
-                             scale * 1.4426950408889634f, gated);
+                             scale * 1.4426950408889634f, gated, none);
   if (e != cudaSuccess) return (int)e;
   if (n_splits > 1)
     e = trl_launch(attn_combine_kernel, dim3(T, n_q), dim3(min(D, 256)), 0, st, (const float*)po,
                    (const float*)pm, (const float*)pl, (const bf16*)gate_src, gate_ld, (bf16*)out, n_q,
                    D, n_splits, gated);
   return (int)e;
+}
+
+// The whole attention layer of a decode tick in ONE launch (bf16 pool, D = 256, rotary width 64, one new
+// token per sequence): q / k RMSNorm + rotation + KV write, split-KV attention on the tensor cores, merge of
+// the splits by the last CTA of each (token, kv head) and the sigmoid gate.  qkv: the fused projection rows
+// [T, ld]; counters: T * n_kv ints, zero on entry and zero again on exit.  Scratch as trl_attn_paged.
+TRL_API int trl_attn_decode_fused(const void* qkv, int ld, const void* q_norm, const void* k_norm, const void* positions,
+                                  const void* slot_mapping, void* kcache, void* vcache, const void* block_table,
+                                  int max_blocks, int n_blocks, const void* seq_ids, void* po, void* pm, void* pl,
+                                  void* counters, void* out, int T, int n_q, int n_kv, int D, int rotary, float theta,
+                                  float eps, int n_splits, float scale, int gated, void* stream) {
+  if (D != PF_D || rotary != 2 * DM_ROT_HALF || n_kv <= 0 || n_q <= 0 || n_q % n_kv != 0 || n_q / n_kv > DM_ROWS ||
+      T <= 0 || n_splits < 1 || n_splits > COMBINE_SPLITS || n_blocks <= 0 || ((uintptr_t)kcache & 15) ||
+      ((uintptr_t)vcache & 15) || ((uintptr_t)qkv & 15) || ld % 8 != 0)
+    return (int)cudaErrorInvalidValue;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_decode_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DM_SMEM) != cudaSuccess)
+      return 3;
+    configured = true;
+  }
+  DmMaps maps;
+  if (dm_get_maps(kcache, vcache, n_blocks, n_kv, &maps)) return (int)cudaErrorInvalidValue;
+  DmFused fz;
+  fz.q_norm = (const float*)q_norm, fz.k_norm = (const float*)k_norm, fz.slot_mapping = (const int*)slot_mapping;
+  fz.kcache = (bf16*)kcache, fz.vcache = (bf16*)vcache, fz.counters = (int*)counters;
+  fz.log2_theta = log2f(theta), fz.eps = eps, fz.rotary = rotary;
+  return (int)trl_launch(attn_decode_mma_kernel<true>, dim3(n_splits, n_kv, T), dim3((DM_WARPS + 1) * 32), (size_t)DM_SMEM,
+                         (cudaStream_t)stream, maps.mk, maps.mv, maps.mode3d, (const bf16*)qkv, (const bf16*)qkv, ld,
+                         (const int*)block_table, max_blocks, (const int*)seq_ids, (const int*)positions, (float*)po,
+                         (float*)pm, (float*)pl, (bf16*)out, T, n_q, n_kv, n_splits, 1, scale * 1.4426950408889634f, gated,
+                         fz);
 }
 
 // ---- allocation-free variant (declared in attn_static.h) --------------------------------------

@@ -796,6 +796,68 @@ def test_tensor_core_decode_attention_matches_scalar_kernel_and_oracle(w, hist, 
         assert float((outs[mode] - outs["scalar"]).abs().max()) < 0.03, mode
 
 
+@pytest.mark.parametrize("n_q,n_kv", [(24, 4), (8, 2)])
+def test_fused_decode_attention_layer_equals_the_three_launches(n_q, n_kv):
+    """The one-launch form of a decode tick's attention layer (prep + split-KV attention + merge; an
+    option of the backend): against the three-launch form
+    (outputs, and the K / V rows both write into the pool) and the fp32 oracle, with non-trivial norm
+    weights, contexts of 1 key, inside a page, inside a tile and over many tiles, split counts 1, 5 and
+    the backend's choice; twice for the same bits; the arrival counters are back at zero."""
+    import dataclasses
+    from tilerl_b200.batch import Batch
+    from tilerl_b200.config import small_gpu
+    from tilerl_b200.factory import make_ops
+    from tilerl_b200.kv import PagedKvPool
+    from tilerl_b200.ops.backend import RefOps
+    cfg = dataclasses.replace(small_gpu(), n_q_heads=n_q, n_kv_heads=n_kv)
+    assert cfg.head_dim == 256 and cfg.rotary_dim == 64
+    ops = make_ops("cuda")
+    assert ops.attn_mma and hasattr(ops.lib, "trl_attn_decode_fused")
+    d = cfg.head_dim
+    rows = n_q * 2 * d + 2 * n_kv * d
+    g0 = torch.Generator().manual_seed(5)
+    lp = {"q_norm": (1 + 0.2 * torch.randn(d, generator=g0)).cuda(), "k_norm": (1 + 0.2 * torch.randn(d, generator=g0)).cuda()}
+    hist = [0, 9, 70, 300, 1000]
+    outs, pools = {}, {}
+    for mode in ("fused1", "fused5", "fused_auto", "fused_auto2", "three", "ref"):
+        pool = PagedKvPool(cfg, 128, "cuda", dtype=torch.bfloat16 if mode != "ref" else torch.float32)
+        o = RefOps() if mode == "ref" else ops
+        ops.attn_fused = mode.startswith("fused")
+        ops.attn_splits = {"fused1": 1, "fused5": 5}.get(mode, 0)
+        blk, seqs_hist, seqs_now = 1, [], []
+        for i, h in enumerate(hist):
+            nb = (1 + h + 15) // 16
+            blocks = list(range(blk, blk + nb))
+            blk += nb
+            if h:
+                seqs_hist.append(dict(tokens=[0] * h, start=0, blocks=blocks, slot=i + 1))
+            seqs_now.append(dict(tokens=[0], start=h, blocks=blocks, slot=i + 1))
+        gg = torch.Generator().manual_seed(13)
+        for seqs in (seqs_hist, seqs_now):
+            batch = Batch.build(seqs, "cuda")
+            t = sum(len(s_["tokens"]) for s_ in seqs)
+            qkv = (torch.randn(t, rows, generator=gg) * 0.5).cuda().to(torch.bfloat16)
+            res = o.attention(qkv, lp, batch, pool, 0, cfg, n_q, n_kv)
+        outs[mode] = res.float().clone()
+        kc, vc = pool.layer(0)
+        pools[mode] = (kc.float().clone(), vc.float().clone())
+    ops.attn_fused, ops.attn_splits = False, 0
+    torch.cuda.synchronize()
+    ref_o = outs["ref"]
+    for mode in ("fused1", "fused5", "fused_auto", "three"):
+        err = float((outs[mode] - ref_o).abs().max())
+        assert err < 0.03 * float(ref_o.abs().max()) + 0.02, (mode, err)
+        assert float((outs[mode] - outs["three"]).abs().max()) < 0.03, mode
+        # the pool rows the tick wrote: bf16 roundings of the same fp32 values (the two forms sum the
+        # squares of a row in a different order)
+        for a, b in zip(pools[mode], pools["three"]):
+            assert float((a - b).abs().max()) <= 0.02 * float(b.abs().max()), mode
+    assert torch.equal(outs["fused_auto"], outs["fused_auto2"])
+    assert int(ops._attn_counters.abs().sum()) == 0
+    from tilerl_b200.ops import native
+    assert native.read_error()[0] == 0
+
+
 @pytest.mark.parametrize("m", [1, 2])
 @pytest.mark.parametrize("h,ffn,inner", [(1024, 3072, 2048), (5120, 2176, 1152)])
 def test_chained_projections_equal_separate_launches(ops, m, h, ffn, inner):

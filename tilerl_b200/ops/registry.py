@@ -114,6 +114,8 @@ register("fp8", "sm100", {
     "quant_fp8": Kernel("quant_act_fp8_kernel", "csrc/gemm_fp8.cu", "trl_quant_act_fp8",
                         note="RMSNorm / SwiGLU + e4m3 with one scale per token and 128 k"),
     "attn_prep": Kernel("attn_prep_fp8_kernel", "csrc/attn_fp8.cu", "trl_attn_prep_fp8", note="e4m3 KV pool"),
+    "paged_attention_decode_fused": Kernel("attn_decode_mma_kernel<true>", "csrc/attn.cu", "trl_attn_decode_fused",
+                                           note="decode ticks, optional: prep + split-KV attention + split merge in one launch"),
     "paged_attention_decode": Kernel("attn_split_fp8_kernel", "csrc/attn_fp8.cu", "trl_attn_paged_fp8"),
     "paged_attention_prefill": Kernel("attn_prefill_kernel<true>", "csrc/attn.cu", "trl_attn_prefill_fp8"),
 })
