@@ -156,6 +156,14 @@ def test_sparse_decode_runs_on_gpu(setup):
     eng = build_engine(model, ops, slots=2, max_ctx=512, graph=False, prefix=False, sparse=small)
     got = eng.generate(p, sp)[0].tokens
     assert len(got) == 8 and small.stats["sparse_ticks"] > 0
+    # the selection ran on the device (score + radix-select kernels), and equals the torch selection:
+    # the same engine with the kernels hidden commits the same tokens
+    assert small.stats["device_selects"] > 0 and small.stats["device_selects"] == small.stats["refreshes"]
+    host = SparseKV(cfg, SparseConfig(top_k=3, window=2, refresh_ticks=2, min_tokens=64),
+                    score_fn=lambda q, b: __import__("tilerl_b200.sparse", fromlist=["quest_scores"]).quest_scores(q, b))
+    eng = build_engine(model, ops, slots=2, max_ctx=512, graph=False, prefix=False, sparse=host)
+    assert eng.generate(p, sp)[0].tokens == got
+    assert host.stats["device_selects"] == 0 and host.stats["refreshes"] > 0
 
 
 def test_seeded_sampling_is_reproducible_on_gpu(setup):

@@ -241,6 +241,42 @@ def test_spec_accept_kernel_counts_reproduced_drafts_and_selects_the_state_plane
     assert native.read_error()[0] == 0
 
 
+@pytest.mark.parametrize("n_pages,k", [(1, 4), (37, 8), (700, 128), (2500, 128)])
+def test_quest_score_and_topk_kernels_match_the_torch_selection(ops, n_pages, k):
+    """Device page selection against the torch statement of it: Quest upper bounds from the K pages
+    (no bounds tensor), and the ascending indices of the k largest, on page tables in shuffled order,
+    k >= pages, and scores with ties at the k-th value (lowest page indices win)."""
+    from tilerl_b200.ops import native
+    from tilerl_b200.sparse import SparseKV, quest_scores
+    n_q, n_kv, d = 24, 4, 256
+    g = torch.Generator().manual_seed(n_pages + k)
+    kc = (torch.randn(n_pages + 3, n_kv, 16, d, generator=g)).to(DEV, torch.bfloat16)
+    q = torch.randn(n_q, d, generator=g).to(DEV, torch.bfloat16)
+    table = (torch.randperm(n_pages, generator=g) + 2).to(DEV, torch.int32)
+    sel = ops.quest_select(q, kc, table, k)
+    torch.cuda.synchronize()
+    want_scores = quest_scores(q, SparseKV.page_bounds(None, kc, table))
+    got_scores = ops.ws.get("quest_scores", (n_pages,), torch.float32)
+    assert _rel(got_scores, want_scores) < 1e-5
+    kk = min(k, n_pages)
+    assert sel.shape == (kk,)
+    # selection from the kernel's own scores (fp32 sums in another order may swap near-equal neighbours)
+    want = torch.sort(torch.topk(got_scores, kk).indices).values
+    assert torch.equal(sel, want)
+    # ties: scores quantised to a few values; the kept set is every page above the k-th value plus the
+    # lowest-index pages at it
+    if n_pages > k:
+        tied = torch.randint(0, 5, (n_pages,), generator=g).float().to(DEV)
+        out = torch.empty(k, dtype=torch.int64, device=DEV)
+        native.check(ops.lib.trl_topk_pages(tied.data_ptr(), n_pages, k, out.data_ptr(), native.stream()), "topk")
+        torch.cuda.synchronize()
+        kth = torch.sort(tied, descending=True).values[k - 1]
+        above = torch.nonzero(tied > kth).flatten()
+        at = torch.nonzero(tied == kth).flatten()[:k - above.numel()]
+        assert torch.equal(out, torch.sort(torch.cat([above, at])).values)
+    assert native.read_error()[0] == 0
+
+
 def test_quant_kernel_bit_exact_and_dequant(ops):
     g = torch.Generator().manual_seed(3)
     for dtype in (torch.float32, torch.bfloat16):

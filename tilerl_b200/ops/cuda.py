@@ -426,7 +426,7 @@ class CudaOps:
             N.count(2)
             return out
         if sparse_now:
-            table, pos = sp.packed(attn_idx, q, kc)    # same kernel on [selected pages ; trailing window]
+            table, pos = sp.packed(attn_idx, q, kc, ops=self)    # same kernel on [selected pages ; trailing window]
         mma = self.attn_mma and d == 256 and n_q % n_kv == 0 and n_q // n_kv <= 16
         tpg = self._tokens_per_group(batch, t, n_q // n_kv) if mma else 1
         splits = self.attn_splits or self._pick_splits(batch, t // tpg if mma else t, n_kv, 64 if mma else 32)
@@ -585,6 +585,25 @@ class CudaOps:
             full = self.comm.all_gather_logits(logits)
             return full[..., :self.vocab] if self.vocab else full
         return logits
+
+    def quest_select(self, q, kcache, table_early, k: int):
+        """Indices (ascending, int64) of the ``k`` early pages with the largest Quest upper bound for the
+        token whose prepared query rows are ``q [n_q, D]``: one scoring kernel that reads each page's K rows
+        once (min / max per dimension in registers) and one radix-select kernel; ``None`` for shapes the
+        kernels do not take (the caller then scores with torch)."""
+        n = int(table_early.numel())
+        n_kv, d = kcache.shape[1], kcache.shape[-1]
+        if d != 256 or kcache.dtype != torch.bfloat16 or q.dtype != torch.bfloat16 or n == 0 or k <= 0:
+            return None
+        self.flush()
+        scores = self.ws.get("quest_scores", (n,), torch.float32)
+        tab = table_early.to(torch.int32).contiguous()
+        N.check(self.lib.trl_quest_scores(q.contiguous().data_ptr(), kcache.data_ptr(), tab.data_ptr(), scores.data_ptr(),
+                                          n, q.shape[0], n_kv, d, N.stream()), "quest_scores")
+        sel = torch.empty(min(k, n), dtype=torch.int64, device=kcache.device)
+        N.check(self.lib.trl_topk_pages(scores.data_ptr(), n, k, sel.data_ptr(), N.stream()), "topk_pages")
+        N.count(2)
+        return sel
 
     def spec_accept(self, tok, batch, cur, pack) -> None:
         """Greedy acceptance of a verify tick on the device: ``pack[:B*W]`` gets the argmax tokens,

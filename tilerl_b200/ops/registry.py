@@ -135,6 +135,10 @@ register("any", "sm100", {
     "argmax": Kernel("argmax_stage1_kernel + argmax_stage2_kernel", "csrc/misc.cu", "trl_argmax"),
     "sample": Kernel("sample_softmax_kernel", "csrc/misc.cu", "trl_sample_softmax"),
     "sample_nucleus": Kernel("sample_nucleus_kernel", "csrc/misc.cu", "trl_sample_nucleus"),
+    "page_bounds": Kernel("quest_score_kernel", "csrc/sparse.cu", "trl_quest_scores",
+                          note="min / max of a K page per dimension in registers + Quest upper bound, one CTA per page"),
+    "select_pages": Kernel("topk_pages_kernel", "csrc/sparse.cu", "trl_topk_pages",
+                           note="k-th largest by radix select, kept page indices ascending"),
     "spec_accept": Kernel("spec_accept_kernel", "csrc/misc.cu", "trl_spec_accept",
                           note="greedy accept length + GDN state-plane selection of a verify tick, inside its graph"),
     "lora": Kernel("lora_a_kernel + lora_b_kernel", "csrc/misc.cu", "trl_lora_add"),

@@ -75,8 +75,9 @@ class _View:
     def active(self, attn_idx: int) -> bool:
         return any(self.use)
 
-    def packed(self, attn_idx: int, q: torch.Tensor, kcache: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-        """Packed block table ``[B, P]`` and the causal bound ``packed_len - 1`` per token."""
+    def packed(self, attn_idx: int, q: torch.Tensor, kcache: torch.Tensor, ops=None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Packed block table ``[B, P]`` and the causal bound ``packed_len - 1`` per token.  ``ops``: a
+        backend with ``quest_select`` scores and selects on the device (two kernels per refresh)."""
         b = self.batch
         rows, lens = [], []
         for r, rid in enumerate(self.rids):
@@ -87,7 +88,7 @@ class _View:
                 rows.append(table)
                 lens.append(kv_len)
                 continue
-            sel = self.mgr.selection(rid, attn_idx, q[r], table, kcache, n_pages)   # decode-only: token r
+            sel = self.mgr.selection(rid, attn_idx, q[r], table, kcache, n_pages, ops=ops)   # decode-only: token r
             rows.append(table[sel])
             tail_tokens = kv_len - (n_pages - 1) * KV_BLOCK      # tokens in the last (own) page
             lens.append((sel.numel() - 1) * KV_BLOCK + tail_tokens)
@@ -109,7 +110,7 @@ class SparseKV:
         self._sel: Dict[Tuple[int, int], torch.Tensor] = {}     # (rid, layer) -> kept early pages
         self._age: Dict[Tuple[int, int], int] = {}
         self._early: Dict[Tuple[int, int], int] = {}
-        self.stats = dict(sparse_ticks=0, dense_ticks=0, refreshes=0)
+        self.stats = dict(sparse_ticks=0, dense_ticks=0, refreshes=0, device_selects=0)
 
     # engine hooks ---------------------------------------------------------------------------
     def for_batch(self, batch, rids: List[int]):
@@ -136,7 +137,7 @@ class SparseKV:
         return torch.stack([pages.amin(2), pages.amax(2)], dim=2)
 
     def selection(self, rid: int, layer: int, q: torch.Tensor, table: torch.Tensor, kcache: torch.Tensor,
-                  n_pages: int) -> torch.Tensor:
+                  n_pages: int, ops=None) -> torch.Tensor:
         """Kept page indices (ascending, ending with the sequence's trailing window)."""
         key = (rid, layer)
         n_win = min(self.c.window, n_pages)
@@ -145,12 +146,18 @@ class SparseKV:
         cached = self._sel.get(key)
         if cached is None or age >= self.c.refresh_ticks:
             if early > 0 and self.c.top_k > 0:
-                if self.indexer is not None:
-                    scores = self.indexer.scores(layer, q, kcache, table[:early])
-                else:
-                    scores = self.score_fn(q, self.page_bounds(kcache, table[:early]))
                 k = min(self.c.top_k, early)
-                cached = torch.sort(torch.topk(scores, k).indices).values
+                cached = None
+                if self.indexer is None and self.score_fn is quest_scores and hasattr(ops, "quest_select"):
+                    cached = ops.quest_select(q, kcache, table[:early], k)      # device: score + select, two kernels
+                    if cached is not None:
+                        self.stats["device_selects"] += 1
+                if cached is None:
+                    if self.indexer is not None:
+                        scores = self.indexer.scores(layer, q, kcache, table[:early])
+                    else:
+                        scores = self.score_fn(q, self.page_bounds(kcache, table[:early]))
+                    cached = torch.sort(torch.topk(scores, k).indices).values
             else:
                 cached = torch.zeros(0, dtype=torch.long, device=table.device)
             self._sel[key] = cached
