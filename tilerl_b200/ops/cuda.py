@@ -99,8 +99,8 @@ class CudaOps:
         # TRL_GEMV_MMA=1: 3..16 rows against NVFP4 weights go to the mma.sync kernel with f16 activations
         # (csrc/gemv_mma.cu) instead of the activation quantiser + tcgen05 GEMM.  Off by default: launch for
         # launch it ties with that pair on the 27B shapes (gate_up at 8 rows 34.1 us against 34.6), but inside
-        # a B = 8 decode tick it loses, 14.5 ms against 10.65: decoding e2m1 on the CUDA cores costs 26
-        # instructions per MMA (issue slots 46 % busy, no pipe saturated), and its staging of the activation rows
+        # a B = 8 decode tick it loses, 14.5 ms against 10.65: decoding e2m1 on the CUDA cores costs 23.5
+        # instructions per MMA (issue slots 45 % busy, no pipe saturated), and its staging of the activation rows
         # sits behind the dependency of every launch where the GEMM's prologue does not.
         self.gemv_mma = os.environ.get("TRL_GEMV_MMA", "0") == "1" and hasattr(self.lib, "trl_gemv_nvfp4_mma")
         # TRL_ATTN_FUSED=1: decode ticks run prep, split-KV attention and the merge of the splits as ONE launch
