@@ -304,6 +304,13 @@ constexpr int PF_D = 256, PF_TQ = 16, PF_BC = 32, PF_ROW = PF_D * 2 /*bytes*/, P
 
 // byte offset of 16-byte chunk `c` of row `r` in a swizzled [rows][512 B] tile
 __device__ __forceinline__ uint32_t pf_off(int r, int c) { return (uint32_t)(r * PF_ROW + ((c ^ (r & 7)) << 4)); }
+// bf16 pool: a K / V tile of 32 keys is two pages, each brought by one tiled copy as four slabs
+// [16 keys][128 B] under the tensor map's 128-byte swizzle (see attn_decode_mma_kernel below)
+__device__ __forceinline__ uint32_t pt_off(int r, int c) {
+  return (uint32_t)((r >> 4) * (KVB * PF_ROW) + (c >> 3) * (KVB * 128) + (r & 15) * 128 + (((c & 7) ^ (r & 7)) << 4));
+}
+__device__ __forceinline__ uint32_t dm_try_wait(uint32_t bar, uint32_t parity);
+constexpr long long PF_WAIT_CYCLES = 4000000000LL;
 
 // FP8: the pool holds e4m3 rows with one fp32 scale per (token, kv head).  The raw bytes of the
 // next tile are staged with cp.async (double buffered) while this tile is computed; a conversion
@@ -332,8 +339,13 @@ attn_prefill_kernel(const bf16* q, const bf16* gate_src, int gate_ld,
                     const float* kscale, const float* vscale,
                     const int* block_table, int max_blocks, const int* q_start,
                     const int* q_len, const int* positions, bf16* out,
-                    int n_q, int n_kv, float scale_log2e, int gated) {
-  extern __shared__ __align__(1024) unsigned char pf_smem[];
+                    int n_q, int n_kv, float scale_log2e, int gated,
+                    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, int map3d) {
+  extern __shared__ unsigned char pf_smem_raw[];
+  __shared__ uint64_t pf_full[2];
+  __shared__ volatile int pf_ok;
+  const uint32_t pf_raw_a = (uint32_t)__cvta_generic_to_shared(pf_smem_raw);
+  unsigned char* pf_smem = pf_smem_raw + (((pf_raw_a + 1023u) & ~1023u) - pf_raw_a);    // swizzle atoms are 1024-byte aligned
   pdl_launch_dependents();
   pdl_wait();
   const int tile = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
@@ -382,6 +394,31 @@ attn_prefill_kernel(const bf16* q, const bf16* gate_src, int gate_ld,
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
+  // bf16 pool: thread 0 issues one tiled copy per K / V page of the tile (two pages), counted on full[buf]
+  const uint32_t full_a = (uint32_t)__cvta_generic_to_shared(pf_full);
+  auto load_kv_tma = [&](int kt, int buf) {
+    const int j0 = kt * PF_BC;
+    const int n_pg = min(PF_BC / KVB, (n_keys - j0 + KVB - 1) / KVB);
+    const uint32_t bar = full_a + 8u * buf;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(n_pg * 2 * KVB * PF_ROW)) : "memory");
+    for (int pg = 0; pg < n_pg; ++pg) {
+      const int y = (table[j0 / KVB + pg] * n_kv + kvh) * KVB;
+      const uint32_t dk = ks_a + buf * PF_BC * PF_ROW + pg * (KVB * PF_ROW), dv = vs_a + buf * PF_BC * PF_ROW + pg * (KVB * PF_ROW);
+      if (map3d) {
+        asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                     ::"r"(dk), "l"(&map_k), "r"(0), "r"(y), "r"(0), "r"(bar) : "memory");
+        asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                     ::"r"(dv), "l"(&map_v), "r"(0), "r"(y), "r"(0), "r"(bar) : "memory");
+      } else {
+        for (int sl = 0; sl < 4; ++sl) {
+          asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                       ::"r"(dk + sl * (KVB * 128)), "l"(&map_k), "r"(sl * 64), "r"(y), "r"(bar) : "memory");
+          asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                       ::"r"(dv + sl * (KVB * 128)), "l"(&map_v), "r"(sl * 64), "r"(y), "r"(bar) : "memory");
+        }
+      }
+    }
+  };
   auto stage_fp8 = [&](int kt, int sb) {
     const int j0 = kt * PF_BC;
     const unsigned char* k8 = reinterpret_cast<const unsigned char*>(kcache);
@@ -429,23 +466,55 @@ attn_prefill_kernel(const bf16* q, const bf16* gate_src, int gate_ld,
   for (int i = 0; i < PF_D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
 
-  if constexpr (FP8) stage_fp8(0, 0);
-  else load_kv(0, 0);
+  auto kv_off = [](int r, int c) { return FP8 ? pf_off(r, c) : pt_off(r, c); };
+  if constexpr (!FP8) {
+    // barriers; the V buffers start as zeros (a tile whose second page lies past the bound is not copied
+    // there, and 0 x whatever shared memory held must be 0)
+    if (threadIdx.x == 0) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(full_a));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(full_a + 8u));
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      pf_ok = 1;
+    }
+    for (int x = threadIdx.x; x < 2 * PF_BC * PF_CHUNKS; x += blockDim.x)
+      *reinterpret_cast<uint4*>(vs + (size_t)x * 16) = make_uint4(0u, 0u, 0u, 0u);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x == 0) load_kv_tma(0, 0);
+  } else {
+    (void)load_kv;
+    stage_fp8(0, 0);
+  }
   for (int kt = 0; kt < n_tiles; ++kt) {
     const int buf = FP8 ? 0 : (kt & 1);
-    if (kt + 1 < n_tiles) {
-      if constexpr (FP8) stage_fp8(kt + 1, (kt + 1) & 1);
-      else load_kv(kt + 1, buf ^ 1);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
-    __syncthreads();
+    bool have = true;
     if constexpr (FP8) {
+      if (kt + 1 < n_tiles) {
+        stage_fp8(kt + 1, (kt + 1) & 1);
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+      } else {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+      }
+      __syncthreads();
       convert_fp8(kt, kt & 1);
       __syncthreads();
+    } else {
+      if (kt + 1 < n_tiles && threadIdx.x == 0) load_kv_tma(kt + 1, buf ^ 1);
+      const uint32_t bar = full_a + 8u * buf, parity = (uint32_t)(kt >> 1) & 1u;
+      if (!dm_try_wait(bar, parity)) {
+        const long long t_begin = clock64();
+        for (uint32_t it = 1; !dm_try_wait(bar, parity); ++it) {
+          if ((it & 63) == 0 && (!pf_ok || clock64() - t_begin > PF_WAIT_CYCLES)) {
+            if (pf_ok) trl_set_error(TRL_ERR_MBAR_TIMEOUT, (int)blockIdx.x, 420 + buf, kt);
+            pf_ok = 0;
+            have = false;
+            break;
+          }
+        }
+      }
     }
     const uint32_t kb = ks_a + buf * PF_BC * PF_ROW, vb = vs_a + buf * PF_BC * PF_ROW;
+    if (have) {
     // ---- S = Q K^T for 32 keys: 4 n-tiles of 8 keys
     float sc[4][4];
 #pragma unroll
@@ -457,7 +526,7 @@ attn_prefill_kernel(const bf16* q, const bf16* gate_src, int gate_ld,
 #pragma unroll
       for (int np = 0; np < 2; ++np) {             // two n-tiles per ldmatrix.x4
         uint32_t b[4];
-        ldsm_x4(b, kb + pf_off(np * 16 + (lane & 7) + (lane >> 4) * 8, kk * 2 + ((lane >> 3) & 1)));
+        ldsm_x4(b, kb + kv_off(np * 16 + (lane & 7) + (lane >> 4) * 8, kk * 2 + ((lane >> 3) & 1)));
         mma_bf16(sc[np * 2], a, b[0], b[1]);
         mma_bf16(sc[np * 2 + 1], a, b[2], b[3]);
       }
@@ -506,12 +575,16 @@ attn_prefill_kernel(const bf16* q, const bf16* gate_src, int gate_ld,
 #pragma unroll
       for (int nd = 0; nd < PF_D / 8; nd += 2) {
         uint32_t b[4];
-        ldsm_x4_t(b, vb + pf_off(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, nd + (lane >> 4)));
+        ldsm_x4_t(b, vb + kv_off(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, nd + (lane >> 4)));
         mma_bf16(o[nd], pa[kk], b[0], b[1]);
         mma_bf16(o[nd + 1], pa[kk], b[2], b[3]);
       }
     }
+    }
     __syncthreads();                               // the other buffer may be overwritten next round
+    if constexpr (!FP8) {
+      if (!pf_ok) break;                           // a wait ran out (error word set): every thread leaves together
+    }
   }
   // ---- epilogue: normalise, gate, store
   const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
@@ -1156,24 +1229,28 @@ TRL_API size_t trl_attn_static_scratch_needed(int T, int n_q, int D, int n_split
 // Tiled prefill attention over whole sequences of the batch (D = 256, G = n_q / n_kv <= 8):
 // q_start / q_len give each sequence's token range in the flat batch; `out` [T, n_q * D].
 TRL_API int trl_attn_prefill(const void* q, const void* gate_src, int gate_ld, const void* kcache, const void* vcache,
-                             const void* block_table, int max_blocks, const void* q_start, const void* q_len,
+                             const void* block_table, int max_blocks, int n_blocks, const void* q_start, const void* q_len,
                              const void* positions, void* out, int B, int max_q_len, int n_q, int n_kv, int D,
                              float scale, int gated, void* stream) {
   const int G = n_kv > 0 ? n_q / n_kv : 0;
   if (D != PF_D || G < 1 || G > 8 || n_q % n_kv != 0 || B <= 0 || max_q_len <= 0) return (int)cudaErrorInvalidValue;
-  const size_t smem = (size_t)G * PF_TQ * PF_ROW + (size_t)4 * PF_BC * PF_ROW;
+  if (n_blocks <= 0 || ((uintptr_t)kcache & 15) || ((uintptr_t)vcache & 15)) return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)G * PF_TQ * PF_ROW + (size_t)4 * PF_BC * PF_ROW + 1024;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(attn_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * PF_TQ * PF_ROW + 4 * PF_BC * PF_ROW) != cudaSuccess)
+    if (cudaFuncSetAttribute(attn_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * PF_TQ * PF_ROW + 4 * PF_BC * PF_ROW + 1024) != cudaSuccess)
       return 3;
     configured = true;
   }
+  DmMaps maps;
+  if (dm_get_maps(kcache, vcache, n_blocks, n_kv, &maps)) return (int)cudaErrorInvalidValue;
   const dim3 grid((max_q_len + PF_TQ - 1) / PF_TQ, n_kv, B);
   return (int)trl_launch(attn_prefill_kernel<false>, grid, dim3(G * 32), smem, (cudaStream_t)stream, (const bf16*)q,
                          (const bf16*)gate_src, gate_ld, (const bf16*)kcache, (const bf16*)vcache,
                          (const float*)nullptr, (const float*)nullptr,
                          (const int*)block_table, max_blocks, (const int*)q_start, (const int*)q_len,
-                         (const int*)positions, (bf16*)out, n_q, n_kv, scale * 1.4426950408889634f, gated);
+                         (const int*)positions, (bf16*)out, n_q, n_kv, scale * 1.4426950408889634f, gated, maps.mk, maps.mv,
+                         maps.mode3d);
 }
 
 // The same over an e4m3 pool: kcache / vcache are the e4m3 bytes of one layer, kscale / vscale its
@@ -1185,7 +1262,7 @@ TRL_API int trl_attn_prefill_fp8(const void* q, const void* gate_src, int gate_l
                                  float scale, int gated, void* stream) {
   const int G = n_kv > 0 ? n_q / n_kv : 0;
   if (D != PF_D || G < 1 || G > 8 || n_q % n_kv != 0 || B <= 0 || max_q_len <= 0) return (int)cudaErrorInvalidValue;
-  constexpr size_t kv_bytes = (size_t)2 * PF_BC * PF_ROW + (size_t)4 * PF_BC * PF_D + (size_t)4 * PF_BC * sizeof(float);
+  constexpr size_t kv_bytes = (size_t)2 * PF_BC * PF_ROW + (size_t)4 * PF_BC * PF_D + (size_t)4 * PF_BC * sizeof(float) + 1024;
   const size_t smem = (size_t)G * PF_TQ * PF_ROW + kv_bytes;
   static bool configured = false;
   if (!configured) {
@@ -1199,7 +1276,8 @@ TRL_API int trl_attn_prefill_fp8(const void* q, const void* gate_src, int gate_l
                          (const bf16*)gate_src, gate_ld, (const bf16*)kcache, (const bf16*)vcache,
                          (const float*)kscale, (const float*)vscale,
                          (const int*)block_table, max_blocks, (const int*)q_start, (const int*)q_len,
-                         (const int*)positions, (bf16*)out, n_q, n_kv, scale * 1.4426950408889634f, gated);
+                         (const int*)positions, (bf16*)out, n_q, n_kv, scale * 1.4426950408889634f, gated, CUtensorMap{},
+                         CUtensorMap{}, 0);
 }
 
 TRL_API int trl_attn_paged_static(const void* q, const void* gate_src, int gate_ld, const void* kcache,

@@ -420,9 +420,9 @@ class CudaOps:
             # 16 query tokens by the tiled tensor-core kernel
             N.check(self.lib.trl_attn_prefill(
                 q.data_ptr(), qkv.data_ptr(), qkv.stride(0), kc.data_ptr(), vc.data_ptr(), table.data_ptr(),
-                table.stride(0), batch.q_start.data_ptr(), batch.q_len.data_ptr(), pos.data_ptr(), out.data_ptr(),
-                batch.n_seqs, batch.max_q_len, n_q, n_kv, d, 1.0 / math.sqrt(d), int(cfg.attn_gated), st),
-                "attn_prefill")
+                table.stride(0), kc.shape[0], batch.q_start.data_ptr(), batch.q_len.data_ptr(), pos.data_ptr(),
+                out.data_ptr(), batch.n_seqs, batch.max_q_len, n_q, n_kv, d, 1.0 / math.sqrt(d), int(cfg.attn_gated),
+                st), "attn_prefill")
             N.count(2)
             return out
         if sparse_now:

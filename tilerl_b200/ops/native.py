@@ -64,7 +64,7 @@ _SIGS = {
     "trl_attn_prep_fp8": [P, I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P],
     "trl_attn_paged_fp8": [P, P, I, P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, F, I, P],
     "trl_attn_prefill_fp8": [P, P, I, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, F, I, P],
-    "trl_attn_prefill": [P, P, I, P, P, P, I, P, P, P, P, I, I, I, I, I, F, I, P],
+    "trl_attn_prefill": [P, P, I, P, P, P, I, I, P, P, P, P, I, I, I, I, I, F, I, P],
     "trl_lora_add": [P, I, P, F, P, P, P, P, I, I, I, I, I, F, P],
     "trl_adamw": [P, P, P, P, P, L, F, F, F, F, F, I, F, P],
     "trl_quant_nvfp4": [P, I, L, L, P, P, P, P, I, P],
