@@ -601,6 +601,11 @@ quant_act_kernel(const bf16* x, int ldx, const float* __restrict__ norm_w, float
                  uint8_t* xq, uint8_t* sf, float* rs, int K, int J,
                  int kt4, int swiglu_in) {
   __shared__ float red[32];
+  // one CTA per row (gridDim.y == 1): the pass that finds the row maximum leaves the (normalised) row in
+  // shared memory as bf16, and the quantising pass reads it from there -- read from L2 again, that pass
+  // is a chain of dependent loads, one per 1024 elements of the row
+  extern __shared__ __align__(16) uint2 qa_row[];
+  const bool staged = gridDim.y == 1;
   pdl_launch_dependents();
   pdl_wait();
   const int tok = blockIdx.x;
@@ -646,10 +651,62 @@ quant_act_kernel(const bf16* x, int ldx, const float* __restrict__ norm_w, float
       v[3] = __bfloat162float(__float2bfloat16(v[3] * rstd * w.w));
     }
     amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))));
+    if (staged) qa_row[k >> 2] = make_uint2(f2_to_bf162_bits(v[0], v[1]), f2_to_bf162_bits(v[2], v[3]));   // exact: v is bf16-valued
   }
   amax = block_max(amax, red);
   const float rs0 = fmaxf(amax, 1e-30f) * (1.f / (6.f * 448.f));
   if (blockIdx.y == 0 && threadIdx.x < J) rs[tok * J + threadIdx.x] = rs0 * exp2f(-2.f * (float)threadIdx.x);
+  if (staged) {
+    // one CTA per row: a thread takes whole 16-element blocks out of the staged row (the scale arithmetic
+    // is paid once per block, no shuffles; 8 bytes of e2m1 per term and block in one store).  Same
+    // arithmetic per element as the quarter-block form below, so the same bits.
+    const int n_blk = kt4 * 4;                            // 16-element blocks of the padded row
+    for (int b = threadIdx.x; b < n_blk; b += blockDim.x) {
+      const int k = b * 16;                               // K % 16 == 0: a block is whole or padding
+      float r[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) r[i] = 0.f;
+      if (k < K) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint2 u = qa_row[b * 4 + i];
+          const float2 a = bf162_bits_to_f2(u.x), b2 = bf162_bits_to_f2(u.y);
+          r[4 * i] = a.x, r[4 * i + 1] = a.y, r[4 * i + 2] = b2.x, r[4 * i + 3] = b2.y;
+        }
+      }
+      float rscale = rs0;
+      for (int j = 0; j < J; ++j, rscale *= 0.25f) {
+        const int col = tok * J + j;
+        float bm = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) bm = fmaxf(bm, fabsf(r[i]));
+        const float s = fminf(__fdividef(bm, 6.f * rscale), 448.f);
+        uint16_t s16;
+        asm("{ .reg .b16 t; cvt.rn.satfinite.e4m3x2.f32 t, %1, %2; mov.b16 %0, t; }" : "=h"(s16) : "f"(0.f), "f"(s));
+        const float sfv = h2_to_f2(cvt_e4m3x2_to_h2(s16)).x;
+        const float denom = sfv * rscale;
+        const float inv = denom > 0.f ? __frcp_rn(denom) : 0.f;
+        uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {                     // byte i: elements 2i (low nibble), 2i + 1
+          uint16_t by;
+          asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u16.u8 %0, t; }" : "=h"(by) : "f"(r[2 * i + 1] * inv), "f"(r[2 * i] * inv));
+          packed[i >> 2] |= (uint32_t)(by & 0xff) << (8 * (i & 3));
+          if (j + 1 < J) {                                // the next term encodes the remainder
+            uint32_t h;
+            asm("{ .reg .b8 t; cvt.u8.u16 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(h) : "h"(by));
+            const float2 d = h2_to_f2(h);
+            r[2 * i] = fmaf(-d.x, denom, r[2 * i]);
+            r[2 * i + 1] = fmaf(-d.y, denom, r[2 * i + 1]);
+          }
+        }
+        if (k < K) *reinterpret_cast<uint2*>(xq + (size_t)col * (K >> 1) + (size_t)b * 8) = make_uint2(packed[0], packed[1]);
+        sf[((size_t)(col >> 7) * kt4 + (b >> 2)) * SF_ATOM + (col & 31) * 16 + ((col & 127) >> 5) * 4 + (b & 3)] =
+            (k < K) ? (uint8_t)(s16 & 0xff) : (uint8_t)0;
+      }
+    }
+    return;
+  }
   // this thread's quarter blocks: one per slice; gridDim.y slices run in parallel, the rest in
   // a loop (one CTA per row when there are enough rows to fill the GPU: the row is then read
   // from L2 by one CTA instead of by every slice's CTA)
@@ -757,7 +814,15 @@ TRL_API int trl_quant_act_nvfp4(const void* x, int ldx, const void* norm_w, floa
   const int nk = (K + KT_ELEMS - 1) / KT_ELEMS;
   int slices = (nk * KT_ELEMS / 4 + 255) / 256;  // 4 elements per thread
   if (tokens >= 128) slices = 1;                        // enough rows to fill the GPU: one CTA per row
-  return (int)trl_launch(quant_act_kernel, dim3(tokens, slices), dim3(256), 0, (cudaStream_t)stream, (const bf16*)x,
+  const size_t smem = slices == 1 ? (size_t)((K + 3) / 4) * sizeof(uint2) : 0;      // the staged row, bf16
+  if (smem > 48 * 1024) {
+    static size_t configured = 0;
+    if (configured < smem) {
+      if (cudaFuncSetAttribute(quant_act_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 3;
+      configured = smem;
+    }
+  }
+  return (int)trl_launch(quant_act_kernel, dim3(tokens, slices), dim3(256), smem, (cudaStream_t)stream, (const bf16*)x,
                          ldx, (const float*)norm_w, eps, (uint8_t*)xq, (uint8_t*)sf, (float*)rs, K, J, nk * 4,
                          swiglu_in);
 }
