@@ -34,7 +34,7 @@ attn_prep_kernel(const bf16* qkv, int ld, const float* __restrict__ qw,
                  const float* __restrict__ kw, const int* positions,
                  const int* slot_mapping, bf16* q_out,
                  bf16* kcache, bf16* vcache, int n_q, int n_kv, int D,
-                 int rotary, float log2_theta, float eps, int gated) {
+                 int rotary, float log2_theta, float eps, int gated, int n_slots) {
   extern __shared__ float sm[];
   float* cs = sm;                 // [rotary/2] cos
   float* sn = sm + rotary / 2;    // [rotary/2] sin
@@ -54,7 +54,8 @@ attn_prep_kernel(const bf16* qkv, int ld, const float* __restrict__ qw,
   __syncthreads();
   const bf16* row = qkv + (size_t)t * ld;
   const int per_q = gated ? 2 * D : D;
-  const int slot = slot_mapping[t];
+  int slot = slot_mapping[t];
+  if (slot >= 0) slot = trl_checked(slot, n_slots, 1);
   float* hb = buf + (size_t)warp * D;
   // heads 0..n_q-1 = q, n_q..n_q+n_kv-1 = k, then v; CTA blockIdx.y takes heads [y * nw, (y + 1) * nw):
   // a decode tick's single token is spread over several CTAs instead of one walking 32 heads
@@ -340,7 +341,8 @@ attn_prefill_kernel(const bf16* q, const bf16* gate_src, int gate_ld,
                     const int* block_table, int max_blocks, const int* q_start,
                     const int* q_len, const int* positions, bf16* out,
                     int n_q, int n_kv, float scale_log2e, int gated,
-                    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, int map3d) {
+                    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, int map3d,
+                    int n_blocks) {
   extern __shared__ unsigned char pf_smem_raw[];
   __shared__ uint64_t pf_full[2];
   __shared__ volatile int pf_ok;
@@ -402,7 +404,7 @@ attn_prefill_kernel(const bf16* q, const bf16* gate_src, int gate_ld,
     const uint32_t bar = full_a + 8u * buf;
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(n_pg * 2 * KVB * PF_ROW)) : "memory");
     for (int pg = 0; pg < n_pg; ++pg) {
-      const int y = (table[j0 / KVB + pg] * n_kv + kvh) * KVB;
+      const int y = (trl_checked(table[j0 / KVB + pg], n_blocks, 3) * n_kv + kvh) * KVB;
       const uint32_t dk = ks_a + buf * PF_BC * PF_ROW + pg * (KVB * PF_ROW), dv = vs_a + buf * PF_BC * PF_ROW + pg * (KVB * PF_ROW);
       if (map3d) {
         asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
@@ -707,7 +709,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                        const bf16* q, const bf16* gate_src, int gate_ld,
                        const int* block_table, int max_blocks, const int* seq_ids, const int* positions,
                        float* po, float* pm, float* pl, bf16* out, int T, int n_q, int n_kv, int n_splits,
-                       int tpg, float scale_log2e, int gated, const DmFused fz) {
+                       int tpg, float scale_log2e, int gated, const DmFused fz, int n_blocks) {
   extern __shared__ unsigned char dm_smem_raw[];
   __shared__ float s_m[DM_WARPS][DM_ROWS], s_l[DM_WARPS][DM_ROWS];
   __shared__ int s_tab[DM_TAB];
@@ -776,7 +778,8 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         const uint4 v = dm_prep_row(row + (size_t)(kvh * G + job) * per_q, fz.q_norm, fz.eps, s_cs, s_sn, lane);
         *reinterpret_cast<uint4*>(qs + dm_off(job, lane)) = v;
       } else if (new_pos >= lo && new_pos < hi) {
-        const int slot = fz.slot_mapping[t0];
+        int slot = fz.slot_mapping[t0];
+        if (slot >= 0) slot = trl_checked(slot, n_blocks * KVB, 4);
         const size_t dst = (((size_t)(slot / KVB) * n_kv + kvh) * KVB + (slot % KVB)) * PF_D + lane * 8;
         if (job == rows) {
           const uint4 v = dm_prep_row(row + (size_t)n_q * per_q + (size_t)kvh * PF_D, fz.k_norm, fz.eps, s_cs, s_sn, lane);
@@ -828,7 +831,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       const int is_v = lane >> 4, pg = (lane >> 2) & 3, sl = lane & 3;
       if (pg < n_pg && (!map3d || sl == 0)) {
         const int pi = j0 / KVB + pg;
-        const int blk = tab_cached ? s_tab[pi - page0] : table[pi];
+        const int blk = trl_checked(tab_cached ? s_tab[pi - page0] : table[pi], n_blocks, 2);
         const int y = (blk * n_kv + kvh) * KVB;
         const uint32_t dst = (is_v ? vs_a : ks_a) + st * DM_TILE + pg * DM_PAGE + sl * DM_SLAB;
         const CUtensorMap* mp = is_v ? &map_v : &map_k;
@@ -1027,17 +1030,18 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 
 }  // namespace
 
+// n_blocks: pages of the pool (the checked build compares every KV slot against n_blocks * 16).
 TRL_API int trl_attn_prep(const void* qkv, int ld, const void* q_norm, const void* k_norm,
                           const void* positions, const void* slot_mapping, void* q_out, void* kcache,
                           void* vcache, int T, int n_q, int n_kv, int D, int rotary, float theta,
-                          float eps, int gated, void* stream) {
+                          float eps, int gated, int n_blocks, void* stream) {
   const int threads = 256;
   const size_t smem = (size_t)(rotary + (threads / 32) * D) * sizeof(float);
   const int chunks = (n_q + 2 * n_kv + threads / 32 - 1) / (threads / 32);   // one warp per head
   return (int)trl_launch(attn_prep_kernel, dim3(T, chunks), dim3(threads), smem, (cudaStream_t)stream,
                          (const bf16*)qkv, ld, (const float*)q_norm, (const float*)k_norm,
                          (const int*)positions, (const int*)slot_mapping, (bf16*)q_out, (bf16*)kcache,
-                         (bf16*)vcache, n_q, n_kv, D, rotary, log2f(theta), eps, gated);
+                         (bf16*)vcache, n_q, n_kv, D, rotary, log2f(theta), eps, gated, n_blocks * KVB);
 }
 
 // Scratch: po [T*n_q*n_splits*D] fp32, pm/pl [T*n_q*n_splits] fp32 (unused when n_splits == 1).
@@ -1169,7 +1173,7 @@ TRL_API int trl_attn_decode_mma(const void* q, const void* gate_src, int gate_ld
                              maps.mode3d, (const bf16*)q, (const bf16*)gate_src, gate_ld,
                              (const int*)block_table, max_blocks, (const int*)seq_ids, (const int*)positions,
                              (float*)po, (float*)pm, (float*)pl, (bf16*)out, T, n_q, n_kv, n_splits, tpg,
-                             scale * 1.4426950408889634f, gated, none);
+                             scale * 1.4426950408889634f, gated, none, n_blocks);
   if (e != cudaSuccess) return (int)e;
   if (n_splits > 1)
     e = trl_launch(attn_combine_kernel, dim3(T, n_q), dim3(min(D, 256)), 0, st, (const float*)po,
@@ -1207,7 +1211,7 @@ TRL_API int trl_attn_decode_fused(const void* qkv, int ld, const void* q_norm, c
                          (cudaStream_t)stream, maps.mk, maps.mv, maps.mode3d, (const bf16*)qkv, (const bf16*)qkv, ld,
                          (const int*)block_table, max_blocks, (const int*)seq_ids, (const int*)positions, (float*)po,
                          (float*)pm, (float*)pl, (bf16*)out, T, n_q, n_kv, n_splits, 1, scale * 1.4426950408889634f, gated,
-                         fz);
+                         fz, n_blocks);
 }
 
 // ---- allocation-free variant (declared in attn_static.h) --------------------------------------
@@ -1250,7 +1254,7 @@ TRL_API int trl_attn_prefill(const void* q, const void* gate_src, int gate_ld, c
                          (const float*)nullptr, (const float*)nullptr,
                          (const int*)block_table, max_blocks, (const int*)q_start, (const int*)q_len,
                          (const int*)positions, (bf16*)out, n_q, n_kv, scale * 1.4426950408889634f, gated, maps.mk, maps.mv,
-                         maps.mode3d);
+                         maps.mode3d, n_blocks);
 }
 
 // The same over an e4m3 pool: kcache / vcache are the e4m3 bytes of one layer, kscale / vscale its
@@ -1277,7 +1281,7 @@ TRL_API int trl_attn_prefill_fp8(const void* q, const void* gate_src, int gate_l
                          (const float*)kscale, (const float*)vscale,
                          (const int*)block_table, max_blocks, (const int*)q_start, (const int*)q_len,
                          (const int*)positions, (bf16*)out, n_q, n_kv, scale * 1.4426950408889634f, gated, CUtensorMap{},
-                         CUtensorMap{}, 0);
+                         CUtensorMap{}, 0, 0);
 }
 
 TRL_API int trl_attn_paged_static(const void* q, const void* gate_src, int gate_ld, const void* kcache,

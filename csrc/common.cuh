@@ -42,6 +42,23 @@ __device__ __forceinline__ void trl_set_error(int code, int a, int b, int c) {
   }
 }
 
+// Checked table index.  Builds with -DTRL_DEBUG_BOUNDS only (python -m tilerl_b200.build --bounds): an index
+// outside [0, n) records the error word {TRL_ERR_BOUNDS, site, index, n} and comes back clamped into range,
+// so the access that follows stays inside the buffer and the context stays usable; the normal build
+// compiles to the bare index.  Sites: 1 KV slot of a token (attn_prep), 2 block-table entry in decode
+// attention, 3 block-table entry in prefill attention, 4 KV slot in the one-launch decode attention.
+#ifdef TRL_DEBUG_BOUNDS
+__device__ __forceinline__ int trl_checked(int i, int n, int site) {
+  if ((unsigned)i >= (unsigned)n) {
+    trl_set_error(TRL_ERR_BOUNDS, site, i, n);
+    return n > 0 ? min(max(i, 0), n - 1) : 0;
+  }
+  return i;
+}
+#else
+__device__ __forceinline__ int trl_checked(int i, int, int) { return i; }
+#endif
+
 // ---- tensor-parallel push target (see comm.cu) --------------------------------------------
 // Peer workspace pointers for the row-parallel GEMV epilogue that writes its fp32 partial
 // rows into every rank's one-shot all-reduce slot.

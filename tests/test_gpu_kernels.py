@@ -277,6 +277,71 @@ def test_quest_score_and_topk_kernels_match_the_torch_selection(ops, n_pages, k)
     assert native.read_error()[0] == 0
 
 
+_BOUNDS_CHILD = r"""
+import ctypes, math, sys, torch
+from tilerl_b200.ops import native as N
+assert N._PATH.endswith("_C_bounds.so"), N._PATH
+lib = N.lib()
+dev = "cuda"
+n_q, n_kv, d, real_blocks, told_blocks = 8, 2, 256, 32, 8
+kc = torch.zeros(real_blocks, n_kv, 16, d, dtype=torch.bfloat16, device=dev)
+vc = torch.zeros_like(kc)
+rows = n_q * 2 * d + 2 * n_kv * d
+qkv = (torch.randn(1, rows, device=dev) * 0.5).to(torch.bfloat16)
+ones = torch.ones(d, device=dev)
+q = torch.zeros(1, n_q, d, dtype=torch.bfloat16, device=dev)
+pos = torch.tensor([40], dtype=torch.int32, device=dev)
+res = {}
+# site 1: the token's KV slot lies in page 20 -- inside the allocation, beyond the 8 pages the call declares
+slot = torch.tensor([20 * 16 + 8], dtype=torch.int32, device=dev)
+N.check(lib.trl_attn_prep(qkv.data_ptr(), rows, ones.data_ptr(), ones.data_ptr(), pos.data_ptr(), slot.data_ptr(), q.data_ptr(),
+                          kc.data_ptr(), vc.data_ptr(), 1, n_q, n_kv, d, 64, 1e6, 1e-6, 1, told_blocks, N.stream()), "prep")
+torch.cuda.synchronize()
+res["prep"] = list(N.read_error(True))
+res["prep_rows_written"] = int((kc.float().abs().sum((1, 2, 3)) > 0).nonzero().flatten().tolist() == [told_blocks - 1])
+# site 2: a block-table entry (page 20) beyond the declared pages, in decode attention
+table = torch.tensor([[1, 2, 20, 3]], dtype=torch.int32, device=dev)
+seq = torch.zeros(1, dtype=torch.int32, device=dev)
+po = torch.zeros(n_q * 4 * d, device=dev); pm = torch.zeros(n_q * 4, device=dev); pl = torch.zeros(n_q * 4, device=dev)
+out = torch.zeros(1, n_q * d, dtype=torch.bfloat16, device=dev)
+N.check(lib.trl_attn_decode_mma(q.data_ptr(), qkv.data_ptr(), rows, kc.data_ptr(), vc.data_ptr(), table.data_ptr(), 4, told_blocks,
+                                seq.data_ptr(), pos.data_ptr(), po.data_ptr(), pm.data_ptr(), pl.data_ptr(), out.data_ptr(),
+                                1, n_q, n_kv, d, 1, 1, 1.0 / math.sqrt(d), 1, N.stream()), "decode")
+torch.cuda.synchronize()
+res["decode"] = list(N.read_error(True))
+res["finite"] = bool(torch.isfinite(out.float()).all())
+# in range: no error word
+table_ok = torch.tensor([[1, 2, 5, 3]], dtype=torch.int32, device=dev)
+N.check(lib.trl_attn_decode_mma(q.data_ptr(), qkv.data_ptr(), rows, kc.data_ptr(), vc.data_ptr(), table_ok.data_ptr(), 4, told_blocks,
+                                seq.data_ptr(), pos.data_ptr(), po.data_ptr(), pm.data_ptr(), pl.data_ptr(), out.data_ptr(),
+                                1, n_q, n_kv, d, 1, 1, 1.0 / math.sqrt(d), 1, N.stream()), "decode")
+torch.cuda.synchronize()
+res["clean"] = list(N.read_error(True))
+print("RESULT", res)
+"""
+
+
+def test_checked_build_records_table_indices_out_of_range_and_clamps_them():
+    """The -DTRL_DEBUG_BOUNDS build (loaded in a child process): a KV slot and a block-table entry that
+    point past the pages the call declares -- but inside the real allocation, so nothing can leave it --
+    are recorded as {bounds, site, index, limit} and clamped; indices in range leave the error word clear."""
+    import ast
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lib = os.path.join(root, "tilerl_b200", "_C_bounds.so")
+    assert os.path.exists(lib), "build it: python -m tilerl_b200.build --bounds"
+    env = dict(os.environ, TRL_BOUNDS_LIB="1", PYTHONPATH=root)
+    r = subprocess.run([sys.executable, "-c", _BOUNDS_CHILD], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    res = ast.literal_eval(next(l for l in r.stdout.splitlines() if l.startswith("RESULT"))[7:])
+    assert res["prep"] == [2, 1, 20 * 16 + 8, 8 * 16]                  # TRL_ERR_BOUNDS, site 1, index, limit
+    assert res["prep_rows_written"] == 1                               # the row went to the last declared page
+    assert res["decode"][:2] == [2, 2] and res["decode"][2:] == [20, 8]
+    assert res["finite"] and res["clean"] == [0, 0, 0, 0]
+
+
 def test_quant_kernel_bit_exact_and_dequant(ops):
     g = torch.Generator().manual_seed(3)
     for dtype in (torch.float32, torch.bfloat16):

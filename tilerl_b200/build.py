@@ -52,13 +52,20 @@ def _stamp(path: str) -> str:
     return h.hexdigest()
 
 
-def build(force: bool = False, verbose: bool = False, extra_flags=(), trace: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, extra_flags=(), trace: bool = False, bounds: bool = False) -> str:
     """``trace=True`` builds ``tilerl_b200/_C_trace.so`` with ``-DTRL_TRACE`` (per-launch timestamps of a
-    tick, read by ``tilerl_b200.utils.tick_trace``) next to the normal library."""
-    obj_dir = OBJ + ("_trace" if trace else "")
-    out_path = OUT.replace("_C.so", "_C_trace.so") if trace else OUT
+    tick, read by ``tilerl_b200.utils.tick_trace``) next to the normal library.  ``bounds=True`` builds
+    ``tilerl_b200/_C_bounds.so`` with ``-DTRL_DEBUG_BOUNDS``: the indices the kernels take from tables
+    (KV slot of a token, block-table entries) are checked against the pool size; one out of range records
+    an error word {bounds, site, index, limit} and is clamped, so the access stays inside the buffer."""
+    assert not (trace and bounds)
+    variant = "_trace" if trace else ("_bounds" if bounds else "")
+    obj_dir = OBJ + variant
+    out_path = OUT.replace("_C.so", f"_C{variant}.so")
     if trace:
         extra_flags = tuple(extra_flags) + ("-DTRL_TRACE",)
+    if bounds:
+        extra_flags = tuple(extra_flags) + ("-DTRL_DEBUG_BOUNDS",)
     os.makedirs(obj_dir, exist_ok=True)
     nvcc = _nvcc()
     jobs = []
@@ -116,6 +123,6 @@ def build_tests(force: bool = False) -> list:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose=True, trace="--trace" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose=True, trace="--trace" in sys.argv, bounds="--bounds" in sys.argv))
     if "--tests" in sys.argv:
         print("\n".join(build_tests(force="--force" in sys.argv)))

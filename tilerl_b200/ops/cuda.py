@@ -410,7 +410,7 @@ class CudaOps:
             qkv.data_ptr(), qkv.stride(0), self._f32(lp["q_norm"]).data_ptr(),
             self._f32(lp["k_norm"]).data_ptr(), batch.positions.data_ptr(),
             batch.slot_mapping.data_ptr(), q.data_ptr(), kc.data_ptr(), vc.data_ptr(), t, n_q, n_kv, d,
-            cfg.rotary_dim, float(cfg.rope_theta), cfg.rms_eps, int(cfg.attn_gated), st), "attn_prep")
+            cfg.rotary_dim, float(cfg.rope_theta), cfg.rms_eps, int(cfg.attn_gated), kc.shape[0], st), "attn_prep")
         table, pos = batch.block_table, batch.positions
         sp = batch.sparse
         sparse_now = sp is not None and sp.active(attn_idx)

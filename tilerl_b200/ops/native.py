@@ -16,9 +16,11 @@ from typing import Optional
 import torch
 
 _LIB: Optional[ctypes.CDLL] = None
-# TRL_TRACE_LIB=1 loads the timeline build (``python -m tilerl_b200.build --trace``) instead
+# TRL_TRACE_LIB=1 loads the timeline build (``python -m tilerl_b200.build --trace``) instead,
+# TRL_BOUNDS_LIB=1 the build with checked table indices (``python -m tilerl_b200.build --bounds``)
 _PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
-                     "_C_trace.so" if os.environ.get("TRL_TRACE_LIB") == "1" else "_C.so")
+                     "_C_trace.so" if os.environ.get("TRL_TRACE_LIB") == "1" else
+                     ("_C_bounds.so" if os.environ.get("TRL_BOUNDS_LIB") == "1" else "_C.so"))
 
 P, I, L, F = c_void_p, c_int, c_long, c_float
 
@@ -28,7 +30,7 @@ _SIGS = {
     "trl_set_pdl": [I],
     "trl_trace_read": [P, I, I],
     "trl_error_read": [P, I],
-    "trl_attn_prep": [P, I, P, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P],
+    "trl_attn_prep": [P, I, P, P, P, P, P, P, P, I, I, I, I, I, F, F, I, I, P],
     "trl_attn_paged": [P, P, I, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, F, I, P],
     "trl_gdn": [P, I, P, P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, P, P, P, P, P, P, P,
                 I, I, I, I, I, I, I, F, P],
