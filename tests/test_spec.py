@@ -84,3 +84,87 @@ def test_drafter_checkpoint_round_trip(tmp_path):
     if other.cfg.hidden != cfg.hidden:
         with pytest.raises(ValueError):
             load_drafter(other, str(tmp_path / "block"))
+
+
+def _drafter(width=4, **kw):
+    from tilerl_b200.models.hybrid import HybridModel
+    from tilerl_b200.spec import BlockDrafterConfig
+    cfg = tiny_hybrid()
+    model = HybridModel.build_random(cfg, seed=0)
+    return cfg, BlockDrafter(model, BlockDrafterConfig(width=width, n_layers=2, n_heads=4, n_kv_heads=2, **kw), seed=3)
+
+
+def test_block_drafter_conv_is_identity_at_init_and_zero_padded_at_the_block_start():
+    """The grouped two-tap conv along the block: with the initial coefficients it passes its input
+    through; with a second tap, slot j reads slot j - 1 only, and slot 0 reads nothing before it."""
+    cfg, d = _drafter()
+    w, h = d.cfg.width, cfg.hidden
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(w, h, generator=g)
+    zero = torch.zeros(w, d.cfg.conv_taps, d.groups)
+    base = d.p["l0.attn_conv.base"][0]
+    assert torch.allclose(d._conv(x, zero, base), x)
+    base2 = base.clone()
+    base2[1] = 0.5                                           # tap 1: half of the slot before
+    y = d._conv(x, zero, base2)
+    assert torch.allclose(y[0], x[0]) and torch.allclose(y[1:], x[1:] + 0.5 * x[:-1], atol=1e-6)
+    x2 = x.clone()
+    x2[1] += 1.0                                             # a change in slot 1 reaches slots 1 and 2 only
+    changed = (d._conv(x2, zero, base2) - y).abs().sum(-1) > 0
+    assert changed.tolist() == [False, True, True, False]
+    # per-slot offsets act on one group of channels
+    delta = zero.clone()
+    delta[2, 0, 1] = 1.0                                     # slot 2, tap 0, group 1: coefficient 2 instead of 1
+    z = d._conv(x, delta, base)
+    gs = d.gsize
+    assert torch.allclose(z[2, gs:2 * gs], 2 * x[2, gs:2 * gs]) and torch.allclose(z[2, :gs], x[2, :gs])
+    assert torch.allclose(z[[0, 1, 3]], x[[0, 1, 3]])
+
+
+def test_block_drafter_selector_walk_is_argmax_until_trained_and_then_follows_the_pairwise_term():
+    cfg, d = _drafter(top_k=4, sel_rank=4)
+    g = torch.Generator().manual_seed(1)
+    hid = torch.randn(3, cfg.hidden, generator=g)
+    plain = d._head(hid).argmax(-1).tolist()
+    assert d.paths(hid, anchor=5) == plain                   # succ == 0: the pairwise term vanishes
+    # make the runner-up of slot 1 the strongly preferred successor of the token chosen for slot 0
+    logits = d._head(hid)
+    top = torch.topk(logits, 4, dim=-1)
+    runner_up, prev = int(top.indices[1, 1]), plain[0]
+    proj1 = (hid[1] @ d.p["sel.proj"].t()).float()
+    direction = d.p["sel.pred"][prev].float() * proj1
+    d.p["sel.succ"][runner_up] = direction * (10.0 * float(top.values[1, 0] - top.values[1, 1] + 1.0) / float(direction.dot(direction)))
+    walked = d.paths(hid, anchor=5)
+    assert walked[0] == plain[0] and walked[1] == runner_up
+    # the walk is sequential: another anchor only matters through slot 0's pairwise term
+    assert d.paths(hid, anchor=6)[0] == plain[0]
+
+
+def test_block_drafter_context_kv_grows_by_the_new_rows_and_matches_a_fresh_projection():
+    """The per-request context K / V cache: rows are projected when they enter and appended; proposing
+    from the cache gives the drafts of a drafter that projects the whole window again."""
+    from types import SimpleNamespace
+    cfg, d = _drafter()
+    g = torch.Generator().manual_seed(2)
+    eng = SimpleNamespace(spec_width=4)
+    taps_all = {l: torch.randn(12, cfg.hidden, generator=g) for l in d.aux_layers}
+    req = SimpleNamespace(rid=1, state="prefill", toks=[3, 4, 5], n_last_commit=1)
+    first = d.propose(eng, req, {l: t[:8] for l, t in taps_all.items()}, 0, 8, 3)
+    assert d.ctx_kv[1][0].shape[0] == 8
+    req.state, req.toks = "decode", [3, 4, 5, 6]
+    second = d.propose(eng, req, {l: t[8:12] for l, t in taps_all.items()}, 0, 4, 3)   # 4 rows ran, 1 was committed
+    assert d.ctx_kv[1][0].shape[0] == 9 and d.ctx[1].shape[0] == 9
+    # from scratch: the same 9 context rows projected in one go
+    _, d2 = _drafter()
+    rows = {l: torch.cat([t[:8], t[8:9]]) for l, t in taps_all.items()}
+    req2 = SimpleNamespace(rid=7, state="prefill", toks=[3, 4, 5, 6], n_last_commit=1)
+    assert d2.propose(eng, req2, rows, 0, 9, 3) == second
+    for a, b in zip(d.ctx_kv[1], d2.ctx_kv[7]):
+        assert torch.allclose(a, b, atol=1e-6)
+    assert len(first) == 3 and len(second) == 3
+    d.release(1)
+    assert 1 not in d.ctx_kv and 1 not in d.ctx
+    # the window: a context longer than the window keeps its newest rows
+    _, d3 = _drafter(window=6)
+    d3.propose(eng, SimpleNamespace(rid=2, state="prefill", toks=[1], n_last_commit=1), taps_all, 0, 12, 2)
+    assert d3.ctx_kv[2][0].shape[0] == 6

@@ -60,6 +60,10 @@ class BlockDrafterConfig:
     taps: int = 3
     window: int = 64          # context positions the block attends to
     ffn_mult: float = 2.0
+    top_k: int = 8            # candidates per slot the selector walk chooses from
+    sel_rank: int = 16        # rank of the pairwise (previous token, candidate) selector
+    conv_taps: int = 2        # depthwise conv along the block before / after each sub-layer
+    conv_group: int = 64      # channels that share one conv coefficient
 
 
 class BlockDrafter:
@@ -84,6 +88,8 @@ class BlockDrafter:
         self.p: Dict[str, torch.Tensor] = {"fc": w(h, len(self.aux_layers) * h), "mask": w(h), "pos": w(c.width, h),
                                            "ctx_norm": torch.ones(h, device=dev, dtype=dtype),
                                            "out_norm": torch.ones(h, device=dev, dtype=dtype)}
+        self.groups = max(1, h // c.conv_group)
+        self.gsize = h // self.groups
         for i in range(c.n_layers):
             q = f"l{i}."
             self.p[q + "norm1"] = torch.ones(h, device=dev, dtype=dtype)
@@ -93,14 +99,28 @@ class BlockDrafter:
             self.p[q + "o"] = w(h, c.n_heads * self.hd)
             self.p[q + "gate_up"] = w(2 * ffn, h)
             self.p[q + "down"] = w(h, ffn)
-        self.ctx: Dict[int, List[torch.Tensor]] = {}   # rid -> per-layer context features [n, H]
+            for name in ("attn_conv", "mlp_conv"):
+                # [side (before / after the sub-layer), tap, group, channel]: tap 0 starts as the identity
+                base = torch.zeros(2, c.conv_taps, self.groups, self.gsize)
+                base[:, 0] = 1.0
+                self.p[q + name + ".base"] = base.to(dev, dtype)
+                self.p[q + name + ".proj"] = w(2 * c.conv_taps * self.groups, h, s=0.002)
+        # pairwise selector over the top-k candidates of a slot: score += succ[cand] . (pred[prev] * proj(h));
+        # `succ` starts at zero, so an untrained selector is the plain argmax
+        self.p["sel.proj"] = w(c.sel_rank, h)
+        self.p["sel.pred"] = w(mc.vocab, c.sel_rank)
+        self.p["sel.succ"] = torch.zeros(mc.vocab, c.sel_rank, device=dev, dtype=dtype)
+        self.ctx: Dict[int, torch.Tensor] = {}         # rid -> context features [n, H] (kept for inspection)
+        self.ctx_kv: Dict[int, List[torch.Tensor]] = {}   # rid -> per layer [n, 2, n_kv, hd]: K / V of the context rows
 
     # ---- engine hooks -------------------------------------------------------------------
     def release(self, rid: int) -> None:
         self.ctx.pop(rid, None)
+        self.ctx_kv.pop(rid, None)
 
     def invalidate(self) -> None:
         self.ctx.clear()
+        self.ctx_kv.clear()
 
     def _embed(self, tok: int) -> torch.Tensor:
         return self.model.params["embed"][tok].to(self.p["fc"].dtype)
@@ -125,24 +145,73 @@ class BlockDrafter:
         p = torch.softmax(s, -1)
         return torch.einsum("hgws,shd->whgd", p, v.float()).reshape(q.shape[0], -1)
 
-    def block_hidden(self, last_tok: int, ctx: torch.Tensor) -> torch.Tensor:
-        """Run the mask-token block over the context features; returns [W, H]."""
+    def context_kv(self, feats: torch.Tensor) -> List[torch.Tensor]:
+        """K / V of context rows for every layer: ``[n, H]`` -> per layer ``[n, 2, n_kv, hd]``.  They depend
+        on the row's features only (the context carries no position code), so rows are projected once,
+        when they enter the context, and appended (parity: the incremental context of spec.py:1005-1017,
+        src/tilerl)."""
+        c = self.cfg
+        return [(feats @ self.p[f"l{i}.kv"].t()).view(feats.shape[0], 2, c.n_kv_heads, self.hd) for i in range(c.n_layers)]
+
+    def _conv(self, x: torch.Tensor, delta: torch.Tensor, base: torch.Tensor) -> torch.Tensor:
+        """Grouped depthwise conv along the block's slots with per-slot coefficients: ``x [W, H]``,
+        ``delta [W, taps, groups]`` (this slot's offsets), ``base [taps, groups, gsize]``.
+        out[j] = sum_tap coef[j, tap] * x[j - tap]; a tap that reaches before slot 0 contributes nothing,
+        so nothing of an earlier block leaks in (parity: spec.py:1135-1146, src/tilerl)."""
+        w_, taps = x.shape[0], base.shape[0]
+        xb = x.float().view(w_, self.groups, self.gsize)
+        coef = base.float().unsqueeze(0) + delta.float().unsqueeze(-1)          # [W, taps, groups, gsize]
+        out = coef[:, 0] * xb
+        for tap in range(1, taps):
+            out[tap:] += coef[tap:, tap] * xb[:-tap]
+        return out.reshape(w_, -1).to(x.dtype)
+
+    def _conv_in(self, x: torch.Tensor, norm_key: str, conv_key: str):
+        """Norm, the conv before the sub-layer, and the offsets of its partner after it (one
+        projection yields both sides)."""
+        c = self.cfg
+        hx = ref.rmsnorm(x, self.p[norm_key], 1e-6).to(x.dtype)
+        d = (hx @ self.p[conv_key + ".proj"].t()).view(x.shape[0], 2, c.conv_taps, self.groups)
+        return self._conv(hx, d[:, 0], self.p[conv_key + ".base"][0]), d[:, 1]
+
+    def block_hidden(self, last_tok: int, ctx, ctx_kv: Optional[List[torch.Tensor]] = None) -> torch.Tensor:
+        """Run the mask-token block over the context; returns [W, H].  ``ctx``: context features
+        ``[n, H]``; ``ctx_kv``: their per-layer K / V if the caller keeps them (else projected here)."""
         c = self.cfg
         x = torch.stack([self._embed(last_tok)] + [self.p["mask"]] * (c.width - 1)) + self.p["pos"]
-        ctx = ctx[-c.window:]
+        if ctx_kv is None:
+            ctx_kv = self.context_kv(ctx[-c.window:])
         for i in range(c.n_layers):
             q_ = f"l{i}."
-            hx = ref.rmsnorm(x, self.p[q_ + "norm1"], 1e-6).to(x.dtype)
-            src = torch.cat([ctx, hx])                      # context rows first, then the block itself
-            kv = (src @ self.p[q_ + "kv"].t()).view(src.shape[0], 2, c.n_kv_heads, self.hd)
+            hx, after = self._conv_in(x, q_ + "norm1", q_ + "attn_conv")
+            own = (hx @ self.p[q_ + "kv"].t()).view(c.width, 2, c.n_kv_heads, self.hd)
+            kv = torch.cat([ctx_kv[i][-c.window:].to(own.dtype), own])       # context rows first, then the block itself
             q = (hx @ self.p[q_ + "q"].t()).view(c.width, c.n_heads, self.hd)
-            a = self._attend(q, kv[:, 0], kv[:, 1]).to(x.dtype)
-            x = x + a @ self.p[q_ + "o"].t()
-            hx = ref.rmsnorm(x, self.p[q_ + "norm2"], 1e-6).to(x.dtype)
+            a = self._attend(q, kv[:, 0], kv[:, 1]).to(x.dtype) @ self.p[q_ + "o"].t()
+            x = x + self._conv(a, after, self.p[q_ + "attn_conv.base"][1])
+            hx, after = self._conv_in(x, q_ + "norm2", q_ + "mlp_conv")
             gu = hx @ self.p[q_ + "gate_up"].t()
             f = gu.shape[-1] // 2
-            x = x + (F.silu(gu[:, :f]) * gu[:, f:]) @ self.p[q_ + "down"].t()
+            m = (F.silu(gu[:, :f]) * gu[:, f:]) @ self.p[q_ + "down"].t()
+            x = x + self._conv(m, after, self.p[q_ + "mlp_conv.base"][1])
         return x
+
+    def paths(self, hidden: torch.Tensor, anchor: int) -> List[int]:
+        """Top-k candidates per slot from the trunk's head, then one greedy walk: a slot's candidate is
+        scored by its logit plus a low-rank pairwise term with the token chosen for the slot before
+        (``succ[cand] . (pred[prev] * proj(h))``), so the block is read out sequentially although it
+        was computed in parallel (parity: spec.py:1071-1100, src/tilerl)."""
+        c = self.cfg
+        logits = self._head(hidden)                                            # [slots, vocab]
+        unary, cand = torch.topk(logits, min(c.top_k, logits.shape[-1]), dim=-1)
+        proj = (hidden.to(self.p["sel.proj"].dtype) @ self.p["sel.proj"].t()).float()   # [slots, r]
+        pred, succ = self.p["sel.pred"], self.p["sel.succ"]
+        prev, out = torch.as_tensor(int(anchor), device=hidden.device), []
+        for j in range(hidden.shape[0]):                                      # on the device: one host sync for the block
+            pair = succ[cand[j]].float() @ (pred[prev].float() * proj[j])     # [k]
+            prev = cand[j][(unary[j].float() + pair).argmax()]
+            out.append(prev)
+        return [int(t) for t in torch.stack(out).tolist()] if out else []
 
     def propose(self, engine, req, taps, tok_off: int, n_run: int, k: int) -> List[int]:
         """Drafts for the next verify tick.  ``taps``: trunk residual-stream taps of this tick's
@@ -154,11 +223,15 @@ class BlockDrafter:
             engine.spec_width else n_run
         feats = self.context_features(taps, slice(tok_off, tok_off + n_valid))
         old = self.ctx.get(req.rid)
-        ctx = feats if old is None else torch.cat([old, feats])[-self.cfg.window:]
+        ctx = (feats if old is None else torch.cat([old, feats]))[-self.cfg.window:]
         self.ctx[req.rid] = ctx
-        hid = self.block_hidden(req.toks[-1], ctx)
-        logits = self._head(hid[1:1 + k] if hid.shape[0] > k else hid[-k:])
-        return [int(t) for t in logits.argmax(-1).tolist()][:k]
+        # only the rows that entered the context this tick are projected to K / V
+        new_kv = self.context_kv(feats)
+        old_kv = self.ctx_kv.get(req.rid)
+        kv = [(n if o is None else torch.cat([o, n]))[-self.cfg.window:] for o, n in zip(old_kv or [None] * len(new_kv), new_kv)]
+        self.ctx_kv[req.rid] = kv
+        hid = self.block_hidden(req.toks[-1], ctx, kv)
+        return self.paths(hid[1:1 + k] if hid.shape[0] > k else hid[-k:], req.toks[-1])[:k]
 
 
 class ChainDrafter:
