@@ -5,6 +5,8 @@
 //                        tokens in registers and scores the page with the Quest upper bound
 //                        sum_{kv head} sum_{query head of the group} sum_d max(q_d min_d, q_d max_d).
 //                        No bounds tensor is materialised.
+//   page_mean_kernel   : mean key of a page per kv head (input of the learned indexer's projection);
+//   index_score_kernel : the learned indexer's page score, sum over index heads of relu(q . k) / sqrt(d).
 //   topk_pages_kernel  : one CTA per sequence.  k-th largest score by a 4-pass radix select over
 //                        order-preserving keys, then the kept page indices in ascending order
 //                        (all scores above the k-th, and the first equals in page order until k).
@@ -67,6 +69,61 @@ quest_score_kernel(const bf16* q, const bf16* kcache, const int* table, float* s
     float tot = 0.f;
     for (int w2 = 0; w2 < nw; ++w2) tot += s_part[w2];
     scores[page] = tot;
+  }
+}
+
+// Mean key of a page per kv head: pooled[page][kvh * D + d] = mean over the page's 16 tokens (fp32).  The learned
+// indexer projects these rows with its own small matrix (a library GEMM) before scoring.
+__global__ void __launch_bounds__(128)
+page_mean_kernel(const bf16* kcache, const int* table, float* pooled, int n_kv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int page = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int blk = table[page];
+  for (int kvh = warp; kvh < n_kv; kvh += nw) {
+    const bf16* rows = kcache + ((size_t)blk * n_kv + kvh) * QS_PAGE * QS_D + lane * 8;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll 4
+    for (int r = 0; r < QS_PAGE; ++r) {
+      const uint4 v = *reinterpret_cast<const uint4*>(rows + (size_t)r * QS_D);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = bf162_bits_to_f2(w[i]);
+        acc[2 * i] += f.x, acc[2 * i + 1] += f.y;
+      }
+    }
+    float* dst = pooled + ((size_t)page * n_kv + kvh) * QS_D + lane * 8;
+    *reinterpret_cast<float4*>(dst) = make_float4(acc[0] * 0.0625f, acc[1] * 0.0625f, acc[2] * 0.0625f, acc[3] * 0.0625f);
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[4] * 0.0625f, acc[5] * 0.0625f, acc[6] * 0.0625f, acc[7] * 0.0625f);
+  }
+}
+
+// Learned-indexer score of a page: sum over index heads of relu(q_idx[h] . k_idx[page][h]) / sqrt(d).
+// q_idx [H, d], k_idx [pages, H, d] fp32; one warp per head, heads summed in ascending order.
+__global__ void __launch_bounds__(128)
+index_score_kernel(const float* q_idx, const float* k_idx, float* scores, int H, int d) {
+  __shared__ float s_part[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int page = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  float mine = 0.f;
+  for (int h = warp; h < H; h += nw) {
+    const float* kr = k_idx + ((size_t)page * H + h) * d;
+    const float* qr = q_idx + (size_t)h * d;
+    float s = 0.f;
+    for (int i = lane; i < d; i += 32) s = fmaf(qr[i], kr[i], s);
+    s = warp_sum(s);
+    mine += fmaxf(s, 0.f);
+  }
+  if (lane == 0) s_part[warp] = mine;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int w2 = 0; w2 < nw; ++w2) tot += s_part[w2];
+    scores[page] = tot * rsqrtf((float)d);
   }
 }
 
@@ -162,4 +219,18 @@ TRL_API int trl_topk_pages(const void* scores, int n, int k, void* sel, void* st
   if (n <= 0 || k <= 0) return (int)cudaErrorInvalidValue;
   return (int)trl_launch(topk_pages_kernel, dim3(1), dim3(TK_THREADS), 0, (cudaStream_t)stream, (const float*)scores, n, k,
                          (long long*)sel);
+}
+
+// pooled[p] = mean K row of page table[p] per kv head: [n_pages, n_kv * 256] fp32.
+TRL_API int trl_page_mean(const void* kcache, const void* table, void* pooled, int n_pages, int n_kv, int D, void* stream) {
+  if (D != QS_D || n_pages <= 0 || n_kv <= 0) return (int)cudaErrorInvalidValue;
+  return (int)trl_launch(page_mean_kernel, dim3(n_pages), dim3(128), 0, (cudaStream_t)stream, (const bf16*)kcache,
+                         (const int*)table, (float*)pooled, n_kv);
+}
+
+// scores[p] = sum_h relu(q_idx[h] . k_idx[p][h]) / sqrt(d); q_idx [H, d], k_idx [n_pages, H, d], fp32.
+TRL_API int trl_index_scores(const void* q_idx, const void* k_idx, void* scores, int n_pages, int H, int d, void* stream) {
+  if (n_pages <= 0 || H <= 0 || d <= 0) return (int)cudaErrorInvalidValue;
+  return (int)trl_launch(index_score_kernel, dim3(n_pages), dim3(128), 0, (cudaStream_t)stream, (const float*)q_idx,
+                         (const float*)k_idx, (float*)scores, H, d);
 }

@@ -342,6 +342,34 @@ def test_checked_build_records_table_indices_out_of_range_and_clamps_them():
     assert res["finite"] and res["clean"] == [0, 0, 0, 0]
 
 
+@pytest.mark.parametrize("n_pages,k", [(5, 8), (300, 64), (2100, 128)])
+def test_learned_indexer_selection_on_the_device_matches_the_torch_scores(ops, n_pages, k):
+    """Page mean keys (one read of every K page), the indexer's projections (library GEMMs), the
+    relu-dot score kernel and the radix-select top-k against ``LearnedIndexer.scores``."""
+    from tilerl_b200.config import small_gpu
+    from tilerl_b200.ops import native
+    from tilerl_b200.sparse_index import LearnedIndexer
+    import dataclasses
+    n_q, n_kv, d = 8, 2, 256
+    cfg = dataclasses.replace(small_gpu(), n_q_heads=n_q, n_kv_heads=n_kv)
+    ix = LearnedIndexer(cfg, heads=4, dim=128, seed=3, device=DEV)
+    g = torch.Generator().manual_seed(n_pages)
+    kc = torch.randn(n_pages + 2, n_kv, 16, d, generator=g).to(DEV, torch.bfloat16)
+    q = torch.randn(n_q, d, generator=g).to(DEV, torch.bfloat16)
+    table = (torch.randperm(n_pages, generator=g) + 1).to(DEV, torch.int32)
+    sel = ops.index_select(ix, 0, q, kc, table, k)
+    torch.cuda.synchronize()
+    want_scores = ix.scores(0, q, kc, table)
+    got_scores = ops.ws.get("quest_scores", (n_pages,), torch.float32)
+    assert _rel(got_scores, want_scores) < 1e-3                  # tf32 / summation order of the two GEMMs
+    kk = min(k, n_pages)
+    assert torch.equal(sel, torch.sort(torch.topk(got_scores, kk).indices).values)
+    # the pooled rows themselves
+    pooled = ops.ws.get("index_pooled", (n_pages, n_kv * d), torch.float32)
+    assert _rel(pooled, kc[table.long()].float().mean(2).reshape(n_pages, -1)) < 1e-6
+    assert native.read_error()[0] == 0
+
+
 def test_quant_kernel_bit_exact_and_dequant(ops):
     g = torch.Generator().manual_seed(3)
     for dtype in (torch.float32, torch.bfloat16):

@@ -605,6 +605,28 @@ class CudaOps:
         N.count(2)
         return sel
 
+    def index_select(self, indexer, layer: int, q, kcache, table_early, k: int):
+        """The learned indexer's selection on the device: page mean keys by one kernel that reads each K
+        page once, the indexer's two small projections as library GEMMs, scores and the ascending top-k
+        by kernels.  ``None`` for shapes the kernels do not take."""
+        n = int(table_early.numel())
+        n_kv, d = kcache.shape[1], kcache.shape[-1]
+        if d != 256 or kcache.dtype != torch.bfloat16 or n == 0 or k <= 0:
+            return None
+        self.flush()
+        tab = table_early.to(torch.int32).contiguous()
+        pooled = self.ws.get("index_pooled", (n, n_kv * d), torch.float32)
+        N.check(self.lib.trl_page_mean(kcache.data_ptr(), tab.data_ptr(), pooled.data_ptr(), n, n_kv, d, N.stream()), "page_mean")
+        k_idx = (pooled @ indexer.wk[layer].float()).contiguous()                 # [n, H * dim]
+        q_idx = (q.float().reshape(-1) @ indexer.wq[layer].float()).contiguous()   # [H * dim]
+        scores = self.ws.get("quest_scores", (n,), torch.float32)
+        N.check(self.lib.trl_index_scores(q_idx.data_ptr(), k_idx.data_ptr(), scores.data_ptr(), n, indexer.heads,
+                                          indexer.dim, N.stream()), "index_scores")
+        sel = torch.empty(min(k, n), dtype=torch.int64, device=kcache.device)
+        N.check(self.lib.trl_topk_pages(scores.data_ptr(), n, k, sel.data_ptr(), N.stream()), "topk_pages")
+        N.count(3)
+        return sel
+
     def spec_accept(self, tok, batch, cur, pack) -> None:
         """Greedy acceptance of a verify tick on the device: ``pack[:B*W]`` gets the argmax tokens,
         ``pack[B*W:]`` the number of drafts each sequence's trunk reproduced, and ``cur`` (the GDN pool's

@@ -61,6 +61,8 @@ _SIGS = {
     "trl_attn_decode_fused": [P, I, P, P, P, P, P, P, P, I, I, P, P, P, P, P, P, I, I, I, I, I, F, F, I, F, I, P],
     "trl_quest_scores": [P, P, P, P, I, I, I, I, P],
     "trl_topk_pages": [P, I, I, P, P],
+    "trl_page_mean": [P, P, P, I, I, I, P],
+    "trl_index_scores": [P, P, P, I, I, I, P],
     "trl_spec_accept": [P, P, P, P, P, P, I, I, P],
     "trl_gemv_nvfp4_mma": [P, I, P, P, P, P, F, P, I, P, I, I, I, I, I, P],
     "trl_attn_prep_fp8": [P, I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, F, I, P],

@@ -137,6 +137,8 @@ register("any", "sm100", {
     "sample_nucleus": Kernel("sample_nucleus_kernel", "csrc/misc.cu", "trl_sample_nucleus"),
     "page_bounds": Kernel("quest_score_kernel", "csrc/sparse.cu", "trl_quest_scores",
                           note="min / max of a K page per dimension in registers + Quest upper bound, one CTA per page"),
+    "learned_index_scores": Kernel("page_mean_kernel + index_score_kernel", "csrc/sparse.cu", "trl_index_scores",
+                                   note="page mean keys from the K pages, relu-dot scores; the projections are library GEMMs"),
     "select_pages": Kernel("topk_pages_kernel", "csrc/sparse.cu", "trl_topk_pages",
                            note="k-th largest by radix select, kept page indices ascending"),
     "spec_accept": Kernel("spec_accept_kernel", "csrc/misc.cu", "trl_spec_accept",

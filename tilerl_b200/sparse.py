@@ -152,6 +152,10 @@ class SparseKV:
                     cached = ops.quest_select(q, kcache, table[:early], k)      # device: score + select, two kernels
                     if cached is not None:
                         self.stats["device_selects"] += 1
+                if cached is None and self.indexer is not None and hasattr(ops, "index_select"):
+                    cached = ops.index_select(self.indexer, layer, q, kcache, table[:early], k)
+                    if cached is not None:
+                        self.stats["device_selects"] += 1
                 if cached is None:
                     if self.indexer is not None:
                         scores = self.indexer.scores(layer, q, kcache, table[:early])
