@@ -119,3 +119,48 @@ def test_committed_measurements_pass_the_schema_and_their_floors():
         assert B.validate(r)["status"] == "ok", r
     dec = [r for r in recs if r["metric"] == "decode_tok_s" and r["shape"]["tp"] == 1]
     assert dec and dec[0]["floor"] > dec[0]["value"] > 92.4      # above the reference's published figure
+
+
+def test_memory_plan_optional_rows_and_optimizer_variants():
+    cfg = qwen38_27b()
+    base = memory.plan(cfg)
+    p = memory.plan(cfg, drafter={"width": 8}, indexer={}, host_pages=1000)
+    assert {"drafter parameters", "drafter context (per-request K / V)", "page indexer"} <= set(p.rows)
+    assert p.blocks < base.blocks                            # the extras come out of what the KV pool gets
+    assert any(n.startswith("host KV tier") for n in p.notes)
+    assert memory.fit_num_blocks(1000, 100, 0.5) == 5 and memory.fit_num_blocks(-5, 100) == 0
+    # the drafter row follows the drafter's real parameter count
+    from tilerl_b200.config import tiny_hybrid
+    from tilerl_b200.models.hybrid import HybridModel
+    from tilerl_b200.spec import BlockDrafter, BlockDrafterConfig
+    small = tiny_hybrid()
+    dc = BlockDrafterConfig(width=4, n_layers=2, n_heads=4, n_kv_heads=2)
+    d = BlockDrafter(HybridModel.build_random(small, seed=0), dc)
+    want = sum(t.numel() * t.element_size() for t in d.p.values())
+    got = memory.drafter_bytes(small, width=4, n_layers=2, n_heads=4, n_kv_heads=2, taps=len(d.aux_layers))["drafter parameters"]
+    assert got == want
+    full = {o: memory.train_plan(cfg, mode="full", zero=8, optimizer=o) for o in ("adamw", "adafactor", "iso")}
+    assert sum(full["adafactor"].values()) < sum(full["iso"].values()) < sum(full["adamw"].values())
+    assert "iso momentum (fp32)" in full["iso"] and "adam moments (fp32 x2)" in full["adamw"]
+    with pytest.raises(ValueError):
+        memory.train_plan(cfg, optimizer="sgd")
+
+
+def test_memory_measure_reports_what_a_live_engine_holds():
+    import torch
+    from helpers import make_engine, rand_prompts
+    from tilerl_b200.config import tiny_hybrid
+    from tilerl_b200.engine import SamplingParams
+    from tilerl_b200.spec import BlockDrafter
+    cfg = tiny_hybrid()
+    eng = make_engine(cfg, blocks=64)
+    eng.drafter = BlockDrafter(eng.model)
+    eng.generate(rand_prompts(cfg, 1, 12, seed=1), SamplingParams(max_tokens=3))
+    m = memory.measure(eng)
+    assert m["kv pool"] == eng.kv.k.numel() * eng.kv.k.element_size() * 2
+    assert m["gdn state slots"] >= eng.states.states.numel() * eng.states.states.element_size()
+    assert m["weights"] >= sum(t.numel() * t.element_size() for t in eng.model.params.values() if isinstance(t, torch.Tensor))
+    assert m["drafter parameters"] == sum(t.numel() * t.element_size() for t in eng.drafter.p.values())
+    p = memory.plan(cfg, blocks=64, slots=4)
+    table = memory.memory_table(p, measured=m, peak=sum(m.values()))
+    assert "measured GiB" in table and "transient" in table

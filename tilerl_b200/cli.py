@@ -140,8 +140,12 @@ def cmd_serve(args) -> int:
     from .config import get_config
     cfg = get_config(args.model)
     if args.dry_run:
+        fp8 = args.kv_format == "fp8"
+        host_pages = args.kv_cold_bytes // memory.kv_block_bytes(cfg, 1, fp8) if args.kv_cold_bytes else 0
         p = memory.plan(cfg, slots=args.slots, blocks=args.blocks, max_batched_tokens=args.max_batched_tokens,
-                        planes=args.spec_width if (args.draft or args.draft_checkpoint) else 1, kv_fp8=args.kv_format == "fp8")
+                        planes=args.spec_width if (args.draft or args.draft_checkpoint) else 1, kv_fp8=fp8,
+                        drafter={"width": args.spec_width} if args.draft == "block" else None,
+                        indexer={} if (args.sparse_k and args.scorer == "learned") else None, host_pages=host_pages)
         print(memory.memory_table(p))
         return 0
     from .engine import StepLimits
