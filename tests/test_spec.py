@@ -168,3 +168,64 @@ def test_block_drafter_context_kv_grows_by_the_new_rows_and_matches_a_fresh_proj
     _, d3 = _drafter(window=6)
     d3.propose(eng, SimpleNamespace(rid=2, state="prefill", toks=[1], n_last_commit=1), taps_all, 0, 12, 2)
     assert d3.ctx_kv[2][0].shape[0] == 6
+
+
+class _FakeVerifyGraph:
+    """Stands where the CUDA-graph verify runner stands, on the CPU: runs the same forward eagerly,
+    walks every chain under greedy acceptance and selects the state plane -- what the graph's last
+    kernel does on the device -- and hands the counts to the engine."""
+
+    def __init__(self, eng):
+        self.eng, self.replays = eng, 0
+
+    def run(self, seqs, need_logits):
+        from tilerl_b200.batch import Batch
+        from tilerl_b200.graph import VerifyOut
+        e = self.eng
+        keep = max(len(s["tokens"]) for s in seqs)
+        batch = Batch.build(seqs, e.device, keep_steps=keep)
+        aux = tuple(e.drafter.aux_layers) if e.drafter is not None else ()
+        res = e.model.forward(batch, e.ops, e.kv, e.states, last_only=False, aux_layers=aux)
+        logits, taps = (res[0], res[2]) if aux else (res, None)
+        amax = [int(t) for t in logits.argmax(-1).tolist()]
+        accept, off = [], 0
+        for s in seqs:
+            chain, ok = s["tokens"], 0
+            while ok + 1 < len(chain) and amax[off + ok] == chain[ok + 1]:
+                ok += 1
+            e.states.select_step(s["slot"], ok)
+            accept.append(ok)
+            off += len(chain)
+        self.replays += 1
+        return VerifyOut(logits, amax, taps, accept)
+
+
+def test_engine_commits_from_device_side_accept_counts_like_the_host_walk():
+    """With accept counts handed over by the verify runner the engine only commits: same tokens and
+    acceptance counters as its own host walk, for a drafter that is always right, one that never is,
+    and the block drafter; sampling requests keep the host walk."""
+    cfg = tiny_hybrid()
+    prompts = rand_prompts(cfg, 2, 20, seed=4)
+    sp = SamplingParams(max_tokens=14)
+    want, base = _run(cfg, prompts, sp)
+    model = base.model
+    cont = {tuple(p): w for p, w in zip(prompts, want)}
+    for name, mk in (("oracle", lambda: OracleDrafter(cont)), ("const", lambda: ConstantDrafter(3)),
+                     ("block", lambda: BlockDrafter(model, seed=1))):
+        host_tokens, host = _run(cfg, prompts, sp, drafter=mk(), width=4, model=model)
+        eng = make_engine(cfg, model=model, drafter=mk(), spec_width=4, planes=4, blocks=160)
+        eng.vgraph = _FakeVerifyGraph(eng)
+        got = [r.tokens for r in eng.generate(prompts, sp)]
+        assert got == host_tokens == want, name
+        assert eng.vgraph.replays > 0 and eng.counters["spec_device_accepts"] > 0, name
+        assert (eng.counters["spec_drafted"], eng.counters["spec_accepted"]) == \
+            (host.counters["spec_drafted"], host.counters["spec_accepted"]), name
+        assert host.counters["spec_device_accepts"] == 0
+    # a request that samples: the runner's counts are ignored, the host walk decides
+    sps = SamplingParams(max_tokens=10, temperature=1.0, top_p=0.9, seed=7)
+    want_s, _ = _run(cfg, prompts, sps, model=model)
+    eng = make_engine(cfg, model=model, drafter=OracleDrafter({tuple(p): w for p, w in zip(prompts, want_s)}),
+                      spec_width=4, planes=4, blocks=160)
+    eng.vgraph = _FakeVerifyGraph(eng)
+    assert [r.tokens for r in eng.generate(prompts, sps)] == want_s
+    assert eng.counters["spec_device_accepts"] == 0
