@@ -144,3 +144,26 @@ def test_bench_record_line_appends_validated_records(tmp_path, monkeypatch, caps
     recs = benchrec.load(str(store))
     assert {r["metric"] for r in recs} == {"decode_tok_s", "decode_ms_per_tick", "prefill_tok_s", "e2e_request_tok_s", "ttft_ms"}
     assert all(r["status"] == "ok" and r["shape"]["tp"] == 2 for r in recs)
+
+
+def test_train_rl_on_a_jsonl_of_prompts_and_answers_with_evals_before_and_after(tmp_path, capsys, monkeypatch):
+    """GRPO on real prompts: --data gives {prompt, answer} rows (the reward is an exact match of the last
+    number of the completion), --eval-gsm8k scores greedy accuracy before and after, --lineage records the
+    parent run, --length-penalty reaches the loop."""
+    monkeypatch.setenv("TRL_RUNS", str(tmp_path / "runs"))
+    data = tmp_path / "train.jsonl"
+    data.write_text("\n".join(json.dumps({"prompt": f"{a}+{b}=", "answer": str(a + b)}) for a, b in ((1, 2), (3, 4), (2, 2), (5, 1))))
+    ev = tmp_path / "eval.jsonl"
+    ev.write_text("\n".join(json.dumps({"question": f"{a}+{a}=", "answer": str(2 * a)}) for a in (1, 2, 3)))
+    assert cli.main(["train", "--model", "tiny", "--device", "cpu", "--rl", "--steps", "1", "--group", "2",
+                 "--prompts-per-step", "2", "--max-tokens", "4", "--data", str(data), "--eval-gsm8k", str(ev),
+                 "--eval-n", "2", "--eval-max-new-tokens", "4", "--length-penalty", "0.01", "--lineage", "abc123"]) == 0
+    out = [json.loads(ln) for ln in capsys.readouterr().out.splitlines() if ln.startswith("{")]
+    assert "eval_before" in out[0] and out[0]["eval_before"]["n"] == 2
+    assert "eval_after" in out[-1] and 0.0 <= out[-1]["eval_after"]["accuracy"] <= 1.0
+    steps = [o for o in out if "reward" in o or "mean_reward" in o]
+    assert len(steps) == 1
+    runs = os.listdir(tmp_path / "runs")
+    man = json.load(open(tmp_path / "runs" / runs[0] / "manifest.json"))
+    assert man["parent"] == "abc123" and man["inputs"]["data"] == str(data)
+    assert any("eval_before_accuracy" in m for m in man["metrics"])

@@ -90,6 +90,16 @@ def build_parser() -> argparse.ArgumentParser:
     t.add_argument("--eval-every", type=int, default=0, help="adapter runs: eval reward on held-out prompts every N steps")
     t.add_argument("--patience", type=int, default=3, help="adapter runs: stop after this many evals without improvement")
     t.add_argument("--runs", default=None, help="run manifest directory (default: $TRL_RUNS or ./runs)")
+    t.add_argument("--data", default=None,
+                   help="JSONL of {prompt, answer}: real prompts; the reward is an exact match of the completion's last number")
+    t.add_argument("--eval-gsm8k", default=None,
+                   help="JSONL of {prompt | question, answer}: greedy exact-match accuracy before and after the run")
+    t.add_argument("--eval-n", type=int, default=100, help="rows of --eval-gsm8k to score")
+    t.add_argument("--eval-max-new-tokens", type=int, default=256)
+    t.add_argument("--length-penalty", type=float, default=0.0,
+                   help="RL reward subtracts this per generated token: orders an all-right group by length (a group whose "
+                        "task reward ties still gets no gradient from length alone)")
+    t.add_argument("--lineage", default=None, metavar="ID", help="id of the run this one descends from")
 
     b = sub.add_parser("bench", help="prefill / decode throughput, kernel roofline table, calibration")
     _add_model_flags(b)
@@ -266,18 +276,47 @@ def cmd_train(args) -> int:
         if args.load_adapter:
             load_adapter(model, args.load_adapter)
     opt = make_optimizer(flags.get("optim", "adamw"), model.trainable(), flags["lr"])
-    run = Run({"cmd": "train", **flags}, root=args.runs or runs_dir())
-    eng = build_engine(model, ops, device=dev, slots=flags["group"] * flags["prompts_per_step"] + 1,
-                       max_ctx=args.prompt_len + flags["max_tokens"] + 32, prefix=False, graph=False)
+    run = Run({"cmd": "train", **flags, **({"data": args.data} if args.data else {})}, root=args.runs or runs_dir(),
+              parent=args.lineage)
     g = torch.Generator().manual_seed(args.seed)
-    prompts = [torch.randint(0, cfg.vocab, (args.prompt_len,), generator=g).tolist() for _ in range(64)]
+    reward_fn = evals.REWARDS.get(flags["reward"], evals.reward_even)
+    tok = eval_items = None
+    if args.data or args.eval_gsm8k:
+        from .tokenizer import load_tokenizer
+        tok = load_tokenizer(args.tokenizer, cfg.vocab)
+
+        def read_jsonl(path):
+            with open(path) as f:
+                rows = [json.loads(ln) for ln in f if ln.strip()]
+            return [{"question": r.get("prompt", r.get("question")), "answer": str(r["answer"])} for r in rows]
+    if args.data:
+        items = read_jsonl(args.data)
+        prompts = [tok.encode(it["question"]) for it in items]
+        reward_fn = evals.make_text_reward(tok, {it["question"]: it["answer"] for it in items}, kind="gsm8k")
+    else:
+        prompts = [torch.randint(0, cfg.vocab, (args.prompt_len,), generator=g).tolist() for _ in range(64)]
+    if args.eval_gsm8k:
+        eval_items = read_jsonl(args.eval_gsm8k)[:args.eval_n]
+    longest = max(len(p) for p in prompts + ([tok.encode(it["question"]) for it in eval_items] if eval_items else []))
+    eng = build_engine(model, ops, device=dev, slots=max(flags["group"] * flags["prompts_per_step"], 8) + 1,
+                       max_ctx=max(args.prompt_len, longest) + max(flags["max_tokens"], args.eval_max_new_tokens if eval_items else 0) + 32,
+                       prefix=False, graph=False)
+
+    def score(tag):
+        if not eval_items:
+            return
+        eng.invalidate_weights()
+        res = evals.evaluate(eng, tok, eval_items, kind="gsm8k", max_tokens=args.eval_max_new_tokens)
+        run.log(**{f"eval_{tag}_{k}": v for k, v in res.items()})
+        print(json.dumps({f"eval_{tag}": res}), flush=True)
+    score("before")
     post = (lambda m: m.requantize_()) if not flags.get("lora_rank") else None
     if flags.get("lora_rank") and (flags.get("rl") or flags.get("opd")) and (args.eval_every or flags.get("eval_every")):
         # adapter run with evals, early stop and best-adapter save
         kw = dict(max_tokens=flags["max_tokens"], prompts_per_step=flags["prompts_per_step"])
         if not flags.get("opd"):
             kw.update(group=flags["group"], clip_eps=args.clip_eps, kl_coef=args.kl_coef, micro=flags.get("micro") or 0)
-        out = rl.train_adapters(eng, model, prompts[:48], evals.REWARDS.get(flags["reward"], evals.reward_even), opt,
+        out = rl.train_adapters(eng, model, prompts[:48], reward_fn, opt,
                                 steps=flags["steps"], eval_prompts=prompts[48:], eval_every=args.eval_every or flags["eval_every"],
                                 patience=flags.get("patience", args.patience), save_dir=args.save_model, run=run,
                                 opd=bool(flags.get("opd")), **kw)
@@ -288,16 +327,17 @@ def cmd_train(args) -> int:
         loop = rl.opd_loop(eng, model, prompts, opt, steps=flags["steps"], max_tokens=flags["max_tokens"],
                            prompts_per_step=flags["prompts_per_step"])
     elif flags.get("rl"):
-        loop = rl.grpo_loop(eng, model, prompts, evals.REWARDS.get(flags["reward"], evals.reward_even), opt,
+        loop = rl.grpo_loop(eng, model, prompts, reward_fn, opt,
                             steps=flags["steps"], group=flags["group"], prompts_per_step=flags["prompts_per_step"],
                             max_tokens=flags["max_tokens"], clip_eps=args.clip_eps, kl_coef=args.kl_coef,
-                            micro=flags.get("micro") or 0, post_step=post)
+                            micro=flags.get("micro") or 0, post_step=post, length_penalty=args.length_penalty)
     else:
         data = iter(lambda: torch.randint(0, cfg.vocab, (2, args.prompt_len), generator=g), None)
         loop = iter(rl.pretrain(model, data, opt, steps=flags["steps"], lr=flags["lr"]))
     for m in loop:
         run.log(**{k: v for k, v in m.items() if not isinstance(v, dict)})
         print(json.dumps(m, default=str), flush=True)
+    score("after")
     if args.save_model:
         if flags.get("lora_rank"):
             save_adapter(model, args.save_model)
