@@ -167,3 +167,22 @@ def test_train_rl_on_a_jsonl_of_prompts_and_answers_with_evals_before_and_after(
     man = json.load(open(tmp_path / "runs" / runs[0] / "manifest.json"))
     assert man["parent"] == "abc123" and man["inputs"]["data"] == str(data)
     assert any("eval_before_accuracy" in m for m in man["metrics"])
+
+
+def test_train_dry_run_prints_the_training_memory_plan_and_ledger_reads_time_to_score(tmp_path, capsys):
+    assert cli.main(["train", "--model", "qwen38-27b", "--dry-run", "--optim", "adafactor", "--zero", "8",
+                     "--train-seq-len", "4096"]) == 0
+    out = capsys.readouterr().out
+    assert "fp32 master" in out and "adafactor second moment" in out and "total" in out
+    assert cli.main(["train", "--model", "qwen38-27b", "--dry-run", "--lora-rank", "16"]) == 0
+    assert "adapters (fp32)" in capsys.readouterr().out
+    from tilerl_b200 import ledger
+    r = ledger.Run({"cmd": "train"}, root=str(tmp_path))
+    r.log(step=0, eval_reward=0.1)
+    r.log(step=1, eval_reward=0.6)
+    r.finish()
+    assert cli.main(["ledger", "--runs", str(tmp_path), "--time-to-score", "0.5"]) == 0
+    line = capsys.readouterr().out.strip().splitlines()[-1]
+    assert "eval_reward>=0.5:" in line and "never" not in line
+    assert cli.main(["ledger", "--runs", str(tmp_path), "--time-to-score", "0.9"]) == 0
+    assert "never" in capsys.readouterr().out

@@ -100,6 +100,10 @@ def build_parser() -> argparse.ArgumentParser:
                    help="RL reward subtracts this per generated token: orders an all-right group by length (a group whose "
                         "task reward ties still gets no gradient from length alone)")
     t.add_argument("--lineage", default=None, metavar="ID", help="id of the run this one descends from")
+    t.add_argument("--dry-run", action="store_true", help="print the training-side memory plan and exit")
+    t.add_argument("--train-seq-len", type=int, default=0, metavar="S",
+                   help="--dry-run: token rows per micro-batch of the checkpointed tape (default: prompt + --max-tokens)")
+    t.add_argument("--zero", type=int, default=1, help="--dry-run: ranks a full-parameter run shards its state over (ZeRO-3)")
 
     b = sub.add_parser("bench", help="prefill / decode throughput, kernel roofline table, calibration")
     _add_model_flags(b)
@@ -135,6 +139,9 @@ def build_parser() -> argparse.ArgumentParser:
     lg.add_argument("--runs", default=None, help="run manifest directory (default: $TRL_RUNS or ./runs)")
     lg.add_argument("--show", default=None)
     lg.add_argument("--devices", action="store_true")
+    lg.add_argument("--time-to-score", type=float, default=None, metavar="SCORE",
+                    help="per run: seconds of training until --metric first reached SCORE")
+    lg.add_argument("--metric", default="eval_reward", help="logged metric that --time-to-score reads")
     return ap
 
 
@@ -247,6 +254,16 @@ def cmd_train(args) -> int:
                                                                   opd=args.opd),
                                                            **{k: v for k, v in over.items() if v is not None}}
     cfg = get_config(flags.get("model", args.model))
+    if args.dry_run:
+        from . import memory
+        rows = memory.train_plan(cfg, mode="lora" if flags.get("lora_rank") else "full", rank=flags.get("lora_rank") or 16,
+                                 zero=args.zero, optimizer=flags.get("optim") or "adamw",
+                                 micro_tokens=args.train_seq_len or (args.prompt_len + flags["max_tokens"]))
+        width = max(len(k) for k in rows) + 1
+        for k, v in rows.items():
+            print(f"{k:{width}s} {v / memory.GIB:10.2f} GiB")
+        print(f"{'total':{width}s} {sum(rows.values()) / memory.GIB:10.2f} GiB")
+        return 0
     if flags.get("indexer_warmup"):
         # the warm-up runs the dense model on the reference backend and trains only the indexer
         from .factory import build_model as _bm
@@ -442,7 +459,11 @@ def cmd_ledger(args) -> int:
                          indent=1))
         return 0
     for r in ledger.list_runs(args.runs):
-        print(f"{r['id']}  {r['status']:12s} {r['seconds']:8.1f}s  {r['inputs'].get('recipe') or r['inputs'].get('cmd', '')}")
+        line = f"{r['id']}  {r['status']:12s} {r['seconds']:8.1f}s  {r['inputs'].get('recipe') or r['inputs'].get('cmd', '')}"
+        if args.time_to_score is not None:
+            t = ledger.time_to_score(r, args.metric, args.time_to_score)
+            line += f"  {args.metric}>={args.time_to_score:g}: " + (f"{t:.1f}s" if t is not None else "never")
+        print(line)
     return 0
 
 
