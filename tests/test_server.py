@@ -229,6 +229,28 @@ def test_stream_pacing():
     t[0] = 1.0
     assert "".join(first + p.pop_ready()) == "bcde"
     assert Pacer(enabled=False).pop_ready() == []
+    # headroom: nothing leaves until `depth` items arrived (or the wait cap ran out), then the usual cadence
+    t[0] = 0.0
+    p = Pacer(enabled=True, max_delay_s=0.5, clock=lambda: t[0], depth=3)
+    p.push(["a"])
+    t[0] = 0.05
+    p.push(["b"])
+    assert p.pop_ready() == []
+    t[0] = 0.10
+    p.push(["c"])
+    got = p.pop_ready()
+    assert got and got[0] == "a"
+    t[0] = 2.0
+    assert "".join(got + p.pop_ready()) == "abc"
+    t[0] = 0.0
+    p = Pacer(enabled=True, max_delay_s=0.5, clock=lambda: t[0], depth=10)
+    p.push(["x"])
+    t[0] = 0.1
+    p.push(["y"])
+    assert p.pop_ready() == []
+    t[0] = 0.7                                  # the cap: a short stream is not held back for ever
+    assert p.pop_ready()[0] == "x"
+    assert Pacer(enabled=True, depth=5).pop_ready(flush=True) == []
 
 
 def test_web_client_modules_are_served(served):

@@ -58,6 +58,8 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--cold-ssd-path", default=None, help="spill file behind the host tier")
     s.add_argument("--completion-timeout-s", type=float, default=600.0)
     s.add_argument("--stream-pace", action="store_true")
+    s.add_argument("--stream-pace-depth", type=int, default=0, metavar="N",
+                   help="tokens buffered before a paced stream starts (headroom for one stall of the engine)")
     s.add_argument("--no-warmup", action="store_true")
     s.add_argument("--dry-run", action="store_true", help="print the memory ledger and exit")
     s.add_argument("--no-card-guard", action="store_true", help="start even if other processes hold the GPU")
@@ -219,7 +221,8 @@ def cmd_serve(args) -> int:
     if not args.no_warmup:
         eng.precapture((1,))
     eng.run()
-    app = create_app(eng, tok, cfg.name, pace=args.stream_pace, completion_timeout_s=args.completion_timeout_s)
+    app = create_app(eng, tok, cfg.name, pace=args.stream_pace, pace_depth=args.stream_pace_depth,
+                     completion_timeout_s=args.completion_timeout_s)
     import uvicorn
     uvicorn.run(app, host=args.host, port=args.port, log_level="warning")
     return 0

@@ -113,9 +113,9 @@ document.getElementById('f').onsubmit=e=>{e.preventDefault();
 </script></body></html>"""
 
 
-def create_app(engine, tokenizer, model_name: str = "tilerl-b200", *, pace: bool = False,
+def create_app(engine, tokenizer, model_name: str = "tilerl-b200", *, pace: bool = False, pace_depth: int = 0,
                completion_timeout_s: Optional[float] = None) -> FastAPI:
-    ctx = core.ServeContext(engine, tokenizer, model_name, pace=pace)
+    ctx = core.ServeContext(engine, tokenizer, model_name, pace=pace, pace_depth=pace_depth)
     if completion_timeout_s is not None:
         ctx.completion_timeout_s = completion_timeout_s
     app = FastAPI(title="tilerl-b200")
@@ -202,7 +202,7 @@ def create_app(engine, tokenizer, model_name: str = "tilerl-b200", *, pace: bool
                     d["usage"] = usage
                 return f"data: {json.dumps(d, ensure_ascii=False)}\n\n"
             yield chunk({"role": "assistant", "content": ""})
-            pacer = Pacer(enabled=ctx.pace)
+            pacer = Pacer(enabled=ctx.pace, depth=ctx.pace_depth)
             try:
                 async for ch, text in core.deltas(ctx, job, disconnected=request.is_disconnected):
                     key = "reasoning_content" if ch == "reasoning" else "content"

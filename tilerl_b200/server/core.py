@@ -29,6 +29,7 @@ class ServeContext:
     completion_timeout_s: float = float(os.environ.get("TRL_COMPLETION_TIMEOUT_S", "600"))
     health_stuck_s: float = float(os.environ.get("TRL_HEALTH_STUCK_S", "30"))
     pace: bool = False
+    pace_depth: int = 0          # items buffered before a paced stream starts releasing
     started: float = field(default_factory=time.time)
 
 

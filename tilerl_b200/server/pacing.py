@@ -15,8 +15,14 @@ from typing import Deque, List, Optional, Tuple
 
 class Pacer:
     def __init__(self, enabled: bool = True, max_delay_s: float = 0.25, alpha: float = 0.2,
-                 clock=time.monotonic):
+                 clock=time.monotonic, depth: int = 0):
+        """``depth``: items buffered before the paced release starts (headroom that rides over one stall
+        of the producer, e.g. a sparse-KV refresh tick); the wait for it is capped by ``max_delay_s``."""
         self.enabled = enabled
+        self.depth = max(0, int(depth))
+        self._pushed = 0
+        self._first_arrival: Optional[float] = None
+        self._started = self.depth == 0
         self.max_delay_s = max_delay_s
         self.alpha = alpha
         self.clock = clock
@@ -34,6 +40,9 @@ class Pacer:
             inst = len(items) / dt
             self.rate = inst if self.rate is None else (1 - self.alpha) * self.rate + self.alpha * inst
         self._last_arrival = now
+        if self._first_arrival is None:
+            self._first_arrival = now
+        self._pushed += len(items)
         for it in items:
             self.queue.append((now, it))
 
@@ -45,6 +54,11 @@ class Pacer:
             self._last_release = self.clock()
             return out
         now = self.clock()
+        if not self._started:
+            first = now if self._first_arrival is None else self._first_arrival
+            if self._pushed < self.depth and now - first < self.max_delay_s:
+                return []                 # still filling the headroom
+            self._started = True
         out: List[str] = []
         gap = 1.0 / max(self.rate, 1e-3)
         while self.queue:
