@@ -186,3 +186,12 @@ def test_train_dry_run_prints_the_training_memory_plan_and_ledger_reads_time_to_
     assert "eval_reward>=0.5:" in line and "never" not in line
     assert cli.main(["ledger", "--runs", str(tmp_path), "--time-to-score", "0.9"]) == 0
     assert "never" in capsys.readouterr().out
+
+
+def test_spill_file_capacity_follows_the_flag_or_the_free_space(tmp_path):
+    assert cli.ssd_slots(str(tmp_path / "spill.bin"), 10 * 4096, 4096) == 10
+    assert cli.ssd_slots(str(tmp_path / "spill.bin"), 100, 4096) == 1
+    free = cli.ssd_slots(str(tmp_path / "spill.bin"), 0, 1 << 20)
+    assert 1 <= free <= 1 << 24
+    args = cli.build_parser().parse_args(["serve", "--cold-ssd-path", "x", "--cold-ssd-bytes", "123", "--stream-pace-depth", "12"])
+    assert args.cold_ssd_bytes == 123 and args.stream_pace_depth == 12

@@ -56,6 +56,8 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--kv-cold-bytes", type=int, default=0, help="pinned host bytes for demoted prefix pages (0: off)")
     s.add_argument("--dram-bytes", type=int, default=1 << 30, help="host bytes for demoted GDN snapshots")
     s.add_argument("--cold-ssd-path", default=None, help="spill file behind the host tier")
+    s.add_argument("--cold-ssd-bytes", type=int, default=0, metavar="BYTES",
+                   help="capacity of the spill file (0 with --cold-ssd-path: half of the free space of its filesystem)")
     s.add_argument("--completion-timeout-s", type=float, default=600.0)
     s.add_argument("--stream-pace", action="store_true")
     s.add_argument("--stream-pace-depth", type=int, default=0, metavar="N",
@@ -154,6 +156,15 @@ def _device(args) -> str:
     return "cuda" if torch.cuda.is_available() else "cpu"
 
 
+def ssd_slots(path: str, capacity_bytes: int, slot_bytes: int) -> int:
+    """Pages the spill file may hold: ``capacity_bytes`` of them, or, with no capacity given, half of the
+    free space of the file's filesystem; at least one, at most 2^24."""
+    import shutil
+    if capacity_bytes <= 0:
+        capacity_bytes = shutil.disk_usage(os.path.dirname(os.path.abspath(path)) or ".").free // 2
+    return int(max(1, min(1 << 24, capacity_bytes // max(1, slot_bytes))))
+
+
 def cmd_serve(args) -> int:
     from . import memory
     from .config import get_config
@@ -212,7 +223,8 @@ def cmd_serve(args) -> int:
         from .kv_tiers import ColdSsdFile, DramSnapshots, HostKvPages
         ssd = None
         if args.cold_ssd_path:
-            ssd = ColdSsdFile(args.cold_ssd_path, slot_bytes=eng.kv.block_bytes(), slots=4096)
+            ssd = ColdSsdFile(args.cold_ssd_path, slot_bytes=eng.kv.block_bytes(),
+                              slots=ssd_slots(args.cold_ssd_path, args.cold_ssd_bytes, eng.kv.block_bytes()))
         eng.prefix.host = HostKvPages(args.kv_cold_bytes, pin=dev != "cpu", cold=ssd)
         eng.prefix.dram = DramSnapshots(args.dram_bytes)
     if args.kv_store:
