@@ -217,3 +217,35 @@ def test_opd_loop_teacher_generates_student_trains_and_weights_are_restored():
     moved = sum(float((after[k] - before[k]).abs().sum()) for k in before)
     assert moved > 0
     assert len(eng.prefix) == 0          # nothing cached under either set of weights survives a step
+
+
+def test_grpo_judge_orders_a_tied_group_and_leaves_decided_groups_alone():
+    """A judge sees each group's completions after the rule-based reward: a tie becomes a signal (non-zero
+    advantages, a finite loss), and the judge's view of the rewards is what the rule produced."""
+    from helpers import make_engine, rand_prompts
+    from tilerl_b200 import evals, rl
+    from tilerl_b200.config import tiny_hybrid
+    from tilerl_b200.optim import make_optimizer
+    cfg = tiny_hybrid()
+    eng = make_engine(cfg, blocks=96)
+    model = eng.model
+    model.add_lora(rank=2)
+    opt = make_optimizer("adamw", model.trainable(), 1e-4)
+    prompts = rand_prompts(cfg, 2, 8, seed=3)
+    seen = []
+
+    def judge(prompt, comps, rewards):
+        seen.append((list(prompt), [list(c) for c in comps], list(rewards)))
+        return evals.judge_tiebreak(rewards, ["x" * len(set(c)) for c in comps], lambda a, b: 1.0 if len(a) > len(b) else (0.0 if len(a) < len(b) else 0.5))
+
+    tie = lambda p, c: 1.0                                    # every rollout "right": the rule alone gives no gradient
+    m_plain = next(rl.grpo_loop(eng, model, prompts, tie, opt, steps=1, group=4, prompts_per_step=1, max_tokens=6))
+    m_judge = next(rl.grpo_loop(eng, model, prompts, tie, opt, steps=1, group=4, prompts_per_step=1, max_tokens=6, judge=judge))
+    assert len(seen) == 1 and seen[0][2] == [1.0] * 4 and len(seen[0][1]) == 4
+    assert m_plain["loss"] == 0.0 or abs(m_plain["loss"]) < 1e-12
+    assert m_judge["loss"] == m_judge["loss"]                  # finite
+    # the policy as its own judge: deterministic, symmetric in the order it is asked
+    from tilerl_b200.tokenizer import ByteTokenizer
+    cmp = evals.policy_compare(eng, ByteTokenizer(cfg.vocab), question="2+2=")
+    a, b = cmp("4", "5"), cmp("5", "4")
+    assert 0.0 <= a <= 1.0 and abs(a + b - 1.0) < 1e-9

@@ -104,6 +104,8 @@ def build_parser() -> argparse.ArgumentParser:
                    help="RL reward subtracts this per generated token: orders an all-right group by length (a group whose "
                         "task reward ties still gets no gradient from length alone)")
     t.add_argument("--lineage", default=None, metavar="ID", help="id of the run this one descends from")
+    t.add_argument("--judge", action="store_true",
+                   help="RL: let the policy order the rollouts of a group whose rule-based rewards tie (the rule decides first)")
     t.add_argument("--dry-run", action="store_true", help="print the training-side memory plan and exit")
     t.add_argument("--train-seq-len", type=int, default=0, metavar="S",
                    help="--dry-run: token rows per micro-batch of the checkpointed tape (default: prompt + --max-tokens)")
@@ -341,6 +343,14 @@ def cmd_train(args) -> int:
         res = evals.evaluate(eng, tok, eval_items, kind="gsm8k", max_tokens=args.eval_max_new_tokens)
         run.log(**{f"eval_{tag}_{k}": v for k, v in res.items()})
         print(json.dumps({f"eval_{tag}": res}), flush=True)
+    judge = None
+    if args.judge:
+        from .tokenizer import load_tokenizer
+        jtok = tok or load_tokenizer(args.tokenizer, cfg.vocab)
+
+        def judge(prompt_ids, completions, rewards):
+            cmp = evals.policy_compare(eng, jtok, question=jtok.decode(prompt_ids))
+            return evals.judge_tiebreak(rewards, [jtok.decode(c) for c in completions], cmp)
     score("before")
     post = (lambda m: m.requantize_()) if not flags.get("lora_rank") else None
     if flags.get("lora_rank") and (flags.get("rl") or flags.get("opd")) and (args.eval_every or flags.get("eval_every")):
@@ -362,7 +372,7 @@ def cmd_train(args) -> int:
         loop = rl.grpo_loop(eng, model, prompts, reward_fn, opt,
                             steps=flags["steps"], group=flags["group"], prompts_per_step=flags["prompts_per_step"],
                             max_tokens=flags["max_tokens"], clip_eps=args.clip_eps, kl_coef=args.kl_coef,
-                            micro=flags.get("micro") or 0, post_step=post, length_penalty=args.length_penalty)
+                            micro=flags.get("micro") or 0, post_step=post, length_penalty=args.length_penalty, judge=judge)
     else:
         data = iter(lambda: torch.randint(0, cfg.vocab, (2, args.prompt_len), generator=g), None)
         loop = iter(rl.pretrain(model, data, opt, steps=flags["steps"], lr=flags["lr"]))

@@ -146,3 +146,24 @@ def judge_tiebreak(rewards: Sequence[float], completions: Sequence[str], compare
         for k, i in enumerate(idx):
             out[i] += eps * sc[k] / top
     return out
+
+
+def policy_compare(engine, tokenizer, question: str = "", max_tokens: int = 2) -> Callable[[str, str], float]:
+    """``compare(a, b)`` for :func:`judge_tiebreak` answered by the policy itself: the two completions are
+    shown as answers A and B, the engine decodes greedily and the first ``A`` / ``B`` of its reply decides
+    (1.0: a is better, 0.0: b is, 0.5: neither letter).  Both orders are asked and averaged, so a policy
+    that always says "A" ranks nothing.  Parity: the reference's self-judge (src/tilerl/judge.py)."""
+    from .engine import SamplingParams
+
+    def ask(first: str, second: str) -> float:
+        text = (f"{question}\nAnswer A:\n{first}\nAnswer B:\n{second}\n"
+                "Which answer is better? Reply with A or B.\n")
+        out = tokenizer.decode(engine.generate([tokenizer.encode(text)], SamplingParams(max_tokens=max_tokens))[0].tokens)
+        for ch in out:
+            if ch in "AB":
+                return 1.0 if ch == "A" else 0.0
+        return 0.5
+
+    def compare(a: str, b: str) -> float:
+        return 0.5 * (ask(a, b) + (1.0 - ask(b, a)))
+    return compare

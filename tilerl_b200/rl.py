@@ -262,8 +262,10 @@ def grpo_loop(engine: Engine, model, prompts: Sequence[Sequence[int]], reward_fn
               optimizer, *, steps: int, group: int = 4, prompts_per_step: int = 2,
               max_tokens: int = 16, clip_eps: float = 0.2, kl_coef: float = 0.0, lr: Optional[float] = None,
               micro: int = 0, seed: int = 0, on_policy_updates: int = 1, post_step: Optional[Callable] = None,
-              length_penalty: float = 0.0, **fb) -> Iterator[Dict[str, object]]:
-    """Yields one metrics dict per RL step (mean reward, loss, seconds by phase)."""
+              length_penalty: float = 0.0, judge: Optional[Callable] = None, **fb) -> Iterator[Dict[str, object]]:
+    """Yields one metrics dict per RL step (mean reward, loss, seconds by phase).  ``judge(prompt,
+    completions, rewards) -> rewards``: called per group after the rule-based reward, it may order the
+    completions that tie (the rule decides first; see ``evals.judge_tiebreak``)."""
     engine.invalidate_weights()
     cursor = 0
     for step in range(steps):
@@ -282,6 +284,10 @@ def grpo_loop(engine: Engine, model, prompts: Sequence[Sequence[int]], reward_fn
         comps = [r.tokens if r is not None else [] for r in results]
         live = [len(c) > 0 for c in comps]
         task = [float(reward_fn(batch_prompts[i // group], c)) for i, c in enumerate(comps)]
+        if judge is not None:
+            for gi in range(prompts_per_step):
+                sl = slice(gi * group, (gi + 1) * group)
+                task[sl] = [float(x) for x in judge(batch_prompts[gi], comps[sl], task[sl])]
         rewards = [t - length_penalty * len(c) for t, c in zip(task, comps)]
         # the task reward is the signal: a group that only differs in length gets no gradient
         adv = group_advantages(rewards, group, live, signal=task, groups=prompts_per_step)
