@@ -221,7 +221,7 @@ def test_opd_loop_teacher_generates_student_trains_and_weights_are_restored():
 
 def test_grpo_judge_orders_a_tied_group_and_leaves_decided_groups_alone():
     """A judge sees each group's completions after the rule-based reward: a tie becomes a signal (non-zero
-    advantages, a finite loss), and the judge's view of the rewards is what the rule produced."""
+    advantages, a finite loss), and the rewards handed to it are what the rule produced."""
     from helpers import make_engine, rand_prompts
     from tilerl_b200 import evals, rl
     from tilerl_b200.config import tiny_hybrid
