@@ -180,3 +180,25 @@ def test_batched_sampler_seam_gets_every_sampling_row_of_a_tick():
     assert calls and all(len(c[0]) == 2 for c in calls)          # the two sampling rows, never the other two
     assert all(c[1] == [0, 5] and c[2] == [1.0, 0.9] for c in calls)
     assert all(t in (1, 2, 3, 4) for t in got[3])
+
+
+def test_pool_exhaustion_preempts_the_newest_request_and_recomputes_it_without_changing_its_output():
+    """Two requests that cannot both grow to their full length in a small KV pool: the newer one gives its
+    pages back, waits, is recomputed by a prefill over prompt + generated tokens and finishes with exactly
+    the tokens it produces when memory is plentiful (greedy and seeded sampling); nothing leaks."""
+    cfg = tiny_hybrid()
+    prompts = rand_prompts(cfg, 2, 20, seed=11)
+    for sp in (SamplingParams(max_tokens=44), SamplingParams(max_tokens=44, temperature=1.0, top_p=0.9, seed=3)):
+        roomy = make_engine(cfg, blocks=64)
+        want = [r.tokens for r in roomy.generate(prompts, sp)]
+        assert roomy.counters["preempted"] == 0
+        tight = make_engine(cfg, model=roomy.model, blocks=7)      # 6 usable pages: one request alone needs 4, then 5
+        got = tight.generate(prompts, sp)
+        assert [r.tokens for r in got] == want
+        assert all(r.finish_reason == "length" and len(r.tokens) == 44 for r in got)
+        assert tight.counters["preempted"] >= 1 and tight.counters["failed"] == 0
+        assert tight.kv.used_blocks == 0 and tight.states.free_slots == roomy.states.free_slots
+    # a request that cannot fit even alone is still cut short rather than spinning
+    lone = make_engine(cfg, model=roomy.model, blocks=3)
+    res = lone.generate(prompts[:1], SamplingParams(max_tokens=44))[0]
+    assert res.finish_reason in ("length", "error") and len(res.tokens) < 44

@@ -110,10 +110,17 @@ class _Req:
     prefix_tokens: int = 0
     published: bool = False
     n_last_commit: int = 1   # tokens committed by the last tick (valid tap rows for the drafter)
+    resumed: int = 0         # > 0: preempted after this many generated tokens; its context is being recomputed
 
     @property
     def toks(self) -> List[int]:
         return self.prompt + self.out
+
+    @property
+    def context(self) -> List[int]:
+        """Tokens a prefill has to run before the request can decode: the prompt, or, after a preemption,
+        the prompt and every generated token but the last (which is the input of the next decode tick)."""
+        return self.prompt if not self.resumed else self.prompt + self.out[:self.resumed - 1]
 
 
 @dataclass
@@ -147,6 +154,7 @@ class Engine:
         # benchmark seam: count every draft as accepted, to time the verify tick at full acceptance
         # on models whose greedy choice flips with rounding (random-init weights)
         self.spec_force_accept = False
+        self._events = 0                      # requests finished or preempted so far (progress without a forward)
         # False: walk the chain on the host even when the verify graph counted the accepted drafts (test seam)
         self.spec_device_accept = True
         self.graph = graph_runner
@@ -331,10 +339,11 @@ class Engine:
     def step(self) -> bool:
         with self._lock:
             t0 = time.perf_counter()
+            ev0 = self._events
             self._admit()
             plan = self._build_plan()
             if not plan:
-                return False
+                return self._events != ev0        # nothing to run; a request that was finished or set aside still counts as progress
             t1 = time.perf_counter()
             if self.nvtx:
                 torch.cuda.nvtx.range_push(f"tick/{len(plan)}seq/{sum(len(t) for _, t, _ in plan)}tok")
@@ -375,8 +384,8 @@ class Engine:
         while self._waiting and len(self._running) < self.limits.max_batch:
             r = self._waiting[0]
             spec_pad = self.spec_width
-            need_tokens = len(r.prompt) + 1 + spec_pad
-            hit = self.prefix.lookup(r.prompt)
+            need_tokens = len(r.context) + 1 + spec_pad
+            hit = self.prefix.lookup(r.context)
             have = len(hit.blocks) if hit else 0
             need = self._blocks_needed(need_tokens) - have
             if self.kv.free_blocks < need:
@@ -404,7 +413,8 @@ class Engine:
                 r.blocks.append(self.kv.alloc_block())
             r.state = PREFILL
             self._running.append(r)
-            self.counters["prompt_tokens"] += len(r.prompt)
+            if not r.resumed:
+                self.counters["prompt_tokens"] += len(r.prompt)
 
     def _grow(self, r: _Req, upto_tokens: int) -> bool:
         while len(r.blocks) * KV_BLOCK < upto_tokens:
@@ -426,25 +436,38 @@ class Engine:
             chain = [r.toks[-1]] + (r.drafts if self.spec_width else [])
             start = len(r.toks) - 1
             if not self._grow(r, start + len(chain)):
-                self._running.remove(r)
-                self._finish(r, "length" if r.out else "error")
-                self.counters["preempted"] += 1
-                continue
+                # the pool is exhausted: the newest running requests give their pages back and wait to be
+                # recomputed; only a request that cannot grow with the pool to itself is cut short
+                while not self._grow(r, start + len(chain)):
+                    victim = next((v for v in reversed(self._running) if v is not r and v.state in (DECODE, PREFILL)
+                                   and all(v is not q for q, _, _ in plan)), None)
+                    if victim is None:
+                        break
+                    self._preempt(victim)
+                if not self._grow(r, start + len(chain)):
+                    if any(v is not r for v in self._running):
+                        self._preempt(r)           # others hold the pool and are already planned: this one waits
+                    else:
+                        self._running.remove(r)
+                        self._finish(r, "length" if r.out else "error")
+                        self.counters["failed"] += 0 if r.out else 1
+                    continue
             plan.append((r, chain, start))
             budget -= len(chain)
         for r in self._running:
             if r.state != PREFILL or budget <= 0:
                 continue
-            n_prompt = len(r.prompt)
+            ctx = r.context
+            n_prompt = len(ctx)
             end = min(n_prompt, r.n_computed + budget)
             if end < n_prompt:
                 al = self.limits.prefill_align
                 end = max(r.n_computed + 1, r.n_computed + (end - r.n_computed) // al * al)
             boundary = (n_prompt - 1) // KV_BLOCK * KV_BLOCK
             if not isinstance(self.prefix, NoPrefixStore) and r.n_computed < boundary < end \
-                    and not r.published:
+                    and not r.published and not r.resumed:
                 end = boundary  # stop at the block boundary so the GDN snapshot matches it
-            toks = r.prompt[r.n_computed:end]
+            toks = ctx[r.n_computed:end]
             plan.append((r, toks, r.n_computed))
             budget -= len(toks)
         return plan
@@ -504,12 +527,17 @@ class Engine:
             last = base + n - 1 if verify else i   # row of its last token
             if r.state == PREFILL:
                 r.n_computed = start + n
-                self._maybe_publish(r)
-                if r.n_computed == len(r.prompt):
-                    r.state = DECODE
-                    r.t_first = time.monotonic()
-                    self._commit(r, [self._sample(r, logits, last, 0, amax)])
-                    self._offer_draft(r, taps, tok_off, n)
+                if r.resumed:
+                    if r.n_computed == len(r.context):       # recomputed: the next tick decodes from its last token
+                        r.state, r.resumed = DECODE, 0
+                        r.n_computed = len(r.toks) - 1
+                else:
+                    self._maybe_publish(r)
+                    if r.n_computed == len(r.prompt):
+                        r.state = DECODE
+                        r.t_first = time.monotonic()
+                        self._commit(r, [self._sample(r, logits, last, 0, amax)])
+                        self._offer_draft(r, taps, tok_off, n)
             else:
                 self._verify_commit(r, toks, logits, base, verify, amax,
                                     dev_accept[i] if dev_accept is not None else None)
@@ -539,7 +567,7 @@ class Engine:
             if p.temperature <= 0.0 or p.allowed_ids is not None:
                 continue
             if r.state == PREFILL:
-                if start + n != len(r.prompt):
+                if r.resumed or start + n != len(r.prompt):
                     continue
                 cand = [(base + n - 1 if verify else i, 0)]
             else:
@@ -655,7 +683,30 @@ class Engine:
             self.prefix.insert(r.prompt[:boundary], r.blocks, snap)
             r.published = True
 
+    def _preempt(self, r: _Req) -> None:
+        """Take a running request off the GPU: its KV pages and state slot go back to the pools and it
+        returns to the head of the waiting queue; when it is admitted again its context (prompt and the
+        tokens generated so far) is recomputed by a prefill and decoding continues where it stopped, so
+        the client sees no difference but the delay."""
+        self._events += 1
+        self._running.remove(r)
+        for b in r.blocks:
+            self.kv.release(b)
+        r.blocks = []
+        if r.slot > 0:
+            self.states.release(r.slot)
+            r.slot = -1
+        if self.drafter is not None and hasattr(self.drafter, "release"):
+            self.drafter.release(r.rid)
+        if self.sparse is not None:
+            self.sparse.release(r.rid)
+        r.resumed = len(r.out) if r.out else 0
+        r.n_computed, r.prefix_tokens, r.drafts, r.state = 0, 0, [], WAITING
+        self._waiting.appendleft(r)
+        self.counters["preempted"] += 1
+
     def _finish(self, r: _Req, reason: str) -> None:
+        self._events += 1
         r.finish_reason = reason
         r.state = DONE
         r.t_done = time.monotonic()
