@@ -137,6 +137,24 @@ def test_spec_decode_matches_plain_on_gpu(setup):
             assert (ch["spec_drafted"], ch["spec_accepted"]) == (c["spec_drafted"], c["spec_accepted"])
 
 
+def test_pool_exhaustion_preempts_and_recomputes_on_gpu(setup):
+    """A KV pool too small for two requests at their full length: the newer one is preempted and
+    recomputed; both finish with the tokens of a roomy pool (up to a near-tie of the logits: the
+    recomputed context comes from a prefill where the first pass decoded token by token)."""
+    from tilerl_b200.engine import SamplingParams
+    from tilerl_b200.factory import build_engine
+    cfg, ops, model = setup
+    prompts = _prompts(cfg, 2, 20, 23)
+    sp = SamplingParams(max_tokens=44)
+    roomy = build_engine(model, ops, slots=4, max_ctx=256, graph=False, prefix=False)
+    want = [r.tokens for r in roomy.generate(prompts, sp)]
+    tight = build_engine(model, ops, slots=4, max_ctx=256, blocks=7, graph=True, prefix=False)
+    res = tight.generate(prompts, sp)
+    assert all(r.finish_reason == "length" and len(r.tokens) == 44 for r in res)
+    assert tight.stats()["preempted"] >= 1 and tight.kv.used_blocks == 0
+    _assert_same_or_near_tie(cfg, ops, model, prompts, want, [r.tokens for r in res], "preempted")
+
+
 def test_sparse_decode_runs_on_gpu(setup):
     """Top-k page selection with k >= pages is exactly dense; with a small k it still runs the
     packed table through the same kernel and stays finite."""
