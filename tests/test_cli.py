@@ -195,3 +195,9 @@ def test_spill_file_capacity_follows_the_flag_or_the_free_space(tmp_path):
     assert 1 <= free <= 1 << 24
     args = cli.build_parser().parse_args(["serve", "--cold-ssd-path", "x", "--cold-ssd-bytes", "123", "--stream-pace-depth", "12"])
     assert args.cold_ssd_bytes == 123 and args.stream_pace_depth == 12
+
+
+def test_text_reward_recipes_need_gold_answers():
+    with pytest.raises(SystemExit) as e:
+        cli.main(["train", "--recipe", "grpo-gsm8k-27b", "--device", "cpu", "--steps", "1"])
+    assert "--data" in str(e.value)

@@ -323,10 +323,14 @@ def cmd_train(args) -> int:
             with open(path) as f:
                 rows = [json.loads(ln) for ln in f if ln.strip()]
             return [{"question": r.get("prompt", r.get("question")), "answer": str(r["answer"])} for r in rows]
+    if flags.get("reward") in ("gsm8k", "boxed") and not args.data and (flags.get("rl") or flags.get("opd")):
+        raise SystemExit(f"reward {flags['reward']!r} scores completions against gold answers: give --data rows.jsonl "
+                         "with {prompt, answer} rows")
     if args.data:
         items = read_jsonl(args.data)
         prompts = [tok.encode(it["question"]) for it in items]
-        reward_fn = evals.make_text_reward(tok, {it["question"]: it["answer"] for it in items}, kind="gsm8k")
+        reward_fn = evals.make_text_reward(tok, {it["question"]: it["answer"] for it in items},
+                                           kind="boxed" if flags.get("reward") == "boxed" else "gsm8k")
     else:
         prompts = [torch.randint(0, cfg.vocab, (args.prompt_len,), generator=g).tolist() for _ in range(64)]
     if args.eval_gsm8k:
