@@ -271,6 +271,9 @@ def cmd_train(args) -> int:
                                                                   opd=args.opd),
                                                            **{k: v for k, v in over.items() if v is not None}}
     cfg = get_config(flags.get("model", args.model))
+    if not args.dry_run and flags.get("reward") in ("gsm8k", "boxed") and not args.data and (flags.get("rl") or flags.get("opd")):
+        raise SystemExit(f"reward {flags['reward']!r} scores completions against gold answers: give --data rows.jsonl "
+                         "with {prompt, answer} rows")
     if args.dry_run:
         from . import memory
         rows = memory.train_plan(cfg, mode="lora" if flags.get("lora_rank") else "full", rank=flags.get("lora_rank") or 16,
@@ -323,9 +326,6 @@ def cmd_train(args) -> int:
             with open(path) as f:
                 rows = [json.loads(ln) for ln in f if ln.strip()]
             return [{"question": r.get("prompt", r.get("question")), "answer": str(r["answer"])} for r in rows]
-    if flags.get("reward") in ("gsm8k", "boxed") and not args.data and (flags.get("rl") or flags.get("opd")):
-        raise SystemExit(f"reward {flags['reward']!r} scores completions against gold answers: give --data rows.jsonl "
-                         "with {prompt, answer} rows")
     if args.data:
         items = read_jsonl(args.data)
         prompts = [tok.encode(it["question"]) for it in items]
