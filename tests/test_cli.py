@@ -67,6 +67,26 @@ def test_generate_and_merge(tmp_path, capsys):
     assert len(open(files[0]).read().splitlines()) == 2
 
 
+def test_generate_sampling_flags_reach_the_requests(tmp_path, capsys, monkeypatch):
+    from tilerl_b200 import engine as eng
+    seen = []
+    real = eng.SamplingParams
+
+    def spy(**kw):
+        seen.append(kw)
+        return real(**kw)
+
+    monkeypatch.setattr(eng, "SamplingParams", spy)
+    p = tmp_path / "p.jsonl"
+    p.write_text('{"prompt": "hi"}\n{"prompt": "yo"}\n{"prompt": "ok"}\n')
+    assert cli.main(["generate", "--model", "tiny", "--device", "cpu", "--prompts", str(p), "--out",
+                     str(tmp_path / "gen"), "--max-new-tokens", "2", "--temperature", "0.8", "--top-p", "0.9",
+                     "--top-k", "5", "--batch", "2"]) == 0
+    capsys.readouterr()
+    assert len(seen) == 3 and all(k["top_p"] == 0.9 and k["top_k"] == 5 and k["max_tokens"] == 2 for k in seen)
+    assert len({k["seed"] for k in seen}) == 3
+
+
 def test_unknown_recipe():
     with pytest.raises(KeyError):
         cli.main(["train", "--recipe", "nope", "--device", "cpu"])

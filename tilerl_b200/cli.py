@@ -132,8 +132,11 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--prompts", required=True)
     g.add_argument("--out", required=True)
     g.add_argument("--workers", type=int, default=1)
-    g.add_argument("--max-tokens", type=int, default=64)
+    g.add_argument("--max-tokens", "--max-new-tokens", dest="max_tokens", type=int, default=64)
     g.add_argument("--temperature", type=float, default=0.0)
+    g.add_argument("--top-p", type=float, default=1.0)
+    g.add_argument("--top-k", type=int, default=0)
+    g.add_argument("--batch", type=int, default=8, help="prompts a worker keeps in flight")
 
     m = sub.add_parser("merge", help="merge fine-tuned checkpoints")
     m.add_argument("--base", required=True)
@@ -466,7 +469,7 @@ def cmd_generate(args) -> int:
     from .generate import generate
     files = generate(args.model, args.prompts, args.out, workers=args.workers, device=_device(args),
                      max_tokens=args.max_tokens, temperature=args.temperature, checkpoint=args.checkpoint,
-                     tokenizer_path=args.tokenizer, seed=args.seed)
+                     tokenizer_path=args.tokenizer, seed=args.seed, top_p=args.top_p, top_k=args.top_k, batch=args.batch)
     print(json.dumps({"files": files}))
     return 0
 

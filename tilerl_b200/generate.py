@@ -29,7 +29,8 @@ def read_prompts(path: str) -> List[str]:
 
 def run_worker(worker: int, n_workers: int, model_name: str, prompts_path: str, out_dir: str, *,
                device: str = "cpu", max_tokens: int = 64, temperature: float = 0.0, checkpoint: Optional[str] = None,
-               tokenizer_path: Optional[str] = None, batch: int = 8, seed: int = 0) -> str:
+               tokenizer_path: Optional[str] = None, batch: int = 8, seed: int = 0, top_p: float = 1.0,
+               top_k: int = 0) -> str:
     from .engine import SamplingParams
     from .factory import build_serving_engine
     from .tokenizer import load_tokenizer
@@ -45,7 +46,8 @@ def run_worker(worker: int, n_workers: int, model_name: str, prompts_path: str, 
         for i in range(0, len(prompts), batch):
             chunk = prompts[i:i + batch]
             ids = [tok.encode(p) for p in chunk]
-            sp = [SamplingParams(max_tokens=max_tokens, temperature=temperature, seed=seed + worker * 100003 + i + j)
+            sp = [SamplingParams(max_tokens=max_tokens, temperature=temperature, top_p=top_p, top_k=top_k,
+                                 seed=seed + worker * 100003 + i + j)
                   for j in range(len(chunk))]
             for p, r in zip(chunk, eng.generate(ids, sp)):
                 f.write(json.dumps({"prompt": p, "completion": tok.decode(r.tokens), "tokens": len(r.tokens),
