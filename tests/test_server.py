@@ -284,3 +284,77 @@ def test_messages_request_capture(served, tmp_path, monkeypatch):
     run(go())
     lines = rec.read_text().splitlines()
     assert len(lines) == 1 and json.loads(lines[0])["body"]["max_tokens"] == 4
+
+
+# ---- idempotency keys --------------------------------------------------------------------------
+def _res(n, reason="stop"):
+    from tilerl_b200.engine import Result
+    return Result(1, list(range(n)), [0.0] * n, reason, 3)
+
+
+def test_key_registry_budgets_and_states():
+    from tilerl_b200.server.idempotency import KeyRegistry, result_bytes
+    reg = KeyRegistry(max_bytes=3 * result_bytes(_res(100)), max_entries=8, entry_ceiling=result_bytes(_res(500)))
+    box = {}
+    reg.register("a", 1, 3)
+    assert reg.lookup("a").state == "running" and reg.take("a", 1, box.get) is None     # nothing finished yet
+    box[1] = _res(100)
+    first = reg.take("a", 1, lambda rid: box.pop(rid, None))
+    again = reg.take("a", 1, lambda rid: box.pop(rid, None))           # the engine gave it away; the copy replays
+    assert first is again and reg.lookup("a").state == "done" and reg.stored("a") is first
+    for i, k in enumerate("bcd"):                                      # byte budget: the oldest finished entry goes
+        reg.register(k, 10 + i, 3)
+        reg.take(k, 10 + i, lambda rid: _res(100))
+    assert reg.lookup("a") is None and reg.lookup("d") is not None and reg.stats()["retained"] == 3
+    reg.register("big", 20, 3)                                          # above the per-entry ceiling: not retained
+    assert len(reg.take("big", 20, lambda rid: _res(501)).tokens) == 501 and reg.lookup("big") is None
+    reg.register("gone", 21, 3)                                         # a cancelled run is not replayed
+    assert reg.take("gone", 21, lambda rid: _res(2, "cancelled")).finish_reason == "cancelled"
+    assert reg.lookup("gone") is None
+    small = KeyRegistry(max_entries=2)                                  # entry count is the second bound
+    for i in range(4):
+        small.register(str(i), i, 1)
+        small.take(str(i), i, lambda rid: _res(1))
+    assert small.stats()["retained"] == 2 and small.lookup("3") is not None and small.lookup("0") is None
+    s = reg.stats()
+    assert s["oversize"] == 1 and s["dropped"] == 1 and s["evicted"] >= 1 and s["retained_bytes"] <= reg.max_bytes
+
+
+def test_idempotency_key_replays_and_joins_instead_of_generating_again(served):
+    eng, app = served
+    ask = {"messages": [{"role": "user", "content": "tell me"}], "max_tokens": 10, "temperature": 1.0,
+           "enable_thinking": False}
+
+    async def go():
+        async with _client(app) as c:
+            a = (await c.post("/v1/chat/completions", json={**ask, "idempotency_key": "k1"})).json()
+            done = eng.counters["finished"]
+            b = (await c.post("/v1/chat/completions", json={**ask, "idempotency_key": "k1"})).json()
+            assert eng.counters["finished"] == done                     # nothing ran for the retry
+            assert a["choices"][0]["message"] == b["choices"][0]["message"] and a["usage"] == b["usage"]
+            # the retry may come back as a stream: the retained answer arrives as one completed stream
+            text = ""
+            async with c.stream("POST", "/v1/chat/completions", json={**ask, "idempotency_key": "k1", "stream": True}) as r:
+                async for line in r.aiter_lines():
+                    if line.startswith("data: {"):
+                        for ch in json.loads(line[6:])["choices"]:
+                            text += ch["delta"].get("content") or ""
+            assert text.strip() == (a["choices"][0]["message"]["content"] or "").strip() and eng.counters["finished"] == done
+            # two requests racing with one key: one generation, two equal answers
+            x, y = await asyncio.gather(c.post("/v1/chat/completions", json={**ask, "idempotency_key": "k2"}),
+                                        c.post("/v1/chat/completions", json={**ask, "idempotency_key": "k2"}))
+            assert x.status_code == y.status_code == 200 and eng.counters["finished"] == done + 1
+            assert x.json()["choices"][0]["message"] == y.json()["choices"][0]["message"]
+            # the other dialects take the same field; a key of the wrong type is refused
+            m = {"model": "m", "max_tokens": 8, "messages": [{"role": "user", "content": "hi"}], "idempotency_key": "k3"}
+            m1, m2 = (await c.post("/v1/messages", json=m)).json(), (await c.post("/v1/messages", json=m)).json()
+            assert m1["content"] == m2["content"] and eng.counters["finished"] == done + 2
+            r1 = await c.post("/v1/responses", json={"input": "hi", "max_output_tokens": 8, "idempotency_key": "k4"})
+            r2 = await c.post("/v1/responses", json={"input": "hi", "max_output_tokens": 8, "idempotency_key": "k4"})
+            assert r1.status_code == r2.status_code == 200 and eng.counters["finished"] == done + 3
+            bad = await c.post("/v1/chat/completions", json={**ask, "idempotency_key": 7})
+            assert bad.status_code == 400 and "idempotency_key" in bad.json()["error"]["message"]
+            h = (await c.get("/health")).json()["idempotency"]
+            assert h["retained"] == 4 and h["replayed"] >= 4 and h["attached"] + h["replayed"] >= 5
+    run(go())
+    assert eng.kv.used_blocks == 0

@@ -10,6 +10,7 @@ Parity: the reference tests its TypeScript client against recorded WebSocket fix
 import json
 import os
 import re
+import time
 
 import pytest
 
@@ -117,7 +118,7 @@ def test_every_request_key_the_client_may_send_is_accepted(served):
     values = {"max_tokens": 4, "temperature": 0.7, "top_p": 0.9, "top_k": 4, "seed": 1, "stop": ["\n\n"],
               "tools": [{"type": "function", "function": {"name": "f", "description": "d",
                                                           "parameters": {"type": "object", "properties": {}}}}],
-              "enable_thinking": False, "reasoning_effort": "low"}
+              "enable_thinking": False, "reasoning_effort": "low", "idempotency_key": "turn-0123"}
     assert set(keys) <= set(values), set(keys) - set(values)
     for k in keys:                       # one key at a time, so a rejected key is named
         frames = _session(app, {"messages": [{"role": "user", "content": "hi"}], "stream": True, k: values[k],
@@ -202,3 +203,64 @@ def test_reveal_buffer_keeps_order_and_bounds_the_lag():
         assert left <= total * (1 - (1000 / 60) / 250) ** k + k + 1, (t, left)
     assert drained and drained[0] <= 8 * 250                  # 5000 characters gone within 2 s
     assert len(out) > 5                                      # revealed over several frames, not at once
+
+
+def test_a_retried_turn_joins_or_replays_and_a_cancel_frame_stops_the_run(served):
+    eng, app = served
+    req = {"messages": [{"role": "user", "content": "go on"}], "stream": True, "max_tokens": 6, "temperature": 1.0,
+           "idempotency_key": "turn-abc"}
+    first = _session(app, req)
+    done = eng.counters["finished"]
+    second = _session(app, req)                               # the retry: same key, nothing generated
+    text = lambda frames: "".join(f["text"] for f in frames if f["type"] == "delta")
+    assert first[-1]["type"] == second[-1]["type"] == "done" and text(first) == text(second)
+    assert first[-1]["usage"] == second[-1]["usage"] and eng.counters["finished"] == done
+    # the Stop button: a cancel frame ends a keyed run for good, and the key is free again
+    from starlette.testclient import TestClient
+    slow = {**req, "idempotency_key": "turn-stop", "max_tokens": 1500}
+    with TestClient(app) as tc:
+        with tc.websocket_connect("/ws/chat") as ws:
+            ws.send_text(json.dumps(slow))
+            ws.send_text(json.dumps({"type": "cancel"}))
+            frames = []
+            while True:
+                f = json.loads(ws.receive_text())
+                frames.append(f)
+                if f["type"] in ("done", "error"):
+                    break
+    assert frames[-1] == {"type": "error", "message": "cancelled", "code": "cancelled"} or frames[-1]["type"] == "done"
+    if frames[-1]["type"] == "error":
+        assert eng.counters["cancelled"] >= 1
+    for _ in range(200):
+        if eng.kv.used_blocks == 0:
+            break
+        time.sleep(0.01)
+    assert eng.kv.used_blocks == 0
+
+
+def _replay_skip(shown, sockets):
+    """transport.js: per channel, a socket counts what it has delivered (`seen`); text below the count already
+    shown by earlier sockets (`shown`) is skipped."""
+    out = ""
+    for deltas in sockets:
+        seen = 0
+        for t in deltas:
+            start, seen = seen, seen + len(t)
+            skip = max(0, shown - start)
+            if skip < len(t):
+                shown += len(t) - skip
+                out += t[skip:]
+    return out
+
+
+def test_transport_shows_each_character_once_when_a_socket_is_reopened():
+    src = _js("transport.js")
+    assert "Math.max(0, shown[f.channel] - from)" in src and "f.text.slice(skip)" in src
+    assert 'JSON.stringify({type: "cancel"})' in src and "request.idempotency_key ? retries : 0" in src
+    answer = "the quick brown fox jumps over the lazy dog"
+    # the first socket dies after 17 characters; the second replays the answer in other pieces
+    assert _replay_skip(0, [["the qu", "ick brown f"], ["the quick ", "brown fox jum", "ps over the lazy dog"]]) == answer
+    assert _replay_skip(0, [[answer], [answer]]) == answer              # dropped after everything but the final frame
+    assert _replay_skip(0, [[], ["the quick", answer[9:]]]) == answer   # dropped before the first delta
+    key = _js("protocol.js")
+    assert "export function newKey" in key and '"turn-" + s' in key

@@ -33,7 +33,7 @@ CHAT_FIELDS = {
     "model", "messages", "max_tokens", "max_completion_tokens", "temperature", "top_p", "top_k", "seed", "stop",
     "stream", "stream_options", "logprobs", "top_logprobs", "tools", "tool_choice", "reasoning_effort",
     "chat_template_kwargs", "enable_thinking", "n", "user", "metadata", "presence_penalty",
-    "frequency_penalty", "response_format", "parallel_tool_calls", "store",
+    "frequency_penalty", "response_format", "parallel_tool_calls", "store", "idempotency_key",
 }
 
 
@@ -213,7 +213,7 @@ def create_app(engine, tokenizer, model_name: str = "tilerl-b200", *, pace: bool
                     yield chunk(json.loads(item))
                 res = None
                 for _ in range(500):
-                    res = engine.take(job.rid)
+                    res = core.take(ctx, job)
                     if res is not None:
                         break
                     await asyncio.sleep(0.01)
@@ -248,24 +248,57 @@ def create_app(engine, tokenizer, model_name: str = "tilerl-b200", *, pace: bool
             await ws.send_text(json.dumps({"type": "error", "message": str(e), "code": "overloaded"}))
             await ws.close()
             return
+        # The socket is read while the answer streams: a {"type": "cancel"} frame stops the run for good
+        # (the Stop button), a dropped socket abandons it (a keyed run goes on for the client's retry).
+        gone = asyncio.Event()
+
+        async def listen():
+            try:
+                while True:
+                    raw = await ws.receive_text()
+                    try:
+                        msg = json.loads(raw)
+                    except ValueError:
+                        continue
+                    if isinstance(msg, dict) and msg.get("type") == "cancel":
+                        core.cancel(ctx, job)
+                        gone.set()
+                        return
+            except (WebSocketDisconnect, RuntimeError):
+                core.abandon(ctx, job)
+                gone.set()
+
+        async def disconnected():
+            return gone.is_set()
+
+        listener = asyncio.create_task(listen())
         try:
-            async for ch, text in core.deltas(ctx, job):
+            async for ch, text in core.deltas(ctx, job, disconnected=disconnected):
                 await ws.send_text(json.dumps({"type": "delta", "channel": ch, "text": text}))
             res = None
             for _ in range(500):
-                res = engine.take(job.rid)
+                if gone.is_set():
+                    break
+                res = core.take(ctx, job)
                 if res is not None:
                     break
                 await asyncio.sleep(0.01)
-            if res is not None:
+            if res is not None and res.finish_reason != "cancelled":
                 f = core.finalize(ctx, job, res)
                 if f.tool_calls:
                     await ws.send_text(json.dumps({"type": "tool_calls", "tool_calls": _tool_calls_json(f.tool_calls)}))
                 await ws.send_text(json.dumps({"type": "done", "finish_reason": f.finish_reason, "usage": _usage(f)}))
+            elif gone.is_set() or res is not None:
+                await ws.send_text(json.dumps({"type": "error", "message": "cancelled", "code": "cancelled"}))
         except WebSocketDisconnect:
-            engine.cancel(job.rid)
+            core.abandon(ctx, job)
         except (TimeoutError, RuntimeError) as e:
-            await ws.send_text(json.dumps({"type": "error", "message": str(e)}))
+            try:
+                await ws.send_text(json.dumps({"type": "error", "message": str(e)}))
+            except (WebSocketDisconnect, RuntimeError):
+                pass
+        finally:
+            listener.cancel()
 
     from .messages import mount as mount_messages
     from .responses import mount as mount_responses

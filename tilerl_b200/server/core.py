@@ -19,6 +19,7 @@ from typing import Any, AsyncIterator, Dict, List, Optional, Tuple
 
 from ..engine import Engine, EngineOverloaded, SamplingParams
 from . import prompt as P
+from .idempotency import RUNNING, KeyRegistry
 
 
 @dataclass
@@ -31,6 +32,7 @@ class ServeContext:
     pace: bool = False
     pace_depth: int = 0          # items buffered before a paced stream starts releasing
     started: float = field(default_factory=time.time)
+    keys: KeyRegistry = field(default_factory=KeyRegistry)   # idempotency_key -> run (see idempotency.py)
 
 
 def overloaded_body(msg: str = "engine overloaded, retry later") -> Dict[str, Any]:
@@ -53,6 +55,17 @@ class Job:
     stop_texts: Tuple[str, ...]
     tools: Optional[List[Dict[str, Any]]]
     want_logprobs: bool = False
+    key: Optional[str] = None       # the request's idempotency_key, if it sent one
+    attached: bool = False          # True: this job joined a run that an earlier request with the key started
+
+
+def _key_of(body: Optional[Dict[str, Any]]) -> Optional[str]:
+    key = (body or {}).get("idempotency_key")
+    if key is None:
+        return None
+    if not isinstance(key, str) or not key or len(key) > 256:
+        raise P.BadRequest("idempotency_key must be a non-empty string of at most 256 characters", "idempotency_key")
+    return key
 
 
 def submit(ctx: ServeContext, messages: List[Dict[str, Any]], *, tools=None, thinking: bool = True,
@@ -65,8 +78,54 @@ def submit(ctx: ServeContext, messages: List[Dict[str, Any]], *, tools=None, thi
     sp = SamplingParams(max_tokens=int(max_tokens), temperature=s["temperature"], top_p=s["top_p"],
                         top_k=s["top_k"], seed=int(seed) if seed is not None else int(time.time_ns() & 0x7FFFFFFF),
                         stop_texts=stops, logprobs=logprobs, max_think_tokens=think_cap)
-    rid = ctx.engine.submit(ids, sp)
-    return Job(rid, len(ids), thinking, stops, tools, logprobs)
+    key = _key_of(body)
+    if key is None:
+        return Job(ctx.engine.submit(ids, sp), len(ids), thinking, stops, tools, logprobs)
+    with ctx.keys.submit_lock():        # two requests racing with one key start one generation
+        e = ctx.keys.lookup(key)
+        if e is not None:               # running: wait on the same request; finished: replay the retained result
+            return Job(e.rid, e.prompt_tokens, thinking, stops, tools, logprobs, key, True)
+        rid = ctx.engine.submit(ids, sp)
+        ctx.keys.register(key, rid, len(ids))
+    return Job(rid, len(ids), thinking, stops, tools, logprobs, key)
+
+
+def take(ctx: ServeContext, job: Job):
+    """``Engine.take`` for a job: a keyed job's result is kept for the key's other waiters and replays."""
+    if job.key is None:
+        return ctx.engine.take(job.rid)
+    return ctx.keys.take(job.key, job.rid, ctx.engine.take)
+
+
+def peek(ctx: ServeContext, job: Job) -> Tuple[List[int], bool]:
+    """Tokens so far and whether the run is over; a keyed job whose result another waiter already took
+    reads the retained copy (the engine no longer knows the request)."""
+    if job.key is not None:
+        res = ctx.keys.stored(job.key)
+        if res is not None:
+            return list(res.tokens), True
+    toks, done = ctx.engine.peek(job.rid)
+    if job.key is not None and done and not toks:
+        res = ctx.keys.stored(job.key)
+        if res is not None:
+            return list(res.tokens), True
+    return toks, done
+
+
+def abandon(ctx: ServeContext, job: Job) -> None:
+    """The client went away.  A request without a key is cancelled; a keyed one keeps running, and its
+    result is retained so that the client's retry with the same key finds it."""
+    if job.key is None:
+        ctx.engine.cancel(job.rid)
+        ctx.engine.take(job.rid)
+
+
+def cancel(ctx: ServeContext, job: Job) -> None:
+    """Stop the run for good (time-out, stop string reached): a later request with the key runs again."""
+    ctx.engine.cancel(job.rid)
+    ctx.engine.take(job.rid)
+    if job.key is not None:
+        ctx.keys.forget(job.key)
 
 
 def _stable_text(ctx: ServeContext, tokens: List[int]) -> str:
@@ -96,7 +155,7 @@ async def deltas(ctx: ServeContext, job: Job, *, disconnected=None, poll_s: floa
     t0 = time.monotonic()
     markers = list(job.stop_texts) + ["</think>", "<tool_call>"]
     while True:
-        toks, done = ctx.engine.peek(job.rid)
+        toks, done = peek(ctx, job)
         text = _strip_specials(_stable_text(ctx, toks))
         text, stopped = _truncate_at_stop(text, job.stop_texts)
         closed = "</think>" in text or not job.thinking
@@ -116,14 +175,17 @@ async def deltas(ctx: ServeContext, job: Job, *, disconnected=None, poll_s: floa
             yield "content", answer[sent_c:]
             sent_c = len(answer)
         if fin:
-            if stopped and not done:
-                ctx.engine.cancel(job.rid)
+            if stopped and not done and job.key is None:
+                ctx.engine.cancel(job.rid)     # (a keyed run ends by the engine's own stop-text check)
             return
         if disconnected is not None and await disconnected():
-            ctx.engine.cancel(job.rid)
+            if job.key is None:
+                ctx.engine.cancel(job.rid)     # (the caller's take() that follows finds the result)
             return
         if time.monotonic() - t0 > ctx.completion_timeout_s:
             ctx.engine.cancel(job.rid)
+            if job.key is not None:
+                ctx.keys.forget(job.key)
             raise TimeoutError("completion timed out")
         await asyncio.sleep(poll_s)
 
@@ -161,16 +223,14 @@ async def complete(ctx: ServeContext, job: Job, disconnected=None) -> Optional[F
     """Wait for the request; ``None`` if the client went away (request cancelled)."""
     t0 = time.monotonic()
     while True:
-        res = ctx.engine.take(job.rid)
+        res = take(ctx, job)
         if res is not None:
             return finalize(ctx, job, res)
         if disconnected is not None and await disconnected():
-            ctx.engine.cancel(job.rid)
-            ctx.engine.take(job.rid)
+            abandon(ctx, job)
             return None
         if time.monotonic() - t0 > ctx.completion_timeout_s:
-            ctx.engine.cancel(job.rid)
-            ctx.engine.take(job.rid)
+            cancel(ctx, job)
             raise TimeoutError("completion timed out")
         await asyncio.sleep(0.01)
 
@@ -183,5 +243,5 @@ def health(ctx: ServeContext) -> Tuple[int, Dict[str, Any]]:
     status = 503 if (stuck or degraded) else 200
     body = {"status": "ok" if status == 200 else ("degraded" if degraded else "stuck"),
             "model": ctx.model_name, "uptime_s": round(time.time() - ctx.started, 1),
-            "liveness": live, "stats": stats}
+            "liveness": live, "stats": stats, "idempotency": ctx.keys.stats()}
     return status, body

@@ -26,7 +26,7 @@ from . import core
 from . import prompt as P
 
 FIELDS = {"model", "messages", "system", "max_tokens", "thinking", "tools", "tool_choice", "stop_sequences",
-          "temperature", "top_p", "top_k", "stream", "metadata", "service_tier"}
+          "temperature", "top_p", "top_k", "stream", "metadata", "service_tier", "idempotency_key"}
 
 
 def to_chat_messages(body: Dict[str, Any]) -> List[Dict[str, Any]]:
@@ -171,7 +171,7 @@ def mount(app, ctx: core.ServeContext) -> None:
                     yield ev("content_block_stop", {"type": "content_block_stop", "index": index})
                 res = None
                 for _ in range(500):
-                    res = ctx.engine.take(job.rid)
+                    res = core.take(ctx, job)
                     if res is not None:
                         break
                     await asyncio.sleep(0.01)

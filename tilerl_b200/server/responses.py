@@ -27,7 +27,7 @@ from . import prompt as P
 
 FIELDS = {"model", "input", "instructions", "max_output_tokens", "temperature", "top_p", "tools", "tool_choice",
           "reasoning", "stream", "store", "metadata", "parallel_tool_calls", "previous_response_id", "text",
-          "truncation", "user", "include"}
+          "truncation", "user", "include", "idempotency_key"}
 
 
 def to_chat_messages(body: Dict[str, Any]) -> List[Dict[str, Any]]:
@@ -153,7 +153,7 @@ def mount(app, ctx: core.ServeContext) -> None:
                     yield ev("response.output_item.done", {"output_index": index, "item": {"id": item_id, "type": open_kind}})
                 res = None
                 for _ in range(500):
-                    res = ctx.engine.take(job.rid)
+                    res = core.take(ctx, job)
                     if res is not None:
                         break
                     await asyncio.sleep(0.01)

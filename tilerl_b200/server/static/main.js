@@ -1,4 +1,4 @@
-import {buildRequest} from "./protocol.js";
+import {buildRequest, newKey} from "./protocol.js";
 import {startChat} from "./transport.js";
 import {StreamBuffer} from "./streamBuffer.js";
 import {MessageView} from "./render.js";
@@ -25,7 +25,7 @@ form.addEventListener("submit", (ev) => {
   const view = new MessageView(log, "assistant");
   const bufs = {reasoning: new StreamBuffer((t) => view.append("reasoning", t)), content: new StreamBuffer((t) => view.append("content", t))};
   meter.reset(); stopBtn.disabled = false;
-  running = startChat(buildRequest(history, opts()), {
+  running = startChat(buildRequest(history, {...opts(), idempotency_key: newKey()}), {
     onDelta(ch, t) { meter.onDelta(t); bufs[ch].push(t); },
     onToolCalls(calls) { view.toolCalls(calls); },
     onEnd(f) {
