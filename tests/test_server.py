@@ -339,7 +339,10 @@ def test_idempotency_key_replays_and_joins_instead_of_generating_again(served):
                     if line.startswith("data: {"):
                         for ch in json.loads(line[6:])["choices"]:
                             text += ch["delta"].get("content") or ""
-            assert text.strip() == (a["choices"][0]["message"]["content"] or "").strip() and eng.counters["finished"] == done
+            # (random bytes: the stream holds back an unfinished UTF-8 tail or tag that the whole answer shows)
+            norm = lambda t: "".join(ch for ch in t if ch != "\ufffd" and not ch.isspace())
+            assert norm(a["choices"][0]["message"]["content"] or "").startswith(norm(text))
+            assert eng.counters["finished"] == done
             # two requests racing with one key: one generation, two equal answers
             x, y = await asyncio.gather(c.post("/v1/chat/completions", json={**ask, "idempotency_key": "k2"}),
                                         c.post("/v1/chat/completions", json={**ask, "idempotency_key": "k2"}))
@@ -358,3 +361,41 @@ def test_idempotency_key_replays_and_joins_instead_of_generating_again(served):
             assert h["retained"] == 4 and h["replayed"] >= 4 and h["attached"] + h["replayed"] >= 5
     run(go())
     assert eng.kv.used_blocks == 0
+
+
+def test_messages_stop_sequence_usage_fields_and_keepalive(served):
+    eng, app = served
+    from tilerl_b200.server import core, messages
+    ctx = app.state.ctx
+    tok = ctx.tokenizer
+    # the matched stop string: the first to occur; reported as stop_reason "stop_sequence"
+    job = core.Job(1, 7, False, ("END", "ZZ"), None)
+    res = _res(0)
+    res.tokens = tok.encode("alpha ZZ beta END")
+    f = core.finalize(ctx, job, res)
+    assert f.content == "alpha" and f.stop_match == "ZZ" and messages._stop_reason(f) == "stop_sequence"
+    res.tokens = tok.encode("no stop here")
+    f = core.finalize(ctx, job, res)
+    assert f.stop_match is None and messages._stop_reason(f) == "end_turn"
+    assert messages._usage(10, 4, 6) == {"input_tokens": 4, "output_tokens": 4, "cache_creation_input_tokens": 0,
+                                         "cache_read_input_tokens": 6}
+    ctx.keepalive_s = 0.0            # every poll without new text pings
+
+    async def go():
+        async with _client(app) as c:
+            j = (await c.post("/v1/messages", json={"model": "m", "max_tokens": 6,
+                                                    "messages": [{"role": "user", "content": "hi"}]})).json()
+            assert set(j["usage"]) == {"input_tokens", "output_tokens", "cache_creation_input_tokens",
+                                       "cache_read_input_tokens"} and j["stop_sequence"] is None
+            async with c.stream("POST", "/v1/messages", json={"model": "m", "max_tokens": 40, "stream": True,
+                                                              "messages": [{"role": "user", "content": "hi"}]}) as s:
+                lines = [ln async for ln in s.aiter_lines()]
+            events = [ln[7:] for ln in lines if ln.startswith("event: ")]
+            assert "ping" in events and events[0] == "message_start" and events[-1] == "message_stop"
+            start = json.loads(next(ln for ln in lines if ln.startswith("data: ") and "message_start" in ln)[6:])
+            assert start["message"]["usage"]["output_tokens"] == 0 and "cache_read_input_tokens" in start["message"]["usage"]
+            async with c.stream("POST", "/v1/chat/completions", json={
+                    "messages": [{"role": "user", "content": "hi"}], "max_tokens": 40, "stream": True}) as s:
+                raw = [ln async for ln in s.aiter_lines()]
+            assert any(ln.startswith(": keepalive") for ln in raw) and raw[-2 if raw[-1] == "" else -1] == "data: [DONE]"
+    run(go())

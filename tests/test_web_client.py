@@ -229,8 +229,8 @@ def test_a_retried_turn_joins_or_replays_and_a_cancel_frame_stops_the_run(served
                 if f["type"] in ("done", "error"):
                     break
     assert frames[-1] == {"type": "error", "message": "cancelled", "code": "cancelled"} or frames[-1]["type"] == "done"
-    if frames[-1]["type"] == "error":
-        assert eng.counters["cancelled"] >= 1
+    if frames[-1]["type"] == "error":       # (cancelled in flight, or already finished and discarded unsent)
+        assert app.state.ctx.keys.lookup("turn-stop") is None
     for _ in range(200):
         if eng.kv.used_blocks == 0:
             break

@@ -204,7 +204,11 @@ def create_app(engine, tokenizer, model_name: str = "tilerl-b200", *, pace: bool
             yield chunk({"role": "assistant", "content": ""})
             pacer = Pacer(enabled=ctx.pace, depth=ctx.pace_depth)
             try:
-                async for ch, text in core.deltas(ctx, job, disconnected=request.is_disconnected):
+                async for ch, text in core.deltas(ctx, job, disconnected=request.is_disconnected,
+                                                  heartbeat_s=ctx.keepalive_s):
+                    if ch == "ping":
+                        yield ": keepalive\n\n"          # an SSE comment: clients ignore it, proxies see traffic
+                        continue
                     key = "reasoning_content" if ch == "reasoning" else "content"
                     pacer.push([json.dumps({key: text})])
                     for item in pacer.pop_ready():

@@ -31,6 +31,7 @@ class ServeContext:
     health_stuck_s: float = float(os.environ.get("TRL_HEALTH_STUCK_S", "30"))
     pace: bool = False
     pace_depth: int = 0          # items buffered before a paced stream starts releasing
+    keepalive_s: float = float(os.environ.get("TRL_SSE_KEEPALIVE_S", "10"))   # silence before a stream pings
     started: float = field(default_factory=time.time)
     keys: KeyRegistry = field(default_factory=KeyRegistry)   # idempotency_key -> run (see idempotency.py)
 
@@ -147,12 +148,21 @@ def _truncate_at_stop(text: str, stops: Tuple[str, ...]) -> Tuple[str, bool]:
     return (text[:cut], True) if cut >= 0 else (text, False)
 
 
-async def deltas(ctx: ServeContext, job: Job, *, disconnected=None, poll_s: float = 0.01
-                 ) -> AsyncIterator[Tuple[str, str]]:
+def _matched_stop(text: str, stops: Tuple[str, ...]) -> Optional[str]:
+    """The stop string that ends the text: the one that occurs first (the longest of those that start there)."""
+    hits = [(text.find(s), -len(s), s) for s in stops if s and s in text]
+    return min(hits)[2] if hits else None
+
+
+async def deltas(ctx: ServeContext, job: Job, *, disconnected=None, poll_s: float = 0.01,
+                 heartbeat_s: Optional[float] = None) -> AsyncIterator[Tuple[str, str]]:
     """Yield ``(channel, new_text)`` as tokens arrive.  Channels: ``reasoning``, ``content``.
-    Text that could still turn into a stop string or a tool-call tag is held back."""
+    Text that could still turn into a stop string or a tool-call tag is held back.  With
+    ``heartbeat_s`` a ``("ping", "")`` item is yielded whenever that long passed without one, so that a
+    long cold prefill does not leave the connection silent (the reference's streams send nothing until
+    the completion is whole, ``docs/api-compat-surface.md``)."""
     sent_r = sent_c = 0
-    t0 = time.monotonic()
+    t0 = last = time.monotonic()
     markers = list(job.stop_texts) + ["</think>", "<tool_call>"]
     while True:
         toks, done = peek(ctx, job)
@@ -170,10 +180,13 @@ async def deltas(ctx: ServeContext, job: Job, *, disconnected=None, poll_s: floa
                 reasoning = reasoning[:len(reasoning) - P.holdback(reasoning, markers)]
         if len(reasoning) > sent_r:
             yield "reasoning", reasoning[sent_r:]
-            sent_r = len(reasoning)
+            sent_r, last = len(reasoning), time.monotonic()
         if len(answer) > sent_c:
             yield "content", answer[sent_c:]
-            sent_c = len(answer)
+            sent_c, last = len(answer), time.monotonic()
+        if heartbeat_s is not None and not fin and time.monotonic() - last >= heartbeat_s:
+            yield "ping", ""
+            last = time.monotonic()
         if fin:
             if stopped and not done and job.key is None:
                 ctx.engine.cancel(job.rid)     # (a keyed run ends by the engine's own stop-text check)
@@ -201,10 +214,12 @@ class Final:
     logprobs: List[float]
     tokens: List[int]
     cached_tokens: int = 0
+    stop_match: Optional[str] = None      # the stop string that ended the answer, if one did
 
 
 def finalize(ctx: ServeContext, job: Job, res) -> Final:
     text = _strip_specials(ctx.tokenizer.decode(res.tokens))
+    match = _matched_stop(text, job.stop_texts)
     text, stopped = _truncate_at_stop(text, job.stop_texts)
     reasoning, answer = P.split_think(text, job.thinking)
     answer, calls = P.parse_tool_calls(answer, job.tools)
@@ -216,7 +231,7 @@ def finalize(ctx: ServeContext, job: Job, res) -> Final:
     elif stopped:
         reason = "stop"
     return Final(reasoning, answer, calls, reason, res.prompt_tokens, len(res.tokens), list(res.logprobs),
-                 list(res.tokens), res.cached_tokens)
+                 list(res.tokens), res.cached_tokens, match if stopped and not calls else None)
 
 
 async def complete(ctx: ServeContext, job: Job, disconnected=None) -> Optional[Final]:

@@ -83,7 +83,20 @@ def _normalise(body: Dict[str, Any]) -> Dict[str, Any]:
 
 
 def _stop_reason(f: core.Final) -> str:
-    return {"stop": "end_turn", "length": "max_tokens", "tool_calls": "tool_use"}.get(f.finish_reason, "end_turn")
+    """``tool_use`` first, then ``stop_sequence`` (one of the request's ``stop_sequences`` ended the answer),
+    else ``max_tokens`` / ``end_turn``."""
+    if f.finish_reason == "tool_calls":
+        return "tool_use"
+    if f.stop_match is not None:
+        return "stop_sequence"
+    return {"stop": "end_turn", "length": "max_tokens"}.get(f.finish_reason, "end_turn")
+
+
+def _usage(prompt_tokens: int, output_tokens: int, cached: int) -> Dict[str, int]:
+    """All four fields are always present; tokens served from the prefix cache count as cache reads and are
+    left out of ``input_tokens``' uncached remainder as the vendor's accounting does."""
+    return {"input_tokens": max(0, prompt_tokens - cached), "output_tokens": output_tokens,
+            "cache_creation_input_tokens": 0, "cache_read_input_tokens": cached}
 
 
 def _blocks(f: core.Final) -> List[Dict[str, Any]]:
@@ -141,9 +154,8 @@ def mount(app, ctx: core.ServeContext) -> None:
             if f is None:
                 return err(499, "client_closed", "client closed request")
             return {"id": mid, "type": "message", "role": "assistant", "model": model, "content": _blocks(f),
-                    "stop_reason": _stop_reason(f), "stop_sequence": None,
-                    "usage": {"input_tokens": f.prompt_tokens, "output_tokens": f.completion_tokens,
-                              "cache_read_input_tokens": f.cached_tokens}}
+                    "stop_reason": _stop_reason(f), "stop_sequence": f.stop_match,
+                    "usage": _usage(f.prompt_tokens, f.completion_tokens, f.cached_tokens)}
 
         async def sse():
             def ev(name: str, data: Dict[str, Any]) -> str:
@@ -151,17 +163,21 @@ def mount(app, ctx: core.ServeContext) -> None:
             yield ev("message_start", {"type": "message_start", "message": {
                 "id": mid, "type": "message", "role": "assistant", "model": model, "content": [],
                 "stop_reason": None, "stop_sequence": None,
-                "usage": {"input_tokens": job.prompt_tokens, "output_tokens": 0}}})
+                "usage": _usage(job.prompt_tokens, 0, 0)}})
             index, open_kind = -1, None
             try:
-                async for ch, text in core.deltas(ctx, job, disconnected=request.is_disconnected):
+                async for ch, text in core.deltas(ctx, job, disconnected=request.is_disconnected,
+                                                  heartbeat_s=ctx.keepalive_s):
+                    if ch == "ping":
+                        yield ev("ping", {"type": "ping"})
+                        continue
                     kind = "thinking" if ch == "reasoning" else "text"
                     if kind != open_kind:
                         if open_kind is not None:
                             yield ev("content_block_stop", {"type": "content_block_stop", "index": index})
                         index += 1
                         open_kind = kind
-                        block = {"type": "thinking", "thinking": ""} if kind == "thinking" else {"type": "text", "text": ""}
+                        block = {"type": "thinking", "thinking": "", "signature": ""} if kind == "thinking" else {"type": "text", "text": ""}
                         yield ev("content_block_start", {"type": "content_block_start", "index": index,
                                                          "content_block": block})
                     delta = ({"type": "thinking_delta", "thinking": text} if kind == "thinking"
@@ -188,7 +204,7 @@ def mount(app, ctx: core.ServeContext) -> None:
                                                                "partial_json": json.dumps(c["arguments"])}})
                     yield ev("content_block_stop", {"type": "content_block_stop", "index": index})
                 yield ev("message_delta", {"type": "message_delta",
-                                           "delta": {"stop_reason": _stop_reason(f), "stop_sequence": None},
+                                           "delta": {"stop_reason": _stop_reason(f), "stop_sequence": f.stop_match},
                                            "usage": {"output_tokens": f.completion_tokens}})
                 yield ev("message_stop", {"type": "message_stop"})
             except (TimeoutError, RuntimeError) as e:

@@ -138,7 +138,11 @@ def mount(app, ctx: core.ServeContext) -> None:
             yield ev("response.created", {"response": _response(rid, model, None, "in_progress", created)})
             index, open_kind, item_id = -1, None, None
             try:
-                async for ch, text in core.deltas(ctx, job, disconnected=request.is_disconnected):
+                async for ch, text in core.deltas(ctx, job, disconnected=request.is_disconnected,
+                                                  heartbeat_s=ctx.keepalive_s):
+                    if ch == "ping":
+                        yield ": keepalive\n\n"          # an SSE comment: clients ignore it, proxies see traffic
+                        continue
                     kind = "reasoning" if ch == "reasoning" else "message"
                     if kind != open_kind:
                         if open_kind is not None:
