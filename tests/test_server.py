@@ -163,6 +163,9 @@ def test_responses_api(served):
             j = r.json()
             assert j["object"] == "response" and j["output"][-1]["type"] == "message"
             assert j["usage"]["output_tokens"] <= 8
+            assert j["usage"]["output_tokens_details"]["reasoning_tokens"] == 0         # effort none: no reasoning span
+            assert j["usage"]["input_tokens_details"] == {"cached_tokens": j["usage"]["input_tokens_details"]["cached_tokens"],
+                                                          "cache_write_tokens": 0}
             async with c.stream("POST", "/v1/responses", json={"input": [{"type": "message", "role": "user",
                                 "content": [{"type": "input_text", "text": "hi"}]}], "max_output_tokens": 6,
                                 "stream": True}) as s:
@@ -170,6 +173,17 @@ def test_responses_api(served):
             assert datas[0]["type"] == "response.created" and datas[-1]["type"] == "response.completed"
             assert [d["sequence_number"] for d in datas] == list(range(len(datas)))
     run(go())
+    from tilerl_b200.server import core, responses
+    ctx = app.state.ctx
+    res = _res(0)
+    res.tokens = ctx.tokenizer.encode("<think>\nsome thought</think>\n\nthe answer")
+    f = core.finalize(ctx, core.Job(1, 5, True, (), None), res)
+    body = responses._response("resp-1", "m", f, "completed", 0)
+    item = body["output"][0]
+    assert item["type"] == "reasoning" and item["summary"][0] == {"type": "summary_text", "text": f.reasoning}
+    assert item["content"][0] == {"type": "reasoning_text", "text": f.reasoning}
+    n = body["usage"]["output_tokens_details"]["reasoning_tokens"]
+    assert n == len(ctx.tokenizer.encode(f.reasoning)) and 0 < n < body["usage"]["output_tokens"]
 
 
 def test_real_sdk_clients(served):

@@ -215,6 +215,7 @@ class Final:
     tokens: List[int]
     cached_tokens: int = 0
     stop_match: Optional[str] = None      # the stop string that ended the answer, if one did
+    reasoning_tokens: int = 0             # tokens of the extracted reasoning span
 
 
 def finalize(ctx: ServeContext, job: Job, res) -> Final:
@@ -231,7 +232,8 @@ def finalize(ctx: ServeContext, job: Job, res) -> Final:
     elif stopped:
         reason = "stop"
     return Final(reasoning, answer, calls, reason, res.prompt_tokens, len(res.tokens), list(res.logprobs),
-                 list(res.tokens), res.cached_tokens, match if stopped and not calls else None)
+                 list(res.tokens), res.cached_tokens, match if stopped and not calls else None,
+                 min(len(res.tokens), len(ctx.tokenizer.encode(reasoning))) if reasoning else 0)
 
 
 async def complete(ctx: ServeContext, job: Job, disconnected=None) -> Optional[Final]:

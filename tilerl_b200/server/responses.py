@@ -69,7 +69,8 @@ def _output_items(f: core.Final) -> List[Dict[str, Any]]:
     items: List[Dict[str, Any]] = []
     if f.reasoning:
         items.append({"type": "reasoning", "id": core.new_id("rs"),
-                      "summary": [{"type": "summary_text", "text": f.reasoning}]})
+                      "summary": [{"type": "summary_text", "text": f.reasoning}],
+                      "content": [{"type": "reasoning_text", "text": f.reasoning}]})   # (older SDKs read `content`)
     if f.content or not f.tool_calls:
         items.append({"type": "message", "id": core.new_id("msg"), "role": "assistant", "status": "completed",
                       "content": [{"type": "output_text", "text": f.content, "annotations": []}]})
@@ -86,7 +87,8 @@ def _response(rid: str, model: str, f, status: str, created: int) -> Dict[str, A
         body["output_text"] = f.content
         body["usage"] = {"input_tokens": f.prompt_tokens, "output_tokens": f.completion_tokens,
                          "total_tokens": f.prompt_tokens + f.completion_tokens,
-                         "input_tokens_details": {"cached_tokens": f.cached_tokens}}
+                         "input_tokens_details": {"cached_tokens": f.cached_tokens, "cache_write_tokens": 0},
+                         "output_tokens_details": {"reasoning_tokens": f.reasoning_tokens}}
         if f.finish_reason == "length":
             body["status"] = "incomplete"
             body["incomplete_details"] = {"reason": "max_output_tokens"}
