@@ -202,3 +202,32 @@ def test_pool_exhaustion_preempts_the_newest_request_and_recomputes_it_without_c
     lone = make_engine(cfg, model=roomy.model, blocks=3)
     res = lone.generate(prompts[:1], SamplingParams(max_tokens=44))[0]
     assert res.finish_reason in ("length", "error") and len(res.tokens) < 44
+
+
+def test_long_fill_cap_bounds_the_prefill_chunk_only_while_the_engine_is_shared():
+    cfg = tiny_hybrid()
+    long_p, short_p = rand_prompts(cfg, 1, 200, seed=21)[0], rand_prompts(cfg, 1, 20, seed=22)[0]
+    limits = StepLimits(max_batched_tokens=128, prefill_align=8, long_prefill_cap=16, long_prefill_min=100)
+    eng = make_engine(cfg, limits=limits, blocks=128)
+    ref_long = make_engine(cfg, blocks=128).generate([long_p], SamplingParams(max_tokens=4))[0].tokens
+    ref_short = make_engine(cfg, blocks=128).generate([short_p], SamplingParams(max_tokens=4))[0].tokens
+    # alone in the engine the fill takes the whole budget: 200 tokens in two ticks
+    alone = make_engine(cfg, limits=limits, blocks=128)
+    rid = alone.submit(long_p, SamplingParams(max_tokens=4))
+    alone.step()
+    assert alone._reqs[rid].n_computed == 128
+    # shared: the long fill advances 16 tokens per tick, the short request prefills beside it and finishes first
+    a = eng.submit(long_p, SamplingParams(max_tokens=4))
+    b = eng.submit(short_p, SamplingParams(max_tokens=4))
+    eng.step()
+    assert eng._reqs[a].n_computed == 16 and eng._reqs[b].n_computed == 20
+    ticks = 1
+    while eng._reqs[b].state != "done":
+        eng.step()
+        ticks += 1
+    assert ticks <= 6 and eng._reqs[a].state == "prefill" and eng._reqs[a].n_computed <= 16 * ticks
+    eng.step()                             # alone again: the cap lifts
+    assert eng._reqs[a].n_computed >= 16 * ticks + 100 or eng._reqs[a].state != "prefill"
+    while eng._reqs[a].state != "done":
+        eng.step()
+    assert eng.take(a).tokens == ref_long and eng.take(b).tokens == ref_short

@@ -46,6 +46,9 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--indexer", default=None, help="directory holding indexer.safetensors (for --scorer learned)")
     s.add_argument("--sparse-min-tokens", type=int, default=4096)
     s.add_argument("--sparse-window-tokens", type=int, default=128)
+    s.add_argument("--sparse-prefill-tokens", type=int, default=0,
+                   help="prefill tokens per tick of a fill of --sparse-min-tokens or more while other requests share "
+                        "the engine (0: the whole --max-batched-tokens budget)")
     s.add_argument("--sparse-refresh-ticks", type=int, default=8)
     s.add_argument("--kv-format", default="bf16", choices=["bf16", "fp8"],
                    help="KV pool format: bf16, or e4m3 with one fp32 scale per token and head")
@@ -222,7 +225,9 @@ def cmd_serve(args) -> int:
                        prefix=not args.no_prefix, graph=args.graph, spec_width=args.spec_width if drafter else 0,
                        drafter=drafter, sparse=sparse, kv_fp8=args.kv_format == "fp8",
                        reserve_bytes=args.device_reserve_mib << 20,
-                       limits=StepLimits(args.max_batch, args.max_batched_tokens, max_inflight=args.max_inflight),
+                       limits=StepLimits(args.max_batch, args.max_batched_tokens, max_inflight=args.max_inflight,
+                                         long_prefill_cap=args.sparse_prefill_tokens,
+                                         long_prefill_min=max(1, args.sparse_min_tokens)),
                        eos_id=tok.eos_id, detokenize=tok.decode, think_ids=getattr(tok, "think_ids", None))
     if args.kv_cold_bytes and hasattr(eng.prefix, "host"):
         from .kv_tiers import ColdSsdFile, DramSnapshots, HostKvPages

@@ -83,6 +83,13 @@ class StepLimits:
     max_total_tokens: int = 1 << 30  # KV tokens across running sequences
     max_inflight: int = 1024         # waiting + running requests
     prefill_align: int = 64          # prefill chunk widths are multiples of this
+    # A long cold fill sharing the engine with other requests takes at most `long_prefill_cap` tokens per
+    # tick once its context reaches `long_prefill_min`, so a short request that arrives during the fill
+    # waits for a short tick (reference docs/serve-cold-prefill-cap.md: 192 on its shared server, 0 =
+    # uncapped for a job that owns the engine).  0 switches the cap off; a fill alone in the engine is
+    # never capped.
+    long_prefill_cap: int = 0
+    long_prefill_min: int = 4096
 
 
 WAITING, PREFILL, DECODE, DONE = "waiting", "prefill", "decode", "done"
@@ -459,7 +466,11 @@ class Engine:
                 continue
             ctx = r.context
             n_prompt = len(ctx)
-            end = min(n_prompt, r.n_computed + budget)
+            take = budget
+            cap = self.limits.long_prefill_cap
+            if cap and n_prompt >= self.limits.long_prefill_min and (len(self._running) > 1 or self._waiting):
+                take = min(take, max(cap, self.limits.prefill_align))
+            end = min(n_prompt, r.n_computed + take)
             if end < n_prompt:
                 al = self.limits.prefill_align
                 end = max(r.n_computed + 1, r.n_computed + (end - r.n_computed) // al * al)
