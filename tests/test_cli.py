@@ -116,7 +116,8 @@ def test_train_deterministic_flag_repeats_the_run(capsys, tmp_path, monkeypatch)
     monkeypatch.setenv("TRL_RUNS", str(tmp_path))
     outs = []
     for _ in range(2):
-        assert cli.main(["train", "--recipe", "grpo-tiny-smoke", "--device", "cpu", "--deterministic", "--steps", "2"]) == 0
+        assert cli.main(["train", "--recipe", "grpo-tiny-smoke", "--device", "cpu", "--deterministic", "--steps", "2",
+                         "--force"]) == 0
         lines = [json.loads(ln) for ln in capsys.readouterr().out.splitlines() if ln.startswith("{")]
         outs.append([(ln.get("loss"), ln.get("reward_mean")) for ln in lines if "loss" in ln])
     assert outs[0] and outs[0] == outs[1]
@@ -221,3 +222,55 @@ def test_text_reward_recipes_need_gold_answers():
     with pytest.raises(SystemExit) as e:
         cli.main(["train", "--recipe", "grpo-gsm8k-27b", "--device", "cpu", "--steps", "1"])
     assert "--data" in str(e.value)
+
+
+def test_train_hands_back_a_finished_run_and_force_trains_again(capsys, tmp_path, monkeypatch):
+    monkeypatch.setenv("TRL_RUNS", str(tmp_path))
+    cmd = ["train", "--recipe", "grpo-tiny-smoke", "--device", "cpu", "--steps", "1", "--seed", "11"]
+    assert cli.main(cmd) == 0
+    first = [json.loads(ln) for ln in capsys.readouterr().out.splitlines() if ln.startswith("{")]
+    assert any("loss" in ln for ln in first)
+    assert cli.main(cmd) == 0                                   # the same inputs: the same run, already done
+    again = [json.loads(ln) for ln in capsys.readouterr().out.splitlines() if ln.startswith("{")]
+    assert len(again) == 1 and again[0]["reused"] is True and again[0]["status"] == "done"
+    assert cli.main(cmd + ["--json"]) == 0                      # --json: the whole manifest
+    man = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert man["id"] == again[0]["run"] and man["inputs"]["seed"] == 11 and man["metrics"]
+    assert cli.main(cmd + ["--force", "--json"]) == 0           # trained again: one line, the fresh manifest
+    out = [ln for ln in capsys.readouterr().out.splitlines() if ln.startswith("{")]
+    assert len(out) == 1 and json.loads(out[0])["id"] == man["id"] and json.loads(out[0])["status"] == "done"
+    assert cli.main(cmd[:-1] + ["12"]) == 0                     # another seed is another run
+    other = [json.loads(ln) for ln in capsys.readouterr().out.splitlines() if ln.startswith("{")]
+    assert any("loss" in ln for ln in other)
+
+
+def test_rollout_length_guards():
+    from tilerl_b200 import rl
+    rl.refuse_short_rollouts(None, 512)                       # nothing measured: nothing to compare
+    rl.refuse_short_rollouts(300.0, 512)                      # 300 <= 0.8 * 512
+    rl.refuse_short_rollouts(1038.0, 512, allow=True)
+    with pytest.raises(SystemExit) as e:
+        rl.refuse_short_rollouts(1038.0, 512)
+    assert "1038" in str(e.value) and "1298" in str(e.value) and "--allow-short-rollouts" in str(e.value)
+    d = rl.RolloutDrift(cap=100)
+    assert all(d.update(95.0, i + 1) for i in range(4))       # fewer than five steps: no verdict yet
+    assert d.update(20.0, 5) is True and d.mean == pytest.approx(80.0)        # (4 * 95 + 20) / 5 = 80 <= 80
+    assert d.update(95.0, 6) is True and d.mean == pytest.approx(80.0)        # the window is the last five
+    d2 = rl.RolloutDrift(cap=100)
+    for i in range(5):
+        ok = d2.update(90.0, i + 1)
+    assert ok is False and "average 90.0" in d2.reason and "above 112" in d2.reason
+
+
+def test_train_stops_when_rollouts_run_into_the_cap(capsys, tmp_path, monkeypatch):
+    # the tiny random policy never ends by itself: every rollout runs to the cap, and the sixth step never starts
+    monkeypatch.setenv("TRL_RUNS", str(tmp_path))
+    cmd = ["train", "--rl", "--model", "tiny", "--device", "cpu", "--steps", "8", "--max-tokens", "4", "--group", "2",
+           "--prompts-per-step", "1", "--seed", "5"]
+    assert cli.main(cmd) == 1
+    cap = capsys.readouterr()
+    steps = [json.loads(ln) for ln in cap.out.splitlines() if ln.startswith("{") and "loss" in ln]
+    assert len(steps) == 5 and "rollout cap is 4" in cap.err
+    assert cli.main(cmd + ["--allow-short-rollouts"]) == 0
+    steps = [json.loads(ln) for ln in capsys.readouterr().out.splitlines() if ln.startswith("{") and "loss" in ln]
+    assert len(steps) == 8

@@ -109,6 +109,13 @@ def build_parser() -> argparse.ArgumentParser:
     t.add_argument("--lineage", default=None, metavar="ID", help="id of the run this one descends from")
     t.add_argument("--judge", action="store_true",
                    help="RL: let the policy order the rollouts of a group whose rule-based rewards tie (the rule decides first)")
+    t.add_argument("--max-think-tokens", type=int, default=0,
+                   help="RL rollouts: cap on the reasoning span, closed by force past it (0: no cap)")
+    t.add_argument("--allow-short-rollouts", action="store_true",
+                   help="skip the rollout-length guards (before training and every five steps); smoke recipes want "
+                        "the truncation, a real run almost never does")
+    t.add_argument("--force", action="store_true", help="train again even if a run with these inputs already finished")
+    t.add_argument("--json", action="store_true", help="print the run manifest as JSON instead of step lines")
     t.add_argument("--dry-run", action="store_true", help="print the training-side memory plan and exit")
     t.add_argument("--train-seq-len", type=int, default=0, metavar="S",
                    help="--dry-run: token rows per micro-batch of the checkpointed tape (default: prompt + --max-tokens)")
@@ -278,6 +285,8 @@ def cmd_train(args) -> int:
                                                                   optim="adamw", reward="even", rl=args.rl,
                                                                   opd=args.opd),
                                                            **{k: v for k, v in over.items() if v is not None}}
+    if flags.get("allow_short_rollouts"):        # (a smoke recipe runs into its cap on purpose)
+        args.allow_short_rollouts = True
     cfg = get_config(flags.get("model", args.model))
     if not args.dry_run and flags.get("reward") in ("gsm8k", "boxed") and not args.data and (flags.get("rl") or flags.get("opd")):
         raise SystemExit(f"reward {flags['reward']!r} scores completions against gold answers: give --data rows.jsonl "
@@ -312,6 +321,21 @@ def cmd_train(args) -> int:
             run.artifacts["indexer"] = args.save_model
         run.finish()
         return 0
+    # everything that changes what the run computes is in its id: two runs that differ in one of these are
+    # two runs, and the same command asked twice is handed the finished manifest
+    inputs = {"cmd": "train", **flags, **({"data": args.data} if args.data else {}), "seed": args.seed,
+              "checkpoint": args.checkpoint, "length_penalty": args.length_penalty, "judge": bool(args.judge),
+              "max_think_tokens": args.max_think_tokens, "allow_short_rollouts": bool(args.allow_short_rollouts),
+              "clip_eps": args.clip_eps, "kl_coef": args.kl_coef, "load_adapter": args.load_adapter,
+              "prompt_len": args.prompt_len}
+    if not args.force:
+        from .ledger import finished_run
+        man = finished_run(inputs, args.lineage, args.runs or runs_dir())
+        if man is not None:
+            print(json.dumps(man if args.json else {"run": man["id"], "status": "done", "reused": True,
+                                                    "hint": "--force trains it again"}, default=str), flush=True)
+            return 0
+    say = (lambda *a, **k: None) if args.json else print
     dev = _device(args)
     ops = make_ops(dev)
     model = build_model(cfg, dev, seed=args.seed, checkpoint=args.checkpoint, ops=ops if dev != "cpu" else None,
@@ -321,8 +345,7 @@ def cmd_train(args) -> int:
         if args.load_adapter:
             load_adapter(model, args.load_adapter)
     opt = make_optimizer(flags.get("optim", "adamw"), model.trainable(), flags["lr"])
-    run = Run({"cmd": "train", **flags, **({"data": args.data} if args.data else {})}, root=args.runs or runs_dir(),
-              parent=args.lineage)
+    run = Run(inputs, root=args.runs or runs_dir(), parent=args.lineage)
     g = torch.Generator().manual_seed(args.seed)
     reward_fn = evals.REWARDS.get(flags["reward"], evals.reward_even)
     tok = eval_items = None
@@ -350,11 +373,19 @@ def cmd_train(args) -> int:
 
     def score(tag):
         if not eval_items:
-            return
+            return None
         eng.invalidate_weights()
         res = evals.evaluate(eng, tok, eval_items, kind="gsm8k", max_tokens=args.eval_max_new_tokens)
         run.log(**{f"eval_{tag}_{k}": v for k, v in res.items()})
-        print(json.dumps({f"eval_{tag}": res}), flush=True)
+        say(json.dumps({f"eval_{tag}": res}), flush=True)
+        return res
+
+    def done():
+        run.finish()
+        if args.json:
+            from .ledger import load_run
+            print(json.dumps(load_run(run.id, run.root), default=str), flush=True)
+        return 0
     judge = None
     if args.judge:
         from .tokenizer import load_tokenizer
@@ -363,7 +394,10 @@ def cmd_train(args) -> int:
         def judge(prompt_ids, completions, rewards):
             cmp = evals.policy_compare(eng, jtok, question=jtok.decode(prompt_ids))
             return evals.judge_tiebreak(rewards, [jtok.decode(c) for c in completions], cmp)
-    score("before")
+    before = score("before")
+    if flags.get("rl") and before:      # the base policy's own length against the rollout cap, both measured
+        if before["mean_tokens"] < args.eval_max_new_tokens:      # (an eval that hit its own cap measured the cap)
+            rl.refuse_short_rollouts(before["mean_tokens"], flags["max_tokens"], args.allow_short_rollouts)
     post = (lambda m: m.requantize_()) if not flags.get("lora_rank") else None
     if flags.get("lora_rank") and (flags.get("rl") or flags.get("opd")) and (args.eval_every or flags.get("eval_every")):
         # adapter run with evals, early stop and best-adapter save
@@ -374,9 +408,8 @@ def cmd_train(args) -> int:
                                 steps=flags["steps"], eval_prompts=prompts[48:], eval_every=args.eval_every or flags["eval_every"],
                                 patience=flags.get("patience", args.patience), save_dir=args.save_model, run=run,
                                 opd=bool(flags.get("opd")), **kw)
-        print(json.dumps({k: v for k, v in out.items() if k != "history"}, default=str), flush=True)
-        run.finish()
-        return 0
+        say(json.dumps({k: v for k, v in out.items() if k != "history"}, default=str), flush=True)
+        return done()
     if flags.get("opd"):
         loop = rl.opd_loop(eng, model, prompts, opt, steps=flags["steps"], max_tokens=flags["max_tokens"],
                            prompts_per_step=flags["prompts_per_step"])
@@ -384,13 +417,19 @@ def cmd_train(args) -> int:
         loop = rl.grpo_loop(eng, model, prompts, reward_fn, opt,
                             steps=flags["steps"], group=flags["group"], prompts_per_step=flags["prompts_per_step"],
                             max_tokens=flags["max_tokens"], clip_eps=args.clip_eps, kl_coef=args.kl_coef,
-                            micro=flags.get("micro") or 0, post_step=post, length_penalty=args.length_penalty, judge=judge)
+                            micro=flags.get("micro") or 0, post_step=post, length_penalty=args.length_penalty, judge=judge,
+                            max_think_tokens=args.max_think_tokens or None)
     else:
         data = iter(lambda: torch.randint(0, cfg.vocab, (2, args.prompt_len), generator=g), None)
         loop = iter(rl.pretrain(model, data, opt, steps=flags["steps"], lr=flags["lr"]))
+    drift = rl.RolloutDrift(flags["max_tokens"]) if flags.get("rl") and not args.allow_short_rollouts else None
     for m in loop:
         run.log(**{k: v for k, v in m.items() if not isinstance(v, dict)})
-        print(json.dumps(m, default=str), flush=True)
+        say(json.dumps(m, default=str), flush=True)
+        if drift is not None and "mean_completion_tokens" in m and not drift.update(m["mean_completion_tokens"], m["step"] + 1):
+            run.gate("rollout_window_mean", drift.mean, drift.threshold, higher_is_better=False)
+            print(drift.reason, file=sys.stderr, flush=True)
+            break
     score("after")
     if args.save_model:
         if flags.get("lora_rank"):
@@ -398,8 +437,8 @@ def cmd_train(args) -> int:
         else:
             save_checkpoint(model, args.save_model)
         run.artifacts["model"] = args.save_model
-    run.finish()
-    return 0
+    done()
+    return 0 if run.status == "done" else 1
 
 
 def cmd_bench(args) -> int:

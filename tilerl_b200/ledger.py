@@ -81,6 +81,19 @@ class Run:
         os.replace(tmp, os.path.join(self.dir, "manifest.json"))
 
 
+def finished_run(inputs: Dict[str, Any], parent: Optional[str] = None, root: Optional[str] = None
+                 ) -> Optional[Dict[str, Any]]:
+    """The manifest of a run with exactly these inputs that already ended with status ``done``, else None.
+    A run's id is the hash of its inputs, so the same command asked twice is the same run: the caller
+    hands back the finished manifest instead of training again unless it was told to (``train --force``;
+    reference ``src/tilerl/ledger.py`` finish / reuse of a finished manifest)."""
+    try:
+        man = load_run(run_id({**inputs, "parent": parent}), root)
+    except (OSError, json.JSONDecodeError):
+        return None
+    return man if man.get("status") == "done" else None
+
+
 def load_run(rid: str, root: Optional[str] = None) -> Dict[str, Any]:
     with open(os.path.join(root or runs_dir(), rid, "manifest.json")) as f:
         return json.load(f)

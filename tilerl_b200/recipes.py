@@ -8,7 +8,7 @@ from typing import Any, Dict
 
 RECIPES: Dict[str, Dict[str, Any]] = {
     "grpo-tiny-smoke": dict(model="tiny-hybrid", rl=True, group=4, prompts_per_step=2, steps=2, max_tokens=8,
-                            lr=1e-5, lora_rank=0, reward="even", optim="adamw"),
+                            lr=1e-5, lora_rank=0, reward="even", optim="adamw", allow_short_rollouts=True),
     "indexer-warmup": dict(model="qwen38-27b", indexer_warmup=True, steps=200, lr=1e-3, ctx=8192),
     "grpo-gsm8k-27b": dict(model="qwen38-27b", rl=True, group=8, prompts_per_step=8, steps=100, max_tokens=1024,
                            lr=1e-6, lora_rank=16, reward="gsm8k", optim="adamw", micro=1, eval_every=10,

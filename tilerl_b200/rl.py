@@ -258,11 +258,54 @@ def drain(engine: Engine, rids: Sequence[int], max_ticks: int = 1 << 30) -> List
     return [engine.take(r) for r in rids]
 
 
+ROLLOUT_HEADROOM = 0.8      # mean completion length above this share of the cap: rollouts are being cut off
+
+
+def refuse_short_rollouts(mean_len: Optional[float], cap: int, allow: bool = False) -> None:
+    """Stop before training when rollouts cannot reach an answer: the policy's measured mean completion
+    length against the rollout cap.  Truncated rollouts never state the answer, every sample of a group
+    scores the floor, and the run trains on a constant reward -- which reads like a hard task, not like
+    a wrong flag.  ``allow`` is for runs that want the truncation (smoke recipes).  Reference
+    ``src/tilerl/train.py:1841`` (``_refuse_short_rollouts``)."""
+    if not mean_len or allow or mean_len <= ROLLOUT_HEADROOM * cap:
+        return
+    raise SystemExit(f"error: the policy averages {mean_len:.0f} completion tokens but the rollout cap is {cap}. "
+                     f"Rollouts would be cut off before they answer, so every group ties at the floor and no "
+                     f"gradient flows. Raise --max-tokens above {mean_len / ROLLOUT_HEADROOM:.0f}, pick an easier "
+                     f"task, or pass --allow-short-rollouts if the truncation is deliberate.")
+
+
+class RolloutDrift:
+    """The same check inside the loop: the mean completion length of the last ``window`` steps against the
+    cap (reference ``src/tilerl/train.py:2448``).  ``update`` returns False once the window mean passes
+    the headroom; ``reason`` then says what to change."""
+
+    def __init__(self, cap: int, window: int = 5):
+        self.cap, self.window, self.threshold = cap, window, ROLLOUT_HEADROOM * cap
+        self.values: List[float] = []
+        self.reason: Optional[str] = None
+        self.mean: Optional[float] = None
+
+    def update(self, mean_len: float, step: int) -> bool:
+        self.values.append(float(mean_len))
+        if len(self.values) < self.window:
+            return True
+        self.mean = sum(self.values[-self.window:]) / self.window
+        if self.mean <= self.threshold:
+            return True
+        self.reason = (f"error: at step {step} the last {self.window} steps average {self.mean:.1f} completion "
+                       f"tokens but the rollout cap is {self.cap}. Rollouts risk being cut off before they answer. "
+                       f"Raise --max-tokens above {self.mean / ROLLOUT_HEADROOM:.0f}, pick an easier task, or pass "
+                       f"--allow-short-rollouts if the truncation is deliberate.")
+        return False
+
+
 def grpo_loop(engine: Engine, model, prompts: Sequence[Sequence[int]], reward_fn: Callable,
               optimizer, *, steps: int, group: int = 4, prompts_per_step: int = 2,
               max_tokens: int = 16, clip_eps: float = 0.2, kl_coef: float = 0.0, lr: Optional[float] = None,
               micro: int = 0, seed: int = 0, on_policy_updates: int = 1, post_step: Optional[Callable] = None,
-              length_penalty: float = 0.0, judge: Optional[Callable] = None, **fb) -> Iterator[Dict[str, object]]:
+              length_penalty: float = 0.0, judge: Optional[Callable] = None,
+              max_think_tokens: Optional[int] = None, **fb) -> Iterator[Dict[str, object]]:
     """Yields one metrics dict per RL step (mean reward, loss, seconds by phase).  ``judge(prompt,
     completions, rewards) -> rewards``: called per group after the rule-based reward, it may order the
     completions that tie (the rule decides first; see ``evals.judge_tiebreak``)."""
@@ -276,7 +319,8 @@ def grpo_loop(engine: Engine, model, prompts: Sequence[Sequence[int]], reward_fn
         for pi, p in enumerate(batch_prompts):
             for g in range(group):
                 sp = SamplingParams(max_tokens=max_tokens, temperature=1.0, top_p=1.0, top_k=0,
-                                    seed=seed + ((step * 1009 + pi) * 131 + g), logprobs=True)
+                                    seed=seed + ((step * 1009 + pi) * 131 + g), logprobs=True,
+                                    max_think_tokens=max_think_tokens)
                 require_on_policy(sp)
                 rids.append(engine.submit(p, sp))
         results = drain(engine, rids)
@@ -317,6 +361,7 @@ def grpo_loop(engine: Engine, model, prompts: Sequence[Sequence[int]], reward_fn
         yield dict(step=step, reward=sum(rewards) / len(rewards), loss=stats.get("loss", 0.0),
                    grad_norm=stats.get("grad_norm", 0.0), tokens=stats.get("tokens", 0),
                    tied_groups=n_tied, completion_tokens=sum(len(c) for c in comps),
+                   mean_completion_tokens=sum(len(c) for c in comps) / max(1, len(comps)),
                    timings=dict(rollout=t1 - t0, score=t2 - t1, train=t3 - t2,
                                 invalidate=t4 - t3, total=t4 - t0))
 
