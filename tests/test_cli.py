@@ -274,3 +274,36 @@ def test_train_stops_when_rollouts_run_into_the_cap(capsys, tmp_path, monkeypatc
     assert cli.main(cmd + ["--allow-short-rollouts"]) == 0
     steps = [json.loads(ln) for ln in capsys.readouterr().out.splitlines() if ln.startswith("{") and "loss" in ln]
     assert len(steps) == 8
+
+
+def test_train_curve_subset_mmlu_arm_and_rollout_rows(tmp_path, capsys, monkeypatch):
+    monkeypatch.setenv("TRL_RUNS", str(tmp_path / "runs"))
+    data = tmp_path / "train.jsonl"
+    data.write_text("\n".join(json.dumps({"prompt": f"{a}+{b}=", "answer": str(a + b)}) for a, b in ((1, 2), (3, 4))))
+    ev = tmp_path / "eval.jsonl"
+    ev.write_text("\n".join(json.dumps({"question": f"{a}+{a}=", "answer": str(2 * a)}) for a in range(1, 9)))
+    mm = tmp_path / "mmlu.jsonl"
+    mm.write_text("\n".join(json.dumps({"question": f"q{i}?", "choices": ["w", "x", "y", "z"], "answer": "B"}) for i in range(3)))
+    base = ["train", "--model", "tiny", "--device", "cpu", "--rl", "--steps", "2", "--group", "2", "--prompts-per-step", "1",
+            "--max-tokens", "4", "--data", str(data), "--eval-gsm8k", str(ev), "--eval-n", "2", "--eval-max-new-tokens", "4",
+            "--eval-every", "1", "--allow-short-rollouts"]
+    with pytest.raises(SystemExit) as e:                        # 4 rows: SE 25 pt against a 5 pt effect
+        cli.main(base + ["--eval-curve-n", "4"])
+    assert "25.0 pt" in str(e.value) and ">=100" in str(e.value)
+    assert cli.main(base + ["--eval-curve-n", "4", "--curve-target-pt", "30", "--eval-mmlu", str(mm)]) == 0
+    out = [json.loads(ln) for ln in capsys.readouterr().out.splitlines() if ln.startswith("{")]
+    curve = [o for o in out if "curve_step" in o]
+    assert [c["curve_step"] for c in curve] == [0, 1, 2] and all(c["curve_n"] == 4 and "curve_se_pt" in c for c in curve)
+    assert sum("mmlu_before" in o for o in out) == 1 and sum("mmlu_after" in o for o in out) == 1
+    assert next(o for o in out if "mmlu_before" in o)["mmlu_before"]["n"] == 2       # --eval-n rows
+    run = os.listdir(tmp_path / "runs")[0]
+    rows = [json.loads(ln) for ln in open(tmp_path / "runs" / run / "rollouts.jsonl")]
+    assert len(rows) == 4 and {r["step"] for r in rows} == {0, 1}          # steps x group x prompts
+    assert all({"tokens", "reward", "task", "finish", "prompt"} <= set(r) for r in rows)
+    man = json.load(open(tmp_path / "runs" / run / "manifest.json"))
+    assert not any("rollouts" in m for m in man["metrics"]) and any("curve_accuracy" in m for m in man["metrics"])
+    from tilerl_b200 import ledger
+    a, b = ledger.curve_rows(list(range(50)), 10, 0), ledger.curve_rows(list(range(50)), 10, 0)
+    assert a == b and a != list(range(10)) and len(set(a)) == 10       # a fixed shuffle, not the head of the file
+    assert ledger.binomial_se_pt(0.5, 100) == pytest.approx(5.0) and ledger.binomial_se_pt(1.0, 10) == 0.0
+    ledger.refuse_blind_curve(100, 5.0)                                   # SE exactly at the target passes

@@ -109,6 +109,13 @@ def build_parser() -> argparse.ArgumentParser:
     t.add_argument("--lineage", default=None, metavar="ID", help="id of the run this one descends from")
     t.add_argument("--judge", action="store_true",
                    help="RL: let the policy order the rollouts of a group whose rule-based rewards tie (the rule decides first)")
+    t.add_argument("--eval-mmlu", default=None, metavar="JSONL",
+                   help="rows {question, choices[4], answer letter}: multiple-choice accuracy before and after")
+    t.add_argument("--eval-curve-n", type=int, default=100,
+                   help="rows of --eval-gsm8k scored every --eval-every steps (a fixed-seed subset)")
+    t.add_argument("--eval-curve-seed", type=int, default=0)
+    t.add_argument("--curve-target-pt", type=float, default=5.0,
+                   help="effect in points the curve is there to locate; the run refuses when 50/sqrt(--eval-curve-n) exceeds it")
     t.add_argument("--max-think-tokens", type=int, default=0,
                    help="RL rollouts: cap on the reasoning span, closed by force past it (0: no cap)")
     t.add_argument("--allow-short-rollouts", action="store_true",
@@ -285,6 +292,10 @@ def cmd_train(args) -> int:
                                                                   optim="adamw", reward="even", rl=args.rl,
                                                                   opd=args.opd),
                                                            **{k: v for k, v in over.items() if v is not None}}
+    curve_every = (args.eval_every or 0) if args.eval_gsm8k and not flags.get("lora_rank") else 0
+    if curve_every and not args.dry_run:
+        from .ledger import refuse_blind_curve
+        refuse_blind_curve(args.eval_curve_n, args.curve_target_pt)
     if flags.get("allow_short_rollouts"):        # (a smoke recipe runs into its cap on purpose)
         args.allow_short_rollouts = True
     cfg = get_config(flags.get("model", args.model))
@@ -327,7 +338,9 @@ def cmd_train(args) -> int:
               "checkpoint": args.checkpoint, "length_penalty": args.length_penalty, "judge": bool(args.judge),
               "max_think_tokens": args.max_think_tokens, "allow_short_rollouts": bool(args.allow_short_rollouts),
               "clip_eps": args.clip_eps, "kl_coef": args.kl_coef, "load_adapter": args.load_adapter,
-              "prompt_len": args.prompt_len}
+              "prompt_len": args.prompt_len, "eval_gsm8k": args.eval_gsm8k, "eval_mmlu": args.eval_mmlu,
+              "eval_n": args.eval_n, "eval_every": args.eval_every, "eval_curve_n": args.eval_curve_n,
+              "eval_curve_seed": args.eval_curve_seed}
     if not args.force:
         from .ledger import finished_run
         man = finished_run(inputs, args.lineage, args.runs or runs_dir())
@@ -349,7 +362,7 @@ def cmd_train(args) -> int:
     g = torch.Generator().manual_seed(args.seed)
     reward_fn = evals.REWARDS.get(flags["reward"], evals.reward_even)
     tok = eval_items = None
-    if args.data or args.eval_gsm8k:
+    if args.data or args.eval_gsm8k or args.eval_mmlu:
         from .tokenizer import load_tokenizer
         tok = load_tokenizer(args.tokenizer, cfg.vocab)
 
@@ -364,14 +377,31 @@ def cmd_train(args) -> int:
                                            kind="boxed" if flags.get("reward") == "boxed" else "gsm8k")
     else:
         prompts = [torch.randint(0, cfg.vocab, (args.prompt_len,), generator=g).tolist() for _ in range(64)]
+    mmlu_items = curve_items = None
     if args.eval_gsm8k:
-        eval_items = read_jsonl(args.eval_gsm8k)[:args.eval_n]
-    longest = max(len(p) for p in prompts + ([tok.encode(it["question"]) for it in eval_items] if eval_items else []))
+        every = read_jsonl(args.eval_gsm8k)
+        eval_items = every[:args.eval_n]
+        if curve_every:
+            from .ledger import curve_rows
+            curve_items = curve_rows(every, args.eval_curve_n, args.eval_curve_seed)
+            if len(curve_items) < args.eval_curve_n:
+                print(f"curve subset is {len(curve_items)} rows, not the {args.eval_curve_n} asked for", file=sys.stderr)
+    if args.eval_mmlu:
+        with open(args.eval_mmlu) as f:
+            mmlu_items = [json.loads(ln) for ln in f if ln.strip()][:args.eval_n]
+    eval_texts = [it["question"] for it in (eval_items or []) + (curve_items or [])] + \
+                 [it["question"] + "\n" + "\n".join(it["choices"]) + "\nA. B. C. D. Answer:" for it in (mmlu_items or [])]
+    longest = max(len(p) for p in prompts + [tok.encode(t) for t in eval_texts])
     eng = build_engine(model, ops, device=dev, slots=max(flags["group"] * flags["prompts_per_step"], 8) + 1,
-                       max_ctx=max(args.prompt_len, longest) + max(flags["max_tokens"], args.eval_max_new_tokens if eval_items else 0) + 32,
+                       max_ctx=max(args.prompt_len, longest) + max(flags["max_tokens"], args.eval_max_new_tokens if eval_texts else 0) + 32,
                        prefix=False, graph=False)
 
     def score(tag):
+        if mmlu_items:
+            eng.invalidate_weights()
+            res = evals.evaluate(eng, tok, mmlu_items, kind="choice", max_tokens=min(8, args.eval_max_new_tokens))
+            run.log(**{f"mmlu_{tag}_{k}": v for k, v in res.items()})
+            say(json.dumps({f"mmlu_{tag}": res}), flush=True)
         if not eval_items:
             return None
         eng.invalidate_weights()
@@ -379,6 +409,15 @@ def cmd_train(args) -> int:
         run.log(**{f"eval_{tag}_{k}": v for k, v in res.items()})
         say(json.dumps({f"eval_{tag}": res}), flush=True)
         return res
+
+    def curve_point(step):
+        from .ledger import binomial_se_pt
+        eng.invalidate_weights()
+        res = evals.evaluate(eng, tok, curve_items, kind="gsm8k", max_tokens=args.eval_max_new_tokens)
+        pt = dict(curve_step=step, curve_accuracy=res["accuracy"], curve_n=res["n"],
+                  curve_se_pt=round(binomial_se_pt(res["accuracy"], res["n"]), 2), curve_mean_tokens=res["mean_tokens"])
+        run.log(**pt)
+        say(json.dumps(pt), flush=True)
 
     def done():
         run.finish()
@@ -423,9 +462,18 @@ def cmd_train(args) -> int:
         data = iter(lambda: torch.randint(0, cfg.vocab, (2, args.prompt_len), generator=g), None)
         loop = iter(rl.pretrain(model, data, opt, steps=flags["steps"], lr=flags["lr"]))
     drift = rl.RolloutDrift(flags["max_tokens"]) if flags.get("rl") and not args.allow_short_rollouts else None
+    if curve_items:
+        curve_point(0)
     for m in loop:
-        run.log(**{k: v for k, v in m.items() if not isinstance(v, dict)})
+        rows = m.pop("rollouts", None) if isinstance(m, dict) else None
+        if rows:            # one JSON row per completion beside the manifest
+            with open(os.path.join(run.dir, "rollouts.jsonl"), "a") as f:
+                for r in rows:
+                    f.write(json.dumps({"step": m["step"], **r}) + "\n")
+        run.log(**{k: v for k, v in m.items() if not isinstance(v, (dict, list))})
         say(json.dumps(m, default=str), flush=True)
+        if curve_items and (m["step"] + 1) % curve_every == 0:
+            curve_point(m["step"] + 1)
         if drift is not None and "mean_completion_tokens" in m and not drift.update(m["mean_completion_tokens"], m["step"] + 1):
             run.gate("rollout_window_mean", drift.mean, drift.threshold, higher_is_better=False)
             print(drift.reason, file=sys.stderr, flush=True)

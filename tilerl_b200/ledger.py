@@ -130,6 +130,36 @@ def time_to_score(run: Dict[str, Any], key: str, target: float) -> Optional[floa
     return None
 
 
+def refuse_blind_curve(n: int, target_pt: float) -> None:
+    """Refuse an accuracy curve whose subset cannot resolve the effect it is there to locate, before the
+    run spends the time.  Worst-case binomial standard error (p = 0.5) in points is 50 / sqrt(n); strictly
+    above the target, the step at which the curve crosses would be chosen by which rows fell into the
+    subset.  Reference ``src/tilerl/ledger.py:614``."""
+    if n <= 0:
+        return
+    se = 50.0 / (n ** 0.5)
+    if se > target_pt:
+        raise SystemExit(f"--eval-curve-n {n} carries a worst-case binomial SE of {se:.1f} pt, above the "
+                         f"--curve-target-pt {target_pt:g} effect the curve locates: the crossing step would be chosen "
+                         f"by which rows fell where. Raise --eval-curve-n to >={(50.0 / target_pt) ** 2:.0f}, or raise "
+                         f"the target")
+
+
+def curve_rows(rows: List[Any], n: int, seed: int) -> List[Any]:
+    """The curve subset: the first ``n`` rows of a fixed-seed shuffle, not of the file (an ordered test file
+    biases its head), the same rows at every step and in every run so that points pair up.  Reference
+    ``src/tilerl/train.py:1729``."""
+    import random
+    pool = list(rows)
+    random.Random(seed).shuffle(pool)
+    return pool[:n]
+
+
+def binomial_se_pt(correct_rate: float, n: int) -> float:
+    """Standard error of an accuracy measured on ``n`` rows, in points, at the point's own rate."""
+    return 100.0 * (max(0.0, correct_rate * (1.0 - correct_rate)) / max(1, n)) ** 0.5
+
+
 class EarlyStop:
     """Stop when the monitored score has not improved by ``min_delta`` for ``patience`` evals."""
 

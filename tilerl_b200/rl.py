@@ -362,6 +362,11 @@ def grpo_loop(engine: Engine, model, prompts: Sequence[Sequence[int]], reward_fn
                    grad_norm=stats.get("grad_norm", 0.0), tokens=stats.get("tokens", 0),
                    tied_groups=n_tied, completion_tokens=sum(len(c) for c in comps),
                    mean_completion_tokens=sum(len(c) for c in comps) / max(1, len(comps)),
+                   # one row per completion, so that length and reward stay paired (group means per step
+                   # confound them with the difficulty of the step's prompts)
+                   rollouts=[dict(prompt=i // group, tokens=len(c), reward=rewards[i], task=task[i],
+                                  finish=(results[i].finish_reason if results[i] is not None else "lost"))
+                             for i, c in enumerate(comps)],
                    timings=dict(rollout=t1 - t0, score=t2 - t1, train=t3 - t2,
                                 invalidate=t4 - t3, total=t4 - t0))
 
@@ -461,7 +466,7 @@ def train_adapters(engine: Engine, model, prompts: Sequence[Sequence[int]], rewa
     for m in loop:
         history.append(m)
         if run is not None:
-            run.log(**{k: v for k, v in m.items() if not isinstance(v, dict)})
+            run.log(**{k: v for k, v in m.items() if not isinstance(v, (dict, list))})
         step = int(m["step"])
         if eval_every and eval_prompts and (step + 1) % eval_every == 0:
             score = eval_reward(engine, eval_prompts, reward_fn, max_tokens=loop_kw.get("max_tokens", 16))

@@ -55,7 +55,7 @@ def main(argv=None):
                           micro=args.micro, post_step=post, checkpoint_layers=True, fused_ce=True):
         torch.cuda.synchronize()
         rows.append(m)
-        print(json.dumps(m, default=float), flush=True)
+        print(json.dumps({k: v for k, v in m.items() if k != "rollouts"}, default=float), flush=True)
     last = rows[-1]["timings"]
     print(json.dumps(dict(metric="grpo_step_s", value=round(last["total"], 3), rollout_s=round(last["rollout"], 3),
                           train_s=round(last["train"], 3), completion_tokens=rows[-1]["completion_tokens"],
