@@ -307,3 +307,31 @@ def test_train_curve_subset_mmlu_arm_and_rollout_rows(tmp_path, capsys, monkeypa
     assert a == b and a != list(range(10)) and len(set(a)) == 10       # a fixed shuffle, not the head of the file
     assert ledger.binomial_se_pt(0.5, 100) == pytest.approx(5.0) and ledger.binomial_se_pt(1.0, 10) == 0.0
     ledger.refuse_blind_curve(100, 5.0)                                   # SE exactly at the target passes
+
+
+def test_serve_dry_run_json_against_a_given_free_size_and_state_budget(capsys):
+    assert cli.main(["serve", "--model", "qwen38-27b", "--dry-run", "--slots", "16", "--json"]) == 0
+    whole = json.loads(capsys.readouterr().out)
+    assert whole["rows"]["weights"] > 10 << 30 and whole["total_static"] == sum(whole["rows"].values())
+    assert whole["free_after"] == whole["device_bytes"] - whole["total_static"] and whole["blocks"] > 0
+    assert cli.main(["serve", "--model", "qwen38-27b", "--dry-run", "--slots", "16", "--json", "--device-free",
+                     str(80 << 30), "--state-bytes", str(3 << 30)]) == 0
+    part = json.loads(capsys.readouterr().out)
+    assert part["device_bytes"] == 80 << 30 and part["rows"]["prefix state store"] == 3 << 30
+    assert 0 < part["blocks"] < whole["blocks"] and part["rows"]["weights"] == whole["rows"]["weights"]
+
+
+def test_bench_kernels_takes_a_context_a_prefill_length_and_a_device_name(capsys):
+    assert cli.main(["bench", "--model", "qwen38-27b", "--kernels", "--context", "32768", "--device-name", "h20"]) == 0
+    out = capsys.readouterr().out
+    assert out.startswith("# floors (nominal): 4000 GB/s") and "attn.paged" in out
+    paged = next(ln for ln in out.splitlines() if ln.startswith("attn.paged"))
+    assert float(paged.split()[-5]) > 2000                # 16 layers x 134 MB of K / V at a 32 768-token context
+    assert cli.main(["bench", "--model", "qwen38-27b", "--kernels", "--prefill", "2048"]) == 0
+    out = capsys.readouterr().out
+    assert "lm_head (last token)" in out and "gdn.step" not in out          # the prefill table alone
+    with pytest.raises(SystemExit) as e:
+        cli.main(["bench", "--model", "qwen38-27b", "--kernels", "--device-name", "tpu"])
+    assert "no floor known" in str(e.value)
+    from tilerl_b200.calibration import peaks_for
+    assert peaks_for("NVIDIA B200").source in ("measured", "fallback") and peaks_for("V100-SXM2").hbm_gbs == 900.0

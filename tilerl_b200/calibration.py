@@ -40,6 +40,29 @@ def load_peaks(path: Optional[str] = None) -> Peaks:
     return Peaks(**FALLBACK)
 
 
+# Floors of other parts, for reading the declared cost table against the hardware a published figure was
+# taken on.  These are the vendors' nominal dense figures (memory GB/s, bf16 or fp16 tensor TFLOP/s, link
+# GB/s per direction), not measurements; only the B200 row is measured (or the pool's earlier fallback).
+NOMINAL = {
+    "h20": dict(hbm_gbs=4000.0, bf16_tflops=148.0, bf16_tflops_sustained=148.0, nvlink_gbs=450.0, source="nominal"),
+    "h100": dict(hbm_gbs=3350.0, bf16_tflops=989.0, bf16_tflops_sustained=989.0, nvlink_gbs=450.0, source="nominal"),
+    "v100": dict(hbm_gbs=900.0, bf16_tflops=125.0, bf16_tflops_sustained=125.0, nvlink_gbs=150.0, source="nominal"),
+}
+
+
+def peaks_for(device_name: Optional[str] = None, path: Optional[str] = None) -> Peaks:
+    """Floors the cost table is divided by: ``None`` / ``b200`` -> this machine's measured file (or the
+    fallback); another known name -> its nominal figures; an unknown name has no floor (reference
+    ``tilerl bench --kernels --device-name``, ``src/tilerl/calibration.py``)."""
+    name = (device_name or "b200").lower().replace("nvidia", "").replace("-", "").replace(" ", "")
+    if name.startswith("b200"):
+        return load_peaks(path)
+    for key, row in NOMINAL.items():
+        if name.startswith(key):
+            return Peaks(**row)
+    raise KeyError(f"no floor known for device {device_name!r}; known: b200, {', '.join(sorted(NOMINAL))}")
+
+
 def _best_ms(fn, reps: int = 10, warm: int = 3) -> float:
     import torch
     for _ in range(warm):

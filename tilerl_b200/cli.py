@@ -46,6 +46,11 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--indexer", default=None, help="directory holding indexer.safetensors (for --scorer learned)")
     s.add_argument("--sparse-min-tokens", type=int, default=4096)
     s.add_argument("--sparse-window-tokens", type=int, default=128)
+    s.add_argument("--state-bytes", type=int, default=0,
+                   help="device budget in bytes for the prefix store's GDN snapshots (0: a share of what the KV pool leaves)")
+    s.add_argument("--device-free", type=int, default=None, metavar="BYTES",
+                   help="with --dry-run: plan against this many free device bytes instead of a whole B200")
+    s.add_argument("--json", action="store_true", help="with --dry-run: print the memory rows as JSON")
     s.add_argument("--sparse-prefill-tokens", type=int, default=0,
                    help="prefill tokens per tick of a fill of --sparse-min-tokens or more while other requests share "
                         "the engine (0: the whole --max-batched-tokens budget)")
@@ -134,6 +139,10 @@ def build_parser() -> argparse.ArgumentParser:
     b.add_argument("--gen", type=int, default=64)
     b.add_argument("--batches", default="1")
     b.add_argument("--kernels", action="store_true", help="print the declared cost table and bounds")
+    b.add_argument("--context", type=int, default=None, help="--kernels: pooled context tokens a decode tick reads (default: --prompt-len)")
+    b.add_argument("--prefill", type=int, default=0, metavar="S", help="--kernels: print the prefill table for S tokens instead of decode")
+    b.add_argument("--device-name", default=None,
+                   help="--kernels: the part whose floors divide the table (default: this B200's measured floors; h20, h100, v100: nominal)")
     b.add_argument("--registry", action="store_true", help="print the kernel support matrix (op, precision, target, kernel)")
     b.add_argument("--calibrate", action="store_true", help="measure HBM / GEMM / H2D floors")
     b.add_argument("--tp", type=int, default=1)
@@ -197,8 +206,9 @@ def cmd_serve(args) -> int:
         p = memory.plan(cfg, slots=args.slots, blocks=args.blocks, max_batched_tokens=args.max_batched_tokens,
                         planes=args.spec_width if (args.draft or args.draft_checkpoint) else 1, kv_fp8=fp8,
                         drafter={"width": args.spec_width} if args.draft == "block" else None,
-                        indexer={} if (args.sparse_k and args.scorer == "learned") else None, host_pages=host_pages)
-        print(memory.memory_table(p))
+                        indexer={} if (args.sparse_k and args.scorer == "learned") else None, host_pages=host_pages,
+                        state_bytes=args.state_bytes, **({"device_bytes": args.device_free} if args.device_free else {}))
+        print(json.dumps(memory.plan_json(p, args.device_free or memory.B200_BYTES)) if args.json else memory.memory_table(p))
         return 0
     from .engine import StepLimits
     from .factory import build_engine, build_model, make_ops
@@ -243,6 +253,8 @@ def cmd_serve(args) -> int:
                                          long_prefill_cap=args.sparse_prefill_tokens,
                                          long_prefill_min=max(1, args.sparse_min_tokens)),
                        eos_id=tok.eos_id, detokenize=tok.decode, think_ids=getattr(tok, "think_ids", None))
+    if args.state_bytes and hasattr(eng.prefix, "max_state_bytes"):
+        eng.prefix.max_state_bytes = args.state_bytes          # device budget of resident GDN snapshots
     if args.kv_cold_bytes and hasattr(eng.prefix, "host"):
         from .kv_tiers import ColdSsdFile, DramSnapshots, HostKvPages
         ssd = None
@@ -524,7 +536,17 @@ def cmd_bench(args) -> int:
         return 0
     pk = load_peaks()
     if args.kernels:
-        rows = kc.tick_rows(cfg, kc.TickShape(batch=int(args.batches.split(",")[0]), ctx=args.prompt_len, tp=args.tp))
+        from .calibration import peaks_for
+        try:
+            pk = peaks_for(args.device_name)
+        except KeyError as e:
+            raise SystemExit(str(e.args[0]))
+        print(f"# floors ({pk.source}): {pk.hbm_gbs:.0f} GB/s memory, {pk.bf16_tflops:.0f} TFLOP/s bf16, {pk.nvlink_gbs:.0f} GB/s link")
+        if args.prefill:
+            print(kc.table(kc.prefill_rows(cfg, args.prefill, args.tp), pk.hbm_gbs, 4 * pk.bf16_tflops, pk.nvlink_gbs))
+            return 0
+        rows = kc.tick_rows(cfg, kc.TickShape(batch=int(args.batches.split(",")[0]), ctx=args.context or args.prompt_len,
+                                              tp=args.tp))
         print(kc.table(rows, pk.hbm_gbs, pk.bf16_tflops, pk.nvlink_gbs))
         print(kc.table(kc.prefill_rows(cfg, args.prompt_len, args.tp), pk.hbm_gbs, 4 * pk.bf16_tflops, pk.nvlink_gbs))
         return 0

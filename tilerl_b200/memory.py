@@ -91,10 +91,12 @@ def indexer_bytes(cfg: ModelConfig, *, heads: int = 4, dim: int = 128, tp: int =
 def plan(cfg: ModelConfig, *, device_bytes: int = B200_BYTES, tp: int = 1, slots: int = 64, planes: int = 1,
          max_batched_tokens: int = 8192, reserve_bytes: int = 2 * GIB, pool_fraction: float = 2 / 3,
          state_fraction: float = 1 / 4, kv_fp8: bool = False, blocks: Optional[int] = None,
-         drafter: Optional[dict] = None, indexer: Optional[dict] = None, host_pages: int = 0) -> Plan:
+         drafter: Optional[dict] = None, indexer: Optional[dict] = None, host_pages: int = 0,
+         state_bytes: int = 0) -> Plan:
     """``drafter`` / ``indexer``: keyword dicts for :func:`drafter_bytes` / :func:`indexer_bytes` (``{}`` for the
     defaults); ``host_pages``: pages of the host KV tier (pinned host memory, reported in the notes, not
-    charged to the device)."""
+    charged to the device); ``state_bytes``: a fixed budget for the prefix store's GDN snapshots (0: the
+    default share of what the pool leaves)."""
     p = Plan(slots=slots)
     p.rows["weights"] = weight_bytes(cfg, tp)
     p.rows["gdn state slots"] = slots * state_slot_bytes(cfg, tp, planes)
@@ -116,7 +118,8 @@ def plan(cfg: ModelConfig, *, device_bytes: int = B200_BYTES, tp: int = 1, slots
     per_block = kv_block_bytes(cfg, tp, kv_fp8)
     p.blocks = int(blocks if blocks is not None else fit_num_blocks(left, per_block, pool_fraction))
     p.rows["kv pool"] = p.blocks * per_block
-    p.rows["prefix state store"] = int(left * state_fraction * (1 - pool_fraction) * 3) if blocks is None else 0
+    p.rows["prefix state store"] = int(state_bytes) if state_bytes else \
+        (int(left * state_fraction * (1 - pool_fraction) * 3) if blocks is None else 0)
     p.notes.append(f"kv pool holds {p.blocks * 16:,} tokens ({p.blocks:,} pages of 16)")
     return p
 
@@ -175,6 +178,16 @@ def train_plan(cfg: ModelConfig, *, mode: str = "lora", rank: int = 16, zero: in
         rows[f"{optimizer} second moment (factored, fp32)"] = st["second"] * 4 // div
     rows["tape activations (checkpointed)"] = micro_tokens * cfg.hidden * 2 * (cfg.n_layers + 8)
     return rows
+
+
+def plan_json(p: Plan, device_bytes: Optional[int] = None) -> Dict[str, object]:
+    """The plan's rows as plain data (``serve --dry-run --json``)."""
+    out: Dict[str, object] = {"rows": {k: int(v) for k, v in p.rows.items()}, "total_static": int(p.total),
+                              "blocks": int(p.blocks), "slots": int(p.slots), "notes": list(p.notes)}
+    if device_bytes is not None:
+        out["device_bytes"] = int(device_bytes)
+        out["free_after"] = int(device_bytes - p.total)
+    return out
 
 
 def memory_table(p: Plan, measured: Optional[Dict[str, int]] = None, peak: Optional[int] = None) -> str:
