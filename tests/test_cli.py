@@ -335,3 +335,36 @@ def test_bench_kernels_takes_a_context_a_prefill_length_and_a_device_name(capsys
     assert "no floor known" in str(e.value)
     from tilerl_b200.calibration import peaks_for
     assert peaks_for("NVIDIA B200").source in ("measured", "fallback") and peaks_for("V100-SXM2").hbm_gbs == 900.0
+
+
+def test_train_indexer_corpus_run_reports_recall_per_length_and_a_control(tmp_path, capsys, monkeypatch):
+    import torch
+    monkeypatch.setenv("TRL_RUNS", str(tmp_path / "runs"))
+    g = torch.Generator().manual_seed(0)
+
+    def spans(d, split, ctx, n):
+        os.makedirs(d, exist_ok=True)
+        with open(os.path.join(d, f"{split}_{ctx}.jsonl"), "w") as f:
+            for _ in range(n):
+                f.write(json.dumps({"ctx": ctx, "ids": torch.randint(0, 200, (ctx,), generator=g).tolist()}) + "\n")
+    main_dir, ctl = str(tmp_path / "corpus"), str(tmp_path / "control")
+    for ctx in (96, 128, 160):
+        spans(main_dir, "train", ctx, 2)
+        spans(main_dir, "held", ctx, 3)
+    spans(ctl, "held", 96, 1)
+    from tilerl_b200.sparse_index import load_spans
+    cut = load_spans(main_dir, "held", 4)                      # 4 spans over three lengths: 2 / 1 / 1
+    assert {k: len(v) for k, v in cut.items()} == {"128": 1, "160": 1, "96": 1} | {sorted(cut)[0]: 2}
+    assert cli.main(["train", "--model", "tiny-hybrid", "--indexer-warmup", "--indexer-corpus", main_dir,
+                     "--indexer-control-corpus", ctl, "--steps", "4", "--k-pages", "2", "--q-samples", "4",
+                     "--held-spans", "4", "--indexer-di", "32", "--save-model", str(tmp_path / "ix")]) == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert set(out["recall_before"]) == set(out["recall_after"]) == {"96", "128", "160"}
+    assert all(0.0 < v <= 1.0 for v in out["recall_after"].values()) and out["di"] == 32 and out["k_pages"] == 2
+    assert set(out["control"]["recall_after"]) == {"96"} and out["tokens_seen"] > 0 and out["passed"] is True
+    assert os.path.exists(tmp_path / "ix" / "indexer.safetensors")
+    # the gate: a threshold no indexer reaches fails the run
+    assert cli.main(["train", "--model", "tiny-hybrid", "--indexer-warmup", "--indexer-corpus", main_dir, "--steps", "1",
+                     "--k-pages", "1", "--q-samples", "2", "--held-spans", "3", "--recall-threshold", "1.01"]) == 1
+    man = [json.load(open(tmp_path / "runs" / d / "manifest.json")) for d in os.listdir(tmp_path / "runs")]
+    assert sorted(m["status"] for m in man) == ["done", "gate_failed"]

@@ -114,6 +114,17 @@ def build_parser() -> argparse.ArgumentParser:
     t.add_argument("--lineage", default=None, metavar="ID", help="id of the run this one descends from")
     t.add_argument("--judge", action="store_true",
                    help="RL: let the policy order the rollouts of a group whose rule-based rewards tie (the rule decides first)")
+    t.add_argument("--indexer-corpus", default=None, metavar="DIR",
+                   help="--indexer-warmup over prepared spans: files {train,held}_<label>.jsonl of {ctx, ids} rows; reports "
+                        "recall at --k-pages per held length before and after")
+    t.add_argument("--indexer-control-corpus", default=None, metavar="DIR",
+                   help="held spans of another corpus, scored before / after under the same trained weights")
+    t.add_argument("--indexer-di", type=int, default=128, help="width of an indexer head")
+    t.add_argument("--k-pages", type=int, default=128, help="pages the recall keeps")
+    t.add_argument("--q-samples", type=int, default=16, help="query positions per span and layer")
+    t.add_argument("--q-min-pos", type=int, default=0, help="query positions start here")
+    t.add_argument("--held-spans", type=int, default=0, help="use this many held spans, dealt evenly over the lengths (0: all)")
+    t.add_argument("--recall-threshold", type=float, default=0.0, help="gate: the worst after-recall must reach this")
     t.add_argument("--eval-mmlu", default=None, metavar="JSONL",
                    help="rows {question, choices[4], answer letter}: multiple-choice accuracy before and after")
     t.add_argument("--eval-curve-n", type=int, default=100,
@@ -329,7 +340,32 @@ def cmd_train(args) -> int:
         from .factory import build_model as _bm
         from .sparse_index import LearnedIndexer, warmup
         model = _bm(cfg, "cpu", seed=args.seed, checkpoint=args.checkpoint)
-        ix = LearnedIndexer(cfg, seed=args.seed)
+        ix = LearnedIndexer(cfg, seed=args.seed, dim=args.indexer_di)
+        if args.indexer_corpus:
+            from .sparse_index import corpus_run, load_spans
+            held = load_spans(args.indexer_corpus, "held", args.held_spans)
+            control = load_spans(args.indexer_control_corpus, "held", args.held_spans) if args.indexer_control_corpus else None
+            run = Run({"cmd": "train", **flags, "indexer_corpus": args.indexer_corpus, "k_pages": args.k_pages,
+                       "q_samples": args.q_samples, "q_min_pos": args.q_min_pos, "di": args.indexer_di, "seed": args.seed,
+                       "held_spans": args.held_spans, "control": args.indexer_control_corpus},
+                      root=args.runs or runs_dir())
+            out = corpus_run(model, ix, load_spans(args.indexer_corpus, "train"), held, args.k_pages, steps=flags["steps"],
+                             lr=flags.get("lr") or 3e-3, q_samples=args.q_samples, q_min_pos=args.q_min_pos, seed=args.seed,
+                             control=control, recall_threshold=args.recall_threshold)
+            for i, kl in enumerate(out["kl_curve"]):
+                run.log(step=i, kl=kl)
+            run.log(**{f"recall_after_{k}": v for k, v in out["recall_after"].items()},
+                    **{f"recall_before_{k}": v for k, v in out["recall_before"].items()})
+            run.gate("worst_recall_after", out["worst_recall_after"], args.recall_threshold)
+            print(json.dumps({k: v for k, v in out.items() if k != "kl_curve"} |
+                             {"kl_first": out["kl_curve"][0], "kl_last": out["kl_curve"][-1]}))
+            if args.save_model:
+                from safetensors.torch import save_file
+                os.makedirs(args.save_model, exist_ok=True)
+                save_file(ix.state_dict(), os.path.join(args.save_model, "indexer.safetensors"))
+                run.artifacts["indexer"] = args.save_model
+            run.finish()
+            return 0 if out["passed"] else 1
         g = torch.Generator().manual_seed(args.seed)
         seqs = [torch.randint(0, cfg.vocab, (flags.get("ctx") or 256,), generator=g) for _ in range(4)]
         run = Run({"cmd": "train", **flags}, root=args.runs or runs_dir())

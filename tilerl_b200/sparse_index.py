@@ -166,3 +166,82 @@ def topk_recall(model, ix: LearnedIndexer, ids: torch.Tensor, top_k: int, n_quer
                 idx = torch.topk(s, min(top_k, s.numel())).indices
                 kept.append(float(teacher[idx].sum()))
     return sum(kept) / len(kept)
+
+
+# ---- corpus run: recall before / after over prepared spans ---------------------------------------------------
+def load_spans(cdir: str, split: str, max_total: int = 0) -> Dict[str, List[torch.Tensor]]:
+    """Spans of a prepared corpus directory: files ``<split>_<label>.jsonl`` whose rows are
+    ``{"ctx": length, "ids": [...]}``, grouped by length label.  ``max_total`` > 0 keeps that many spans in
+    all, dealt round-robin over the sorted lengths (16 over three lengths -> 6 / 5 / 5), so that a cut run
+    is not weighted toward the cheap short spans.  Reference ``src/tilerl/train.py:1306-1331``."""
+    import glob
+    import itertools
+    import json
+    import os
+    groups: Dict[str, List[torch.Tensor]] = {}
+    for path in sorted(glob.glob(os.path.join(cdir, f"{split}_*.jsonl"))):
+        with open(path) as f:
+            rows = [json.loads(ln) for ln in f if ln.strip()]
+        if rows:
+            groups[str(rows[0].get("ctx", len(rows[0]["ids"])))] = [torch.tensor(r["ids"], dtype=torch.long) for r in rows]
+    if max_total:
+        labels = sorted(groups)
+        picked = {c: 0 for c in labels}
+        for c in itertools.islice(itertools.cycle(labels), max_total):
+            if picked[c] < len(groups[c]):
+                picked[c] += 1
+        groups = {c: groups[c][:picked[c]] for c in labels}
+    return groups
+
+
+def held_recall(model, ix: LearnedIndexer, held: Dict[str, List[torch.Tensor]], k_pages: int, *, q_samples: int = 16,
+                q_min_pos: int = 0, seed: int = 1) -> Dict[str, float]:
+    """Recall at ``k_pages`` per span length: the share of the dense attention mass that the indexer's top
+    pages keep, over ``q_samples`` seeded query positions at or after ``q_min_pos`` in every held span."""
+    out: Dict[str, float] = {}
+    for label, spans in sorted(held.items()):
+        vals = []
+        for j, ids in enumerate(spans):
+            qk = capture_qk(model, ids)
+            t = qk[0][0].shape[0]
+            lo = min(max(4 * KV_BLOCK, q_min_pos), t - 1)
+            g = torch.Generator().manual_seed(seed + 100003 * j)
+            kept = []
+            with torch.no_grad():
+                for layer, (q, k) in enumerate(qk):
+                    for qpos in torch.randint(lo, t, (max(1, q_samples),), generator=g).tolist():
+                        teacher = page_mass(q[qpos], k, qpos)
+                        s = _student(ix, layer, q[qpos], k, qpos)
+                        kept.append(float(teacher[torch.topk(s, min(k_pages, s.numel())).indices].sum()))
+            vals.append(sum(kept) / len(kept))
+        out[label] = sum(vals) / max(1, len(vals))
+    return out
+
+
+def corpus_run(model, ix: LearnedIndexer, train_groups: Dict[str, List[torch.Tensor]],
+               held: Dict[str, List[torch.Tensor]], k_pages: int, *, steps: int, lr: float = 3e-3, q_samples: int = 16,
+               q_min_pos: int = 0, seed: int = 0, control: Optional[Dict[str, List[torch.Tensor]]] = None,
+               recall_threshold: float = 0.0) -> Dict[str, object]:
+    """The indexer's science run: recall at ``k_pages`` per held span length before and after the warm-up,
+    the KL curve and the tokens seen; ``control`` (held spans of another corpus) is scored under the same
+    trained weights, to show that the recall is not an artefact of one corpus' tokenisation.  ``passed`` is
+    the worst after-recall against ``recall_threshold``.  Reference ``src/tilerl/train.py:1295-1360``
+    (``_train_indexer_recall``) and ``:622`` (``indexer_warmup_run``)."""
+    import itertools
+    batches = [b for row in itertools.zip_longest(*train_groups.values()) for b in row if b is not None]
+    if not batches:
+        raise ValueError("no training spans")
+    kw = dict(q_samples=q_samples, q_min_pos=q_min_pos, seed=seed + 1)
+    before = held_recall(model, ix, held, k_pages, **kw)
+    ctl_before = held_recall(model, ix, control, k_pages, **kw) if control else None
+    kl = warmup(model, ix, batches, steps=steps, lr=lr, queries_per_seq=max(1, q_samples // 2), seed=seed)
+    after = held_recall(model, ix, held, k_pages, **kw)
+    out: Dict[str, object] = {"recall_before": before, "recall_after": after, "kl_curve": kl, "k_pages": k_pages,
+                              "tokens_seen": sum(int(batches[s % len(batches)].numel()) for s in range(steps)),
+                              "q_samples": q_samples, "q_min_pos": q_min_pos, "di": ix.dim, "heads": ix.heads}
+    if control:
+        out["control"] = {"recall_before": ctl_before, "recall_after": held_recall(model, ix, control, k_pages, **kw)}
+    worst = min(after.values()) if after else 0.0
+    out["passed"] = bool(worst >= recall_threshold)
+    out["worst_recall_after"] = worst
+    return out
