@@ -368,3 +368,32 @@ def test_train_indexer_corpus_run_reports_recall_per_length_and_a_control(tmp_pa
                      "--k-pages", "1", "--q-samples", "2", "--held-spans", "3", "--recall-threshold", "1.01"]) == 1
     man = [json.load(open(tmp_path / "runs" / d / "manifest.json")) for d in os.listdir(tmp_path / "runs")]
     assert sorted(m["status"] for m in man) == ["done", "gate_failed"]
+
+
+def test_merge_is_a_run_whose_parents_are_the_runs_that_wrote_its_inputs(tmp_path, capsys, monkeypatch):
+    runs = str(tmp_path / "runs")
+    monkeypatch.setenv("TRL_RUNS", runs)
+    outs = []
+    for seed in ("1", "2", "3"):             # a base and two "specialists": full-parameter runs that save a checkpoint
+        out = str(tmp_path / f"ckpt{seed}")
+        assert cli.main(["train", "--model", "tiny", "--device", "cpu", "--steps", "1", "--seed", seed, "--prompt-len", "8",
+                         "--save-model", out]) == 0
+        outs.append(out)
+    capsys.readouterr()
+    merged = str(tmp_path / "merged")
+    cmd = ["merge", "--base", outs[0], "--specialists", f"{outs[1]},{outs[2]}", "--out", merged, "--method", "ties"]
+    assert cli.main(cmd) == 0
+    rec = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rec["tensors"] > 0 and len(rec["parents"]) == 3 and os.path.isdir(merged)
+    from tilerl_b200 import ledger
+    man = ledger.load_run(rec["run"], runs)
+    assert man["status"] == "done" and man["parents"] == rec["parents"] and man["artifacts"]["model"] == merged
+    assert all(ledger.load_run(p, runs)["inputs"]["cmd"] == "train" for p in man["parents"])
+    assert ledger.find_run_for_artifact(str(tmp_path / "nowhere"), runs) is None
+    assert ledger.find_run_for_artifact(merged, runs) == rec["run"]
+    assert cli.main(cmd) == 0                                   # the same merge asked again: the finished run
+    assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["reused"] is True
+    assert cli.main(cmd + ["--force", "--json"]) == 0
+    assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["id"] == rec["run"]
+    with pytest.raises(SystemExit):
+        cli.main(["merge", "--base", outs[0], "--out", merged])

@@ -177,9 +177,14 @@ def build_parser() -> argparse.ArgumentParser:
 
     m = sub.add_parser("merge", help="merge fine-tuned checkpoints")
     m.add_argument("--base", required=True)
-    m.add_argument("--tuned", nargs="+", required=True)
+    m.add_argument("--tuned", nargs="+", default=None, help="fine-tuned checkpoint directories")
+    m.add_argument("--specialists", type=lambda v: [x for x in v.split(",") if x], default=None,
+                   help="the same as --tuned, comma-separated")
     m.add_argument("--out", required=True)
     m.add_argument("--method", default="average", choices=["average", "ties", "dare", "iso"])
+    m.add_argument("--runs", default=None, help="run manifest directory (default: $TRL_RUNS or ./runs)")
+    m.add_argument("--force", action="store_true", help="merge again even if a finished run with these inputs exists")
+    m.add_argument("--json", action="store_true", help="print the run manifest as JSON")
 
     lg = sub.add_parser("ledger", help="list runs, show lineage, list devices")
     lg.add_argument("--runs", default=None, help="run manifest directory (default: $TRL_RUNS or ./runs)")
@@ -625,9 +630,27 @@ def cmd_generate(args) -> int:
 
 
 def cmd_merge(args) -> int:
+    from .ledger import Run, find_run_for_artifact, finished_run, load_run, runs_dir
     from .merge import merge_checkpoints
-    n = merge_checkpoints(args.base, args.tuned, args.out, args.method)
-    print(json.dumps({"tensors": n, "out": args.out}))
+    tuned = list(args.tuned or []) + list(args.specialists or [])
+    if not tuned:
+        raise SystemExit("merge needs --tuned DIR [DIR ...] or --specialists DIR,DIR")
+    root = args.runs or runs_dir()
+    inputs = {"cmd": "merge", "base": args.base, "specialists": tuned, "method": args.method, "out": args.out}
+    prev = None if args.force else finished_run(inputs, None, root)
+    if prev is not None and os.path.isdir(args.out):
+        print(json.dumps(prev, default=str) if args.json else
+              json.dumps({"run": prev["id"], "status": "done", "reused": True, "hint": "--force merges again"}))
+        return 0
+    # lineage goes through the runs that wrote the inputs; a directory no run lists contributes no parent
+    parents = [pid for pid in (find_run_for_artifact(p, root) for p in [args.base] + tuned) if pid is not None]
+    run = Run(inputs, root=root, parents=parents)
+    n = merge_checkpoints(args.base, tuned, args.out, args.method)
+    run.log(tensors=n)
+    run.artifacts["model"] = args.out
+    run.finish()
+    print(json.dumps(load_run(run.id, root), default=str) if args.json else
+          json.dumps({"tensors": n, "out": args.out, "run": run.id, "parents": parents}))
     return 0
 
 

@@ -48,6 +48,7 @@ class Run:
     artifacts: Dict[str, str] = field(default_factory=dict)
     started: float = field(default_factory=time.time)
     status: str = "running"
+    parents: List[str] = field(default_factory=list)     # a merge descends from the runs that wrote its inputs
 
     def __post_init__(self):
         self.id = self.id or run_id({**self.inputs, "parent": self.parent})
@@ -72,7 +73,7 @@ class Run:
 
     def write(self) -> None:
         man = {"id": self.id, "parent": self.parent, "inputs": self.inputs, "status": self.status,
-               "started": self.started, "seconds": round(time.time() - self.started, 3), "metrics": self.metrics,
+               "parents": list(self.parents), "started": self.started, "seconds": round(time.time() - self.started, 3), "metrics": self.metrics,
                "gates": [{"name": g.name, "value": g.value, "threshold": g.threshold, "passed": g.passed}
                          for g in self.gates], "artifacts": self.artifacts}
         tmp = os.path.join(self.dir, "manifest.json.tmp")
@@ -92,6 +93,21 @@ def finished_run(inputs: Dict[str, Any], parent: Optional[str] = None, root: Opt
     except (OSError, json.JSONDecodeError):
         return None
     return man if man.get("status") == "done" else None
+
+
+def find_run_for_artifact(path: str, root: Optional[str] = None) -> Optional[str]:
+    """Id of the newest finished run whose manifest lists ``path`` among its artifacts, else None.  A
+    checkpoint directory carries no run id of its own; lineage goes through the manifest that wrote it, and
+    an id is never guessed from a path component.  Reference ``src/tilerl/cli.py:386-392``."""
+    want = os.path.realpath(path)
+    best = None
+    for man in list_runs(root):
+        if man.get("status") != "done":
+            continue
+        if any(os.path.realpath(str(v)) == want for v in (man.get("artifacts") or {}).values()):
+            if best is None or man.get("started", 0) >= best.get("started", 0):
+                best = man
+    return best["id"] if best else None
 
 
 def load_run(rid: str, root: Optional[str] = None) -> Dict[str, Any]:
