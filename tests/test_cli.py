@@ -397,3 +397,24 @@ def test_merge_is_a_run_whose_parents_are_the_runs_that_wrote_its_inputs(tmp_pat
     assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["id"] == rec["run"]
     with pytest.raises(SystemExit):
         cli.main(["merge", "--base", outs[0], "--out", merged])
+
+
+def test_serve_records_residency_and_the_devices_ledger_reads_it(tmp_path, capsys, monkeypatch):
+    store = tmp_path / "bench.jsonl"
+    monkeypatch.setenv("TRL_BENCH_STORE", str(store))
+    assert cli.main(["serve", "--model", "tiny", "--device", "cpu", "--slots", "4", "--blocks", "64", "--no-warmup",
+                     "--record-residency", "--port", "0"]) == 0
+    res = json.loads(capsys.readouterr().out.strip().splitlines()[-1])["residency"]
+    assert res["static"] > 0 and res["peak"] >= res["static"] and res["transient"] == res["peak"] - res["static"]
+    from tilerl_b200 import benchrec, ledger
+    recs = benchrec.load(str(store))
+    assert {r["metric"] for r in recs} >= {"resident_peak_bytes", "resident_static_bytes"}
+    assert all(r["shape"] == {"model": "tiny", "slots": 4, "tp": 1} and r["unit"] == "B" for r in recs)
+    benchrec.append(benchrec.make_record("hbm_copy_gbs", 6850.0, {}, target="b200"), str(store))
+    benchrec.append(benchrec.make_record("bf16_gemm_tflops", 1590.0, {}, target="b200"), str(store))
+    secs = {s["device"]: s for s in ledger.device_sections(benchrec.load(str(store)))}
+    assert secs["cpu"]["residency"]["peak"] == res["peak"] and secs["cpu"]["hbm_copy_gbs"] is None
+    assert secs["b200"]["hbm_copy_gbs"]["value"] == 6850.0 and secs["b200"]["residency"] is None
+    assert cli.main(["ledger", "--devices"]) == 0
+    out = capsys.readouterr().out
+    assert "hbm_copy_gbs 6850.0" in out and "resident" in out and "none recorded (run serve --record-residency)" in out

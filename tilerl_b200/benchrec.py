@@ -45,6 +45,10 @@ METRICS: Dict[str, tuple] = {
     "gsm8k_acc": ("frac", True, ("model", "n")),
     "kv_boot_s": ("s", False, ("model", "entries")),
     "resync_ms": ("ms", False, ("model", "tp")),
+    # what a serving engine holds after its warm-up: the sum of its static pools and the allocator's peak above it
+    "resident_peak_bytes": ("B", False, ("model", "slots", "tp")),
+    "resident_static_bytes": ("B", False, ("model", "slots", "tp")),
+    "resident_transient_bytes": ("B", False, ("model", "slots", "tp")),
 }
 
 

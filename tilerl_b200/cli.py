@@ -51,6 +51,9 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--device-free", type=int, default=None, metavar="BYTES",
                    help="with --dry-run: plan against this many free device bytes instead of a whole B200")
     s.add_argument("--json", action="store_true", help="with --dry-run: print the memory rows as JSON")
+    s.add_argument("--record-residency", action="store_true",
+                   help="after building and warming the engine, append its resident peak and the static / transient split "
+                        "to the bench store (with --port 0: record and exit)")
     s.add_argument("--sparse-prefill-tokens", type=int, default=0,
                    help="prefill tokens per tick of a fill of --sparse-min-tokens or more while other requests share "
                         "the engine (0: the whole --max-batched-tokens budget)")
@@ -284,6 +287,16 @@ def cmd_serve(args) -> int:
         print(json.dumps({"kv_boot": KvBootStore(args.kv_store).boot(eng)}))
     if not args.no_warmup:
         eng.precapture((1,))
+    if args.record_residency:
+        from . import benchrec, memory
+        res = memory.residency(eng)
+        shape = {"model": cfg.name, "slots": args.slots, "tp": 1}
+        for k, v in res.items():
+            if v > 0:
+                benchrec.append(benchrec.make_record(f"resident_{k}_bytes", v, shape, target="cpu" if dev == "cpu" else "b200"))
+        print(json.dumps({"residency": res}), flush=True)
+        if args.port == 0:            # record and leave: nothing is served
+            return 0
     eng.run()
     app = create_app(eng, tok, cfg.name, pace=args.stream_pace, pace_depth=args.stream_pace_depth,
                      completion_timeout_s=args.completion_timeout_s)
@@ -566,7 +579,12 @@ def cmd_bench(args) -> int:
     cfg = get_config(args.model)
     if args.calibrate:
         import dataclasses
-        print(json.dumps(dataclasses.asdict(calibrate(_device(args)))))
+        pk = calibrate(_device(args))
+        print(json.dumps(dataclasses.asdict(pk)))
+        if args.record:             # the floors join the bench store, where `ledger --devices` reads them
+            from . import benchrec
+            benchrec.append(benchrec.make_record("hbm_copy_gbs", pk.hbm_gbs, {}))
+            benchrec.append(benchrec.make_record("bf16_gemm_tflops", pk.bf16_tflops, {}))
         return 0
     if args.registry:
         from .ops import registry as R
@@ -657,7 +675,9 @@ def cmd_merge(args) -> int:
 def cmd_ledger(args) -> int:
     from . import ledger
     if args.devices:
+        from . import benchrec
         print(json.dumps(ledger.devices(), indent=1))
+        print(ledger.format_device_sections(ledger.device_sections(benchrec.load(benchrec.store_path()))))
         return 0
     if args.show:
         print(json.dumps({"run": ledger.load_run(args.show, args.runs), "lineage": ledger.lineage(args.show, args.runs)},

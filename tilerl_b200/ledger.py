@@ -205,3 +205,42 @@ def devices() -> List[Dict[str, Any]]:
                 for i in range(torch.cuda.device_count())]
     except Exception:  # noqa: BLE001
         return []
+
+
+def device_sections(records: List[Dict[str, Any]]) -> List[Dict[str, Any]]:
+    """One section per target in the bench store: its newest measured floors (copy bandwidth, bf16 GEMM
+    rate) and its newest residency triple.  Reference ``src/tilerl/cli.py`` (``_device_ledger_rows``)."""
+    out: Dict[str, Dict[str, Any]] = {}
+    for r in sorted(records, key=lambda r: r.get("ts", 0)):
+        sec = out.setdefault(r.get("target", "?"), {"device": r.get("target", "?"), "hbm_copy_gbs": None,
+                                                    "bf16_gemm_tflops": None, "residency": None})
+        m = r.get("metric")
+        if m in ("hbm_copy_gbs", "bf16_gemm_tflops"):
+            sec[m] = {"value": r["value"], "commit": r.get("commit"), "ts": r.get("ts")}
+        elif m in ("resident_peak_bytes", "resident_static_bytes", "resident_transient_bytes"):
+            res = sec["residency"] if sec["residency"] and sec["residency"].get("shape") == r.get("shape") else \
+                {"shape": r.get("shape"), "commit": r.get("commit"), "ts": r.get("ts")}
+            res[m.split("_")[1]] = r["value"]
+            sec["residency"] = res
+    return list(out.values())
+
+
+def format_device_sections(sections: List[Dict[str, Any]]) -> str:
+    lines = ["devices (newest measured floor + residency per target):"]
+    for s in sections:
+        lines.append(f"  {s['device']}")
+        bw, pk, res = s["hbm_copy_gbs"], s["bf16_gemm_tflops"], s["residency"]
+        if bw is None or pk is None:
+            lines.append("    copy bandwidth / bf16 peak: none recorded (run bench --calibrate --record)")
+        else:
+            lines.append(f"    hbm_copy_gbs {bw['value']:.1f} (commit {bw['commit']})  bf16_gemm_tflops {pk['value']:.1f} "
+                         f"(commit {pk['commit']})")
+        if res is None or "peak" not in res:
+            lines.append("    residency: none recorded (run serve --record-residency)")
+        else:
+            mib = 2 ** 20
+            lines.append(f"    resident {res['peak'] / mib:10.2f} MiB = static {res.get('static', 0) / mib:.2f} + transient "
+                         f"{res.get('transient', 0) / mib:.2f}  {res['shape']} (commit {res['commit']})")
+    if len(lines) == 1:
+        lines.append("  (no calibration or residency rows in the bench store)")
+    return "\n".join(lines)

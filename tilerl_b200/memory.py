@@ -247,3 +247,16 @@ def measure(engine) -> Dict[str, int]:
     if ix is not None:
         out["page indexer"] = sum(size(t) for t in ix.parameters())
     return out
+
+
+def residency(engine) -> Dict[str, int]:
+    """Resident bytes of a live engine: ``static`` = the sum of :func:`measure`'s rows, ``peak`` = the
+    allocator's high-water mark on the engine's device (on the CPU backend, where nothing keeps one, the
+    static sum), ``transient`` = peak - static.  ``serve --record-residency`` appends the three to the bench
+    store (reference ``tilerl serve --dry-run --record-residency``, ``src/tilerl/memory.py:542``)."""
+    import torch
+    static = sum(measure(engine).values())
+    dev = torch.device(engine.device)
+    peak = int(torch.cuda.max_memory_allocated(dev)) if dev.type == "cuda" else static
+    peak = max(peak, static)
+    return {"static": int(static), "peak": int(peak), "transient": int(peak - static)}
