@@ -418,3 +418,14 @@ def test_serve_records_residency_and_the_devices_ledger_reads_it(tmp_path, capsy
     assert cli.main(["ledger", "--devices"]) == 0
     out = capsys.readouterr().out
     assert "hbm_copy_gbs 6850.0" in out and "resident" in out and "none recorded (run serve --record-residency)" in out
+
+
+def test_serve_draft_window_flag_reaches_the_plan(capsys, monkeypatch):
+    def ctx_gib(extra):
+        assert cli.main(["serve", "--model", "qwen38-27b", "--dry-run", "--slots", "16", "--draft", "block", "--json"] + extra) == 0
+        rows = json.loads(capsys.readouterr().out)["rows"]
+        return next(v for k, v in rows.items() if "drafter context" in k)
+    base = ctx_gib([])
+    assert ctx_gib(["--draft-attn-window-tokens", "128"]) == 2 * base          # default window 64
+    monkeypatch.setenv("TRL_DRAFT_ATTN_WINDOW_TOKENS", "32")
+    assert ctx_gib([]) * 2 == base and ctx_gib(["--draft-attn-window-tokens", "64"]) == base      # the flag wins

@@ -40,6 +40,9 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--draft", default=None, choices=[None, "block", "chain"])
     s.add_argument("--draft-checkpoint", default=None, help="directory written by spec.save_drafter (kind is read from it)")
     s.add_argument("--spec-width", type=int, default=8)
+    s.add_argument("--draft-attn-window-tokens", type=int, default=None,
+                   help="trailing context rows the block drafter reads (omitted: $TRL_DRAFT_ATTN_WINDOW_TOKENS, else the "
+                        "drafter's own setting)")
     s.add_argument("--sparse-k", type=int, default=0)
     s.add_argument("--scorer", default="quest", choices=["quest", "learned"],
                    help="sparse page scores: Quest min/max bounds, or the learned indexer")
@@ -215,6 +218,15 @@ def ssd_slots(path: str, capacity_bytes: int, slot_bytes: int) -> int:
     return int(max(1, min(1 << 24, capacity_bytes // max(1, slot_bytes))))
 
 
+def _draft_window(args) -> int:
+    w = args.draft_attn_window_tokens
+    if w is None:
+        w = int(os.environ.get("TRL_DRAFT_ATTN_WINDOW_TOKENS", "0") or 0)
+    if w < 0:
+        raise SystemExit("--draft-attn-window-tokens must not be negative")
+    return int(w)
+
+
 def cmd_serve(args) -> int:
     from . import memory
     from .config import get_config
@@ -224,7 +236,8 @@ def cmd_serve(args) -> int:
         host_pages = args.kv_cold_bytes // memory.kv_block_bytes(cfg, 1, fp8) if args.kv_cold_bytes else 0
         p = memory.plan(cfg, slots=args.slots, blocks=args.blocks, max_batched_tokens=args.max_batched_tokens,
                         planes=args.spec_width if (args.draft or args.draft_checkpoint) else 1, kv_fp8=fp8,
-                        drafter={"width": args.spec_width} if args.draft == "block" else None,
+                        drafter=({"width": args.spec_width, **({"window": _draft_window(args)} if _draft_window(args) else {})}
+                                 if args.draft == "block" else None),
                         indexer={} if (args.sparse_k and args.scorer == "learned") else None, host_pages=host_pages,
                         state_bytes=args.state_bytes, **({"device_bytes": args.device_free} if args.device_free else {}))
         print(json.dumps(memory.plan_json(p, args.device_free or memory.B200_BYTES)) if args.json else memory.memory_table(p))
@@ -249,6 +262,8 @@ def cmd_serve(args) -> int:
     elif args.draft:
         from .spec import BlockDrafter, ChainDrafter
         drafter = BlockDrafter(model) if args.draft == "block" else ChainDrafter(model)
+    if drafter is not None and _draft_window(args) and hasattr(getattr(drafter, "cfg", None), "window"):
+        drafter.cfg.window = _draft_window(args)     # a read window: rows kept and attended per request
     sparse = None
     if args.sparse_k:
         from .sparse import SparseConfig, SparseKV
