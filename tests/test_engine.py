@@ -231,3 +231,17 @@ def test_long_fill_cap_bounds_the_prefill_chunk_only_while_the_engine_is_shared(
     while eng._reqs[a].state != "done":
         eng.step()
     assert eng.take(a).tokens == ref_long and eng.take(b).tokens == ref_short
+
+
+def test_stats_report_tick_kinds_memory_rows_and_prefix_traffic():
+    cfg = tiny_hybrid()
+    eng = make_engine(cfg)
+    eng.prefix = PrefixStore(eng.kv)
+    p = rand_prompts(cfg, 1, 40, seed=2)[0]
+    eng.generate([p], SamplingParams(max_tokens=4))
+    s = eng.stats()
+    assert s["dense_ticks"] == s["ticks"] > 0 and s["sparse_ticks"] == 0 and s["verify_ticks"] == 0
+    assert s["memory"]["kv pool"] > 0 and s["memory"]["weights"] > 0 and s["memory"]["gdn state slots"] > 0
+    assert s["prefix_state_bytes"] > 0 and s["spec_acceptance"] is None and s["prefix_promotions"] == 0
+    import json
+    json.dumps(s)                      # the health route serialises it

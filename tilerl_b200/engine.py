@@ -181,12 +181,13 @@ class Engine:
         self.counters = dict(ticks=0, prefill_ticks=0, decode_ticks=0, mixed_ticks=0,
                              graph_ticks=0, tokens_generated=0, prompt_tokens=0,
                              spec_drafted=0, spec_accepted=0, spec_device_accepts=0, cancelled=0, failed=0,
-                             finished=0, preempted=0)
+                             finished=0, preempted=0, sparse_ticks=0, dense_ticks=0, verify_ticks=0)
         self.timing = os.environ.get("TRL_STEP_TIMING") == "1"
         # TRL_NVTX=1: every tick and its sampling phase become NVTX ranges, so a profiler can be
         # limited to them (ncu --nvtx --nvtx-include "tick/", nsys --capture-range=nvtx)
         self.nvtx = os.environ.get("TRL_NVTX") == "1" and torch.device(self.device).type == "cuda"
         self.last_tick_ms: Dict[str, float] = {}
+        self._memory_rows: Optional[Dict[str, int]] = None
         self.io_h2d = 0   # bytes copied host->device for tick inputs (eager ticks)
         self.io_d2h = 0   # bytes read back (sampled tokens / logits rows)
 
@@ -285,7 +286,10 @@ class Engine:
                 self.io_d2h + (g.d2h_bytes if g is not None else 0))
 
     def stats(self) -> Dict[str, object]:
-        return dict(
+        """Lock-free snapshot for ``/health``: queue depths, pool use, prefix and tier traffic, tick counts by
+        kind, speculative acceptance, and the bytes the engine's static pools hold (reference
+        ``src/tilerl/engine.py:1711``)."""
+        out = dict(
             waiting=len(self._waiting), running=len(self._running),
             blocks_used=self.kv.used_blocks, blocks_free=self.kv.free_blocks,
             slots_free=self.states.free_slots,
@@ -293,6 +297,22 @@ class Engine:
             prefix_misses=self.prefix.misses, prefix_evictions=self.prefix.evictions,
             **self.counters,
         )
+        for k in ("promotions", "demotions", "state_bytes"):
+            v = getattr(self.prefix, k, None)
+            if v is not None:
+                out[f"prefix_{k}"] = int(v)
+        drafted = self.counters["spec_drafted"]
+        out["spec_acceptance"] = round(self.counters["spec_accepted"] / drafted, 4) if drafted else None
+        if self.sparse is not None and isinstance(getattr(self.sparse, "stats", None), dict):
+            out["sparse"] = dict(self.sparse.stats)
+        if self._memory_rows is None:          # the static pools do not move after construction: measured once
+            try:
+                from .memory import measure
+                self._memory_rows = {k: int(v) for k, v in measure(self).items() if k != "prefix state store"}
+            except Exception:  # noqa: BLE001 - a stats call must not fail a health probe
+                self._memory_rows = {}
+        out["memory"] = dict(self._memory_rows)
+        return out
 
     # ---- daemon loop ----------------------------------------------------------------------
     def run(self, batching_window_s: float = 0.010) -> None:
@@ -497,6 +517,7 @@ class Engine:
         amax = None
         vout = None
         dev_accept = None       # per sequence: drafts accepted, counted (and the state plane selected) on the device
+        sparse_tick = False     # True when this tick's attention reads selected pages
         if logits is None and self.vgraph is not None and decode_only and verify and self.sparse is None:
             greedy = all(self._is_plain_greedy(r) for r, _, _ in plan)
             vout = self.vgraph.run(seqs, need_logits=not greedy)
@@ -515,6 +536,7 @@ class Engine:
             self.io_h2d += batch.h2d_bytes
             if self.sparse is not None:
                 batch.sparse = self.sparse.for_batch(batch, [r.rid for r, _, _ in plan])
+                sparse_tick = batch.sparse is not None
             aux = tuple(self.drafter.aux_layers) if self.drafter is not None else ()
             res = self.model.forward(batch, self.ops, self.kv, self.states,
                                      last_only=not verify, aux_layers=aux)
@@ -531,6 +553,9 @@ class Engine:
         kinds = {r.state for r, _, _ in plan}
         key = "mixed_ticks" if len(kinds) > 1 else ("decode_ticks" if DECODE in kinds else "prefill_ticks")
         self.counters[key] += 1
+        self.counters["sparse_ticks" if sparse_tick else "dense_ticks"] += 1
+        if verify:
+            self.counters["verify_ticks"] += 1
         tok_off = 0
         for i, (r, toks, start) in enumerate(plan):
             n = len(toks)
