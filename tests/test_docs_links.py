@@ -2,7 +2,7 @@
 
 Every back-quoted token of a Markdown file that starts with one of the repository's own top-level
 folders must name a file or folder that is there; a ``path::name`` token must also find ``name`` in
-that file.  Checked: every file under ``profiles/`` and every Markdown file of the repository root that
+that file.  Checked: every file under ``profiles/``, ``docs/`` and ``web/`` and every Markdown file of the repository root that
 carries the marker comment ``<!-- docs-links: checked -->`` (notes written by other parties quote
 paths of other snapshots and carry no marker).  Paths of other projects (they start with other
 folders) are not checked.  Parity: the reference's docs-link gate (tests/test_docs_links.py).
@@ -41,7 +41,8 @@ def _exists(tok: str) -> bool:
 def test_paths_quoted_in_the_markdown_files_exist():
     files = [p for p in glob.glob(os.path.join(ROOT, "*.md")) if MARKER in open(p, errors="ignore").read(2000)]
     assert len(files) >= 3, "the repository's own documents carry the marker"
-    files += glob.glob(os.path.join(ROOT, "profiles", "*.md"))
+    files += glob.glob(os.path.join(ROOT, "profiles", "*.md")) + glob.glob(os.path.join(ROOT, "docs", "*.md")) + \
+        glob.glob(os.path.join(ROOT, "web", "*.md"))
     missing = []
     for f in files:
         for tok in _tokens(open(f, errors="ignore").read()):
