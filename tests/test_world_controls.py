@@ -37,6 +37,20 @@ def _cp_mutated(rank, world, mutation):
     elif mutation == "local-positions":   # causal mask and RoPE from rank-local positions
         CP.positions_for = lambda seq_len, cp: torch.arange(seq_len // cp.world)
         gate_cp.__dict__["_patched_positions"] = True
+    elif mutation == "kv-not-gathered":   # no exchange: every slot of the gathered K / V holds this rank's own rows
+        gather0 = CP.gather_kv
+
+        def own_only(k, v, pos, cp):
+            _, _, pa = gather0(k, v, pos, cp)
+            return torch.cat([k] * cp.world, 1), torch.cat([v] * cp.world, 1), pa
+        CP.gather_kv = own_only
+    elif mutation == "kv-positions-local":  # the gathered keys all carry this rank's positions: the causal mask is wrong
+        gather = CP.gather_kv
+
+        def gather_kv(k, v, pos, cp):
+            ka, va, _ = gather(k, v, pos, cp)
+            return ka, va, pos.repeat(cp.world)
+        CP.gather_kv = gather_kv
     return gate_cp._cp_rank(rank, world, True)
 
 
@@ -67,6 +81,16 @@ def test_cp_control_all_gather_backward_keeps_local_slice():
 
 def test_cp_control_rank_local_positions():
     logits, _ = _cp_metrics("local-positions")
+    assert logits > 1e-3
+
+
+def test_cp_control_keys_of_other_ranks_never_gathered():
+    logits, _ = _cp_metrics("kv-not-gathered")
+    assert logits > 1e-3
+
+
+def test_cp_control_gathered_keys_carry_local_positions():
+    logits, _ = _cp_metrics("kv-positions-local")
     assert logits > 1e-3
 
 
@@ -112,6 +136,15 @@ def _tp_train_mutated(rank, world, mutation):
     elif mutation == "no-fork":
         # the identity-forward / all-reduce-backward at the entry of a column-parallel block is dropped
         T.tp_fork = lambda tape, x: x
+    elif mutation == "ce-local-max":
+        # the vocabulary-sharded cross entropy skips the max over ranks: every rank exponentiates against
+        # its own maximum and the summed denominators do not belong together
+        import torch.distributed as dist
+        real = dist.all_reduce
+
+        def all_reduce(t, op=dist.ReduceOp.SUM, group=None, **kw):
+            return None if op == dist.ReduceOp.MAX else real(t, op=op, group=group, **kw)
+        dist.all_reduce = all_reduce
     return gate_tp._train_rank(rank, world, 1e9, False)
 
 
@@ -134,6 +167,11 @@ def test_tp_train_control_head_norm_gradients_not_summed():
 
 def test_tp_train_control_without_fork():
     worst, worst_rep = _tp_train_worst("no-fork")
+    assert worst > 1e-2 or worst_rep > 1e-4
+
+
+def test_tp_train_control_sharded_cross_entropy_with_rank_local_max():
+    worst, worst_rep = _tp_train_worst("ce-local-max")
     assert worst > 1e-2 or worst_rep > 1e-4
 
 
@@ -188,6 +226,14 @@ def _zero3_mutated(rank, world, mutation):
         def all_gather(self, shard, full, stream=None):
             full.view(self.world, -1).copy_(shard.to(full.dtype).view(1, -1).expand(self.world, -1))
         Z.TorchComm.all_gather = all_gather
+    elif mutation == "rotated-gather":
+        # the all-gather delivers every shard one slot too far: the full parameter is a rotation of itself
+        def all_gather(self, shard, full, stream=None):
+            import torch.distributed as dist
+            parts = [torch.empty_like(shard) for _ in range(self.world)]
+            dist.all_gather(parts, shard.contiguous(), group=self.group)
+            full.view(self.world, -1).copy_(torch.stack(parts[1:] + parts[:1]).to(full.dtype))
+        Z.TorchComm.all_gather = all_gather
     return gate_z._zero3_rank(rank, world, False, 2, None)
 
 
@@ -198,6 +244,11 @@ def test_zero3_control_reduce_scatter_returns_the_neighbours_slice():
 
 def test_zero3_control_all_gather_without_communication():
     got = run_world(2, _zero3_mutated, "stale-gather")
+    assert gate_z._update_error(got[0][0], gate_z._single_step(2)) > 0.05
+
+
+def test_zero3_control_all_gather_rotates_the_shards():
+    got = run_world(2, _zero3_mutated, "rotated-gather")
     assert gate_z._update_error(got[0][0], gate_z._single_step(2)) > 0.05
 
 
@@ -217,15 +268,18 @@ def test_dp_control_without_gradient_all_reduce():
 CONTROLS = {
     "test_world_cp.py": ["test_cp_negative_control_without_halo", "test_cp_control_gdn_states_not_composed_across_ranks",
                          "test_cp_control_fold_without_decay", "test_cp_control_all_gather_backward_keeps_local_slice",
-                         "test_cp_control_rank_local_positions"],
+                         "test_cp_control_rank_local_positions", "test_cp_control_keys_of_other_ranks_never_gathered",
+                         "test_cp_control_gathered_keys_carry_local_positions"],
     "test_world_tp.py": ["test_tp_serving_negative_control_no_collective", "test_tp_train_step_negative_control_local_norm",
                          "test_tp_control_every_rank_loads_rank0_shard", "test_tp_control_vocabulary_shards_not_gathered",
-                         "test_tp_train_control_head_norm_gradients_not_summed", "test_tp_train_control_without_fork"],
+                         "test_tp_train_control_head_norm_gradients_not_summed", "test_tp_train_control_without_fork",
+                         "test_tp_train_control_sharded_cross_entropy_with_rank_local_max"],
     "test_world_mesh.py": ["test_mesh_negative_control_without_dp_mean", "test_mesh_control_tp_collectives_over_the_whole_world",
                            "test_mesh_control_replicas_read_the_same_half_batch"],
     "test_world_zero3.py": ["test_zero3_negative_control_no_reduction",
                             "test_zero3_control_reduce_scatter_returns_the_neighbours_slice",
-                            "test_zero3_control_all_gather_without_communication", "test_dp_control_without_gradient_all_reduce"],
+                            "test_zero3_control_all_gather_without_communication", "test_dp_control_without_gradient_all_reduce",
+                            "test_zero3_control_all_gather_rotates_the_shards"],
 }
 
 
@@ -237,4 +291,4 @@ def test_every_world_gate_has_a_control_and_every_listed_control_exists():
     for names in CONTROLS.values():
         for n in names:
             assert f"def {n}(" in source, n
-    assert sum(len(v) for v in CONTROLS.values()) >= 18
+    assert sum(len(v) for v in CONTROLS.values()) >= 22
