@@ -192,6 +192,10 @@ def _mesh_mutated(rank, world, mutation):
             cfg, ids = gate_mesh._setup_orig()
             return cfg, torch.cat([ids[:2], ids[:2]])
         gate_mesh._setup = setup
+    elif mutation == "transposed-coords":
+        # a rank reads its (dp, tp) coordinates with the axes swapped while the groups follow the real
+        # formula: two members of one TP group hold the same shard
+        Mesh.coords = lambda self, r: (r % self.dp, r // self.dp, 0)
     return gate_mesh._mesh_rank(rank, world, False)
 
 
@@ -204,6 +208,12 @@ def test_mesh_control_tp_collectives_over_the_whole_world():
 def test_mesh_control_replicas_read_the_same_half_batch():
     cfg, _ = gate_mesh._setup()
     got = run_world(4, _mesh_mutated, "same-batch")
+    assert gate_mesh._check(got, gate_mesh._single(), cfg) > 1e-2
+
+
+def test_mesh_control_rank_coordinates_transposed():
+    cfg, _ = gate_mesh._setup()
+    got = run_world(4, _mesh_mutated, "transposed-coords")
     assert gate_mesh._check(got, gate_mesh._single(), cfg) > 1e-2
 
 
@@ -275,7 +285,8 @@ CONTROLS = {
                          "test_tp_train_control_head_norm_gradients_not_summed", "test_tp_train_control_without_fork",
                          "test_tp_train_control_sharded_cross_entropy_with_rank_local_max"],
     "test_world_mesh.py": ["test_mesh_negative_control_without_dp_mean", "test_mesh_control_tp_collectives_over_the_whole_world",
-                           "test_mesh_control_replicas_read_the_same_half_batch"],
+                           "test_mesh_control_replicas_read_the_same_half_batch",
+                           "test_mesh_control_rank_coordinates_transposed"],
     "test_world_zero3.py": ["test_zero3_negative_control_no_reduction",
                             "test_zero3_control_reduce_scatter_returns_the_neighbours_slice",
                             "test_zero3_control_all_gather_without_communication", "test_dp_control_without_gradient_all_reduce",
@@ -291,4 +302,4 @@ def test_every_world_gate_has_a_control_and_every_listed_control_exists():
     for names in CONTROLS.values():
         for n in names:
             assert f"def {n}(" in source, n
-    assert sum(len(v) for v in CONTROLS.values()) >= 22
+    assert sum(len(v) for v in CONTROLS.values()) >= 23
