@@ -429,3 +429,19 @@ def test_serve_draft_window_flag_reaches_the_plan(capsys, monkeypatch):
     assert ctx_gib(["--draft-attn-window-tokens", "128"]) == 2 * base          # default window 64
     monkeypatch.setenv("TRL_DRAFT_ATTN_WINDOW_TOKENS", "32")
     assert ctx_gib([]) * 2 == base and ctx_gib(["--draft-attn-window-tokens", "64"]) == base      # the flag wins
+
+
+def test_a_run_that_loads_an_adapter_descends_from_the_run_that_wrote_it(tmp_path, capsys, monkeypatch):
+    runs = str(tmp_path / "runs")
+    monkeypatch.setenv("TRL_RUNS", runs)
+    out = str(tmp_path / "adapter")
+    base = ["train", "--model", "tiny", "--device", "cpu", "--steps", "1", "--lora-rank", "2", "--prompt-len", "8"]
+    assert cli.main(base + ["--save-model", out]) == 0
+    from tilerl_b200 import ledger
+    first = ledger.list_runs(runs)
+    assert len(first) == 1 and first[0]["artifacts"]["model"] == out
+    assert cli.main(base + ["--load-adapter", out, "--seed", "3"]) == 0
+    capsys.readouterr()
+    child = [r for r in ledger.list_runs(runs) if r["id"] != first[0]["id"]]
+    assert len(child) == 1 and child[0]["parent"] == first[0]["id"]
+    assert ledger.lineage(child[0]["id"], runs) == [child[0]["id"], first[0]["id"]]

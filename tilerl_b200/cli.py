@@ -422,6 +422,11 @@ def cmd_train(args) -> int:
               "prompt_len": args.prompt_len, "eval_gsm8k": args.eval_gsm8k, "eval_mmlu": args.eval_mmlu,
               "eval_n": args.eval_n, "eval_every": args.eval_every, "eval_curve_n": args.eval_curve_n,
               "eval_curve_seed": args.eval_curve_seed}
+    if args.load_adapter and not args.lineage:
+        # a run that starts from a saved adapter descends from the run that wrote it (looked up through the
+        # manifests' artifacts, never guessed from the path)
+        from .ledger import find_run_for_artifact
+        args.lineage = find_run_for_artifact(args.load_adapter, args.runs or runs_dir())
     if not args.force:
         from .ledger import finished_run
         man = finished_run(inputs, args.lineage, args.runs or runs_dir())
