@@ -164,3 +164,15 @@ def test_memory_measure_reports_what_a_live_engine_holds():
     p = memory.plan(cfg, blocks=64, slots=4)
     table = memory.memory_table(p, measured=m, peak=sum(m.values()))
     assert "measured GiB" in table and "transient" in table
+
+
+def test_bench_schema_document_lists_the_registry():
+    import os
+    import re
+    doc = open(os.path.join(os.path.dirname(os.path.dirname(__file__)), "docs", "bench-schema.md")).read()
+    listed = set(re.findall(r"^\| `([a-z0-9_]+)` \| [^|]+ \| (?:higher|lower) \|", doc, re.M))
+    assert listed == set(benchrec.METRICS), listed ^ set(benchrec.METRICS)
+    for name, (unit, hib, keys) in benchrec.METRICS.items():
+        row = next(ln for ln in doc.splitlines() if ln.startswith(f"| `{name}` |"))
+        assert f"| {unit} |" in row and ("higher" if hib else "lower") in row and all(f"`{k}`" in row for k in keys)
+    assert str(benchrec.GATE_RATIO) in doc
