@@ -2,6 +2,7 @@
 ``openai`` and ``anthropic`` SDK clients pointed at it."""
 import asyncio
 import json
+import time
 
 import httpx
 import pytest
@@ -414,3 +415,23 @@ def test_messages_stop_sequence_usage_fields_and_keepalive(served):
                 raw = [ln async for ln in s.aiter_lines()]
             assert any(ln.startswith(": keepalive") for ln in raw) and raw[-2 if raw[-1] == "" else -1] == "data: [DONE]"
     run(go())
+
+
+def test_an_abandoned_keyed_run_finishes_and_its_result_waits_in_the_registry(served):
+    eng, app = served
+    from tilerl_b200.server import core
+    ctx = app.state.ctx
+    job = core.submit(ctx, [{"role": "user", "content": "hi"}], max_tokens=6, thinking=False,
+                      body={"idempotency_key": "left"})
+    core.abandon(ctx, job)                               # the client went away mid-run: the run goes on
+    assert ctx.keys.lookup("left") is not None
+    for _ in range(500):
+        if eng.peek(job.rid)[1]:
+            break
+        time.sleep(0.01)
+    again = core.submit(ctx, [{"role": "user", "content": "hi"}], max_tokens=6, thinking=False,
+                        body={"idempotency_key": "left"})      # the retry: sweeps, then replays
+    assert again.attached and again.rid == job.rid and not ctx.orphans
+    assert job.rid not in eng._reqs                      # the engine no longer holds the finished request
+    res = core.take(ctx, again)
+    assert res is not None and res.finish_reason in ("stop", "length") and eng.kv.used_blocks == 0

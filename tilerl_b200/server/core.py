@@ -34,6 +34,7 @@ class ServeContext:
     keepalive_s: float = float(os.environ.get("TRL_SSE_KEEPALIVE_S", "10"))   # silence before a stream pings
     started: float = field(default_factory=time.time)
     keys: KeyRegistry = field(default_factory=KeyRegistry)   # idempotency_key -> run (see idempotency.py)
+    orphans: List[Tuple[str, int]] = field(default_factory=list)   # keyed runs whose client left before the end
 
 
 def overloaded_body(msg: str = "engine overloaded, retry later") -> Dict[str, Any]:
@@ -80,6 +81,7 @@ def submit(ctx: ServeContext, messages: List[Dict[str, Any]], *, tools=None, thi
                         top_k=s["top_k"], seed=int(seed) if seed is not None else int(time.time_ns() & 0x7FFFFFFF),
                         stop_texts=stops, logprobs=logprobs, max_think_tokens=think_cap)
     key = _key_of(body)
+    sweep_orphans(ctx)
     if key is None:
         return Job(ctx.engine.submit(ids, sp), len(ids), thinking, stops, tools, logprobs)
     with ctx.keys.submit_lock():        # two requests racing with one key start one generation
@@ -119,6 +121,25 @@ def abandon(ctx: ServeContext, job: Job) -> None:
     if job.key is None:
         ctx.engine.cancel(job.rid)
         ctx.engine.take(job.rid)
+    else:
+        ctx.orphans.append((job.key, job.rid))
+        sweep_orphans(ctx)
+
+
+def sweep_orphans(ctx: ServeContext) -> None:
+    """Move the results of finished keyed runs that nobody waits for out of the engine and into the key
+    registry (whose budget bounds them), so that an abandoned run does not stay in the engine's table until
+    a retry that may never come.  Called on every submission and whenever a client leaves."""
+    if not ctx.orphans:
+        return
+    left = []
+    for key, rid in ctx.orphans:
+        toks, done = ctx.engine.peek(rid)
+        if done:
+            ctx.keys.take(key, rid, ctx.engine.take)
+        else:
+            left.append((key, rid))
+    ctx.orphans[:] = left
 
 
 def cancel(ctx: ServeContext, job: Job) -> None:
