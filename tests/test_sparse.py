@@ -93,3 +93,27 @@ def test_sparse_engine_accepts_a_learned_indexer():
     # k covers every page: the learned scorer may order them freely, the result equals dense
     assert eng.generate(p, SamplingParams(max_tokens=6))[0].tokens == want
     assert sp.stats["sparse_ticks"] > 0
+
+
+def test_prefix_store_serves_sparse_requests_and_a_hit_equals_the_cold_run():
+    """Pages never leave the device here, so the prefix store of the dense path is the sparse one too: a
+    follower adopts the publisher's blocks and GDN snapshot, and its page selection reads bounds computed
+    from those very pages."""
+    from tilerl_b200.kv import PrefixStore
+    cfg = tiny_hybrid()
+    p = rand_prompts(cfg, 1, 90, seed=8)[0]
+    sp = SamplingParams(max_tokens=10)
+    mk = lambda: SparseKV(cfg, SparseConfig(top_k=2, window=1, refresh_ticks=2, min_tokens=32))   # noqa: E731
+    cold_eng = make_engine(cfg, blocks=200, sparse=mk())
+    cold = cold_eng.generate([p], sp)[0]
+    mgr = mk()
+    eng = make_engine(cfg, blocks=200, model=cold_eng.model, sparse=mgr)
+    eng.prefix = PrefixStore(eng.kv)
+    first = eng.generate([p], sp)[0]
+    warm = eng.generate([p], sp)[0]
+    assert first.tokens == cold.tokens == warm.tokens
+    assert eng.prefix.hits == 1 and warm.cached_tokens >= 80 and mgr.stats["sparse_ticks"] > 0
+    s = eng.stats()
+    assert s["sparse_ticks"] > 0 and s["sparse"]["sparse_ticks"] == mgr.stats["sparse_ticks"]
+    eng.invalidate_weights()
+    assert eng.kv.used_blocks == 0
