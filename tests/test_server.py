@@ -435,3 +435,20 @@ def test_an_abandoned_keyed_run_finishes_and_its_result_waits_in_the_registry(se
     assert job.rid not in eng._reqs                      # the engine no longer holds the finished request
     res = core.take(ctx, again)
     assert res is not None and res.finish_reason in ("stop", "length") and eng.kv.used_blocks == 0
+
+
+def test_metrics_route_exposes_the_stats_snapshot_as_prometheus_text(served):
+    eng, app = served
+
+    async def go():
+        async with _client(app) as c:
+            await c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4})
+            r = await c.get("/metrics")
+            assert r.status_code == 200 and r.headers["content-type"].startswith("text/plain")
+            return r.text
+    text = run(go())
+    rows = dict(ln.rsplit(" ", 1) for ln in text.strip().splitlines())
+    assert float(rows["tilerl_finished"]) >= 1 and float(rows["tilerl_tokens_generated"]) >= 1
+    assert float(rows['tilerl_memory{row="kv pool"}']) > 0 and rows["tilerl_degraded"] == "0"
+    assert "tilerl_idempotency_retained" in rows and "tilerl_blocks_free" in rows
+    assert all(ln.startswith("tilerl_") for ln in text.strip().splitlines())

@@ -158,6 +158,11 @@ def create_app(engine, tokenizer, model_name: str = "tilerl-b200", *, pace: bool
         from fastapi.staticfiles import StaticFiles
         app.mount("/static", StaticFiles(directory=static_dir), name="static")
 
+    @app.get("/metrics")
+    async def metrics():
+        from fastapi.responses import PlainTextResponse
+        return PlainTextResponse(core.metrics_text(ctx), media_type="text/plain; version=0.0.4")
+
     @app.post("/v1/chat/completions")
     async def chat(request: Request):
         try:

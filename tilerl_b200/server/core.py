@@ -283,3 +283,31 @@ def health(ctx: ServeContext) -> Tuple[int, Dict[str, Any]]:
             "model": ctx.model_name, "uptime_s": round(time.time() - ctx.started, 1),
             "liveness": live, "stats": stats, "idempotency": ctx.keys.stats()}
     return status, body
+
+
+def metrics_text(ctx: ServeContext) -> str:
+    """``GET /metrics``: the numeric part of ``Engine.stats()`` in the Prometheus text exposition format
+    (gauges named ``tilerl_<key>``; nested rows such as the memory table become a ``row`` label).  The
+    reference exposes its stats through ``/health`` only; this is the same snapshot for a scraper."""
+    live = ctx.engine.liveness()
+    lines = []
+
+    def emit(name: str, value, labels: str = "") -> None:
+        if isinstance(value, bool):
+            value = int(value)
+        if isinstance(value, (int, float)):
+            lines.append(f"tilerl_{name}{labels} {value}")
+
+    for k, v in sorted(ctx.engine.stats().items()):
+        if isinstance(v, dict):
+            for row, x in sorted(v.items()):
+                label = str(row).replace("\\", "/").replace('"', "'")
+                emit(k, x, f'{{row="{label}"}}')
+        else:
+            emit(k, v)
+    emit("last_progress_age_seconds", round(float(live["last_progress_age_s"]), 3))
+    emit("degraded", live["degraded"] is not None)
+    emit("uptime_seconds", round(time.time() - ctx.started, 1))
+    for k, v in sorted(ctx.keys.stats().items()):
+        emit(f"idempotency_{k}", v)
+    return "\n".join(lines) + "\n"
