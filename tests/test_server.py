@@ -452,3 +452,19 @@ def test_metrics_route_exposes_the_stats_snapshot_as_prometheus_text(served):
     assert float(rows['tilerl_memory{row="kv pool"}']) > 0 and rows["tilerl_degraded"] == "0"
     assert "tilerl_idempotency_retained" in rows and "tilerl_blocks_free" in rows
     assert all(ln.startswith("tilerl_") for ln in text.strip().splitlines())
+
+
+def test_messages_count_tokens_matches_what_a_request_is_charged(served):
+    eng, app = served
+
+    async def go():
+        async with _client(app) as c:
+            body = {"model": "m", "system": "be brief", "messages": [{"role": "user", "content": "how many tokens is this?"}]}
+            n = (await c.post("/v1/messages/count_tokens", json=body)).json()["input_tokens"]
+            done = eng.counters["finished"]
+            j = (await c.post("/v1/messages", json={**body, "max_tokens": 4})).json()
+            assert n == j["usage"]["input_tokens"] + j["usage"]["cache_read_input_tokens"] and n > 10
+            assert eng.counters["finished"] == done + 1                     # counting generated nothing
+            bad = await c.post("/v1/messages/count_tokens", json={"model": "m", "messages": []})
+            assert bad.status_code == 400 and bad.json()["type"] == "error"
+    run(go())

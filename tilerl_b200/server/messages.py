@@ -127,6 +127,20 @@ def mount(app, ctx: core.ServeContext) -> None:
     def err(status: int, typ: str, msg: str):
         return JSONResponse({"type": "error", "error": {"type": typ, "message": msg}}, status_code=status)
 
+    @app.post("/v1/messages/count_tokens")
+    async def count_tokens(request: Request):
+        """Prompt tokens of a messages body, rendered exactly as ``/v1/messages`` would render it; nothing is
+        generated (the vendor's route of that name: agent clients call it to budget their context)."""
+        try:
+            body = await request.json()
+            n = _normalise({**body, "max_tokens": body.get("max_tokens", 1)})
+            text = P.render_chat(to_chat_messages(body), tools=n["tools"], enable_thinking=n["thinking"])
+            return {"input_tokens": len(ctx.tokenizer.encode(text))}
+        except P.BadRequest as e:
+            return err(400, "invalid_request_error", str(e))
+        except (ValueError, json.JSONDecodeError) as e:
+            return err(400, "invalid_request_error", str(e))
+
     @app.post("/v1/messages")
     async def messages(request: Request):
         try:
